@@ -1,0 +1,61 @@
+"""ctypes binding of libb200nodes.so.  The library is required: there is no fallback path."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200nodes.so")
+
+vp, i32, f32, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+
+
+class MoeLists(C.Structure):
+    _fields_ = [(n, vp) for n in ("counts", "offsets", "row_of_pair", "slot_of_row", "wt_of_row", "blk_expert",
+                                  "blk_row0", "blk_rows", "nblocks")]
+
+
+class MoeWeights(C.Structure):
+    _fields_ = [(n, vp) for n in ("w13", "s13", "w2", "s2", "sh13", "shs13", "sh2", "shs2")]
+
+
+# name -> (restype, argtypes); mirrors include/b200nodes.h
+PROTOTYPES = {
+    "b200_abi_version": (i32, []),
+    "b200_last_error": (C.c_char_p, []),
+    "b200_router": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
+    "b200_moe_max_blocks": (i32, [i32, i32, i32, i32]),
+    "b200_moe_build_lists": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, i32, C.POINTER(MoeLists), vp]),
+    "b200_moe_w8a8_workspace_bytes": (sz, [i32, i32, i32, i32]),
+    "b200_moe_w8a8": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(MoeWeights), C.POINTER(MoeLists), vp, vp, sz, vp,
+                            vp, vp, vp]),
+    "b200_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
+    "b200_gdn_verify": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, f32, i32, vp, vp, vp]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m bundles_b200.build` (nvcc, sm_100a). "
+                "There is no CPU or PyTorch fallback.")
+        _lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(_lib, name)
+            fn.restype = res
+            fn.argtypes = args
+    return _lib
+
+
+class B200Error(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib().b200_last_error().decode(errors="replace")
+        raise B200Error(f"{what} failed with code {rc}: {msg}")

@@ -1,0 +1,382 @@
+// Gated DeltaNet speculative verify: conv + SiLU, q/k L2 norm, gates, delta-rule recurrence over
+// the 4 draft tokens in closed form, gated RMSNorm, and the explicit state / conv-state write-back
+// at the accepted length.
+//
+// Replaces qk_gdn_verify.cu:293 gdn_verify_kernel (host glue gdn_fused.py:37-57).  The reference
+// keeps a read-only fp32 checkpoint plus a (d, k, g) ring; the target carries the state explicitly,
+// so a unit reads its 128 x 128 fp32 tile, and writes it back advanced by accepted[b] tokens.
+// The window algebra is the reference's (qk_gdn_verify.cu:633-762):
+//   hq_s = S q_s, hk_s = S k_s;  R_s = beta_s (v_s - e^{G_s} hk_s);  D = (I + A)^-1 R with
+//   A_ij = beta_i e^{G_i - G_j} k_i.k_j (i > j);  o_s = e^{G_s} hq_s + sum_{i<=s} D_i e^{G_s - G_i} k_i.q_s;
+//   S_n = e^{G_{n-1}} S + sum_{i<n} e^{G_{n-1} - G_i} D_i k_i^T.
+// All dot products are fp32 FMAs (the reference uses TF32 MMAs, qk_gdn_verify.cu:173-179).
+//
+// HBM-bound: 64 KB in and (when accepted > 0) 64 KB out per (sequence, value head).  One CTA per
+// unit; the tile moves with one bulk copy each way (cp.async.bulk), three CTAs share an SM so the
+// copies of one overlap the arithmetic of the others.  The two value heads of a key head run as a
+// 2-CTA cluster: both read the q/k conv state, meet at a cluster barrier, then rank 0 rolls it.
+#include "common.cuh"
+#include "host.h"
+
+namespace b200 {
+
+constexpr int G_HK = 16, G_HV = 32, G_D = 128, G_NT = 4;
+constexpr int G_QDIM = G_HK * G_D;             // 2048
+constexpr int G_CONV = 2 * G_QDIM + G_HV * G_D;  // 8192
+constexpr int G_ZDIM = G_HV * G_D;             // 4096
+constexpr int G_THREADS = 256;
+constexpr uint32_t G_TILE_BYTES = G_D * G_D * 4;
+
+struct GdnSmem {
+  float S[G_D * G_D];       // state tile, S[v][k]
+  float q[G_NT][G_D];       // normalised, scaled q
+  float k[G_NT][G_D];       // normalised k
+  float v[G_NT][G_D];       // conv v; later c_i * D_i for the state update
+  float hq[G_D][G_NT];      // S q_s
+  float hk[G_D][G_NT];      // S k_s
+  float kk[G_NT][G_NT], kq[G_NT][G_NT];
+  float g[G_NT], beta[G_NT], G[G_NT];
+  float red[8][G_NT];
+  float nrm[2][G_NT][4];
+  uint64_t bar;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+// one channel: window [s0 s1 s2 x0..x3]; y[s] = bf16(silu(sum of bf16-rounded tap products, oldest first))
+// (conv_tap, qk_gdn_verify.cu:240-247); rolls the conv state by `n_acc` tokens if `write`.
+__device__ __forceinline__ void conv_channel(const bf16* __restrict__ mixed_b, bf16* __restrict__ cs_b,
+                                             const bf16* __restrict__ conv_w, int ch, int n_acc, bool write,
+                                             float (&y)[G_NT]) {
+  bf16 win[G_NT + 3];
+  win[0] = cs_b[ch * 3 + 0];
+  win[1] = cs_b[ch * 3 + 1];
+  win[2] = cs_b[ch * 3 + 2];
+#pragma unroll
+  for (int s = 0; s < G_NT; ++s) win[3 + s] = mixed_b[static_cast<size_t>(s) * G_CONV + ch];
+  const uint2 wr = *reinterpret_cast<const uint2*>(conv_w + ch * 4);
+  const bf16 w0 = __ushort_as_bfloat16(wr.x & 0xffff), w1 = __ushort_as_bfloat16(wr.x >> 16);
+  const bf16 w2 = __ushort_as_bfloat16(wr.y & 0xffff), w3 = __ushort_as_bfloat16(wr.y >> 16);
+#pragma unroll
+  for (int s = 0; s < G_NT; ++s) {
+    float acc = bf2f(__hmul(win[s], w0));
+    acc += bf2f(__hmul(win[s + 1], w1));
+    acc += bf2f(__hmul(win[s + 2], w2));
+    acc += bf2f(__hmul(win[s + 3], w3));
+    y[s] = rbf(acc / (1.f + __expf(-acc)));
+  }
+  if (write && n_acc > 0) {
+    bf16 a = win[0], b = win[1], c = win[2];
+#pragma unroll
+    for (int n = 1; n <= G_NT; ++n)
+      if (n_acc == n) {
+        a = win[n];
+        b = win[n + 1];
+        c = win[n + 2];
+      }
+    cs_b[ch * 3 + 0] = a;
+    cs_b[ch * 3 + 1] = b;
+    cs_b[ch * 3 + 2] = c;
+  }
+}
+
+struct GdnArgs {
+  const bf16* mixed;
+  const bf16* z;
+  const bf16* a;
+  const bf16* b;
+  bf16* conv_state;
+  const bf16* conv_w;
+  const float* a_log;
+  const float* dt_bias;
+  float* state;
+  const int32_t* accepted;
+  const bf16* norm_w;
+  float eps;
+  int B;
+  bf16* out;
+  int32_t* status;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS) gdn_verify_kernel(const GdnArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  GdnSmem& sm = *reinterpret_cast<GdnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int hv = blockIdx.x, hk = hv >> 1, b = blockIdx.y;
+  int n_acc = p.accepted[b];
+  n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
+  float* gstate = p.state + (static_cast<size_t>(b) * G_HV + hv) * (G_D * G_D);
+
+  if (tid == 0) {
+    mbar_init(&sm.bar, 1);
+    sm.abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    mbar_expect_tx(&sm.bar, G_TILE_BYTES);
+    bulk_load(sm.S, gstate, G_TILE_BYTES, &sm.bar);
+  }
+
+  // ---- conv + SiLU on q, k (key head hk) and v (value head hv); L2 norms ----
+  const bf16* mixed_b = p.mixed + static_cast<size_t>(b) * G_NT * G_CONV;
+  bf16* cs_b = p.conv_state + static_cast<size_t>(b) * G_CONV * 3;
+  {
+    float y[G_NT];
+    const int c = tid & 127;
+    const bool is_k = tid >= 128;
+    // q/k conv state is shared by the cluster pair: read now, rank 0 rolls it after the barrier
+    conv_channel(mixed_b, cs_b, p.conv_w, (is_k ? G_QDIM : 0) + hk * G_D + c, 0, false, y);
+    float ss[G_NT];
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) ss[s] = y[s] * y[s];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) ss[s] += __shfl_xor_sync(FULL_MASK, ss[s], o);
+    if (lane == 0)
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) sm.nrm[is_k][s][warp & 3] = ss[s];
+    __syncthreads();
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) {
+      const float n = sm.nrm[is_k][s][0] + sm.nrm[is_k][s][1] + sm.nrm[is_k][s][2] + sm.nrm[is_k][s][3];
+      const float r = (1.f / sqrtf(n + 1e-6f)) * (is_k ? 1.f : 0.08838834764831845f);  // d_k^-0.5
+      (is_k ? sm.k : sm.q)[s][c] = y[s] * r;
+    }
+  }
+  cluster_sync();  // both value heads of the key head hold their q/k windows
+  if ((hv & 1) == 0 && n_acc > 0) {
+    float y[G_NT];
+    const int c = tid & 127;
+    conv_channel(mixed_b, cs_b, p.conv_w, (tid >= 128 ? G_QDIM : 0) + hk * G_D + c, n_acc, true, y);
+  }
+  if (tid < 128) {
+    float y[G_NT];
+    conv_channel(mixed_b, cs_b, p.conv_w, 2 * G_QDIM + hv * G_D + tid, n_acc, true, y);
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) sm.v[s][tid] = y[s];
+  } else if (tid < 128 + G_NT) {
+    // gates (qk_gdn_verify.cu:616-631)
+    const int s = tid - 128;
+    const float av = bf2f(p.a[(static_cast<size_t>(b) * G_NT + s) * G_HV + hv]);
+    const float bv = bf2f(p.b[(static_cast<size_t>(b) * G_NT + s) * G_HV + hv]);
+    const float xg = av + p.dt_bias[hv];
+    const float sp = xg <= 20.f ? log1pf(expf(xg)) : xg;
+    sm.g[s] = -expf(p.a_log[hv]) * sp;
+    sm.beta[s] = 1.f / (1.f + expf(-bv));
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float run = 0.f;
+    for (int s = 0; s < G_NT; ++s) {
+      run += sm.g[s];
+      sm.G[s] = run;
+    }
+  }
+  // k_i . k_j and k_i . q_j: 32 dots of length 128, 4 per warp
+  for (int d = warp * 4; d < warp * 4 + 4; ++d) {
+    const int i = (d >> 2) & 3, j = d & 3;
+    const float* other = d < 16 ? sm.k[j] : sm.q[j];
+    float acc = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc = fmaf(sm.k[i][lane + 32 * c], other[lane + 32 * c], acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(FULL_MASK, acc, o);
+    if (lane == 0) (d < 16 ? sm.kk : sm.kq)[i][j] = acc;
+  }
+
+  // ---- the state tile ----
+  const bool landed = mbar_wait(&sm.bar, 0, &sm.abort_flag, p.status, ST_WAIT_STATE);
+  __syncthreads();
+  if (!landed || sm.abort_flag) {
+    // the copy may still be in flight: give it a bounded grace period, then leave without touching memory
+    const unsigned long long t0 = globaltimer();
+    while (tid == 0 && !mbar_try(&sm.bar, 0) && globaltimer() - t0 < 20000000ull) {
+    }
+    return;
+  }
+
+  // thread = 4 state rows x one of 8 interleaved k slices (float4 chunks ks + 8 i)
+  const int rg = tid >> 3, ks = tid & 7;
+  {
+    float acc[4][8];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int x = 0; x < 8; ++x) acc[r][x] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c4 = (ks + 8 * i) * 4;
+      float4 sv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) sv[r] = *reinterpret_cast<const float4*>(&sm.S[(rg * 4 + r) * G_D + c4]);
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        const float4 vv = *reinterpret_cast<const float4*>(x < 4 ? &sm.q[x][c4] : &sm.k[x - 4][c4]);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          acc[r][x] = fmaf(sv[r].x, vv.x, acc[r][x]);
+          acc[r][x] = fmaf(sv[r].y, vv.y, acc[r][x]);
+          acc[r][x] = fmaf(sv[r].z, vv.z, acc[r][x]);
+          acc[r][x] = fmaf(sv[r].w, vv.w, acc[r][x]);
+        }
+      }
+    }
+    // transposing reduction over the 8 slice lanes: 32 -> 16 -> 8 -> 4 values per lane
+    float v16[16], v8[8], v4[4];
+    const bool b2 = ks & 4, b1 = ks & 2, b0 = ks & 1;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float lo = acc[i >> 3][i & 7], hi = acc[2 + (i >> 3)][i & 7];
+      const float send = b2 ? lo : hi, keep = b2 ? hi : lo;
+      v16[i] = keep + __shfl_xor_sync(FULL_MASK, send, 4);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float lo = v16[i], hi = v16[8 + i];
+      const float send = b1 ? lo : hi, keep = b1 ? hi : lo;
+      v8[i] = keep + __shfl_xor_sync(FULL_MASK, send, 2);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float lo = v8[i], hi = v8[4 + i];
+      const float send = b0 ? lo : hi, keep = b0 ? hi : lo;
+      v4[i] = keep + __shfl_xor_sync(FULL_MASK, send, 1);
+    }
+    // lane (b2 b1 b0) now holds row 2*b2 + b1 of its group, vectors 4*b0 .. 4*b0 + 3 (q first, then k)
+    const int row = rg * 4 + (ks >> 1);
+    *reinterpret_cast<float4*>(b0 ? sm.hk[row] : sm.hq[row]) = make_float4(v4[0], v4[1], v4[2], v4[3]);
+  }
+  __syncthreads();
+
+  // ---- per value row: R, D = (I + A)^-1 R, outputs; gated RMSNorm ----
+  float o[G_NT] = {0.f, 0.f, 0.f, 0.f};
+  if (tid < G_D) {
+    const int v = tid;
+    float G[G_NT], bt[G_NT], eG[G_NT], R[G_NT], D[G_NT];
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) {
+      G[s] = sm.G[s];
+      bt[s] = sm.beta[s];
+      eG[s] = __expf(G[s]);
+    }
+    const float4 hq4 = *reinterpret_cast<const float4*>(sm.hq[v]);
+    const float4 hk4 = *reinterpret_cast<const float4*>(sm.hk[v]);
+    const float hq[G_NT] = {hq4.x, hq4.y, hq4.z, hq4.w}, hkv[G_NT] = {hk4.x, hk4.y, hk4.z, hk4.w};
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) R[s] = bt[s] * (sm.v[s][v] - eG[s] * hkv[s]);
+#pragma unroll
+    for (int i = 0; i < G_NT; ++i) {
+      float d = R[i];
+#pragma unroll
+      for (int j = 0; j < i; ++j) d = fmaf(-(bt[i] * __expf(G[i] - G[j]) * sm.kk[i][j]), D[j], d);
+      D[i] = d;
+    }
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) {
+      float acc = eG[s] * hq[s];
+#pragma unroll
+      for (int i = 0; i <= s; ++i) acc = fmaf(D[i] * __expf(G[s] - G[i]), sm.kq[i][s], acc);
+      o[s] = rbf(acc);  // the core output is stored in bf16 before the norm (qk_gdn_verify.cu:761)
+    }
+    __syncwarp();
+    // c_i D_i for the state update replaces v (each thread only touches its own column)
+#pragma unroll
+    for (int i = 0; i < G_NT; ++i) sm.v[i][v] = i < n_acc ? D[i] * __expf(G[n_acc - 1] - G[i]) : 0.f;
+  }
+  {
+    float ss[G_NT];
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) ss[s] = o[s] * o[s];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) ss[s] += __shfl_xor_sync(FULL_MASK, ss[s], off);
+    if (lane == 0)
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) sm.red[warp][s] = ss[s];
+  }
+  __syncthreads();
+  if (tid < G_D) {
+    const float nw = bf2f(p.norm_w[tid]);
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) {
+      const float var = (sm.red[0][s] + sm.red[1][s] + sm.red[2][s] + sm.red[3][s]) * (1.f / G_D);
+      const float rstd = rsqrtf(var + p.eps);
+      const size_t idx = (static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv * G_D + tid;
+      const float zz = bf2f(p.z[idx]);
+      p.out[idx] = f2bf(o[s] * rstd * nw * (zz * (1.f / (1.f + __expf(-zz)))));
+    }
+  }
+
+  // ---- state after n_acc tokens, written back in one bulk copy ----
+  if (n_acc > 0) {
+    const float decay = __expf(sm.G[n_acc - 1]);
+    float cd[4][G_NT];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int i = 0; i < G_NT; ++i) cd[r][i] = sm.v[i][rg * 4 + r];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c4 = (ks + 8 * i) * 4;
+      float4 kv[G_NT];
+#pragma unroll
+      for (int t = 0; t < G_NT; ++t) kv[t] = *reinterpret_cast<const float4*>(&sm.k[t][c4]);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        float4* sp = reinterpret_cast<float4*>(&sm.S[(rg * 4 + r) * G_D + c4]);
+        float4 sv = *sp;
+        sv.x *= decay; sv.y *= decay; sv.z *= decay; sv.w *= decay;
+#pragma unroll
+        for (int t = 0; t < G_NT; ++t) {
+          sv.x = fmaf(cd[r][t], kv[t].x, sv.x);
+          sv.y = fmaf(cd[r][t], kv[t].y, sv.y);
+          sv.z = fmaf(cd[r][t], kv[t].z, sv.z);
+          sv.w = fmaf(cd[r][t], kv[t].w, sv.w);
+        }
+        *sp = sv;
+      }
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0) {
+      bulk_store(gstate, sm.S, G_TILE_BYTES);
+      bulk_commit();
+      bulk_wait_all();
+    }
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, const void* b, void* conv_state,
+                               const void* conv_w, const float* a_log, const float* dt_bias, float* state,
+                               const int32_t* accepted, const void* norm_w, float eps, int B, void* out,
+                               int32_t* status, void* stream) {
+  if (!mixed || !z || !a || !b || !conv_state || !conv_w || !a_log || !dt_bias || !state || !accepted || !norm_w || !out)
+    return fail(B200_E_ARG, "b200_gdn_verify: null pointer");
+  if (B < 0 || B > 65535) return fail(B200_E_ARG, "b200_gdn_verify: B=%d out of range", B);
+  if (reinterpret_cast<uintptr_t>(state) & 15) return fail(B200_E_ALIGN, "b200_gdn_verify: state must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(conv_w) & 7) return fail(B200_E_ALIGN, "b200_gdn_verify: conv_w must be 8-byte aligned");
+  if (B == 0) return 0;
+  GdnArgs p{static_cast<const bf16*>(mixed), static_cast<const bf16*>(z), static_cast<const bf16*>(a),
+            static_cast<const bf16*>(b), static_cast<bf16*>(conv_state), static_cast<const bf16*>(conv_w), a_log,
+            dt_bias, state, accepted, static_cast<const bf16*>(norm_w), eps, B, static_cast<bf16*>(out), status};
+  const int smem = static_cast<int>(sizeof(GdnSmem)) + 128;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaFuncSetAttribute(gdn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    attr_done[dev] = true;
+  }
+  gdn_verify_kernel<<<dim3(G_HV, B), G_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  return launch_status("b200_gdn_verify");
+}

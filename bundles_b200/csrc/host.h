@@ -1,0 +1,51 @@
+// Host-side helpers shared by the C-ABI translation units: error reporting, the device view of the
+// routing lists, and the TMA tensor-map encoder (looked up through the runtime so that the library
+// loads on a machine without a CUDA driver).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/b200nodes.h"
+
+namespace b200 {
+
+struct MoeLists {
+  int32_t* counts;
+  int32_t* offsets;
+  int32_t* row_of_pair;
+  int32_t* slot_of_row;
+  float* wt_of_row;
+  int32_t* blk_expert;
+  int32_t* blk_row0;
+  int32_t* blk_rows;
+  int32_t* nblocks;
+};
+
+char* last_error_buffer();  // thread-local, 512 bytes
+
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+inline int launch_status(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return 0;
+  return fail(static_cast<int>(e), "%s: launch failed: %s", what, cudaGetErrorString(e));
+}
+
+// 2-D tensor map over a row-major byte matrix [rows, row_bytes] (element type uint8), box
+// [box_rows, 128 bytes], 128-byte swizzle, zero fill outside the matrix.
+int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                       const char* what);
+
+int sm_count();  // SMs of the current device (cached per device)
+
+}  // namespace b200

@@ -1,0 +1,537 @@
+// MoE block: activation quantise + permute, grouped expert GEMMs on tcgen05 tensor cores with
+// TMEM accumulators and TMA-fed shared-memory rings, SwiGLU / unpermute epilogues, combine.
+//
+// Replaces the reference's decode MoE (i8x_decode.py:528-576 moe_row_batch; qk_moe_up16.cu:139
+// up_kernel, qk_moe_dn16.cu:136 down_kernel, qk_route.cu:686 combine_norm_kernel) at the target
+// formats (int8 W8A8: qk_moe_prefill_i8.cu:3646-3655,4061-4071; fp8 128x128 block scales).
+//
+// GEMM orientation (the reference's "weights as the MMA M side", qk_moe_up16.cu:9): one UMMA is
+// M = 128 weight rows x N = 16..128 tokens of one expert x K = 32 bytes.  Weights arrive by 2-D TMA
+// straight from the expert tensors ([rows, K] bytes, 128-byte swizzle); tokens were permuted into
+// expert-sorted rows by the quantise kernel, so the token operand is a plain 2-D TMA box as well.
+// A CTA is persistent and walks (block, 128-row weight tile) pairs: warp 0 issues TMA, warp 1 issues
+// MMAs and owns the TMEM allocation, warps 2-5 drain TMEM (each its own 32-lane quadrant).
+// At decode sizes this path is bound by the HBM stream of expert weights, not by the tensor pipe.
+#include "common.cuh"
+#include "host.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------------------------------
+// activation quantise + permute (int8): one CTA per token
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(FULL_MASK, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = lane < nw ? red[lane] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r = fmaxf(r, __shfl_xor_sync(FULL_MASK, r, o));
+  __syncthreads();
+  return r;
+}
+
+// round half away from zero, clamp to +-127 (qwen36_lmhead8/w8a8.py:15-22)
+__device__ __forceinline__ int q8(float x, float safe) {
+  const float v = __fdiv_rn(x, safe);
+  float r = v >= 0.f ? floorf(v + 0.5f) : -floorf(0.5f - v);
+  r = fminf(fmaxf(r, -127.f), 127.f);
+  return static_cast<int>(r);
+}
+
+// x bf16 [T, H] -> int8 rows written at every sorted row of the token (its K routed rows and its
+// shared-expert row), scale per row.  256 threads, 8 elements per thread per pass.
+__global__ void __launch_bounds__(256) quant_permute_i8_kernel(const bf16* __restrict__ x, int T, int H, int K,
+                                                               const int32_t* __restrict__ row_of_pair,
+                                                               int with_shared, int8_t* __restrict__ xq,
+                                                               float* __restrict__ xs) {
+  __shared__ float red[8];
+  __shared__ int rows[40];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  if (tid < K) rows[tid] = row_of_pair[t * K + tid];
+  if (tid == K) rows[K] = with_shared ? T * K + t : -1;
+  const bf16* xr = x + static_cast<size_t>(t) * H;
+  float amax = 0.f;
+  for (int c = tid * 8; c < H; c += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + c);
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf_lo(v.x)), fabsf(bf_hi(v.x))), fmaxf(fabsf(bf_lo(v.y)), fabsf(bf_hi(v.y)))));
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf_lo(v.z)), fabsf(bf_hi(v.z))), fmaxf(fabsf(bf_lo(v.w)), fabsf(bf_hi(v.w)))));
+  }
+  amax = block_max(amax, red);
+  const float scale = __fdiv_rn(amax, 127.f);
+  const float safe = amax > 0.f ? scale : 1.f;
+  for (int c = tid * 8; c < H; c += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + c);
+    const float f[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo |= (static_cast<uint32_t>(q8(f[i], safe)) & 0xffu) << (8 * i);
+      hi |= (static_cast<uint32_t>(q8(f[4 + i], safe)) & 0xffu) << (8 * i);
+    }
+    for (int j = 0; j <= K; ++j) {
+      const int row = rows[j];
+      if (row >= 0) *reinterpret_cast<uint2*>(xq + static_cast<size_t>(row) * H + c) = make_uint2(lo, hi);
+    }
+  }
+  if (tid <= K && rows[tid] >= 0) xs[rows[tid]] = scale;
+}
+
+// h bf16 [rows, I] -> int8 + per-row scale (the re-quantisation before the down GEMM,
+// qk_moe_prefill_i8.cu:4061-4066).  One warp per sorted row; rows without a slot are skipped.
+__global__ void __launch_bounds__(256) quant_rows_i8_kernel(const bf16* __restrict__ h, int rows, int I,
+                                                            const int32_t* __restrict__ slot_of_row,
+                                                            int8_t* __restrict__ hq, float* __restrict__ hs) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows || slot_of_row[row] < 0) return;
+  const bf16* hr = h + static_cast<size_t>(row) * I;
+  float amax = 0.f;
+  for (int c = lane * 8; c < I; c += 256) {
+    const uint4 v = *reinterpret_cast<const uint4*>(hr + c);
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf_lo(v.x)), fabsf(bf_hi(v.x))), fmaxf(fabsf(bf_lo(v.y)), fabsf(bf_hi(v.y)))));
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf_lo(v.z)), fabsf(bf_hi(v.z))), fmaxf(fabsf(bf_lo(v.w)), fabsf(bf_hi(v.w)))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(FULL_MASK, amax, o));
+  const float scale = __fdiv_rn(amax, 127.f);
+  const float safe = amax > 0.f ? scale : 1.f;
+  for (int c = lane * 8; c < I; c += 256) {
+    const uint4 v = *reinterpret_cast<const uint4*>(hr + c);
+    const float f[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo |= (static_cast<uint32_t>(q8(f[i], safe)) & 0xffu) << (8 * i);
+      hi |= (static_cast<uint32_t>(q8(f[4 + i], safe)) & 0xffu) << (8 * i);
+    }
+    *reinterpret_cast<uint2*>(hq + static_cast<size_t>(row) * I + c) = make_uint2(lo, hi);
+  }
+  if (lane == 0) hs[row] = scale;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// grouped int8 GEMM on tcgen05 (kind::i8), swap-AB
+// ---------------------------------------------------------------------------------------------------
+struct GemmArgs {
+  MoeLists L;
+  int E_local;      // local routed experts; block expert == E_local means the shared expert
+  int mtiles;       // 128-row weight tiles per expert (up: I/128, down: H/128)
+  int ksteps;       // K / 128
+  int w_rows;       // weight rows per expert (up: 2I, down: H)
+  int I, H;
+  int total_rows;   // T * (K + 1)
+  const float* s_w;     // routed weight scales [E_local, w_rows]
+  const float* s_w_sh;  // shared-expert weight scales [w_rows]
+  const float* a_scale; // activation scale per sorted row
+  bf16* h_out;          // up: SwiGLU output, sorted rows [total_rows, I]
+  bf16* cache;          // down: [total_rows, H] by slot
+  int32_t* dbg_acc;     // up: raw accumulators by slot [total_rows, 2I] or null
+  bf16* dbg_h;          // up: h by slot or null
+  int32_t* status;
+};
+
+constexpr int TILE_BYTES = 128 * 128;   // one 128-row x 128-byte operand tile
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+template <bool UP>
+struct GemmCfg {
+  static constexpr int NA = UP ? 2 : 1;                      // weight tiles per stage (gate + up)
+  static constexpr int STAGE = NA * TILE_BYTES + TILE_BYTES;  // + token tile (<= 128 rows)
+  static constexpr int STAGES = UP ? 4 : 6;
+  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <bool UP>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWsh,
+                   const __grid_constant__ CUtensorMap tmX, const GemmArgs p) {
+  using C = GemmCfg<UP>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* tfull = empty + C::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmWsh);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  int nblocks = p.L.nblocks[0];
+  const int ntiles = nblocks * p.mtiles;
+
+  // every role decodes a tile the same way; a malformed list entry is skipped by all of them
+  auto decode = [&](int tile, int& e, int& row0, int& n, int& mt) -> bool {
+    const int blk = tile / p.mtiles;
+    mt = tile - blk * p.mtiles;
+    e = p.L.blk_expert[blk];
+    row0 = p.L.blk_row0[blk];
+    n = p.L.blk_rows[blk];
+    return e >= 0 && e <= p.E_local && n >= 1 && n <= 128 && row0 >= 0 && row0 + n <= p.total_rows;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
+        int e, row0, n, mt;
+        if (!decode(tile, e, row0, n, mt)) continue;
+        const int nb16 = (n + 15) >> 4;
+        const CUtensorMap* mapW = (e == p.E_local) ? &tmWsh : &tmW;
+        const int wrow = (e == p.E_local ? 0 : e * p.w_rows) + mt * 128;
+        for (int ks = 0; ks < p.ksteps; ++ks) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * C::STAGE;
+          uint8_t* sB = sA + C::NA * TILE_BYTES;
+          mbar_expect_tx(&full[stage], C::NA * TILE_BYTES + nb16 * 2048);
+          tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
+          if (UP) tma_load_2d(sA + TILE_BYTES, mapW, ks * 128, wrow + p.I, &full[stage]);
+          for (int b = 0; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
+          ++issued;
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // abandoned: give the copies already in flight a bounded time to land before the CTA exits
+        const unsigned long long t0 = globaltimer();
+        const int back = issued < C::STAGES ? issued : C::STAGES;
+        for (int i = 1; i <= back; ++i) {
+          int s = stage - i;
+          uint32_t ph = phase;
+          if (s < 0) {
+            s += C::STAGES;
+            ph ^= 1u;
+          }
+          while (!mbar_try(&full[s], ph) && globaltimer() - t0 < 20000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
+        int e, row0, n, mt;
+        if (!decode(tile, e, row0, n, mt)) continue;
+        const int buf = it & 1;
+        const uint32_t bphase = (it >> 1) & 1;
+        ++it;
+        if (!mbar_wait(&tempty[buf], bphase ^ 1u, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t N = static_cast<uint32_t>((n + 15) & ~15);
+        const uint32_t idesc = umma_idesc(UMMA_C_S32, UMMA_AB_INT8, N);
+        const uint32_t d0 = tmem_base + buf * 256;
+        for (int ks = 0; ks < p.ksteps; ++ks) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, ST_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * C::STAGE);
+          const uint32_t sB = sA + C::NA * TILE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t db = umma_desc_sw128(sB + kk * 32);
+            const uint32_t acc = (ks | kk) != 0;
+            tc_mma_i8(d0, umma_desc_sw128(sA + kk * 32), db, idesc, acc);
+            if (UP) tc_mma_i8(d0 + 128, umma_desc_sw128(sA + TILE_BYTES + kk * 32), db, idesc, acc);
+          }
+          tc_commit(&empty[stage]);
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tc_commit(&tfull[buf]);
+      }
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, TMEM lane quadrant = warp % 4 ----------------
+    const int q = warp & 3;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+      int e, row0, n, mt;
+      if (!decode(tile, e, row0, n, mt)) {
+        if (lane == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_LIST);
+        continue;
+      }
+      const int buf = it & 1;
+      const uint32_t bphase = (it >> 1) & 1;
+      ++it;
+      if (!mbar_wait(&tfull[buf], bphase, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + buf * 256 + (static_cast<uint32_t>(q * 32) << 16);
+      const int r = mt * 128 + q * 32 + lane;  // weight row inside the expert (up: channel of I; down: column of H)
+      const bool shared_e = (e == p.E_local);
+      if (UP) {
+        const float* sw = shared_e ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * p.w_rows;
+        const float wsg = sw[r], wsu = sw[p.I + r];
+        for (int c0 = 0; c0 < n; c0 += 16) {
+          uint32_t rg[16], ru[16];
+          tmem_ld16(taddr + c0, rg);
+          tmem_ld16(taddr + 128 + c0, ru);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int col = c0 + i;
+            if (col < n) {
+              const int row = row0 + col;
+              const float xs = p.a_scale[row];
+              const float g = rbf(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(rg[i])), xs), wsg));
+              const float u = rbf(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ru[i])), xs), wsu));
+              const bf16 hv = f2bf(__fmul_rn(__fdiv_rn(g, 1.f + __expf(-g)), u));
+              p.h_out[static_cast<size_t>(row) * p.I + r] = hv;
+              if (p.dbg_acc || p.dbg_h) {
+                const int slot = p.L.slot_of_row[row];
+                if (slot >= 0 && slot < p.total_rows) {
+                  if (p.dbg_acc) {
+                    p.dbg_acc[static_cast<size_t>(slot) * 2 * p.I + r] = static_cast<int>(rg[i]);
+                    p.dbg_acc[static_cast<size_t>(slot) * 2 * p.I + p.I + r] = static_cast<int>(ru[i]);
+                  }
+                  if (p.dbg_h) p.dbg_h[static_cast<size_t>(slot) * p.I + r] = hv;
+                }
+              }
+            }
+          }
+        }
+      } else {
+        const float ws = shared_e ? p.s_w_sh[r] : p.s_w[static_cast<size_t>(e) * p.w_rows + r];
+        for (int c0 = 0; c0 < n; c0 += 16) {
+          uint32_t ra[16];
+          tmem_ld16(taddr + c0, ra);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int col = c0 + i;
+            if (col < n) {
+              const int row = row0 + col;
+              const int slot = p.L.slot_of_row[row];
+              if (slot >= 0 && slot < p.total_rows) {
+                const float y = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ra[i])), p.a_scale[row]), ws);
+                p.cache[static_cast<size_t>(slot) * p.H + r] = f2bf(__fmul_rn(y, p.L.wt_of_row[row]));
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[buf]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// combine
+// ---------------------------------------------------------------------------------------------------
+// One CTA per token, 256 threads, 8 columns per thread per pass.  gate = sigmoid(x . gate_w) in fp32
+// (i8x_decode.py:436-438); out = bf16(sum of the K routed rows in slot order + gate * shared row).
+__global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict__ cache, const bf16* __restrict__ x,
+                                                          const bf16* __restrict__ gate_w,
+                                                          const int64_t* __restrict__ pos, int T, int H, int K,
+                                                          bf16* __restrict__ out) {
+  __shared__ float red[8];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  bf16* orow = out + static_cast<size_t>(t) * H;
+  if (pos != nullptr && pos[t] == 0) {
+    for (int c = tid * 8; c < H; c += 2048) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  float gate = 0.f;
+  if (gate_w != nullptr) {
+    float dot = 0.f;
+    for (int c = tid * 8; c < H; c += 2048) {
+      const uint4 a = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H + c);
+      const uint4 w = *reinterpret_cast<const uint4*>(gate_w + c);
+      dot = fmaf(bf_lo(a.x), bf_lo(w.x), dot); dot = fmaf(bf_hi(a.x), bf_hi(w.x), dot);
+      dot = fmaf(bf_lo(a.y), bf_lo(w.y), dot); dot = fmaf(bf_hi(a.y), bf_hi(w.y), dot);
+      dot = fmaf(bf_lo(a.z), bf_lo(w.z), dot); dot = fmaf(bf_hi(a.z), bf_hi(w.z), dot);
+      dot = fmaf(bf_lo(a.w), bf_lo(w.w), dot); dot = fmaf(bf_hi(a.w), bf_hi(w.w), dot);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(FULL_MASK, dot, o);
+    if ((tid & 31) == 0) red[tid >> 5] = dot;
+    __syncthreads();
+    float s = 0.f;
+    for (int w = 0; w < 8; ++w) s += red[w];
+    gate = 1.f / (1.f + __expf(-s));
+  }
+  for (int c = tid * 8; c < H; c += 2048) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < K; ++j) {
+      const uint4 v = *reinterpret_cast<const uint4*>(cache + (static_cast<size_t>(t) * K + j) * H + c);
+      acc[0] += bf_lo(v.x); acc[1] += bf_hi(v.x); acc[2] += bf_lo(v.y); acc[3] += bf_hi(v.y);
+      acc[4] += bf_lo(v.z); acc[5] += bf_hi(v.z); acc[6] += bf_lo(v.w); acc[7] += bf_hi(v.w);
+    }
+    if (gate_w != nullptr) {
+      const uint4 v = *reinterpret_cast<const uint4*>(cache + (static_cast<size_t>(T) * K + t) * H + c);
+      acc[0] += gate * bf_lo(v.x); acc[1] += gate * bf_hi(v.x); acc[2] += gate * bf_lo(v.y); acc[3] += gate * bf_hi(v.y);
+      acc[4] += gate * bf_lo(v.z); acc[5] += gate * bf_hi(v.z); acc[6] += gate * bf_lo(v.w); acc[7] += gate * bf_hi(v.w);
+    }
+    *reinterpret_cast<uint4*>(orow + c) = make_uint4(pack_bf2(acc[0], acc[1]), pack_bf2(acc[2], acc[3]),
+                                                     pack_bf2(acc[4], acc[5]), pack_bf2(acc[6], acc[7]));
+  }
+}
+
+// workspace layout of the int8 block (all offsets 1024-byte aligned)
+struct W8Layout {
+  size_t xq, xs, h, hq, hs, total;
+};
+static W8Layout w8_layout(int T, int H, int I, int K) {
+  const size_t rows = static_cast<size_t>(T) * (K + 1);
+  auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+  W8Layout l;
+  size_t o = 0;
+  l.xq = o; o = up(o + rows * H);
+  l.xs = o; o = up(o + rows * 4);
+  l.h = o;  o = up(o + rows * I * 2);
+  l.hq = o; o = up(o + rows * I);
+  l.hs = o; o = up(o + rows * 4);
+  l.total = o;
+  return l;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_moe_w8a8_workspace_bytes(int T, int H, int I, int K) {
+  if (T <= 0 || H <= 0 || I <= 0 || K <= 0) return 0;
+  return w8_layout(T, H, I, K).total;
+}
+
+extern "C" int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
+                             const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes,
+                             int32_t* dbg_acc13, void* dbg_h, int32_t* status, void* stream) {
+  if (!x || !w || !lists || !cache || !ws || !w->w13 || !w->s13 || !w->w2 || !w->s2)
+    return fail(B200_E_ARG, "b200_moe_w8a8: null pointer");
+  if (T <= 0 || K <= 0 || K > 32 || E_local <= 0 || H % 128 || I % 128 || H <= 0 || I <= 0)
+    return fail(B200_E_ARG, "b200_moe_w8a8: need H %% 128 == 0, I %% 128 == 0, 1 <= K <= 32 (T=%d H=%d I=%d K=%d)", T, H,
+                I, K);
+  const W8Layout l = w8_layout(T, H, I, K);
+  if (ws_bytes < l.total) return fail(B200_E_WS, "b200_moe_w8a8: workspace %zu < %zu bytes", ws_bytes, l.total);
+  if (reinterpret_cast<uintptr_t>(ws) & 1023) return fail(B200_E_ALIGN, "b200_moe_w8a8: workspace must be 1024-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(cache)) & 15)
+    return fail(B200_E_ALIGN, "b200_moe_w8a8: x and cache must be 16-byte aligned");
+  const bool shared = w->sh13 != nullptr;
+  if (shared && (!w->shs13 || !w->sh2 || !w->shs2)) return fail(B200_E_ARG, "b200_moe_w8a8: incomplete shared expert");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* base = static_cast<uint8_t*>(ws);
+  int8_t* xq = reinterpret_cast<int8_t*>(base + l.xq);
+  float* xs = reinterpret_cast<float*>(base + l.xs);
+  bf16* h = reinterpret_cast<bf16*>(base + l.h);
+  int8_t* hq = reinterpret_cast<int8_t*>(base + l.hq);
+  float* hs = reinterpret_cast<float*>(base + l.hs);
+  const int rows = T * (K + 1);
+  MoeLists L{lists->counts,     lists->offsets,  lists->row_of_pair, lists->slot_of_row, lists->wt_of_row,
+             lists->blk_expert, lists->blk_row0, lists->blk_rows,    lists->nblocks};
+
+  CUtensorMap tmW13, tmSh13, tmXq, tmW2, tmSh2, tmHq;
+  int rc;
+  if ((rc = make_tmap_bytes_2d(&tmW13, w->w13, static_cast<uint64_t>(E_local) * 2 * I, H, 128, "w13"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmSh13, shared ? w->sh13 : w->w13, 2 * I, H, 128, "sh13"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmXq, xq, rows, H, 16, "xq"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmW2, w->w2, static_cast<uint64_t>(E_local) * H, I, 128, "w2"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmSh2, shared ? w->sh2 : w->w2, H, I, 128, "sh2"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmHq, hq, rows, I, 16, "hq"))) return rc;
+
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaFuncSetAttribute(moe_gemm_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<true>::SMEM);
+    cudaFuncSetAttribute(moe_gemm_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<false>::SMEM);
+    attr_done[dev] = true;
+  }
+
+  quant_permute_i8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, K, L.row_of_pair, shared ? 1 : 0, xq, xs);
+
+  GemmArgs a{};
+  a.L = L;
+  a.E_local = E_local;
+  a.I = I;
+  a.H = H;
+  a.total_rows = rows;
+  a.status = status;
+  const int grid = sm_count();
+
+  a.mtiles = I / 128;
+  a.ksteps = H / 128;
+  a.w_rows = 2 * I;
+  a.s_w = w->s13;
+  a.s_w_sh = w->shs13;
+  a.a_scale = xs;
+  a.h_out = h;
+  a.dbg_acc = dbg_acc13;
+  a.dbg_h = static_cast<bf16*>(dbg_h);
+  moe_gemm_i8_kernel<true><<<grid, GEMM_THREADS, GemmCfg<true>::SMEM, st>>>(tmW13, tmSh13, tmXq, a);
+
+  quant_rows_i8_kernel<<<(rows + 7) / 8, 256, 0, st>>>(h, rows, I, L.slot_of_row, hq, hs);
+
+  a.mtiles = H / 128;
+  a.ksteps = I / 128;
+  a.w_rows = H;
+  a.s_w = w->s2;
+  a.s_w_sh = w->shs2;
+  a.a_scale = hs;
+  a.h_out = nullptr;
+  a.cache = static_cast<bf16*>(cache);
+  a.dbg_acc = nullptr;
+  a.dbg_h = nullptr;
+  moe_gemm_i8_kernel<false><<<grid, GEMM_THREADS, GemmCfg<false>::SMEM, st>>>(tmW2, tmSh2, tmHq, a);
+  return launch_status("b200_moe_w8a8");
+}
+
+extern "C" int b200_moe_combine(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T, int H,
+                                int K, void* out, void* stream) {
+  if (!cache || !out || (gate_w && !x)) return fail(B200_E_ARG, "b200_moe_combine: null pointer");
+  if (T < 0 || H <= 0 || H % 8 || K <= 0) return fail(B200_E_ARG, "b200_moe_combine: need H %% 8 == 0 (H=%d K=%d)", H, K);
+  if (T == 0) return 0;
+  moe_combine_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const bf16*>(cache), static_cast<const bf16*>(x), static_cast<const bf16*>(gate_w), pos, T, H, K,
+      static_cast<bf16*>(out));
+  return launch_status("b200_moe_combine");
+}

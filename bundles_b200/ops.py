@@ -1,0 +1,176 @@
+"""Host-side operators: torch tensors in, C-ABI calls out.
+
+torch is used for device memory and the current stream only; every computation happens in
+libb200nodes.so.  Each function mirrors the reference operator it replaces (names in the
+docstrings) and raises `B200Error` on a non-zero return code, as the reference's TORCH_CHECKs
+raise RuntimeError (qk_route.cu:1128-1133).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import B200Error, MoeLists, MoeWeights, check
+
+__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_combine", "gdn_verify",
+           "new_status", "read_status", "B200Error"]
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t, dtype, name, dims=None):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == dtype and t.is_contiguous()):
+        raise B200Error(f"{name} must be a contiguous CUDA tensor of {dtype}")
+    if dims is not None and t.dim() != dims:
+        raise B200Error(f"{name} must have {dims} dimensions, got {tuple(t.shape)}")
+
+
+def new_status(device) -> torch.Tensor:
+    """A zeroed device status word for kernels with bounded waits (see include/b200nodes.h)."""
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def read_status(status: torch.Tensor) -> int:
+    return int(status[0].item())
+
+
+# ---------------------------------------------------------------------------------------------------
+def router(x, wr, top_k, bias=None, round_bf16=False, logits=None):
+    """Gate logits + softmax top-k + renormalise (reference: qk_route.route / i8x_dec_topk).
+    Returns (logits fp32 [T,E], ids int32 [T,K], wts fp32 [T,K])."""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(wr, torch.float32, "wr", 2)
+    T, H = x.shape
+    E = wr.shape[0]
+    if bias is not None:
+        _need(bias, torch.float32, "bias", 1)
+    if logits is None:
+        logits = torch.empty(T, E, dtype=torch.float32, device=x.device)
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=x.device)
+    wts = torch.empty(T, top_k, dtype=torch.float32, device=x.device)
+    check(_lib.lib().b200_router(_p(x), _p(wr), _p(bias), T, H, E, top_k, 1 if round_bf16 else 0, _p(logits),
+                                 _p(ids), _p(wts), _stream()), "b200_router")
+    return logits, ids, wts
+
+
+class RoutingLists:
+    """Device buffers of the routing lists (reference: `Workspace`, i8x_decode.py:495-518)."""
+
+    def __init__(self, T, K, E_local, block_rows, device):
+        self.T, self.K, self.E_local, self.block_rows = T, K, E_local, block_rows
+        self.max_blocks = _lib.lib().b200_moe_max_blocks(T, K, E_local, block_rows)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.counts = torch.zeros(E_local + 1, **i32)
+        self.offsets = torch.zeros(E_local + 2, **i32)
+        self.row_of_pair = torch.zeros(T * K, **i32)
+        self.slot_of_row = torch.zeros(T * (K + 1), **i32)
+        self.wt_of_row = torch.zeros(T * (K + 1), dtype=torch.float32, device=device)
+        self.blk_expert = torch.zeros(self.max_blocks, **i32)
+        self.blk_row0 = torch.zeros(self.max_blocks, **i32)
+        self.blk_rows = torch.zeros(self.max_blocks, **i32)
+        self.nblocks = torch.zeros(1, **i32)
+        self.c = MoeLists(*[t.data_ptr() for t in (self.counts, self.offsets, self.row_of_pair, self.slot_of_row,
+                                                   self.wt_of_row, self.blk_expert, self.blk_row0, self.blk_rows,
+                                                   self.nblocks)])
+
+
+def build_lists(ids, wts, lists: RoutingLists, pos=None, e_lo=0, with_shared=True):
+    """Per-expert sorted rows + GEMM block list (reference: i8x_dec_lists)."""
+    _need(ids, torch.int32, "ids", 2)
+    _need(wts, torch.float32, "wts", 2)
+    if pos is not None:
+        _need(pos, torch.int64, "pos", 1)
+    T, K = ids.shape
+    if (T, K) != (lists.T, lists.K):
+        raise B200Error("routing lists were sized for another (T, K)")
+    check(_lib.lib().b200_moe_build_lists(_p(ids), _p(wts), _p(pos), T, K, e_lo, lists.E_local, lists.block_rows,
+                                          1 if with_shared else 0, C.byref(lists.c), _stream()),
+          "b200_moe_build_lists")
+    return lists
+
+
+@dataclass
+class MoeW8A8Weights:
+    """Private int8 copy of one layer's experts (reference: `Copy`, i8x_kernels.py:69-110)."""
+    w13: torch.Tensor       # int8 [E, 2I, H]
+    s13: torch.Tensor       # fp32 [E, 2I]
+    w2: torch.Tensor        # int8 [E, H, I]
+    s2: torch.Tensor        # fp32 [E, H]
+    sh13: torch.Tensor | None = None   # int8 [2I, H]
+    shs13: torch.Tensor | None = None
+    sh2: torch.Tensor | None = None    # int8 [H, I]
+    shs2: torch.Tensor | None = None
+
+    def c_struct(self):
+        return MoeWeights(*[0 if t is None else t.data_ptr() for t in (self.w13, self.s13, self.w2, self.s2,
+                                                                        self.sh13, self.shs13, self.sh2, self.shs2)])
+
+
+def moe_w8a8_workspace(T, H, I, K, device):
+    n = _lib.lib().b200_moe_w8a8_workspace_bytes(T, H, I, K)
+    buf = torch.empty(n + 1024, dtype=torch.uint8, device=device)
+    off = (-buf.data_ptr()) % 1024
+    return buf[off:off + n]
+
+
+def moe_w8a8(x, w: MoeW8A8Weights, lists: RoutingLists, cache=None, ws=None, status=None, dbg_acc13=None,
+             dbg_h=None):
+    """Routed + shared expert MLPs in int8 W8A8 (reference: i8x_decode.moe_row_batch up/down).
+    Returns cache bf16 [T*(K+1), H] indexed by slot."""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(w.w13, torch.int8, "w13", 3)
+    _need(w.w2, torch.int8, "w2", 3)
+    T, H = x.shape
+    E, twoI, _ = w.w13.shape
+    I = twoI // 2
+    K = lists.K
+    if cache is None:
+        cache = torch.zeros(T * (K + 1), H, dtype=torch.bfloat16, device=x.device)
+    if ws is None:
+        ws = moe_w8a8_workspace(T, H, I, K, x.device)
+    wc = w.c_struct()
+    check(_lib.lib().b200_moe_w8a8(_p(x), T, H, I, K, E, C.byref(wc), C.byref(lists.c), _p(cache), _p(ws),
+                                   ws.numel(), _p(dbg_acc13), _p(dbg_h), _p(status), _stream()), "b200_moe_w8a8")
+    return cache
+
+
+def moe_combine(cache, x, gate_w, top_k, pos=None, out=None):
+    """Sum of the routed rows + sigmoid-gated shared row (reference: i8x_dec_combine)."""
+    _need(cache, torch.bfloat16, "cache", 2)
+    _need(x, torch.bfloat16, "x", 2)
+    T, H = x.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    check(_lib.lib().b200_moe_combine(_p(cache), _p(x), _p(gate_w), _p(pos), T, H, top_k, _p(out), _stream()),
+          "b200_moe_combine")
+    return out
+
+
+def gdn_verify(mixed, z, a, b, conv_state, conv_w, a_log, dt_bias, state, accepted, norm_w, eps=1e-6, out=None,
+               status=None):
+    """Gated DeltaNet verify over 4 draft tokens; updates `state` and `conv_state` in place to the
+    accepted length (reference: qk_gdn_verify.gdn_verify_fused).  Returns out bf16 [B*4, 4096]."""
+    _need(mixed, torch.bfloat16, "mixed", 2)
+    _need(state, torch.float32, "state", 4)
+    _need(conv_state, torch.bfloat16, "conv_state", 3)
+    _need(accepted, torch.int32, "accepted", 1)
+    B = state.shape[0]
+    if tuple(mixed.shape) != (B * 4, 8192) or tuple(state.shape) != (B, 32, 128, 128) or \
+            tuple(conv_state.shape) != (B, 8192, 3):
+        raise B200Error(f"gdn_verify: unexpected shapes mixed={tuple(mixed.shape)} state={tuple(state.shape)} "
+                        f"conv_state={tuple(conv_state.shape)}")
+    if out is None:
+        out = torch.empty(B * 4, 4096, dtype=torch.bfloat16, device=mixed.device)
+    check(_lib.lib().b200_gdn_verify(_p(mixed), _p(z), _p(a), _p(b), _p(conv_state), _p(conv_w), _p(a_log),
+                                     _p(dt_bias), _p(state), _p(accepted), _p(norm_w), float(eps), B, _p(out),
+                                     _p(status), _stream()), "b200_gdn_verify")
+    return out

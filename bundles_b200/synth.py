@@ -1,0 +1,140 @@
+"""Seeded synthetic inputs and random-init weights of the benchmark configurations.
+
+No dataset or checkpoint is involved: weights are N(0, 0.02) quantised to the named formats,
+activations are bf16 N(0, 1).  Everything is generated with a CPU `torch.Generator` so that the
+parity tests can hand identical bytes to the CUDA path and to the checker.  Quantisation here is
+the one-time `prepare` step of the layer node (the reference quantises its private expert copy at
+prepare time as well: i8x_reloc.py:193-241, i8x_kernels.py:112-148).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+SEEDS = {"moe_fp8": 1001, "moe_w8a8": 1002, "gdn": 1003, "attn": 1004, "step": 1005}
+
+
+def _gen(seed):
+    return torch.Generator().manual_seed(int(seed))
+
+
+def quant_int8_rows(w: torch.Tensor):
+    """Symmetric int8 per row (last dim): scale = amax / 127, round half away from zero, clamp +-127
+    (qwen36_lmhead8/lmhead8.py:95-108 `quantize_rows`).  Returns (int8, fp32 scale)."""
+    wf = w.float()
+    amax = wf.abs().amax(dim=-1)
+    scale = amax / 127.0
+    safe = torch.where(amax > 0, scale, torch.ones_like(scale))
+    v = wf / safe.unsqueeze(-1)
+    r = torch.where(v >= 0, torch.floor(v + 0.5), -torch.floor(0.5 - v)).clamp_(-127, 127)
+    return r.to(torch.int8), scale
+
+
+def quant_fp8_blocks(w: torch.Tensor, block: int = 128):
+    """e4m3 with one fp32 scale per 128 x 128 block: scale = max(amax / 448, 1e-12), y = e4m3(w / scale)
+    computed as w * (1 / scale) (fp8.py:21-34 scale rule).  Returns (uint8 codes, fp32 scales)."""
+    wf = w.float()
+    *lead, n, k = wf.shape
+    b = wf.reshape(*lead, n // block, block, k // block, block)
+    amax = b.abs().amax(dim=(-3, -1))
+    scale = (amax / 448.0).clamp_min(1e-12)
+    inv = 1.0 / scale
+    y = (b * inv[..., :, None, :, None]).clamp_(-448.0, 448.0)
+    codes = y.reshape(*lead, n, k).to(torch.float8_e4m3fn).view(torch.uint8)
+    return codes, scale
+
+
+def zipf_bias(E: int, s: float, gen) -> torch.Tensor:
+    """bias_e = log(rank_e^-s / Z) over a seeded permutation of the experts (skewed expert load)."""
+    perm = torch.randperm(E, generator=gen)
+    p = torch.arange(1, E + 1, dtype=torch.float64).pow(-s)
+    p = p / p.sum()
+    bias = torch.empty(E, dtype=torch.float64)
+    bias[perm] = p.log()
+    return bias.float()
+
+
+def moe_common(seed, T, H, E, gen=None):
+    g = gen or _gen(seed)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    wr = torch.randn(E, H, generator=g) * 0.02
+    gate_w = (torch.randn(H, generator=g) * 0.02).to(torch.bfloat16)
+    return g, x, wr, gate_w
+
+
+def moe_w8a8(seed=SEEDS["moe_w8a8"], T=256, H=2048, I=512, E=512, zipf_s=1.1):
+    """Config: int8 W8A8 routed MoE at decode (per-output-channel weights, per-token activations),
+    Zipf-skewed router bias."""
+    g, x, wr, gate_w = moe_common(seed, T, H, E)
+    bias = zipf_bias(E, zipf_s, g) if zipf_s else None
+    w13q = torch.empty(E, 2 * I, H, dtype=torch.int8)
+    s13 = torch.empty(E, 2 * I)
+    w2q = torch.empty(E, H, I, dtype=torch.int8)
+    s2 = torch.empty(E, H)
+    for e0 in range(0, E, 32):
+        n = min(32, E - e0)
+        w13q[e0:e0 + n], s13[e0:e0 + n] = quant_int8_rows(torch.randn(n, 2 * I, H, generator=g) * 0.02)
+        w2q[e0:e0 + n], s2[e0:e0 + n] = quant_int8_rows(torch.randn(n, H, I, generator=g) * 0.02)
+    sh13q, shs13 = quant_int8_rows(torch.randn(2 * I, H, generator=g) * 0.02)
+    sh2q, shs2 = quant_int8_rows(torch.randn(H, I, generator=g) * 0.02)
+    return dict(x=x, wr=wr, bias=bias, gate_w=gate_w, w13=w13q, s13=s13, w2=w2q, s2=s2, sh13=sh13q, shs13=shs13,
+                sh2=sh2q, shs2=shs2)
+
+
+def moe_fp8(seed=SEEDS["moe_fp8"], T=16, H=2048, I=512, E=512):
+    """Config: single fp8 MoE block, 128 x 128 block scales."""
+    g, x, wr, gate_w = moe_common(seed, T, H, E)
+    w13q = torch.empty(E, 2 * I, H, dtype=torch.uint8)
+    s13 = torch.empty(E, 2 * I // 128, H // 128)
+    w2q = torch.empty(E, H, I, dtype=torch.uint8)
+    s2 = torch.empty(E, H // 128, I // 128)
+    for e0 in range(0, E, 32):
+        n = min(32, E - e0)
+        w13q[e0:e0 + n], s13[e0:e0 + n] = quant_fp8_blocks(torch.randn(n, 2 * I, H, generator=g) * 0.02)
+        w2q[e0:e0 + n], s2[e0:e0 + n] = quant_fp8_blocks(torch.randn(n, H, I, generator=g) * 0.02)
+    sh13q, shs13 = quant_fp8_blocks(torch.randn(2 * I, H, generator=g) * 0.02)
+    sh2q, shs2 = quant_fp8_blocks(torch.randn(H, I, generator=g) * 0.02)
+    return dict(x=x, wr=wr, bias=None, gate_w=gate_w, w13=w13q, s13=s13, w2=w2q, s2=s2, sh13=sh13q, shs13=shs13,
+                sh2=sh2q, shs2=shs2)
+
+
+def gdn(seed=SEEDS["gdn"], B=32):
+    """Config: Gated DeltaNet speculative verify, 4 draft tokens, 16 q/k heads, 32 v heads, d = 128."""
+    g = _gen(seed)
+    bf = torch.bfloat16
+    return dict(
+        mixed=torch.randn(B * 4, 8192, generator=g).to(bf),
+        z=torch.randn(B * 4, 4096, generator=g).to(bf),
+        a=torch.randn(B * 4, 32, generator=g).to(bf),
+        b=torch.randn(B * 4, 32, generator=g).to(bf),
+        conv_state=torch.randn(B, 8192, 3, generator=g).to(bf),
+        conv_w=(torch.randn(8192, 4, generator=g) * 0.5).to(bf),
+        a_log=torch.rand(32, generator=g) * math.log(16.0),
+        dt_bias=torch.randn(32, generator=g),
+        state=torch.randn(B, 32, 128, 128, generator=g) * 0.1,
+        accepted=torch.randint(0, 5, (B,), generator=g, dtype=torch.int32),
+        norm_w=(1.0 + torch.randn(128, generator=g) * 0.1).to(bf),
+    )
+
+
+def attn(seed=SEEDS["attn"], T=4096, H=2048):
+    """Config: fused gated-attention projections; W [9216, 2048] fp8 block-scaled."""
+    g = _gen(seed)
+    bf = torch.bfloat16
+    wq, ws = quant_fp8_blocks(torch.randn(9216, H, generator=g) * 0.02)
+    return dict(x=torch.randn(T, H, generator=g).to(bf), w=wq, w_s=ws,
+                q_norm_w=(torch.randn(256, generator=g) * 0.1).to(bf),
+                k_norm_w=(torch.randn(256, generator=g) * 0.1).to(bf),
+                positions=torch.arange(T, dtype=torch.int64))
+
+
+def lmhead(seed=SEEDS["step"], T=64, V=151936, H=2048):
+    """Config: fp8 LM head [V, 2048] with 128 x 128 block scales (V padded up to a block multiple
+    inside the scale tensor only)."""
+    g = _gen(seed + 7)
+    vb = (V + 127) // 128 * 128
+    w = torch.zeros(vb, H)
+    w[:V] = torch.randn(V, H, generator=g) * 0.02
+    wq, ws = quant_fp8_blocks(w)
+    return dict(x=torch.randn(T, H, generator=g).to(torch.bfloat16), w=wq[:V].contiguous(), w_s=ws)

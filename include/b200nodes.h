@@ -1,0 +1,152 @@
+/*
+ * b200nodes — C ABI of the B200 (sm_100a) decode / speculative-verify hot path.
+ *
+ * These entry points are what a host binding for the reference bundle's two ops
+ * (`model.layers.*` -> qwen36_layer/layer.py, `logits_processor` -> qwen36_lmhead8/node.py,
+ * manifest.toml:142-157 of snapshot qwen36_nodes_kb34) calls instead of the reference's pybind
+ * units.  Conventions:
+ *   - plain pointers and sizes only; every pointer is DEVICE memory unless its name ends in
+ *     `_host`; the library allocates nothing and frees nothing, the caller owns all memory;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing synchronises;
+ *   - bf16 tensors are passed as `const void*` / `void*` (2 bytes per element, row-major);
+ *   - every function returns 0 on success, a negative B200_E_* code on an argument error or a
+ *     positive cudaError_t value if a launch failed; nothing throws across the ABI;
+ *     b200_last_error() returns a thread-local message for the last non-zero return;
+ *   - kernels that wait on asynchronous copies bound every wait; when a wait gives up the kernel
+ *     writes a B200_ST_* code into `status` (a device int32, may be NULL) and returns early.
+ *     The caller reads it after synchronising the stream; 0 means no wait was abandoned.
+ *   - there is no CPU fallback.
+ */
+#ifndef B200NODES_H
+#define B200NODES_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ABI_VERSION 1
+
+#define B200_E_ARG (-1)      /* null pointer, bad size or unsupported shape */
+#define B200_E_ALIGN (-2)    /* pointer not aligned as documented */
+#define B200_E_WS (-3)       /* workspace too small */
+#define B200_E_DRIVER (-4)   /* tensor-map encoder unavailable (no CUDA driver) */
+
+#define B200_ST_WAIT_FULL 101
+#define B200_ST_WAIT_EMPTY 102
+#define B200_ST_WAIT_TMEM_FULL 103
+#define B200_ST_WAIT_TMEM_EMPTY 104
+#define B200_ST_WAIT_STATE 105
+#define B200_ST_WAIT_STORE 106
+#define B200_ST_BAD_LIST 110
+
+int b200_abi_version(void);
+const char* b200_last_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Router.  Replaces qk_route.route / route48 / route16w (qk_route.cu:214,496,972) and the Triton
+ * twins i8x_dec_gate / i8x_dec_topk (i8x_decode.py:226-262).
+ *
+ * logits[t,e] = sum_k x[t,k] * wr[e,k] (+ bias[e]) in fp32 with a fixed summation tree (one fma
+ * chain from 0 per 128-deep k slice, ascending k; slices added in slice order; bias last), so
+ * that expert ids are reproducible bit for bit.  Then softmax over E, top-k by largest logit with
+ * ties to the smaller expert id (-0 == +0, NaN lowest), weights renormalised over the picks
+ * (i8x_decode.py:99-117).
+ *   x bf16 [T,H]; wr fp32 [E,H]; bias fp32 [E] or NULL; logits fp32 [T,E] (output, also scratch);
+ *   ids int32 [T,K]; wts fp32 [T,K].  H % 128 == 0, E % 32 == 0, E <= 1024, K <= 32.
+ *   flags bit 0: round the logits to bf16 before the softmax / top-k (the reference's behaviour,
+ *   i8x_decode.py:100).
+ */
+int b200_router(const void* x, const float* wr, const float* bias, int T, int H, int E, int K, int flags,
+                float* logits, int32_t* ids, float* wts, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Routing lists.  Replaces i8x_dec_lists (i8x_decode.py:264-289) and the list-building tail of
+ * route_kernel (qk_route.cu:297-357).
+ *
+ * Sorted-row layout used by the MoE kernels: routed pairs (slot p = t*K + j, i8x_decode.py:297)
+ * are grouped by expert, in ascending slot order inside an expert, at rows [0, T*K); the shared
+ * expert's rows are [T*K, T*K + T) (slot T*K + t, i8x_decode.py:442).  Only experts in
+ * [e_lo, e_lo + E_local) are listed (expert-parallel shard); tokens with pos[t] == 0 are graph
+ * padding and are skipped (qk_route.cu:229,307).  `block_rows` is the largest N tile of the
+ * GEMM that will consume the lists (128 for int8, 64 for fp8).
+ */
+typedef struct b200_moe_lists {
+  int32_t* counts;      /* [E_local + 1]   rows per local expert; entry E_local = shared expert */
+  int32_t* offsets;     /* [E_local + 2]   first sorted row per expert (shared expert at T*K) */
+  int32_t* row_of_pair; /* [T*K]           sorted row of routed slot p, or -1 */
+  int32_t* slot_of_row; /* [T*(K+1)]       slot id of a sorted row, or -1 */
+  float* wt_of_row;     /* [T*(K+1)]       routing weight of a sorted row (1 for the shared expert) */
+  int32_t* blk_expert;  /* [max_blocks]    local expert of each GEMM block (E_local = shared) */
+  int32_t* blk_row0;    /* [max_blocks]    first sorted row of the block */
+  int32_t* blk_rows;    /* [max_blocks]    rows in the block, 1..block_rows */
+  int32_t* nblocks;     /* [1] */
+} b200_moe_lists;
+
+/* max_blocks the caller must provide for a given problem */
+int b200_moe_max_blocks(int T, int K, int E_local, int block_rows);
+
+int b200_moe_build_lists(const int32_t* ids, const float* wts, const int64_t* pos, int T, int K, int e_lo,
+                         int E_local, int block_rows, int with_shared, const b200_moe_lists* lists, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * MoE block, int8 W8A8.  Replaces i8x_decode.moe_row_batch (i8x_decode.py:528-576): up + SwiGLU
+ * (i8x_dec_up, qk_moe_up16.cu:139), down (i8x_dec_down, qk_moe_dn16.cu:136) and, via
+ * b200_moe_combine, the combine; the W8A8 arithmetic is the reference's w8_up / w8_dn lane
+ * (qk_moe_prefill_i8.cu:3646-3655,4061-4071): int32 accumulation over the whole K, value =
+ * (float(acc) * xs[row]) * ws[col], h rounded to bf16 and re-quantised per row.
+ *
+ *   x bf16 [T,H];  w13 int8 [E_local,2I,H] (rows 0..I-1 gate, I..2I-1 up), s13 fp32 [E_local,2I];
+ *   w2 int8 [E_local,H,I], s2 fp32 [E_local,H];  shared expert sh13 [2I,H], shs13 [2I],
+ *   sh2 [H,I], shs2 [H] (NULL sh13 = no shared expert);
+ *   cache bf16 [T*(K+1),H] (output): row `slot` = bf16(down row * routing weight)
+ *   (i8x_decode.py:420-422).  H % 128 == 0, I % 128 == 0.
+ *   ws: workspace of b200_moe_w8a8_workspace_bytes() bytes, 1024-byte aligned.
+ *   dbg_acc13 int32 [T*(K+1), 2I] or NULL: raw up accumulators per slot (parity checks).
+ *   dbg_h bf16 [T*(K+1), I] or NULL: SwiGLU output per slot.
+ */
+typedef struct b200_moe_weights {
+  const void* w13;
+  const float* s13;
+  const void* w2;
+  const float* s2;
+  const void* sh13;
+  const float* shs13;
+  const void* sh2;
+  const float* shs2;
+} b200_moe_weights;
+
+size_t b200_moe_w8a8_workspace_bytes(int T, int H, int I, int K);
+int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
+                  const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, int32_t* dbg_acc13,
+                  void* dbg_h, int32_t* status, void* stream);
+
+/* Combine.  Replaces i8x_dec_combine (i8x_decode.py:425-443) / combine_norm_kernel
+ * (qk_route.cu:686-820, without the next-layer norm): out[t] = bf16(sum_j cache[t*K+j] in slot
+ * order + sigmoid(x[t].gate_w) * cache[T*K+t]); rows with pos[t] == 0 are written as zeros.
+ * gate_w NULL = no shared expert.  H % 8 == 0. */
+int b200_moe_combine(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T, int H, int K,
+                     void* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Gated DeltaNet speculative verify.  Replaces qk_gdn_verify.gdn_verify_fused
+ * (qk_gdn_verify.cu:293, gdn_fused.py:37-57) with an explicit state instead of the ReplaySSM
+ * ring: causal conv (width 4, carried 3-token state) + SiLU, q/k L2 norm, gates, delta-rule
+ * recurrence over the 4 draft tokens, gated RMSNorm; the state written back is the state after
+ * accepted[b] tokens and the conv state is rolled by accepted[b] tokens.
+ *   mixed bf16 [B*4, 8192] ([q 2048 | k 2048 | v 4096]); z bf16 [B*4, 4096]; a, b bf16 [B*4, 32];
+ *   conv_state bf16 [B, 8192, 3] (in/out); conv_w bf16 [8192, 4]; a_log, dt_bias fp32 [32];
+ *   state fp32 [B, 32, 128, 128] (S[v][k], in/out); accepted int32 [B] in 0..4;
+ *   norm_w bf16 [128]; out bf16 [B*4, 4096].  state must be 16-byte aligned.
+ */
+int b200_gdn_verify(const void* mixed, const void* z, const void* a, const void* b, void* conv_state,
+                    const void* conv_w, const float* a_log, const float* dt_bias, float* state,
+                    const int32_t* accepted, const void* norm_w, float eps, int B, void* out, int32_t* status,
+                    void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200NODES_H */

@@ -1,0 +1,63 @@
+"""CPU checks of the C-ABI library: it loads without a GPU, exports every symbol the public
+header declares, and rejects bad arguments with error codes before touching the device."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from bundles_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "b200nodes.h")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.lib()
+
+
+def declared_symbols():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = declared_symbols()
+    assert len(names) >= 9
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, f"declared in include/b200nodes.h but not exported: {missing}"
+
+
+def test_prototypes_cover_header(lib):
+    assert set(_lib.PROTOTYPES) == set(declared_symbols())
+
+
+def test_version_and_error_text(lib):
+    assert lib.b200_abi_version() == 1
+    rc = lib.b200_router(None, None, None, 4, 2048, 512, 10, 0, None, None, None, None)
+    assert rc == -1
+    assert b"b200_router" in lib.b200_last_error()
+
+
+def test_argument_checks_return_codes(lib):
+    one = C.c_void_p(4096)  # never dereferenced: the checks fail first
+    # H not a multiple of 128
+    assert lib.b200_router(one, one, None, 4, 100, 512, 10, 0, one, one, one, None) == -1
+    # K > E
+    assert lib.b200_router(one, one, None, 4, 2048, 32, 33, 0, one, one, one, None) == -1
+    # misaligned x
+    assert lib.b200_router(C.c_void_p(4100), one, None, 4, 2048, 512, 10, 0, one, one, one, None) == -2
+    assert lib.b200_moe_max_blocks(256, 10, 512, 128) >= 512 + 20 + 2
+    assert lib.b200_moe_w8a8_workspace_bytes(256, 2048, 512, 10) > 256 * 11 * 2048
+    assert lib.b200_moe_combine(None, None, None, None, 1, 2048, 10, None, None) == -1
+    assert lib.b200_gdn_verify(*([None] * 11), 1e-6, 1, None, None, None) == -1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.lib()
