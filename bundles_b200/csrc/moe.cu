@@ -445,7 +445,7 @@ extern "C" size_t b200_moe_w8a8_workspace_bytes(int T, int H, int I, int K) {
 
 extern "C" int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
                              const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes,
-                             int32_t* dbg_acc13, void* dbg_h, int32_t* status, void* stream) {
+                             int32_t* dbg_acc13, void* dbg_h, int stages, int32_t* status, void* stream) {
   if (!x || !w || !lists || !cache || !ws || !w->w13 || !w->s13 || !w->w2 || !w->s2)
     return fail(B200_E_ARG, "b200_moe_w8a8: null pointer");
   if (T <= 0 || K <= 0 || K > 32 || E_local <= 0 || H % 128 || I % 128 || H <= 0 || I <= 0)
@@ -487,7 +487,9 @@ extern "C" int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_lo
     attr_done[dev] = true;
   }
 
-  quant_permute_i8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, K, L.row_of_pair, shared ? 1 : 0, xq, xs);
+  if (stages == 0) stages = 15;
+  if (stages & B200_MOE_STAGE_QUANT)
+    quant_permute_i8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, K, L.row_of_pair, shared ? 1 : 0, xq, xs);
 
   GemmArgs a{};
   a.L = L;
@@ -507,9 +509,11 @@ extern "C" int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_lo
   a.h_out = h;
   a.dbg_acc = dbg_acc13;
   a.dbg_h = static_cast<bf16*>(dbg_h);
-  moe_gemm_i8_kernel<true><<<grid, GEMM_THREADS, GemmCfg<true>::SMEM, st>>>(tmW13, tmSh13, tmXq, a);
+  if (stages & B200_MOE_STAGE_UP)
+    moe_gemm_i8_kernel<true><<<grid, GEMM_THREADS, GemmCfg<true>::SMEM, st>>>(tmW13, tmSh13, tmXq, a);
 
-  quant_rows_i8_kernel<<<(rows + 7) / 8, 256, 0, st>>>(h, rows, I, L.slot_of_row, hq, hs);
+  if (stages & B200_MOE_STAGE_HQUANT)
+    quant_rows_i8_kernel<<<(rows + 7) / 8, 256, 0, st>>>(h, rows, I, L.slot_of_row, hq, hs);
 
   a.mtiles = H / 128;
   a.ksteps = I / 128;
@@ -521,7 +525,8 @@ extern "C" int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_lo
   a.cache = static_cast<bf16*>(cache);
   a.dbg_acc = nullptr;
   a.dbg_h = nullptr;
-  moe_gemm_i8_kernel<false><<<grid, GEMM_THREADS, GemmCfg<false>::SMEM, st>>>(tmW2, tmSh2, tmHq, a);
+  if (stages & B200_MOE_STAGE_DOWN)
+    moe_gemm_i8_kernel<false><<<grid, GEMM_THREADS, GemmCfg<false>::SMEM, st>>>(tmW2, tmSh2, tmHq, a);
   return launch_status("b200_moe_w8a8");
 }
 

@@ -1,0 +1,49 @@
+"""The sparse-MoE block of one decoder layer: router -> routing lists -> expert MLPs -> combine.
+
+Host-side mirror of the reference's `moe_row_batch` (i8x_decode.py:528-576) and of the `mlp`
+override its layer node installs (layer.py:434-480): same inputs (hidden states, optional
+positions whose zeros mark graph-padding rows), same output (bf16 [T, H]); the workspaces are
+allocated once per (device, T) and reused, as the reference's `Workspace` is (i8x_decode.py:495-526).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+
+class MoeBlockW8A8:
+    """int8 W8A8 experts (per-output-channel weight scales, per-token activation scales)."""
+
+    def __init__(self, wr, weights: ops.MoeW8A8Weights, gate_w, top_k, bias=None, e_lo=0, round_bf16=False):
+        self.wr, self.w, self.gate_w, self.bias = wr, weights, gate_w, bias
+        self.top_k, self.e_lo, self.round_bf16 = top_k, e_lo, round_bf16
+        self.E_local = weights.w13.shape[0]
+        self.I = weights.w2.shape[-1]
+        self.H = weights.w13.shape[-1]
+        self._ws = {}
+        self.status = ops.new_status(wr.device)
+        self.launches_per_call = 8  # gate, top-k, lists, quant+permute, up, h-quant, down, combine
+
+    def _buffers(self, T, device):
+        b = self._ws.get(T)
+        if b is None:
+            K = self.top_k
+            b = dict(lists=ops.RoutingLists(T, K, self.E_local, 128, device),
+                     ws=ops.moe_w8a8_workspace(T, self.H, self.I, K, device),
+                     cache=torch.zeros(T * (K + 1), self.H, dtype=torch.bfloat16, device=device),
+                     logits=torch.empty(T, self.wr.shape[0], dtype=torch.float32, device=device),
+                     out=torch.empty(T, self.H, dtype=torch.bfloat16, device=device))
+            self._ws[T] = b
+        return b
+
+    def forward(self, x: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
+        T = x.shape[0]
+        b = self._buffers(T, x.device)
+        _, ids, wts = ops.router(x, self.wr, self.top_k, self.bias, self.round_bf16, logits=b["logits"])
+        ops.build_lists(ids, wts, b["lists"], positions, e_lo=self.e_lo, with_shared=self.w.sh13 is not None)
+        ops.moe_w8a8(x, self.w, b["lists"], cache=b["cache"], ws=b["ws"], status=self.status)
+        return ops.moe_combine(b["cache"], x, self.gate_w if self.w.sh13 is not None else None, self.top_k, positions,
+                               out=b["out"])
+
+    __call__ = forward

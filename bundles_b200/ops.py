@@ -122,8 +122,11 @@ def moe_w8a8_workspace(T, H, I, K, device):
     return buf[off:off + n]
 
 
+STAGE_QUANT, STAGE_UP, STAGE_HQUANT, STAGE_DOWN = 1, 2, 4, 8
+
+
 def moe_w8a8(x, w: MoeW8A8Weights, lists: RoutingLists, cache=None, ws=None, status=None, dbg_acc13=None,
-             dbg_h=None):
+             dbg_h=None, stages=0):
     """Routed + shared expert MLPs in int8 W8A8 (reference: i8x_decode.moe_row_batch up/down).
     Returns cache bf16 [T*(K+1), H] indexed by slot."""
     _need(x, torch.bfloat16, "x", 2)
@@ -139,7 +142,8 @@ def moe_w8a8(x, w: MoeW8A8Weights, lists: RoutingLists, cache=None, ws=None, sta
         ws = moe_w8a8_workspace(T, H, I, K, x.device)
     wc = w.c_struct()
     check(_lib.lib().b200_moe_w8a8(_p(x), T, H, I, K, E, C.byref(wc), C.byref(lists.c), _p(cache), _p(ws),
-                                   ws.numel(), _p(dbg_acc13), _p(dbg_h), _p(status), _stream()), "b200_moe_w8a8")
+                                   ws.numel(), _p(dbg_acc13), _p(dbg_h), int(stages), _p(status), _stream()),
+          "b200_moe_w8a8")
     return cache
 
 

@@ -15,8 +15,12 @@ import torch
 SEEDS = {"moe_fp8": 1001, "moe_w8a8": 1002, "gdn": 1003, "attn": 1004, "step": 1005}
 
 
-def _gen(seed):
-    return torch.Generator().manual_seed(int(seed))
+def _gen(seed, device="cpu"):
+    return torch.Generator(device=device).manual_seed(int(seed))
+
+
+def _randn(*shape, g):
+    return torch.randn(*shape, generator=g, device=g.device)
 
 
 def quant_int8_rows(w: torch.Tensor):
@@ -55,29 +59,30 @@ def zipf_bias(E: int, s: float, gen) -> torch.Tensor:
     return bias.float()
 
 
-def moe_common(seed, T, H, E, gen=None):
-    g = gen or _gen(seed)
-    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
-    wr = torch.randn(E, H, generator=g) * 0.02
-    gate_w = (torch.randn(H, generator=g) * 0.02).to(torch.bfloat16)
+def moe_common(seed, T, H, E, device="cpu"):
+    g = _gen(seed, device)
+    x = _randn(T, H, g=g).to(torch.bfloat16)
+    wr = _randn(E, H, g=g) * 0.02
+    gate_w = (_randn(H, g=g) * 0.02).to(torch.bfloat16)
     return g, x, wr, gate_w
 
 
-def moe_w8a8(seed=SEEDS["moe_w8a8"], T=256, H=2048, I=512, E=512, zipf_s=1.1):
+def moe_w8a8(seed=SEEDS["moe_w8a8"], T=256, H=2048, I=512, E=512, zipf_s=1.1, device="cpu"):
     """Config: int8 W8A8 routed MoE at decode (per-output-channel weights, per-token activations),
-    Zipf-skewed router bias."""
-    g, x, wr, gate_w = moe_common(seed, T, H, E)
-    bias = zipf_bias(E, zipf_s, g) if zipf_s else None
-    w13q = torch.empty(E, 2 * I, H, dtype=torch.int8)
-    s13 = torch.empty(E, 2 * I)
-    w2q = torch.empty(E, H, I, dtype=torch.int8)
-    s2 = torch.empty(E, H)
+    Zipf-skewed router bias.  `device` selects where the random stream is drawn (the CPU stream is
+    the one the parity tests use; a CUDA stream gives different, equally distributed values)."""
+    g, x, wr, gate_w = moe_common(seed, T, H, E, device)
+    bias = zipf_bias(E, zipf_s, _gen(seed + 1)).to(device) if zipf_s else None
+    w13q = torch.empty(E, 2 * I, H, dtype=torch.int8, device=device)
+    s13 = torch.empty(E, 2 * I, device=device)
+    w2q = torch.empty(E, H, I, dtype=torch.int8, device=device)
+    s2 = torch.empty(E, H, device=device)
     for e0 in range(0, E, 32):
         n = min(32, E - e0)
-        w13q[e0:e0 + n], s13[e0:e0 + n] = quant_int8_rows(torch.randn(n, 2 * I, H, generator=g) * 0.02)
-        w2q[e0:e0 + n], s2[e0:e0 + n] = quant_int8_rows(torch.randn(n, H, I, generator=g) * 0.02)
-    sh13q, shs13 = quant_int8_rows(torch.randn(2 * I, H, generator=g) * 0.02)
-    sh2q, shs2 = quant_int8_rows(torch.randn(H, I, generator=g) * 0.02)
+        w13q[e0:e0 + n], s13[e0:e0 + n] = quant_int8_rows(_randn(n, 2 * I, H, g=g) * 0.02)
+        w2q[e0:e0 + n], s2[e0:e0 + n] = quant_int8_rows(_randn(n, H, I, g=g) * 0.02)
+    sh13q, shs13 = quant_int8_rows(_randn(2 * I, H, g=g) * 0.02)
+    sh2q, shs2 = quant_int8_rows(_randn(H, I, g=g) * 0.02)
     return dict(x=x, wr=wr, bias=bias, gate_w=gate_w, w13=w13q, s13=s13, w2=w2q, s2=s2, sh13=sh13q, shs13=shs13,
                 sh2=sh2q, shs2=shs2)
 

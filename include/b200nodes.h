@@ -106,7 +106,13 @@ int b200_moe_build_lists(const int32_t* ids, const float* wts, const int64_t* po
  *   ws: workspace of b200_moe_w8a8_workspace_bytes() bytes, 1024-byte aligned.
  *   dbg_acc13 int32 [T*(K+1), 2I] or NULL: raw up accumulators per slot (parity checks).
  *   dbg_h bf16 [T*(K+1), I] or NULL: SwiGLU output per slot.
+ *   stages: 0 runs the whole block; otherwise a mask of B200_MOE_STAGE_* runs only those launches
+ *   on the data the earlier ones left in `ws` (used to time one kernel on its own).
  */
+#define B200_MOE_STAGE_QUANT 1   /* quantise + permute activations */
+#define B200_MOE_STAGE_UP 2      /* gate/up GEMM + SwiGLU */
+#define B200_MOE_STAGE_HQUANT 4  /* re-quantise h */
+#define B200_MOE_STAGE_DOWN 8    /* down GEMM + weighted unpermute */
 typedef struct b200_moe_weights {
   const void* w13;
   const float* s13;
@@ -121,7 +127,7 @@ typedef struct b200_moe_weights {
 size_t b200_moe_w8a8_workspace_bytes(int T, int H, int I, int K);
 int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
                   const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, int32_t* dbg_acc13,
-                  void* dbg_h, int32_t* status, void* stream);
+                  void* dbg_h, int stages, int32_t* status, void* stream);
 
 /* Combine.  Replaces i8x_dec_combine (i8x_decode.py:425-443) / combine_norm_kernel
  * (qk_route.cu:686-820, without the next-layer norm): out[t] = bf16(sum_j cache[t*K+j] in slot
