@@ -141,7 +141,7 @@ struct GemmCfg {
   static constexpr int NA = UP ? 2 : 1;                      // weight tiles per stage (gate + up)
   static constexpr int STAGE = NA * TILE_BYTES + TILE_BYTES;  // + token tile (<= 128 rows)
   static constexpr int STAGES = UP ? 4 : 6;
-  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + 4 * 128 * 12 /*row metadata, one copy per epilogue warp*/;
 };
 
 template <bool UP>
@@ -157,6 +157,11 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // per-tile row metadata for the epilogue: each epilogue warp keeps its own copy, so no barrier
+  // between warps is needed (a warp-private buffer is refilled only after that warp is done with it)
+  float* m_scale_all = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE + 256);  // [4][128] activation scale
+  float* m_wt_all = m_scale_all + 512;                                                // [4][128] routing weight
+  int* m_slot_all = reinterpret_cast<int*>(m_wt_all + 512);                           // [4][128] slot or -1
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -285,6 +290,12 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   } else {
     // ---------------- epilogue: warps 2..5, TMEM lane quadrant = warp % 4 ----------------
     const int q = warp & 3;
+    float* ms = m_scale_all + q * 128;
+    float* m_wt = m_wt_all + q * 128;
+    int* m_slot = m_slot_all + q * 128;
+    const float* __restrict__ a_scale = p.a_scale;
+    const float* __restrict__ wt_of_row = p.L.wt_of_row;
+    const int32_t* __restrict__ slot_of_row = p.L.slot_of_row;
     int it = 0;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
       int e, row0, n, mt;
@@ -295,6 +306,24 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int buf = it & 1;
       const uint32_t bphase = (it >> 1) & 1;
       ++it;
+      // stage this block's row metadata while the MMAs run
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = lane + 32 * i;
+        float sc = 0.f, wt = 0.f;
+        int slot = -1;
+        if (c < n) {
+          sc = a_scale[row0 + c];
+          slot = slot_of_row[row0 + c];
+          if (!UP) wt = wt_of_row[row0 + c];
+          if (slot >= p.total_rows) slot = -1;
+        }
+        ms[c] = sc;
+        m_wt[c] = wt;
+        m_slot[c] = slot;
+      }
+      __syncwarp();
       if (!mbar_wait(&tfull[buf], bphase, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + buf * 256 + (static_cast<uint32_t>(q * 32) << 16);
@@ -303,51 +332,50 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (UP) {
         const float* sw = shared_e ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * p.w_rows;
         const float wsg = sw[r], wsu = sw[p.I + r];
+        bf16* __restrict__ hout = p.h_out + static_cast<size_t>(row0) * p.I + r;
         for (int c0 = 0; c0 < n; c0 += 16) {
           uint32_t rg[16], ru[16];
           tmem_ld16(taddr + c0, rg);
           tmem_ld16(taddr + 128 + c0, ru);
           tmem_ld_wait();
+          bf16 hv[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int col = c0 + i;
-            if (col < n) {
-              const int row = row0 + col;
-              const float xs = p.a_scale[row];
-              const float g = rbf(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(rg[i])), xs), wsg));
-              const float u = rbf(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ru[i])), xs), wsu));
-              const bf16 hv = f2bf(__fmul_rn(__fdiv_rn(g, 1.f + __expf(-g)), u));
-              p.h_out[static_cast<size_t>(row) * p.I + r] = hv;
-              if (p.dbg_acc || p.dbg_h) {
-                const int slot = p.L.slot_of_row[row];
-                if (slot >= 0 && slot < p.total_rows) {
-                  if (p.dbg_acc) {
-                    p.dbg_acc[static_cast<size_t>(slot) * 2 * p.I + r] = static_cast<int>(rg[i]);
-                    p.dbg_acc[static_cast<size_t>(slot) * 2 * p.I + p.I + r] = static_cast<int>(ru[i]);
-                  }
-                  if (p.dbg_h) p.dbg_h[static_cast<size_t>(slot) * p.I + r] = hv;
+            const float xs = ms[c0 + i];
+            const float g = rbf(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(rg[i])), xs), wsg));
+            const float u = rbf(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ru[i])), xs), wsu));
+            hv[i] = f2bf(__fmul_rn(__fdiv_rn(g, 1.f + __expf(-g)), u));
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (c0 + i < n) hout[static_cast<size_t>(c0 + i) * p.I] = hv[i];
+          if (p.dbg_acc || p.dbg_h) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int slot = c0 + i < n ? m_slot[c0 + i] : -1;
+              if (slot >= 0) {
+                if (p.dbg_acc) {
+                  p.dbg_acc[static_cast<size_t>(slot) * 2 * p.I + r] = static_cast<int>(rg[i]);
+                  p.dbg_acc[static_cast<size_t>(slot) * 2 * p.I + p.I + r] = static_cast<int>(ru[i]);
                 }
+                if (p.dbg_h) p.dbg_h[static_cast<size_t>(slot) * p.I + r] = hv[i];
               }
             }
           }
         }
       } else {
         const float ws = shared_e ? p.s_w_sh[r] : p.s_w[static_cast<size_t>(e) * p.w_rows + r];
+        bf16* __restrict__ cache = p.cache + r;
         for (int c0 = 0; c0 < n; c0 += 16) {
           uint32_t ra[16];
           tmem_ld16(taddr + c0, ra);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int col = c0 + i;
-            if (col < n) {
-              const int row = row0 + col;
-              const int slot = p.L.slot_of_row[row];
-              if (slot >= 0 && slot < p.total_rows) {
-                const float y = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ra[i])), p.a_scale[row]), ws);
-                p.cache[static_cast<size_t>(slot) * p.H + r] = f2bf(__fmul_rn(y, p.L.wt_of_row[row]));
-              }
-            }
+            const int slot = m_slot[c0 + i];
+            const float y = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ra[i])), ms[c0 + i]), ws);
+            const bf16 o = f2bf(__fmul_rn(y, m_wt[c0 + i]));
+            if (slot >= 0) cache[static_cast<size_t>(slot) * p.H] = o;
           }
         }
       }

@@ -7,118 +7,134 @@
 // FMA kernel whose summation order is part of the contract:
 //   p_s  = fma chain from 0 over k = 128 s .. 128 s + 127 (ascending), s = 0 .. H/128 - 1
 //   logit = ((p_0 + p_1) + p_2) + ... ; bias added last.
-// Sixteen-thread groups own one 128-deep slice each, so a 2048-deep dot product is 128 dependent
-// FMAs long instead of 2048; the slices meet in shared memory and are added in slice order.
+// Each 128-deep slice is computed by its own CTAs (a 2048-deep dot product is then 128 dependent
+// FMAs long and 16 times more parallel); the top-k kernel adds the slice partials in slice order.
 #include "common.cuh"
 #include "host.h"
 
 namespace b200 {
 
-constexpr int RT_TOK = 16, RT_EXP = 16, RT_SLICE = 128, RT_THREADS = 256;
+constexpr int RT_TOK = 64, RT_EXP = 64, RT_SLICE = 128, RT_THREADS = 256, RT_PITCH = RT_SLICE + 4;
+constexpr int RT_SMEM = 2 * RT_TOK * RT_PITCH * 4;
 
-// grid (ceil(T/16), E/16, ceil(nslices/16)); block 256 = 16 slices x (4 x 4 thread tiles of 4 x 4 outputs)
-__global__ void __launch_bounds__(RT_THREADS) router_logits_kernel(const bf16* __restrict__ x,
-                                                                   const float* __restrict__ wr,
-                                                                   const float* __restrict__ bias, int T, int H, int E,
-                                                                   float* __restrict__ logits) {
-  __shared__ float part[16][RT_TOK][RT_EXP + 1];
+// One CTA = a 64-token x 64-expert tile of ONE 128-deep k slice: both operand tiles are staged in
+// shared memory as fp32 (rows padded to 132 floats so 16-byte reads of consecutive rows hit
+// different banks), each thread owns 4 tokens x 4 experts and runs their 16 fma chains over the
+// slice in ascending k.  Slice partials go to `part[s][t][e]`; the top-k kernel adds them in slice
+// order.  grid (ceil(T/64), E/64, H/128).
+__global__ void __launch_bounds__(RT_THREADS) router_partials_kernel(const bf16* __restrict__ x,
+                                                                     const float* __restrict__ wr, int T, int H,
+                                                                     int E, float* __restrict__ part) {
+  extern __shared__ float rt_smem[];
+  float* xs = rt_smem;                       // [64][132]
+  float* ws = rt_smem + RT_TOK * RT_PITCH;   // [64][132]
   const int tid = threadIdx.x;
-  const int s_local = tid >> 4;            // slice owned inside a 16-slice pass
-  const int ty = (tid >> 2) & 3, tx = tid & 3;
-  const int t0 = blockIdx.x * RT_TOK + ty * 4, e0 = blockIdx.y * RT_EXP + tx * 4;
-  const int nslices = H / RT_SLICE;
-  const int ot = tid >> 4, oe = tid & 15;  // output owned in the combine phase
-  float total = 0.f;
-  for (int sbase = 0; sbase < nslices; sbase += 16) {
-    const int s = sbase + s_local;
-    float acc[4][4];
+  const int t0 = blockIdx.x * RT_TOK, e0 = blockIdx.y * RT_EXP, s = blockIdx.z;
+  // stage: 64 rows x 128 k of x (bf16 -> fp32) and of wr
+  for (int i = tid; i < RT_TOK * (RT_SLICE / 8); i += RT_THREADS) {
+    const int r = i >> 4, c = (i & 15) * 8;
+    const int t = min(t0 + r, T - 1);  // rows past T repeat the last row and are dropped at the store
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H + s * RT_SLICE + c));
+    float* d = xs + r * RT_PITCH + c;
+    *reinterpret_cast<float4*>(d) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+    *reinterpret_cast<float4*>(d + 4) = make_float4(bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w));
+  }
+  for (int i = tid; i < RT_EXP * (RT_SLICE / 4); i += RT_THREADS) {
+    const int r = i >> 5, c = (i & 31) * 4;
+    *reinterpret_cast<float4*>(ws + r * RT_PITCH + c) =
+        __ldg(reinterpret_cast<const float4*>(wr + static_cast<size_t>(e0 + r) * H + s * RT_SLICE + c));
+  }
+  __syncthreads();
+  const int ty = tid >> 4, tx = tid & 15;  // tokens ty + 16 i, experts tx + 16 j
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
+  for (int k = 0; k < RT_SLICE; k += 4) {
+    float4 xv[4], wv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) xv[i] = *reinterpret_cast<const float4*>(xs + (ty + 16 * i) * RT_PITCH + k);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const float4*>(ws + (tx + 16 * j) * RT_PITCH + k);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-    if (s < nslices) {
-      const bf16* xp[4];
-      const float* wp[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int t = min(t0 + i, T - 1);  // rows past T are computed on a clamped row and dropped
-        xp[i] = x + static_cast<size_t>(t) * H + s * RT_SLICE;
-        wp[i] = wr + static_cast<size_t>(e0 + i) * H + s * RT_SLICE;
+      for (int j = 0; j < 4; ++j) {
+        acc[i][j] = __fmaf_rn(xv[i].x, wv[j].x, acc[i][j]);
+        acc[i][j] = __fmaf_rn(xv[i].y, wv[j].y, acc[i][j]);
+        acc[i][j] = __fmaf_rn(xv[i].z, wv[j].z, acc[i][j]);
+        acc[i][j] = __fmaf_rn(xv[i].w, wv[j].w, acc[i][j]);
       }
-#pragma unroll 2
-      for (int k = 0; k < RT_SLICE; k += 8) {
-        float xv[4][8], wv[4][8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4 xr = __ldg(reinterpret_cast<const uint4*>(xp[i] + k));
-          xv[i][0] = bf_lo(xr.x); xv[i][1] = bf_hi(xr.x); xv[i][2] = bf_lo(xr.y); xv[i][3] = bf_hi(xr.y);
-          xv[i][4] = bf_lo(xr.z); xv[i][5] = bf_hi(xr.z); xv[i][6] = bf_lo(xr.w); xv[i][7] = bf_hi(xr.w);
-          const float4 w0 = __ldg(reinterpret_cast<const float4*>(wp[i] + k));
-          const float4 w1 = __ldg(reinterpret_cast<const float4*>(wp[i] + k + 4));
-          wv[i][0] = w0.x; wv[i][1] = w0.y; wv[i][2] = w0.z; wv[i][3] = w0.w;
-          wv[i][4] = w1.x; wv[i][5] = w1.y; wv[i][6] = w1.z; wv[i][7] = w1.w;
-        }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(xv[i][kk], wv[j][kk], acc[i][j]);
-      }
-    }
-    __syncthreads();  // previous pass's partials have been consumed
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) part[s_local][ty * 4 + i][tx * 4 + j] = acc[i][j];
-    __syncthreads();
-    const int lim = min(16, nslices - sbase);
-    for (int q = 0; q < lim; ++q) {
-      const float pv = part[q][ot][oe];
-      total = (sbase + q == 0) ? pv : __fadd_rn(total, pv);
-    }
   }
-  const int t = blockIdx.x * RT_TOK + ot, e = blockIdx.y * RT_EXP + oe;
-  if (t < T) {
-    if (bias) total = __fadd_rn(total, __ldg(bias + e));
-    logits[static_cast<size_t>(t) * E + e] = total;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = t0 + ty + 16 * i;
+    if (t < T)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        part[(static_cast<size_t>(s) * T + t) * E + e0 + tx + 16 * j] = acc[i][j];
   }
 }
 
-// Sortable key: larger logit first, then smaller expert id; -0 == +0; NaN ranks below everything
-// (the reference's 24-bit key has the same order: qk_route.cu:71-75,142).
-__device__ __forceinline__ unsigned long long topk_key(float v, int id) {
-  uint32_t u;
-  if (v != v) {
-    u = 0u;
-  } else {
-    v += 0.f;  // -0 -> +0
-    u = __float_as_uint(v);
-    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-    if (u == 0u) u = 1u;
-  }
-  return (static_cast<unsigned long long>(u) << 32) | static_cast<uint32_t>(0xffffffffu - static_cast<uint32_t>(id));
+// Sortable 32-bit key of a logit: larger first; -0 == +0; NaN ranks below every number (key 1);
+// key 0 marks an entry that is absent or already picked.  Ties between equal keys go to the
+// smaller expert id (the reference's order: qk_route.cu:71-75,142).
+__device__ __forceinline__ uint32_t topk_key(float v) {
+  if (v != v) return 1u;
+  v += 0.f;  // -0 -> +0
+  uint32_t u = __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return u < 2u ? 2u : u;
+}
+__device__ __forceinline__ float topk_unkey(uint32_t u) {
+  return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
 }
 
-// one warp per token; lane l holds experts l, l + 32, ...
+// One warp per token; lane l holds experts l, l + 32, ...  Adds the slice partials in slice order
+// (+ bias), optionally stores the logits, then softmax + K rounds of (warp max of the value key,
+// warp min of the id among the lanes that hold it), both single redux instructions.
 template <int PER_LANE>
-__global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits, int T, int E, int K,
-                                                          int round_bf16, int32_t* __restrict__ ids,
-                                                          float* __restrict__ wts) {
+__global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ part, int nslices,
+                                                          const float* __restrict__ bias, int T, int E, int K,
+                                                          int round_bf16, float* __restrict__ logits,
+                                                          int32_t* __restrict__ ids, float* __restrict__ wts) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
   float xv[PER_LANE];
-  unsigned long long key[PER_LANE];
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) xv[j] = 0.f;
+#pragma unroll 4
+  for (int s = 0; s < nslices; ++s) {
+    const float* pr = part + (static_cast<size_t>(s) * T + t) * E;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E) {
+        const float pv = pr[e];
+        xv[j] = s == 0 ? pv : __fadd_rn(xv[j], pv);
+      }
+    }
+  }
+  uint32_t key[PER_LANE];
   float mx = -INFINITY;
 #pragma unroll
   for (int j = 0; j < PER_LANE; ++j) {
     const int e = lane + 32 * j;
-    float v = e < E ? logits[static_cast<size_t>(t) * E + e] : -INFINITY;
-    if (round_bf16) v = rbf(v);
+    float v = xv[j];
+    if (e < E) {
+      if (bias) v = __fadd_rn(v, __ldg(bias + e));
+      if (logits) logits[static_cast<size_t>(t) * E + e] = v;
+      if (round_bf16) v = rbf(v);
+      key[j] = topk_key(v);
+      if (v == v) mx = fmaxf(mx, v + 0.f);
+    } else {
+      key[j] = 0u;
+      v = __int_as_float(0x7fc00000);
+    }
     xv[j] = v;
-    key[j] = e < E ? topk_key(v, e) : 0ull;
-    if (v == v) mx = fmaxf(mx, v);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(FULL_MASK, mx, o));
@@ -126,46 +142,42 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
 #pragma unroll
   for (int j = 0; j < PER_LANE; ++j) {
     const float v = xv[j];
-    const float ex = (v == v && lane + 32 * j < E) ? expf(v - mx) : 0.f;
-    xv[j] = ex;
-    sum += ex;
+    sum += (v == v) ? expf((v + 0.f) - mx) : 0.f;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(FULL_MASK, sum, o);
-  float my_w = 0.f;   // lane k keeps the k-th pick
+  uint32_t bk = 0u;
+  int bj = 0;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j)
+    if (key[j] > bk) {
+      bk = key[j];
+      bj = j;
+    }
+  float my_w = 0.f, tot = 0.f;
   int my_id = 0;
-  float tot = 0.f;
   for (int k = 0; k < K; ++k) {
-    unsigned long long best = 0ull;
-    int bj = 0;
-#pragma unroll
-    for (int j = 0; j < PER_LANE; ++j)
-      if (key[j] > best) {
-        best = key[j];
-        bj = j;
-      }
-    unsigned long long win = best;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const unsigned long long other = __shfl_xor_sync(FULL_MASK, win, o);
-      win = other > win ? other : win;
-    }
-    const int id = static_cast<int>(0xffffffffu - static_cast<uint32_t>(win & 0xffffffffull));
-    const int owner = id & 31;
-    float pr = 0.f;
-    if (lane == owner) {
-#pragma unroll
-      for (int j = 0; j < PER_LANE; ++j)
-        if (j == bj) {
-          pr = __fdiv_rn(xv[j], sum);
-          key[j] = 0ull;
-        }
-    }
-    pr = __shfl_sync(FULL_MASK, pr, owner);
+    const uint32_t m = __reduce_max_sync(FULL_MASK, bk);
+    const uint32_t cand = (bk == m) ? static_cast<uint32_t>(lane + 32 * bj) : 0x7fffffffu;
+    const int id = static_cast<int>(__reduce_min_sync(FULL_MASK, cand));
+    const float pr = m <= 1u ? 0.f : __fdiv_rn(expf(topk_unkey(m) - mx), sum);
     tot = __fadd_rn(tot, pr);
     if (lane == k) {
       my_w = pr;
       my_id = id;
+    }
+    if (lane == (id & 31)) {  // the owner drops the pick and rescans its entries
+      const int dead = id >> 5;
+      bk = 0u;
+      bj = 0;
+#pragma unroll
+      for (int j = 0; j < PER_LANE; ++j) {
+        if (j == dead) key[j] = 0u;
+        if (key[j] > bk) {
+          bk = key[j];
+          bj = j;
+        }
+      }
     }
   }
   const float den = tot > 0.f ? tot : 1.f;
@@ -176,73 +188,125 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
 }
 
 // ---- routing lists ---------------------------------------------------------------------------------
-// One CTA.  Warp 0 ranks the routed pairs in slot order (stable inside an expert) with match.any;
-// the whole CTA then scatters rows and writes the block list.
-constexpr int LISTS_THREADS = 1024, LISTS_MAX_E = 1024;
+// One CTA of 32 warps.  The local expert of every routed pair is staged in shared memory; warp w
+// ranks its contiguous segment of pairs with match.any against its own counters, a per-expert scan
+// over the 32 warps turns those into stable ranks (ascending slot order inside an expert), then
+// rows are scattered and the block list is written.
+constexpr int LISTS_THREADS = 1024, LISTS_WARPS = 32, LISTS_MAX_E = 1024;
 
 __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t* __restrict__ ids,
                                                                   const float* __restrict__ wts,
                                                                   const int64_t* __restrict__ pos, int T, int K,
                                                                   int e_lo, int E_local, int block_rows,
                                                                   int with_shared, int max_blocks, MoeLists L) {
-  __shared__ int cnt[LISTS_MAX_E + 1];
-  __shared__ int off[LISTS_MAX_E + 2];
-  __shared__ int bstart[LISTS_MAX_E + 2];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  extern __shared__ int lists_smem[];
   const int P = T * K;
-  for (int e = tid; e <= E_local; e += LISTS_THREADS) cnt[e] = 0;
+  const int E1 = E_local + 1;
+  int* cnt = lists_smem;                   // [E1]   rows per expert
+  int* off = cnt + E1;                     // [E1+1] first row per expert
+  int* bstart = off + E1 + 1;              // [E1+1] first block per expert
+  int* wsum = bstart + E1 + 1;             // [64]   scan scratch
+  uint16_t* cntw = reinterpret_cast<uint16_t*>(wsum + 64);        // [32][E1] per-warp counters -> bases
+  int16_t* sid = reinterpret_cast<int16_t*>(cntw + LISTS_WARPS * E1);  // [P] local expert or -1
+  uint16_t* srank = reinterpret_cast<uint16_t*>(sid + P);              // [P] rank inside the warp segment
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  for (int i = tid; i < LISTS_WARPS * E1; i += LISTS_THREADS) cntw[i] = 0;
+  for (int p = tid; p < P; p += LISTS_THREADS) {
+    const int e = ids[p] - e_lo;
+    const bool ok = (pos == nullptr) || (pos[p / K] != 0);
+    sid[p] = (ok && e >= 0 && e < E_local) ? static_cast<int16_t>(e) : static_cast<int16_t>(-1);
+  }
   for (int r = tid; r < T * (K + 1); r += LISTS_THREADS) {
     L.slot_of_row[r] = -1;
     L.wt_of_row[r] = 0.f;
   }
   __syncthreads();
-  if (warp == 0) {
-    for (int p0 = 0; p0 < P; p0 += 32) {
+  const int seg = ((P + LISTS_WARPS - 1) / LISTS_WARPS + 31) & ~31;
+  {
+    uint16_t* mine = cntw + warp * E1;
+    const int p_end = min(P, (warp + 1) * seg);
+    for (int p0 = warp * seg; p0 < p_end; p0 += 32) {
       const int p = p0 + lane;
-      int le = -1;
-      if (p < P) {
-        const int e = ids[p] - e_lo;
-        const bool ok = (pos == nullptr) || (pos[p / K] != 0);
-        if (ok && e >= 0 && e < E_local) le = e;
-      }
+      const int le = p < p_end ? sid[p] : -1;
       const unsigned same = __match_any_sync(FULL_MASK, le);
       const int before = __popc(same & ((1u << lane) - 1u));
       int base = 0;
-      if (le >= 0) base = cnt[le];
+      if (le >= 0) base = mine[le];
       __syncwarp();
-      if (le >= 0 && before == 0) cnt[le] = base + __popc(same);
+      if (le >= 0 && before == 0) mine[le] = static_cast<uint16_t>(base + __popc(same));
       __syncwarp();
-      if (p < P) L.row_of_pair[p] = le >= 0 ? base + before : -1;  // rank for now
+      if (p < p_end) srank[p] = static_cast<uint16_t>(base + before);
     }
   }
   __syncthreads();
-  if (tid == 0) {
-    int run = 0, blocks = 0;
-    for (int e = 0; e < E_local; ++e) {
-      off[e] = run;
-      bstart[e] = blocks;
-      run += cnt[e];
-      blocks += (cnt[e] + block_rows - 1) / block_rows;
+  // per expert: exclusive scan of the warp counters -> base of each warp's segment; total -> cnt
+  int c = 0, nb = 0;
+  if (tid < E1) {
+    if (tid < E_local) {
+      int run = 0;
+      for (int w = 0; w < LISTS_WARPS; ++w) {
+        const int v = cntw[w * E1 + tid];
+        cntw[w * E1 + tid] = static_cast<uint16_t>(run);
+        run += v;
+      }
+      c = run;
+    } else {
+      c = with_shared ? T : 0;
     }
-    off[E_local] = P;  // the shared expert's rows start after the routed region
-    cnt[E_local] = with_shared ? T : 0;
-    bstart[E_local] = blocks;
-    blocks += (cnt[E_local] + block_rows - 1) / block_rows;
-    off[E_local + 1] = P + cnt[E_local];
-    bstart[E_local + 1] = blocks;
-    L.nblocks[0] = blocks <= max_blocks ? blocks : 0;
+    cnt[tid] = c;
+    nb = (c + block_rows - 1) / block_rows;
+  }
+  // block-wide exclusive scans of (rows of routed experts, blocks) over experts
+  int rows_incl = (tid < E_local) ? c : 0, blks_incl = nb;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(FULL_MASK, rows_incl, o), b2 = __shfl_up_sync(FULL_MASK, blks_incl, o);
+    if (lane >= o) {
+      rows_incl += a;
+      blks_incl += b2;
+    }
+  }
+  if (lane == 31) {
+    wsum[warp] = rows_incl;
+    wsum[32 + warp] = blks_incl;
   }
   __syncthreads();
-  for (int e = tid; e <= E_local; e += LISTS_THREADS) L.counts[e] = cnt[e];
-  for (int e = tid; e <= E_local + 1; e += LISTS_THREADS) L.offsets[e] = off[e];
+  if (warp == 0) {
+    int a = wsum[lane], b2 = wsum[32 + lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a2 = __shfl_up_sync(FULL_MASK, a, o), b3 = __shfl_up_sync(FULL_MASK, b2, o);
+      if (lane >= o) {
+        a += a2;
+        b2 += b3;
+      }
+    }
+    wsum[lane] = a;
+    wsum[32 + lane] = b2;
+  }
+  __syncthreads();
+  const int rows_excl = rows_incl - ((tid < E_local) ? c : 0) + (warp ? wsum[warp - 1] : 0);
+  const int blks_excl = blks_incl - nb + (warp ? wsum[32 + warp - 1] : 0);
+  const int total_blocks = wsum[63];
+  if (tid < E1) {
+    off[tid] = tid < E_local ? rows_excl : P;  // the shared expert's rows start after the routed region
+    bstart[tid] = blks_excl;
+    L.counts[tid] = c;
+    L.offsets[tid] = off[tid];
+    if (tid == E_local) L.offsets[E1] = P + c;
+  }
+  if (tid == 0) L.nblocks[0] = total_blocks <= max_blocks ? total_blocks : 0;
+  __syncthreads();
   for (int p = tid; p < P; p += LISTS_THREADS) {
-    const int rank = L.row_of_pair[p];
-    if (rank >= 0) {
-      const int row = off[ids[p] - e_lo] + rank;
-      L.row_of_pair[p] = row;
+    const int e = sid[p];
+    int row = -1;
+    if (e >= 0) {
+      row = off[e] + cntw[(p / seg) * E1 + e] + srank[p];
       L.slot_of_row[row] = p;
       L.wt_of_row[row] = wts[p];
     }
+    L.row_of_pair[p] = row;
   }
   if (with_shared)
     for (int t = tid; t < T; t += LISTS_THREADS) {
@@ -250,43 +314,63 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
       L.slot_of_row[P + t] = ok ? P + t : -1;
       L.wt_of_row[P + t] = 1.f;
     }
-  if (bstart[E_local + 1] <= max_blocks)
-    for (int e = tid; e <= E_local; e += LISTS_THREADS) {
-      const int c = cnt[e];
-      int b = bstart[e];
-      for (int r0 = 0; r0 < c; r0 += block_rows, ++b) {
-        L.blk_expert[b] = e;
-        L.blk_row0[b] = off[e] + r0;
-        L.blk_rows[b] = min(block_rows, c - r0);
-      }
+  if (total_blocks <= max_blocks && tid < E1) {
+    int b = bstart[tid];
+    for (int r0 = 0; r0 < c; r0 += block_rows, ++b) {
+      L.blk_expert[b] = tid;
+      L.blk_row0[b] = off[tid] + r0;
+      L.blk_rows[b] = min(block_rows, c - r0);
     }
+  }
+}
+
+static size_t lists_smem_bytes(int T, int K, int E_local) {
+  const size_t E1 = E_local + 1, P = static_cast<size_t>(T) * K;
+  return (E1 + 2 * (E1 + 1) + 64) * 4 + LISTS_WARPS * E1 * 2 + P * 4 + 16;
 }
 
 }  // namespace b200
 
 using namespace b200;
 
+extern "C" size_t b200_router_scratch_bytes(int T, int H, int E) {
+  if (T <= 0 || H <= 0 || E <= 0 || H % RT_SLICE) return 0;
+  return static_cast<size_t>(H / RT_SLICE) * T * E * sizeof(float);
+}
+
 extern "C" int b200_router(const void* x, const float* wr, const float* bias, int T, int H, int E, int K, int flags,
-                           float* logits, int32_t* ids, float* wts, void* stream) {
-  if (!x || !wr || !logits || !ids || !wts) return fail(B200_E_ARG, "b200_router: null pointer");
-  if (T < 0 || H <= 0 || H % RT_SLICE || E <= 0 || E % 32 || E > 1024 || K <= 0 || K > 32 || K > E)
-    return fail(B200_E_ARG, "b200_router: need H %% 128 == 0, E %% 32 == 0, E <= 1024, 1 <= K <= 32 (T=%d H=%d E=%d K=%d)",
+                           float* logits, int32_t* ids, float* wts, void* scratch, size_t scratch_bytes,
+                           void* stream) {
+  if (!x || !wr || !ids || !wts || !scratch) return fail(B200_E_ARG, "b200_router: null pointer");
+  if (T < 0 || H <= 0 || H % RT_SLICE || E <= 0 || E % RT_EXP || E > 1024 || K <= 0 || K > 32 || K > E)
+    return fail(B200_E_ARG, "b200_router: need H %% 128 == 0, E %% 64 == 0, E <= 1024, 1 <= K <= 32 (T=%d H=%d E=%d K=%d)",
                 T, H, E, K);
-  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wr)) & 15)
-    return fail(B200_E_ALIGN, "b200_router: x and wr must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wr) | reinterpret_cast<uintptr_t>(scratch)) & 15)
+    return fail(B200_E_ALIGN, "b200_router: x, wr and scratch must be 16-byte aligned");
   if (T == 0) return 0;
+  if (scratch_bytes < b200_router_scratch_bytes(T, H, E))
+    return fail(B200_E_WS, "b200_router: scratch %zu < %zu bytes", scratch_bytes, b200_router_scratch_bytes(T, H, E));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  dim3 grid((T + RT_TOK - 1) / RT_TOK, E / RT_EXP);
-  router_logits_kernel<<<grid, RT_THREADS, 0, st>>>(static_cast<const bf16*>(x), wr, bias, T, H, E, logits);
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaFuncSetAttribute(router_partials_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM);
+    attr_done[dev] = true;
+  }
+  float* part = static_cast<float*>(scratch);
+  const int nslices = H / RT_SLICE;
+  dim3 grid((T + RT_TOK - 1) / RT_TOK, E / RT_EXP, nslices);
+  router_partials_kernel<<<grid, RT_THREADS, RT_SMEM, st>>>(static_cast<const bf16*>(x), wr, T, H, E, part);
   const int per_lane = (E + 31) / 32;
-  dim3 g2((T + 7) / 8);
+  dim3 g2((T + 3) / 4);
   const int rb = flags & 1;
   if (per_lane <= 8)
-    router_topk_kernel<8><<<g2, 256, 0, st>>>(logits, T, E, K, rb, ids, wts);
+    router_topk_kernel<8><<<g2, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
   else if (per_lane <= 16)
-    router_topk_kernel<16><<<g2, 256, 0, st>>>(logits, T, E, K, rb, ids, wts);
+    router_topk_kernel<16><<<g2, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
   else
-    router_topk_kernel<32><<<g2, 256, 0, st>>>(logits, T, E, K, rb, ids, wts);
+    router_topk_kernel<32><<<g2, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
   return launch_status("b200_router");
 }
 
@@ -308,7 +392,17 @@ extern "C" int b200_moe_build_lists(const int32_t* ids, const float* wts, const 
                 block_rows);
   MoeLists L{lists->counts,     lists->offsets,  lists->row_of_pair, lists->slot_of_row, lists->wt_of_row,
              lists->blk_expert, lists->blk_row0, lists->blk_rows,    lists->nblocks};
-  moe_lists_kernel<<<1, LISTS_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+  const size_t smem = lists_smem_bytes(T, K, E_local);
+  if (smem > 200 * 1024 || T * (K + 1) > 65535 * 4)
+    return fail(B200_E_ARG, "b200_moe_build_lists: T*K = %d is above the single-CTA limit", T * K);
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaFuncSetAttribute(moe_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    attr_done[dev] = true;
+  }
+  moe_lists_kernel<<<1, LISTS_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(
       ids, wts, pos, T, K, e_lo, E_local, block_rows, with_shared, b200_moe_max_blocks(T, K, E_local, block_rows), L);
   return launch_status("b200_moe_build_lists");
 }

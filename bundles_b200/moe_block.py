@@ -32,7 +32,9 @@ class MoeBlockW8A8:
             b = dict(lists=ops.RoutingLists(T, K, self.E_local, 128, device),
                      ws=ops.moe_w8a8_workspace(T, self.H, self.I, K, device),
                      cache=torch.zeros(T * (K + 1), self.H, dtype=torch.bfloat16, device=device),
-                     logits=torch.empty(T, self.wr.shape[0], dtype=torch.float32, device=device),
+                     scratch=ops.router_scratch(T, self.H, self.wr.shape[0], device),
+                     ids=torch.empty(T, K, dtype=torch.int32, device=device),
+                     wts=torch.empty(T, K, dtype=torch.float32, device=device),
                      out=torch.empty(T, self.H, dtype=torch.bfloat16, device=device))
             self._ws[T] = b
         return b
@@ -40,7 +42,8 @@ class MoeBlockW8A8:
     def forward(self, x: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
         T = x.shape[0]
         b = self._buffers(T, x.device)
-        _, ids, wts = ops.router(x, self.wr, self.top_k, self.bias, self.round_bf16, logits=b["logits"])
+        _, ids, wts = ops.router(x, self.wr, self.top_k, self.bias, self.round_bf16, scratch=b["scratch"],
+                                 want_logits=False)
         ops.build_lists(ids, wts, b["lists"], positions, e_lo=self.e_lo, with_shared=self.w.sh13 is not None)
         ops.moe_w8a8(x, self.w, b["lists"], cache=b["cache"], ws=b["ws"], status=self.status)
         return ops.moe_combine(b["cache"], x, self.gate_w if self.w.sh13 is not None else None, self.top_k, positions,

@@ -54,13 +54,15 @@ const char* b200_last_error(void);
  * that expert ids are reproducible bit for bit.  Then softmax over E, top-k by largest logit with
  * ties to the smaller expert id (-0 == +0, NaN lowest), weights renormalised over the picks
  * (i8x_decode.py:99-117).
- *   x bf16 [T,H]; wr fp32 [E,H]; bias fp32 [E] or NULL; logits fp32 [T,E] (output, also scratch);
- *   ids int32 [T,K]; wts fp32 [T,K].  H % 128 == 0, E % 32 == 0, E <= 1024, K <= 32.
+ *   x bf16 [T,H]; wr fp32 [E,H]; bias fp32 [E] or NULL; logits fp32 [T,E] (output) or NULL;
+ *   ids int32 [T,K]; wts fp32 [T,K]; scratch: b200_router_scratch_bytes() bytes (slice partials),
+ *   16-byte aligned.  H % 128 == 0, E % 64 == 0, E <= 1024, K <= 32.
  *   flags bit 0: round the logits to bf16 before the softmax / top-k (the reference's behaviour,
  *   i8x_decode.py:100).
  */
+size_t b200_router_scratch_bytes(int T, int H, int E);
 int b200_router(const void* x, const float* wr, const float* bias, int T, int H, int E, int K, int flags,
-                float* logits, int32_t* ids, float* wts, void* stream);
+                float* logits, int32_t* ids, float* wts, void* scratch, size_t scratch_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Routing lists.  Replaces i8x_dec_lists (i8x_decode.py:264-289) and the list-building tail of

@@ -37,7 +37,7 @@ def test_prototypes_cover_header(lib):
 
 def test_version_and_error_text(lib):
     assert lib.b200_abi_version() == 1
-    rc = lib.b200_router(None, None, None, 4, 2048, 512, 10, 0, None, None, None, None)
+    rc = lib.b200_router(None, None, None, 4, 2048, 512, 10, 0, None, None, None, None, 0, None)
     assert rc == -1
     assert b"b200_router" in lib.b200_last_error()
 
@@ -45,11 +45,14 @@ def test_version_and_error_text(lib):
 def test_argument_checks_return_codes(lib):
     one = C.c_void_p(4096)  # never dereferenced: the checks fail first
     # H not a multiple of 128
-    assert lib.b200_router(one, one, None, 4, 100, 512, 10, 0, one, one, one, None) == -1
+    assert lib.b200_router(one, one, None, 4, 100, 512, 10, 0, one, one, one, one, 1 << 30, None) == -1
     # K > E
-    assert lib.b200_router(one, one, None, 4, 2048, 32, 33, 0, one, one, one, None) == -1
+    assert lib.b200_router(one, one, None, 4, 2048, 64, 65, 0, one, one, one, one, 1 << 30, None) == -1
     # misaligned x
-    assert lib.b200_router(C.c_void_p(4100), one, None, 4, 2048, 512, 10, 0, one, one, one, None) == -2
+    assert lib.b200_router(C.c_void_p(4100), one, None, 4, 2048, 512, 10, 0, one, one, one, one, 1 << 30, None) == -2
+    # scratch too small
+    assert lib.b200_router(one, one, None, 4, 2048, 512, 10, 0, one, one, one, one, 64, None) == -3
+    assert lib.b200_router_scratch_bytes(256, 2048, 512) == 16 * 256 * 512 * 4
     assert lib.b200_moe_max_blocks(256, 10, 512, 128) >= 512 + 20 + 2
     assert lib.b200_moe_w8a8_workspace_bytes(256, 2048, 512, 10) > 256 * 11 * 2048
     assert lib.b200_moe_combine(None, None, None, None, 1, 2048, 10, None, None) == -1

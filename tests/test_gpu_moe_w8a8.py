@@ -72,7 +72,7 @@ def test_small_block():
 
 def test_skewed_load_spills_over_one_block():
     # Zipf skew with few experts: the hottest expert gets more than 128 tokens -> several N blocks
-    cfg = synth.moe_w8a8(seed=12, T=256, E=32, zipf_s=1.1)
+    cfg = synth.moe_w8a8(seed=12, T=256, E=64, zipf_s=1.1)
     _check(cfg, 10)
 
 
@@ -90,7 +90,7 @@ def test_block_rows_16():
 
 
 def test_single_token_top1():
-    cfg = synth.moe_w8a8(seed=15, T=1, E=32, zipf_s=0)
+    cfg = synth.moe_w8a8(seed=15, T=1, E=64, zipf_s=0)
     _check(cfg, 1)
 
 
