@@ -25,6 +25,8 @@ PROTOTYPES = {
     "b200_last_error": (C.c_char_p, []),
     "b200_router_scratch_bytes": (sz, [i32, i32, i32]),
     "b200_router": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, sz, vp]),
+    "b200_router_static_max_scratch_bytes": (sz, []),
+    "b200_router_static": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
     "b200_moe_max_blocks": (i32, [i32, i32, i32, i32]),
     "b200_moe_build_lists": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, i32, C.POINTER(MoeLists), vp]),
     "b200_moe_w8a8_workspace_bytes": (sz, [i32, i32, i32, i32]),

@@ -12,6 +12,8 @@
 #include "common.cuh"
 #include "host.h"
 
+#include <mutex>
+
 namespace b200 {
 
 constexpr int RT_TOK = 64, RT_EXP = 64, RT_SLICE = 128, RT_THREADS = 256, RT_PITCH = RT_SLICE + 4;
@@ -372,6 +374,58 @@ extern "C" int b200_router(const void* x, const float* wr, const float* bias, in
   else
     router_topk_kernel<32><<<g2, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
   return launch_status("b200_router");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Router variant for callers that cannot allocate device memory.
+//
+// Some hosts of this library are handed nothing but their input and output buffers: a plugin slot
+// that a serving engine calls once per decode step has no allocator of its own (the engine planned
+// every byte of device memory at start-up and owns the pool), and a cudaMalloc from inside the step
+// would stall the whole device or break the engine's memory budget.  For them the slice partials of
+// the gate live in the array below instead of a caller-provided scratch buffer.  The array is part
+// of the loaded library image: every GPU that loads the library holds these 2 MiB until the process
+// exits.  It is shared by all calls and keeps the previous call's partials; nothing in it has to
+// start at zero because the gate kernel overwrites every partial the top-k kernel reads.  Two calls
+// that overlap on the GPU (different streams, or different host threads) would race on it.
+constexpr size_t ROUTER_STATIC_SCRATCH_BYTES = size_t(2) << 20;  // e.g. 64 tokens x 512 experts x 16 slices x 4 B
+static __device__ __align__(256) unsigned char g_router_static_scratch[ROUTER_STATIC_SCRATCH_BYTES];
+
+extern "C" size_t b200_router_static_max_scratch_bytes(void) { return ROUTER_STATIC_SCRATCH_BYTES; }
+
+extern "C" int b200_router_static(const void* x, const float* wr, const float* bias, int T, int H, int E, int K,
+                                  int flags, float* logits, int32_t* ids, float* wts, void* stream) {
+  if (T < 0 || H <= 0 || E <= 0 || H % RT_SLICE)
+    return fail(B200_E_ARG, "b200_router_static: bad shape (T=%d H=%d E=%d)", T, H, E);
+  const size_t need = static_cast<size_t>(H / RT_SLICE) * static_cast<size_t>(T) * static_cast<size_t>(E) * sizeof(float);
+  if (need > ROUTER_STATIC_SCRATCH_BYTES)
+    return fail(B200_E_WS,
+                "b200_router_static: T=%d H=%d E=%d needs %zu bytes of slice partials, the built-in scratch holds %zu; "
+                "use b200_router with a caller-provided scratch buffer",
+                T, H, E, need, ROUTER_STATIC_SCRATCH_BYTES);
+  // In host code the array's name is only a handle; the device address is looked up once per device,
+  // with that device current, and cached.
+  static void* dev_ptr[64] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess || dev < 0 || dev >= 64)
+    return fail(err != cudaSuccess ? static_cast<int>(err) : B200_E_ARG, "b200_router_static: cudaGetDevice failed: %s",
+                cudaGetErrorString(err));
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev_ptr[dev] == nullptr) {
+      void* ptr = nullptr;
+      err = cudaGetSymbolAddress(&ptr, g_router_static_scratch);
+      if (err != cudaSuccess || ptr == nullptr)
+        return fail(err != cudaSuccess ? static_cast<int>(err) : B200_E_DRIVER,
+                    "b200_router_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+      dev_ptr[dev] = ptr;
+    }
+    scratch = dev_ptr[dev];
+  }
+  return b200_router(x, wr, bias, T, H, E, K, flags, logits, ids, wts, scratch, ROUTER_STATIC_SCRATCH_BYTES, stream);
 }
 
 extern "C" int b200_moe_max_blocks(int T, int K, int E_local, int block_rows) {

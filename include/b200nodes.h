@@ -64,6 +64,25 @@ size_t b200_router_scratch_bytes(int T, int H, int E);
 int b200_router(const void* x, const float* wr, const float* bias, int T, int H, int E, int K, int flags,
                 float* logits, int32_t* ids, float* wts, void* scratch, size_t scratch_bytes, void* stream);
 
+/* Router without a scratch argument, for hosts that cannot allocate device memory.
+ * (No counterpart in the reference: its units allocate through torch.)
+ *
+ * A plugin slot that a serving engine calls per decode step gets its inputs and outputs from the
+ * engine and nothing else; the engine owns the memory pool, and a cudaMalloc inside the step would
+ * stall the device.  This entry point takes the same arguments as b200_router minus the scratch:
+ * the slice partials go to a 2 MiB array built into the library (held by every GPU that loads the
+ * library, until exit).  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - Limit: (H/128) * T * E * 4 bytes must fit in b200_router_static_max_scratch_bytes() (2 MiB,
+ *     e.g. 64 tokens x 512 experts at H = 2048); larger problems return B200_E_WS.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call before any stream capture.
+ *   - All calls share the array, and it keeps the last call's contents (nothing needs clearing:
+ *     every partial that is read was written by the same call).  Calls that overlap on the GPU race.
+ */
+size_t b200_router_static_max_scratch_bytes(void);
+int b200_router_static(const void* x, const float* wr, const float* bias, int T, int H, int E, int K, int flags,
+                       float* logits, int32_t* ids, float* wts, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Routing lists.  Replaces i8x_dec_lists (i8x_decode.py:264-289) and the list-building tail of
  * route_kernel (qk_route.cu:297-357).
