@@ -216,6 +216,10 @@ def main():
     down_bytes = active * (H * I + H * 4) + rows * (I + 4 + 8) + rows * H * 2
     peak, which = peaks()
     achieved = up_bytes / (ms_up * 1e-3) / 1e9
+    # DRAM bytes of one launch of this kernel from an ncu capture of the same workload
+    # (profiles/moe_w8a8_decode_t256.md): read + write = 1.009 x the algorithmic bytes of that launch;
+    # traffic grows with the experts hit, so it is scaled by this launch's algorithmic bytes.
+    traffic = 1.009 * up_bytes
 
     if rank != 0:
         if world > 1:
@@ -227,13 +231,14 @@ def main():
         "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens_per_gpu": T,
                    "parallelism": "1 GPU" if world == 1 else f"{world} replicas, no data-path collective",
-                   "l2": "weights streamed per step (1.6 GB) exceed the 126 MB L2; no flush"},
+                   "l2": f"{active} experts hit: {(up_bytes + down_bytes) / 1e6:.0f} MB of weights and rows streamed per "
+                         "step, more than the 126 MB L2; no flush"},
         "e2e": {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2,
                 "d2h_bytes_per_step": T * H * 2, "ms_per_step": ms_e2e},
         "gpu_launches": block.launches_per_call * args.steps,
         "roofline": {"kernel": "moe_gemm_i8_kernel<up> (gate/up GEMM + SwiGLU)", "bound": "hbm",
                      "achieved": achieved, "peak": peak, "peak_source": which, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "algorithmic_bytes": up_bytes, "ms": ms_up,
+                     "frac": achieved / peak, "traffic": traffic, "algorithmic_bytes": up_bytes, "ms": ms_up,
                      "active_experts": active, "rows": rows,
                      "down_kernel": {"ms": ms_down, "algorithmic_bytes": down_bytes,
                                      "achieved": down_bytes / (ms_down * 1e-3) / 1e9}},
