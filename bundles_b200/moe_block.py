@@ -15,13 +15,16 @@ from . import ops
 class MoeBlockW8A8:
     """int8 W8A8 experts (per-output-channel weight scales, per-token activation scales)."""
 
-    def __init__(self, wr, weights: ops.MoeW8A8Weights, gate_w, top_k, bias=None, e_lo=0, round_bf16=False):
+    def __init__(self, wr, weights: ops.MoeW8A8Weights, gate_w, top_k, bias=None, e_lo=0, round_bf16=False,
+                 use_graph=True):
         self.wr, self.w, self.gate_w, self.bias = wr, weights, gate_w, bias
         self.top_k, self.e_lo, self.round_bf16 = top_k, e_lo, round_bf16
         self.E_local = weights.w13.shape[0]
         self.I = weights.w2.shape[-1]
         self.H = weights.w13.shape[-1]
         self._ws = {}
+        self._graphs = {}
+        self.use_graph = use_graph
         self.status = ops.new_status(wr.device)
         self.launches_per_call = 8  # gate, top-k, lists, quant+permute, up, h-quant, down, combine
 
@@ -40,10 +43,41 @@ class MoeBlockW8A8:
         return b
 
     def forward(self, x: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
+        """One pass of the block.  With `use_graph` the eight launches of a given (T, with/without
+        positions) are captured once into a CUDA graph and replayed (the reference's ops run inside the
+        engine's captured decode graph as well, layer.py:174-189); the input is copied into the graph's
+        static buffer and the returned tensor is the graph's static output, overwritten by the next call."""
+        if not self.use_graph or torch.cuda.is_current_stream_capturing():
+            return self._forward_eager(x, positions)
+        T = x.shape[0]
+        key = (T, positions is not None)
+        g = self._graphs.get(key)
+        if g is None:
+            dev = self.wr.device
+            xs = torch.empty(x.shape, dtype=x.dtype, device=dev)
+            ps = None if positions is None else torch.empty(positions.shape, dtype=positions.dtype, device=dev)
+            xs.copy_(x)
+            if ps is not None:
+                ps.copy_(positions)
+            self._forward_eager(xs, ps)                      # warm-up: one-time attribute set-up, buffers
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self._forward_eager(xs, ps)
+            g = (graph, xs, ps, out)
+            self._graphs[key] = g
+        graph, xs, ps, out = g
+        xs.copy_(x, non_blocking=True)
+        if ps is not None:
+            ps.copy_(positions, non_blocking=True)
+        graph.replay()
+        return out
+
+    def _forward_eager(self, x: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
         T = x.shape[0]
         b = self._buffers(T, x.device)
         _, ids, wts = ops.router(x, self.wr, self.top_k, self.bias, self.round_bf16, scratch=b["scratch"],
-                                 want_logits=False)
+                                 want_logits=False, ids=b["ids"], wts=b["wts"])
         ops.build_lists(ids, wts, b["lists"], positions, e_lo=self.e_lo, with_shared=self.w.sh13 is not None)
         ops.moe_w8a8(x, self.w, b["lists"], cache=b["cache"], ws=b["ws"], status=self.status)
         return ops.moe_combine(b["cache"], x, self.gate_w if self.w.sh13 is not None else None, self.top_k, positions,

@@ -49,7 +49,8 @@ def router_scratch(T, H, E, device):
     return torch.empty(max(n, 16), dtype=torch.uint8, device=device)
 
 
-def router(x, wr, top_k, bias=None, round_bf16=False, logits=None, scratch=None, want_logits=True):
+def router(x, wr, top_k, bias=None, round_bf16=False, logits=None, scratch=None, want_logits=True, ids=None,
+           wts=None):
     """Gate logits + softmax top-k + renormalise (reference: qk_route.route / i8x_dec_topk).
     Returns (logits fp32 [T,E] or None, ids int32 [T,K], wts fp32 [T,K])."""
     _need(x, torch.bfloat16, "x", 2)
@@ -62,8 +63,10 @@ def router(x, wr, top_k, bias=None, round_bf16=False, logits=None, scratch=None,
         logits = torch.empty(T, E, dtype=torch.float32, device=x.device)
     if scratch is None:
         scratch = router_scratch(T, H, E, x.device)
-    ids = torch.empty(T, top_k, dtype=torch.int32, device=x.device)
-    wts = torch.empty(T, top_k, dtype=torch.float32, device=x.device)
+    if ids is None:
+        ids = torch.empty(T, top_k, dtype=torch.int32, device=x.device)
+    if wts is None:
+        wts = torch.empty(T, top_k, dtype=torch.float32, device=x.device)
     check(_lib.lib().b200_router(_p(x), _p(wr), _p(bias), T, H, E, top_k, 1 if round_bf16 else 0, _p(logits),
                                  _p(ids), _p(wts), _p(scratch), scratch.numel(), _stream()), "b200_router")
     return logits, ids, wts

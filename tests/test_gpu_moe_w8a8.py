@@ -113,3 +113,23 @@ def test_linearity_property_full_size():
     ref = rows.sum(axis=1) + gate[:, None].astype(np.float32) * sh
     ok, err, nbad = close_bf16(out, ref, rtol=1e-2, atol=5e-3)
     assert ok, (err, nbad)
+
+
+def test_block_class_graph_replay_matches_eager_and_oracle():
+    from bundles_b200 import moe_block
+    cfg = synth.moe_w8a8(seed=17, T=32, E=64, zipf_s=1.1)
+    d = _to_dev(cfg)
+    w = ops.MoeW8A8Weights(d["w13"], d["s13"], d["w2"], d["s2"], d["sh13"], d["shs13"], d["sh2"], d["shs2"])
+    blk = moe_block.MoeBlockW8A8(d["wr"], w, d["gate_w"], 10, bias=d["bias"])
+    eager = blk._forward_eager(d["x"]).clone()
+    first = blk(d["x"]).clone()                       # captures
+    x2 = torch.randn(32, 2048, generator=torch.Generator().manual_seed(99)).to(torch.bfloat16)
+    blk(x2.to(dev()))                                 # replay on other data
+    again = blk(cfg["x"].pin_memory()).clone()        # replay from pinned host memory
+    torch.cuda.synchronize()
+    assert ops.read_status(blk.status) == 0
+    assert torch.equal(eager, first) and torch.equal(eager, again)
+    ref_l, ids, wts = orouter.route(bf16_to_np(cfg["x"]), cfg["wr"].numpy(), 10, cfg["bias"].numpy())
+    ref_out, _ = _oracle(cfg, ids, wts, 10)
+    ok, err, nbad = close_bf16(bf16_to_np(eager), ref_out)
+    assert ok, (err, nbad)
