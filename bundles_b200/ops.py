@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import B200Error, MoeLists, MoeWeights, check
 
-__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_combine", "gdn_verify",
+__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_fp8", "moe_combine", "gdn_verify",
            "new_status", "read_status", "B200Error"]
 
 
@@ -154,6 +154,36 @@ def moe_w8a8(x, w: MoeW8A8Weights, lists: RoutingLists, cache=None, ws=None, sta
     check(_lib.lib().b200_moe_w8a8(_p(x), T, H, I, K, E, C.byref(wc), C.byref(lists.c), _p(cache), _p(ws),
                                    ws.numel(), _p(dbg_acc13), _p(dbg_h), int(stages), _p(status), _stream()),
           "b200_moe_w8a8")
+    return cache
+
+
+def moe_fp8_workspace(T, H, I, K, device):
+    n = _lib.lib().b200_moe_fp8_workspace_bytes(T, H, I, K)
+    buf = torch.empty(n + 1024, dtype=torch.uint8, device=device)
+    off = (-buf.data_ptr()) % 1024
+    return buf[off:off + n]
+
+
+def moe_fp8(x, w: MoeW8A8Weights, lists: RoutingLists, cache=None, ws=None, status=None, dbg_h=None, stages=0):
+    """Routed + shared expert MLPs in fp8 e4m3 with 128 x 128 block scales (weights as uint8 codes in
+    the same container as the int8 block; scales [E, rows/128, K/128]).  Lists need block_rows <= 64.
+    Returns cache bf16 [T*(K+1), H] indexed by slot."""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(w.w13, torch.uint8, "w13", 3)
+    _need(w.w2, torch.uint8, "w2", 3)
+    if lists.block_rows > 64:
+        raise B200Error("moe_fp8 needs routing lists built with block_rows <= 64")
+    T, H = x.shape
+    E, twoI, _ = w.w13.shape
+    I = twoI // 2
+    K = lists.K
+    if cache is None:
+        cache = torch.zeros(T * (K + 1), H, dtype=torch.bfloat16, device=x.device)
+    if ws is None:
+        ws = moe_fp8_workspace(T, H, I, K, x.device)
+    wc = w.c_struct()
+    check(_lib.lib().b200_moe_fp8(_p(x), T, H, I, K, E, C.byref(wc), C.byref(lists.c), _p(cache), _p(ws), ws.numel(),
+                                  _p(dbg_h), int(stages), _p(status), _stream()), "b200_moe_fp8")
     return cache
 
 

@@ -150,6 +150,20 @@ int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_local, const 
                   const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, int32_t* dbg_acc13,
                   void* dbg_h, int stages, int32_t* status, void* stream);
 
+/* MoE block, fp8 e4m3 with 128x128 weight block scales and per-(token,128-channel) activation
+ * scales.  The reference has no block-scaled fp8 MoE; the arithmetic is its scaled-GEMM recipe
+ * applied per block: per 128-k block the MMA chain starts from zero and is promoted
+ * acc = fma(partial, a_scale * w_scale, acc) in increasing k (qk_lt.cu:361-364,
+ * qk_moe_prefill_i8.cu:3649-3651); activations are quantised scale = max(amax/448, 1e-12),
+ * y = e4m3(x * (1/scale)) (fp8.py:21-34); SwiGLU rounding points as in the int8 block.
+ * Same layouts with e4m3 bytes; s13 fp32 [E_local, 2I/128, H/128], s2 fp32 [E_local, H/128, I/128];
+ * shared scales likewise without the expert axis.  The routing lists must have been built with
+ * block_rows <= 64.  H, I multiples of 128, <= 4096. */
+size_t b200_moe_fp8_workspace_bytes(int T, int H, int I, int K);
+int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
+                 const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, void* dbg_h, int stages,
+                 int32_t* status, void* stream);
+
 /* Combine.  Replaces i8x_dec_combine (i8x_decode.py:425-443) / combine_norm_kernel
  * (qk_route.cu:686-820, without the next-layer norm): out[t] = bf16(sum_j cache[t*K+j] in slot
  * order + sigmoid(x[t].gate_w) * cache[T*K+t]); rows with pos[t] == 0 are written as zeros.
