@@ -87,10 +87,17 @@ struct F8Args {
   bf16* cache;           // down: [total_rows, H] by slot
   bf16* dbg_h;           // up: h by slot or null
   int32_t* status;
+  // LM-head mode: one dense block of `total_rows` tokens against w_rows vocabulary rows
+  unsigned long long* lm_keys;  // [total_rows] packed (value, id) maxima, zeroed before the launch
+  float* lm_logits;             // [total_rows, w_rows] or null
+  int lm_shard_lo;
 };
 
-template <bool UP>
+constexpr int MODE_DOWN = 0, MODE_UP = 1, MODE_LM = 2;
+
+template <int MODE>
 struct F8Cfg {
+  static constexpr bool UP = MODE == MODE_UP;
   static constexpr int NA = UP ? 2 : 1;
   static constexpr int STAGE = NA * F8_TILE + F8_BTILE;
   static constexpr int STAGES = UP ? 4 : 6;
@@ -99,11 +106,12 @@ struct F8Cfg {
   static constexpr int TMEM = UP ? 256 : 128;
 };
 
-template <bool UP>
+template <int MODE>
 __global__ void __launch_bounds__(F8_THREADS, 1)
 moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWsh,
                    const __grid_constant__ CUtensorMap tmX, const F8Args p) {
-  using C = F8Cfg<UP>;
+  using C = F8Cfg<MODE>;
+  constexpr bool UP = MODE == MODE_UP, LM = MODE == MODE_LM;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE);
@@ -135,9 +143,16 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int ntiles = p.L.nblocks[0] * p.mtiles;
+  const int ntiles = LM ? p.mtiles : p.L.nblocks[0] * p.mtiles;
 
   auto decode = [&](int tile, int& e, int& row0, int& n, int& mt) -> bool {
+    if (LM) {  // dense: every tile is 128 vocabulary rows against all the tokens
+      e = 0;
+      row0 = 0;
+      n = p.total_rows;
+      mt = tile;
+      return n >= 1 && n <= 64;
+    }
     const int blk = tile / p.mtiles;
     mt = tile - blk * p.mtiles;
     e = p.L.blk_expert[blk];
@@ -246,7 +261,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (int c = lane; c < 64; c += 32) {
         int slot = -1;
         float wt = 0.f;
-        if (c < n) {
+        if (!LM && c < n) {
           slot = p.L.slot_of_row[row0 + c];
           wt = p.L.wt_of_row[row0 + c];
           if (slot >= p.total_rows) slot = -1;
@@ -295,7 +310,32 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       if (!ok) break;
       const int r = mt * 128 + q * 32 + lane;
-      if (UP) {
+      if (LM) {
+        // per token: the largest logit of this warp's 32 vocabulary rows and its id (ties to the lower
+        // id), merged across warps, tiles and CTAs with one 64-bit atomic max per token
+        const bool live = r < p.w_rows;
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          if (c < n) {
+            const float v = acc_a[c];
+            if (p.lm_logits && live) p.lm_logits[static_cast<size_t>(c) * p.w_rows + r] = v;
+            uint32_t key = 0u;
+            if (live && v == v) {
+              const float vz = v + 0.f;
+              key = __float_as_uint(vz);
+              key = (key & 0x80000000u) ? ~key : (key | 0x80000000u);
+              if (key < 2u) key = 2u;
+            } else if (live) {
+              key = 1u;
+            }
+            const uint32_t m = __reduce_max_sync(FULL_MASK, key);
+            const uint32_t id = __reduce_min_sync(FULL_MASK, (key == m && live) ? static_cast<uint32_t>(r) : 0xffffffffu);
+            if (lane == 0 && m != 0u)
+              atomicMax(p.lm_keys + c, (static_cast<unsigned long long>(m) << 32) |
+                                           (0xffffffffu - static_cast<uint32_t>(p.lm_shard_lo + static_cast<int>(id))));
+          }
+        }
+      } else if (UP) {
         bf16* __restrict__ hout = p.h_out + static_cast<size_t>(row0) * p.I + r;
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
@@ -387,8 +427,8 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaFuncSetAttribute(moe_gemm_f8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<true>::SMEM);
-    cudaFuncSetAttribute(moe_gemm_f8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<false>::SMEM);
+    cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<MODE_UP>::SMEM);
+    cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<MODE_DOWN>::SMEM);
     attr_done[dev] = true;
   }
   if (stages == 0) stages = 15;
@@ -411,7 +451,7 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
   a.h_out = h;
   a.dbg_h = static_cast<bf16*>(dbg_h);
   if (stages & B200_MOE_STAGE_UP)
-    moe_gemm_f8_kernel<true><<<grid, F8_THREADS, F8Cfg<true>::SMEM, st>>>(tmW13, tmSh13, tmXq, a);
+    moe_gemm_f8_kernel<MODE_UP><<<grid, F8_THREADS, F8Cfg<MODE_UP>::SMEM, st>>>(tmW13, tmSh13, tmXq, a);
   if (stages & B200_MOE_STAGE_HQUANT)
     quant_rows_f8_kernel<<<(rows + 7) / 8, 256, 0, st>>>(h, rows, I, L.slot_of_row, hq, hs);
   a.mtiles = H / 128;
@@ -424,6 +464,125 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
   a.cache = static_cast<bf16*>(cache);
   a.dbg_h = nullptr;
   if (stages & B200_MOE_STAGE_DOWN)
-    moe_gemm_f8_kernel<false><<<grid, F8_THREADS, F8Cfg<false>::SMEM, st>>>(tmW2, tmSh2, tmHq, a);
+    moe_gemm_f8_kernel<MODE_DOWN><<<grid, F8_THREADS, F8Cfg<MODE_DOWN>::SMEM, st>>>(tmW2, tmSh2, tmHq, a);
   return launch_status("b200_moe_fp8");
+}
+
+// ---- LM head shard with fused argmax ------------------------------------------------------------------
+namespace b200 {
+__global__ void lmhead_finish_kernel(const unsigned long long* __restrict__ keys, int T, float* __restrict__ max_out,
+                                     int32_t* __restrict__ idx_out) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const unsigned long long k = keys[t];
+  const uint32_t m = static_cast<uint32_t>(k >> 32);
+  float v;
+  if (m <= 1u)
+    v = __int_as_float(0x7fc00000);  // no finite candidate in this shard
+  else
+    v = __uint_as_float((m & 0x80000000u) ? (m & 0x7fffffffu) : ~m);
+  max_out[t] = v;
+  idx_out[t] = m == 0u ? -1 : static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(k & 0xffffffffull));
+}
+
+// tokens[t] = id of the largest value over the S shards; ties to the lower id; NaN never wins
+__global__ void argmax_merge_kernel(const float* __restrict__ maxes, const int32_t* __restrict__ idxs, int S, int T,
+                                    int32_t* __restrict__ tokens) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  float best = 0.f;
+  int id = -1;
+  for (int s = 0; s < S; ++s) {
+    const float v = maxes[static_cast<size_t>(s) * T + t];
+    const int i = idxs[static_cast<size_t>(s) * T + t];
+    if (i < 0 || v != v) continue;
+    if (id < 0 || v > best || (v == best && i < id)) {
+      best = v;
+      id = i;
+    }
+  }
+  if (id < 0)
+    for (int s = 0; s < S; ++s) {
+      const int i = idxs[static_cast<size_t>(s) * T + t];
+      if (i >= 0 && (id < 0 || i < id)) id = i;
+    }
+  tokens[t] = id;
+}
+
+struct LmLayout {
+  size_t xq, xs, keys, total;
+};
+static LmLayout lm_layout(int T, int H) {
+  auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+  LmLayout l;
+  size_t o = 0;
+  l.xq = o; o = up(o + static_cast<size_t>(64) * H);  // 64 rows so that every 16-row TMA box is in bounds
+  l.xs = o; o = up(o + static_cast<size_t>(T) * (H / 128) * 4);
+  l.keys = o; o = up(o + static_cast<size_t>(T) * 8);
+  l.total = o;
+  return l;
+}
+}  // namespace b200
+
+extern "C" size_t b200_lmhead_workspace_bytes(int T, int H) {
+  if (T <= 0 || H <= 0) return 0;
+  return lm_layout(T, H).total;
+}
+
+extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, const float* w_s, int V_shard,
+                                  int shard_lo, float* max_out, int32_t* idx_out, float* logits_out, void* ws,
+                                  size_t ws_bytes, int32_t* status, void* stream) {
+  if (!x || !w || !w_s || !max_out || !idx_out || !ws) return fail(B200_E_ARG, "b200_lmhead_argmax: null pointer");
+  if (T <= 0 || T > 64 || H <= 0 || H % 128 || H / 128 > F8_MAXKG || V_shard <= 0 || shard_lo < 0)
+    return fail(B200_E_ARG, "b200_lmhead_argmax: need 1 <= T <= 64, H %% 128 == 0, H <= 4096 (T=%d H=%d V=%d)", T, H,
+                V_shard);
+  const LmLayout l = lm_layout(T, H);
+  if (ws_bytes < l.total) return fail(B200_E_WS, "b200_lmhead_argmax: workspace %zu < %zu bytes", ws_bytes, l.total);
+  if (reinterpret_cast<uintptr_t>(ws) & 1023) return fail(B200_E_ALIGN, "b200_lmhead_argmax: workspace must be 1024-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* base = static_cast<uint8_t*>(ws);
+  uint8_t* xq = base + l.xq;
+  float* xs = reinterpret_cast<float*>(base + l.xs);
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(base + l.keys);
+  CUtensorMap tmW, tmX;
+  int rc;
+  if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(V_shard), H, 128, "lm_head weight"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "lm_head activations"))) return rc;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_LM>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<MODE_LM>::SMEM);
+    attr_done[dev] = true;
+  }
+  cudaMemsetAsync(keys, 0, static_cast<size_t>(T) * 8, st);
+  // K = 0 routed picks: the "shared expert" row of token t is row t
+  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 1, xq, xs);
+  F8Args a{};
+  a.E_local = 1;
+  a.mtiles = (V_shard + 127) / 128;
+  a.ksteps = H / 128;
+  a.w_rows = V_shard;
+  a.I = 0;
+  a.H = H;
+  a.total_rows = T;
+  a.s_w = w_s;
+  a.s_w_sh = w_s;
+  a.a_scale = xs;
+  a.status = status;
+  a.lm_keys = keys;
+  a.lm_logits = logits_out;
+  a.lm_shard_lo = shard_lo;
+  const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
+  moe_gemm_f8_kernel<MODE_LM><<<grid, F8_THREADS, F8Cfg<MODE_LM>::SMEM, st>>>(tmW, tmW, tmX, a);
+  lmhead_finish_kernel<<<1, 64, 0, st>>>(keys, T, max_out, idx_out);
+  return launch_status("b200_lmhead_argmax");
+}
+
+extern "C" int b200_argmax_merge(const float* maxes, const int32_t* idxs, int S, int T, int32_t* tokens, void* stream) {
+  if (!maxes || !idxs || !tokens) return fail(B200_E_ARG, "b200_argmax_merge: null pointer");
+  if (S <= 0 || T < 0) return fail(B200_E_ARG, "b200_argmax_merge: bad shape (S=%d T=%d)", S, T);
+  if (T == 0) return 0;
+  argmax_merge_kernel<<<(T + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(maxes, idxs, S, T, tokens);
+  return launch_status("b200_argmax_merge");
 }

@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import B200Error, MoeLists, MoeWeights, check
 
-__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_fp8", "moe_combine", "gdn_verify",
+__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_fp8", "moe_combine", "lmhead_argmax", "argmax_merge", "gdn_verify",
            "new_status", "read_status", "B200Error"]
 
 
@@ -197,6 +197,41 @@ def moe_combine(cache, x, gate_w, top_k, pos=None, out=None):
     check(_lib.lib().b200_moe_combine(_p(cache), _p(x), _p(gate_w), _p(pos), T, H, top_k, _p(out), _stream()),
           "b200_moe_combine")
     return out
+
+
+def lmhead_workspace(T, H, device):
+    n = _lib.lib().b200_lmhead_workspace_bytes(T, H)
+    buf = torch.empty(n + 1024, dtype=torch.uint8, device=device)
+    off = (-buf.data_ptr()) % 1024
+    return buf[off:off + n]
+
+
+def lmhead_argmax(x, w, w_s, shard_lo=0, want_logits=False, ws=None, status=None):
+    """One vocabulary shard of the fp8 LM head with the argmax fused in (reference: the logits GEMM of
+    qwen36_lmhead8; the argmax has no counterpart there).  Returns (max fp32 [T], idx int32 [T], logits or None)."""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(w, torch.uint8, "w", 2)
+    _need(w_s, torch.float32, "w_s", 2)
+    T, H = x.shape
+    V = w.shape[0]
+    mx = torch.empty(T, dtype=torch.float32, device=x.device)
+    idx = torch.empty(T, dtype=torch.int32, device=x.device)
+    logits = torch.empty(T, V, dtype=torch.float32, device=x.device) if want_logits else None
+    if ws is None:
+        ws = lmhead_workspace(T, H, x.device)
+    check(_lib.lib().b200_lmhead_argmax(_p(x), T, H, _p(w), _p(w_s), V, int(shard_lo), _p(mx), _p(idx), _p(logits),
+                                        _p(ws), ws.numel(), _p(status), _stream()), "b200_lmhead_argmax")
+    return mx, idx, logits
+
+
+def argmax_merge(maxes, idxs):
+    """[S, T] shard maxima and ids -> tokens int32 [T] (largest value, ties to the lower id)."""
+    _need(maxes, torch.float32, "maxes", 2)
+    _need(idxs, torch.int32, "idxs", 2)
+    S, T = maxes.shape
+    tokens = torch.empty(T, dtype=torch.int32, device=maxes.device)
+    check(_lib.lib().b200_argmax_merge(_p(maxes), _p(idxs), S, T, _p(tokens), _stream()), "b200_argmax_merge")
+    return tokens
 
 
 def gdn_verify(mixed, z, a, b, conv_state, conv_w, a_log, dt_bias, state, accepted, norm_w, eps=1e-6, out=None,

@@ -187,6 +187,24 @@ int b200_gdn_verify(const void* mixed, const void* z, const void* a, const void*
                     const int32_t* accepted, const void* norm_w, float eps, int B, void* out, int32_t* status,
                     void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * LM head shard with fused argmax.  Replaces the logits GEMM of qwen36_lmhead8
+ * (lmhead8.py:171-197, w8a8.py:99-120, qk_proj_decode.cu:1210,1468: vocabulary rows on the MMA M
+ * side, weight streamed once); the reference returns logits and has no argmax
+ * (node.py:136-151).  Per row of x: the largest fp8 block-scaled logit over this shard's
+ * vocabulary rows and its global id (shard_lo + local row); ties go to the lower id, NaN never wins.
+ *   x bf16 [T,H], 1 <= T <= 64, H % 128 == 0, H <= 4096; w e4m3 [V_shard,H];
+ *   w_s fp32 [ceil(V_shard/128), H/128]; max_out fp32 [T]; idx_out int32 [T];
+ *   logits_out fp32 [T,V_shard] or NULL; ws: b200_lmhead_workspace_bytes(T,H) bytes, 1024-byte aligned.
+ */
+size_t b200_lmhead_workspace_bytes(int T, int H);
+int b200_lmhead_argmax(const void* x, int T, int H, const void* w, const float* w_s, int V_shard, int shard_lo,
+                       float* max_out, int32_t* idx_out, float* logits_out, void* ws, size_t ws_bytes,
+                       int32_t* status, void* stream);
+/* Merge S gathered shard results (maxes, idxs: [S,T]) into tokens [T]: largest value, ties to the
+ * lower id.  This is the step after the all-gather of (max, argmax) pairs of a vocab-sharded head. */
+int b200_argmax_merge(const float* maxes, const int32_t* idxs, int S, int T, int32_t* tokens, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
