@@ -46,6 +46,8 @@ inline int launch_status(const char* what) {
 int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
                        const char* what);
 
+void b200_quant_rows_f8_launch(const void* x, int T, int H, uint8_t* xq, float* xs, cudaStream_t st);
+
 int sm_count();  // SMs of the current device (cached per device)
 
 }  // namespace b200

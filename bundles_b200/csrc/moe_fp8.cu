@@ -363,6 +363,11 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   }
 }
 
+// x bf16 [T, H] -> e4m3 rows [T, H] + scales [T, H/128] in token order (no permutation)
+void b200_quant_rows_f8_launch(const void* x, int T, int H, uint8_t* xq, float* xs, cudaStream_t st) {
+  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 1, xq, xs);
+}
+
 struct F8Layout {
   size_t xq, xs, h, hq, hs, total;
 };

@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import B200Error, MoeLists, MoeWeights, check
 
-__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_fp8", "moe_combine", "lmhead_argmax", "argmax_merge", "gdn_verify",
+__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_fp8", "moe_combine", "attn_front", "lmhead_argmax", "argmax_merge", "gdn_verify",
            "new_status", "read_status", "B200Error"]
 
 
@@ -197,6 +197,34 @@ def moe_combine(cache, x, gate_w, top_k, pos=None, out=None):
     check(_lib.lib().b200_moe_combine(_p(cache), _p(x), _p(gate_w), _p(pos), T, H, top_k, _p(out), _stream()),
           "b200_moe_combine")
     return out
+
+
+def attn_front(x, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, eps=1e-6, out_fp8=True, ws=None, status=None):
+    """Fused QKV + gate projection with q/k RMSNorm and partial RoPE (reference: fp8.linear_q followed by
+    qk_attn_verify.attn_prefill_front).  Returns (q [T,16,256], gate bf16 [T,16,256], k, v [T,2,256]);
+    q, k, v are uint8 e4m3 codes when out_fp8 else bf16."""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(w, torch.uint8, "w", 2)
+    _need(w_s, torch.float32, "w_s", 2)
+    _need(positions, torch.int64, "positions", 1)
+    _need(cos_sin, torch.float32, "cos_sin", 2)
+    T = x.shape[0]
+    if x.shape[1] != 2048 or tuple(w.shape) != (9216, 2048) or tuple(w_s.shape) != (72, 16) or cos_sin.shape[1] != 64:
+        raise B200Error("attn_front: expected x [T,2048], w [9216,2048], w_s [72,16], cos_sin [max_pos,64]")
+    dt = torch.uint8 if out_fp8 else torch.bfloat16
+    q = torch.empty(T, 16, 256, dtype=dt, device=x.device)
+    k = torch.empty(T, 2, 256, dtype=dt, device=x.device)
+    v = torch.empty(T, 2, 256, dtype=dt, device=x.device)
+    gate = torch.empty(T, 16, 256, dtype=torch.bfloat16, device=x.device)
+    if ws is None:
+        n = _lib.lib().b200_attn_front_workspace_bytes(T)
+        buf = torch.empty(n + 1024, dtype=torch.uint8, device=x.device)
+        off = (-buf.data_ptr()) % 1024
+        ws = buf[off:off + n]
+    check(_lib.lib().b200_attn_front(_p(x), T, _p(w), _p(w_s), _p(q_norm_w), _p(k_norm_w), _p(positions), _p(cos_sin),
+                                     cos_sin.shape[0], float(eps), 1 if out_fp8 else 0, _p(q), _p(gate), _p(k), _p(v),
+                                     _p(ws), ws.numel(), _p(status), _stream()), "b200_attn_front")
+    return q, gate, k, v
 
 
 def lmhead_workspace(T, H, device):

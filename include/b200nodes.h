@@ -188,6 +188,26 @@ int b200_gdn_verify(const void* mixed, const void* z, const void* a, const void*
                     void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Fused gated-attention projection front.  Replaces fp8.linear_q + qk_attn_verify.
+ * attn_prefill_front (fp8.py:77-108, qk_attn_verify.cu:765-800): fp8 block-scaled GEMM
+ * x[T,2048] . W[9216,2048]^T (activations quantised per token per 128 channels, per-128-k
+ * promotion), the result rounded to bf16 as the reference's projection stores it, then per head:
+ * q/k RMSNorm x * rsqrt(mean x^2 + eps) * (1 + w) -> bf16 and neox RoPE on dims (i, i+32), i < 32
+ * -> bf16 (qk_attn_verify.cu:180-208), all in the GEMM epilogue.  Column layout per q head h: q at
+ * h*512, gate at h*512+256; K at 8192; V at 8704 (qk_attn_verify.cu:25,443,450).
+ *   x bf16 [T,2048]; w e4m3 [9216,2048]; w_s fp32 [72,16]; q_norm_w, k_norm_w bf16 [256];
+ *   positions int64 [T] (clamped to [0, max_pos)); cos_sin fp32 [max_pos, 64] = [cos 32 | sin 32];
+ *   q [T,16,256], k, v [T,2,256]: e4m3 bytes (cvt.rn.satfinite, qk_attn_verify.cu:142-146) if
+ *   out_fp8 else bf16; gate bf16 [T,16,256].  All 16-byte aligned.
+ *   ws: b200_attn_front_workspace_bytes(T) bytes, 1024-byte aligned.
+ */
+size_t b200_attn_front_workspace_bytes(int T);
+int b200_attn_front(const void* x, int T, const void* w, const float* w_s, const void* q_norm_w,
+                    const void* k_norm_w, const int64_t* positions, const float* cos_sin, int max_pos, float eps,
+                    int out_fp8, void* q, void* gate, void* k, void* v, void* ws, size_t ws_bytes, int32_t* status,
+                    void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * LM head shard with fused argmax.  Replaces the logits GEMM of qwen36_lmhead8
  * (lmhead8.py:171-197, w8a8.py:99-120, qk_proj_decode.cu:1210,1468: vocabulary rows on the MMA M
  * side, weight streamed once); the reference returns logits and has no argmax
