@@ -126,6 +126,72 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_expert_parallel(args, rank, world, dev, cfg):
+    """N > 1: experts split over the ranks (512 / N each), every rank brings its own 256 tokens (weak
+    scaling: rows per rank stay ~2560 routed + 256 shared).  All ranks draw the SAME layer (seed) and keep
+    their slice of it."""
+    import torch
+    import torch.distributed as dist
+    from bundles_b200 import ops, parallel, synth
+    full = synth.moe_w8a8(seed=synth.SEEDS["moe_w8a8"], T=T, H=H, I=I, E=E, device=dev)
+    e_lo, e_n = parallel.expert_range(E, rank, world)
+    w_local = ops.MoeW8A8Weights(full["w13"][e_lo:e_lo + e_n].clone(), full["s13"][e_lo:e_lo + e_n].clone(),
+                                 full["w2"][e_lo:e_lo + e_n].clone(), full["s2"][e_lo:e_lo + e_n].clone(),
+                                 full["sh13"], full["shs13"], full["sh2"], full["shs2"])
+    wr, gate_w, bias = full["wr"], full["gate_w"], full["bias"]
+    del full
+    torch.cuda.empty_cache()
+    backend = parallel.GpuMoeBackend(wr, w_local, gate_w, K, e_lo, bias=bias)
+    ep = parallel.ExpertParallelMoe(backend, K, H)
+    g = torch.Generator(device=dev).manual_seed(7000 + rank)
+    x_dev = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    x_host = x_dev.cpu().pin_memory()
+    out_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    if rank == 0:
+        sampler.start()
+    ms_step = timed(lambda: ep(x_dev))
+
+    def e2e_step():
+        out_host.copy_(ep(x_host.to(dev, non_blocking=True)), non_blocking=True)
+
+    ms_e2e = timed(e2e_step)
+    clocks = sampler.stop() if rank == 0 else None
+    status = torch.tensor([ops.read_status(backend.status)], device=dev)
+    dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        line = {"metric": METRIC, "value": world * T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "tokens_per_gpu": T,
+                           "parallelism": f"ep{world}: {E // world} experts per rank; all-gather of tokens and routing, "
+                                          "reduce-scatter of the weighted expert rows (NCCL)",
+                           "l2": "weights streamed per step exceed the 126 MB L2; no flush"},
+                "e2e": {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2,
+                        "d2h_bytes_per_step": T * H * 2, "ms_per_step": ms_e2e},
+                "gpu_launches": backend.launches_per_call * args.steps, "clocks": clocks,
+                "device_status": int(status.item())}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -133,6 +199,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="ep", choices=["ep", "replicas"],
+                    help="N > 1: expert-parallel (experts split over ranks) or independent replicas")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -162,6 +230,9 @@ def main():
         cfg = synth.moe_w8a8(seed=synth.SEEDS["moe_w8a8"] + rank, T=T, H=H, I=I, E=E, device=dev)
     w = ops.MoeW8A8Weights(cfg["w13"], cfg["s13"], cfg["w2"], cfg["s2"], cfg["sh13"], cfg["shs13"], cfg["sh2"],
                            cfg["shs2"])
+    if world > 1 and args.parallel == "ep":
+        run_expert_parallel(args, rank, world, dev, cfg)
+        return
     block = moe_block.MoeBlockW8A8(cfg["wr"], w, cfg["gate_w"], K, bias=cfg["bias"])
     x_dev = cfg["x"]
     x_host = x_dev.cpu().pin_memory()

@@ -1,0 +1,141 @@
+"""Multi-GPU partitioning of the hot path on one node: expert-parallel MoE and the vocab-sharded
+LM head.  One process per GPU, `torch.distributed` (NCCL on GPUs, gloo in the CPU tests).
+
+The reference is single-GPU (it raises for TP != 1: layer.py:396-402) and has no collective at all,
+so there is no reference call to mirror here; the partitioning is the one the target names:
+experts split evenly over ranks (expert e lives on rank e // E_local), vocabulary rows split on
+128-row scale-block boundaries.
+
+Expert-parallel step, exact by construction:
+  1. every rank routes its own tokens; x, ids and weights are all-gathered (a token is needed by
+     up to min(K, world) ranks, so for K >= world gathering each row once moves no more bytes than a
+     per-destination all-to-all would);
+  2. every rank builds the routing lists of ITS experts over all tokens, runs their MLPs and writes
+     bf16(y * w) into a zero-initialised cache [T_all * K, H] at the global slot t * K + j;
+  3. the cache is reduce-scattered (sum): every slot is non-zero on exactly one rank and x + 0 == x,
+     so each home rank receives its tokens' K rows bit-exactly, whatever the reduction order;
+  4. the home rank adds the K rows in slot order and the sigmoid-gated shared-expert row (computed
+     locally for its own tokens), exactly as the single-GPU combine does.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def expert_range(n_experts: int, rank: int, world: int):
+    if n_experts % world:
+        raise ValueError(f"{n_experts} experts do not split evenly over {world} ranks")
+    per = n_experts // world
+    return rank * per, per
+
+
+def vocab_shards(vocab: int, world: int, block: int = 128):
+    """Row ranges per rank, cut on 128-row scale-block boundaries; the first (blocks % world) ranks
+    take one block more (151936 rows over 8 ranks -> 3 x 19072 + 5 x 18944)."""
+    nb = (vocab + block - 1) // block
+    base, extra = divmod(nb, world)
+    out, lo = [], 0
+    for r in range(world):
+        hi = min(vocab, lo + (base + (1 if r < extra else 0)) * block)
+        out.append((lo, hi))
+        lo = hi
+    return out
+
+
+class ExpertParallelMoe:
+    """Expert-parallel MoE block.  `local` is the compute backend of this rank:
+        local.route(x) -> (ids int32 [T,K], wts fp32 [T,K])                      (all experts' router)
+        local.experts(x_all, ids_all, wts_all, cache_all) -> None                (fills this rank's slots, routed only)
+        local.shared_and_combine(x, routed_rows [T*K,H]) -> out bf16 [T,H]       (shared expert + combine, own tokens)
+    On GPUs the backend wraps the C-ABI operators (`GpuMoeBackend`); the CPU tests plug the oracle in.
+    """
+
+    def __init__(self, local, top_k: int, hidden: int, group=None):
+        self.local, self.K, self.H, self.group = local, top_k, hidden, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        T, H = x.shape
+        W, K = self.world, self.K
+        ids, wts = self.local.route(x)
+        x_all = torch.empty(W * T, H, dtype=x.dtype, device=x.device)
+        ids_all = torch.empty(W * T, K, dtype=ids.dtype, device=x.device)
+        wts_all = torch.empty(W * T, K, dtype=wts.dtype, device=x.device)
+        dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(ids_all, ids.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(wts_all, wts.contiguous(), group=self.group)
+        cache_all = torch.zeros(W * T * K, H, dtype=x.dtype, device=x.device)
+        self.local.experts(x_all, ids_all, wts_all, cache_all)
+        if dist.get_backend(self.group) == "gloo":   # gloo has no reduce-scatter: all-reduce and keep our slice
+            dist.all_reduce(cache_all, op=dist.ReduceOp.SUM, group=self.group)
+            mine = cache_all[self.rank * T * K:(self.rank + 1) * T * K]
+        else:
+            mine = torch.empty(T * K, H, dtype=x.dtype, device=x.device)
+            dist.reduce_scatter_tensor(mine, cache_all, op=dist.ReduceOp.SUM, group=self.group)
+        return self.local.shared_and_combine(x, mine)
+
+    __call__ = forward
+
+
+class GpuMoeBackend:
+    """This rank's share of an int8 W8A8 MoE layer on its GPU, through the C-ABI operators."""
+
+    def __init__(self, wr, weights, gate_w, top_k, e_lo, bias=None):
+        from . import ops
+        self.ops = ops
+        self.wr, self.w, self.gate_w, self.K, self.e_lo, self.bias = wr, weights, gate_w, top_k, e_lo, bias
+        self.E_local = weights.w13.shape[0]
+        self.status = ops.new_status(wr.device)
+        self._lists = {}
+        # the shared expert runs on the home rank only: a weights view without / with only the shared expert
+        self.w_routed = ops.MoeW8A8Weights(weights.w13, weights.s13, weights.w2, weights.s2)
+        self.launches_per_call = 14
+
+    def _get_lists(self, T, shared):
+        key = (T, shared)
+        if key not in self._lists:
+            self._lists[key] = self.ops.RoutingLists(T, self.K, self.E_local, 128, self.wr.device)
+        return self._lists[key]
+
+    def route(self, x):
+        _, ids, wts = self.ops.router(x, self.wr, self.K, self.bias, want_logits=False)
+        return ids, wts
+
+    def experts(self, x_all, ids_all, wts_all, cache_all):
+        T = x_all.shape[0]
+        lists = self._get_lists(T, False)
+        self.ops.build_lists(ids_all, wts_all, lists, None, e_lo=self.e_lo, with_shared=False)
+        # the kernel addresses cache rows by slot < T*(K+1); only routed slots are written here
+        self.ops.moe_w8a8(x_all, self.w_routed, lists, cache=cache_all, status=self.status)
+
+    def shared_and_combine(self, x, routed_rows):
+        ops = self.ops
+        T, H = x.shape
+        K = self.K
+        cache = torch.empty(T * (K + 1), H, dtype=x.dtype, device=x.device)
+        cache[:T * K].copy_(routed_rows)
+        # shared expert only: lists with no routed pair (ids outside this rank's window) + the shared rows
+        lists = self._get_lists(T, True)
+        none_ids = torch.full((T, K), -1, dtype=torch.int32, device=x.device)
+        zero_w = torch.zeros(T, K, dtype=torch.float32, device=x.device)
+        ops.build_lists(none_ids, zero_w, lists, None, e_lo=0, with_shared=True)
+        w_sh = ops.MoeW8A8Weights(self.w.w13, self.w.s13, self.w.w2, self.w.s2, self.w.sh13, self.w.shs13,
+                                  self.w.sh2, self.w.shs2)
+        ops.moe_w8a8(x, w_sh, lists, cache=cache, status=self.status)
+        return ops.moe_combine(cache, x, self.gate_w, K)
+
+
+def sharded_argmax(x, w_shard, w_s_shard, shard_lo, group=None):
+    """Vocab-sharded greedy token: per-shard (max, argmax) on this rank, all-gather of the pairs,
+    merge (largest value, ties to the lower id).  Returns tokens int32 [T] (same on every rank)."""
+    from . import ops
+    world = dist.get_world_size(group)
+    mx, idx, _ = ops.lmhead_argmax(x, w_shard, w_s_shard, shard_lo)
+    T = x.shape[0]
+    maxes = torch.empty(world, T, dtype=torch.float32, device=x.device)
+    idxs = torch.empty(world, T, dtype=torch.int32, device=x.device)
+    dist.all_gather_into_tensor(maxes, mx, group=group)
+    dist.all_gather_into_tensor(idxs, idx, group=group)
+    return ops.argmax_merge(maxes, idxs)
