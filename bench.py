@@ -126,6 +126,135 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def other_kernels(dev, steps, warmup):
+    """The other kernels of the hot path at their named configurations, each timed alone with CUDA events
+    (inputs larger than L2 or rotated over several copies so that every launch reads HBM)."""
+    import math
+    import torch
+    from bundles_b200 import ops, synth
+    from bundles_b200.synth import quant_fp8_blocks
+    hbm, which = peaks()
+    out = {}
+
+    def timed(fn, n=steps, calls=1, graph=True):
+        """ms per call of fn.  The calls are captured into a CUDA graph (`calls` of them, e.g. one per
+        rotating buffer) so that host-side launch cost does not hide the device time."""
+        for _ in range(max(warmup, calls)):
+            fn()
+        torch.cuda.synchronize()
+        run = fn
+        per = 1
+        if graph:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for _ in range(calls):
+                    fn()
+            run, per = gr.replay, calls
+            run()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (n * per)
+
+    # dense fp8 GEMM peak of this GPU (cuBLASLt through torch._scaled_mm, 8192^3), the tensor-pipe denominator
+    fp8_peak = None
+    try:
+        a = torch.randn(8192, 8192, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(8192, 8192, device=dev).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev)
+        ms = min(timed(lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16), 5,
+                       graph=False) for _ in range(3))
+        fp8_peak = 2 * 8192 ** 3 / (ms * 1e-3) / 1e12
+        del a, b
+    except Exception as exc:  # noqa: BLE001
+        out["fp8_peak_error"] = repr(exc)[:120]
+    out["fp8_dense_tflops_measured"] = fp8_peak
+
+    # Gated DeltaNet verify: B = 32 x 4 drafts; 4 rotating copies of the state (268 MB > L2)
+    g = {k: v.to(dev) for k, v in synth.gdn().items()}
+    states = [g["state"].clone() for _ in range(4)]
+    convs = [g["conv_state"].clone() for _ in range(4)]
+    st = ops.new_status(dev)
+    it = [0]
+
+    def gdn_step():
+        i = it[0] % 4
+        it[0] += 1
+        ops.gdn_verify(g["mixed"], g["z"], g["a"], g["b"], convs[i], g["conv_w"], g["a_log"], g["dt_bias"], states[i],
+                       g["accepted"], g["norm_w"], 1e-6, status=st)
+
+    ms = timed(gdn_step, calls=4)
+    B = 32
+    wrote = int((g["accepted"] > 0).sum().item())
+    gbytes = B * 32 * 65536 + wrote * 32 * 65536 + B * 4 * (8192 + 4096 + 64) * 2 + B * 8192 * 3 * 2 * 2 + B * 4 * 4096 * 2
+    out["gdn_verify"] = {"config": "B=32 x 4 drafts, 16/32 heads, d=128, accepted~U{0..4}", "ms": ms,
+                         "algorithmic_bytes": gbytes, "achieved_gbs": gbytes / ms / 1e6, "bound": "hbm",
+                         "frac": gbytes / ms / 1e6 / hbm, "peak_source": which, "status": ops.read_status(st)}
+    del states, convs, g
+
+    # fused attention projection front: T = 4096
+    a = {k: v.to(dev) for k, v in synth.attn().items()}
+    half = 32
+    inv = torch.pow(torch.tensor(1e7, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / 64)
+    ang = torch.arange(4096, dtype=torch.float64)[:, None] * inv[None, :]
+    cs = torch.cat([ang.cos(), ang.sin()], 1).float().to(dev)
+    ms = timed(lambda: ops.attn_front(a["x"], a["w"], a["w_s"], a["q_norm_w"], a["k_norm_w"], a["positions"], cs, 1e-6,
+                                      True, status=st))
+    fl = 2 * 4096 * 2048 * 9216
+    out["attn_front"] = {"config": "T=4096, W [9216,2048] fp8 block-scaled, norm + RoPE fused, e4m3 q/k/v", "ms": ms,
+                         "flops": fl, "achieved_tflops": fl / ms / 1e9, "bound": "tensor",
+                         "frac_of_measured_fp8_dense": (fl / ms / 1e9 / fp8_peak) if fp8_peak else None,
+                         "includes": "activation quantiser launch", "status": ops.read_status(st)}
+    del a
+
+    # LM head shard (1/8 of the vocabulary), T = 64, 4 rotating weight copies (156 MB > L2)
+    lm = synth.lmhead(T=64, V=19072)
+    x = lm["x"].to(dev)
+    ws_ = lm["w_s"].to(dev)
+    wcopies = [lm["w"].to(dev).clone() for _ in range(4)]
+    it[0] = 0
+
+    def lm_step():
+        i = it[0] % 4
+        it[0] += 1
+        ops.lmhead_argmax(x, wcopies[i], ws_, 0, status=st)
+
+    ms = timed(lm_step, calls=4)
+    lb = 19072 * 2048 + 149 * 16 * 4 + 64 * 2048 * 2
+    out["lmhead_shard_argmax"] = {"config": "T=64, shard 19072 x 2048 fp8 (1/8 of 151936)", "ms": ms,
+                                  "algorithmic_bytes": lb, "achieved_gbs": lb / ms / 1e6, "bound": "hbm",
+                                  "frac": lb / ms / 1e6 / hbm, "status": ops.read_status(st)}
+    del wcopies
+
+    # fp8 MoE block, T = 16 (single block configuration)
+    c = {k: (v.to(dev) if v is not None else None) for k, v in synth.moe_fp8(E=512).items()}
+    w = ops.MoeW8A8Weights(c["w13"], c["s13"], c["w2"], c["s2"], c["sh13"], c["shs13"], c["sh2"], c["shs2"])
+    _, ids, wts = ops.router(c["x"], c["wr"], 10)
+    lists = ops.RoutingLists(16, 10, 512, 64, dev)
+    ops.build_lists(ids, wts, lists)
+    wsb = ops.moe_fp8_workspace(16, 2048, 512, 10, dev)
+    cache = torch.zeros(16 * 11, 2048, dtype=torch.bfloat16, device=dev)
+    ms = timed(lambda: ops.moe_fp8(c["x"], w, lists, cache=cache, ws=wsb, status=st))
+    act = int((lists.counts > 0).sum().item())
+    fb = act * (3 * 2048 * 512 + 768 * 4) + 16 * 2048 * 4
+    out["moe_fp8_t16"] = {"config": "T=16, E=512, top-10, fp8 128x128 block scales (4 launches)", "ms": ms,
+                          "active_experts": act, "algorithmic_bytes": fb, "achieved_gbs": fb / ms / 1e6,
+                          "bound": "hbm", "frac": fb / ms / 1e6 / hbm,
+                          "note": "the same weights every step: partly L2-resident when < 126 MB",
+                          "status": ops.read_status(st)}
+    # router alone at T = 256 and T = 64
+    for Tn in (256, 64):
+        xr = torch.randn(Tn, 2048, device=dev).to(torch.bfloat16)
+        scr = ops.router_scratch(Tn, 2048, 512, dev)
+        ms = timed(lambda: ops.router(xr, c["wr"], 10, scratch=scr, want_logits=False))
+        out[f"router_t{Tn}"] = {"ms": ms, "flops": 2 * Tn * 512 * 2048, "bytes": 4 * 512 * 2048 + 2 * Tn * 2048}
+    return out
+
+
 def run_expert_parallel(args, rank, world, dev, cfg):
     """N > 1: experts split over the ranks (512 / N each), every rank brings its own 256 tokens (weak
     scaling: rows per rank stay ~2560 routed + 256 shared).  All ranks draw the SAME layer (seed) and keep
@@ -199,6 +328,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel measurements of the other rows")
     ap.add_argument("--parallel", default="ep", choices=["ep", "replicas"],
                     help="N > 1: expert-parallel (experts split over ranks) or independent replicas")
     args = ap.parse_args()
@@ -317,6 +447,13 @@ def main():
                                      "achieved": down_bytes / (ms_down * 1e-3) / 1e9}},
         "clocks": clocks, "device_status": status,
     }
+    if world == 1 and not args.no_kernels:
+        del block, w, cfg
+        torch.cuda.empty_cache()
+        try:
+            line["kernels"] = other_kernels(dev, args.steps, args.warmup)
+        except Exception as exc:  # noqa: BLE001  (the headline line must still be printed)
+            line["kernels"] = {"error": repr(exc)[:300]}
     if cfg_host is not None:
         dt, cores = cpu_baseline(cfg_host)
         line["cpu_baseline"] = {"value": T / dt, "unit": "tokens/s", "cores": cores, "kind": "port",

@@ -101,7 +101,7 @@ struct GdnArgs {
   int32_t* status;
 };
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS) gdn_verify_kernel(const GdnArgs p) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 3) gdn_verify_kernel(const GdnArgs p) {
   extern __shared__ uint8_t smem_raw[];
   GdnSmem& sm = *reinterpret_cast<GdnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -347,7 +347,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS) gdn_verif
     if (tid == 0) {
       bulk_store(gstate, sm.S, G_TILE_BYTES);
       bulk_commit();
-      bulk_wait_all();
+      bulk_wait_read_all();  // the tile has left shared memory; the write itself completes with the grid
     }
   }
 }

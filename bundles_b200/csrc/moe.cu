@@ -10,7 +10,7 @@
 // straight from the expert tensors ([rows, K] bytes, 128-byte swizzle); tokens were permuted into
 // expert-sorted rows by the quantise kernel, so the token operand is a plain 2-D TMA box as well.
 // A CTA is persistent and walks (block, 128-row weight tile) pairs: warp 0 issues TMA, warp 1 issues
-// MMAs and owns the TMEM allocation, warps 2-5 drain TMEM (each its own 32-lane quadrant).
+// MMAs and owns the TMEM allocation, warps 2-9 drain TMEM (two per 32-lane quadrant).
 // At decode sizes this path is bound by the HBM stream of expert weights, not by the tensor pipe.
 #include "common.cuh"
 #include "host.h"
@@ -133,7 +133,7 @@ struct GemmArgs {
 };
 
 constexpr int TILE_BYTES = 128 * 128;   // one 128-row x 128-byte operand tile
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;   // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int TMEM_COLS = 512;
 
 template <bool UP>
@@ -141,7 +141,7 @@ struct GemmCfg {
   static constexpr int NA = UP ? 2 : 1;                      // weight tiles per stage (gate + up)
   static constexpr int STAGE = NA * TILE_BYTES + TILE_BYTES;  // + token tile (<= 128 rows)
   static constexpr int STAGES = UP ? 4 : 6;
-  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + 4 * 128 * 12 /*row metadata, one copy per epilogue warp*/;
+  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + 8 * 128 * 12 /*row metadata, one copy per epilogue warp*/;
 };
 
 template <bool UP>
@@ -159,9 +159,9 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   // per-tile row metadata for the epilogue: each epilogue warp keeps its own copy, so no barrier
   // between warps is needed (a warp-private buffer is refilled only after that warp is done with it)
-  float* m_scale_all = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE + 256);  // [4][128] activation scale
-  float* m_wt_all = m_scale_all + 512;                                                // [4][128] routing weight
-  int* m_slot_all = reinterpret_cast<int*>(m_wt_all + 512);                           // [4][128] slot or -1
+  float* m_scale_all = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE + 256);  // [8][128] activation scale
+  float* m_wt_all = m_scale_all + 1024;                                               // [8][128] routing weight
+  int* m_slot_all = reinterpret_cast<int*>(m_wt_all + 1024);                          // [8][128] slot or -1
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -171,7 +171,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], 4);
+      mbar_init(&tempty[b], 8);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -288,11 +288,14 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   } else {
-    // ---------------- epilogue: warps 2..5, TMEM lane quadrant = warp % 4 ----------------
+    // ---------------- epilogue: warps 2..9; TMEM lane quadrant = warp % 4, and the two warps of a quadrant
+    // (they share a scheduler, so one covers the other's TMEM and memory latencies) take alternate
+    // 16-column chunks of the tile ----------------
     const int q = warp & 3;
-    float* ms = m_scale_all + q * 128;
-    float* m_wt = m_wt_all + q * 128;
-    int* m_slot = m_slot_all + q * 128;
+    const int half = (warp - 2) >> 2;
+    float* ms = m_scale_all + (warp - 2) * 128;
+    float* m_wt = m_wt_all + (warp - 2) * 128;
+    int* m_slot = m_slot_all + (warp - 2) * 128;
     const float* __restrict__ a_scale = p.a_scale;
     const float* __restrict__ wt_of_row = p.L.wt_of_row;
     const int32_t* __restrict__ slot_of_row = p.L.slot_of_row;
@@ -333,7 +336,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const float* sw = shared_e ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * p.w_rows;
         const float wsg = sw[r], wsu = sw[p.I + r];
         bf16* __restrict__ hout = p.h_out + static_cast<size_t>(row0) * p.I + r;
-        for (int c0 = 0; c0 < n; c0 += 16) {
+        for (int c0 = half * 16; c0 < n; c0 += 32) {
           uint32_t rg[16], ru[16];
           tmem_ld16(taddr + c0, rg);
           tmem_ld16(taddr + 128 + c0, ru);
@@ -366,7 +369,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       } else {
         const float ws = shared_e ? p.s_w_sh[r] : p.s_w[static_cast<size_t>(e) * p.w_rows + r];
         bf16* __restrict__ cache = p.cache + r;
-        for (int c0 = 0; c0 < n; c0 += 16) {
+        for (int c0 = half * 16; c0 < n; c0 += 32) {
           uint32_t ra[16];
           tmem_ld16(taddr + c0, ra);
           tmem_ld_wait();

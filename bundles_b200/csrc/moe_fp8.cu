@@ -16,7 +16,7 @@ namespace b200 {
 
 constexpr int F8_TILE = 128 * 128;       // weight tile bytes per stage
 constexpr int F8_BTILE = 64 * 128;       // token tile bytes per stage (<= 64 rows)
-constexpr int F8_THREADS = 192;
+constexpr int F8_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int F8_MAXKG = 32;             // k blocks per row of scales held in shared memory (K <= 4096)
 
 // ---- activation quantisers ----------------------------------------------------------------------------
@@ -88,7 +88,7 @@ struct F8Args {
   bf16* dbg_h;           // up: h by slot or null
   int32_t* status;
   // LM-head mode: one dense block of `total_rows` tokens against w_rows vocabulary rows
-  unsigned long long* lm_keys;  // [total_rows] packed (value, id) maxima, zeroed before the launch
+  unsigned long long* lm_keys;  // [mtiles * 4][total_rows] packed (value, id) maxima, one row per (tile, warp)
   float* lm_logits;             // [total_rows, w_rows] or null
   int lm_shard_lo;
 };
@@ -101,7 +101,7 @@ struct F8Cfg {
   static constexpr int NA = UP ? 2 : 1;
   static constexpr int STAGE = NA * F8_TILE + F8_BTILE;
   static constexpr int STAGES = UP ? 4 : 6;
-  static constexpr int META = 4 * (64 * F8_MAXKG * 4 + 64 * 8);  // per epilogue warp: scales, slot, weight
+  static constexpr int META = 8 * (32 * F8_MAXKG * 4 + 32 * 8);  // per epilogue warp: scales, slot, weight of its 32 columns
   static constexpr int SMEM = STAGES * STAGE + 1024 + 256 + META;
   static constexpr int TMEM = UP ? 256 : 128;
 };
@@ -130,7 +130,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&pfull[b], 1);
-      mbar_init(&pempty[b], 4);
+      mbar_init(&pempty[b], 8);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -242,14 +242,18 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   } else {
-    // ---------------- promotion + epilogue: warps 2..5, TMEM lane quadrant = warp % 4 ----------------
+    // ---------------- promotion + epilogue: warps 2..9.  TMEM lane quadrant = warp % 4; the two warps of a
+    // quadrant share a scheduler and take alternate 16-column chunks (chunk index parity = `half`), so each
+    // thread keeps at most 32 (+32 for up) accumulators ----------------
     const int q = warp & 3;
-    float* m_as = reinterpret_cast<float*>(meta + q * (64 * F8_MAXKG * 4 + 64 * 8));  // [64][ksteps]
-    float* m_wt = m_as + 64 * F8_MAXKG;                                                // [64]
-    int* m_slot = reinterpret_cast<int*>(m_wt + 64);                                   // [64]
+    const int half = (warp - 2) >> 2;
+    float* m_as = reinterpret_cast<float*>(meta + (warp - 2) * (32 * F8_MAXKG * 4 + 32 * 8));  // [32][ksteps]
+    float* m_wt = m_as + 32 * F8_MAXKG;                                                         // [32]
+    int* m_slot = reinterpret_cast<int*>(m_wt + 32);                                            // [32]
     const float* __restrict__ a_scale = p.a_scale;
     uint32_t g = 0;
     bool ok = true;
+    // local column l (0..31) of this warp is tile column col(l) = (l / 16) * 32 + half * 16 + l % 16
     for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
       int e, row0, n, mt;
       if (!decode(tile, e, row0, n, mt)) {
@@ -257,8 +261,13 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         continue;
       }
       __syncwarp();
-      for (int i = lane; i < n * p.ksteps; i += 32) m_as[i] = a_scale[static_cast<size_t>(row0) * p.ksteps + i];
-      for (int c = lane; c < 64; c += 32) {
+      for (int i = lane; i < 32 * p.ksteps; i += 32) {
+        const int l = i / p.ksteps, ks = i - l * p.ksteps;
+        const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+        m_as[i] = c < n ? a_scale[static_cast<size_t>(row0 + c) * p.ksteps + ks] : 0.f;
+      }
+      {
+        const int c = (lane >> 4) * 32 + half * 16 + (lane & 15);
         int slot = -1;
         float wt = 0.f;
         if (!LM && c < n) {
@@ -266,41 +275,41 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           wt = p.L.wt_of_row[row0 + c];
           if (slot >= p.total_rows) slot = -1;
         }
-        m_slot[c] = slot;
-        m_wt[c] = wt;
+        m_slot[lane] = slot;
+        m_wt[lane] = wt;
       }
       __syncwarp();
       const bool shared_e = (e == p.E_local);
       const float* swb = shared_e ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * (p.w_rows / 128) * p.ksteps;
       const float* sw_a = swb + static_cast<size_t>(mt) * p.ksteps;                      // gate / down block row
       const float* sw_b = swb + static_cast<size_t>(p.I / 128 + mt) * p.ksteps;          // up block row (UP only)
-      float acc_a[64], acc_b[UP ? 64 : 1];
+      float acc_a[32], acc_b[UP ? 32 : 1];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) acc_a[c] = 0.f;
+      for (int c = 0; c < 32; ++c) acc_a[c] = 0.f;
       if (UP)
 #pragma unroll
-        for (int c = 0; c < 64; ++c) acc_b[c] = 0.f;
+        for (int c = 0; c < 32; ++c) acc_b[c] = 0.f;
       for (int ks = 0; ks < p.ksteps; ++ks, ++g) {
         const uint32_t pb = g & 1u, pphase = (g >> 1) & 1u;
+        const float wsa = __ldg(sw_a + ks), wsb = UP ? __ldg(sw_b + ks) : 0.f;
         if (!mbar_wait(&pfull[pb], pphase, abort_flag, p.status, ST_WAIT_TMEM_FULL)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + pb * (UP ? 128 : 64) + (static_cast<uint32_t>(q * 32) << 16);
-        const float wsa = sw_a[ks], wsb = UP ? sw_b[ks] : 0.f;
+        const uint32_t taddr = tmem_base + pb * (UP ? 128 : 64) + half * 16 + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) {
-          if (c0 < n) {
+        for (int h2 = 0; h2 < 2; ++h2) {
+          if (h2 * 32 + half * 16 < n) {
             uint32_t ra[16], rb[16];
-            tmem_ld16(taddr + c0, ra);
-            if (UP) tmem_ld16(taddr + 64 + c0, rb);
+            tmem_ld16(taddr + h2 * 32, ra);
+            if (UP) tmem_ld16(taddr + 64 + h2 * 32, rb);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float as = m_as[(c0 + i) * p.ksteps + ks];
-              acc_a[c0 + i] = __fmaf_rn(__uint_as_float(ra[i]), __fmul_rn(as, wsa), acc_a[c0 + i]);
-              if (UP) acc_b[c0 + i] = __fmaf_rn(__uint_as_float(rb[i]), __fmul_rn(as, wsb), acc_b[c0 + i]);
+              const float as = m_as[(h2 * 16 + i) * p.ksteps + ks];
+              acc_a[h2 * 16 + i] = __fmaf_rn(__uint_as_float(ra[i]), __fmul_rn(as, wsa), acc_a[h2 * 16 + i]);
+              if (UP) acc_b[h2 * 16 + i] = __fmaf_rn(__uint_as_float(rb[i]), __fmul_rn(as, wsb), acc_b[h2 * 16 + i]);
             }
           }
         }
@@ -312,12 +321,13 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int r = mt * 128 + q * 32 + lane;
       if (LM) {
         // per token: the largest logit of this warp's 32 vocabulary rows and its id (ties to the lower
-        // id), merged across warps, tiles and CTAs with one 64-bit atomic max per token
+        // id) as one packed 64-bit key per (tile, quadrant, token); a small kernel takes the max over them
         const bool live = r < p.w_rows;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int l = 0; l < 32; ++l) {
+          const int c = (l >> 4) * 32 + half * 16 + (l & 15);
           if (c < n) {
-            const float v = acc_a[c];
+            const float v = acc_a[l];
             if (p.lm_logits && live) p.lm_logits[static_cast<size_t>(c) * p.w_rows + r] = v;
             uint32_t key = 0u;
             if (live && v == v) {
@@ -330,28 +340,32 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             }
             const uint32_t m = __reduce_max_sync(FULL_MASK, key);
             const uint32_t id = __reduce_min_sync(FULL_MASK, (key == m && live) ? static_cast<uint32_t>(r) : 0xffffffffu);
-            if (lane == 0 && m != 0u)
-              atomicMax(p.lm_keys + c, (static_cast<unsigned long long>(m) << 32) |
-                                           (0xffffffffu - static_cast<uint32_t>(p.lm_shard_lo + static_cast<int>(id))));
+            if (lane == 0)
+              p.lm_keys[(static_cast<size_t>(tile) * 4 + q) * n + c] =
+                  m == 0u ? 0ull
+                          : (static_cast<unsigned long long>(m) << 32) |
+                                (0xffffffffu - static_cast<uint32_t>(p.lm_shard_lo + static_cast<int>(id)));
           }
         }
       } else if (UP) {
         bf16* __restrict__ hout = p.h_out + static_cast<size_t>(row0) * p.I + r;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int l = 0; l < 32; ++l) {
+          const int c = (l >> 4) * 32 + half * 16 + (l & 15);
           if (c < n) {
-            const float gv = rbf(acc_a[c]), uv = rbf(acc_b[c]);
+            const float gv = rbf(acc_a[l]), uv = rbf(acc_b[l]);
             const bf16 hv = f2bf(__fmul_rn(__fdiv_rn(gv, 1.f + __expf(-gv)), uv));
             hout[static_cast<size_t>(c) * p.I] = hv;
-            if (p.dbg_h && m_slot[c] >= 0) p.dbg_h[static_cast<size_t>(m_slot[c]) * p.I + r] = hv;
+            if (p.dbg_h && m_slot[l] >= 0) p.dbg_h[static_cast<size_t>(m_slot[l]) * p.I + r] = hv;
           }
         }
       } else {
         bf16* __restrict__ cache = p.cache + r;
 #pragma unroll
-        for (int c = 0; c < 64; ++c)
-          if (c < n && m_slot[c] >= 0)
-            cache[static_cast<size_t>(m_slot[c]) * p.H] = f2bf(__fmul_rn(acc_a[c], m_wt[c]));
+        for (int l = 0; l < 32; ++l) {
+          const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+          if (c < n && m_slot[l] >= 0) cache[static_cast<size_t>(m_slot[l]) * p.H] = f2bf(__fmul_rn(acc_a[l], m_wt[l]));
+        }
       }
     }
   }
@@ -475,11 +489,21 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
 
 // ---- LM head shard with fused argmax ------------------------------------------------------------------
 namespace b200 {
-__global__ void lmhead_finish_kernel(const unsigned long long* __restrict__ keys, int T, float* __restrict__ max_out,
-                                     int32_t* __restrict__ idx_out) {
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= T) return;
-  const unsigned long long k = keys[t];
+__global__ void lmhead_finish_kernel(const unsigned long long* __restrict__ keys, int parts, int T,
+                                     float* __restrict__ max_out, int32_t* __restrict__ idx_out) {
+  // one warp per token: max over the (tile, warp) partial keys
+  const int t = blockIdx.x, lane = threadIdx.x;
+  unsigned long long k = 0ull;
+  for (int i = lane; i < parts; i += 32) {
+    const unsigned long long v = keys[static_cast<size_t>(i) * T + t];
+    k = v > k ? v : k;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long v = __shfl_xor_sync(FULL_MASK, k, o);
+    k = v > k ? v : k;
+  }
+  if (lane != 0) return;
   const uint32_t m = static_cast<uint32_t>(k >> 32);
   float v;
   if (m <= 1u)
@@ -517,21 +541,21 @@ __global__ void argmax_merge_kernel(const float* __restrict__ maxes, const int32
 struct LmLayout {
   size_t xq, xs, keys, total;
 };
-static LmLayout lm_layout(int T, int H) {
+static LmLayout lm_layout(int T, int H, int V_shard) {
   auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
   LmLayout l;
   size_t o = 0;
   l.xq = o; o = up(o + static_cast<size_t>(64) * H);  // 64 rows so that every 16-row TMA box is in bounds
   l.xs = o; o = up(o + static_cast<size_t>(T) * (H / 128) * 4);
-  l.keys = o; o = up(o + static_cast<size_t>(T) * 8);
+  l.keys = o; o = up(o + static_cast<size_t>((V_shard + 127) / 128) * 4 * T * 8);
   l.total = o;
   return l;
 }
 }  // namespace b200
 
-extern "C" size_t b200_lmhead_workspace_bytes(int T, int H) {
-  if (T <= 0 || H <= 0) return 0;
-  return lm_layout(T, H).total;
+extern "C" size_t b200_lmhead_workspace_bytes(int T, int H, int V_shard) {
+  if (T <= 0 || H <= 0 || V_shard <= 0) return 0;
+  return lm_layout(T, H, V_shard).total;
 }
 
 extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, const float* w_s, int V_shard,
@@ -541,7 +565,7 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   if (T <= 0 || T > 64 || H <= 0 || H % 128 || H / 128 > F8_MAXKG || V_shard <= 0 || shard_lo < 0)
     return fail(B200_E_ARG, "b200_lmhead_argmax: need 1 <= T <= 64, H %% 128 == 0, H <= 4096 (T=%d H=%d V=%d)", T, H,
                 V_shard);
-  const LmLayout l = lm_layout(T, H);
+  const LmLayout l = lm_layout(T, H, V_shard);
   if (ws_bytes < l.total) return fail(B200_E_WS, "b200_lmhead_argmax: workspace %zu < %zu bytes", ws_bytes, l.total);
   if (reinterpret_cast<uintptr_t>(ws) & 1023) return fail(B200_E_ALIGN, "b200_lmhead_argmax: workspace must be 1024-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -560,7 +584,6 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
     cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_LM>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<MODE_LM>::SMEM);
     attr_done[dev] = true;
   }
-  cudaMemsetAsync(keys, 0, static_cast<size_t>(T) * 8, st);
   // K = 0 routed picks: the "shared expert" row of token t is row t
   quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 1, xq, xs);
   F8Args a{};
@@ -580,7 +603,7 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   a.lm_shard_lo = shard_lo;
   const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
   moe_gemm_f8_kernel<MODE_LM><<<grid, F8_THREADS, F8Cfg<MODE_LM>::SMEM, st>>>(tmW, tmW, tmX, a);
-  lmhead_finish_kernel<<<1, 64, 0, st>>>(keys, T, max_out, idx_out);
+  lmhead_finish_kernel<<<T, 32, 0, st>>>(keys, a.mtiles * 4, T, max_out, idx_out);
   return launch_status("b200_lmhead_argmax");
 }
 

@@ -108,17 +108,21 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
   float xv[PER_LANE];
 #pragma unroll
   for (int j = 0; j < PER_LANE; ++j) xv[j] = 0.f;
-#pragma unroll 4
-  for (int s = 0; s < nslices; ++s) {
-    const float* pr = part + (static_cast<size_t>(s) * T + t) * E;
+  // four slices at a time: all loads of a batch are issued before the first add (the adds keep slice order)
+  for (int s0 = 0; s0 < nslices; s0 += 4) {
+    float pv[4][PER_LANE];
 #pragma unroll
-    for (int j = 0; j < PER_LANE; ++j) {
-      const int e = lane + 32 * j;
-      if (e < E) {
-        const float pv = pr[e];
-        xv[j] = s == 0 ? pv : __fadd_rn(xv[j], pv);
-      }
+    for (int u = 0; u < 4; ++u) {
+      const float* pr = part + (static_cast<size_t>(min(s0 + u, nslices - 1)) * T + t) * E;
+#pragma unroll
+      for (int j = 0; j < PER_LANE; ++j) pv[u][j] = (lane + 32 * j < E) ? __ldg(pr + lane + 32 * j) : 0.f;
     }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (s0 + u < nslices) {
+#pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) xv[j] = (s0 + u == 0) ? pv[u][j] : __fadd_rn(xv[j], pv[u][j]);
+      }
   }
   uint32_t key[PER_LANE];
   float mx = -INFINITY;

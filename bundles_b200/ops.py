@@ -227,8 +227,8 @@ def attn_front(x, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, eps=1e-6, out_
     return q, gate, k, v
 
 
-def lmhead_workspace(T, H, device):
-    n = _lib.lib().b200_lmhead_workspace_bytes(T, H)
+def lmhead_workspace(T, H, V, device):
+    n = _lib.lib().b200_lmhead_workspace_bytes(T, H, V)
     buf = torch.empty(n + 1024, dtype=torch.uint8, device=device)
     off = (-buf.data_ptr()) % 1024
     return buf[off:off + n]
@@ -246,7 +246,7 @@ def lmhead_argmax(x, w, w_s, shard_lo=0, want_logits=False, ws=None, status=None
     idx = torch.empty(T, dtype=torch.int32, device=x.device)
     logits = torch.empty(T, V, dtype=torch.float32, device=x.device) if want_logits else None
     if ws is None:
-        ws = lmhead_workspace(T, H, x.device)
+        ws = lmhead_workspace(T, H, V, x.device)
     check(_lib.lib().b200_lmhead_argmax(_p(x), T, H, _p(w), _p(w_s), V, int(shard_lo), _p(mx), _p(idx), _p(logits),
                                         _p(ws), ws.numel(), _p(status), _stream()), "b200_lmhead_argmax")
     return mx, idx, logits

@@ -215,9 +215,10 @@ int b200_attn_front(const void* x, int T, const void* w, const float* w_s, const
  * vocabulary rows and its global id (shard_lo + local row); ties go to the lower id, NaN never wins.
  *   x bf16 [T,H], 1 <= T <= 64, H % 128 == 0, H <= 4096; w e4m3 [V_shard,H];
  *   w_s fp32 [ceil(V_shard/128), H/128]; max_out fp32 [T]; idx_out int32 [T];
- *   logits_out fp32 [T,V_shard] or NULL; ws: b200_lmhead_workspace_bytes(T,H) bytes, 1024-byte aligned.
+ *   logits_out fp32 [T,V_shard] or NULL; ws: b200_lmhead_workspace_bytes(T,H,V_shard) bytes,
+ *   1024-byte aligned.
  */
-size_t b200_lmhead_workspace_bytes(int T, int H);
+size_t b200_lmhead_workspace_bytes(int T, int H, int V_shard);
 int b200_lmhead_argmax(const void* x, int T, int H, const void* w, const float* w_s, int V_shard, int shard_lo,
                        float* max_out, int32_t* idx_out, float* logits_out, void* ws, size_t ws_bytes,
                        int32_t* status, void* stream);
