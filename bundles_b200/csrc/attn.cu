@@ -10,10 +10,10 @@
 // 256 features of one head are the N side (TMEM columns), so a thread that owns a TMEM lane owns a
 // whole token row of the head and the RMS reduction stays thread-local.  Tile = 128 tokens x 256
 // features x K 128 per stage; per 128-k block the chain starts from zero in one of two TMEM partial
-// buffers (2 x 256 columns = all of TMEM) and sixteen epilogue warps promote it into registers,
-// acc = fma(partial, a_scale[token] * w_scale[block], acc): four warps share a lane quadrant (and a
-// scheduler) and take 64 columns each, inside one weight scale block, so the scale is one scalar per
-// thread and k block.
+// buffers (2 x 256 columns = all of TMEM) and eight epilogue warps promote it into registers,
+// acc = fma(partial, a_scale[token] * w_scale[block], acc): two warps share a lane quadrant and take
+// 128 columns each, which is exactly one weight scale block, so the scale is one scalar per thread
+// and k block.
 #include "common.cuh"
 #include "host.h"
 
@@ -23,9 +23,9 @@ constexpr int AT_H = 2048, AT_HD = 256, AT_HQ = 16, AT_HKV = 2, AT_ROT = 64;
 constexpr int AT_NCOLS = AT_HQ * 2 * AT_HD + 2 * AT_HKV * AT_HD;  // 9216
 constexpr int AT_NT = AT_NCOLS / AT_HD;                           // 36 head tiles
 constexpr int AT_KS = AT_H / 128;                                 // 16
-constexpr int AT_THREADS = 576;                                   // TMA warp, MMA warp, 16 epilogue warps
+constexpr int AT_THREADS = 320;                                   // TMA warp, MMA warp, 8 epilogue warps
 constexpr int AT_A = 128 * 128, AT_B = 256 * 128, AT_STAGE = AT_A + AT_B, AT_STAGES = 4;
-constexpr int AT_META = 2 * 4 * 128 * 4 /*ss quarters, two phases*/ + 2 * 256 * 4 /*1 + w*/;
+constexpr int AT_META = 2 * 2 * 128 * 4 /*ss halves, two phases*/ + 2 * 256 * 4 /*1 + w*/;
 constexpr int AT_SMEM = AT_STAGES * AT_STAGE + 1024 + 256 + AT_META;
 
 struct AttnArgs {
@@ -56,8 +56,8 @@ attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   uint64_t* ssbar = pempty + 2;         // [1] both column halves have published their sum of squares
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ssbar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* m_ss = reinterpret_cast<float*>(smem + AT_STAGES * AT_STAGE + 256);  // [2 phases][4 quarters][128]
-  float* m_w1 = m_ss + 1024;                                                   // [2][256]: 1 + q_norm_w, 1 + k_norm_w
+  float* m_ss = reinterpret_cast<float*>(smem + AT_STAGES * AT_STAGE + 256);  // [2 phases][2 halves][128]
+  float* m_w1 = m_ss + 512;                                                    // [2][256]: 1 + q_norm_w, 1 + k_norm_w
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -67,9 +67,9 @@ attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&pfull[b], 1);
-      mbar_init(&pempty[b], 16);
+      mbar_init(&pempty[b], 8);
     }
-    mbar_init(ssbar, 512);
+    mbar_init(ssbar, 256);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmX);
@@ -154,11 +154,9 @@ attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       }
     }
   } else {
-    // ---------------- promotion + fused epilogue: warps 2..17 ----------------
-    // TMEM lane quadrant = warp % 4; the four warps of a quadrant share a scheduler (one covers the
-    // others' TMEM latency) and take 64 of the head's 256 features each.
-    const int q = warp & 3;
-    const int cq = (warp - 2) >> 2;       // column quarter of the head: features cq*64 .. cq*64 + 63
+    // ---------------- promotion + fused epilogue: warps 2..9 ----------------
+    const int q = warp & 3;               // TMEM lane quadrant
+    const int hh = (warp - 2) >> 2;       // column half of the head: 0 -> features 0..127, 1 -> 128..255
     const int row = q * 32 + lane;        // token row inside the tile
     uint32_t g = 0, sscount = 0;
     bool ok = true;
@@ -166,10 +164,10 @@ attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       const int j = tile / mtiles, mt = tile - j * mtiles;
       const int t = mt * 128 + row;
       const float* asrow = p.a_scale + static_cast<size_t>(t < p.T ? t : 0) * AT_KS;  // this token's scales
-      const float* wsrow = p.w_s + static_cast<size_t>(2 * j + (cq >> 1)) * AT_KS;
-      float acc[64];
+      const float* wsrow = p.w_s + static_cast<size_t>(2 * j + hh) * AT_KS;
+      float acc[128];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) acc[c] = 0.f;
+      for (int c = 0; c < 128; ++c) acc[c] = 0.f;
       for (int ks = 0; ks < AT_KS; ++ks, ++g) {
         const uint32_t pb = g & 1u, pphase = (g >> 1) & 1u;
         const float sc = __fmul_rn(__ldg(asrow + ks), __ldg(wsrow + ks));  // issued before the wait
@@ -178,9 +176,9 @@ attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           break;
         }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + pb * 256 + cq * 64 + (static_cast<uint32_t>(q * 32) << 16);
+        const uint32_t taddr = tmem_base + pb * 256 + hh * 128 + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 32) {
+        for (int c0 = 0; c0 < 128; c0 += 32) {
           uint32_t r[32];
           tmem_ld32(taddr + c0, r);
           tmem_ld_wait();
@@ -192,28 +190,28 @@ attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         if (lane == 0) mbar_arrive(&pempty[pb]);
       }
       if (!ok) break;
-      // ---- epilogue on the thread's 64 features of token t ----
+      // ---- epilogue on the thread's 128 features of token t ----
       const bool is_q = j < 2 * AT_HQ && (j & 1) == 0;
       const bool is_gate = j < 2 * AT_HQ && (j & 1) == 1;
       const bool is_k = j >= 2 * AT_HQ && j < 2 * AT_HQ + AT_HKV;
       const int head = j < 2 * AT_HQ ? (j >> 1) : (is_k ? j - 2 * AT_HQ : j - 2 * AT_HQ - AT_HKV);
 #pragma unroll
-      for (int c = 0; c < 64; ++c) acc[c] = rbf(acc[c]);  // the projection is stored as bf16 before the front
+      for (int c = 0; c < 128; ++c) acc[c] = rbf(acc[c]);  // the projection is stored as bf16 before the front
       if (is_q || is_k) {
         float ss = 0.f;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) ss = fmaf(acc[c], acc[c], ss);
-        float* ssb = m_ss + (sscount & 1u) * 512;  // two phases: a fast thread may already write the next tile's
-        ssb[cq * 128 + row] = ss;
+        for (int c = 0; c < 128; ++c) ss = fmaf(acc[c], acc[c], ss);
+        float* ssb = m_ss + (sscount & 1u) * 256;  // two phases: a fast thread may already write the next tile's
+        ssb[hh * 128 + row] = ss;
         mbar_arrive(ssbar);
         if (!mbar_wait(ssbar, sscount & 1u, abort_flag, p.status, ST_WAIT_STORE)) break;
         ++sscount;
-        const float tot = (ssb[row] + ssb[128 + row]) + (ssb[256 + row] + ssb[384 + row]);
+        const float tot = ssb[row] + ssb[128 + row];
         const float inv = rsqrtf(tot / AT_HD + p.eps);
-        const float* w1 = m_w1 + (is_k ? 256 : 0) + cq * 64;
+        const float* w1 = m_w1 + (is_k ? 256 : 0) + hh * 128;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) acc[c] = rbf(acc[c] * inv * w1[c]);
-        if (cq == 0 && t < p.T) {
+        for (int c = 0; c < 128; ++c) acc[c] = rbf(acc[c] * inv * w1[c]);
+        if (hh == 0 && t < p.T) {
           long long pos = p.positions[t];
           pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
           const float* cs = p.cos_sin + static_cast<size_t>(pos) * AT_ROT;
@@ -228,19 +226,19 @@ attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       }
       if (t < p.T) {
         if (is_gate) {
-          uint4* dst = reinterpret_cast<uint4*>(p.gate + (static_cast<size_t>(t) * AT_HQ + head) * AT_HD + cq * 64);
+          uint4* dst = reinterpret_cast<uint4*>(p.gate + (static_cast<size_t>(t) * AT_HQ + head) * AT_HD + hh * 128);
 #pragma unroll
-          for (int c = 0; c < 64; c += 8)
+          for (int c = 0; c < 128; c += 8)
             dst[c >> 3] = make_uint4(pack_bf2(acc[c], acc[c + 1]), pack_bf2(acc[c + 2], acc[c + 3]),
                                      pack_bf2(acc[c + 4], acc[c + 5]), pack_bf2(acc[c + 6], acc[c + 7]));
         } else {
           void* base = is_q ? p.q : (is_k ? p.k : p.v);
           const int heads = is_q ? AT_HQ : AT_HKV;
-          const size_t off = (static_cast<size_t>(t) * heads + head) * AT_HD + cq * 64;
+          const size_t off = (static_cast<size_t>(t) * heads + head) * AT_HD + hh * 128;
           if (p.out_fp8) {
             uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(base) + off);
 #pragma unroll
-            for (int c = 0; c < 64; c += 16)
+            for (int c = 0; c < 128; c += 16)
               dst[c >> 4] = make_uint4(e4m3x4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]),
                                        e4m3x4(acc[c + 4], acc[c + 5], acc[c + 6], acc[c + 7]),
                                        e4m3x4(acc[c + 8], acc[c + 9], acc[c + 10], acc[c + 11]),
@@ -248,7 +246,7 @@ attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           } else {
             uint4* dst = reinterpret_cast<uint4*>(static_cast<bf16*>(base) + off);
 #pragma unroll
-            for (int c = 0; c < 64; c += 8)
+            for (int c = 0; c < 128; c += 8)
               dst[c >> 3] = make_uint4(pack_bf2(acc[c], acc[c + 1]), pack_bf2(acc[c + 2], acc[c + 3]),
                                        pack_bf2(acc[c + 4], acc[c + 5]), pack_bf2(acc[c + 6], acc[c + 7]));
           }

@@ -14,6 +14,7 @@ from . import ops
 
 class MoeBlockW8A8:
     """int8 W8A8 experts (per-output-channel weight scales, per-token activation scales)."""
+    BLOCK_ROWS = 128          # largest N tile of the int8 GEMMs
 
     def __init__(self, wr, weights: ops.MoeW8A8Weights, gate_w, top_k, bias=None, e_lo=0, round_bf16=False,
                  use_graph=True):
@@ -32,8 +33,8 @@ class MoeBlockW8A8:
         b = self._ws.get(T)
         if b is None:
             K = self.top_k
-            b = dict(lists=ops.RoutingLists(T, K, self.E_local, 128, device),
-                     ws=ops.moe_w8a8_workspace(T, self.H, self.I, K, device),
+            b = dict(lists=ops.RoutingLists(T, K, self.E_local, self.BLOCK_ROWS, device),
+                     ws=self._workspace(T, K, device),
                      cache=torch.zeros(T * (K + 1), self.H, dtype=torch.bfloat16, device=device),
                      scratch=ops.router_scratch(T, self.H, self.wr.shape[0], device),
                      ids=torch.empty(T, K, dtype=torch.int32, device=device),
@@ -79,8 +80,25 @@ class MoeBlockW8A8:
         _, ids, wts = ops.router(x, self.wr, self.top_k, self.bias, self.round_bf16, scratch=b["scratch"],
                                  want_logits=False, ids=b["ids"], wts=b["wts"])
         ops.build_lists(ids, wts, b["lists"], positions, e_lo=self.e_lo, with_shared=self.w.sh13 is not None)
-        ops.moe_w8a8(x, self.w, b["lists"], cache=b["cache"], ws=b["ws"], status=self.status)
+        self._experts(x, b)
         return ops.moe_combine(b["cache"], x, self.gate_w if self.w.sh13 is not None else None, self.top_k, positions,
                                out=b["out"])
 
     __call__ = forward
+
+    def _workspace(self, T, K, device):
+        return ops.moe_w8a8_workspace(T, self.H, self.I, K, device)
+
+    def _experts(self, x, b):
+        ops.moe_w8a8(x, self.w, b["lists"], cache=b["cache"], ws=b["ws"], status=self.status)
+
+
+class MoeBlockFp8(MoeBlockW8A8):
+    """fp8 e4m3 experts with 128 x 128 weight block scales and per-(token, 128-channel) activation scales."""
+    BLOCK_ROWS = 64           # the fp8 GEMMs keep their final accumulators in registers: N <= 64
+
+    def _workspace(self, T, K, device):
+        return ops.moe_fp8_workspace(T, self.H, self.I, K, device)
+
+    def _experts(self, x, b):
+        ops.moe_fp8(x, self.w, b["lists"], cache=b["cache"], ws=b["ws"], status=self.status)

@@ -28,7 +28,9 @@ def quant_int8_rows(w: torch.Tensor):
     (qwen36_lmhead8/lmhead8.py:95-108 `quantize_rows`).  Returns (int8, fp32 scale)."""
     wf = w.float()
     amax = wf.abs().amax(dim=-1)
-    scale = amax / 127.0
+    # tensor / tensor: an IEEE division on every device (tensor / python scalar is a multiplication by the
+    # rounded reciprocal on CUDA, one ulp off amax / 127 now and then)
+    scale = amax / torch.full_like(amax, 127.0)
     safe = torch.where(amax > 0, scale, torch.ones_like(scale))
     v = wf / safe.unsqueeze(-1)
     r = torch.where(v >= 0, torch.floor(v + 0.5), -torch.floor(0.5 - v)).clamp_(-127, 127)
@@ -42,8 +44,8 @@ def quant_fp8_blocks(w: torch.Tensor, block: int = 128):
     *lead, n, k = wf.shape
     b = wf.reshape(*lead, n // block, block, k // block, block)
     amax = b.abs().amax(dim=(-3, -1))
-    scale = (amax / 448.0).clamp_min(1e-12)
-    inv = 1.0 / scale
+    scale = (amax / torch.full_like(amax, 448.0)).clamp_min(1e-12)   # IEEE division, see quant_int8_rows
+    inv = torch.ones_like(scale) / scale
     y = (b * inv[..., :, None, :, None]).clamp_(-448.0, 448.0)
     codes = y.reshape(*lead, n, k).to(torch.float8_e4m3fn).view(torch.uint8)
     return codes, scale
