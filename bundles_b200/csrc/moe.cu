@@ -311,9 +311,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       ++it;
       // stage this block's row metadata while the MMAs run
       __syncwarp();
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int c = lane + 32 * i;
+      for (int c = lane; c < ((n + 15) & ~15); c += 32) {  // entries past n only pad the last 16-column chunk
         float sc = 0.f, wt = 0.f;
         int slot = -1;
         if (c < n) {
@@ -347,7 +345,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             const float xs = ms[c0 + i];
             const float g = rbf(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(rg[i])), xs), wsg));
             const float u = rbf(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ru[i])), xs), wsu));
-            hv[i] = f2bf(__fmul_rn(__fdiv_rn(g, 1.f + __expf(-g)), u));
+            hv[i] = f2bf(__fmul_rn(__fdividef(g, 1.f + __expf(-g)), u));
           }
 #pragma unroll
           for (int i = 0; i < 16; ++i)

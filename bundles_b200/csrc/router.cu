@@ -94,43 +94,52 @@ __device__ __forceinline__ float topk_unkey(uint32_t u) {
   return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
 }
 
-// One warp per token; lane l holds experts l, l + 32, ...  Adds the slice partials in slice order
-// (+ bias), optionally stores the logits, then softmax + K rounds of (warp max of the value key,
-// warp min of the id among the lanes that hold it), both single redux instructions.
-template <int PER_LANE>
+// One CTA of four warps per token.  Warp w owns experts [w * E/4, (w+1) * E/4), lane l holds experts
+// base + l + 32 j.  Each lane adds its experts' slice partials in slice order (+ bias); every load of
+// the token is in flight at once.  Each warp then takes its own top K with two redux instructions per
+// pick (warp max of the value key, warp min of the id among the lanes that hold it); warp 0 merges the
+// 4 K candidates the same way.  Softmax statistics go through shared memory.
+constexpr int TK_WARPS = 4;
+template <int PL>  // experts per lane: ceil(E / 128)
 __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ part, int nslices,
                                                           const float* __restrict__ bias, int T, int E, int K,
                                                           int round_bf16, float* __restrict__ logits,
                                                           int32_t* __restrict__ ids, float* __restrict__ wts) {
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= T) return;
-  float xv[PER_LANE];
+  __shared__ float s_max[TK_WARPS], s_sum[TK_WARPS];
+  __shared__ uint32_t c_key[TK_WARPS * 32];
+  __shared__ int c_id[TK_WARPS * 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x;
+  const int EW = E / TK_WARPS;  // experts of this warp; entry j of lane l exists when l + 32 j < EW
+  const int ebase = warp * EW;
+  float xv[PL];
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) xv[j] = 0.f;
-  // four slices at a time: all loads of a batch are issued before the first add (the adds keep slice order)
-  for (int s0 = 0; s0 < nslices; s0 += 4) {
-    float pv[4][PER_LANE];
+  for (int j = 0; j < PL; ++j) xv[j] = 0.f;
+  {
+    // slice partials: groups of 8 slices, all loads of a group issued before its adds
+    for (int s0 = 0; s0 < nslices; s0 += 8) {
+      float pv[8][PL];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float* pr = part + (static_cast<size_t>(min(s0 + u, nslices - 1)) * T + t) * E;
+      for (int u = 0; u < 8; ++u) {
+        const float* pr = part + (static_cast<size_t>(min(s0 + u, nslices - 1)) * T + t) * E + ebase + lane;
 #pragma unroll
-      for (int j = 0; j < PER_LANE; ++j) pv[u][j] = (lane + 32 * j < E) ? __ldg(pr + lane + 32 * j) : 0.f;
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-      if (s0 + u < nslices) {
-#pragma unroll
-        for (int j = 0; j < PER_LANE; ++j) xv[j] = (s0 + u == 0) ? pv[u][j] : __fadd_rn(xv[j], pv[u][j]);
+        for (int j = 0; j < PL; ++j) pv[u][j] = (lane + 32 * j < EW) ? __ldg(pr + 32 * j) : 0.f;
       }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (s0 + u < nslices) {
+#pragma unroll
+          for (int j = 0; j < PL; ++j) xv[j] = (s0 + u == 0) ? pv[u][j] : __fadd_rn(xv[j], pv[u][j]);
+        }
+    }
   }
-  uint32_t key[PER_LANE];
+  uint32_t key[PL];
   float mx = -INFINITY;
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) {
-    const int e = lane + 32 * j;
+  for (int j = 0; j < PL; ++j) {
+    const int e = ebase + lane + 32 * j;
     float v = xv[j];
-    if (e < E) {
+    if (lane + 32 * j < EW) {
       if (bias) v = __fadd_rn(v, __ldg(bias + e));
       if (logits) logits[static_cast<size_t>(t) * E + e] = v;
       if (round_bf16) v = rbf(v);
@@ -138,46 +147,50 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
       if (v == v) mx = fmaxf(mx, v + 0.f);
     } else {
       key[j] = 0u;
-      v = __int_as_float(0x7fc00000);
+      v = __int_as_float(0x7fc00000);  // absent: contributes nothing to the softmax sum
     }
     xv[j] = v;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(FULL_MASK, mx, o));
+  if (lane == 0) s_max[warp] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(s_max[0], s_max[1]), fmaxf(s_max[2], s_max[3]));
   float sum = 0.f;
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) {
+  for (int j = 0; j < PL; ++j) {
     const float v = xv[j];
     sum += (v == v) ? expf((v + 0.f) - mx) : 0.f;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(FULL_MASK, sum, o);
+  if (lane == 0) s_sum[warp] = sum;
+  // this warp's top K (K <= 32): lane k keeps the k-th pick
   uint32_t bk = 0u;
   int bj = 0;
 #pragma unroll
-  for (int j = 0; j < PER_LANE; ++j)
+  for (int j = 0; j < PL; ++j)
     if (key[j] > bk) {
       bk = key[j];
       bj = j;
     }
-  float my_w = 0.f, tot = 0.f;
-  int my_id = 0;
-  for (int k = 0; k < K; ++k) {
+  uint32_t my_key = 0u;
+  int my_id = 0x7fffffff;
+  const int Kw = min(K, E / TK_WARPS);
+  for (int k = 0; k < Kw; ++k) {
     const uint32_t m = __reduce_max_sync(FULL_MASK, bk);
-    const uint32_t cand = (bk == m) ? static_cast<uint32_t>(lane + 32 * bj) : 0x7fffffffu;
+    const uint32_t cand = (bk == m) ? static_cast<uint32_t>(ebase + lane + 32 * bj) : 0x7fffffffu;
     const int id = static_cast<int>(__reduce_min_sync(FULL_MASK, cand));
-    const float pr = m <= 1u ? 0.f : __fdiv_rn(expf(topk_unkey(m) - mx), sum);
-    tot = __fadd_rn(tot, pr);
     if (lane == k) {
-      my_w = pr;
+      my_key = m;
       my_id = id;
     }
-    if (lane == (id & 31)) {  // the owner drops the pick and rescans its entries
-      const int dead = id >> 5;
+    if (lane == ((id - ebase) & 31)) {  // the owner drops the pick and rescans its entries
+      const int dead = (id - ebase) >> 5;
       bk = 0u;
       bj = 0;
 #pragma unroll
-      for (int j = 0; j < PER_LANE; ++j) {
+      for (int j = 0; j < PL; ++j) {
         if (j == dead) key[j] = 0u;
         if (key[j] > bk) {
           bk = key[j];
@@ -186,9 +199,52 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
       }
     }
   }
+  c_key[warp * 32 + lane] = my_key;  // lanes >= Kw hold key 0 (absent)
+  c_id[warp * 32 + lane] = my_id;
+  __syncthreads();
+  if (warp != 0) return;
+  sum = (s_sum[0] + s_sum[1]) + (s_sum[2] + s_sum[3]);
+  // merge: lane l holds candidate l of every warp; pick by larger key, then smaller id
+  uint32_t ck[TK_WARPS];
+  int ci[TK_WARPS];
+#pragma unroll
+  for (int w = 0; w < TK_WARPS; ++w) {
+    ck[w] = c_key[w * 32 + lane];
+    ci[w] = c_id[w * 32 + lane];
+  }
+  auto rescan = [&](uint32_t& best_k, int& best_i) {
+    best_k = 0u;
+    best_i = 0x7fffffff;
+#pragma unroll
+    for (int w = 0; w < TK_WARPS; ++w)
+      if (ck[w] > best_k || (ck[w] == best_k && ck[w] != 0u && ci[w] < best_i)) {
+        best_k = ck[w];
+        best_i = ci[w];
+      }
+  };
+  int bi;
+  rescan(bk, bi);
+  float my_w = 0.f, tot = 0.f;
+  int out_id = 0;
+  for (int k = 0; k < K; ++k) {
+    const uint32_t m = __reduce_max_sync(FULL_MASK, bk);
+    const int id = static_cast<int>(__reduce_min_sync(FULL_MASK, (bk == m) ? static_cast<uint32_t>(bi) : 0x7fffffffu));
+    const float pr = m <= 1u ? 0.f : __fdiv_rn(expf(topk_unkey(m) - mx), sum);
+    tot = __fadd_rn(tot, pr);
+    if (lane == k) {
+      my_w = pr;
+      out_id = id;
+    }
+    if (bk == m && bi == id) {  // exactly one lane holds this (key, id)
+#pragma unroll
+      for (int w = 0; w < TK_WARPS; ++w)
+        if (ck[w] == m && ci[w] == id) ck[w] = 0u;
+      rescan(bk, bi);
+    }
+  }
   const float den = tot > 0.f ? tot : 1.f;
   if (lane < K) {
-    ids[static_cast<size_t>(t) * K + lane] = my_id;
+    ids[static_cast<size_t>(t) * K + lane] = out_id;
     wts[static_cast<size_t>(t) * K + lane] = __fdiv_rn(my_w, den);
   }
 }
@@ -339,8 +395,9 @@ static size_t lists_smem_bytes(int T, int K, int E_local) {
 
 using namespace b200;
 
+// scratch: slice partials [H/128][T][E] fp32
 extern "C" size_t b200_router_scratch_bytes(int T, int H, int E) {
-  if (T <= 0 || H <= 0 || E <= 0 || H % RT_SLICE) return 0;
+  if (T <= 0 || H <= 0 || E <= 0 || H % RT_SLICE || E % RT_EXP) return 0;
   return static_cast<size_t>(H / RT_SLICE) * T * E * sizeof(float);
 }
 
@@ -368,15 +425,16 @@ extern "C" int b200_router(const void* x, const float* wr, const float* bias, in
   const int nslices = H / RT_SLICE;
   dim3 grid((T + RT_TOK - 1) / RT_TOK, E / RT_EXP, nslices);
   router_partials_kernel<<<grid, RT_THREADS, RT_SMEM, st>>>(static_cast<const bf16*>(x), wr, T, H, E, part);
-  const int per_lane = (E + 31) / 32;
-  dim3 g2((T + 3) / 4);
   const int rb = flags & 1;
-  if (per_lane <= 8)
-    router_topk_kernel<8><<<g2, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
-  else if (per_lane <= 16)
-    router_topk_kernel<16><<<g2, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
+  const int pl = (E + 127) / 128;
+  if (pl <= 1)
+    router_topk_kernel<1><<<T, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
+  else if (pl <= 2)
+    router_topk_kernel<2><<<T, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
+  else if (pl <= 4)
+    router_topk_kernel<4><<<T, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
   else
-    router_topk_kernel<32><<<g2, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
+    router_topk_kernel<8><<<T, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
   return launch_status("b200_router");
 }
 
@@ -392,7 +450,7 @@ extern "C" int b200_router(const void* x, const float* wr, const float* bias, in
 // exits.  It is shared by all calls and keeps the previous call's partials; nothing in it has to
 // start at zero because the gate kernel overwrites every partial the top-k kernel reads.  Two calls
 // that overlap on the GPU (different streams, or different host threads) would race on it.
-constexpr size_t ROUTER_STATIC_SCRATCH_BYTES = size_t(2) << 20;  // e.g. 64 tokens x 512 experts x 16 slices x 4 B
+constexpr size_t ROUTER_STATIC_SCRATCH_BYTES = size_t(2) << 20;  // 64 tokens x 512 experts x 16 slices x 4 B
 static __device__ __align__(256) unsigned char g_router_static_scratch[ROUTER_STATIC_SCRATCH_BYTES];
 
 extern "C" size_t b200_router_static_max_scratch_bytes(void) { return ROUTER_STATIC_SCRATCH_BYTES; }
@@ -401,10 +459,11 @@ extern "C" int b200_router_static(const void* x, const float* wr, const float* b
                                   int flags, float* logits, int32_t* ids, float* wts, void* stream) {
   if (T < 0 || H <= 0 || E <= 0 || H % RT_SLICE)
     return fail(B200_E_ARG, "b200_router_static: bad shape (T=%d H=%d E=%d)", T, H, E);
-  const size_t need = static_cast<size_t>(H / RT_SLICE) * static_cast<size_t>(T) * static_cast<size_t>(E) * sizeof(float);
+  if (E % RT_EXP) return fail(B200_E_ARG, "b200_router_static: E must be a multiple of 64 (E=%d)", E);
+  const size_t need = T == 0 ? 0 : b200_router_scratch_bytes(T, H, E);
   if (need > ROUTER_STATIC_SCRATCH_BYTES)
     return fail(B200_E_WS,
-                "b200_router_static: T=%d H=%d E=%d needs %zu bytes of slice partials, the built-in scratch holds %zu; "
+                "b200_router_static: T=%d H=%d E=%d needs %zu bytes of scratch, the built-in scratch holds %zu; "
                 "use b200_router with a caller-provided scratch buffer",
                 T, H, E, need, ROUTER_STATIC_SCRATCH_BYTES);
   // In host code the array's name is only a handle; the device address is looked up once per device,

@@ -72,8 +72,8 @@ int b200_router(const void* x, const float* wr, const float* bias, int T, int H,
  * stall the device.  This entry point takes the same arguments as b200_router minus the scratch:
  * the slice partials go to a 2 MiB array built into the library (held by every GPU that loads the
  * library, until exit).  It calls no cudaMalloc / cudaFree and no allocating library routine.
- *   - Limit: (H/128) * T * E * 4 bytes must fit in b200_router_static_max_scratch_bytes() (2 MiB,
- *     e.g. 64 tokens x 512 experts at H = 2048); larger problems return B200_E_WS.
+ *   - Limit: b200_router_scratch_bytes(T, H, E) must fit in b200_router_static_max_scratch_bytes()
+ *     (2 MiB: 64 tokens x 512 experts at H = 2048 fit exactly); larger problems return B200_E_WS.
  *   - The first call on each device looks up the array's device address (with that device
  *     current); make that first call before any stream capture.
  *   - All calls share the array, and it keeps the last call's contents (nothing needs clearing:
