@@ -93,7 +93,7 @@ struct F8Args {
   int lm_shard_lo;
 };
 
-constexpr int MODE_DOWN = 0, MODE_UP = 1, MODE_LM = 2;
+constexpr int MODE_DOWN = 0, MODE_UP = 1, MODE_LM = 2, MODE_DENSE = 3;
 
 template <int MODE>
 struct F8Cfg {
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(F8_THREADS, 1)
 moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWsh,
                    const __grid_constant__ CUtensorMap tmX, const F8Args p) {
   using C = F8Cfg<MODE>;
-  constexpr bool UP = MODE == MODE_UP, LM = MODE == MODE_LM;
+  constexpr bool UP = MODE == MODE_UP, LM = MODE == MODE_LM || MODE == MODE_DENSE, DENSE = MODE == MODE_DENSE;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE);
@@ -319,7 +319,17 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       if (!ok) break;
       const int r = mt * 128 + q * 32 + lane;
-      if (LM) {
+      if (DENSE) {
+        // plain projection: out[token][feature] = bf16(acc)
+        if (r < p.w_rows) {
+          bf16* __restrict__ o = p.h_out + r;
+#pragma unroll
+          for (int l = 0; l < 32; ++l) {
+            const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+            if (c < n) o[static_cast<size_t>(c) * p.w_rows] = f2bf(acc_a[l]);
+          }
+        }
+      } else if (LM) {
         // per token: the largest logit of this warp's 32 vocabulary rows and its id (ties to the lower
         // id) as one packed 64-bit key per (tile, quadrant, token); a small kernel takes the max over them
         const bool live = r < p.w_rows;
@@ -613,4 +623,104 @@ extern "C" int b200_argmax_merge(const float* maxes, const int32_t* idxs, int S,
   if (T == 0) return 0;
   argmax_merge_kernel<<<(T + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(maxes, idxs, S, T, tokens);
   return launch_status("b200_argmax_merge");
+}
+
+// ---- dense decode-width projection (fp8 block-scaled weight, <= 64 rows) and the add + norm after it ----
+namespace b200 {
+// r = bf16(proj + residual) (the projection is already rounded to bf16; the add is fp32), written back to
+// `residual`; y = bf16(r * rsqrt(mean r^2 + eps) * (1 + w)).  One CTA per row.
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const bf16* __restrict__ proj, bf16* __restrict__ residual,
+                                                          const bf16* __restrict__ w, float eps, int H,
+                                                          bf16* __restrict__ out) {
+  __shared__ float red[8];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  float ss = 0.f;
+  for (int c = tid * 8; c < H; c += 2048) {
+    const uint4 a = *reinterpret_cast<const uint4*>(proj + static_cast<size_t>(t) * H + c);
+    const uint4 b = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * H + c);
+    float r[8] = {rbf(bf_lo(a.x) + bf_lo(b.x)), rbf(bf_hi(a.x) + bf_hi(b.x)), rbf(bf_lo(a.y) + bf_lo(b.y)),
+                  rbf(bf_hi(a.y) + bf_hi(b.y)), rbf(bf_lo(a.z) + bf_lo(b.z)), rbf(bf_hi(a.z) + bf_hi(b.z)),
+                  rbf(bf_lo(a.w) + bf_lo(b.w)), rbf(bf_hi(a.w) + bf_hi(b.w))};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(r[i], r[i], ss);
+    *reinterpret_cast<uint4*>(residual + static_cast<size_t>(t) * H + c) =
+        make_uint4(pack_bf2(r[0], r[1]), pack_bf2(r[2], r[3]), pack_bf2(r[4], r[5]), pack_bf2(r[6], r[7]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(FULL_MASK, ss, o);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rstd = rsqrtf(tot / H + eps);
+  for (int c = tid * 8; c < H; c += 2048) {  // each thread re-reads the rows it wrote itself
+    const uint4 b = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * H + c);
+    const uint4 g = *reinterpret_cast<const uint4*>(w + c);
+    const float r[8] = {bf_lo(b.x), bf_hi(b.x), bf_lo(b.y), bf_hi(b.y), bf_lo(b.z), bf_hi(b.z), bf_lo(b.w), bf_hi(b.w)};
+    const float gw[8] = {bf_lo(g.x), bf_hi(g.x), bf_lo(g.y), bf_hi(g.y), bf_lo(g.z), bf_hi(g.z), bf_lo(g.w), bf_hi(g.w)};
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = r[i] * rstd * (1.f + gw[i]);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + c) =
+        make_uint4(pack_bf2(y[0], y[1]), pack_bf2(y[2], y[3]), pack_bf2(y[4], y[5]), pack_bf2(y[6], y[7]));
+  }
+}
+}  // namespace b200
+
+extern "C" size_t b200_dense_fp8_workspace_bytes(int T, int H) {
+  if (T <= 0 || H <= 0) return 0;
+  auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+  return up(static_cast<size_t>(64) * H) + up(static_cast<size_t>(T) * (H / 128) * 4);
+}
+
+extern "C" int b200_dense_fp8(const void* x, int T, int H, const void* w, const float* w_s, int N, void* out, void* ws,
+                              size_t ws_bytes, int32_t* status, void* stream) {
+  if (!x || !w || !w_s || !out || !ws) return fail(B200_E_ARG, "b200_dense_fp8: null pointer");
+  if (T <= 0 || T > 64 || H <= 0 || H % 128 || H / 128 > F8_MAXKG || N <= 0)
+    return fail(B200_E_ARG, "b200_dense_fp8: need 1 <= T <= 64, H %% 128 == 0, H <= 4096 (T=%d H=%d N=%d)", T, H, N);
+  if (ws_bytes < b200_dense_fp8_workspace_bytes(T, H))
+    return fail(B200_E_WS, "b200_dense_fp8: workspace %zu < %zu bytes", ws_bytes, b200_dense_fp8_workspace_bytes(T, H));
+  if (reinterpret_cast<uintptr_t>(ws) & 1023) return fail(B200_E_ALIGN, "b200_dense_fp8: workspace must be 1024-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* xq = static_cast<uint8_t*>(ws);
+  float* xs = reinterpret_cast<float*>(xq + ((static_cast<size_t>(64) * H + 1023) & ~size_t(1023)));
+  CUtensorMap tmW, tmX;
+  int rc;
+  if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(N), H, 128, "dense weight"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "dense activations"))) return rc;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         F8Cfg<MODE_DENSE>::SMEM);
+    attr_done[dev] = true;
+  }
+  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 1, xq, xs);
+  F8Args a{};
+  a.E_local = 1;
+  a.mtiles = (N + 127) / 128;
+  a.ksteps = H / 128;
+  a.w_rows = N;
+  a.H = H;
+  a.total_rows = T;
+  a.s_w = w_s;
+  a.s_w_sh = w_s;
+  a.a_scale = xs;
+  a.h_out = static_cast<bf16*>(out);
+  a.status = status;
+  const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
+  moe_gemm_f8_kernel<MODE_DENSE><<<grid, F8_THREADS, F8Cfg<MODE_DENSE>::SMEM, st>>>(tmW, tmW, tmX, a);
+  return launch_status("b200_dense_fp8");
+}
+
+extern "C" int b200_add_rmsnorm(const void* proj, void* residual, const void* w, float eps, int T, int H, void* out,
+                                void* stream) {
+  if (!proj || !residual || !w || !out) return fail(B200_E_ARG, "b200_add_rmsnorm: null pointer");
+  if (T < 0 || H <= 0 || H % 8) return fail(B200_E_ARG, "b200_add_rmsnorm: need H %% 8 == 0 (H=%d)", H);
+  if (T == 0) return 0;
+  add_rmsnorm_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const bf16*>(proj), static_cast<bf16*>(residual), static_cast<const bf16*>(w), eps, H,
+      static_cast<bf16*>(out));
+  return launch_status("b200_add_rmsnorm");
 }

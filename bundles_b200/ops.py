@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import B200Error, MoeLists, MoeWeights, check
 
-__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_fp8", "moe_combine", "attn_front", "lmhead_argmax", "argmax_merge", "gdn_verify",
+__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_fp8", "moe_combine", "attn_front", "dense_fp8", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
            "new_status", "read_status", "B200Error"]
 
 
@@ -225,6 +225,38 @@ def attn_front(x, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, eps=1e-6, out_
                                      cos_sin.shape[0], float(eps), 1 if out_fp8 else 0, _p(q), _p(gate), _p(k), _p(v),
                                      _p(ws), ws.numel(), _p(status), _stream()), "b200_attn_front")
     return q, gate, k, v
+
+
+def dense_fp8(x, w, w_s, out=None, ws=None, status=None):
+    """Decode-width projection out = bf16(x . W^T) with an fp8 block-scaled weight, T <= 64 rows
+    (reference: qk_proj_decode gdn_in_proj / qkv_proj / dense8)."""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(w, torch.uint8, "w", 2)
+    _need(w_s, torch.float32, "w_s", 2)
+    T, H = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    if ws is None:
+        n = _lib.lib().b200_dense_fp8_workspace_bytes(T, H)
+        buf = torch.empty(n + 1024, dtype=torch.uint8, device=x.device)
+        off = (-buf.data_ptr()) % 1024
+        ws = buf[off:off + n]
+    check(_lib.lib().b200_dense_fp8(_p(x), T, H, _p(w), _p(w_s), N, _p(out), _p(ws), ws.numel(), _p(status),
+                                    _stream()), "b200_dense_fp8")
+    return out
+
+
+def add_rmsnorm(proj, residual, w, eps=1e-6, out=None):
+    """residual <- bf16(proj + residual); returns bf16(residual * rstd * (1 + w)) (reference: proj.project_add_norm)."""
+    _need(proj, torch.bfloat16, "proj", 2)
+    _need(residual, torch.bfloat16, "residual", 2)
+    T, H = proj.shape
+    if out is None:
+        out = torch.empty_like(proj)
+    check(_lib.lib().b200_add_rmsnorm(_p(proj), _p(residual), _p(w), float(eps), T, H, _p(out), _stream()),
+          "b200_add_rmsnorm")
+    return out
 
 
 def lmhead_workspace(T, H, V, device):

@@ -208,6 +208,23 @@ int b200_attn_front(const void* x, int T, const void* w, const float* w_s, const
                     void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Decode-width dense projections.  Replace the reference's weight-streaming projections between
+ * the named kernels: gdn_in_proj / qkv_proj (qk_proj_decode.cu:409-470, dense8.py:317-353) and
+ * o_proj + add + Gemma norm (proj.py:30-112).  The reference streams bf16 or W8A16 weights; the
+ * target keeps every weight in the one fp8 block-scaled format.
+ *   b200_dense_fp8: out[T,N] = bf16(x[T,H] . W[N,H]^T), x bf16 quantised per token per 128
+ *     channels, W e4m3 [N,H] with scales fp32 [ceil(N/128), H/128], per-128-k promotion;
+ *     1 <= T <= 64, H % 128 == 0, H <= 4096; ws: b200_dense_fp8_workspace_bytes(T,H), 1024-aligned.
+ *   b200_add_rmsnorm: residual <- bf16(proj + residual) (proj is already bf16; the add is fp32:
+ *     proj.py:75-77), out = bf16(residual * rsqrt(mean residual^2 + eps) * (1 + w)) (proj.py:78-81).
+ */
+size_t b200_dense_fp8_workspace_bytes(int T, int H);
+int b200_dense_fp8(const void* x, int T, int H, const void* w, const float* w_s, int N, void* out, void* ws,
+                   size_t ws_bytes, int32_t* status, void* stream);
+int b200_add_rmsnorm(const void* proj, void* residual, const void* w, float eps, int T, int H, void* out,
+                     void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * LM head shard with fused argmax.  Replaces the logits GEMM of qwen36_lmhead8
  * (lmhead8.py:171-197, w8a8.py:99-120, qk_proj_decode.cu:1210,1468: vocabulary rows on the MMA M
  * side, weight streamed once); the reference returns logits and has no argmax

@@ -111,3 +111,18 @@ def vocab_shards(vocab: int, world: int, block: int = 128):
         out.append((lo, hi))
         lo = hi
     return out
+
+
+def dense_fp8(x, wq, w_s):
+    """out = bf16(x . W^T): the decode-width projections between the named kernels (gdn in_proj, qkv_proj,
+    o_proj: qk_proj_decode.cu:409-470, dense8.py:317-353) at the target's fp8 block-scaled format."""
+    return bf16_round(lmhead_logits(x, wq, w_s))
+
+
+def add_rmsnorm(proj, residual, w, eps=1e-6):
+    """r = bf16(proj + residual) (proj already bf16, fp32 add: proj.py:75-77); y = bf16(r * rsqrt(mean r^2 +
+    eps) * (1 + w)) (proj.py:78-81).  Returns (y, r)."""
+    r = bf16_round((np.asarray(proj, dtype=F32) + np.asarray(residual, dtype=F32)).astype(F32))
+    var = np.mean(r.astype(np.float64) ** 2, axis=-1, keepdims=True)
+    y = bf16_round((r * (1.0 / np.sqrt(var + eps)).astype(F32) * (F32(1.0) + np.asarray(w, dtype=F32))[None, :]).astype(F32))
+    return y, r

@@ -105,7 +105,7 @@ def gemm_fp8_blocks(aq, a_s, wq, w_s):
     a = e4m3_decode(aq).astype(np.float64).reshape(M, K // 128, 128)
     w = e4m3_decode(wq).astype(np.float64).reshape(N, K // 128, 128)
     acc = np.zeros((M, N), dtype=F32)
-    ws_full = np.repeat(np.asarray(w_s, dtype=F32), 128, axis=0)  # [N, K/128]
+    ws_full = np.repeat(np.asarray(w_s, dtype=F32), 128, axis=0)[:N]  # [N, K/128]; N may end inside a block
     for g in range(K // 128):
         part = (a[:, g, :] @ w[:, g, :].T).astype(F32)
         sc = (a_s[:, g][:, None] * ws_full[:, g][None, :]).astype(F32)

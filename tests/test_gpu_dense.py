@@ -1,0 +1,43 @@
+"""Decode-width dense projection (fp8 block-scaled) and add + RMSNorm on the GPU through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from bundles_b200 import ops, synth
+from oracle import attn_lmhead as oat
+from tests.util import bf16_to_np, close_bf16, dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("T,H,N", [(64, 2048, 12352), (8, 4096, 2048), (1, 2048, 9216), (33, 2048, 200)])
+def test_dense_projection(T, H, N):
+    g = torch.Generator().manual_seed(T + N)
+    npad = (N + 127) // 128 * 128
+    w = torch.zeros(npad, H)
+    w[:N] = torch.randn(N, H, generator=g) * 0.02
+    codes, scales = synth.quant_fp8_blocks(w)
+    codes = codes[:N].contiguous()
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    st = ops.new_status(dev())
+    out = ops.dense_fp8(x.to(dev()), codes.to(dev()), scales.to(dev()), status=st)
+    torch.cuda.synchronize()
+    assert ops.read_status(st) == 0
+    ref = oat.dense_fp8(bf16_to_np(x), codes.numpy(), scales.numpy())
+    ok, err, nbad = close_bf16(bf16_to_np(out), ref)
+    assert ok, (err, nbad)
+
+
+def test_add_rmsnorm():
+    g = torch.Generator().manual_seed(5)
+    T, H = 37, 2048
+    proj = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    res = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w = (torch.randn(H, generator=g) * 0.1).to(torch.bfloat16)
+    r_dev = res.to(dev()).clone()
+    y = ops.add_rmsnorm(proj.to(dev()), r_dev, w.to(dev()), 1e-6)
+    torch.cuda.synchronize()
+    ry, rr = oat.add_rmsnorm(bf16_to_np(proj), bf16_to_np(res), bf16_to_np(w), 1e-6)
+    assert np.array_equal(bf16_to_np(r_dev), rr)
+    ok, err, nbad = close_bf16(bf16_to_np(y), ry)
+    assert ok, (err, nbad)
