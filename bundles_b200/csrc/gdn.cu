@@ -9,11 +9,13 @@
 //   hq_s = S q_s, hk_s = S k_s;  R_s = beta_s (v_s - e^{G_s} hk_s);  D = (I + A)^-1 R with
 //   A_ij = beta_i e^{G_i - G_j} k_i.k_j (i > j);  o_s = e^{G_s} hq_s + sum_{i<=s} D_i e^{G_s - G_i} k_i.q_s;
 //   S_n = e^{G_{n-1}} S + sum_{i<n} e^{G_{n-1} - G_i} D_i k_i^T.
-// All dot products are fp32 FMAs (the reference uses TF32 MMAs, qk_gdn_verify.cu:173-179).
+// The 128 x 128 x 8 products S [q | k] run on the tensor core in tf32 (tcgen05.mma kind::tf32 straight
+// from the swizzled state tile in shared memory, accumulators in TMEM), the reference's precision for
+// these dots (TF32 mma.sync, qk_gdn_verify.cu:173-179); everything else is fp32.
 //
 // HBM-bound: 64 KB in and (when accepted > 0) 64 KB out per (sequence, value head).  One CTA per
-// unit; the tile moves with one bulk copy each way (cp.async.bulk), three CTAs share an SM so the
-// copies of one overlap the arithmetic of the others.  The two value heads of a key head run as a
+// unit; the tile moves by TMA tensor copies each way (128-byte swizzle, the layout the MMA reads),
+// three CTAs share an SM so the copies of one overlap the arithmetic of the others.  The two value heads of a key head run as a
 // 2-CTA cluster: both read the q/k conv state, meet at a cluster barrier, then rank 0 rolls it.
 #include "common.cuh"
 #include "host.h"
@@ -27,60 +29,76 @@ constexpr int G_ZDIM = G_HV * G_D;             // 4096
 constexpr int G_THREADS = 256;
 constexpr uint32_t G_TILE_BYTES = G_D * G_D * 4;
 
+// Shared memory of one unit.  S holds the state tile as four 128-row x 32-float sub-tiles in the
+// 128-byte-swizzled K-major layout that both TMA (tensor loads / stores) and the tensor core (A operand
+// of the tf32 MMA) use: element (v, k) lives at sub-tile k / 32, row v, 16-byte chunk ((k % 32) / 4) ^
+// (v & 7).  QK holds [q_0..q_3 | k_0..k_3] as the B operand in the same layout with 8 rows per
+// sub-tile; the MMA reads 16 rows (N = 16 is the smallest N for M = 128): rows 8..15 alias the next
+// kilobyte and only feed accumulator columns nobody reads.
 struct GdnSmem {
-  float S[G_D * G_D];       // state tile, S[v][k]
-  float q[G_NT][G_D];       // normalised, scaled q
-  float k[G_NT][G_D];       // normalised k
+  float S[4][G_D * 32];     // 64 KB, 1024-byte aligned
+  float QK[4][8 * 32];      // 4 KB
+  float k[G_NT][G_D];       // normalised k, plain layout (state update, k.k / k.q dots); also the alias pad of QK
   float v[G_NT][G_D];       // conv v; later c_i * D_i for the state update
-  float hq[G_D][G_NT];      // S q_s
-  float hk[G_D][G_NT];      // S k_s
   float kk[G_NT][G_NT], kq[G_NT][G_NT];
   float g[G_NT], beta[G_NT], G[G_NT];
+  float cA[G_NT][G_NT];     // beta_i e^{G_i - G_j} k_i.k_j   (i > j)
+  float cF[G_NT][G_NT];     // e^{G_s - G_i} k_i.q_s          (i <= s), indexed [i][s]
+  float cE[G_NT], cR[G_NT], cC[G_NT];  // e^{G_s}; beta_s; e^{G_{n-1} - G_i} for i < n_acc else 0
   float red[8][G_NT];
   float nrm[2][G_NT][4];
-  uint64_t bar;
+  uint64_t bar_load, bar_mma;
+  uint32_t tmem_slot;
   int abort_flag;
 };
+__device__ __forceinline__ int sw_chunk(int row, int chunk) { return (chunk ^ (row & 7)) << 2; }  // float offset in a 32-float row
 
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 
-// one channel: window [s0 s1 s2 x0..x3]; y[s] = bf16(silu(sum of bf16-rounded tap products, oldest first))
-// (conv_tap, qk_gdn_verify.cu:240-247); rolls the conv state by `n_acc` tokens if `write`.
-__device__ __forceinline__ void conv_channel(const bf16* __restrict__ mixed_b, bf16* __restrict__ cs_b,
-                                             const bf16* __restrict__ conv_w, int ch, int n_acc, bool write,
-                                             float (&y)[G_NT]) {
+// One conv channel: window [s0 s1 s2 x0..x3] and the four taps, loaded up front so that every global
+// load of the prologue is in flight at once.
+struct ConvIn {
   bf16 win[G_NT + 3];
-  win[0] = cs_b[ch * 3 + 0];
-  win[1] = cs_b[ch * 3 + 1];
-  win[2] = cs_b[ch * 3 + 2];
+  uint2 w;
+};
+__device__ __forceinline__ void conv_load(const bf16* __restrict__ mixed_b, const bf16* __restrict__ cs_b,
+                                          const bf16* __restrict__ conv_w, int ch, ConvIn& in) {
+  in.win[0] = cs_b[ch * 3 + 0];
+  in.win[1] = cs_b[ch * 3 + 1];
+  in.win[2] = cs_b[ch * 3 + 2];
 #pragma unroll
-  for (int s = 0; s < G_NT; ++s) win[3 + s] = mixed_b[static_cast<size_t>(s) * G_CONV + ch];
-  const uint2 wr = *reinterpret_cast<const uint2*>(conv_w + ch * 4);
-  const bf16 w0 = __ushort_as_bfloat16(wr.x & 0xffff), w1 = __ushort_as_bfloat16(wr.x >> 16);
-  const bf16 w2 = __ushort_as_bfloat16(wr.y & 0xffff), w3 = __ushort_as_bfloat16(wr.y >> 16);
+  for (int s = 0; s < G_NT; ++s) in.win[3 + s] = mixed_b[static_cast<size_t>(s) * G_CONV + ch];
+  in.w = *reinterpret_cast<const uint2*>(conv_w + ch * 4);
+}
+// y[s] = bf16(silu(sum of bf16-rounded tap products, oldest first)) (conv_tap, qk_gdn_verify.cu:240-247)
+__device__ __forceinline__ void conv_apply(const ConvIn& in, float (&y)[G_NT]) {
+  const bf16 w0 = __ushort_as_bfloat16(in.w.x & 0xffff), w1 = __ushort_as_bfloat16(in.w.x >> 16);
+  const bf16 w2 = __ushort_as_bfloat16(in.w.y & 0xffff), w3 = __ushort_as_bfloat16(in.w.y >> 16);
 #pragma unroll
   for (int s = 0; s < G_NT; ++s) {
-    float acc = bf2f(__hmul(win[s], w0));
-    acc += bf2f(__hmul(win[s + 1], w1));
-    acc += bf2f(__hmul(win[s + 2], w2));
-    acc += bf2f(__hmul(win[s + 3], w3));
+    float acc = bf2f(__hmul(in.win[s], w0));
+    acc += bf2f(__hmul(in.win[s + 1], w1));
+    acc += bf2f(__hmul(in.win[s + 2], w2));
+    acc += bf2f(__hmul(in.win[s + 3], w3));
     y[s] = rbf(acc / (1.f + __expf(-acc)));
   }
-  if (write && n_acc > 0) {
-    bf16 a = win[0], b = win[1], c = win[2];
+}
+// conv state after n_acc tokens = window elements [n_acc, n_acc + 3)
+__device__ __forceinline__ void conv_roll(const ConvIn& in, bf16* __restrict__ cs_b, int ch, int n_acc) {
+  if (n_acc <= 0) return;
+  bf16 a = in.win[0], b = in.win[1], c = in.win[2];
 #pragma unroll
-    for (int n = 1; n <= G_NT; ++n)
-      if (n_acc == n) {
-        a = win[n];
-        b = win[n + 1];
-        c = win[n + 2];
-      }
-    cs_b[ch * 3 + 0] = a;
-    cs_b[ch * 3 + 1] = b;
-    cs_b[ch * 3 + 2] = c;
-  }
+  for (int n = 1; n <= G_NT; ++n)
+    if (n_acc == n) {
+      a = in.win[n];
+      b = in.win[n + 1];
+      c = in.win[n + 2];
+    }
+  cs_b[ch * 3 + 0] = a;
+  cs_b[ch * 3 + 1] = b;
+  cs_b[ch * 3 + 2] = c;
 }
 
 struct GdnArgs {
@@ -101,64 +119,49 @@ struct GdnArgs {
   int32_t* status;
 };
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 3) gdn_verify_kernel(const GdnArgs p) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 3)
+gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   extern __shared__ uint8_t smem_raw[];
-  GdnSmem& sm = *reinterpret_cast<GdnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  GdnSmem& sm = *reinterpret_cast<GdnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int hv = blockIdx.x, hk = hv >> 1, b = blockIdx.y;
   int n_acc = p.accepted[b];
   n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
-  float* gstate = p.state + (static_cast<size_t>(b) * G_HV + hv) * (G_D * G_D);
+  const int srow0 = (b * G_HV + hv) * G_D;  // first row of this unit in the [B*32*128, 128] view of the state
 
   if (tid == 0) {
-    mbar_init(&sm.bar, 1);
+    mbar_init(&sm.bar_load, 1);
+    mbar_init(&sm.bar_mma, 1);
     sm.abort_flag = 0;
     mbar_fence_init();
+    tma_prefetch_desc(&tmS);
   }
+  if (warp == 0) tmem_alloc(&sm.tmem_slot, 32);
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm.tmem_slot;
   if (tid == 0) {
-    mbar_expect_tx(&sm.bar, G_TILE_BYTES);
-    bulk_load(sm.S, gstate, G_TILE_BYTES, &sm.bar);
+    mbar_expect_tx(&sm.bar_load, G_TILE_BYTES);
+#pragma unroll
+    for (int sub = 0; sub < 4; ++sub) tma_load_2d(sm.S[sub], &tmS, 32 * sub, srow0, &sm.bar_load);
   }
 
-  // ---- conv + SiLU on q, k (key head hk) and v (value head hv); L2 norms ----
+  // ---- every global input of this unit is requested before anything is computed ----
   const bf16* mixed_b = p.mixed + static_cast<size_t>(b) * G_NT * G_CONV;
   bf16* cs_b = p.conv_state + static_cast<size_t>(b) * G_CONV * 3;
-  {
-    float y[G_NT];
-    const int c = tid & 127;
-    const bool is_k = tid >= 128;
-    // q/k conv state is shared by the cluster pair: read now, rank 0 rolls it after the barrier
-    conv_channel(mixed_b, cs_b, p.conv_w, (is_k ? G_QDIM : 0) + hk * G_D + c, 0, false, y);
-    float ss[G_NT];
+  const int c = tid & 127;
+  const bool is_k = tid >= 128;
+  const int ch_qk = (is_k ? G_QDIM : 0) + hk * G_D + c;
+  const int ch_v = 2 * G_QDIM + hv * G_D + c;
+  ConvIn in_qk, in_v;
+  conv_load(mixed_b, cs_b, p.conv_w, ch_qk, in_qk);
+  float zz[G_NT] = {0.f, 0.f, 0.f, 0.f}, nw = 0.f;
+  if (!is_k) {
+    conv_load(mixed_b, cs_b, p.conv_w, ch_v, in_v);
 #pragma unroll
-    for (int s = 0; s < G_NT; ++s) ss[s] = y[s] * y[s];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s) ss[s] += __shfl_xor_sync(FULL_MASK, ss[s], o);
-    if (lane == 0)
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s) sm.nrm[is_k][s][warp & 3] = ss[s];
-    __syncthreads();
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) {
-      const float n = sm.nrm[is_k][s][0] + sm.nrm[is_k][s][1] + sm.nrm[is_k][s][2] + sm.nrm[is_k][s][3];
-      const float r = (1.f / sqrtf(n + 1e-6f)) * (is_k ? 1.f : 0.08838834764831845f);  // d_k^-0.5
-      (is_k ? sm.k : sm.q)[s][c] = y[s] * r;
-    }
-  }
-  cluster_sync();  // both value heads of the key head hold their q/k windows
-  if ((hv & 1) == 0 && n_acc > 0) {
-    float y[G_NT];
-    const int c = tid & 127;
-    conv_channel(mixed_b, cs_b, p.conv_w, (tid >= 128 ? G_QDIM : 0) + hk * G_D + c, n_acc, true, y);
-  }
-  if (tid < 128) {
-    float y[G_NT];
-    conv_channel(mixed_b, cs_b, p.conv_w, 2 * G_QDIM + hv * G_D + tid, n_acc, true, y);
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) sm.v[s][tid] = y[s];
+    for (int s = 0; s < G_NT; ++s) zz[s] = bf2f(p.z[(static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv * G_D + c]);
+    nw = bf2f(p.norm_w[c]);
   } else if (tid < 128 + G_NT) {
     // gates (qk_gdn_verify.cu:616-631)
     const int s = tid - 128;
@@ -169,124 +172,143 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 3) gdn_ve
     sm.g[s] = -expf(p.a_log[hv]) * sp;
     sm.beta[s] = 1.f / (1.f + expf(-bv));
   }
-  __syncthreads();
-  if (tid == 0) {
-    float run = 0.f;
+  // ---- conv + SiLU on q, k (key head hk) and v (value head hv); L2 norms ----
+  {
+    float y[G_NT];
+    conv_apply(in_qk, y);
+    float ss[G_NT];
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) ss[s] = y[s] * y[s];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) ss[s] += __shfl_xor_sync(FULL_MASK, ss[s], o);
+    if (lane == 0)
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) sm.nrm[is_k][s][warp & 3] = ss[s];
+    if (!is_k) {
+      float yv[G_NT];
+      conv_apply(in_v, yv);
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) sm.v[s][c] = yv[s];
+    }
+    __syncthreads();
+    const int sub = c >> 5, chk = (c & 31) >> 2, e = c & 3;
+#pragma unroll
     for (int s = 0; s < G_NT; ++s) {
-      run += sm.g[s];
-      sm.G[s] = run;
+      const float n = sm.nrm[is_k][s][0] + sm.nrm[is_k][s][1] + sm.nrm[is_k][s][2] + sm.nrm[is_k][s][3];
+      const float r = (1.f / sqrtf(n + 1e-6f)) * (is_k ? 1.f : 0.08838834764831845f);  // d_k^-0.5
+      const float val = y[s] * r;
+      const int row = (is_k ? 4 : 0) + s;
+      sm.QK[sub][row * 32 + sw_chunk(row, chk) + e] = val;
+      if (is_k) sm.k[s][c] = val;
     }
   }
-  // k_i . k_j and k_i . q_j: 32 dots of length 128, 4 per warp
+  // the q/k conv state is shared by the two value heads of the key head: both have read it once the
+  // cluster barrier is passed, then the even head rolls it; every head rolls its own v channels
+  cluster_sync();
+  if ((hv & 1) == 0) conv_roll(in_qk, cs_b, ch_qk, n_acc);
+  if (!is_k) conv_roll(in_v, cs_b, ch_v, n_acc);
+  fence_proxy_async();  // the QK tile was written with ordinary stores; the tensor core reads it through the async proxy
+  __syncthreads();
+
+  // ---- S [q | k]: sixteen tf32 MMAs (M = 128 state rows, N = 16, K = 8 each) into 16 TMEM columns ----
+  bool landed = true;
+  if (tid == 0) {
+    landed = mbar_wait(&sm.bar_load, 0, &sm.abort_flag, p.status, ST_WAIT_STATE);
+    if (landed) {
+      tc_fence_after();
+      const uint32_t idesc = umma_idesc(UMMA_C_F32, UMMA_AB_TF32, 16);
+#pragma unroll
+      for (int sub = 0; sub < 4; ++sub)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tc_mma_tf32(tmem_base, umma_desc_sw128(smem_u32(sm.S[sub]) + kk * 32),
+                      umma_desc_sw128(smem_u32(sm.QK[sub]) + kk * 32), idesc, (sub | kk) != 0);
+      tc_commit(&sm.bar_mma);
+    }
+  }
+  // k_i . k_j and k_i . q_j while the MMAs run: 32 dots of length 128, 4 per warp (q read back from the QK tile)
   for (int d = warp * 4; d < warp * 4 + 4; ++d) {
     const int i = (d >> 2) & 3, j = d & 3;
-    const float* other = d < 16 ? sm.k[j] : sm.q[j];
     float acc = 0.f;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) acc = fmaf(sm.k[i][lane + 32 * c], other[lane + 32 * c], acc);
+    for (int c4 = 0; c4 < 4; ++c4) {
+      const int c = lane + 32 * c4;
+      const float other = d < 16 ? sm.k[j][c] : sm.QK[c >> 5][j * 32 + sw_chunk(j, (c & 31) >> 2) + (c & 3)];
+      acc = fmaf(sm.k[i][c], other, acc);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(FULL_MASK, acc, o);
     if (lane == 0) (d < 16 ? sm.kk : sm.kq)[i][j] = acc;
   }
-
-  // ---- the state tile ----
-  const bool landed = mbar_wait(&sm.bar, 0, &sm.abort_flag, p.status, ST_WAIT_STATE);
-  __syncthreads();
-  if (!landed || sm.abort_flag) {
-    // the copy may still be in flight: give it a bounded grace period, then leave without touching memory
-    const unsigned long long t0 = globaltimer();
-    while (tid == 0 && !mbar_try(&sm.bar, 0) && globaltimer() - t0 < 20000000ull) {
+  __syncthreads();  // kk, kq visible; thread 0 has issued (or abandoned) the MMAs
+  if (tid < 32) {
+    // the window's scalar coefficients, once per unit instead of once per value row
+    float G[G_NT];
+    float run = 0.f;
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) {
+      run += sm.g[s];
+      G[s] = run;
     }
-    return;
-  }
-
-  // thread = 4 state rows x one of 8 interleaved k slices (float4 chunks ks + 8 i)
-  const int rg = tid >> 3, ks = tid & 7;
-  {
-    float acc[4][8];
+    if (lane < 16) {
+      const int i = lane >> 2, j = lane & 3;
+      float Gi = 0.f, Gj = 0.f;
 #pragma unroll
-    for (int r = 0; r < 4; ++r)
-#pragma unroll
-      for (int x = 0; x < 8; ++x) acc[r][x] = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c4 = (ks + 8 * i) * 4;
-      float4 sv[4];
-#pragma unroll
-      for (int r = 0; r < 4; ++r) sv[r] = *reinterpret_cast<const float4*>(&sm.S[(rg * 4 + r) * G_D + c4]);
-#pragma unroll
-      for (int x = 0; x < 8; ++x) {
-        const float4 vv = *reinterpret_cast<const float4*>(x < 4 ? &sm.q[x][c4] : &sm.k[x - 4][c4]);
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          acc[r][x] = fmaf(sv[r].x, vv.x, acc[r][x]);
-          acc[r][x] = fmaf(sv[r].y, vv.y, acc[r][x]);
-          acc[r][x] = fmaf(sv[r].z, vv.z, acc[r][x]);
-          acc[r][x] = fmaf(sv[r].w, vv.w, acc[r][x]);
-        }
+      for (int s = 0; s < G_NT; ++s) {
+        Gi = s == i ? G[s] : Gi;
+        Gj = s == j ? G[s] : Gj;
       }
-    }
-    // transposing reduction over the 8 slice lanes: 32 -> 16 -> 8 -> 4 values per lane
-    float v16[16], v8[8], v4[4];
-    const bool b2 = ks & 4, b1 = ks & 2, b0 = ks & 1;
+      sm.cA[i][j] = i > j ? sm.beta[i] * __expf(Gi - Gj) * sm.kk[i][j] : 0.f;
+      sm.cF[i][j] = i <= j ? __expf(Gj - Gi) * sm.kq[i][j] : 0.f;
+    } else if (lane < 20) {
+      const int s = lane - 16;
+      float Gs = 0.f, Gn = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float lo = acc[i >> 3][i & 7], hi = acc[2 + (i >> 3)][i & 7];
-      const float send = b2 ? lo : hi, keep = b2 ? hi : lo;
-      v16[i] = keep + __shfl_xor_sync(FULL_MASK, send, 4);
+      for (int u = 0; u < G_NT; ++u) {
+        Gs = u == s ? G[u] : Gs;
+        Gn = u == n_acc - 1 ? G[u] : Gn;
+      }
+      sm.cE[s] = __expf(Gs);
+      sm.cR[s] = sm.beta[s];
+      sm.cC[s] = s < n_acc ? __expf(Gn - Gs) : 0.f;
+      sm.G[s] = Gs;
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float lo = v16[i], hi = v16[8 + i];
-      const float send = b1 ? lo : hi, keep = b1 ? hi : lo;
-      v8[i] = keep + __shfl_xor_sync(FULL_MASK, send, 2);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float lo = v8[i], hi = v8[4 + i];
-      const float send = b0 ? lo : hi, keep = b0 ? hi : lo;
-      v4[i] = keep + __shfl_xor_sync(FULL_MASK, send, 1);
-    }
-    // lane (b2 b1 b0) now holds row 2*b2 + b1 of its group, vectors 4*b0 .. 4*b0 + 3 (q first, then k)
-    const int row = rg * 4 + (ks >> 1);
-    *reinterpret_cast<float4*>(b0 ? sm.hk[row] : sm.hq[row]) = make_float4(v4[0], v4[1], v4[2], v4[3]);
   }
   __syncthreads();
+  const bool ok = mbar_wait(&sm.bar_load, 0, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
+                  mbar_wait(&sm.bar_mma, 0, &sm.abort_flag, p.status, ST_WAIT_TMEM_FULL);
+  tc_fence_after();
 
   // ---- per value row: R, D = (I + A)^-1 R, outputs; gated RMSNorm ----
   float o[G_NT] = {0.f, 0.f, 0.f, 0.f};
-  if (tid < G_D) {
+  if (ok && tid < G_D) {
     const int v = tid;
-    float G[G_NT], bt[G_NT], eG[G_NT], R[G_NT], D[G_NT];
+    uint32_t hr[16];
+    tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16), hr);  // warps 0..3 own TMEM lane quadrants 0..3
+    tmem_ld_wait();
+    float R[G_NT], D[G_NT];
 #pragma unroll
-    for (int s = 0; s < G_NT; ++s) {
-      G[s] = sm.G[s];
-      bt[s] = sm.beta[s];
-      eG[s] = __expf(G[s]);
-    }
-    const float4 hq4 = *reinterpret_cast<const float4*>(sm.hq[v]);
-    const float4 hk4 = *reinterpret_cast<const float4*>(sm.hk[v]);
-    const float hq[G_NT] = {hq4.x, hq4.y, hq4.z, hq4.w}, hkv[G_NT] = {hk4.x, hk4.y, hk4.z, hk4.w};
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) R[s] = bt[s] * (sm.v[s][v] - eG[s] * hkv[s]);
+    for (int s = 0; s < G_NT; ++s) R[s] = sm.cR[s] * (sm.v[s][v] - sm.cE[s] * __uint_as_float(hr[4 + s]));
 #pragma unroll
     for (int i = 0; i < G_NT; ++i) {
       float d = R[i];
 #pragma unroll
-      for (int j = 0; j < i; ++j) d = fmaf(-(bt[i] * __expf(G[i] - G[j]) * sm.kk[i][j]), D[j], d);
+      for (int j = 0; j < i; ++j) d = fmaf(-sm.cA[i][j], D[j], d);
       D[i] = d;
     }
 #pragma unroll
     for (int s = 0; s < G_NT; ++s) {
-      float acc = eG[s] * hq[s];
+      float acc = sm.cE[s] * __uint_as_float(hr[s]);
 #pragma unroll
-      for (int i = 0; i <= s; ++i) acc = fmaf(D[i] * __expf(G[s] - G[i]), sm.kq[i][s], acc);
+      for (int i = 0; i <= s; ++i) acc = fmaf(D[i], sm.cF[i][s], acc);
       o[s] = rbf(acc);  // the core output is stored in bf16 before the norm (qk_gdn_verify.cu:761)
     }
     __syncwarp();
     // c_i D_i for the state update replaces v (each thread only touches its own column)
 #pragma unroll
-    for (int i = 0; i < G_NT; ++i) sm.v[i][v] = i < n_acc ? D[i] * __expf(G[n_acc - 1] - G[i]) : 0.f;
+    for (int i = 0; i < G_NT; ++i) sm.v[i][v] = D[i] * sm.cC[i];
   }
   {
     float ss[G_NT];
@@ -300,36 +322,37 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 3) gdn_ve
 #pragma unroll
       for (int s = 0; s < G_NT; ++s) sm.red[warp][s] = ss[s];
   }
+  tc_fence_before();
   __syncthreads();
-  if (tid < G_D) {
-    const float nw = bf2f(p.norm_w[tid]);
+  if (ok && tid < G_D) {
 #pragma unroll
     for (int s = 0; s < G_NT; ++s) {
       const float var = (sm.red[0][s] + sm.red[1][s] + sm.red[2][s] + sm.red[3][s]) * (1.f / G_D);
       const float rstd = rsqrtf(var + p.eps);
       const size_t idx = (static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv * G_D + tid;
-      const float zz = bf2f(p.z[idx]);
-      p.out[idx] = f2bf(o[s] * rstd * nw * (zz * (1.f / (1.f + __expf(-zz)))));
+      p.out[idx] = f2bf(o[s] * rstd * nw * (zz[s] * (1.f / (1.f + __expf(-zz[s])))));
     }
   }
 
-  // ---- state after n_acc tokens, written back in one bulk copy ----
-  if (n_acc > 0) {
-    const float decay = __expf(sm.G[n_acc - 1]);
+  // ---- state after n_acc tokens, in place in the swizzled tile, then four TMA tensor stores ----
+  if (ok && n_acc > 0) {
+    // thread = 4 state rows x one 16-byte chunk position of each 32-float sub-tile row
+    const int rg = tid >> 3, ks = tid & 7;
+    const float decay = sm.cE[n_acc - 1];
     float cd[4][G_NT];
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
       for (int i = 0; i < G_NT; ++i) cd[r][i] = sm.v[i][rg * 4 + r];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c4 = (ks + 8 * i) * 4;
+    for (int sub = 0; sub < 4; ++sub) {
       float4 kv[G_NT];
 #pragma unroll
-      for (int t = 0; t < G_NT; ++t) kv[t] = *reinterpret_cast<const float4*>(&sm.k[t][c4]);
+      for (int t = 0; t < G_NT; ++t) kv[t] = *reinterpret_cast<const float4*>(&sm.k[t][sub * 32 + ks * 4]);
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        float4* sp = reinterpret_cast<float4*>(&sm.S[(rg * 4 + r) * G_D + c4]);
+        const int row = rg * 4 + r;
+        float4* sp = reinterpret_cast<float4*>(&sm.S[sub][row * 32 + sw_chunk(row, ks)]);
         float4 sv = *sp;
         sv.x *= decay; sv.y *= decay; sv.z *= decay; sv.w *= decay;
 #pragma unroll
@@ -345,10 +368,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 3) gdn_ve
     fence_proxy_async();
     __syncthreads();
     if (tid == 0) {
-      bulk_store(gstate, sm.S, G_TILE_BYTES);
+#pragma unroll
+      for (int sub = 0; sub < 4; ++sub) tma_store_2d(&tmS, 32 * sub, srow0, sm.S[sub]);
       bulk_commit();
       bulk_wait_read_all();  // the tile has left shared memory; the write itself completes with the grid
     }
+  }
+  if (!ok && tid == 0) {
+    // an abandoned wait: give the state copy a bounded grace period before the CTA's memory goes away
+    const unsigned long long t0 = globaltimer();
+    while (!mbar_try(&sm.bar_load, 0) && globaltimer() - t0 < 20000000ull) {
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 32);
   }
 }
 
@@ -369,7 +404,9 @@ extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, 
   GdnArgs p{static_cast<const bf16*>(mixed), static_cast<const bf16*>(z), static_cast<const bf16*>(a),
             static_cast<const bf16*>(b), static_cast<bf16*>(conv_state), static_cast<const bf16*>(conv_w), a_log,
             dt_bias, state, accepted, static_cast<const bf16*>(norm_w), eps, B, static_cast<bf16*>(out), status};
-  const int smem = static_cast<int>(sizeof(GdnSmem)) + 128;
+  CUtensorMap tmS;
+  if (int rc = make_tmap_f32_2d(&tmS, state, static_cast<uint64_t>(B) * G_HV * G_D, G_D, G_D, "gdn state")) return rc;
+  const int smem = static_cast<int>(sizeof(GdnSmem)) + 1024;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -377,6 +414,6 @@ extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, 
     cudaFuncSetAttribute(gdn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     attr_done[dev] = true;
   }
-  gdn_verify_kernel<<<dim3(G_HV, B), G_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  gdn_verify_kernel<<<dim3(G_HV, B), G_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tmS, p);
   return launch_status("b200_gdn_verify");
 }

@@ -46,6 +46,24 @@ int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64
   return 0;
 }
 
+int make_tmap_f32_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                     const char* what) {
+  EncodeTiledFn fn = encoder();
+  if (!fn) return fail(B200_E_DRIVER, "%s: cuTensorMapEncodeTiled is not available", what);
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (cols & 3) || cols < 32 || rows == 0)
+    return fail(B200_E_ALIGN, "%s: tensor base must be 16-byte aligned, cols a multiple of 4 and >= 32", what);
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 4};
+  cuuint32_t box[2] = {32, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r =
+      fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200_E_ARG, "%s: cuTensorMapEncodeTiled failed (%d)", what, static_cast<int>(r));
+  return 0;
+}
+
 int sm_count() {
   static int cached[64];
   int dev = 0;

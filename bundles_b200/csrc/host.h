@@ -46,6 +46,10 @@ inline int launch_status(const char* what) {
 int make_tmap_bytes_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
                        const char* what);
 
+// 2-D tensor map over a row-major fp32 matrix [rows, cols], box [box_rows, 32 floats], 128-byte swizzle
+int make_tmap_f32_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                     const char* what);
+
 void b200_quant_rows_f8_launch(const void* x, int T, int H, uint8_t* xq, float* xs, cudaStream_t st);
 
 int sm_count();  // SMs of the current device (cached per device)
