@@ -228,8 +228,9 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
       tc_commit(&sm.bar_mma);
     }
   }
-  // k_i . k_j and k_i . q_j while the MMAs run: 32 dots of length 128, 4 per warp (q read back from the QK tile)
-  for (int d = warp * 4; d < warp * 4 + 4; ++d) {
+  // k_i . k_j and k_i . q_j while the MMAs run: 32 dots of length 128 over warps 1..7 (warp 0 issues the MMAs;
+  // q is read back from the QK tile)
+  for (int d = warp - 1; warp > 0 && d < 32; d += 7) {
     const int i = (d >> 2) & 3, j = d & 3;
     float acc = 0.f;
 #pragma unroll
@@ -243,7 +244,7 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     if (lane == 0) (d < 16 ? sm.kk : sm.kq)[i][j] = acc;
   }
   __syncthreads();  // kk, kq visible; thread 0 has issued (or abandoned) the MMAs
-  if (tid < 32) {
+  if (warp == 1) {
     // the window's scalar coefficients, once per unit instead of once per value row
     float G[G_NT];
     float run = 0.f;
@@ -364,15 +365,15 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
         }
         *sp = sv;
       }
+      // this 16 KB sub-tile is final: hand it to TMA while the next one is being updated
+      fence_proxy_async();
+      __syncthreads();
+      if (tid == 0) {
+        tma_store_2d(&tmS, 32 * sub, srow0, sm.S[sub]);
+        bulk_commit();
+      }
     }
-    fence_proxy_async();
-    __syncthreads();
-    if (tid == 0) {
-#pragma unroll
-      for (int sub = 0; sub < 4; ++sub) tma_store_2d(&tmS, 32 * sub, srow0, sm.S[sub]);
-      bulk_commit();
-      bulk_wait_read_all();  // the tile has left shared memory; the write itself completes with the grid
-    }
+    if (tid == 0) bulk_wait_read_all();  // the tile has left shared memory; the writes complete with the grid
   }
   if (!ok && tid == 0) {
     // an abandoned wait: give the state copy a bounded grace period before the CTA's memory goes away
