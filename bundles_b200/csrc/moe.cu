@@ -130,6 +130,11 @@ struct GemmArgs {
   int32_t* dbg_acc;     // up: raw accumulators by slot [total_rows, 2I] or null
   bf16* dbg_h;          // up: h by slot or null
   int32_t* status;
+  // expert-parallel down epilogue: routed slot s of the gathered batch belongs to rank s / ep_rows, whose
+  // cache (this GPU's own, or a peer's mapped over NVLink) receives the row at local slot s % ep_rows
+  int ep_world;         // 0 / 1: single GPU, rows go to `cache`
+  int ep_rows;          // routed slots per rank = tokens per rank x top-k
+  bf16* ep_cache[8];
 };
 
 constexpr int TILE_BYTES = 128 * 128;   // one 128-row x 128-byte operand tile
@@ -141,7 +146,7 @@ struct GemmCfg {
   static constexpr int NA = UP ? 2 : 1;                      // weight tiles per stage (gate + up)
   static constexpr int STAGE = NA * TILE_BYTES + TILE_BYTES;  // + token tile (<= 128 rows)
   static constexpr int STAGES = UP ? 4 : 6;
-  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + 8 * 128 * 12 /*row metadata, one copy per epilogue warp*/;
+  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + 8 * 128 * 20 /*row metadata, one copy per epilogue warp*/;
 };
 
 template <bool UP>
@@ -162,6 +167,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   float* m_scale_all = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE + 256);  // [8][128] activation scale
   float* m_wt_all = m_scale_all + 1024;                                               // [8][128] routing weight
   int* m_slot_all = reinterpret_cast<int*>(m_wt_all + 1024);                          // [8][128] slot or -1
+  bf16** m_dst_all = reinterpret_cast<bf16**>(m_slot_all + 1024);                     // [8][128] destination row (down)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -296,6 +302,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     float* ms = m_scale_all + (warp - 2) * 128;
     float* m_wt = m_wt_all + (warp - 2) * 128;
     int* m_slot = m_slot_all + (warp - 2) * 128;
+    bf16** m_dst = m_dst_all + (warp - 2) * 128;
     const float* __restrict__ a_scale = p.a_scale;
     const float* __restrict__ wt_of_row = p.L.wt_of_row;
     const int32_t* __restrict__ slot_of_row = p.L.slot_of_row;
@@ -323,6 +330,18 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         ms[c] = sc;
         m_wt[c] = wt;
         m_slot[c] = slot;
+        if (!UP) {
+          bf16* dst = nullptr;
+          if (slot >= 0) {
+            if (p.ep_world > 1) {
+              const int home = slot / p.ep_rows;
+              dst = home < p.ep_world ? p.ep_cache[home] + static_cast<size_t>(slot - home * p.ep_rows) * p.H : nullptr;
+            } else {
+              dst = p.cache + static_cast<size_t>(slot) * p.H;
+            }
+          }
+          m_dst[c] = dst;
+        }
       }
       __syncwarp();
       if (!mbar_wait(&tfull[buf], bphase, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
@@ -366,17 +385,16 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
       } else {
         const float ws = shared_e ? p.s_w_sh[r] : p.s_w[static_cast<size_t>(e) * p.w_rows + r];
-        bf16* __restrict__ cache = p.cache + r;
         for (int c0 = half * 16; c0 < n; c0 += 32) {
           uint32_t ra[16];
           tmem_ld16(taddr + c0, ra);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int slot = m_slot[c0 + i];
+            bf16* dst = m_dst[c0 + i];
             const float y = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ra[i])), ms[c0 + i]), ws);
             const bf16 o = f2bf(__fmul_rn(y, m_wt[c0 + i]));
-            if (slot >= 0) cache[static_cast<size_t>(slot) * p.H] = o;
+            if (dst != nullptr) dst[r] = o;
           }
         }
       }
@@ -472,9 +490,34 @@ extern "C" size_t b200_moe_w8a8_workspace_bytes(int T, int H, int I, int K) {
   return w8_layout(T, H, I, K).total;
 }
 
+static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
+                         const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, int32_t* dbg_acc13,
+                         void* dbg_h, int stages, int32_t* status, void* stream, void* const* peer_cache,
+                         int ep_world, int ep_tokens_per_rank);
+
 extern "C" int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
                              const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes,
                              int32_t* dbg_acc13, void* dbg_h, int stages, int32_t* status, void* stream) {
+  return moe_w8a8_impl(x, T, H, I, K, E_local, w, lists, cache, ws, ws_bytes, dbg_acc13, dbg_h, stages, status, stream,
+                       nullptr, 0, 0);
+}
+
+extern "C" int b200_moe_w8a8_ep(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
+                                const b200_moe_lists* lists, void* const* peer_cache_host, int ep_world,
+                                int ep_tokens_per_rank, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  if (!peer_cache_host || ep_world < 1 || ep_world > 8 || ep_tokens_per_rank <= 0 || T != ep_world * ep_tokens_per_rank)
+    return fail(B200_E_ARG, "b200_moe_w8a8_ep: need 1 <= ep_world <= 8 and T == ep_world * ep_tokens_per_rank (T=%d)", T);
+  for (int r = 0; r < ep_world; ++r)
+    if (!peer_cache_host[r] || (reinterpret_cast<uintptr_t>(peer_cache_host[r]) & 15))
+      return fail(B200_E_ARG, "b200_moe_w8a8_ep: peer cache %d is null or not 16-byte aligned", r);
+  return moe_w8a8_impl(x, T, H, I, K, E_local, w, lists, peer_cache_host[0], ws, ws_bytes, nullptr, nullptr, 0, status,
+                       stream, peer_cache_host, ep_world, ep_tokens_per_rank);
+}
+
+static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
+                         const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, int32_t* dbg_acc13,
+                         void* dbg_h, int stages, int32_t* status, void* stream, void* const* peer_cache,
+                         int ep_world, int ep_tokens_per_rank) {
   if (!x || !w || !lists || !cache || !ws || !w->w13 || !w->s13 || !w->w2 || !w->s2)
     return fail(B200_E_ARG, "b200_moe_w8a8: null pointer");
   if (T <= 0 || K <= 0 || K > 32 || E_local <= 0 || H % 128 || I % 128 || H <= 0 || I <= 0)
@@ -554,6 +597,9 @@ extern "C" int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_lo
   a.cache = static_cast<bf16*>(cache);
   a.dbg_acc = nullptr;
   a.dbg_h = nullptr;
+  a.ep_world = ep_world;
+  a.ep_rows = ep_tokens_per_rank * K;
+  for (int r = 0; r < 8; ++r) a.ep_cache[r] = (peer_cache && r < ep_world) ? static_cast<bf16*>(peer_cache[r]) : nullptr;
   if (stages & B200_MOE_STAGE_DOWN)
     moe_gemm_i8_kernel<false><<<grid, GEMM_THREADS, GemmCfg<false>::SMEM, st>>>(tmW2, tmSh2, tmHq, a);
   return launch_status("b200_moe_w8a8");

@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import B200Error, MoeLists, MoeWeights, check
 
-__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_fp8", "moe_combine", "attn_front", "dense_fp8", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
+__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_w8a8_ep", "moe_fp8", "moe_combine", "attn_front", "dense_fp8", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
            "new_status", "read_status", "B200Error"]
 
 
@@ -185,6 +185,24 @@ def moe_fp8(x, w: MoeW8A8Weights, lists: RoutingLists, cache=None, ws=None, stat
     check(_lib.lib().b200_moe_fp8(_p(x), T, H, I, K, E, C.byref(wc), C.byref(lists.c), _p(cache), _p(ws), ws.numel(),
                                   _p(dbg_h), int(stages), _p(status), _stream()), "b200_moe_fp8")
     return cache
+
+
+def moe_w8a8_ep(x_all, w: MoeW8A8Weights, lists: RoutingLists, peer_ptrs, tokens_per_rank, ws=None, status=None):
+    """Expert-parallel int8 experts: this rank's experts over the gathered tokens, the weighted down rows
+    stored straight into every home rank's routed cache (`peer_ptrs`: device pointers, one per rank)."""
+    _need(x_all, torch.bfloat16, "x_all", 2)
+    T, H = x_all.shape
+    E, twoI, _ = w.w13.shape
+    I = twoI // 2
+    K = lists.K
+    if ws is None:
+        ws = moe_w8a8_workspace(T, H, I, K, x_all.device)
+    world = len(peer_ptrs)
+    arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_ptrs])
+    wc = w.c_struct()
+    check(_lib.lib().b200_moe_w8a8_ep(_p(x_all), T, H, I, K, E, C.byref(wc), C.byref(lists.c), arr, world,
+                                      int(tokens_per_rank), _p(ws), ws.numel(), _p(status), _stream()),
+          "b200_moe_w8a8_ep")
 
 
 def moe_combine(cache, x, gate_w, top_k, pos=None, out=None):

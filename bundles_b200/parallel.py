@@ -127,6 +127,49 @@ class GpuMoeBackend:
         return ops.moe_combine(cache, x, self.gate_w, K)
 
 
+class FusedExpertParallelMoe:
+    """Expert-parallel MoE block whose combine-side exchange is fused into the down GEMM: every rank
+    stores the weighted expert rows straight into the home rank's cache over NVLink (plain peer
+    stores from the GEMM epilogue, `ops.moe_w8a8_ep`), then one barrier, then the home rank adds its
+    tokens' rows in slot order.  The caches are symmetric-memory buffers (one per rank, mapped into
+    every process); x, ids and weights are still all-gathered with NCCL (each token row is needed by up
+    to min(K, world) ranks).  Bit-identical to `ExpertParallelMoe` and to the single-GPU block."""
+
+    def __init__(self, backend: "GpuMoeBackend", top_k: int, hidden: int, tokens_per_rank: int, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.b, self.K, self.H, self.T = backend, top_k, hidden, tokens_per_rank
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        dev = backend.wr.device
+        # routed rows of this rank's tokens; written by every rank (this one included)
+        self.cache_routed = symm.empty(tokens_per_rank * top_k, hidden, dtype=torch.bfloat16, device=dev)
+        self.handle = symm.rendezvous(self.cache_routed, self.group)
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        T_all = tokens_per_rank * self.world
+        self.x_all = torch.empty(T_all, hidden, dtype=torch.bfloat16, device=dev)
+        self.ids_all = torch.empty(T_all, top_k, dtype=torch.int32, device=dev)
+        self.wts_all = torch.empty(T_all, top_k, dtype=torch.float32, device=dev)
+        self.lists = backend.ops.RoutingLists(T_all, top_k, backend.E_local, 128, dev)
+        self.ws = backend.ops.moe_w8a8_workspace(T_all, hidden, backend.w.w2.shape[-1], top_k, dev)
+        self.launches_per_call = 16
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        b, ops = self.b, self.b.ops
+        ids, wts = b.route(x)
+        dist.all_gather_into_tensor(self.x_all, x.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(self.ids_all, ids, group=self.group)
+        dist.all_gather_into_tensor(self.wts_all, wts, group=self.group)
+        ops.build_lists(self.ids_all, self.wts_all, self.lists, None, e_lo=b.e_lo, with_shared=False)
+        # nobody may still be reading last step's rows when the first peer store of this step lands
+        self.handle.barrier(channel=0)
+        ops.moe_w8a8_ep(self.x_all, b.w_routed, self.lists, self.peer_ptrs, self.T, ws=self.ws, status=b.status)
+        self.handle.barrier(channel=1)      # every rank's rows for my tokens have landed
+        return b.shared_and_combine(x, self.cache_routed)
+
+    __call__ = forward
+
+
 def sharded_argmax(x, w_shard, w_s_shard, shard_lo, group=None):
     """Vocab-sharded greedy token: per-shard (max, argmax) on this rank, all-gather of the pairs,
     merge (largest value, ties to the lower id).  Returns tokens int32 [T] (same on every rank)."""

@@ -39,8 +39,13 @@ def _worker(rank, world, port, out):
         # single-GPU block over all tokens on this rank
         w_all = ops.MoeW8A8Weights(d["w13"], d["s13"], d["w2"], d["s2"], d["sh13"], d["shs13"], d["sh2"], d["shs2"])
         ref = moe_block.MoeBlockW8A8(d["wr"], w_all, d["gate_w"], K, bias=d["bias"], use_graph=False)(d["x"])
+        fused = parallel.FusedExpertParallelMoe(backend, K, 2048, T_local)
+        xl = d["x"][rank * T_local:(rank + 1) * T_local].contiguous()
+        y2 = fused(xl).clone()
+        y3 = fused(xl).clone()                      # a second step reuses the peer-written caches
         torch.cuda.synchronize()
         ok_moe = torch.equal(y, ref[rank * T_local:(rank + 1) * T_local]) and ops.read_status(backend.status) == 0
+        ok_moe = ok_moe and torch.equal(y2, y) and torch.equal(y3, y)
         # vocab-sharded greedy token
         V = 128 * 21
         lm = synth.lmhead(seed=401, T=16, V=V)
