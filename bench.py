@@ -323,6 +323,8 @@ def run_expert_parallel(args, rank, world, dev, cfg):
                 "gpu_launches": getattr(ep, "launches_per_call", backend.launches_per_call) * args.steps, "clocks": clocks,
                 "device_status": int(status.item())}
         print(json.dumps(line), flush=True)
+    if hasattr(ep, "close"):
+        ep.close()      # the captured graph holds NCCL kernels: release it before the communicator
     dist.destroy_process_group()
 
 

@@ -33,7 +33,7 @@ PROTOTYPES = {
     "b200_moe_w8a8": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(MoeWeights), C.POINTER(MoeLists), vp, vp, sz, vp,
                             vp, i32, vp, vp]),
     "b200_moe_w8a8_ep": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(MoeWeights), C.POINTER(MoeLists), C.POINTER(vp), i32,
-                               i32, vp, sz, vp, vp]),
+                               i32, i32, vp, sz, vp, vp]),
     "b200_moe_fp8_workspace_bytes": (sz, [i32, i32, i32, i32]),
     "b200_moe_fp8": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(MoeWeights), C.POINTER(MoeLists), vp, vp, sz, vp,
                            i32, vp, vp]),

@@ -134,6 +134,7 @@ struct GemmArgs {
   // cache (this GPU's own, or a peer's mapped over NVLink) receives the row at local slot s % ep_rows
   int ep_world;         // 0 / 1: single GPU, rows go to `cache`
   int ep_rows;          // routed slots per rank = tokens per rank x top-k
+  int ep_rank, ep_tokens;  // this rank and tokens per rank: shared-expert rows are kept only for own tokens
   bf16* ep_cache[8];
 };
 
@@ -333,9 +334,16 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (!UP) {
           bf16* dst = nullptr;
           if (slot >= 0) {
-            if (p.ep_world > 1) {
-              const int home = slot / p.ep_rows;
-              dst = home < p.ep_world ? p.ep_cache[home] + static_cast<size_t>(slot - home * p.ep_rows) * p.H : nullptr;
+            if (p.ep_world >= 1) {
+              const int routed = p.ep_rows * p.ep_world;
+              if (slot < routed) {
+                const int home = slot / p.ep_rows;
+                dst = p.ep_cache[home] + static_cast<size_t>(slot - home * p.ep_rows) * p.H;
+              } else {  // shared-expert row of token t: kept at row ep_rows + local t of this rank's own cache
+                const int t = slot - routed, home = t / p.ep_tokens;
+                if (home == p.ep_rank)
+                  dst = p.ep_cache[home] + static_cast<size_t>(p.ep_rows + t - home * p.ep_tokens) * p.H;
+              }
             } else {
               dst = p.cache + static_cast<size_t>(slot) * p.H;
             }
@@ -503,15 +511,17 @@ extern "C" int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_lo
 }
 
 extern "C" int b200_moe_w8a8_ep(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
-                                const b200_moe_lists* lists, void* const* peer_cache_host, int ep_world,
+                                const b200_moe_lists* lists, void* const* peer_cache_host, int ep_world, int ep_rank,
                                 int ep_tokens_per_rank, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
-  if (!peer_cache_host || ep_world < 1 || ep_world > 8 || ep_tokens_per_rank <= 0 || T != ep_world * ep_tokens_per_rank)
-    return fail(B200_E_ARG, "b200_moe_w8a8_ep: need 1 <= ep_world <= 8 and T == ep_world * ep_tokens_per_rank (T=%d)", T);
+  if (!peer_cache_host || ep_world < 1 || ep_world > 8 || ep_rank < 0 || ep_rank >= ep_world || ep_tokens_per_rank <= 0 ||
+      T != ep_world * ep_tokens_per_rank)
+    return fail(B200_E_ARG, "b200_moe_w8a8_ep: need 1 <= ep_world <= 8, 0 <= ep_rank < ep_world and T == ep_world * "
+                "ep_tokens_per_rank (T=%d)", T);
   for (int r = 0; r < ep_world; ++r)
     if (!peer_cache_host[r] || (reinterpret_cast<uintptr_t>(peer_cache_host[r]) & 15))
       return fail(B200_E_ARG, "b200_moe_w8a8_ep: peer cache %d is null or not 16-byte aligned", r);
   return moe_w8a8_impl(x, T, H, I, K, E_local, w, lists, peer_cache_host[0], ws, ws_bytes, nullptr, nullptr, 0, status,
-                       stream, peer_cache_host, ep_world, ep_tokens_per_rank);
+                       stream, peer_cache_host, ep_world | (ep_rank << 8), ep_tokens_per_rank);
 }
 
 static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
@@ -597,8 +607,11 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
   a.cache = static_cast<bf16*>(cache);
   a.dbg_acc = nullptr;
   a.dbg_h = nullptr;
-  a.ep_world = ep_world;
+  a.ep_world = ep_world & 0xff;
+  a.ep_rank = ep_world >> 8;
+  a.ep_tokens = ep_tokens_per_rank;
   a.ep_rows = ep_tokens_per_rank * K;
+  ep_world &= 0xff;
   for (int r = 0; r < 8; ++r) a.ep_cache[r] = (peer_cache && r < ep_world) ? static_cast<bf16*>(peer_cache[r]) : nullptr;
   if (stages & B200_MOE_STAGE_DOWN)
     moe_gemm_i8_kernel<false><<<grid, GEMM_THREADS, GemmCfg<false>::SMEM, st>>>(tmW2, tmSh2, tmHq, a);

@@ -187,7 +187,8 @@ def moe_fp8(x, w: MoeW8A8Weights, lists: RoutingLists, cache=None, ws=None, stat
     return cache
 
 
-def moe_w8a8_ep(x_all, w: MoeW8A8Weights, lists: RoutingLists, peer_ptrs, tokens_per_rank, ws=None, status=None):
+def moe_w8a8_ep(x_all, w: MoeW8A8Weights, lists: RoutingLists, peer_ptrs, rank, tokens_per_rank, ws=None,
+                status=None):
     """Expert-parallel int8 experts: this rank's experts over the gathered tokens, the weighted down rows
     stored straight into every home rank's routed cache (`peer_ptrs`: device pointers, one per rank)."""
     _need(x_all, torch.bfloat16, "x_all", 2)
@@ -201,7 +202,7 @@ def moe_w8a8_ep(x_all, w: MoeW8A8Weights, lists: RoutingLists, peer_ptrs, tokens
     arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_ptrs])
     wc = w.c_struct()
     check(_lib.lib().b200_moe_w8a8_ep(_p(x_all), T, H, I, K, E, C.byref(wc), C.byref(lists.c), arr, world,
-                                      int(tokens_per_rank), _p(ws), ws.numel(), _p(status), _stream()),
+                                      int(rank), int(tokens_per_rank), _p(ws), ws.numel(), _p(status), _stream()),
           "b200_moe_w8a8_ep")
 
 

@@ -132,42 +132,78 @@ class FusedExpertParallelMoe:
     stores the weighted expert rows straight into the home rank's cache over NVLink (plain peer
     stores from the GEMM epilogue, `ops.moe_w8a8_ep`), then one barrier, then the home rank adds its
     tokens' rows in slot order.  The caches are symmetric-memory buffers (one per rank, mapped into
-    every process); x, ids and weights are still all-gathered with NCCL (each token row is needed by up
-    to min(K, world) ranks).  Bit-identical to `ExpertParallelMoe` and to the single-GPU block."""
+    every process); x and the packed (ids, weights) are all-gathered with NCCL (each token row is needed
+    by up to min(K, world) ranks).  The shared expert runs in the same launches over the gathered
+    tokens (its weights are streamed once either way) and keeps the rows of this rank's own tokens.
+    The whole step is captured into a CUDA graph on first use.  Bit-identical to `ExpertParallelMoe`
+    and to the single-GPU block."""
 
-    def __init__(self, backend: "GpuMoeBackend", top_k: int, hidden: int, tokens_per_rank: int, group=None):
+    def __init__(self, backend: "GpuMoeBackend", top_k: int, hidden: int, tokens_per_rank: int, group=None,
+                 use_graph=True):
         import torch.distributed._symmetric_memory as symm
         self.b, self.K, self.H, self.T = backend, top_k, hidden, tokens_per_rank
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         dev = backend.wr.device
-        # routed rows of this rank's tokens; written by every rank (this one included)
-        self.cache_routed = symm.empty(tokens_per_rank * top_k, hidden, dtype=torch.bfloat16, device=dev)
-        self.handle = symm.rendezvous(self.cache_routed, self.group)
+        # rows of this rank's tokens: K routed rows per token (written by every rank) + the shared-expert row
+        self.cache = symm.empty(tokens_per_rank * (top_k + 1), hidden, dtype=torch.bfloat16, device=dev)
+        self.handle = symm.rendezvous(self.cache, self.group)
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         T_all = tokens_per_rank * self.world
         self.x_all = torch.empty(T_all, hidden, dtype=torch.bfloat16, device=dev)
+        self.route_local = torch.empty(tokens_per_rank, 2 * top_k, dtype=torch.int32, device=dev)
+        self.route_all = torch.empty(T_all, 2 * top_k, dtype=torch.int32, device=dev)
         self.ids_all = torch.empty(T_all, top_k, dtype=torch.int32, device=dev)
         self.wts_all = torch.empty(T_all, top_k, dtype=torch.float32, device=dev)
         self.lists = backend.ops.RoutingLists(T_all, top_k, backend.E_local, 128, dev)
         self.ws = backend.ops.moe_w8a8_workspace(T_all, hidden, backend.w.w2.shape[-1], top_k, dev)
-        self.launches_per_call = 16
+        self.x_static = torch.empty(tokens_per_rank, hidden, dtype=torch.bfloat16, device=dev)
+        self.out = torch.empty(tokens_per_rank, hidden, dtype=torch.bfloat16, device=dev)
+        self.use_graph, self.graph = use_graph, None
+        self.launches_per_call = 8   # router x2, lists, quantise, up, h-quantise, down, combine (+2 NCCL, 2 barriers)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        b, ops = self.b, self.b.ops
+    def _step(self):
+        b, ops, K = self.b, self.b.ops, self.K
+        x = self.x_static
         ids, wts = b.route(x)
-        dist.all_gather_into_tensor(self.x_all, x.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(self.ids_all, ids, group=self.group)
-        dist.all_gather_into_tensor(self.wts_all, wts, group=self.group)
-        ops.build_lists(self.ids_all, self.wts_all, self.lists, None, e_lo=b.e_lo, with_shared=False)
+        self.route_local[:, :K].copy_(ids)
+        self.route_local[:, K:].copy_(wts.view(torch.int32))
+        dist.all_gather_into_tensor(self.x_all, x, group=self.group)
+        dist.all_gather_into_tensor(self.route_all, self.route_local, group=self.group)
+        self.ids_all.copy_(self.route_all[:, :K])
+        self.wts_all.copy_(self.route_all[:, K:].view(torch.float32))
+        ops.build_lists(self.ids_all, self.wts_all, self.lists, None, e_lo=b.e_lo, with_shared=True)
         # nobody may still be reading last step's rows when the first peer store of this step lands
         self.handle.barrier(channel=0)
-        ops.moe_w8a8_ep(self.x_all, b.w_routed, self.lists, self.peer_ptrs, self.T, ws=self.ws, status=b.status)
+        ops.moe_w8a8_ep(self.x_all, b.w, self.lists, self.peer_ptrs, self.rank, self.T, ws=self.ws, status=b.status)
         self.handle.barrier(channel=1)      # every rank's rows for my tokens have landed
-        return b.shared_and_combine(x, self.cache_routed)
+        ops.moe_combine(self.cache, x, b.gate_w, K, out=self.out)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        self.x_static.copy_(x, non_blocking=True)
+        if not self.use_graph:
+            self._step()
+            return self.out
+        if self.graph is None:
+            self._step()                    # warm-up: one-time set-up inside the operators and NCCL
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._step()
+            self.graph = g
+        self.graph.replay()
+        return self.out
 
     __call__ = forward
+
+    def close(self):
+        """Drop the captured graph.  Call before `destroy_process_group`: NCCL does not finish
+        destroying a communicator while a live CUDA graph still holds its kernels."""
+        if self.graph is not None:
+            torch.cuda.synchronize()
+            self.graph = None
 
 
 def sharded_argmax(x, w_shard, w_s_shard, shard_lo, group=None):

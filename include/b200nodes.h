@@ -153,16 +153,18 @@ int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_local, const 
 /* Expert-parallel form of b200_moe_w8a8 with the combine-side exchange fused into the down GEMM.
  * (No counterpart in the reference, which is single-GPU: layer.py:396-402.)
  * x holds the gathered tokens of all ranks, T = ep_world * ep_tokens_per_rank, rank r's tokens at rows
- * [r * ep_tokens_per_rank, ...); `lists` were built for this rank's experts with with_shared = 0.
- * The down epilogue stores bf16(y * routing weight) for global slot s = t*K + j straight into the home
- * rank's cache, peer_cache_host[s / (ep_tokens_per_rank*K)] + (s % (ep_tokens_per_rank*K)) * H, with
- * ordinary stores: peer_cache_host is a HOST array of ep_world DEVICE pointers, entry r being rank r's
- * routed cache [ep_tokens_per_rank*K, H] bf16 as mapped into this process (its own buffer for r ==
- * this rank, peer-mapped memory otherwise).  No TMA touches peer memory.  The caller synchronises the
+ * [r * ep_tokens_per_rank, ...); `lists` were built for this rank's experts (e_lo, E_local), with or
+ * without the shared expert.  The down epilogue stores bf16(y * routing weight) for global slot
+ * s = t*K + j straight into the home rank's cache, peer_cache_host[s / (ep_tokens_per_rank*K)] +
+ * (s % (ep_tokens_per_rank*K)) * H, with ordinary stores; shared-expert rows are kept only for this
+ * rank's own tokens, at row ep_tokens_per_rank*K + local token of its own cache (the layout
+ * b200_moe_combine reads).  peer_cache_host is a HOST array of ep_world DEVICE pointers, entry r being
+ * rank r's cache [ep_tokens_per_rank*(K+1), H] bf16 as mapped into this process (its own buffer for
+ * r == ep_rank, peer-mapped memory otherwise).  No TMA touches peer memory.  The caller synchronises the
  * ranks (any barrier that orders their streams) before the home ranks read their caches. */
 int b200_moe_w8a8_ep(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
-                     const b200_moe_lists* lists, void* const* peer_cache_host, int ep_world, int ep_tokens_per_rank,
-                     void* ws, size_t ws_bytes, int32_t* status, void* stream);
+                     const b200_moe_lists* lists, void* const* peer_cache_host, int ep_world, int ep_rank,
+                     int ep_tokens_per_rank, void* ws, size_t ws_bytes, int32_t* status, void* stream);
 
 /* MoE block, fp8 e4m3 with 128x128 weight block scales and per-(token,128-channel) activation
  * scales.  The reference has no block-scaled fp8 MoE; the arithmetic is its scaled-GEMM recipe

@@ -22,6 +22,8 @@ def _worker(rank, world, port, out):
     from bundles_b200 import moe_block, ops, parallel, synth
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    import faulthandler
+    faulthandler.dump_traceback_later(240, exit=True)   # a rank stuck in a collective ends itself with a traceback
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -44,6 +46,7 @@ def _worker(rank, world, port, out):
         y2 = fused(xl).clone()
         y3 = fused(xl).clone()                      # a second step reuses the peer-written caches
         torch.cuda.synchronize()
+        fused.close()
         ok_moe = torch.equal(y, ref[rank * T_local:(rank + 1) * T_local]) and ops.read_status(backend.status) == 0
         ok_moe = ok_moe and torch.equal(y2, y) and torch.equal(y3, y)
         # vocab-sharded greedy token
