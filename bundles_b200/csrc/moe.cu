@@ -141,19 +141,22 @@ struct GemmArgs {
 constexpr int TILE_BYTES = 128 * 128;   // one 128-row x 128-byte operand tile
 constexpr int GEMM_THREADS = 320;   // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int TMEM_COLS = 512;
+constexpr int I8_CACHED = 64;       // tiles per CTA whose list entries are cached in shared memory
 
 template <bool UP>
 struct GemmCfg {
   static constexpr int NA = UP ? 2 : 1;                      // weight tiles per stage (gate + up)
   static constexpr int STAGE = NA * TILE_BYTES + TILE_BYTES;  // + token tile (<= 128 rows)
   static constexpr int STAGES = UP ? 4 : 6;
-  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + 8 * 128 * 20 /*row metadata, one copy per epilogue warp*/;
+  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + 8 * 128 * 20 /*row metadata, one copy per epilogue warp*/ +
+                              I8_CACHED * 12 /*block-list entries of this CTA's tiles*/;
 };
 
 template <bool UP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWsh,
-                   const __grid_constant__ CUtensorMap tmX, const GemmArgs p) {
+                   const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmX64,
+                   const __grid_constant__ CUtensorMap tmX128, const GemmArgs p) {
   using C = GemmCfg<UP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -169,6 +172,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   float* m_wt_all = m_scale_all + 1024;                                               // [8][128] routing weight
   int* m_slot_all = reinterpret_cast<int*>(m_wt_all + 1024);                          // [8][128] slot or -1
   bf16** m_dst_all = reinterpret_cast<bf16**>(m_slot_all + 1024);                     // [8][128] destination row (down)
+  int* binfo = reinterpret_cast<int*>(m_dst_all + 1024);                              // [I8_CACHED][3] expert, row0, rows
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -185,6 +189,24 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmWsh);
     tma_prefetch_desc(&tmX);
+    tma_prefetch_desc(&tmX64);
+    tma_prefetch_desc(&tmX128);
+  }
+  // Tiles are (block, 128-row weight tile) pairs; CTA b takes tiles b, b + grid, ... (hot and cold blocks mix
+  // evenly).  With every pipeline stage in flight a dependent global load costs microseconds (it queues
+  // behind the weight stream), so nothing on the per-tile path may wait for one: the list entries of this
+  // CTA's tiles are read into shared memory before the stream starts, and the epilogue's row metadata
+  // and weight scales are loaded one tile ahead.
+  const int nblocks = p.L.nblocks[0];
+  const int ntiles = nblocks * p.mtiles;
+  if (threadIdx.x < I8_CACHED) {
+    const int tile = blockIdx.x + threadIdx.x * gridDim.x;
+    if (tile < ntiles) {
+      const int blk = tile / p.mtiles;
+      binfo[threadIdx.x * 3 + 0] = p.L.blk_expert[blk];
+      binfo[threadIdx.x * 3 + 1] = p.L.blk_row0[blk];
+      binfo[threadIdx.x * 3 + 2] = p.L.blk_rows[blk];
+    }
   }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
@@ -192,16 +214,20 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  int nblocks = p.L.nblocks[0];
-  const int ntiles = nblocks * p.mtiles;
-
   // every role decodes a tile the same way; a malformed list entry is skipped by all of them
   auto decode = [&](int tile, int& e, int& row0, int& n, int& mt) -> bool {
     const int blk = tile / p.mtiles;
     mt = tile - blk * p.mtiles;
-    e = p.L.blk_expert[blk];
-    row0 = p.L.blk_row0[blk];
-    n = p.L.blk_rows[blk];
+    const int ci = (tile - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x);
+    if (ci < I8_CACHED) {
+      e = binfo[ci * 3 + 0];
+      row0 = binfo[ci * 3 + 1];
+      n = binfo[ci * 3 + 2];
+    } else {
+      e = p.L.blk_expert[blk];
+      row0 = p.L.blk_row0[blk];
+      n = p.L.blk_rows[blk];
+    }
     return e >= 0 && e <= p.E_local && n >= 1 && n <= 128 && row0 >= 0 && row0 + n <= p.total_rows;
   };
 
@@ -225,10 +251,19 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
           uint8_t* sA = smem + stage * C::STAGE;
           uint8_t* sB = sA + C::NA * TILE_BYTES;
-          mbar_expect_tx(&full[stage], C::NA * TILE_BYTES + nb16 * 2048);
+          // every TMA instruction costs the issuing thread ~80 ns, so the token rows come in as few boxes as
+          // possible: 16-row boxes up to 32 rows, one 64-row box (+ up to two 16-row boxes), or one 128-row
+          // box.  Rows past the block belong to the next expert or are zero-filled past the end of the
+          // tensor; the MMA's N ignores them.
+          const int big = nb16 > 6 ? 8 : (nb16 > 2 ? 4 : 0);       // 16-row units covered by the large box
+          const int small = nb16 > big ? nb16 - big : 0;            // 16-row boxes after it
+          mbar_expect_tx(&full[stage], C::NA * TILE_BYTES + (big + small) * 2048);
           tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
           if (UP) tma_load_2d(sA + TILE_BYTES, mapW, ks * 128, wrow + p.I, &full[stage]);
-          for (int b = 0; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
+          if (big == 8) tma_load_2d(sB, &tmX128, ks * 128, row0, &full[stage]);
+          if (big == 4) tma_load_2d(sB, &tmX64, ks * 128, row0, &full[stage]);
+          for (int b = big; b < big + small; ++b)
+            tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
           ++issued;
           if (++stage == C::STAGES) {
             stage = 0;
@@ -308,58 +343,90 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const float* __restrict__ wt_of_row = p.L.wt_of_row;
     const int32_t* __restrict__ slot_of_row = p.L.slot_of_row;
     int it = 0;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    // everything the epilogue of a tile reads from global memory, loaded one tile ahead into registers:
+    // activation scale, slot and routing weight of columns lane, lane + 32, ..., and the weight scale(s)
+    // of this lane's row.  No loaded value is consumed where it is fetched.
+    struct Pre {
+      float sc[4], wt[4], w0, w1;
+      int sl[4];
+    };
+    const int step = static_cast<int>(gridDim.x);
+    auto fetch = [&](int tile, Pre& m) {
+      m.w0 = m.w1 = 0.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        m.sc[u] = m.wt[u] = 0.f;
+        m.sl[u] = -1;
+      }
       int e, row0, n, mt;
-      if (!decode(tile, e, row0, n, mt)) {
+      if (tile >= ntiles || !decode(tile, e, row0, n, mt)) return;
+      const float* sw = (e == p.E_local) ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * p.w_rows;
+      const int r = mt * 128 + q * 32 + lane;
+      m.w0 = sw[r];
+      if (UP) m.w1 = sw[p.I + r];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = lane + 32 * u;
+        if (c < n) {
+          m.sc[u] = a_scale[row0 + c];
+          m.sl[u] = slot_of_row[row0 + c];
+          if (!UP) m.wt[u] = wt_of_row[row0 + c];
+        }
+      }
+    };
+    Pre pre;
+    fetch(blockIdx.x, pre);
+    for (int tile = blockIdx.x; tile < ntiles; tile += step) {
+      int e, row0, n, mt;
+      const float ws0 = pre.w0, ws1 = pre.w1;
+      const bool good = decode(tile, e, row0, n, mt);
+      if (good) {
+        // stage this tile's row metadata (entries past n only pad the last 16-column chunk)
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = lane + 32 * u;
+          int slot = pre.sl[u];
+          if (slot >= p.total_rows) slot = -1;
+          ms[c] = pre.sc[u];
+          m_wt[c] = pre.wt[u];
+          m_slot[c] = slot;
+          if (!UP) {
+            bf16* dst = nullptr;
+            if (slot >= 0) {
+              if (p.ep_world >= 1) {
+                const int routed = p.ep_rows * p.ep_world;
+                if (slot < routed) {
+                  const int home = slot / p.ep_rows;
+                  dst = p.ep_cache[home] + static_cast<size_t>(slot - home * p.ep_rows) * p.H;
+                } else {  // shared-expert row of token t: kept at row ep_rows + local t of this rank's own cache
+                  const int t = slot - routed, home = t / p.ep_tokens;
+                  if (home == p.ep_rank)
+                    dst = p.ep_cache[home] + static_cast<size_t>(p.ep_rows + t - home * p.ep_tokens) * p.H;
+                }
+              } else {
+                dst = p.cache + static_cast<size_t>(slot) * p.H;
+              }
+            }
+            m_dst[c] = dst;
+          }
+        }
+        __syncwarp();
+      }
+      fetch(tile + step, pre);  // in flight during this tile's epilogue
+      if (!good) {
         if (lane == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_LIST);
         continue;
       }
       const int buf = it & 1;
       const uint32_t bphase = (it >> 1) & 1;
       ++it;
-      // stage this block's row metadata while the MMAs run
-      __syncwarp();
-      for (int c = lane; c < ((n + 15) & ~15); c += 32) {  // entries past n only pad the last 16-column chunk
-        float sc = 0.f, wt = 0.f;
-        int slot = -1;
-        if (c < n) {
-          sc = a_scale[row0 + c];
-          slot = slot_of_row[row0 + c];
-          if (!UP) wt = wt_of_row[row0 + c];
-          if (slot >= p.total_rows) slot = -1;
-        }
-        ms[c] = sc;
-        m_wt[c] = wt;
-        m_slot[c] = slot;
-        if (!UP) {
-          bf16* dst = nullptr;
-          if (slot >= 0) {
-            if (p.ep_world >= 1) {
-              const int routed = p.ep_rows * p.ep_world;
-              if (slot < routed) {
-                const int home = slot / p.ep_rows;
-                dst = p.ep_cache[home] + static_cast<size_t>(slot - home * p.ep_rows) * p.H;
-              } else {  // shared-expert row of token t: kept at row ep_rows + local t of this rank's own cache
-                const int t = slot - routed, home = t / p.ep_tokens;
-                if (home == p.ep_rank)
-                  dst = p.ep_cache[home] + static_cast<size_t>(p.ep_rows + t - home * p.ep_tokens) * p.H;
-              }
-            } else {
-              dst = p.cache + static_cast<size_t>(slot) * p.H;
-            }
-          }
-          m_dst[c] = dst;
-        }
-      }
-      __syncwarp();
       if (!mbar_wait(&tfull[buf], bphase, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + buf * 256 + (static_cast<uint32_t>(q * 32) << 16);
       const int r = mt * 128 + q * 32 + lane;  // weight row inside the expert (up: channel of I; down: column of H)
-      const bool shared_e = (e == p.E_local);
       if (UP) {
-        const float* sw = shared_e ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * p.w_rows;
-        const float wsg = sw[r], wsu = sw[p.I + r];
+        const float wsg = ws0, wsu = ws1;
         bf16* __restrict__ hout = p.h_out + static_cast<size_t>(row0) * p.I + r;
         for (int c0 = half * 16; c0 < n; c0 += 32) {
           uint32_t rg[16], ru[16];
@@ -392,7 +459,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
         }
       } else {
-        const float ws = shared_e ? p.s_w_sh[r] : p.s_w[static_cast<size_t>(e) * p.w_rows + r];
+        const float ws = ws0;
         for (int c0 = half * 16; c0 < n; c0 += 32) {
           uint32_t ra[16];
           tmem_ld16(taddr + c0, ra);
@@ -551,14 +618,18 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
   MoeLists L{lists->counts,     lists->offsets,  lists->row_of_pair, lists->slot_of_row, lists->wt_of_row,
              lists->blk_expert, lists->blk_row0, lists->blk_rows,    lists->nblocks};
 
-  CUtensorMap tmW13, tmSh13, tmXq, tmW2, tmSh2, tmHq;
+  CUtensorMap tmW13, tmSh13, tmXq, tmXq64, tmXq128, tmW2, tmSh2, tmHq, tmHq64, tmHq128;
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW13, w->w13, static_cast<uint64_t>(E_local) * 2 * I, H, 128, "w13"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmSh13, shared ? w->sh13 : w->w13, 2 * I, H, 128, "sh13"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmXq, xq, rows, H, 16, "xq"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmXq64, xq, rows, H, 64, "xq"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmXq128, xq, rows, H, 128, "xq"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmW2, w->w2, static_cast<uint64_t>(E_local) * H, I, 128, "w2"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmSh2, shared ? w->sh2 : w->w2, H, I, 128, "sh2"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmHq, hq, rows, I, 16, "hq"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmHq64, hq, rows, I, 64, "hq"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmHq128, hq, rows, I, 128, "hq"))) return rc;
 
   static bool attr_done[64] = {false};
   int dev = 0;
@@ -592,7 +663,7 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
   a.dbg_acc = dbg_acc13;
   a.dbg_h = static_cast<bf16*>(dbg_h);
   if (stages & B200_MOE_STAGE_UP)
-    moe_gemm_i8_kernel<true><<<grid, GEMM_THREADS, GemmCfg<true>::SMEM, st>>>(tmW13, tmSh13, tmXq, a);
+    moe_gemm_i8_kernel<true><<<grid, GEMM_THREADS, GemmCfg<true>::SMEM, st>>>(tmW13, tmSh13, tmXq, tmXq64, tmXq128, a);
 
   if (stages & B200_MOE_STAGE_HQUANT)
     quant_rows_i8_kernel<<<(rows + 7) / 8, 256, 0, st>>>(h, rows, I, L.slot_of_row, hq, hs);
@@ -614,7 +685,7 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
   ep_world &= 0xff;
   for (int r = 0; r < 8; ++r) a.ep_cache[r] = (peer_cache && r < ep_world) ? static_cast<bf16*>(peer_cache[r]) : nullptr;
   if (stages & B200_MOE_STAGE_DOWN)
-    moe_gemm_i8_kernel<false><<<grid, GEMM_THREADS, GemmCfg<false>::SMEM, st>>>(tmW2, tmSh2, tmHq, a);
+    moe_gemm_i8_kernel<false><<<grid, GEMM_THREADS, GemmCfg<false>::SMEM, st>>>(tmW2, tmSh2, tmHq, tmHq64, tmHq128, a);
   return launch_status("b200_moe_w8a8");
 }
 

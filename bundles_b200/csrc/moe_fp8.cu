@@ -3,7 +3,9 @@
 // epilogues.  The reference has no block-scaled fp8 MoE; the structure follows its int8 twin
 // (qk_moe_prefill_i8.cu:3649-3651, 3905-3945): per 128-k block the MMA chain starts from zero in a
 // TMEM partial buffer and is promoted by the epilogue warps, acc = fma(partial, a_scale * w_scale,
-// acc), with two partial buffers so that block g + 1's MMAs overlap block g's promotion.
+// acc).  All 512 TMEM columns are partial buffers (8 of 64 columns, 4 of 128 for the up GEMM), so the MMA
+// issuer runs as far ahead as the weight stream allows and the promotions follow back to back instead of
+// paying one MMA -> commit -> wait -> load round trip per block.
 //
 // Orientation as in the int8 kernels: M = 128 weight rows (exactly one weight scale block row),
 // N = 16..64 tokens of one expert, K = 32 bytes per MMA; weights and expert-sorted token rows arrive
@@ -17,6 +19,7 @@ namespace b200 {
 constexpr int F8_TILE = 128 * 128;       // weight tile bytes per stage
 constexpr int F8_BTILE = 64 * 128;       // token tile bytes per stage (<= 64 rows)
 constexpr int F8_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
+constexpr int F8_CACHED = 64;            // tiles per CTA whose block-list entries are cached in shared memory
 constexpr int F8_MAXKG = 32;             // k blocks per row of scales held in shared memory (K <= 4096)
 
 // ---- activation quantisers ----------------------------------------------------------------------------
@@ -100,27 +103,40 @@ struct F8Cfg {
   static constexpr bool UP = MODE == MODE_UP;
   static constexpr int NA = UP ? 2 : 1;
   static constexpr int STAGE = NA * F8_TILE + F8_BTILE;
-  static constexpr int STAGES = UP ? 4 : 6;
-  static constexpr int META = 8 * (32 * F8_MAXKG * 4 + 32 * 8);  // per epilogue warp: scales, slot, weight of its 32 columns
-  static constexpr int SMEM = STAGES * STAGE + 1024 + 256 + META;
-  static constexpr int TMEM = UP ? 256 : 128;
+  static constexpr int STAGES = UP ? 4 : 7;
+  static constexpr int PW = UP ? 128 : 64;   // TMEM columns of one partial buffer
+  static constexpr int NPB = 512 / PW;       // partial buffers
+  static constexpr int META_WARP = 32 * F8_MAXKG * 4 + 32 * 8 + 2 * F8_MAXKG * 4;
+  static constexpr int META = 8 * META_WARP;  // per epilogue warp: activation scales, slot, weight of its 32 columns, weight scales
+  static constexpr int SMEM = STAGES * STAGE + 1024 + 256 + META + F8_CACHED * 12;
+  static constexpr int TMEM = 512;
 };
+
+// Optional timeline of CTA 0 (compile with -DB200_TRACE): %globaltimer stamps of the producer's TMA issues (row 0),
+// the MMA issuer's stage arrivals (row 1), the first epilogue warp's promotions (row 2) and tile boundaries (row 3).
+#ifdef B200_TRACE
+__device__ unsigned long long g_trace[4][256];
+#define TRACE(k, i) do { if (blockIdx.x == 0 && (i) < 256) g_trace[k][i] = globaltimer(); } while (0)
+#else
+#define TRACE(k, i) do { } while (0)
+#endif
 
 template <int MODE>
 __global__ void __launch_bounds__(F8_THREADS, 1)
 moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWsh,
-                   const __grid_constant__ CUtensorMap tmX, const F8Args p) {
+                   const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmX64, const F8Args p) {
   using C = F8Cfg<MODE>;
   constexpr bool UP = MODE == MODE_UP, LM = MODE == MODE_LM || MODE == MODE_DENSE, DENSE = MODE == MODE_DENSE;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE);
   uint64_t* empty = full + C::STAGES;
-  uint64_t* pfull = empty + C::STAGES;   // [2] a 128-k partial is complete in TMEM
-  uint64_t* pempty = pfull + 2;          // [2] the epilogue warps have promoted it
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pempty + 2);
+  uint64_t* pfull = empty + C::STAGES;   // [NPB] a 128-k partial is complete in TMEM
+  uint64_t* pempty = pfull + C::NPB;     // [NPB] the epilogue warps have promoted it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pempty + C::NPB);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint8_t* meta = smem + C::STAGES * C::STAGE + 256;
+  int* tinfo = reinterpret_cast<int*>(meta + C::META);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -128,7 +144,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < C::NPB; ++b) {
       mbar_init(&pfull[b], 1);
       mbar_init(&pempty[b], 8);
     }
@@ -137,13 +153,26 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmWsh);
     tma_prefetch_desc(&tmX);
+    tma_prefetch_desc(&tmX64);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, C::TMEM);
-  tc_fence_before();
+  // Tiles are (block, 128-row weight tile) pairs, weight tile fastest; each CTA takes a contiguous range, so
+  // consecutive tiles mostly share their block and its metadata.  The list entries of the CTA's blocks are
+  // read once, before the weight stream starts: afterwards a dependent global load costs microseconds (it
+  // queues behind the stages in flight).
+  const int nblocks = LM ? 1 : p.L.nblocks[0];
+  const int ntiles = nblocks * p.mtiles;
+  const int t_lo = static_cast<int>(static_cast<long long>(blockIdx.x) * ntiles / gridDim.x);
+  const int t_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * ntiles / gridDim.x);
+  const int blk_lo = t_lo / p.mtiles;
+  if (!LM && threadIdx.x < F8_CACHED) {
+    const int blk = blk_lo + threadIdx.x;
+    if (blk < nblocks && blk * p.mtiles < t_hi) {
+      tinfo[threadIdx.x * 3 + 0] = p.L.blk_expert[blk];
+      tinfo[threadIdx.x * 3 + 1] = p.L.blk_row0[blk];
+      tinfo[threadIdx.x * 3 + 2] = p.L.blk_rows[blk];
+    }
+  }
   __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const int ntiles = LM ? p.mtiles : p.L.nblocks[0] * p.mtiles;
 
   auto decode = [&](int tile, int& e, int& row0, int& n, int& mt) -> bool {
     if (LM) {  // dense: every tile is 128 vocabulary rows against all the tokens
@@ -155,18 +184,82 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
     const int blk = tile / p.mtiles;
     mt = tile - blk * p.mtiles;
-    e = p.L.blk_expert[blk];
-    row0 = p.L.blk_row0[blk];
-    n = p.L.blk_rows[blk];
+    const int ci = blk - blk_lo;
+    if (ci < F8_CACHED) {
+      e = tinfo[ci * 3 + 0];
+      row0 = tinfo[ci * 3 + 1];
+      n = tinfo[ci * 3 + 2];
+    } else {
+      e = p.L.blk_expert[blk];
+      row0 = p.L.blk_row0[blk];
+      n = p.L.blk_rows[blk];
+    }
     return e >= 0 && e <= p.E_local && n >= 1 && n <= 64 && row0 >= 0 && row0 + n <= p.total_rows;
   };
+
+  // Per-block metadata of an epilogue warp (activation scales, slot and routing weight of its 32 columns) is
+  // loaded into registers one block ahead: the loads for the next block are issued when a block's first
+  // tile starts and are consumed at the next block's first tile; the first block's loads are issued
+  // before the producer starts.  Weight block scales are loaded two tiles ahead.  No loaded value is
+  // consumed where it is fetched.
+  struct Meta {
+    float v[16];
+    float wt;
+    int slot;
+  };
+  const int ep_half = (warp - 2) >> 2;
+  auto fetch = [&](int blk, Meta& m) {
+    m.wt = 0.f;
+    m.slot = -1;
+#pragma unroll
+    for (int u = 0; u < 16; ++u) m.v[u] = 0.f;
+    int e, row0, n, mt;
+    if (blk >= nblocks || blk * p.mtiles >= t_hi || !decode(blk * p.mtiles, e, row0, n, mt)) return;
+    const int c = (lane >> 4) * 32 + ep_half * 16 + (lane & 15);
+    if (!LM && c < n) {
+      m.slot = p.L.slot_of_row[row0 + c];
+      m.wt = p.L.wt_of_row[row0 + c];
+    }
+    const int total = 32 * p.ksteps;
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const int i = u * 32 + lane;  // i = l * ksteps + ks: consecutive lanes read consecutive floats
+      if (i < total) {
+        const int l = i / p.ksteps;
+        const int cc = (l >> 4) * 32 + ep_half * 16 + (l & 15);
+        if (cc < n) m.v[u] = p.a_scale[static_cast<size_t>(row0 + cc) * p.ksteps + (i - l * p.ksteps)];
+      }
+    }
+  };
+  auto load_ws = [&](int tile, float& w0, float& w1) {
+    w0 = w1 = 0.f;
+    int e, row0, n, mt;
+    if (tile >= t_hi || lane >= p.ksteps || !decode(tile, e, row0, n, mt)) return;
+    const float* swb = (e == p.E_local) ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * (p.w_rows / 128) * p.ksteps;
+    w0 = swb[static_cast<size_t>(mt) * p.ksteps + lane];                        // gate / down block row
+    if (UP) w1 = swb[static_cast<size_t>(p.I / 128 + mt) * p.ksteps + lane];    // up block row
+  };
+  Meta pre;
+  float wsa1 = 0.f, wsb1 = 0.f, wsa2 = 0.f, wsb2 = 0.f;
+  if (warp >= 2) {
+    fetch(blk_lo, pre);
+    load_ws(t_lo, wsa1, wsb1);
+    load_ws(t_lo + 1, wsa2, wsb2);
+  }
+
+  if (warp == 1) tmem_alloc(tmem_slot, C::TMEM);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) TRACE(3, 0);
 
   if (warp == 0) {
     if (lane == 0) {  // ---------------- TMA producer ----------------
       int stage = 0, issued = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
+      for (int tile = t_lo; ok && tile < t_hi; ++tile) {
         int e, row0, n, mt;
         if (!decode(tile, e, row0, n, mt)) continue;
         const int nb16 = (n + 15) >> 4;
@@ -179,10 +272,18 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
           uint8_t* sA = smem + stage * C::STAGE;
           uint8_t* sB = sA + C::NA * F8_TILE;
-          mbar_expect_tx(&full[stage], C::NA * F8_TILE + nb16 * 2048);
+          // every TMA instruction costs the issuing thread ~80 ns: more than 32 token rows come as one 64-row
+          // box (rows past the block belong to the next expert or are zero-filled past the end; the MMA's N
+          // ignores them) instead of three or four 16-row boxes
+          mbar_expect_tx(&full[stage], C::NA * F8_TILE + (nb16 > 2 ? F8_BTILE : nb16 * 2048));
           tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
           if (UP) tma_load_2d(sA + F8_TILE, mapW, ks * 128, wrow + p.I, &full[stage]);
-          for (int b = 0; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
+          if (nb16 > 2) {
+            tma_load_2d(sB, &tmX64, ks * 128, row0, &full[stage]);
+          } else {
+            for (int b = 0; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
+          }
+          TRACE(0, issued);
           ++issued;
           if (++stage == C::STAGES) {
             stage = 0;
@@ -210,22 +311,23 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       int stage = 0;
       uint32_t phase = 0, g = 0;  // g counts 128-k blocks over the CTA's whole life
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
+      for (int tile = t_lo; ok && tile < t_hi; ++tile) {
         int e, row0, n, mt;
         if (!decode(tile, e, row0, n, mt)) continue;
         const uint32_t N = static_cast<uint32_t>((n + 15) & ~15);
         const uint32_t idesc = umma_idesc(UMMA_C_F32, UMMA_AB_E4M3, N);
         for (int ks = 0; ks < p.ksteps && ok; ++ks, ++g) {
-          const uint32_t pb = g & 1u, pphase = (g >> 1) & 1u;
+          const uint32_t pb = g % C::NPB, pphase = (g / C::NPB) & 1u;
           if (!mbar_wait(&pempty[pb], pphase ^ 1u, abort_flag, p.status, ST_WAIT_TMEM_EMPTY) ||
               !mbar_wait(&full[stage], phase, abort_flag, p.status, ST_WAIT_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          TRACE(1, g);
           const uint32_t sA = smem_u32(smem + stage * C::STAGE);
           const uint32_t sB = sA + C::NA * F8_TILE;
-          const uint32_t d0 = tmem_base + pb * (UP ? 128 : 64);
+          const uint32_t d0 = tmem_base + pb * C::PW;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint64_t db = umma_desc_sw128(sB + kk * 32);
@@ -247,42 +349,57 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     // thread keeps at most 32 (+32 for up) accumulators ----------------
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    float* m_as = reinterpret_cast<float*>(meta + (warp - 2) * (32 * F8_MAXKG * 4 + 32 * 8));  // [32][ksteps]
-    float* m_wt = m_as + 32 * F8_MAXKG;                                                         // [32]
-    int* m_slot = reinterpret_cast<int*>(m_wt + 32);                                            // [32]
+    float* m_as = reinterpret_cast<float*>(meta + (warp - 2) * C::META_WARP);  // [ksteps][32]
+    float* m_wt = m_as + 32 * F8_MAXKG;                                        // [32]
+    int* m_slot = reinterpret_cast<int*>(m_wt + 32);                           // [32]
+    float* m_ws = reinterpret_cast<float*>(m_slot + 32);                       // [2][F8_MAXKG] weight block scales
     const float* __restrict__ a_scale = p.a_scale;
     uint32_t g = 0;
     bool ok = true;
     // local column l (0..31) of this warp is tile column col(l) = (l / 16) * 32 + half * 16 + l % 16
-    for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
+    auto stage_block = [&](int row0, int n) {
+      const int total = 32 * p.ksteps;
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int i = u * 32 + lane;
+        if (i < total) {
+          const int l = i / p.ksteps;
+          m_as[(i - l * p.ksteps) * 32 + l] = pre.v[u];
+        }
+      }
+      for (int i = 512 + lane; i < total; i += 32) {  // more than 16 k blocks: the rest is fetched in place
+        const int l = i / p.ksteps;
+        const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+        m_as[(i - l * p.ksteps) * 32 + l] = c < n ? a_scale[static_cast<size_t>(row0 + c) * p.ksteps + (i - l * p.ksteps)] : 0.f;
+      }
+      m_slot[lane] = pre.slot < p.total_rows ? pre.slot : -1;
+      m_wt[lane] = pre.wt;
+    };
+    int staged_blk = -1;
+    if (LM) stage_block(0, p.total_rows);  // the dense modes have one block of token rows: staged once
+    for (int tile = t_lo; ok && tile < t_hi; ++tile) {
       int e, row0, n, mt;
+      const float ws_a = wsa1, ws_b = wsb1;  // this tile's weight block scales; the queue moves on every tile
+      wsa1 = wsa2;
+      wsb1 = wsb2;
+      load_ws(tile + 2, wsa2, wsb2);
       if (!decode(tile, e, row0, n, mt)) {
         if (lane == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_LIST);
         continue;
       }
       __syncwarp();
-      for (int i = lane; i < 32 * p.ksteps; i += 32) {
-        const int l = i / p.ksteps, ks = i - l * p.ksteps;
-        const int c = (l >> 4) * 32 + half * 16 + (l & 15);
-        m_as[i] = c < n ? a_scale[static_cast<size_t>(row0 + c) * p.ksteps + ks] : 0.f;
+      const int blk = LM ? 0 : tile / p.mtiles;
+      if (!LM && blk != staged_blk) {  // first tile of a block
+        staged_blk = blk;
+        stage_block(row0, n);
+        fetch(blk + 1, pre);  // in flight during this block's tiles
       }
-      {
-        const int c = (lane >> 4) * 32 + half * 16 + (lane & 15);
-        int slot = -1;
-        float wt = 0.f;
-        if (!LM && c < n) {
-          slot = p.L.slot_of_row[row0 + c];
-          wt = p.L.wt_of_row[row0 + c];
-          if (slot >= p.total_rows) slot = -1;
-        }
-        m_slot[lane] = slot;
-        m_wt[lane] = wt;
+      if (lane < p.ksteps) {
+        m_ws[lane] = ws_a;
+        if (UP) m_ws[F8_MAXKG + lane] = ws_b;
       }
       __syncwarp();
-      const bool shared_e = (e == p.E_local);
-      const float* swb = shared_e ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * (p.w_rows / 128) * p.ksteps;
-      const float* sw_a = swb + static_cast<size_t>(mt) * p.ksteps;                      // gate / down block row
-      const float* sw_b = swb + static_cast<size_t>(p.I / 128 + mt) * p.ksteps;          // up block row (UP only)
+      if (warp == 2 && lane == 0) TRACE(3, 2 + 2 * ((tile - t_lo)));
       float acc_a[32], acc_b[UP ? 32 : 1];
 #pragma unroll
       for (int c = 0; c < 32; ++c) acc_a[c] = 0.f;
@@ -290,14 +407,15 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
         for (int c = 0; c < 32; ++c) acc_b[c] = 0.f;
       for (int ks = 0; ks < p.ksteps; ++ks, ++g) {
-        const uint32_t pb = g & 1u, pphase = (g >> 1) & 1u;
-        const float wsa = __ldg(sw_a + ks), wsb = UP ? __ldg(sw_b + ks) : 0.f;
+        const uint32_t pb = g % C::NPB, pphase = (g / C::NPB) & 1u;
+        const float wsa = m_ws[ks], wsb = UP ? m_ws[F8_MAXKG + ks] : 0.f;
         if (!mbar_wait(&pfull[pb], pphase, abort_flag, p.status, ST_WAIT_TMEM_FULL)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + pb * (UP ? 128 : 64) + half * 16 + (static_cast<uint32_t>(q * 32) << 16);
+        if (warp == 2 && lane == 0) TRACE(2, g);
+        const uint32_t taddr = tmem_base + pb * C::PW + half * 16 + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
           if (h2 * 32 + half * 16 < n) {
@@ -307,7 +425,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float as = m_as[(h2 * 16 + i) * p.ksteps + ks];
+              const float as = m_as[ks * 32 + h2 * 16 + i];
               acc_a[h2 * 16 + i] = __fmaf_rn(__uint_as_float(ra[i]), __fmul_rn(as, wsa), acc_a[h2 * 16 + i]);
               if (UP) acc_b[h2 * 16 + i] = __fmaf_rn(__uint_as_float(rb[i]), __fmul_rn(as, wsb), acc_b[h2 * 16 + i]);
             }
@@ -318,6 +436,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (lane == 0) mbar_arrive(&pempty[pb]);
       }
       if (!ok) break;
+      if (warp == 2 && lane == 0) TRACE(3, 3 + 2 * ((tile - t_lo)));
       const int r = mt * 128 + q * 32 + lane;
       if (DENSE) {
         // plain projection: out[token][feature] = bf16(acc)
@@ -330,31 +449,55 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
         }
       } else if (LM) {
-        // per token: the largest logit of this warp's 32 vocabulary rows and its id (ties to the lower
-        // id) as one packed 64-bit key per (tile, quadrant, token); a small kernel takes the max over them
+        // per token: the largest logit of this warp's 32 vocabulary rows and the lowest row that holds it,
+        // as one packed 64-bit key per (tile, quadrant, token); a small kernel takes the max over them.
+        // The maximum over the lanes is a transposing butterfly of fmaxf (31 exchanges; NaN never survives
+        // against a number, -0 and +0 compare equal), after which lane l holds local column l; the row
+        // comes from a ballot of the lanes whose value equals the maximum.
         const bool live = r < p.w_rows;
+        float mv[32];
 #pragma unroll
         for (int l = 0; l < 32; ++l) {
-          const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+          mv[l] = live ? acc_a[l] : __int_as_float(0x7fc00000);
+          if (p.lm_logits && live) {
+            const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+            if (c < n) p.lm_logits[static_cast<size_t>(c) * p.w_rows + r] = acc_a[l];
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const bool up_half = (lane & o) != 0;
+#pragma unroll
+          for (int i = 0; i < o; ++i) {
+            const float send = up_half ? mv[i] : mv[i + o];
+            const float keep = up_half ? mv[i + o] : mv[i];
+            mv[i] = fmaxf(keep, __shfl_xor_sync(FULL_MASK, send, o));
+          }
+        }
+        const float best = mv[0];  // column `lane`: NaN only if every live row is NaN (or none is live)
+        uint32_t mine = 0u;
+#pragma unroll
+        for (int l = 0; l < 32; ++l) {
+          const float bl = __shfl_sync(FULL_MASK, best, l);
+          const uint32_t hit = __ballot_sync(FULL_MASK, live && acc_a[l] == bl);
+          if (lane == l) mine = hit;
+        }
+        const uint32_t live_mask = __ballot_sync(FULL_MASK, live);
+        {
+          const int c = (lane >> 4) * 32 + half * 16 + (lane & 15);
           if (c < n) {
-            const float v = acc_a[l];
-            if (p.lm_logits && live) p.lm_logits[static_cast<size_t>(c) * p.w_rows + r] = v;
-            uint32_t key = 0u;
-            if (live && v == v) {
-              const float vz = v + 0.f;
-              key = __float_as_uint(vz);
-              key = (key & 0x80000000u) ? ~key : (key | 0x80000000u);
-              if (key < 2u) key = 2u;
-            } else if (live) {
-              key = 1u;
+            unsigned long long key = 0ull;  // no live row
+            const int base_id = p.lm_shard_lo + mt * 128 + q * 32;
+            if (mine) {
+              uint32_t k = __float_as_uint(best + 0.f);
+              k = (k & 0x80000000u) ? ~k : (k | 0x80000000u);
+              if (k < 2u) k = 2u;
+              key = (static_cast<unsigned long long>(k) << 32) |
+                    (0xffffffffu - static_cast<uint32_t>(base_id + __ffs(mine) - 1));
+            } else if (live_mask) {  // only NaN among the live rows: value part 1, the lowest live row
+              key = (1ull << 32) | (0xffffffffu - static_cast<uint32_t>(base_id + __ffs(live_mask) - 1));
             }
-            const uint32_t m = __reduce_max_sync(FULL_MASK, key);
-            const uint32_t id = __reduce_min_sync(FULL_MASK, (key == m && live) ? static_cast<uint32_t>(r) : 0xffffffffu);
-            if (lane == 0)
-              p.lm_keys[(static_cast<size_t>(tile) * 4 + q) * n + c] =
-                  m == 0u ? 0ull
-                          : (static_cast<unsigned long long>(m) << 32) |
-                                (0xffffffffu - static_cast<uint32_t>(p.lm_shard_lo + static_cast<int>(id)));
+            p.lm_keys[(static_cast<size_t>(tile) * 4 + q) * n + c] = key;
           }
         }
       } else if (UP) {
@@ -379,6 +522,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   }
+  if (warp == 2 && lane == 0) TRACE(3, 1);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -386,6 +530,12 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tmem_dealloc(tmem_base, C::TMEM);
   }
 }
+
+#ifdef B200_TRACE
+extern "C" int b200_trace_read(unsigned long long* host) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace)));
+}
+#endif
 
 // x bf16 [T, H] -> e4m3 rows [T, H] + scales [T, H/128] in token order (no permutation)
 void b200_quant_rows_f8_launch(const void* x, int T, int H, uint8_t* xq, float* xs, cudaStream_t st) {
@@ -444,14 +594,16 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
   const int rows = T * (K + 1);
   MoeLists L{lists->counts,     lists->offsets,  lists->row_of_pair, lists->slot_of_row, lists->wt_of_row,
              lists->blk_expert, lists->blk_row0, lists->blk_rows,    lists->nblocks};
-  CUtensorMap tmW13, tmSh13, tmXq, tmW2, tmSh2, tmHq;
+  CUtensorMap tmW13, tmSh13, tmXq, tmXq64, tmW2, tmSh2, tmHq, tmHq64;
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW13, w->w13, static_cast<uint64_t>(E_local) * 2 * I, H, 128, "w13"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmSh13, shared ? w->sh13 : w->w13, 2 * I, H, 128, "sh13"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmXq, xq, rows, H, 16, "xq"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmXq64, xq, rows, H, 64, "xq"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmW2, w->w2, static_cast<uint64_t>(E_local) * H, I, 128, "w2"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmSh2, shared ? w->sh2 : w->w2, H, I, 128, "sh2"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmHq, hq, rows, I, 16, "hq"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmHq64, hq, rows, I, 64, "hq"))) return rc;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -480,7 +632,7 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
   a.h_out = h;
   a.dbg_h = static_cast<bf16*>(dbg_h);
   if (stages & B200_MOE_STAGE_UP)
-    moe_gemm_f8_kernel<MODE_UP><<<grid, F8_THREADS, F8Cfg<MODE_UP>::SMEM, st>>>(tmW13, tmSh13, tmXq, a);
+    moe_gemm_f8_kernel<MODE_UP><<<grid, F8_THREADS, F8Cfg<MODE_UP>::SMEM, st>>>(tmW13, tmSh13, tmXq, tmXq64, a);
   if (stages & B200_MOE_STAGE_HQUANT)
     quant_rows_f8_kernel<<<(rows + 7) / 8, 256, 0, st>>>(h, rows, I, L.slot_of_row, hq, hs);
   a.mtiles = H / 128;
@@ -493,7 +645,7 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
   a.cache = static_cast<bf16*>(cache);
   a.dbg_h = nullptr;
   if (stages & B200_MOE_STAGE_DOWN)
-    moe_gemm_f8_kernel<MODE_DOWN><<<grid, F8_THREADS, F8Cfg<MODE_DOWN>::SMEM, st>>>(tmW2, tmSh2, tmHq, a);
+    moe_gemm_f8_kernel<MODE_DOWN><<<grid, F8_THREADS, F8Cfg<MODE_DOWN>::SMEM, st>>>(tmW2, tmSh2, tmHq, tmHq64, a);
   return launch_status("b200_moe_fp8");
 }
 
@@ -583,10 +735,11 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   uint8_t* xq = base + l.xq;
   float* xs = reinterpret_cast<float*>(base + l.xs);
   unsigned long long* keys = reinterpret_cast<unsigned long long*>(base + l.keys);
-  CUtensorMap tmW, tmX;
+  CUtensorMap tmW, tmX, tmX64;
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(V_shard), H, 128, "lm_head weight"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "lm_head activations"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, 64, "lm_head activations"))) return rc;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -612,7 +765,7 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   a.lm_logits = logits_out;
   a.lm_shard_lo = shard_lo;
   const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
-  moe_gemm_f8_kernel<MODE_LM><<<grid, F8_THREADS, F8Cfg<MODE_LM>::SMEM, st>>>(tmW, tmW, tmX, a);
+  moe_gemm_f8_kernel<MODE_LM><<<grid, F8_THREADS, F8Cfg<MODE_LM>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
   lmhead_finish_kernel<<<T, 32, 0, st>>>(keys, a.mtiles * 4, T, max_out, idx_out);
   return launch_status("b200_lmhead_argmax");
 }
@@ -684,10 +837,11 @@ extern "C" int b200_dense_fp8(const void* x, int T, int H, const void* w, const 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* xq = static_cast<uint8_t*>(ws);
   float* xs = reinterpret_cast<float*>(xq + ((static_cast<size_t>(64) * H + 1023) & ~size_t(1023)));
-  CUtensorMap tmW, tmX;
+  CUtensorMap tmW, tmX, tmX64;
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(N), H, 128, "dense weight"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "dense activations"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, 64, "dense activations"))) return rc;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -710,7 +864,7 @@ extern "C" int b200_dense_fp8(const void* x, int T, int H, const void* w, const 
   a.h_out = static_cast<bf16*>(out);
   a.status = status;
   const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
-  moe_gemm_f8_kernel<MODE_DENSE><<<grid, F8_THREADS, F8Cfg<MODE_DENSE>::SMEM, st>>>(tmW, tmW, tmX, a);
+  moe_gemm_f8_kernel<MODE_DENSE><<<grid, F8_THREADS, F8Cfg<MODE_DENSE>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
   return launch_status("b200_dense_fp8");
 }
 
