@@ -40,6 +40,9 @@ PROTOTYPES = {
     "b200_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "b200_attn_front_workspace_bytes": (sz, [i32]),
     "b200_attn_front": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, i32, f32, i32, vp, vp, vp, vp, vp, sz, vp, vp]),
+    "b200_attn_verify_splits": (i32, [i32]),
+    "b200_attn_verify_workspace_bytes": (sz, [i32, i32]),
+    "b200_attn_verify": (i32, [vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, i32, f32, i32, vp, vp, sz, vp, vp]),
     "b200_dense_fp8_workspace_bytes": (sz, [i32, i32]),
     "b200_dense_fp8": (i32, [vp, i32, i32, vp, vp, i32, vp, vp, sz, vp, vp]),
     "b200_add_rmsnorm": (i32, [vp, vp, vp, f32, i32, i32, vp, vp]),

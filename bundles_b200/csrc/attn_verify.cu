@@ -1,0 +1,515 @@
+// Attention verify core for the gated full-attention layers: 4 draft tokens per request attend to the
+// request's e4m3 KV pages and causally to each other; split-KV online softmax; output gate.
+// Reference: attn_verify_kernel (qk_attn_verify.cu:354-744): S = q . k in fp32 from e4m3 operands,
+// running maximum raised only when a tile exceeds it by more than 8 in the log2 domain
+// (qk_attn_verify.cu:210, 264-267), P rounded to f16 before the P . V product (:297-301), split partials
+// (o, m, l) merged by an ordered sum (:690-737), out = bf16(bf16(o / l) * sigmoid(gate)) (:559-562).
+//
+// Layout chosen for this GPU (the reference reads 1-token pages through a per-token table, :398-423):
+// pages of 128 tokens; K page [kv head][128 keys][256 dims] e4m3, V page [kv head][256 dims][128 keys]
+// e4m3 (dim-major, so that V arrives as the K-major B operand of the P . V product).  The 4 new tokens
+// are appended to the pages by a small kernel first, and the main kernel sees them as ordinary keys
+// with the causal limit key <= prefix + token.
+//
+// One CTA per (request, kv head, split).  S^T = K . Q^T on tcgen05 kind::f8f6f4 with the 128 keys of a
+// page on the TMEM lanes and the 32 rows (4 tokens x 8 q heads) as columns, so the softmax warps own one
+// key per thread; O = P . V on kind::f16 (P as the A operand: 32 real rows, the other 96 rows of the
+// M = 128 tile read whatever follows P in shared memory and land in TMEM lanes nobody reads), V
+// converted e4m3 -> f16 in shared memory by its own warps; the row sums come from the same P through
+// a ones operand, so numerator and denominator see the same rounded probabilities.
+#include "common.cuh"
+#include "host.h"
+
+namespace b200 {
+
+constexpr int AV_D = 256, AV_HQ = 16, AV_HKV = 2, AV_GQ = 8, AV_NT = 4, AV_ROWS = AV_GQ * AV_NT;  // 32 rows
+constexpr int AV_PAGE = 128;
+constexpr int AV_KTILE = AV_PAGE * AV_D;        // 32 KB e4m3: two [128 keys x 128 B] swizzled blocks
+constexpr int AV_V16 = AV_D * AV_PAGE * 2;      // 64 KB f16: two [256 dims x 64 keys] swizzled blocks
+constexpr int AV_PBUF = 2 * AV_ROWS * 128;      // 8 KB: two [32 rows x 64 keys] f16 blocks
+constexpr int AV_QBUF = 2 * AV_ROWS * 128;      // 8 KB: two [32 rows x 128 B] e4m3 blocks
+constexpr int AV_ONES = 2 * 16 * 128;           // 4 KB: two [16 x 64 keys] f16 blocks, row 0 = 1.0
+constexpr int AV_MAXPAGES = 512;                // pages of one CTA's range whose table entries are cached
+constexpr int AV_SOFT = 8, AV_CONV = 4;         // softmax warps (two per TMEM quadrant), V conversion warps
+constexpr int AV_THREADS = (2 + AV_SOFT + AV_CONV) * 32;  // + TMA warp + MMA warp
+constexpr float AV_RESCALE_LOG2 = 8.f;
+// shared memory map (bytes from the 1024-aligned base); P sits before V16 so that the A operand's rows
+// 32..127 (up to 16 KB past a P block) stay inside the allocation
+constexpr int AV_OFF_K = 0;                              // 2 stages
+constexpr int AV_OFF_V8 = AV_OFF_K + 2 * AV_KTILE;       // 2 stages
+constexpr int AV_OFF_Q = AV_OFF_V8 + 2 * AV_KTILE;
+constexpr int AV_OFF_ONES = AV_OFF_Q + AV_QBUF;
+constexpr int AV_OFF_P = AV_OFF_ONES + AV_ONES;          // 2 buffers
+constexpr int AV_OFF_V16 = AV_OFF_P + 2 * AV_PBUF;
+constexpr int AV_OFF_BAR = AV_OFF_V16 + AV_V16;
+constexpr int AV_OFF_RED = AV_OFF_BAR + 256;             // [2][4][32] floats: per-quadrant row maxima
+constexpr int AV_OFF_PT = AV_OFF_RED + 2 * 4 * 32 * 4;   // cached page-table entries
+constexpr int AV_SMEM = AV_OFF_PT + AV_MAXPAGES * 4 + 1024;
+// TMEM columns: O [0, 256), row sums [256, 272), S double buffer [288, 320) and [320, 352)
+constexpr uint32_t AV_TM_O = 0, AV_TM_L = 256, AV_TM_S = 288;
+
+struct AvArgs {
+  const int32_t* page_table;  // [B, pt_stride]
+  int pt_stride;
+  const int32_t* seqlens;     // [B] tokens including the 4 drafts
+  int B, splits;
+  float scale_log2;
+  float* part_o;              // [B * 2 * splits][32][256] unnormalised
+  float* part_ml;             // [B * 2 * splits][2][32]: running maximum (log2 domain), row sum
+  int32_t* status;
+};
+
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// two e4m3 bytes (low 16 bits) -> two f16 (exact)
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t v) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(static_cast<unsigned short>(v)));
+  return r;
+}
+__device__ __forceinline__ unsigned short f2h_bits(float v) {
+  unsigned short r;
+  asm("cvt.rn.f16.f32 %0, %1;" : "=h"(r) : "f"(v));
+  return r;
+}
+// byte offset of (row, 16-byte chunk) inside a block of 128-byte rows with the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128(int row, int chunk) {
+  return static_cast<uint32_t>((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+constexpr uint32_t UMMA_AB_F16 = 0;
+
+__global__ void __launch_bounds__(AV_THREADS, 1)
+attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const __grid_constant__ CUtensorMap tmQ, const AvArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AV_OFF_BAR);
+  uint64_t* kfull = bars;          // [2] K page landed (TMA)
+  uint64_t* kempty = bars + 2;     // [2] S MMAs of the page done (commit)
+  uint64_t* vfull = bars + 4;      // [2] V page landed (TMA)
+  uint64_t* vempty = bars + 6;     // [2] conversion warps are done with the e4m3 page
+  uint64_t* sfull = bars + 8;      // [2] S^T tile complete in TMEM (commit)
+  uint64_t* sfree = bars + 10;     // [2] softmax warps have read it
+  uint64_t* pready = bars + 12;    // [2] P tile written (and O rescaled if needed)
+  uint64_t* pvdone = bars + 14;    // [2] P . V of the tile done (commit): P buffer, V16 and O are free again
+  uint64_t* v16ready = bars + 16;  // [1] f16 V tile written
+  uint64_t* sbar = bars + 17;      // [1] the softmax warps exchanged their row maxima
+  uint64_t* qfull = bars + 18;     // [1] Q rows landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* redm = reinterpret_cast<float*>(smem + AV_OFF_RED);
+  int32_t* spt = reinterpret_cast<int32_t*>(smem + AV_OFF_PT);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x;
+  const int s = cta % p.splits, grp = cta / p.splits, h = grp % AV_HKV, r = grp / AV_HKV;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kfull[i], 1);
+      mbar_init(&kempty[i], 1);
+      mbar_init(&vfull[i], 1);
+      mbar_init(&vempty[i], AV_CONV);
+      mbar_init(&sfull[i], 1);
+      mbar_init(&sfree[i], AV_SOFT);
+      mbar_init(&pready[i], AV_SOFT);
+      mbar_init(&pvdone[i], 1);
+    }
+    mbar_init(v16ready, AV_CONV);
+    mbar_init(sbar, AV_SOFT);
+    mbar_init(qfull, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmQ);
+  }
+  // the ones operand of the row-sum product: row 0 of each 64-key block is 1.0 (f16), rows 1..15 are zero
+  for (int i = threadIdx.x; i < AV_ONES / 4; i += AV_THREADS) {
+    const int byte = i * 4, blk = byte / 2048, row = (byte % 2048) / 128;
+    (void)blk;
+    reinterpret_cast<uint32_t*>(smem + AV_OFF_ONES)[i] = row == 0 ? 0x3c003c00u : 0u;  // swizzle permutes within a row only
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  pdl_wait();
+  pdl_launch();
+  // this CTA's pages: tokens [0, n) of the request, n = prefix + 4 drafts, split evenly by pages
+  const int n_tok = p.seqlens[r];
+  const int n_prefix = n_tok - AV_NT;
+  const int npages = (n_tok + AV_PAGE - 1) / AV_PAGE;
+  const int pg0 = static_cast<int>(static_cast<long long>(s) * npages / p.splits);
+  const int pg1 = static_cast<int>(static_cast<long long>(s + 1) * npages / p.splits);
+  const int ntiles = pg1 - pg0;
+  for (int i = threadIdx.x; i < ntiles && i < AV_MAXPAGES; i += AV_THREADS)
+    spt[i] = p.page_table[static_cast<size_t>(r) * p.pt_stride + pg0 + i];
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  auto page_of = [&](int i) -> int {
+    return i < AV_MAXPAGES ? spt[i] : p.page_table[static_cast<size_t>(r) * p.pt_stride + pg0 + i];
+  };
+
+  if (warp == 0) {
+    if (lane == 0 && ntiles > 0) {  // ---------------- TMA producer ----------------
+      mbar_expect_tx(qfull, AV_QBUF);
+      for (int t = 0; t < AV_NT; ++t)
+        for (int c = 0; c < 2; ++c)  // the 8 q heads of this kv head for token t: one 8-row swizzle group
+          tma_load_2d(smem + AV_OFF_Q + c * (AV_ROWS * 128) + t * 1024, &tmQ, c * 128,
+                      (r * AV_NT + t) * AV_HQ + h * AV_GQ, qfull);
+      for (int i = 0; i < ntiles; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        const int page = page_of(i);
+        if (!mbar_wait(&kempty[st], ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) break;
+        mbar_expect_tx(&kfull[st], AV_KTILE);
+        tma_load_2d(smem + AV_OFF_K + st * AV_KTILE, &tmK, 0, (page * AV_HKV + h) * AV_PAGE, &kfull[st]);
+        tma_load_2d(smem + AV_OFF_K + st * AV_KTILE + AV_KTILE / 2, &tmK, 128, (page * AV_HKV + h) * AV_PAGE, &kfull[st]);
+        if (!mbar_wait(&vempty[st], ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) break;
+        mbar_expect_tx(&vfull[st], AV_KTILE);
+        tma_load_2d(smem + AV_OFF_V8 + st * AV_KTILE, &tmV, 0, (page * AV_HKV + h) * AV_D, &vfull[st]);
+      }
+      // the kernel's last waits (every P . V commit) cover all copies issued here
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && ntiles > 0) {  // ---------------- MMA issuer ----------------
+      const uint32_t idesc_s = umma_idesc(UMMA_C_F32, UMMA_AB_E4M3, AV_ROWS);   // M = 128 keys, N = 32 rows
+      const uint32_t idesc_o = umma_idesc(UMMA_C_F32, UMMA_AB_F16, AV_D);       // M = 128 rows, N = 256 dims
+      const uint32_t idesc_l = umma_idesc(UMMA_C_F32, UMMA_AB_F16, 16);         // row sums
+      const uint32_t q_base = smem_u32(smem + AV_OFF_Q);
+      bool ok = mbar_wait(qfull, 0, abort_flag, p.status, ST_WAIT_FULL);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&kfull[st], ph, abort_flag, p.status, ST_WAIT_FULL)) return false;
+        if (j >= 2 && !mbar_wait(&sfree[st], ph ^ 1u, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) return false;
+        tc_fence_after();
+        const uint32_t k_base = smem_u32(smem + AV_OFF_K + st * AV_KTILE);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {  // 8 x 32 dims; dims 128..255 are the second swizzled block
+          const uint32_t off = (kk >> 2) * (AV_KTILE / 2) + (kk & 3) * 32;
+          const uint32_t qoff = (kk >> 2) * (AV_ROWS * 128) + (kk & 3) * 32;
+          tc_mma_f8(tmem_base + AV_TM_S + st * 32, umma_desc_sw128(k_base + off), umma_desc_sw128(q_base + qoff), idesc_s,
+                    kk != 0);
+        }
+        tc_commit(&kempty[st]);
+        tc_commit(&sfull[st]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int i = 0; ok && i < ntiles; ++i) {
+        if (i + 1 < ntiles && !issue_s(i + 1)) break;
+        const int b = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        if (!mbar_wait(&pready[b], ph, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
+        if (!mbar_wait(v16ready, i & 1, abort_flag, p.status, ST_WAIT_FULL)) break;
+        tc_fence_after();
+        const uint32_t p_base = smem_u32(smem + AV_OFF_P + b * AV_PBUF);
+        const uint32_t v_base = smem_u32(smem + AV_OFF_V16);
+        const uint32_t o_base = smem_u32(smem + AV_OFF_ONES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {  // 8 x 16 keys; keys 64..127 are the second block of each operand
+          const uint64_t da = umma_desc_sw128(p_base + (kk >> 2) * (AV_ROWS * 128) + (kk & 3) * 32);
+          tc_mma_f16(tmem_base + AV_TM_O, da, umma_desc_sw128(v_base + (kk >> 2) * (AV_D * 128) + (kk & 3) * 32), idesc_o,
+                     (i | kk) != 0);
+          tc_mma_f16(tmem_base + AV_TM_L, da, umma_desc_sw128(o_base + (kk >> 2) * 2048 + (kk & 3) * 32), idesc_l,
+                     (i | kk) != 0);
+        }
+        tc_commit(&pvdone[b]);
+      }
+    }
+  } else if (warp < 2 + AV_SOFT) {
+    // ---------------- softmax: warps 2..9.  TMEM lane quadrant q = warp % 4 holds keys 32 q .. 32 q + 31 of the
+    // page; the two warps of a quadrant take 16 of the 32 rows each.  Every warp keeps the running maximum of
+    // all 32 rows (row j in lane j; identical in all warps: they read the same exchanged maxima) ----------------
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    const int key_in_page = q * 32 + lane;
+    float m_run = -INFINITY;  // lane j: running maximum of row j (log2 domain)
+    bool ok = true;
+    for (int i = 0; ok && i < ntiles; ++i) {
+      const int b = i & 1;
+      const uint32_t ph = (i >> 1) & 1;
+      if (!mbar_wait(&sfull[b], ph, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
+      tc_fence_after();
+      uint32_t raw[16];
+      tmem_ld16(tmem_base + AV_TM_S + b * 32 + half * 16 + (static_cast<uint32_t>(q * 32) << 16), raw);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sfree[b]);
+      // scores of this thread's key against rows half*16 .. +15 (row = token * 8 + head); causal limit per token
+      const int key = (pg0 + i) * AV_PAGE + key_in_page;
+      float sc[16];
+      uint32_t mine = 0u;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int tok = (half * 16 + j) >> 3;
+        const bool valid = key <= n_prefix + tok;
+        sc[j] = valid ? __uint_as_float(raw[j]) * p.scale_log2 : -INFINITY;
+        // order-preserving integer image of the score (NaN scores of garbage keys were masked above)
+        uint32_t k = __float_as_uint(sc[j]);
+        k = (k & 0x80000000u) ? ~k : (k | 0x80000000u);
+        const uint32_t mx = __reduce_max_sync(FULL_MASK, k);
+        if (lane == j) mine = mx;
+      }
+      if (lane < 16) {
+        const uint32_t f = (mine & 0x80000000u) ? (mine & 0x7fffffffu) : ~mine;
+        redm[(b * 4 + q) * 32 + half * 16 + lane] = __uint_as_float(f);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sbar);
+      if (!mbar_wait(sbar, i & 1, abort_flag, p.status, ST_WAIT_STATE)) break;
+      // lane j: tile maximum of row j over the four quadrants, then the lazy update of the running maximum
+      const float tm = fmaxf(fmaxf(redm[(b * 4 + 0) * 32 + lane], redm[(b * 4 + 1) * 32 + lane]),
+                             fmaxf(redm[(b * 4 + 2) * 32 + lane], redm[(b * 4 + 3) * 32 + lane]));
+      const float m_new = tm > m_run + AV_RESCALE_LOG2 ? tm : m_run;  // -inf + 8 = -inf: the first finite maximum is taken
+      const float alpha = (m_new == m_run) ? 1.f : exp2f(m_run - m_new);  // m_run = -inf gives 0
+      const bool move = __any_sync(FULL_MASK, m_new != m_run);
+      m_run = m_new;
+      // the P buffer (and O, for a rescale) must be free: P . V of tile i - 2 (same buffer) / i - 1 done
+      if (i >= 2 && !mbar_wait(&pvdone[b], ph ^ 1u, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) break;
+      if (move && i > 0 && q == 0) {
+        // rows sit on TMEM lanes 0..31 of O: the quadrant-0 warps scale their half of the 256 columns (and the
+        // row sums) by alpha; the first tile overwrites O instead
+        if (!mbar_wait(&pvdone[b ^ 1], ((i - 1) >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        for (int c = 0; c < 8 + (half == 0 ? 1 : 0); ++c) {
+          const uint32_t col = c < 8 ? AV_TM_O + half * 128 + c * 16 : AV_TM_L;
+          uint32_t v[16];
+          tmem_ld16(tmem_base + col, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+          tmem_st16(tmem_base + col, v);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      // P^T -> shared memory as the A operand [row][key], f16, 128-byte swizzle
+      uint8_t* pb = smem + AV_OFF_P + b * AV_PBUF + (key_in_page >> 6) * (AV_ROWS * 128);
+      const int kb = (key_in_page & 63) * 2;  // byte of this key inside the 128-byte row
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int row = half * 16 + j;
+        const float mr = __shfl_sync(FULL_MASK, m_run, row);
+        const float pv = sc[j] == -INFINITY ? 0.f : exp2f(sc[j] - mr);
+        *reinterpret_cast<unsigned short*>(pb + sw128(row, kb >> 4) + (kb & 15)) = f2h_bits(pv);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pready[b]);
+    }
+    // ---------------- epilogue: the quadrant-0 warps write this split's partial (rows on lanes 0..31) ----------------
+    if (ok && q == 0) {
+      float* po = p.part_o + static_cast<size_t>(cta) * AV_ROWS * AV_D + static_cast<size_t>(lane) * AV_D + half * 128;
+      float* pml = p.part_ml + static_cast<size_t>(cta) * 2 * AV_ROWS;
+      if (ntiles == 0) {
+        for (int c = 0; c < 128; c += 4) *reinterpret_cast<float4*>(po + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (half == 0) {
+          pml[lane] = -INFINITY;
+          pml[AV_ROWS + lane] = 0.f;
+        }
+      } else {
+        const int last = ntiles - 1;
+        if (mbar_wait(&pvdone[last & 1], (last >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL)) {
+          tc_fence_after();
+          for (int c = 0; c < 8; ++c) {
+            uint32_t v[16];
+            tmem_ld16(tmem_base + AV_TM_O + half * 128 + c * 16, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<float4*>(po + c * 16 + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                         __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+          }
+          if (half == 0) {
+            uint32_t v[16];
+            tmem_ld16(tmem_base + AV_TM_L, v);
+            tmem_ld_wait();
+            pml[lane] = m_run;
+            pml[AV_ROWS + lane] = __uint_as_float(v[0]);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- V conversion: warps 10..13.  e4m3 page [256 dims][128 keys] -> f16, same orientation, as two
+    // 64-key blocks; 16 keys (one 16-byte chunk) per step ----------------
+    const int ct = (warp - 2 - AV_SOFT) * 32 + lane;  // 0..127
+    for (int i = 0; i < ntiles; ++i) {
+      const int st = i & 1;
+      const uint32_t ph = (i >> 1) & 1;
+      if (!mbar_wait(&vfull[st], ph, abort_flag, p.status, ST_WAIT_FULL)) break;
+      if (i >= 1 && !mbar_wait(&pvdone[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) break;
+      const uint8_t* src = smem + AV_OFF_V8 + st * AV_KTILE;
+      uint8_t* dst = smem + AV_OFF_V16;
+      // keys past the request's last token may hold stale bytes (any bit pattern, NaN included): zero them so that
+      // a zero probability times such a value cannot poison the sums
+      const int keys_valid = min(AV_PAGE, n_tok - (pg0 + i) * AV_PAGE);
+      for (int u = ct; u < AV_D * 8; u += AV_CONV * 32) {
+        const int d = u >> 3, c = u & 7;  // dim row, 16-key chunk
+        uint4 v = *reinterpret_cast<const uint4*>(src + sw128(d, c));
+        const int k0 = c * 16;
+        if (k0 + 16 > keys_valid) {
+          uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            if (k0 + e >= keys_valid) w[e >> 2] &= ~(0xffu << ((e & 3) * 8));
+          v = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        uint4 lo, hi;
+        lo.x = e4m3x2_to_f16x2(v.x & 0xffffu);
+        lo.y = e4m3x2_to_f16x2(v.x >> 16);
+        lo.z = e4m3x2_to_f16x2(v.y & 0xffffu);
+        lo.w = e4m3x2_to_f16x2(v.y >> 16);
+        hi.x = e4m3x2_to_f16x2(v.z & 0xffffu);
+        hi.y = e4m3x2_to_f16x2(v.z >> 16);
+        hi.z = e4m3x2_to_f16x2(v.w & 0xffffu);
+        hi.w = e4m3x2_to_f16x2(v.w >> 16);
+        uint8_t* blk = dst + (c >> 2) * (AV_D * 128);  // keys 0..63 / 64..127
+        *reinterpret_cast<uint4*>(blk + sw128(d, (c & 3) * 2)) = lo;
+        *reinterpret_cast<uint4*>(blk + sw128(d, (c & 3) * 2 + 1)) = hi;
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(v16ready);
+        mbar_arrive(&vempty[st]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// The 4 new tokens of every request go into its pages before the main kernel runs: K rows as they are, V
+// transposed (one byte per dim).  One CTA per (request, token), 256 threads = dims; both kv heads.
+__global__ void __launch_bounds__(256) kv_append_kernel(const uint8_t* __restrict__ k_new, const uint8_t* __restrict__ v_new,
+                                                        const int32_t* __restrict__ page_table, int pt_stride,
+                                                        const int32_t* __restrict__ seqlens, uint8_t* __restrict__ kcache,
+                                                        uint8_t* __restrict__ vcache) {
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.x / AV_NT, t = blockIdx.x % AV_NT, d = threadIdx.x;
+  const int pos = seqlens[r] - AV_NT + t;
+  if (pos < 0) return;
+  const int page = page_table[static_cast<size_t>(r) * pt_stride + pos / AV_PAGE], in_page = pos % AV_PAGE;
+  const size_t tok = static_cast<size_t>(r) * AV_NT + t;
+  for (int h = 0; h < AV_HKV; ++h) {
+    const size_t ph = static_cast<size_t>(page) * AV_HKV + h;
+    kcache[(ph * AV_PAGE + in_page) * AV_D + d] = k_new[(tok * AV_HKV + h) * AV_D + d];
+    vcache[(ph * AV_D + d) * AV_PAGE + in_page] = v_new[(tok * AV_HKV + h) * AV_D + d];
+  }
+}
+
+// Merge of the split partials and the output gate: per (request, kv head, row) the splits are added in split order
+// with weights 2^(m_s - M); out = bf16(bf16(o / l) * sigmoid(gate)).  One CTA per (group, token), 256 threads = dims.
+__global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                           const bf16* __restrict__ gate, int splits,
+                                                           bf16* __restrict__ out) {
+  pdl_wait();
+  pdl_launch();
+  const int grp = blockIdx.x / AV_NT, t = blockIdx.x % AV_NT, d = threadIdx.x;
+  const int h = grp % AV_HKV, r = grp / AV_HKV;
+  for (int g = 0; g < AV_GQ; ++g) {
+    const int row = t * AV_GQ + g;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(static_cast<size_t>(grp) * splits + s) * 2 * AV_ROWS + row]);
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const size_t c = static_cast<size_t>(grp) * splits + s;
+      const float m = part_ml[c * 2 * AV_ROWS + row];
+      const float w = m == -INFINITY ? 0.f : exp2f(m - M);
+      num = fmaf(part_o[(c * AV_ROWS + row) * AV_D + d], w, num);
+      den = fmaf(part_ml[c * 2 * AV_ROWS + AV_ROWS + row], w, den);
+    }
+    const size_t o = (static_cast<size_t>(r) * AV_NT + t) * (AV_HQ * AV_D) + static_cast<size_t>(h * AV_GQ + g) * AV_D + d;
+    const float gv = bf2f(gate[o]);
+    out[o] = f2bf(rbf(num / den) * (1.f / (1.f + __expf(-gv))));
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_attn_verify_splits(int B) {
+  if (B <= 0) return 0;
+  int s = sm_count() / (B * AV_HKV);
+  return s < 1 ? 1 : (s > 16 ? 16 : s);
+}
+
+extern "C" size_t b200_attn_verify_workspace_bytes(int B, int splits) {
+  if (B <= 0 || splits <= 0) return 0;
+  const size_t ctas = static_cast<size_t>(B) * AV_HKV * splits;
+  return ctas * AV_ROWS * AV_D * 4 + ctas * 2 * AV_ROWS * 4;
+}
+
+extern "C" int b200_attn_verify(const void* q, const void* gate, const void* k_new, const void* v_new, void* kcache,
+                                void* vcache, int num_pages, const int32_t* page_table, int pt_stride,
+                                const int32_t* seqlens, int B, float scale, int splits, void* out, void* ws,
+                                size_t ws_bytes, int32_t* status, void* stream) {
+  if (!q || !gate || !k_new || !v_new || !kcache || !vcache || !page_table || !seqlens || !out || !ws)
+    return fail(B200_E_ARG, "b200_attn_verify: null pointer");
+  if (B <= 0 || num_pages <= 0 || pt_stride <= 0 || splits <= 0 || splits > 64)
+    return fail(B200_E_ARG, "b200_attn_verify: need B, num_pages, pt_stride >= 1 and 1 <= splits <= 64 (B=%d splits=%d)", B,
+                splits);
+  if (ws_bytes < b200_attn_verify_workspace_bytes(B, splits))
+    return fail(B200_E_WS, "b200_attn_verify: workspace %zu < %zu bytes", ws_bytes,
+                b200_attn_verify_workspace_bytes(B, splits));
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kcache) | reinterpret_cast<uintptr_t>(vcache) |
+       reinterpret_cast<uintptr_t>(ws)) & 15)
+    return fail(B200_E_ALIGN, "b200_attn_verify: q, caches and workspace must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tmK, tmV, tmQ;
+  int rc;
+  if ((rc = make_tmap_bytes_2d(&tmK, kcache, static_cast<uint64_t>(num_pages) * AV_HKV * AV_PAGE, AV_D, 128, "k cache")))
+    return rc;
+  if ((rc = make_tmap_bytes_2d(&tmV, vcache, static_cast<uint64_t>(num_pages) * AV_HKV * AV_D, AV_PAGE, 256, "v cache")))
+    return rc;
+  if ((rc = make_tmap_bytes_2d(&tmQ, q, static_cast<uint64_t>(B) * AV_NT * AV_HQ, AV_D, 8, "q"))) return rc;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaFuncSetAttribute(attn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AV_SMEM);
+    attr_done[dev] = true;
+  }
+  launch_k(kv_append_kernel, dim3(B * AV_NT), dim3(256), 0, st, static_cast<const uint8_t*>(k_new),
+           static_cast<const uint8_t*>(v_new), page_table, pt_stride, seqlens, static_cast<uint8_t*>(kcache),
+           static_cast<uint8_t*>(vcache));
+  AvArgs a{};
+  a.page_table = page_table;
+  a.pt_stride = pt_stride;
+  a.seqlens = seqlens;
+  a.B = B;
+  a.splits = splits;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.part_o = static_cast<float*>(ws);
+  a.part_ml = a.part_o + static_cast<size_t>(B) * AV_HKV * splits * AV_ROWS * AV_D;
+  a.status = status;
+  launch_k(attn_verify_kernel, dim3(B * AV_HKV * splits), dim3(AV_THREADS), AV_SMEM, st, tmK, tmV, tmQ, a);
+  launch_k(attn_combine_kernel, dim3(B * AV_HKV * AV_NT), dim3(256), 0, st, static_cast<const float*>(a.part_o),
+           static_cast<const float*>(a.part_ml), static_cast<const bf16*>(gate), splits, static_cast<bf16*>(out));
+  return launch_status("b200_attn_verify");
+}

@@ -76,6 +76,11 @@ int sm_count() {
   return cached[dev];
 }
 
+bool pdl_enabled() {
+  static const bool on = getenv("B200_NO_PDL") == nullptr;
+  return on;
+}
+
 }  // namespace b200
 
 extern "C" int b200_abi_version(void) { return B200_ABI_VERSION; }

@@ -8,6 +8,7 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "../../include/b200nodes.h"
 
@@ -53,5 +54,29 @@ int make_tmap_f32_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
 void b200_quant_rows_f8_launch(const void* x, int T, int H, uint8_t* xq, float* xs, cudaStream_t st);
 
 int sm_count();  // SMs of the current device (cached per device)
+
+// Whether kernels are launched with programmatic stream serialization (on unless B200_NO_PDL is set in the
+// environment).  Every kernel of the library then starts while its predecessor in the stream drains: it does
+// its set-up, executes griddepcontrol.wait before the first access to memory that the predecessor writes
+// (and before its own first global write), and only then griddepcontrol.launch_dependents, so a kernel's
+// part before the wait may read what kernels two or more launches back have written (routing lists,
+// for the GEMMs' weight prefetch).
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                            Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 }  // namespace b200

@@ -50,6 +50,8 @@ __global__ void __launch_bounds__(256) quant_permute_i8_kernel(const bf16* __res
   __shared__ float red[8];
   __shared__ int rows[40];
   const int t = blockIdx.x, tid = threadIdx.x;
+  pdl_wait();
+  pdl_launch();
   if (tid < K) rows[tid] = row_of_pair[t * K + tid];
   if (tid == K) rows[K] = with_shared ? T * K + t : -1;
   const bf16* xr = x + static_cast<size_t>(t) * H;
@@ -85,6 +87,8 @@ __global__ void __launch_bounds__(256) quant_rows_i8_kernel(const bf16* __restri
                                                             const int32_t* __restrict__ slot_of_row,
                                                             int8_t* __restrict__ hq, float* __restrict__ hs) {
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  pdl_wait();
+  pdl_launch();
   if (row >= rows || slot_of_row[row] < 0) return;
   const bf16* hr = h + static_cast<size_t>(row) * I;
   float amax = 0.f;
@@ -238,6 +242,29 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
+      // every TMA instruction costs the issuing thread ~80 ns, so the token rows come in as few boxes as
+      // possible: 16-row boxes up to 32 rows, one 64-row box (+ up to two 16-row boxes), or one 128-row
+      // box.  Rows past the block belong to the next expert or are zero-filled past the end of the
+      // tensor; the MMA's N ignores them.
+      auto big_of = [](int nb16) { return nb16 > 6 ? 8 : (nb16 > 2 ? 4 : 0); };  // 16-row units in the large box
+      auto tok_units = [&](int nb16) { const int big = big_of(nb16); return nb16 > big ? nb16 : big; };
+      // The weights do not depend on the kernels before this one: the first stages' weight tiles are requested
+      // before the dependency wait, the token rows of the same stages after it.
+      int pre = 0;
+      for (int tile = blockIdx.x; pre < C::STAGES && tile < ntiles; tile += gridDim.x) {
+        int e, row0, n, mt;
+        if (!decode(tile, e, row0, n, mt)) continue;
+        const CUtensorMap* mapW = (e == p.E_local) ? &tmWsh : &tmW;
+        const int wrow = (e == p.E_local ? 0 : e * p.w_rows) + mt * 128;
+        for (int ks = 0; ks < p.ksteps && pre < C::STAGES; ++ks, ++pre) {
+          uint8_t* sA = smem + pre * C::STAGE;
+          mbar_expect_tx(&full[pre], C::NA * TILE_BYTES + tok_units((n + 15) >> 4) * 2048);
+          tma_load_2d(sA, mapW, ks * 128, wrow, &full[pre]);
+          if (UP) tma_load_2d(sA + TILE_BYTES, mapW, ks * 128, wrow + p.I, &full[pre]);
+        }
+      }
+      pdl_wait();
+      pdl_launch();
       for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
         int e, row0, n, mt;
         if (!decode(tile, e, row0, n, mt)) continue;
@@ -245,25 +272,21 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const CUtensorMap* mapW = (e == p.E_local) ? &tmWsh : &tmW;
         const int wrow = (e == p.E_local ? 0 : e * p.w_rows) + mt * 128;
         for (int ks = 0; ks < p.ksteps; ++ks) {
-          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) {
-            ok = false;
-            break;
-          }
           uint8_t* sA = smem + stage * C::STAGE;
           uint8_t* sB = sA + C::NA * TILE_BYTES;
-          // every TMA instruction costs the issuing thread ~80 ns, so the token rows come in as few boxes as
-          // possible: 16-row boxes up to 32 rows, one 64-row box (+ up to two 16-row boxes), or one 128-row
-          // box.  Rows past the block belong to the next expert or are zero-filled past the end of the
-          // tensor; the MMA's N ignores them.
-          const int big = nb16 > 6 ? 8 : (nb16 > 2 ? 4 : 0);       // 16-row units covered by the large box
-          const int small = nb16 > big ? nb16 - big : 0;            // 16-row boxes after it
-          mbar_expect_tx(&full[stage], C::NA * TILE_BYTES + (big + small) * 2048);
-          tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
-          if (UP) tma_load_2d(sA + TILE_BYTES, mapW, ks * 128, wrow + p.I, &full[stage]);
+          const int big = big_of(nb16);
+          if (issued >= pre) {
+            if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&full[stage], C::NA * TILE_BYTES + tok_units(nb16) * 2048);
+            tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
+            if (UP) tma_load_2d(sA + TILE_BYTES, mapW, ks * 128, wrow + p.I, &full[stage]);
+          }
           if (big == 8) tma_load_2d(sB, &tmX128, ks * 128, row0, &full[stage]);
           if (big == 4) tma_load_2d(sB, &tmX64, ks * 128, row0, &full[stage]);
-          for (int b = big; b < big + small; ++b)
-            tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
+          for (int b = big; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
           ++issued;
           if (++stage == C::STAGES) {
             stage = 0;
@@ -289,6 +312,8 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    pdl_wait();
+    pdl_launch();
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -375,6 +400,8 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     };
     Pre pre;
+    pdl_wait();
+    pdl_launch();
     fetch(blockIdx.x, pre);
     for (int tile = blockIdx.x; tile < ntiles; tile += step) {
       int e, row0, n, mt;
@@ -497,6 +524,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict
                                                           bf16* __restrict__ out) {
   __shared__ float red[8];
   const int t = blockIdx.x, tid = threadIdx.x;
+  pdl_wait();
+  pdl_launch();
   bf16* orow = out + static_cast<size_t>(t) * H;
   if (pos != nullptr && pos[t] == 0) {
     for (int c = tid * 8; c < H; c += 2048) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
@@ -642,7 +671,8 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
 
   if (stages == 0) stages = 15;
   if (stages & B200_MOE_STAGE_QUANT)
-    quant_permute_i8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, K, L.row_of_pair, shared ? 1 : 0, xq, xs);
+    launch_k(quant_permute_i8_kernel, dim3(T), dim3(256), 0, st, static_cast<const bf16*>(x), T, H, K, L.row_of_pair,
+             shared ? 1 : 0, xq, xs);
 
   GemmArgs a{};
   a.L = L;
@@ -663,10 +693,16 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
   a.dbg_acc = dbg_acc13;
   a.dbg_h = static_cast<bf16*>(dbg_h);
   if (stages & B200_MOE_STAGE_UP)
-    moe_gemm_i8_kernel<true><<<grid, GEMM_THREADS, GemmCfg<true>::SMEM, st>>>(tmW13, tmSh13, tmXq, tmXq64, tmXq128, a);
+    // the kernel reads the routing lists before its dependency wait: only safe to start early when the kernel
+    // right before it in the stream is this call's own quantiser (which itself waited for the lists)
+    if (stages & B200_MOE_STAGE_QUANT)
+      launch_k(moe_gemm_i8_kernel<true>, dim3(grid), dim3(GEMM_THREADS), GemmCfg<true>::SMEM, st, tmW13, tmSh13, tmXq,
+               tmXq64, tmXq128, a);
+    else
+      moe_gemm_i8_kernel<true><<<grid, GEMM_THREADS, GemmCfg<true>::SMEM, st>>>(tmW13, tmSh13, tmXq, tmXq64, tmXq128, a);
 
   if (stages & B200_MOE_STAGE_HQUANT)
-    quant_rows_i8_kernel<<<(rows + 7) / 8, 256, 0, st>>>(h, rows, I, L.slot_of_row, hq, hs);
+    launch_k(quant_rows_i8_kernel, dim3((rows + 7) / 8), dim3(256), 0, st, h, rows, I, L.slot_of_row, hq, hs);
 
   a.mtiles = H / 128;
   a.ksteps = I / 128;
@@ -685,7 +721,11 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
   ep_world &= 0xff;
   for (int r = 0; r < 8; ++r) a.ep_cache[r] = (peer_cache && r < ep_world) ? static_cast<bf16*>(peer_cache[r]) : nullptr;
   if (stages & B200_MOE_STAGE_DOWN)
-    moe_gemm_i8_kernel<false><<<grid, GEMM_THREADS, GemmCfg<false>::SMEM, st>>>(tmW2, tmSh2, tmHq, tmHq64, tmHq128, a);
+    if (stages & B200_MOE_STAGE_HQUANT)
+      launch_k(moe_gemm_i8_kernel<false>, dim3(grid), dim3(GEMM_THREADS), GemmCfg<false>::SMEM, st, tmW2, tmSh2, tmHq,
+               tmHq64, tmHq128, a);
+    else
+      moe_gemm_i8_kernel<false><<<grid, GEMM_THREADS, GemmCfg<false>::SMEM, st>>>(tmW2, tmSh2, tmHq, tmHq64, tmHq128, a);
   return launch_status("b200_moe_w8a8");
 }
 
@@ -694,8 +734,7 @@ extern "C" int b200_moe_combine(const void* cache, const void* x, const void* ga
   if (!cache || !out || (gate_w && !x)) return fail(B200_E_ARG, "b200_moe_combine: null pointer");
   if (T < 0 || H <= 0 || H % 8 || K <= 0) return fail(B200_E_ARG, "b200_moe_combine: need H %% 8 == 0 (H=%d K=%d)", H, K);
   if (T == 0) return 0;
-  moe_combine_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const bf16*>(cache), static_cast<const bf16*>(x), static_cast<const bf16*>(gate_w), pos, T, H, K,
-      static_cast<bf16*>(out));
+  launch_k(moe_combine_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const bf16*>(cache),
+           static_cast<const bf16*>(x), static_cast<const bf16*>(gate_w), pos, T, H, K, static_cast<bf16*>(out));
   return launch_status("b200_moe_combine");
 }

@@ -32,6 +32,8 @@ __global__ void __launch_bounds__(RT_THREADS) router_partials_kernel(const bf16*
   float* ws = rt_smem + RT_TOK * RT_PITCH;   // [64][132]
   const int tid = threadIdx.x;
   const int t0 = blockIdx.x * RT_TOK, e0 = blockIdx.y * RT_EXP, s = blockIdx.z;
+  pdl_wait();
+  pdl_launch();
   // stage: 64 rows x 128 k of x (bf16 -> fp32) and of wr
   for (int i = tid; i < RT_TOK * (RT_SLICE / 8); i += RT_THREADS) {
     const int r = i >> 4, c = (i & 15) * 8;
@@ -110,6 +112,8 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
   __shared__ int c_id[TK_WARPS * 32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x;
+  pdl_wait();
+  pdl_launch();
   const int EW = E / TK_WARPS;  // experts of this warp; entry j of lane l exists when l + 32 j < EW
   const int ebase = warp * EW;
   float xv[PL];
@@ -262,6 +266,8 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
                                                                   int e_lo, int E_local, int block_rows,
                                                                   int with_shared, int max_blocks, MoeLists L) {
   extern __shared__ int lists_smem[];
+  pdl_wait();
+  pdl_launch();
   const int P = T * K;
   const int E1 = E_local + 1;
   int* cnt = lists_smem;                   // [E1]   rows per expert
@@ -424,17 +430,17 @@ extern "C" int b200_router(const void* x, const float* wr, const float* bias, in
   float* part = static_cast<float*>(scratch);
   const int nslices = H / RT_SLICE;
   dim3 grid((T + RT_TOK - 1) / RT_TOK, E / RT_EXP, nslices);
-  router_partials_kernel<<<grid, RT_THREADS, RT_SMEM, st>>>(static_cast<const bf16*>(x), wr, T, H, E, part);
+  launch_k(router_partials_kernel, grid, dim3(RT_THREADS), RT_SMEM, st, static_cast<const bf16*>(x), wr, T, H, E, part);
   const int rb = flags & 1;
   const int pl = (E + 127) / 128;
   if (pl <= 1)
-    router_topk_kernel<1><<<T, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
+    launch_k(router_topk_kernel<1>, dim3(T), dim3(128), 0, st, part, nslices, bias, T, E, K, rb, logits, ids, wts);
   else if (pl <= 2)
-    router_topk_kernel<2><<<T, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
+    launch_k(router_topk_kernel<2>, dim3(T), dim3(128), 0, st, part, nslices, bias, T, E, K, rb, logits, ids, wts);
   else if (pl <= 4)
-    router_topk_kernel<4><<<T, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
+    launch_k(router_topk_kernel<4>, dim3(T), dim3(128), 0, st, part, nslices, bias, T, E, K, rb, logits, ids, wts);
   else
-    router_topk_kernel<8><<<T, 128, 0, st>>>(part, nslices, bias, T, E, K, rb, logits, ids, wts);
+    launch_k(router_topk_kernel<8>, dim3(T), dim3(128), 0, st, part, nslices, bias, T, E, K, rb, logits, ids, wts);
   return launch_status("b200_router");
 }
 
@@ -519,7 +525,7 @@ extern "C" int b200_moe_build_lists(const int32_t* ids, const float* wts, const 
     cudaFuncSetAttribute(moe_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     attr_done[dev] = true;
   }
-  moe_lists_kernel<<<1, LISTS_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(
-      ids, wts, pos, T, K, e_lo, E_local, block_rows, with_shared, b200_moe_max_blocks(T, K, E_local, block_rows), L);
+  launch_k(moe_lists_kernel, dim3(1), dim3(LISTS_THREADS), smem, static_cast<cudaStream_t>(stream), ids, wts, pos, T, K,
+           e_lo, E_local, block_rows, with_shared, static_cast<int>(b200_moe_max_blocks(T, K, E_local, block_rows)), L);
   return launch_status("b200_moe_build_lists");
 }

@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import B200Error, MoeLists, MoeWeights, check
 
-__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_w8a8_ep", "moe_fp8", "moe_combine", "attn_front", "dense_fp8", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
+__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_w8a8_ep", "moe_fp8", "moe_combine", "attn_front", "attn_verify", "dense_fp8", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
            "new_status", "read_status", "B200Error"]
 
 
@@ -244,6 +244,36 @@ def attn_front(x, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, eps=1e-6, out_
                                      cos_sin.shape[0], float(eps), 1 if out_fp8 else 0, _p(q), _p(gate), _p(k), _p(v),
                                      _p(ws), ws.numel(), _p(status), _stream()), "b200_attn_front")
     return q, gate, k, v
+
+
+def attn_verify(q, gate, k_new, v_new, kcache, vcache, page_table, seqlens, scale=None, splits=None, out=None, ws=None,
+                status=None):
+    """Attention verify core over paged e4m3 KV (reference: qk_attn_verify.attn_verify_fused).  q uint8 [4B,16,256],
+    gate bf16 [4B,16,256], k_new / v_new uint8 [4B,2,256]; kcache uint8 [P,2,128,256], vcache uint8 [P,2,256,128]
+    (both updated in place with the new tokens); page_table int32 [B,n]; seqlens int32 [B] including the 4
+    drafts.  Returns out bf16 [4B, 4096]."""
+    _need(q, torch.uint8, "q", 3)
+    _need(gate, torch.bfloat16, "gate", 3)
+    _need(k_new, torch.uint8, "k_new", 3)
+    _need(v_new, torch.uint8, "v_new", 3)
+    _need(kcache, torch.uint8, "kcache", 4)
+    _need(vcache, torch.uint8, "vcache", 4)
+    _need(page_table, torch.int32, "page_table", 2)
+    _need(seqlens, torch.int32, "seqlens", 1)
+    B = seqlens.shape[0]
+    if scale is None:
+        scale = 1.0 / 16.0
+    if splits is None:
+        splits = _lib.lib().b200_attn_verify_splits(B)
+    if out is None:
+        out = torch.empty(4 * B, 4096, dtype=torch.bfloat16, device=q.device)
+    if ws is None:
+        n = _lib.lib().b200_attn_verify_workspace_bytes(B, splits)
+        ws = torch.empty(n, dtype=torch.uint8, device=q.device)
+    check(_lib.lib().b200_attn_verify(_p(q), _p(gate), _p(k_new), _p(v_new), _p(kcache), _p(vcache), kcache.shape[0],
+                                      _p(page_table), page_table.shape[1], _p(seqlens), B, float(scale), int(splits),
+                                      _p(out), _p(ws), ws.numel(), _p(status), _stream()), "b200_attn_verify")
+    return out
 
 
 def dense_fp8(x, w, w_s, out=None, ws=None, status=None):

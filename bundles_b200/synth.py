@@ -145,3 +145,26 @@ def lmhead(seed=SEEDS["step"], T=64, V=151936, H=2048):
     w[:V] = torch.randn(V, H, generator=g) * 0.02
     wq, ws = quant_fp8_blocks(w)
     return dict(x=torch.randn(T, H, generator=g).to(torch.bfloat16), w=wq[:V].contiguous(), w_s=ws)
+
+
+def attn_verify(seed=SEEDS["step"], B=64, ctx=8192, ragged=False, device="cpu"):
+    """Config: attention verify over a paged e4m3 KV cache (128-token pages; K [P,2,128,256], V [P,2,256,128]).
+    Every request holds `ctx` tokens including its 4 drafts (`ragged`: lengths drawn from [ctx/2, ctx]); cache,
+    q, k_new, v_new are e4m3 of N(0,1), gate bf16 N(0,1); pages are handed out in a seeded random order, with a
+    few spare pages that no request owns."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    if ragged:
+        seqlens = torch.randint(max(4, ctx // 2), ctx + 1, (B,), generator=g, device=device, dtype=torch.int32)
+    else:
+        seqlens = torch.full((B,), ctx, dtype=torch.int32, device=device)
+    per = (ctx + 127) // 128
+    P = B * per + 3
+    perm = torch.randperm(P, generator=g, device=device).to(torch.int32)
+    page_table = perm[:B * per].reshape(B, per).contiguous()
+
+    def e4(*shape):
+        return torch.randn(*shape, generator=g, device=device).to(torch.float8_e4m3fn).view(torch.uint8)
+
+    return dict(q=e4(4 * B, 16, 256), gate=torch.randn(4 * B, 16, 256, generator=g, device=device).to(torch.bfloat16),
+                k_new=e4(4 * B, 2, 256), v_new=e4(4 * B, 2, 256), kcache=e4(P, 2, 128, 256), vcache=e4(P, 2, 256, 128),
+                page_table=page_table, seqlens=seqlens)

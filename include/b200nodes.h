@@ -204,6 +204,33 @@ int b200_gdn_verify(const void* mixed, const void* z, const void* a, const void*
                     void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Attention verify core.  Replaces qk_attn_verify.attn_verify_fused (attn_fused.py:110-124;
+ * attn_verify_kernel, qk_attn_verify.cu:354-744) behind the projection front above: per request
+ * the 4 draft tokens x 16 q heads attend to the request's e4m3 KV cache and causally to each
+ * other (new token t sees new tokens <= t, qk_attn_verify.cu:521); S = q . k from e4m3 operands
+ * with fp32 accumulation, times `scale`; online softmax in the log2 domain whose running maximum
+ * moves only when a tile exceeds it by more than 8 (:210,264-267); P rounded to f16 before P . V
+ * (:297-301); KV range split over CTAs and merged by an ordered sum (:690-737);
+ * out = bf16(bf16(o / l) * sigmoid(gate)) (:559-562).  The new tokens' K and V rows are written
+ * into the cache first (the reference does it at out_cache_loc, :452-466).
+ *
+ * Cache layout (chosen for this GPU; the reference reads 1-token pages through a per-token table):
+ * pages of 128 tokens; kcache e4m3 [num_pages][2 kv heads][128 keys][256 dims]; vcache e4m3
+ * [num_pages][2][256 dims][128 keys] (dim-major).  page_table int32 [B, pt_stride]: page of tokens
+ * 128 i .. 128 i + 127 of request b; seqlens int32 [B]: tokens of the request INCLUDING the 4
+ * drafts (seqlens >= 4; the drafts occupy positions seqlens-4 .. seqlens-1).
+ *   q e4m3 [4B,16,256], gate bf16 [4B,16,256], k_new, v_new e4m3 [4B,2,256] (b200_attn_front with
+ *   out_fp8 = 1); out bf16 [4B, 4096]; splits: CTAs per (request, kv head), 1..64
+ *   (b200_attn_verify_splits(B) fills the GPU); ws: b200_attn_verify_workspace_bytes(B, splits).
+ */
+int b200_attn_verify_splits(int B);
+size_t b200_attn_verify_workspace_bytes(int B, int splits);
+int b200_attn_verify(const void* q, const void* gate, const void* k_new, const void* v_new, void* kcache,
+                     void* vcache, int num_pages, const int32_t* page_table, int pt_stride,
+                     const int32_t* seqlens, int B, float scale, int splits, void* out, void* ws,
+                     size_t ws_bytes, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Fused gated-attention projection front.  Replaces fp8.linear_q + qk_attn_verify.
  * attn_prefill_front (fp8.py:77-108, qk_attn_verify.cu:765-800): fp8 block-scaled GEMM
  * x[T,2048] . W[9216,2048]^T (activations quantised per token per 128 channels, per-128-k
