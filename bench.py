@@ -196,6 +196,31 @@ def other_kernels(dev, steps, warmup):
                          "frac": gbytes / ms / 1e6 / hbm, "peak_source": which, "status": ops.read_status(st)}
     del states, convs, g
 
+    # attention verify core: 64 requests x 8192 tokens of context (537 MB of e4m3 KV, read once per step), and
+    # the 8-request share of one GPU when the batch is sharded over 8 (9 splits per (request, kv head))
+    for name, Bv in (("attn_verify_b64", 64), ("attn_verify_b8", 8)):
+        try:
+            av = synth.attn_verify(B=Bv, ctx=8192, device=dev)
+            spl = ops._lib.lib().b200_attn_verify_splits(Bv)
+            ws_av = torch.empty(ops._lib.lib().b200_attn_verify_workspace_bytes(Bv, spl), dtype=torch.uint8, device=dev)
+            out_av = torch.empty(4 * Bv, 4096, dtype=torch.bfloat16, device=dev)
+
+            def av_step():
+                ops.attn_verify(av["q"], av["gate"], av["k_new"], av["v_new"], av["kcache"], av["vcache"], av["page_table"],
+                                av["seqlens"], splits=spl, out=out_av, ws=ws_av, status=st)
+
+            ms = timed(av_step)
+            kvb = Bv * 8192 * 2 * 256 * 2
+            out[name] = {"config": f"B={Bv} x 4 drafts, ctx 8192, e4m3 KV in 128-token pages, {spl} split(s); 3 launches "
+                                   "(append, core, merge + gate)", "ms": ms, "algorithmic_bytes": kvb,
+                         "achieved_gbs": kvb / ms / 1e6, "bound": "hbm", "frac": kvb / ms / 1e6 / hbm,
+                         "peak_source": which, "status": ops.read_status(st),
+                         "note": "B=8: 67 MB of KV, L2-resident across timed steps" if Bv == 8 else None}
+            del av, ws_av, out_av
+        except Exception as exc:  # noqa: BLE001
+            out[name] = {"error": repr(exc)[:160]}
+    torch.cuda.empty_cache()
+
     # fused attention projection front: T = 4096
     a = {k: v.to(dev) for k, v in synth.attn().items()}
     half = 32

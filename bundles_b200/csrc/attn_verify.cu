@@ -30,7 +30,7 @@ constexpr int AV_PBUF = 2 * AV_ROWS * 128;      // 8 KB: two [32 rows x 64 keys]
 constexpr int AV_QBUF = 2 * AV_ROWS * 128;      // 8 KB: two [32 rows x 128 B] e4m3 blocks
 constexpr int AV_ONES = 2 * 16 * 128;           // 4 KB: two [16 x 64 keys] f16 blocks, row 0 = 1.0
 constexpr int AV_MAXPAGES = 512;                // pages of one CTA's range whose table entries are cached
-constexpr int AV_SOFT = 8, AV_CONV = 4;         // softmax warps (two per TMEM quadrant), V conversion warps
+constexpr int AV_SOFT = 8, AV_CONV = 8;         // softmax warps (two per TMEM quadrant), V conversion warps
 constexpr int AV_THREADS = (2 + AV_SOFT + AV_CONV) * 32;  // + TMA warp + MMA warp
 constexpr float AV_RESCALE_LOG2 = 8.f;
 // shared memory map (bytes from the 1024-aligned base); P sits before V16 so that the A operand's rows
@@ -94,6 +94,16 @@ __device__ __forceinline__ uint32_t sw128(int row, int chunk) {
 
 constexpr uint32_t UMMA_AB_F16 = 0;
 
+// Optional timeline of CTA 0 (compile with -DB200_TRACE): %globaltimer stamps per page of the K load issue (row 0),
+// the S and P . V MMA issues (1, 2), one softmax warp's S arrival and P hand-over (3, 4), one conversion warp's
+// V arrival and hand-over (5, 6); row 7: kernel start and end.
+#ifdef B200_TRACE
+__device__ unsigned long long g_av_trace[8][128];
+#define AV_TRACE(k, i) do { if (blockIdx.x == 0 && (i) < 128) g_av_trace[k][i] = globaltimer(); } while (0)
+#else
+#define AV_TRACE(k, i) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(AV_THREADS, 1)
 attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const __grid_constant__ CUtensorMap tmQ, const AvArgs p) {
@@ -108,10 +118,11 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   uint64_t* sfree = bars + 10;     // [2] softmax warps have read it
   uint64_t* pready = bars + 12;    // [2] P tile written (and O rescaled if needed)
   uint64_t* pvdone = bars + 14;    // [2] P . V of the tile done (commit): P buffer, V16 and O are free again
-  uint64_t* v16ready = bars + 16;  // [1] f16 V tile written
-  uint64_t* sbar = bars + 17;      // [1] the softmax warps exchanged their row maxima
-  uint64_t* qfull = bars + 18;     // [1] Q rows landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  uint64_t* v16ready = bars + 16;  // [2] f16 V half tile (keys 0..63 / 64..127) written
+  uint64_t* hfree = bars + 18;     // [2] the P . V MMAs that read the half tile are done (commit)
+  uint64_t* sbar = bars + 20;      // [1] the softmax warps exchanged their row maxima
+  uint64_t* qfull = bars + 21;     // [1] Q rows landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* redm = reinterpret_cast<float*>(smem + AV_OFF_RED);
   int32_t* spt = reinterpret_cast<int32_t*>(smem + AV_OFF_PT);
@@ -129,8 +140,9 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       mbar_init(&sfree[i], AV_SOFT);
       mbar_init(&pready[i], AV_SOFT);
       mbar_init(&pvdone[i], 1);
+      mbar_init(&v16ready[i], AV_CONV);
+      mbar_init(&hfree[i], 1);
     }
-    mbar_init(v16ready, AV_CONV);
     mbar_init(sbar, AV_SOFT);
     mbar_init(qfull, 1);
     *abort_flag = 0;
@@ -162,6 +174,7 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) AV_TRACE(7, 0);
   auto page_of = [&](int i) -> int {
     return i < AV_MAXPAGES ? spt[i] : p.page_table[static_cast<size_t>(r) * p.pt_stride + pg0 + i];
   };
@@ -178,6 +191,7 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         const uint32_t ph = (i >> 1) & 1;
         const int page = page_of(i);
         if (!mbar_wait(&kempty[st], ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) break;
+        AV_TRACE(0, i);
         mbar_expect_tx(&kfull[st], AV_KTILE);
         tma_load_2d(smem + AV_OFF_K + st * AV_KTILE, &tmK, 0, (page * AV_HKV + h) * AV_PAGE, &kfull[st]);
         tma_load_2d(smem + AV_OFF_K + st * AV_KTILE + AV_KTILE / 2, &tmK, 128, (page * AV_HKV + h) * AV_PAGE, &kfull[st]);
@@ -200,6 +214,7 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         if (!mbar_wait(&kfull[st], ph, abort_flag, p.status, ST_WAIT_FULL)) return false;
         if (j >= 2 && !mbar_wait(&sfree[st], ph ^ 1u, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) return false;
         tc_fence_after();
+        AV_TRACE(1, j);
         const uint32_t k_base = smem_u32(smem + AV_OFF_K + st * AV_KTILE);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {  // 8 x 32 dims; dims 128..255 are the second swizzled block
@@ -218,19 +233,29 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         const int b = i & 1;
         const uint32_t ph = (i >> 1) & 1;
         if (!mbar_wait(&pready[b], ph, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
-        if (!mbar_wait(v16ready, i & 1, abort_flag, p.status, ST_WAIT_FULL)) break;
         tc_fence_after();
+        AV_TRACE(2, i);
         const uint32_t p_base = smem_u32(smem + AV_OFF_P + b * AV_PBUF);
         const uint32_t v_base = smem_u32(smem + AV_OFF_V16);
         const uint32_t o_base = smem_u32(smem + AV_OFF_ONES);
+        bool good = true;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {  // 8 x 16 keys; keys 64..127 are the second block of each operand
-          const uint64_t da = umma_desc_sw128(p_base + (kk >> 2) * (AV_ROWS * 128) + (kk & 3) * 32);
-          tc_mma_f16(tmem_base + AV_TM_O, da, umma_desc_sw128(v_base + (kk >> 2) * (AV_D * 128) + (kk & 3) * 32), idesc_o,
-                     (i | kk) != 0);
-          tc_mma_f16(tmem_base + AV_TM_L, da, umma_desc_sw128(o_base + (kk >> 2) * 2048 + (kk & 3) * 32), idesc_l,
-                     (i | kk) != 0);
+        for (int hk = 0; hk < 2; ++hk) {  // keys 0..63, then 64..127: the conversion of one half overlaps the MMAs of the other
+          if (!mbar_wait(&v16ready[hk], i & 1, abort_flag, p.status, ST_WAIT_FULL)) {
+            good = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {  // 4 x 16 keys
+            const int kk = hk * 4 + k4;
+            const uint64_t da = umma_desc_sw128(p_base + hk * (AV_ROWS * 128) + k4 * 32);
+            tc_mma_f16(tmem_base + AV_TM_O, da, umma_desc_sw128(v_base + hk * (AV_D * 128) + k4 * 32), idesc_o, (i | kk) != 0);
+            tc_mma_f16(tmem_base + AV_TM_L, da, umma_desc_sw128(o_base + hk * 2048 + k4 * 32), idesc_l, (i | kk) != 0);
+          }
+          tc_commit(&hfree[hk]);
         }
+        if (!good) break;
         tc_commit(&pvdone[b]);
       }
     }
@@ -247,6 +272,7 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       const uint32_t ph = (i >> 1) & 1;
       if (!mbar_wait(&sfull[b], ph, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
       tc_fence_after();
+      if (warp == 4 && lane == 0) AV_TRACE(3, i);
       uint32_t raw[16];
       tmem_ld16(tmem_base + AV_TM_S + b * 32 + half * 16 + (static_cast<uint32_t>(q * 32) << 16), raw);
       tmem_ld_wait();
@@ -314,6 +340,7 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pready[b]);
+      if (warp == 4 && lane == 0) AV_TRACE(4, i);
     }
     // ---------------- epilogue: the quadrant-0 warps write this split's partial (rows on lanes 0..31) ----------------
     if (ok && q == 0) {
@@ -349,51 +376,59 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
     }
   } else {
-    // ---------------- V conversion: warps 10..13.  e4m3 page [256 dims][128 keys] -> f16, same orientation, as two
+    // ---------------- V conversion: warps 10..17.  e4m3 page [256 dims][128 keys] -> f16, same orientation, as two
     // 64-key blocks; 16 keys (one 16-byte chunk) per step ----------------
-    const int ct = (warp - 2 - AV_SOFT) * 32 + lane;  // 0..127
-    for (int i = 0; i < ntiles; ++i) {
+    const int ct = (warp - 2 - AV_SOFT) * 32 + lane;  // 0..255
+    bool ok = true;
+    for (int i = 0; ok && i < ntiles; ++i) {
       const int st = i & 1;
       const uint32_t ph = (i >> 1) & 1;
       if (!mbar_wait(&vfull[st], ph, abort_flag, p.status, ST_WAIT_FULL)) break;
-      if (i >= 1 && !mbar_wait(&pvdone[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) break;
+      if (warp == 2 + AV_SOFT && lane == 0) AV_TRACE(5, i);
       const uint8_t* src = smem + AV_OFF_V8 + st * AV_KTILE;
-      uint8_t* dst = smem + AV_OFF_V16;
       // keys past the request's last token may hold stale bytes (any bit pattern, NaN included): zero them so that
       // a zero probability times such a value cannot poison the sums
       const int keys_valid = min(AV_PAGE, n_tok - (pg0 + i) * AV_PAGE);
-      for (int u = ct; u < AV_D * 8; u += AV_CONV * 32) {
-        const int d = u >> 3, c = u & 7;  // dim row, 16-key chunk
-        uint4 v = *reinterpret_cast<const uint4*>(src + sw128(d, c));
-        const int k0 = c * 16;
-        if (k0 + 16 > keys_valid) {
-          uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-          for (int e = 0; e < 16; ++e)
-            if (k0 + e >= keys_valid) w[e >> 2] &= ~(0xffu << ((e & 3) * 8));
-          v = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int hk = 0; hk < 2; ++hk) {
+        // the half tile is free once the MMAs of the previous page that read it are done
+        if (i >= 1 && !mbar_wait(&hfree[hk], (i - 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
         }
-        uint4 lo, hi;
-        lo.x = e4m3x2_to_f16x2(v.x & 0xffffu);
-        lo.y = e4m3x2_to_f16x2(v.x >> 16);
-        lo.z = e4m3x2_to_f16x2(v.y & 0xffffu);
-        lo.w = e4m3x2_to_f16x2(v.y >> 16);
-        hi.x = e4m3x2_to_f16x2(v.z & 0xffffu);
-        hi.y = e4m3x2_to_f16x2(v.z >> 16);
-        hi.z = e4m3x2_to_f16x2(v.w & 0xffffu);
-        hi.w = e4m3x2_to_f16x2(v.w >> 16);
-        uint8_t* blk = dst + (c >> 2) * (AV_D * 128);  // keys 0..63 / 64..127
-        *reinterpret_cast<uint4*>(blk + sw128(d, (c & 3) * 2)) = lo;
-        *reinterpret_cast<uint4*>(blk + sw128(d, (c & 3) * 2 + 1)) = hi;
+        uint8_t* blk = smem + AV_OFF_V16 + hk * (AV_D * 128);
+        for (int u = ct; u < AV_D * 4; u += AV_CONV * 32) {
+          const int d = u >> 2, c4 = u & 3, c = hk * 4 + c4;  // dim row, 16-key chunk
+          uint4 v = *reinterpret_cast<const uint4*>(src + sw128(d, c));
+          const int k0 = c * 16;
+          if (k0 + 16 > keys_valid) {
+            uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              if (k0 + e >= keys_valid) w[e >> 2] &= ~(0xffu << ((e & 3) * 8));
+            v = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          uint4 lo, hi;
+          lo.x = e4m3x2_to_f16x2(v.x & 0xffffu);
+          lo.y = e4m3x2_to_f16x2(v.x >> 16);
+          lo.z = e4m3x2_to_f16x2(v.y & 0xffffu);
+          lo.w = e4m3x2_to_f16x2(v.y >> 16);
+          hi.x = e4m3x2_to_f16x2(v.z & 0xffffu);
+          hi.y = e4m3x2_to_f16x2(v.z >> 16);
+          hi.z = e4m3x2_to_f16x2(v.w & 0xffffu);
+          hi.w = e4m3x2_to_f16x2(v.w >> 16);
+          *reinterpret_cast<uint4*>(blk + sw128(d, c4 * 2)) = lo;
+          *reinterpret_cast<uint4*>(blk + sw128(d, c4 * 2 + 1)) = hi;
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&v16ready[hk]);
       }
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(v16ready);
-        mbar_arrive(&vempty[st]);
-      }
+      if (!ok) break;
+      if (lane == 0) mbar_arrive(&vempty[st]);
+      if (warp == 2 + AV_SOFT && lane == 0) AV_TRACE(6, i);
     }
   }
+  if (threadIdx.x == 0) AV_TRACE(7, 1);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -452,6 +487,12 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restri
 }  // namespace b200
 
 using namespace b200;
+
+#ifdef B200_TRACE
+extern "C" int b200_av_trace_read(unsigned long long* host) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_av_trace, sizeof(g_av_trace)));
+}
+#endif
 
 extern "C" int b200_attn_verify_splits(int B) {
   if (B <= 0) return 0;

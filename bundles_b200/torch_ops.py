@@ -14,6 +14,8 @@ _lib.define("gdn_verify(Tensor mixed, Tensor z, Tensor a, Tensor b, Tensor(a!) c
             "Tensor a_log, Tensor dt_bias, Tensor(b!) state, Tensor accepted, Tensor norm_w, float eps) -> Tensor")
 _lib.define("attn_front(Tensor x, Tensor w, Tensor w_s, Tensor q_norm_w, Tensor k_norm_w, Tensor positions, "
             "Tensor cos_sin, float eps, bool out_fp8) -> (Tensor, Tensor, Tensor, Tensor)")
+_lib.define("attn_verify(Tensor q, Tensor gate, Tensor k_new, Tensor v_new, Tensor(a!) kcache, Tensor(b!) vcache, "
+            "Tensor page_table, Tensor seqlens, float scale) -> Tensor")
 _lib.define("lmhead_argmax(Tensor x, Tensor w, Tensor w_s, int shard_lo) -> (Tensor, Tensor)")
 _lib.define("moe_combine(Tensor cache, Tensor x, Tensor? gate_w, int top_k, Tensor? pos) -> Tensor")
 
@@ -31,6 +33,10 @@ def _attn(x, w, w_s, qw, kw, positions, cos_sin, eps, out_fp8):
     return ops.attn_front(x, w, w_s, qw, kw, positions, cos_sin, eps, out_fp8)
 
 
+def _attn_verify(q, gate, k_new, v_new, kcache, vcache, page_table, seqlens, scale):
+    return ops.attn_verify(q, gate, k_new, v_new, kcache, vcache, page_table, seqlens, scale)
+
+
 def _lmhead(x, w, w_s, shard_lo):
     mx, idx, _ = ops.lmhead_argmax(x, w, w_s, shard_lo)
     return mx, idx
@@ -43,5 +49,6 @@ def _combine(cache, x, gate_w, top_k, pos):
 _lib.impl("router", _router, "CUDA")
 _lib.impl("gdn_verify", _gdn, "CUDA")
 _lib.impl("attn_front", _attn, "CUDA")
+_lib.impl("attn_verify", _attn_verify, "CUDA")
 _lib.impl("lmhead_argmax", _lmhead, "CUDA")
 _lib.impl("moe_combine", _combine, "CUDA")

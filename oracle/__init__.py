@@ -12,7 +12,7 @@ that run on a CPU (its torch quantisers and its Triton router / SwiGLU / combine
 the Triton interpreter, at the reference's own 256-expert / top-8 shapes) were run once and
 their outputs are committed under `tests/golden/` together with the generating script; the
 oracle functions that have such a counterpart are checked against them.  The GDN recurrence,
-the fp8 128x128 block-scaled GEMMs, the fused attention front at GEMM level and the LM-head
-argmax have no CPU-runnable counterpart in the reference: for those rows PARITY IS UNPINNED by
+the fp8 128x128 block-scaled GEMMs, the fused attention front at GEMM level, the attention-verify
+core and the LM-head argmax have no CPU-runnable counterpart in the reference: for those rows PARITY IS UNPINNED by
 the reference and rests on this restatement alone.
 """
