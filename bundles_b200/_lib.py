@@ -38,6 +38,7 @@ PROTOTYPES = {
     "b200_moe_fp8": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(MoeWeights), C.POINTER(MoeLists), vp, vp, sz, vp,
                            i32, vp, vp]),
     "b200_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
+    "b200_moe_combine_norm": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, f32, vp, vp]),
     "b200_attn_front_workspace_bytes": (sz, [i32]),
     "b200_attn_front": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, i32, f32, i32, vp, vp, vp, vp, vp, sz, vp, vp]),
     "b200_attn_verify_splits": (i32, [i32]),

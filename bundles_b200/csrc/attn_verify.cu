@@ -15,8 +15,8 @@
 // page on the TMEM lanes and the 32 rows (4 tokens x 8 q heads) as columns, so the softmax warps own one
 // key per thread; O = P . V on kind::f16 (P as the A operand: 32 real rows, the other 96 rows of the
 // M = 128 tile read whatever follows P in shared memory and land in TMEM lanes nobody reads), V
-// converted e4m3 -> f16 in shared memory by its own warps; the row sums come from the same P through
-// a ones operand, so numerator and denominator see the same rounded probabilities.
+// converted e4m3 -> f16 in shared memory by its own warps; the row sums are fp32 sums of the unrounded
+// probabilities, as in the reference.
 #include "common.cuh"
 #include "host.h"
 
@@ -28,7 +28,6 @@ constexpr int AV_KTILE = AV_PAGE * AV_D;        // 32 KB e4m3: two [128 keys x 1
 constexpr int AV_V16 = AV_D * AV_PAGE * 2;      // 64 KB f16: two [256 dims x 64 keys] swizzled blocks
 constexpr int AV_PBUF = 2 * AV_ROWS * 128;      // 8 KB: two [32 rows x 64 keys] f16 blocks
 constexpr int AV_QBUF = 2 * AV_ROWS * 128;      // 8 KB: two [32 rows x 128 B] e4m3 blocks
-constexpr int AV_ONES = 2 * 16 * 128;           // 4 KB: two [16 x 64 keys] f16 blocks, row 0 = 1.0
 constexpr int AV_MAXPAGES = 512;                // pages of one CTA's range whose table entries are cached
 constexpr int AV_SOFT = 8, AV_CONV = 8;         // softmax warps (two per TMEM quadrant), V conversion warps
 constexpr int AV_THREADS = (2 + AV_SOFT + AV_CONV) * 32;  // + TMA warp + MMA warp
@@ -38,15 +37,14 @@ constexpr float AV_RESCALE_LOG2 = 8.f;
 constexpr int AV_OFF_K = 0;                              // 2 stages
 constexpr int AV_OFF_V8 = AV_OFF_K + 2 * AV_KTILE;       // 2 stages
 constexpr int AV_OFF_Q = AV_OFF_V8 + 2 * AV_KTILE;
-constexpr int AV_OFF_ONES = AV_OFF_Q + AV_QBUF;
-constexpr int AV_OFF_P = AV_OFF_ONES + AV_ONES;          // 2 buffers
+constexpr int AV_OFF_P = AV_OFF_Q + AV_QBUF;             // 2 buffers
 constexpr int AV_OFF_V16 = AV_OFF_P + 2 * AV_PBUF;
 constexpr int AV_OFF_BAR = AV_OFF_V16 + AV_V16;
-constexpr int AV_OFF_RED = AV_OFF_BAR + 256;             // [2][4][32] floats: per-quadrant row maxima
-constexpr int AV_OFF_PT = AV_OFF_RED + 2 * 4 * 32 * 4;   // cached page-table entries
+constexpr int AV_OFF_RED = AV_OFF_BAR + 256;             // [3][4][32] floats: per-quadrant row maxima; [8][16] row sums
+constexpr int AV_OFF_PT = AV_OFF_RED + (3 * 4 * 32 + 8 * 16) * 4;   // cached page-table entries
 constexpr int AV_SMEM = AV_OFF_PT + AV_MAXPAGES * 4 + 1024;
-// TMEM columns: O [0, 256), row sums [256, 272), S double buffer [288, 320) and [320, 352)
-constexpr uint32_t AV_TM_O = 0, AV_TM_L = 256, AV_TM_S = 288;
+// TMEM columns: O [0, 256), S double buffer [256, 288) and [288, 320)
+constexpr uint32_t AV_TM_O = 0, AV_TM_S = 256;
 
 struct AvArgs {
   const int32_t* page_table;  // [B, pt_stride]
@@ -120,9 +118,9 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   uint64_t* pvdone = bars + 14;    // [2] P . V of the tile done (commit): P buffer, V16 and O are free again
   uint64_t* v16ready = bars + 16;  // [2] f16 V half tile (keys 0..63 / 64..127) written
   uint64_t* hfree = bars + 18;     // [2] the P . V MMAs that read the half tile are done (commit)
-  uint64_t* sbar = bars + 20;      // [1] the softmax warps exchanged their row maxima
-  uint64_t* qfull = bars + 21;     // [1] Q rows landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
+  uint64_t* sbar = bars + 20;      // [2] the softmax warps published their row maxima (by page parity)
+  uint64_t* qfull = bars + 22;     // [1] Q rows landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* redm = reinterpret_cast<float*>(smem + AV_OFF_RED);
   int32_t* spt = reinterpret_cast<int32_t*>(smem + AV_OFF_PT);
@@ -142,20 +140,14 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       mbar_init(&pvdone[i], 1);
       mbar_init(&v16ready[i], AV_CONV);
       mbar_init(&hfree[i], 1);
+      mbar_init(&sbar[i], AV_SOFT);
     }
-    mbar_init(sbar, AV_SOFT);
     mbar_init(qfull, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmQ);
-  }
-  // the ones operand of the row-sum product: row 0 of each 64-key block is 1.0 (f16), rows 1..15 are zero
-  for (int i = threadIdx.x; i < AV_ONES / 4; i += AV_THREADS) {
-    const int byte = i * 4, blk = byte / 2048, row = (byte % 2048) / 128;
-    (void)blk;
-    reinterpret_cast<uint32_t*>(smem + AV_OFF_ONES)[i] = row == 0 ? 0x3c003c00u : 0u;  // swizzle permutes within a row only
   }
   if (warp == 1) tmem_alloc(tmem_slot, 512);
   pdl_wait();
@@ -205,7 +197,6 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     if (lane == 0 && ntiles > 0) {  // ---------------- MMA issuer ----------------
       const uint32_t idesc_s = umma_idesc(UMMA_C_F32, UMMA_AB_E4M3, AV_ROWS);   // M = 128 keys, N = 32 rows
       const uint32_t idesc_o = umma_idesc(UMMA_C_F32, UMMA_AB_F16, AV_D);       // M = 128 rows, N = 256 dims
-      const uint32_t idesc_l = umma_idesc(UMMA_C_F32, UMMA_AB_F16, 16);         // row sums
       const uint32_t q_base = smem_u32(smem + AV_OFF_Q);
       bool ok = mbar_wait(qfull, 0, abort_flag, p.status, ST_WAIT_FULL);
       auto issue_s = [&](int j) -> bool {
@@ -227,9 +218,12 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         tc_commit(&sfull[st]);
         return true;
       };
+      // the score MMAs run two pages ahead of the P . V MMAs: the softmax warps read page i + 1's scores before they
+      // hand over page i's probabilities
       if (ok) ok = issue_s(0);
+      if (ok && ntiles > 1) ok = issue_s(1);
       for (int i = 0; ok && i < ntiles; ++i) {
-        if (i + 1 < ntiles && !issue_s(i + 1)) break;
+        if (i + 2 < ntiles && !issue_s(i + 2)) break;
         const int b = i & 1;
         const uint32_t ph = (i >> 1) & 1;
         if (!mbar_wait(&pready[b], ph, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
@@ -237,7 +231,6 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         AV_TRACE(2, i);
         const uint32_t p_base = smem_u32(smem + AV_OFF_P + b * AV_PBUF);
         const uint32_t v_base = smem_u32(smem + AV_OFF_V16);
-        const uint32_t o_base = smem_u32(smem + AV_OFF_ONES);
         bool good = true;
 #pragma unroll
         for (int hk = 0; hk < 2; ++hk) {  // keys 0..63, then 64..127: the conversion of one half overlaps the MMAs of the other
@@ -251,7 +244,6 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             const int kk = hk * 4 + k4;
             const uint64_t da = umma_desc_sw128(p_base + hk * (AV_ROWS * 128) + k4 * 32);
             tc_mma_f16(tmem_base + AV_TM_O, da, umma_desc_sw128(v_base + hk * (AV_D * 128) + k4 * 32), idesc_o, (i | kk) != 0);
-            tc_mma_f16(tmem_base + AV_TM_L, da, umma_desc_sw128(o_base + hk * 2048 + k4 * 32), idesc_l, (i | kk) != 0);
           }
           tc_commit(&hfree[hk]);
         }
@@ -262,15 +254,19 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   } else if (warp < 2 + AV_SOFT) {
     // ---------------- softmax: warps 2..9.  TMEM lane quadrant q = warp % 4 holds keys 32 q .. 32 q + 31 of the
     // page; the two warps of a quadrant take 16 of the 32 rows each.  Every warp keeps the running maximum of
-    // all 32 rows (row j in lane j; identical in all warps: they read the same exchanged maxima) ----------------
+    // all 32 rows (row j in lane j; identical in all warps: they read the same exchanged maxima) and its own
+    // share of the row sums.  The loop is software-pipelined: the scores of page i + 1 are read and their row
+    // maxima published before the probabilities of page i are formed, so neither the S MMA's completion nor
+    // the exchange of the maxima is waited for where it is needed ----------------
     const int q = warp & 3, half = (warp - 2) >> 2;
     const int key_in_page = q * 32 + lane;
     float m_run = -INFINITY;  // lane j: running maximum of row j (log2 domain)
+    float l_run = 0.f;        // lane l: this warp's 32 keys' share of the sum of row half*16 + (l & 15)
     bool ok = true;
-    for (int i = 0; ok && i < ntiles; ++i) {
+    // stage A of page i: scores -> registers, masked and scaled; per-row maximum of this warp's 32 keys -> redm
+    auto stage_a = [&](int i, float (&sc)[16]) -> bool {
       const int b = i & 1;
-      const uint32_t ph = (i >> 1) & 1;
-      if (!mbar_wait(&sfull[b], ph, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
+      if (!mbar_wait(&sfull[b], (i >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL)) return false;
       tc_fence_after();
       if (warp == 4 && lane == 0) AV_TRACE(3, i);
       uint32_t raw[16];
@@ -279,16 +275,13 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sfree[b]);
-      // scores of this thread's key against rows half*16 .. +15 (row = token * 8 + head); causal limit per token
-      const int key = (pg0 + i) * AV_PAGE + key_in_page;
-      float sc[16];
+      const int key = (pg0 + i) * AV_PAGE + key_in_page;  // causal limit per token: key <= prefix + token
       uint32_t mine = 0u;
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const int tok = (half * 16 + j) >> 3;
-        const bool valid = key <= n_prefix + tok;
-        sc[j] = valid ? __uint_as_float(raw[j]) * p.scale_log2 : -INFINITY;
-        // order-preserving integer image of the score (NaN scores of garbage keys were masked above)
+        sc[j] = key <= n_prefix + tok ? __uint_as_float(raw[j]) * p.scale_log2 : -INFINITY;
+        // order-preserving integer image of the score (NaN scores of stale keys were masked above)
         uint32_t k = __float_as_uint(sc[j]);
         k = (k & 0x80000000u) ? ~k : (k | 0x80000000u);
         const uint32_t mx = __reduce_max_sync(FULL_MASK, k);
@@ -296,27 +289,36 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
       if (lane < 16) {
         const uint32_t f = (mine & 0x80000000u) ? (mine & 0x7fffffffu) : ~mine;
-        redm[(b * 4 + q) * 32 + half * 16 + lane] = __uint_as_float(f);
+        redm[((i % 3) * 4 + q) * 32 + half * 16 + lane] = __uint_as_float(f);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(sbar);
-      if (!mbar_wait(sbar, i & 1, abort_flag, p.status, ST_WAIT_STATE)) break;
-      // lane j: tile maximum of row j over the four quadrants, then the lazy update of the running maximum
-      const float tm = fmaxf(fmaxf(redm[(b * 4 + 0) * 32 + lane], redm[(b * 4 + 1) * 32 + lane]),
-                             fmaxf(redm[(b * 4 + 2) * 32 + lane], redm[(b * 4 + 3) * 32 + lane]));
+      if (lane == 0) mbar_arrive(&sbar[b]);
+      return true;
+    };
+    float sc_cur[16], sc_next[16];
+    if (ntiles > 0) ok = stage_a(0, sc_cur);
+    for (int i = 0; ok && i < ntiles; ++i) {
+      const int b = i & 1;
+      const uint32_t ph = (i >> 1) & 1;
+      if (i + 1 < ntiles && !stage_a(i + 1, sc_next)) break;
+      // stage B of page i: every warp has published its maxima
+      if (!mbar_wait(&sbar[b], ph, abort_flag, p.status, ST_WAIT_STATE)) break;
+      const float* rm = redm + (i % 3) * 4 * 32;
+      const float tm = fmaxf(fmaxf(rm[lane], rm[32 + lane]), fmaxf(rm[64 + lane], rm[96 + lane]));
       const float m_new = tm > m_run + AV_RESCALE_LOG2 ? tm : m_run;  // -inf + 8 = -inf: the first finite maximum is taken
       const float alpha = (m_new == m_run) ? 1.f : exp2f(m_run - m_new);  // m_run = -inf gives 0
       const bool move = __any_sync(FULL_MASK, m_new != m_run);
       m_run = m_new;
-      // the P buffer (and O, for a rescale) must be free: P . V of tile i - 2 (same buffer) / i - 1 done
+      if (move) l_run *= __shfl_sync(FULL_MASK, alpha, half * 16 + (lane & 15));
+      // the P buffer (and O, for a rescale) must be free: P . V of page i - 2 (same buffer) / i - 1 done
       if (i >= 2 && !mbar_wait(&pvdone[b], ph ^ 1u, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) break;
       if (move && i > 0 && q == 0) {
-        // rows sit on TMEM lanes 0..31 of O: the quadrant-0 warps scale their half of the 256 columns (and the
-        // row sums) by alpha; the first tile overwrites O instead
+        // rows sit on TMEM lanes 0..31 of O: the quadrant-0 warps scale their half of the 256 columns by alpha;
+        // the first page overwrites O instead
         if (!mbar_wait(&pvdone[b ^ 1], ((i - 1) >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
-        for (int c = 0; c < 8 + (half == 0 ? 1 : 0); ++c) {
-          const uint32_t col = c < 8 ? AV_TM_O + half * 128 + c * 16 : AV_TM_L;
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t col = AV_TM_O + half * 128 + c * 16;
           uint32_t v[16];
           tmem_ld16(tmem_base + col, v);
           tmem_ld_wait();
@@ -327,22 +329,48 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         tmem_st_wait();
         tc_fence_before();
       }
-      // P^T -> shared memory as the A operand [row][key], f16, 128-byte swizzle
+      // P^T -> shared memory as the A operand [row][key], f16, 128-byte swizzle; the row sums take the same rounded
+      // probabilities (a transposing butterfly over the warp's 32 keys: lane l ends with row half*16 + (l & 15))
       uint8_t* pb = smem + AV_OFF_P + b * AV_PBUF + (key_in_page >> 6) * (AV_ROWS * 128);
       const int kb = (key_in_page & 63) * 2;  // byte of this key inside the 128-byte row
+      float pf[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        const int row = half * 16 + j;
+        const int row = half * 16 + j;  // row & 7 == j & 7: the swizzle term is one of eight per-thread constants
         const float mr = __shfl_sync(FULL_MASK, m_run, row);
-        const float pv = sc[j] == -INFINITY ? 0.f : exp2f(sc[j] - mr);
-        *reinterpret_cast<unsigned short*>(pb + sw128(row, kb >> 4) + (kb & 15)) = f2h_bits(pv);
+        // every (page, row) has at least one key inside the causal limit, so m_run is finite here and a masked
+        // score (-inf) gives exactly 0; the row sums take the unrounded probabilities as the reference does
+        // (qk_attn_verify.cu:290-302)
+        float pv;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pv) : "f"(sc_cur[j] - mr));
+        pf[j] = pv;
+        *reinterpret_cast<unsigned short*>(pb + (row >> 3) * 1024 + (row & 7) * 128 + ((((kb >> 4) ^ (j & 7)) << 4) | (kb & 15))) =
+            f2h_bits(pv);
       }
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pready[b]);
       if (warp == 4 && lane == 0) AV_TRACE(4, i);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int j = 0; j < o; ++j) {
+          const float send = up ? pf[j] : pf[j + o];
+          const float keep = up ? pf[j + o] : pf[j];
+          pf[j] = keep + __shfl_xor_sync(FULL_MASK, send, o);
+        }
+      }
+      l_run += pf[0] + __shfl_xor_sync(FULL_MASK, pf[0], 16);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) sc_cur[j] = sc_next[j];
     }
-    // ---------------- epilogue: the quadrant-0 warps write this split's partial (rows on lanes 0..31) ----------------
+    // ---------------- epilogue: the row sums of the eight warps meet in shared memory; the quadrant-0 warps write
+    // this split's partial (rows on lanes 0..31 of O) ----------------
+    float* lsum = redm + 3 * 4 * 32;  // [8 warps][16]
+    if (lane < 16) lsum[(warp - 2) * 16 + lane] = l_run;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sbar[ntiles & 1]);
     if (ok && q == 0) {
       float* po = p.part_o + static_cast<size_t>(cta) * AV_ROWS * AV_D + static_cast<size_t>(lane) * AV_D + half * 128;
       float* pml = p.part_ml + static_cast<size_t>(cta) * 2 * AV_ROWS;
@@ -354,7 +382,8 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         }
       } else {
         const int last = ntiles - 1;
-        if (mbar_wait(&pvdone[last & 1], (last >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL)) {
+        if (mbar_wait(&pvdone[last & 1], (last >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL) &&
+            mbar_wait(&sbar[ntiles & 1], (ntiles >> 1) & 1, abort_flag, p.status, ST_WAIT_STATE)) {
           tc_fence_after();
           for (int c = 0; c < 8; ++c) {
             uint32_t v[16];
@@ -366,11 +395,12 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                                                                          __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
           }
           if (half == 0) {
-            uint32_t v[16];
-            tmem_ld16(tmem_base + AV_TM_L, v);
-            tmem_ld_wait();
+            // row `lane`: its sum lives in the four warps of half lane / 16 (warp index = 4 * half + quadrant slot)
+            const int hw = lane >> 4, j = lane & 15;
+            float l = 0.f;
+            for (int w = 0; w < 4; ++w) l += lsum[(hw * 4 + w) * 16 + j];
             pml[lane] = m_run;
-            pml[AV_ROWS + lane] = __uint_as_float(v[0]);
+            pml[AV_ROWS + lane] = l;
           }
         }
       }
@@ -395,12 +425,18 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           ok = false;
           break;
         }
-        uint8_t* blk = smem + AV_OFF_V16 + hk * (AV_D * 128);
-        for (int u = ct; u < AV_D * 4; u += AV_CONV * 32) {
-          const int d = u >> 2, c4 = u & 3, c = hk * 4 + c4;  // dim row, 16-key chunk
-          uint4 v = *reinterpret_cast<const uint4*>(src + sw128(d, c));
-          const int k0 = c * 16;
-          if (k0 + 16 > keys_valid) {
+        // thread ct converts chunk c4 = ct % 4 of dim rows ct / 4 + 64 k, k = 0..3: the swizzle term depends on the
+        // row modulo 8 only, so source and destination offsets advance by a constant (64 rows = 8192 bytes)
+        const int c4 = ct & 3, c = hk * 4 + c4, d0 = ct >> 2;
+        const uint8_t* sp = src + sw128(d0, c);
+        uint8_t* dp = smem + AV_OFF_V16 + hk * (AV_D * 128) + sw128(d0, c4 * 2);
+        const uint32_t hi_delta = sw128(d0, c4 * 2 + 1) - sw128(d0, c4 * 2);  // the pair's second chunk (may be negative)
+        const int k0 = c * 16;
+        const bool ragged = k0 + 16 > keys_valid;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint4 v = *reinterpret_cast<const uint4*>(sp + k * 8192);
+          if (ragged) {
             uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int e = 0; e < 16; ++e)
@@ -416,8 +452,8 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           hi.y = e4m3x2_to_f16x2(v.z >> 16);
           hi.z = e4m3x2_to_f16x2(v.w & 0xffffu);
           hi.w = e4m3x2_to_f16x2(v.w >> 16);
-          *reinterpret_cast<uint4*>(blk + sw128(d, c4 * 2)) = lo;
-          *reinterpret_cast<uint4*>(blk + sw128(d, c4 * 2 + 1)) = hi;
+          *reinterpret_cast<uint4*>(dp + k * 8192) = lo;
+          *reinterpret_cast<uint4*>(dp + k * 8192 + static_cast<int>(hi_delta)) = hi;
         }
         fence_proxy_async();
         __syncwarp();

@@ -567,6 +567,86 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict
   }
 }
 
+// The combine with the next layer's input norm folded in (the reference's combine_norm_kernel, qk_route.cu:686-820):
+// out as above; r = bf16(out + residual) written back to `residual`; y = bf16(r * rsqrt(mean r^2 + eps) * (1 + w)).
+// Same arithmetic, in the same order, as moe_combine_kernel followed by add_rmsnorm_kernel.
+__global__ void __launch_bounds__(256) moe_combine_norm_kernel(const bf16* __restrict__ cache, const bf16* __restrict__ x,
+                                                               const bf16* __restrict__ gate_w,
+                                                               const int64_t* __restrict__ pos, int T, int H, int K,
+                                                               bf16* __restrict__ out, bf16* __restrict__ residual,
+                                                               const bf16* __restrict__ norm_w, float eps,
+                                                               bf16* __restrict__ normed) {
+  __shared__ float red[8], red2[8];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  pdl_wait();
+  pdl_launch();
+  const bool pad = pos != nullptr && pos[t] == 0;
+  float gate = 0.f;
+  if (!pad && gate_w != nullptr) {
+    float dot = 0.f;
+    for (int c = tid * 8; c < H; c += 2048) {
+      const uint4 a = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H + c);
+      const uint4 w = *reinterpret_cast<const uint4*>(gate_w + c);
+      dot = fmaf(bf_lo(a.x), bf_lo(w.x), dot); dot = fmaf(bf_hi(a.x), bf_hi(w.x), dot);
+      dot = fmaf(bf_lo(a.y), bf_lo(w.y), dot); dot = fmaf(bf_hi(a.y), bf_hi(w.y), dot);
+      dot = fmaf(bf_lo(a.z), bf_lo(w.z), dot); dot = fmaf(bf_hi(a.z), bf_hi(w.z), dot);
+      dot = fmaf(bf_lo(a.w), bf_lo(w.w), dot); dot = fmaf(bf_hi(a.w), bf_hi(w.w), dot);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(FULL_MASK, dot, o);
+    if ((tid & 31) == 0) red[tid >> 5] = dot;
+    __syncthreads();
+    float s = 0.f;
+    for (int w = 0; w < 8; ++w) s += red[w];
+    gate = 1.f / (1.f + __expf(-s));
+  }
+  float ss = 0.f;
+  for (int c = tid * 8; c < H; c += 2048) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (!pad) {
+      for (int j = 0; j < K; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(cache + (static_cast<size_t>(t) * K + j) * H + c);
+        acc[0] += bf_lo(v.x); acc[1] += bf_hi(v.x); acc[2] += bf_lo(v.y); acc[3] += bf_hi(v.y);
+        acc[4] += bf_lo(v.z); acc[5] += bf_hi(v.z); acc[6] += bf_lo(v.w); acc[7] += bf_hi(v.w);
+      }
+      if (gate_w != nullptr) {
+        const uint4 v = *reinterpret_cast<const uint4*>(cache + (static_cast<size_t>(T) * K + t) * H + c);
+        acc[0] += gate * bf_lo(v.x); acc[1] += gate * bf_hi(v.x); acc[2] += gate * bf_lo(v.y); acc[3] += gate * bf_hi(v.y);
+        acc[4] += gate * bf_lo(v.z); acc[5] += gate * bf_hi(v.z); acc[6] += gate * bf_lo(v.w); acc[7] += gate * bf_hi(v.w);
+      }
+    }
+    const uint4 o4 = make_uint4(pack_bf2(acc[0], acc[1]), pack_bf2(acc[2], acc[3]), pack_bf2(acc[4], acc[5]),
+                                pack_bf2(acc[6], acc[7]));
+    if (out != nullptr) *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + c) = o4;
+    const uint4 b = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * H + c);
+    float r[8] = {rbf(bf_lo(o4.x) + bf_lo(b.x)), rbf(bf_hi(o4.x) + bf_hi(b.x)), rbf(bf_lo(o4.y) + bf_lo(b.y)),
+                  rbf(bf_hi(o4.y) + bf_hi(b.y)), rbf(bf_lo(o4.z) + bf_lo(b.z)), rbf(bf_hi(o4.z) + bf_hi(b.z)),
+                  rbf(bf_lo(o4.w) + bf_lo(b.w)), rbf(bf_hi(o4.w) + bf_hi(b.w))};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(r[i], r[i], ss);
+    *reinterpret_cast<uint4*>(residual + static_cast<size_t>(t) * H + c) =
+        make_uint4(pack_bf2(r[0], r[1]), pack_bf2(r[2], r[3]), pack_bf2(r[4], r[5]), pack_bf2(r[6], r[7]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(FULL_MASK, ss, o);
+  if ((tid & 31) == 0) red2[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < 8; ++i) tot += red2[i];
+  const float rstd = rsqrtf(tot / H + eps);
+  for (int c = tid * 8; c < H; c += 2048) {  // each thread re-reads the rows it wrote itself
+    const uint4 b = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * H + c);
+    const uint4 g = *reinterpret_cast<const uint4*>(norm_w + c);
+    const float r[8] = {bf_lo(b.x), bf_hi(b.x), bf_lo(b.y), bf_hi(b.y), bf_lo(b.z), bf_hi(b.z), bf_lo(b.w), bf_hi(b.w)};
+    const float gw[8] = {bf_lo(g.x), bf_hi(g.x), bf_lo(g.y), bf_hi(g.y), bf_lo(g.z), bf_hi(g.z), bf_lo(g.w), bf_hi(g.w)};
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = r[i] * rstd * (1.f + gw[i]);
+    *reinterpret_cast<uint4*>(normed + static_cast<size_t>(t) * H + c) =
+        make_uint4(pack_bf2(y[0], y[1]), pack_bf2(y[2], y[3]), pack_bf2(y[4], y[5]), pack_bf2(y[6], y[7]));
+  }
+}
+
 // workspace layout of the int8 block (all offsets 1024-byte aligned)
 struct W8Layout {
   size_t xq, xs, h, hq, hs, total;
@@ -737,4 +817,18 @@ extern "C" int b200_moe_combine(const void* cache, const void* x, const void* ga
   launch_k(moe_combine_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const bf16*>(cache),
            static_cast<const bf16*>(x), static_cast<const bf16*>(gate_w), pos, T, H, K, static_cast<bf16*>(out));
   return launch_status("b200_moe_combine");
+}
+
+extern "C" int b200_moe_combine_norm(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T, int H,
+                                     int K, void* out, void* residual, const void* norm_w, float eps, void* normed,
+                                     void* stream) {
+  if (!cache || !x || !residual || !norm_w || !normed) return fail(B200_E_ARG, "b200_moe_combine_norm: null pointer");
+  if (T < 0 || H <= 0 || H % 8 || K <= 0)
+    return fail(B200_E_ARG, "b200_moe_combine_norm: need H %% 8 == 0 (H=%d K=%d)", H, K);
+  if (T == 0) return 0;
+  launch_k(moe_combine_norm_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream),
+           static_cast<const bf16*>(cache), static_cast<const bf16*>(x), static_cast<const bf16*>(gate_w), pos, T, H, K,
+           static_cast<bf16*>(out), static_cast<bf16*>(residual), static_cast<const bf16*>(norm_w), eps,
+           static_cast<bf16*>(normed));
+  return launch_status("b200_moe_combine_norm");
 }

@@ -651,12 +651,15 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
 
 // ---- LM head shard with fused argmax ------------------------------------------------------------------
 namespace b200 {
-__global__ void lmhead_finish_kernel(const unsigned long long* __restrict__ keys, int parts, int T,
-                                     float* __restrict__ max_out, int32_t* __restrict__ idx_out) {
-  // one warp per token: max over the (tile, warp) partial keys
-  const int t = blockIdx.x, lane = threadIdx.x;
+__global__ void __launch_bounds__(256) lmhead_finish_kernel(const unsigned long long* __restrict__ keys, int parts, int T,
+                                                            float* __restrict__ max_out, int32_t* __restrict__ idx_out) {
+  // one CTA per token: max over the (tile, warp) partial keys
+  __shared__ unsigned long long red[8];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+  pdl_wait();
+  pdl_launch();
   unsigned long long k = 0ull;
-  for (int i = lane; i < parts; i += 32) {
+  for (int i = tid; i < parts; i += 256) {
     const unsigned long long v = keys[static_cast<size_t>(i) * T + t];
     k = v > k ? v : k;
   }
@@ -665,7 +668,10 @@ __global__ void lmhead_finish_kernel(const unsigned long long* __restrict__ keys
     const unsigned long long v = __shfl_xor_sync(FULL_MASK, k, o);
     k = v > k ? v : k;
   }
-  if (lane != 0) return;
+  if (lane == 0) red[tid >> 5] = k;
+  __syncthreads();
+  if (tid != 0) return;
+  for (int w = 1; w < 8; ++w) k = red[w] > k ? red[w] : k;
   const uint32_t m = static_cast<uint32_t>(k >> 32);
   float v;
   if (m <= 1u)
@@ -766,7 +772,8 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   a.lm_shard_lo = shard_lo;
   const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
   moe_gemm_f8_kernel<MODE_LM><<<grid, F8_THREADS, F8Cfg<MODE_LM>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
-  lmhead_finish_kernel<<<T, 32, 0, st>>>(keys, a.mtiles * 4, T, max_out, idx_out);
+  launch_k(lmhead_finish_kernel, dim3(T), dim3(256), 0, st, static_cast<const unsigned long long*>(keys), a.mtiles * 4, T,
+           max_out, idx_out);
   return launch_status("b200_lmhead_argmax");
 }
 

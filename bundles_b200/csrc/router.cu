@@ -17,68 +17,105 @@
 namespace b200 {
 
 constexpr int RT_TOK = 64, RT_EXP = 64, RT_SLICE = 128, RT_THREADS = 256, RT_PITCH = RT_SLICE + 4;
-constexpr int RT_SMEM = 2 * RT_TOK * RT_PITCH * 4;
+constexpr int RT_XPITCH = RT_SLICE + 8;  // bf16 elements per staged x row (272 bytes: 16-byte aligned, rows on different banks)
+constexpr int RT_WBUF = RT_EXP * RT_PITCH * 4, RT_XRAW = RT_TOK * RT_XPITCH * 2, RT_XS = RT_TOK * RT_PITCH * 4;
+constexpr int RT_SMEM = 2 * RT_WBUF + 2 * RT_XRAW + RT_XS;
 
-// One CTA = a 64-token x 64-expert tile of ONE 128-deep k slice: both operand tiles are staged in
-// shared memory as fp32 (rows padded to 132 floats so 16-byte reads of consecutive rows hit
-// different banks), each thread owns 4 tokens x 4 experts and runs their 16 fma chains over the
-// slice in ascending k.  Slice partials go to `part[s][t][e]`; the top-k kernel adds them in slice
-// order.  grid (ceil(T/64), E/64, H/128).
-__global__ void __launch_bounds__(RT_THREADS) router_partials_kernel(const bf16* __restrict__ x,
-                                                                     const float* __restrict__ wr, int T, int H,
-                                                                     int E, float* __restrict__ part) {
-  extern __shared__ float rt_smem[];
-  float* xs = rt_smem;                       // [64][132]
-  float* ws = rt_smem + RT_TOK * RT_PITCH;   // [64][132]
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// A unit of work is a 64-token x 64-expert tile of ONE 128-deep k slice.  Persistent CTAs (one per SM) take
+// units b, b + grid, ...: the next unit's operand tiles stream into shared memory with cp.async while the
+// current one is computed, so the FMA pipe never waits for a staging round trip and the last wave is not
+// a whole wave.  Both tiles are read as fp32 from shared memory (rows padded to 132 floats so 16-byte
+// reads of consecutive rows hit different banks; x is converted from its staged bf16 copy first); each
+// thread owns 4 tokens x 4 experts and runs their 16 fma chains over the slice in ascending k.  Slice
+// partials go to `part[s][t][e]`; the top-k kernel adds them in slice order.
+__global__ void __launch_bounds__(RT_THREADS, 1) router_partials_kernel(const bf16* __restrict__ x,
+                                                                        const float* __restrict__ wr, int T, int H,
+                                                                        int E, float* __restrict__ part) {
+  extern __shared__ __align__(16) uint8_t rt_smem[];
+  auto wbuf = [&](int b) { return reinterpret_cast<float*>(rt_smem + b * RT_WBUF); };
+  auto xraw = [&](int b) { return reinterpret_cast<bf16*>(rt_smem + 2 * RT_WBUF + b * RT_XRAW); };
+  float* xs = reinterpret_cast<float*>(rt_smem + 2 * RT_WBUF + 2 * RT_XRAW);
   const int tid = threadIdx.x;
-  const int t0 = blockIdx.x * RT_TOK, e0 = blockIdx.y * RT_EXP, s = blockIdx.z;
+  const int ttiles = (T + RT_TOK - 1) / RT_TOK, etiles = E / RT_EXP, nslices = H / RT_SLICE;
+  const int nunits = ttiles * etiles * nslices;
   pdl_wait();
   pdl_launch();
-  // stage: 64 rows x 128 k of x (bf16 -> fp32) and of wr
-  for (int i = tid; i < RT_TOK * (RT_SLICE / 8); i += RT_THREADS) {
-    const int r = i >> 4, c = (i & 15) * 8;
-    const int t = min(t0 + r, T - 1);  // rows past T repeat the last row and are dropped at the store
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H + s * RT_SLICE + c));
-    float* d = xs + r * RT_PITCH + c;
-    *reinterpret_cast<float4*>(d) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
-    *reinterpret_cast<float4*>(d + 4) = make_float4(bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w));
-  }
-  for (int i = tid; i < RT_EXP * (RT_SLICE / 4); i += RT_THREADS) {
-    const int r = i >> 5, c = (i & 31) * 4;
-    *reinterpret_cast<float4*>(ws + r * RT_PITCH + c) =
-        __ldg(reinterpret_cast<const float4*>(wr + static_cast<size_t>(e0 + r) * H + s * RT_SLICE + c));
-  }
-  __syncthreads();
-  const int ty = tid >> 4, tx = tid & 15;  // tokens ty + 16 i, experts tx + 16 j
-  float acc[4][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-#pragma unroll 4
-  for (int k = 0; k < RT_SLICE; k += 4) {
-    float4 xv[4], wv[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) xv[i] = *reinterpret_cast<const float4*>(xs + (ty + 16 * i) * RT_PITCH + k);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const float4*>(ws + (tx + 16 * j) * RT_PITCH + k);
+  // unit -> (slice, token tile, expert tile), expert tile fastest
+  auto issue = [&](int u, int buf) {
+    const int et = u % etiles, tt = (u / etiles) % ttiles, s = u / (etiles * ttiles);
+    const int t0 = tt * RT_TOK, e0 = et * RT_EXP;
+    for (int i = tid; i < RT_EXP * (RT_SLICE / 4); i += RT_THREADS) {
+      const int r = i >> 5, c = (i & 31) * 4;
+      cp_async16(wbuf(buf) + r * RT_PITCH + c, wr + static_cast<size_t>(e0 + r) * H + s * RT_SLICE + c);
+    }
+    for (int i = tid; i < RT_TOK * (RT_SLICE / 8); i += RT_THREADS) {
+      const int r = i >> 4, c = (i & 15) * 8;
+      const int t = min(t0 + r, T - 1);  // rows past T repeat the last row and are dropped at the store
+      cp_async16(xraw(buf) + r * RT_XPITCH + c, x + static_cast<size_t>(t) * H + s * RT_SLICE + c);
+    }
+    cp_async_commit();
+  };
+  int buf = 0;
+  if (static_cast<int>(blockIdx.x) < nunits) issue(blockIdx.x, 0);
+  for (int u = blockIdx.x; u < nunits; u += gridDim.x, buf ^= 1) {
+    const int next = u + gridDim.x;
+    if (next < nunits) {
+      issue(next, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();  // this unit's tiles have landed (every thread waited for its own copies)
+    for (int i = tid; i < RT_TOK * (RT_SLICE / 8); i += RT_THREADS) {
+      const int r = i >> 4, c = (i & 15) * 8;
+      const uint4 v = *reinterpret_cast<const uint4*>(xraw(buf) + r * RT_XPITCH + c);
+      float* d = xs + r * RT_PITCH + c;
+      *reinterpret_cast<float4*>(d) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+      *reinterpret_cast<float4*>(d + 4) = make_float4(bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w));
+    }
+    __syncthreads();
+    const float* ws = wbuf(buf);
+    const int ty = tid >> 4, tx = tid & 15;  // tokens ty + 16 i, experts tx + 16 j
+    float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        acc[i][j] = __fmaf_rn(xv[i].x, wv[j].x, acc[i][j]);
-        acc[i][j] = __fmaf_rn(xv[i].y, wv[j].y, acc[i][j]);
-        acc[i][j] = __fmaf_rn(xv[i].z, wv[j].z, acc[i][j]);
-        acc[i][j] = __fmaf_rn(xv[i].w, wv[j].w, acc[i][j]);
-      }
-  }
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
+    for (int k = 0; k < RT_SLICE; k += 4) {
+      float4 xv[4], wv[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int t = t0 + ty + 16 * i;
-    if (t < T)
+      for (int i = 0; i < 4; ++i) xv[i] = *reinterpret_cast<const float4*>(xs + (ty + 16 * i) * RT_PITCH + k);
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        part[(static_cast<size_t>(s) * T + t) * E + e0 + tx + 16 * j] = acc[i][j];
+      for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const float4*>(ws + (tx + 16 * j) * RT_PITCH + k);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = __fmaf_rn(xv[i].x, wv[j].x, acc[i][j]);
+          acc[i][j] = __fmaf_rn(xv[i].y, wv[j].y, acc[i][j]);
+          acc[i][j] = __fmaf_rn(xv[i].z, wv[j].z, acc[i][j]);
+          acc[i][j] = __fmaf_rn(xv[i].w, wv[j].w, acc[i][j]);
+        }
+    }
+    const int et = u % etiles, tt = (u / etiles) % ttiles, s = u / (etiles * ttiles);
+    const int t0 = tt * RT_TOK, e0 = et * RT_EXP;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = t0 + ty + 16 * i;
+      if (t < T)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          part[(static_cast<size_t>(s) * T + t) * E + e0 + tx + 16 * j] = acc[i][j];
+    }
+    __syncthreads();  // xs and this unit's buffers are free for the copies issued in the next iteration
   }
 }
 
@@ -429,7 +466,8 @@ extern "C" int b200_router(const void* x, const float* wr, const float* bias, in
   }
   float* part = static_cast<float*>(scratch);
   const int nslices = H / RT_SLICE;
-  dim3 grid((T + RT_TOK - 1) / RT_TOK, E / RT_EXP, nslices);
+  const int nunits = ((T + RT_TOK - 1) / RT_TOK) * (E / RT_EXP) * nslices;
+  dim3 grid(nunits < sm_count() ? nunits : sm_count());
   launch_k(router_partials_kernel, grid, dim3(RT_THREADS), RT_SMEM, st, static_cast<const bf16*>(x), wr, T, H, E, part);
   const int rb = flags & 1;
   const int pl = (E + 127) / 128;

@@ -25,6 +25,7 @@ class MoeBlockW8A8:
         self.H = weights.w13.shape[-1]
         self._ws = {}
         self._graphs = {}
+        self._pipes = {}
         self.use_graph = use_graph
         self.status = ops.new_status(wr.device)
         self.launches_per_call = 8  # gate, top-k, lists, quant+permute, up, h-quant, down, combine
@@ -85,6 +86,60 @@ class MoeBlockW8A8:
                                out=b["out"])
 
     __call__ = forward
+
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """Host-to-host form for a serving loop: `x_host` (pinned bf16 [T, H]) is copied in, the block runs, and
+        the result lands in `out_host` (pinned) asynchronously.  Consecutive calls are pipelined over two sets of
+        device buffers: the copy-in of call i + 1 and the copy-out of call i - 1 run on their own streams
+        beside the kernels of call i.  The result of a call is complete after `synchronize_host()` (or any
+        later device synchronisation); `x_host` may be reused once the call after next has been issued."""
+        T = x_host.shape[0]
+        pipe = self._pipes.get(T)
+        dev = self.wr.device
+        main = torch.cuda.current_stream(dev)
+        if pipe is None:
+            pipe = dict(i=0, s_in=torch.cuda.Stream(dev), s_out=torch.cuda.Stream(dev), slots=[])
+            for _ in range(2):
+                xs = torch.empty(T, self.H, dtype=torch.bfloat16, device=dev)
+                xs.copy_(x_host)
+                self._forward_eager(xs, None)              # warm-up: one-time attribute set-up, buffers
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    out = self._forward_eager(xs, None).clone()   # each slot keeps its own result buffer
+                pipe["slots"].append(dict(graph=graph, xs=xs, out=out, in_ready=torch.cuda.Event(),
+                                          done=torch.cuda.Event(), out_free=torch.cuda.Event(), used=False))
+            self._pipes[T] = pipe
+        slot = pipe["slots"][pipe["i"] & 1]
+        pipe["i"] += 1
+        with torch.cuda.stream(pipe["s_in"]):
+            if slot["used"]:
+                pipe["s_in"].wait_event(slot["done"])      # the call two back has read this input buffer
+            slot["xs"].copy_(x_host, non_blocking=True)
+            slot["in_ready"].record()
+        main.wait_event(slot["in_ready"])
+        if slot["used"]:
+            main.wait_event(slot["out_free"])              # its result has left the device
+        slot["graph"].replay()
+        slot["done"].record(main)
+        with torch.cuda.stream(pipe["s_out"]):
+            pipe["s_out"].wait_event(slot["done"])
+            out_host.copy_(slot["out"], non_blocking=True)
+            slot["out_free"].record()
+        slot["used"] = True
+
+    def join_host(self) -> None:
+        """Make the current stream wait for every pending copy-out of `forward_host` (no host blocking)."""
+        main = torch.cuda.current_stream(self.wr.device)
+        for pipe in self._pipes.values():
+            for slot in pipe["slots"]:
+                if slot["used"]:
+                    main.wait_event(slot["out_free"])
+
+    def synchronize_host(self) -> None:
+        """Block until every result handed to `forward_host` has landed in its host buffer."""
+        for pipe in self._pipes.values():
+            pipe["s_out"].synchronize()
 
     def _workspace(self, T, K, device):
         return ops.moe_w8a8_workspace(T, self.H, self.I, K, device)

@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import B200Error, MoeLists, MoeWeights, check
 
-__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_w8a8_ep", "moe_fp8", "moe_combine", "attn_front", "attn_verify", "dense_fp8", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
+__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_w8a8_ep", "moe_fp8", "moe_combine", "moe_combine_norm", "attn_front", "attn_verify", "dense_fp8", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
            "new_status", "read_status", "B200Error"]
 
 
@@ -244,6 +244,23 @@ def attn_front(x, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, eps=1e-6, out_
                                      cos_sin.shape[0], float(eps), 1 if out_fp8 else 0, _p(q), _p(gate), _p(k), _p(v),
                                      _p(ws), ws.numel(), _p(status), _stream()), "b200_attn_front")
     return q, gate, k, v
+
+
+def moe_combine_norm(cache, x, gate_w, top_k, residual, norm_w, eps=1e-6, pos=None, out=None, normed=None):
+    """Combine with the next layer's input norm folded in (reference: qk_route.combine_norm): `residual` is updated
+    in place to bf16(out + residual); returns (out, normed)."""
+    _need(cache, torch.bfloat16, "cache", 2)
+    _need(x, torch.bfloat16, "x", 2)
+    _need(residual, torch.bfloat16, "residual", 2)
+    _need(norm_w, torch.bfloat16, "norm_w", 1)
+    T, H = x.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    if normed is None:
+        normed = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    check(_lib.lib().b200_moe_combine_norm(_p(cache), _p(x), _p(gate_w), _p(pos), T, H, int(top_k), _p(out), _p(residual),
+                                           _p(norm_w), float(eps), _p(normed), _stream()), "b200_moe_combine_norm")
+    return out, normed
 
 
 def attn_verify(q, gate, k_new, v_new, kcache, vcache, page_table, seqlens, scale=None, splits=None, out=None, ws=None,

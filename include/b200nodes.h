@@ -187,6 +187,14 @@ int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_local, const b
 int b200_moe_combine(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T, int H, int K,
                      void* out, void* stream);
 
+/* The combine with the next layer's input norm folded in, as combine_norm_kernel does (qk_route.cu:686-820,
+ * the tail at :779-819): out as above (may be NULL when only the normed row is wanted);
+ * residual[t] <- r = bf16(out[t] + residual[t]); normed[t] = bf16(r * rsqrt(mean r^2 + eps) * (1 + norm_w)).
+ * Bit-identical to b200_moe_combine followed by b200_add_rmsnorm. */
+int b200_moe_combine_norm(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T, int H,
+                          int K, void* out, void* residual, const void* norm_w, float eps, void* normed,
+                          void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Gated DeltaNet speculative verify.  Replaces qk_gdn_verify.gdn_verify_fused
  * (qk_gdn_verify.cu:293, gdn_fused.py:37-57) with an explicit state instead of the ReplaySSM

@@ -53,7 +53,7 @@ def attn_verify(q, gate, k_new, v_new, kcache, vcache, page_table, seqlens, scal
                     m = s.max()
                     p = np.exp2((s - m).astype(np.float64))
                     p16 = p.astype(np.float16).astype(np.float64)
-                    o = (p16 @ V[:lim + 1]) / p16.sum()
+                    o = (p16 @ V[:lim + 1]) / p.sum()  # the row sum takes the unrounded probabilities (:290-302)
                     ob = bf16_round(o.astype(F32))
                     gv = np.asarray(gate[r * NT + t, hq], dtype=F32)
                     sig = (F32(1.0) / (F32(1.0) + np.exp(-gv, dtype=F32))).astype(F32)

@@ -133,3 +133,33 @@ def test_block_class_graph_replay_matches_eager_and_oracle():
     ref_out, _ = _oracle(cfg, ids, wts, 10)
     ok, err, nbad = close_bf16(bf16_to_np(eager), ref_out)
     assert ok, (err, nbad)
+
+
+def test_combine_norm_equals_combine_then_add_rmsnorm():
+    """The fused combine + next-layer norm is bit-identical to the two separate kernels, padding rows included,
+    and matches the oracle's combine followed by its add + RMSNorm."""
+    from oracle import attn_lmhead as oal
+    g = torch.Generator().manual_seed(77)
+    T, K, H = 37, 10, 2048
+    cache = (torch.randn(T * (K + 1), H, generator=g) * 0.3).to(torch.bfloat16).to(dev())
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev())
+    gate_w = (torch.randn(H, generator=g) * 0.05).to(torch.bfloat16).to(dev())
+    res = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev())
+    nw = (torch.randn(H, generator=g) * 0.1).to(torch.bfloat16).to(dev())
+    pos = torch.arange(1, T + 1, dtype=torch.int64)
+    pos[5] = 0
+    pos = pos.to(dev())
+    out_a = ops.moe_combine(cache, x, gate_w, K, pos)
+    res_a = res.clone()
+    y_a = ops.add_rmsnorm(out_a, res_a, nw, 1e-6)
+    res_b = res.clone()
+    out_b, y_b = ops.moe_combine_norm(cache, x, gate_w, K, res_b, nw, 1e-6, pos)
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, out_b) and torch.equal(res_a, res_b) and torch.equal(y_a, y_b)
+    valid = pos.cpu().numpy() != 0
+    want_out = omoe.combine(bf16_to_np(cache), bf16_to_np(x), bf16_to_np(gate_w), K, valid)
+    want_y, want_r = oal.add_rmsnorm(want_out, bf16_to_np(res), bf16_to_np(nw), 1e-6)
+    ok, err, nbad = close_bf16(bf16_to_np(y_b), want_y)
+    assert ok, f"normed: max err {err}, {nbad} outside tolerance"
+    ok, err, nbad = close_bf16(bf16_to_np(res_b), want_r)
+    assert ok, f"residual: max err {err}, {nbad} outside tolerance"
