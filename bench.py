@@ -126,9 +126,11 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def other_kernels(dev, steps, warmup):
+def other_kernels(dev, steps, warmup, only=None):
     """The other kernels of the hot path at their named configurations, each timed alone with CUDA events
-    (inputs larger than L2 or rotated over several copies so that every launch reads HBM)."""
+    (inputs larger than L2 or rotated over several copies so that every launch reads HBM).  `only`: run a single
+    entry with plain launches instead of graph replays (the target of an ncu capture; `attn_verify` then runs a
+    16-request case, 134 MB of KV)."""
     import math
     import torch
     from bundles_b200 import ops, synth
@@ -136,7 +138,10 @@ def other_kernels(dev, steps, warmup):
     hbm, which = peaks()
     out = {}
 
-    def timed(fn, n=steps, calls=1, graph=True):
+    def want(name):
+        return only is None or only == name
+
+    def timed(fn, n=steps, calls=1, graph=only is None):
         """ms per call of fn.  The calls are captured into a CUDA graph (`calls` of them, e.g. one per
         rotating buffer) so that host-side launch cost does not hide the device time."""
         for _ in range(max(warmup, calls)):
@@ -163,6 +168,8 @@ def other_kernels(dev, steps, warmup):
     # dense fp8 GEMM peak of this GPU (cuBLASLt through torch._scaled_mm, 8192^3), the tensor-pipe denominator
     fp8_peak = None
     try:
+        if only is not None:
+            raise RuntimeError("skipped in single-kernel mode")
         a = torch.randn(8192, 8192, device=dev).to(torch.float8_e4m3fn)
         b = torch.randn(8192, 8192, device=dev).to(torch.float8_e4m3fn).t()
         one = torch.ones((), device=dev)
@@ -175,11 +182,28 @@ def other_kernels(dev, steps, warmup):
     out["fp8_dense_tflops_measured"] = fp8_peak
 
     # Gated DeltaNet verify: B = 32 x 4 drafts; 4 rotating copies of the state (268 MB > L2)
+    st = ops.new_status(dev)
+    it = [0]
+    if want("gdn_verify"):
+        _gdn_entry(dev, ops, synth, timed, st, it, out, hbm, which)
+    for name, Bv in (("attn_verify_b64", 64), ("attn_verify_b8", 8), ("attn_verify", 16)):
+        if not (want(name) and (only is not None or name != "attn_verify")):
+            continue
+        _attn_verify_entry(dev, ops, synth, timed, st, out, hbm, which, name, Bv)
+    torch.cuda.empty_cache()
+    if want("attn_front"):
+        _attn_front_entry(dev, ops, synth, timed, st, out, fp8_peak)
+    if want("lmhead_shard_argmax"):
+        _lmhead_entry(dev, ops, synth, timed, st, it, out, hbm)
+    if want("moe_fp8_t16") or want("router"):
+        _moe_fp8_router_entry(dev, ops, synth, timed, st, out, hbm, want)
+    return out
+
+
+def _gdn_entry(dev, ops, synth, timed, st, it, out, hbm, which):
     g = {k: v.to(dev) for k, v in synth.gdn().items()}
     states = [g["state"].clone() for _ in range(4)]
     convs = [g["conv_state"].clone() for _ in range(4)]
-    st = ops.new_status(dev)
-    it = [0]
 
     def gdn_step():
         i = it[0] % 4
@@ -196,9 +220,12 @@ def other_kernels(dev, steps, warmup):
                          "frac": gbytes / ms / 1e6 / hbm, "peak_source": which, "status": ops.read_status(st)}
     del states, convs, g
 
+
+def _attn_verify_entry(dev, ops, synth, timed, st, out, hbm, which, name, Bv):
     # attention verify core: 64 requests x 8192 tokens of context (537 MB of e4m3 KV, read once per step), and
     # the 8-request share of one GPU when the batch is sharded over 8 (9 splits per (request, kv head))
-    for name, Bv in (("attn_verify_b64", 64), ("attn_verify_b8", 8)):
+    import torch
+    if True:
         try:
             av = synth.attn_verify(B=Bv, ctx=8192, device=dev)
             spl = ops._lib.lib().b200_attn_verify_splits(Bv)
@@ -219,9 +246,11 @@ def other_kernels(dev, steps, warmup):
             del av, ws_av, out_av
         except Exception as exc:  # noqa: BLE001
             out[name] = {"error": repr(exc)[:160]}
-    torch.cuda.empty_cache()
 
+
+def _attn_front_entry(dev, ops, synth, timed, st, out, fp8_peak):
     # fused attention projection front: T = 4096
+    import torch
     a = {k: v.to(dev) for k, v in synth.attn().items()}
     half = 32
     inv = torch.pow(torch.tensor(1e7, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / 64)
@@ -236,6 +265,8 @@ def other_kernels(dev, steps, warmup):
                          "includes": "activation quantiser launch", "status": ops.read_status(st)}
     del a
 
+
+def _lmhead_entry(dev, ops, synth, timed, st, it, out, hbm):
     # LM head shard (1/8 of the vocabulary), T = 64, 4 rotating weight copies (156 MB > L2)
     lm = synth.lmhead(T=64, V=19072)
     x = lm["x"].to(dev)
@@ -255,7 +286,10 @@ def other_kernels(dev, steps, warmup):
                                   "frac": lb / ms / 1e6 / hbm, "status": ops.read_status(st)}
     del wcopies
 
+
+def _moe_fp8_router_entry(dev, ops, synth, timed, st, out, hbm, want):
     # fp8 MoE block, T = 16 (single block configuration)
+    import torch
     c = {k: (v.to(dev) if v is not None else None) for k, v in synth.moe_fp8(E=512).items()}
     w = ops.MoeW8A8Weights(c["w13"], c["s13"], c["w2"], c["s2"], c["sh13"], c["shs13"], c["sh2"], c["shs2"])
     _, ids, wts = ops.router(c["x"], c["wr"], 10)
@@ -263,21 +297,23 @@ def other_kernels(dev, steps, warmup):
     ops.build_lists(ids, wts, lists)
     wsb = ops.moe_fp8_workspace(16, 2048, 512, 10, dev)
     cache = torch.zeros(16 * 11, 2048, dtype=torch.bfloat16, device=dev)
-    ms = timed(lambda: ops.moe_fp8(c["x"], w, lists, cache=cache, ws=wsb, status=st))
-    act = int((lists.counts > 0).sum().item())
-    fb = act * (3 * 2048 * 512 + 768 * 4) + 16 * 2048 * 4
-    out["moe_fp8_t16"] = {"config": "T=16, E=512, top-10, fp8 128x128 block scales (4 launches)", "ms": ms,
+    if want("moe_fp8_t16"):
+        ms = timed(lambda: ops.moe_fp8(c["x"], w, lists, cache=cache, ws=wsb, status=st))
+        act = int((lists.counts > 0).sum().item())
+        fb = act * (3 * 2048 * 512 + 768 * 4) + 16 * 2048 * 4
+        out["moe_fp8_t16"] = {"config": "T=16, E=512, top-10, fp8 128x128 block scales (4 launches)", "ms": ms,
                           "active_experts": act, "algorithmic_bytes": fb, "achieved_gbs": fb / ms / 1e6,
                           "bound": "hbm", "frac": fb / ms / 1e6 / hbm,
                           "note": "the same weights every step: partly L2-resident when < 126 MB",
                           "status": ops.read_status(st)}
     # router alone at T = 256 and T = 64
     for Tn in (256, 64):
+        if not want("router"):
+            break
         xr = torch.randn(Tn, 2048, device=dev).to(torch.bfloat16)
         scr = ops.router_scratch(Tn, 2048, 512, dev)
         ms = timed(lambda: ops.router(xr, c["wr"], 10, scratch=scr, want_logits=False))
         out[f"router_t{Tn}"] = {"ms": ms, "flops": 2 * Tn * 512 * 2048, "bytes": 4 * 512 * 2048 + 2 * Tn * 2048}
-    return out
 
 
 def run_expert_parallel(args, rank, world, dev, cfg):
@@ -363,7 +399,16 @@ def main():
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel measurements of the other rows")
     ap.add_argument("--parallel", default="ep", choices=["ep", "replicas"],
                     help="N > 1: expert-parallel (experts split over ranks) or independent replicas")
+    ap.add_argument("--only-kernel", default=None,
+                    choices=["gdn_verify", "attn_verify", "attn_front", "lmhead_shard_argmax", "moe_fp8_t16", "router"],
+                    help="run one entry of `kernels` alone with plain launches (a small target for an ncu capture) and exit")
     args = ap.parse_args()
+    if args.only_kernel:
+        import torch
+        torch.cuda.set_device(0)
+        print(json.dumps({"kernels": other_kernels(torch.device("cuda", 0), min(args.steps, 3), 1, only=args.only_kernel)}),
+              flush=True)
+        return
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -15,8 +15,9 @@
 //
 // HBM-bound: 64 KB in and (when accepted > 0) 64 KB out per (sequence, value head).  One CTA per
 // unit; the tile moves by TMA tensor copies each way (128-byte swizzle, the layout the MMA reads),
-// three CTAs share an SM so the copies of one overlap the arithmetic of the others.  The two value heads of a key head run as a
-// 2-CTA cluster: both read the q/k conv state, meet at a cluster barrier, then rank 0 rolls it.
+// three CTAs share an SM so the copies of one overlap the arithmetic of the others; the CTAs are persistent
+// and walk the units.  The two value heads of a key head run as a 2-CTA cluster: both read the q/k conv
+// state, meet at a cluster barrier, then rank 0 rolls it.
 #include "common.cuh"
 #include "host.h"
 
@@ -124,10 +125,11 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   extern __shared__ uint8_t smem_raw[];
   GdnSmem& sm = *reinterpret_cast<GdnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int hv = blockIdx.x, hk = hv >> 1, b = blockIdx.y;
-  int n_acc = p.accepted[b];
-  n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
-  const int srow0 = (b * G_HV + hv) * G_D;  // first row of this unit in the [B*32*128, 128] view of the state
+  // Persistent clusters: cluster c takes (sequence, key head) pairs c, c + #clusters, ...; its two CTAs take the
+  // pair's two value heads.  A unit's prologue (conv inputs, gates, norms: global round trips) then runs while the
+  // previous unit's state tile is still leaving shared memory, and no wave of CTAs waits for the slowest of
+  // the wave before.
+  const int rank = blockIdx.x & 1, ncl = gridDim.x >> 1, npairs = p.B * G_HK;
 
   if (tid == 0) {
     mbar_init(&sm.bar_load, 1);
@@ -141,7 +143,19 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_slot;
+  bool ok = true;
+  uint32_t par = 0;  // parity of this unit's phase of both mbarriers
+  for (int pair = blockIdx.x >> 1; pair < npairs; pair += ncl, par ^= 1u) {
+  if (!ok) {  // after an abandoned wait the CTA only keeps its partner's cluster barriers company
+    cluster_sync();
+    continue;
+  }
+  const int b = pair / G_HK, hk = pair - b * G_HK, hv = 2 * hk + rank;
+  int n_acc = p.accepted[b];
+  n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
+  const int srow0 = (b * G_HV + hv) * G_D;  // first row of this unit in the [B*32*128, 128] view of the state
   if (tid == 0) {
+    bulk_wait_read_all();  // the previous unit's tile has left shared memory
     mbar_expect_tx(&sm.bar_load, G_TILE_BYTES);
 #pragma unroll
     for (int sub = 0; sub < 4; ++sub) tma_load_2d(sm.S[sub], &tmS, 32 * sub, srow0, &sm.bar_load);
@@ -215,7 +229,7 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   // ---- S [q | k]: sixteen tf32 MMAs (M = 128 state rows, N = 16, K = 8 each) into 16 TMEM columns ----
   bool landed = true;
   if (tid == 0) {
-    landed = mbar_wait(&sm.bar_load, 0, &sm.abort_flag, p.status, ST_WAIT_STATE);
+    landed = mbar_wait(&sm.bar_load, par, &sm.abort_flag, p.status, ST_WAIT_STATE);
     if (landed) {
       tc_fence_after();
       const uint32_t idesc = umma_idesc(UMMA_C_F32, UMMA_AB_TF32, 16);
@@ -278,8 +292,9 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     }
   }
   __syncthreads();
-  const bool ok = mbar_wait(&sm.bar_load, 0, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
-                  mbar_wait(&sm.bar_mma, 0, &sm.abort_flag, p.status, ST_WAIT_TMEM_FULL);
+  ok = mbar_wait(&sm.bar_load, par, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
+       mbar_wait(&sm.bar_mma, par, &sm.abort_flag, p.status, ST_WAIT_TMEM_FULL);
+  ok = __syncthreads_and(ok);  // one verdict for the CTA
   tc_fence_after();
 
   // ---- per value row: R, D = (I + A)^-1 R, outputs; gated RMSNorm ----
@@ -373,14 +388,16 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
         bulk_commit();
       }
     }
-    if (tid == 0) bulk_wait_read_all();  // the tile has left shared memory; the writes complete with the grid
   }
   if (!ok && tid == 0) {
     // an abandoned wait: give the state copy a bounded grace period before the CTA's memory goes away
     const unsigned long long t0 = globaltimer();
-    while (!mbar_try(&sm.bar_load, 0) && globaltimer() - t0 < 20000000ull) {
+    while (!mbar_try(&sm.bar_load, par) && globaltimer() - t0 < 20000000ull) {
     }
   }
+  __syncthreads();  // every buffer of the unit is free for the next one
+  }  // units
+  if (tid == 0) bulk_wait_read_all();  // the last tile has left shared memory; the writes complete with the grid
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
@@ -415,6 +432,9 @@ extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, 
     cudaFuncSetAttribute(gdn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     attr_done[dev] = true;
   }
-  gdn_verify_kernel<<<dim3(G_HV, B), G_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tmS, p);
+  // three CTAs per SM (shared memory), in clusters of two
+  int ncl = (sm_count() * 3) / 2;
+  if (ncl > B * G_HK) ncl = B * G_HK;
+  gdn_verify_kernel<<<dim3(2 * ncl), G_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tmS, p);
   return launch_status("b200_gdn_verify");
 }

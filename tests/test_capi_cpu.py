@@ -57,6 +57,17 @@ def test_argument_checks_return_codes(lib):
     assert lib.b200_moe_w8a8_workspace_bytes(256, 2048, 512, 10) > 256 * 11 * 2048
     assert lib.b200_moe_combine(None, None, None, None, 1, 2048, 10, None, None) == -1
     assert lib.b200_gdn_verify(*([None] * 11), 1e-6, 1, None, None, None) == -1
+    # attention verify: null pointers, bad split count, workspace too small, misaligned cache
+    assert lib.b200_attn_verify(*([None] * 6), 8, None, 4, None, 2, 0.0625, 1, None, None, 0, None, None) == -1
+    av = [one] * 6 + [8, one, 4, one, 2, 0.0625]
+    assert lib.b200_attn_verify(*av, 65, one, one, 1 << 30, None, None) == -1
+    assert lib.b200_attn_verify(*av, 2, one, one, 64, None, None) == -3
+    bad = [one, one, one, one, C.c_void_p(4100), one, 8, one, 4, one, 2, 0.0625]
+    assert lib.b200_attn_verify(*bad, 2, one, one, 1 << 30, None, None) == -2
+    assert lib.b200_attn_verify_workspace_bytes(2, 3) == 2 * 2 * 3 * (32 * 256 * 4 + 2 * 32 * 4)
+    assert lib.b200_attn_verify_splits(0) == 0
+    assert lib.b200_moe_combine_norm(None, None, None, None, 1, 2048, 10, None, None, None, 1e-6, None, None) == -1
+    assert lib.b200_moe_combine_norm(one, one, None, None, 1, 2047, 10, None, one, one, 1e-6, one, None) == -1
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
