@@ -343,7 +343,7 @@ def run_expert_parallel(args, rank, world, dev, cfg):
     x_host = x_dev.cpu().pin_memory()
     out_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
 
-    def timed(fn):
+    def timed(fn, tail=None):
         for _ in range(args.warmup):
             fn()
         dist.barrier()
@@ -352,6 +352,8 @@ def run_expert_parallel(args, rank, world, dev, cfg):
         e0.record()
         for _ in range(args.steps):
             fn()
+        if tail is not None:
+            tail()  # copies the steps left on other streams join the timed stream before the closing event
         e1.record()
         dist.barrier()
         torch.cuda.synchronize()
@@ -364,10 +366,13 @@ def run_expert_parallel(args, rank, world, dev, cfg):
         sampler.start()
     ms_step = timed(lambda: ep(x_dev))
 
-    def e2e_step():
-        out_host.copy_(ep(x_host.to(dev, non_blocking=True)), non_blocking=True)
+    if hasattr(ep, "forward_host"):
+        ms_e2e = timed(lambda: ep.forward_host(x_host, out_host), tail=ep.join_host)
+    else:
+        def e2e_step():
+            out_host.copy_(ep(x_host.to(dev, non_blocking=True)), non_blocking=True)
 
-    ms_e2e = timed(e2e_step)
+        ms_e2e = timed(e2e_step)
     clocks = sampler.stop() if rank == 0 else None
     status = torch.tensor([ops.read_status(backend.status)], device=dev)
     dist.all_reduce(status, op=dist.ReduceOp.MAX)

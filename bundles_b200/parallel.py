@@ -161,6 +161,7 @@ class FusedExpertParallelMoe:
         self.x_static = torch.empty(tokens_per_rank, hidden, dtype=torch.bfloat16, device=dev)
         self.out = torch.empty(tokens_per_rank, hidden, dtype=torch.bfloat16, device=dev)
         self.use_graph, self.graph = use_graph, None
+        self._pipe = None
         self.launches_per_call = 8   # router x2, lists, quantise, up, h-quantise, down, combine (+2 NCCL, 2 barriers)
 
     def _step(self):
@@ -197,6 +198,47 @@ class FusedExpertParallelMoe:
         return self.out
 
     __call__ = forward
+
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """Host-to-host form: this rank's pinned `x_host` in, its pinned `out_host` out, asynchronously.  The
+        copy-in of call i + 1 and the copy-out of call i - 1 run on their own streams beside the step of call i
+        (two staging buffers each way; the step itself keeps its single captured graph)."""
+        dev = self.x_static.device
+        main = torch.cuda.current_stream(dev)
+        if self._pipe is None:
+            mk = lambda: torch.empty_like(self.x_static)
+            self._pipe = dict(i=0, s_in=torch.cuda.Stream(dev), s_out=torch.cuda.Stream(dev),
+                              slots=[dict(x=mk(), out=mk(), in_ready=torch.cuda.Event(), taken=torch.cuda.Event(),
+                                          done=torch.cuda.Event(), out_free=torch.cuda.Event(), used=False)
+                                     for _ in range(2)])
+        pipe = self._pipe
+        slot = pipe["slots"][pipe["i"] & 1]
+        pipe["i"] += 1
+        with torch.cuda.stream(pipe["s_in"]):
+            if slot["used"]:
+                pipe["s_in"].wait_event(slot["taken"])     # the step two back has taken its input out of this buffer
+            slot["x"].copy_(x_host, non_blocking=True)
+            slot["in_ready"].record()
+        main.wait_event(slot["in_ready"])
+        out = self.forward(slot["x"])
+        slot["taken"].record(main)
+        if slot["used"]:
+            main.wait_event(slot["out_free"])
+        slot["out"].copy_(out, non_blocking=True)
+        slot["done"].record(main)
+        with torch.cuda.stream(pipe["s_out"]):
+            pipe["s_out"].wait_event(slot["done"])
+            out_host.copy_(slot["out"], non_blocking=True)
+            slot["out_free"].record()
+        slot["used"] = True
+
+    def join_host(self) -> None:
+        """Make the current stream wait for every pending copy-out of `forward_host` (no host blocking)."""
+        if self._pipe is not None:
+            main = torch.cuda.current_stream(self.x_static.device)
+            for slot in self._pipe["slots"]:
+                if slot["used"]:
+                    main.wait_event(slot["out_free"])
 
     def close(self):
         """Drop the captured graph.  Call before `destroy_process_group`: NCCL does not finish
