@@ -506,9 +506,9 @@ def main():
     peak, which = peaks()
     achieved = up_bytes / (ms_up * 1e-3) / 1e9
     # DRAM bytes of one launch of this kernel from an ncu capture of the same workload
-    # (profiles/moe_w8a8_decode_t256.md): read + write = 1.02 x the algorithmic bytes of that launch;
+    # (profiles/moe_w8a8_decode_t256.md): read + write = 1.005 x the algorithmic bytes of that launch;
     # traffic grows with the experts hit, so it is scaled by this launch's algorithmic bytes.
-    traffic = 1.02 * up_bytes
+    traffic = 1.005 * up_bytes
 
     if rank != 0:
         if world > 1:
