@@ -506,7 +506,7 @@ def main():
     peak, which = peaks()
     achieved = up_bytes / (ms_up * 1e-3) / 1e9
     # DRAM bytes of one launch of this kernel from an ncu capture of the same workload
-    # (profiles/moe_w8a8_decode_t256.md): read + write = 1.005 x the algorithmic bytes of that launch;
+    # (summary kept under profiles/): read + write = 1.005 x the algorithmic bytes of that launch;
     # traffic grows with the experts hit, so it is scaled by this launch's algorithmic bytes.
     traffic = 1.005 * up_bytes
 

@@ -29,6 +29,7 @@ PROTOTYPES = {
     "b200_router_static": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
     "b200_moe_max_blocks": (i32, [i32, i32, i32, i32]),
     "b200_moe_build_lists": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, i32, C.POINTER(MoeLists), vp]),
+    "b200_moe_build_lists_range": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, C.POINTER(MoeLists), vp]),
     "b200_moe_w8a8_workspace_bytes": (sz, [i32, i32, i32, i32]),
     "b200_moe_w8a8": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(MoeWeights), C.POINTER(MoeLists), vp, vp, sz, vp,
                             vp, i32, vp, vp]),

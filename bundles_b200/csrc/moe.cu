@@ -45,7 +45,7 @@ __device__ __forceinline__ int q8(float x, float safe) {
 // shared-expert row), scale per row.  256 threads, 8 elements per thread per pass.
 __global__ void __launch_bounds__(256) quant_permute_i8_kernel(const bf16* __restrict__ x, int T, int H, int K,
                                                                const int32_t* __restrict__ row_of_pair,
-                                                               int with_shared, int8_t* __restrict__ xq,
+                                                               int shared_lo, int shared_n, int8_t* __restrict__ xq,
                                                                float* __restrict__ xs) {
   __shared__ float red[8];
   __shared__ int rows[40];
@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(256) quant_permute_i8_kernel(const bf16* __res
   pdl_wait();
   pdl_launch();
   if (tid < K) rows[tid] = row_of_pair[t * K + tid];
-  if (tid == K) rows[K] = with_shared ? T * K + t : -1;
+  if (tid == K) rows[K] = (t >= shared_lo && t < shared_lo + shared_n) ? T * K + t : -1;
   const bf16* xr = x + static_cast<size_t>(t) * H;
   float amax = 0.f;
   for (int c = tid * 8; c < H; c += 256 * 8) {
@@ -750,9 +750,15 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
   }
 
   if (stages == 0) stages = 15;
+  // tokens that get a shared-expert row: all of them, or this rank's own under expert parallelism
+  int shared_lo = 0, shared_n = T;
+  if ((ep_world & 0xff) >= 1) {
+    shared_lo = (ep_world >> 8) * ep_tokens_per_rank;
+    shared_n = ep_tokens_per_rank;
+  }
   if (stages & B200_MOE_STAGE_QUANT)
     launch_k(quant_permute_i8_kernel, dim3(T), dim3(256), 0, st, static_cast<const bf16*>(x), T, H, K, L.row_of_pair,
-             shared ? 1 : 0, xq, xs);
+             shared_lo, shared ? shared_n : 0, xq, xs);
 
   GemmArgs a{};
   a.L = L;

@@ -301,7 +301,7 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
                                                                   const float* __restrict__ wts,
                                                                   const int64_t* __restrict__ pos, int T, int K,
                                                                   int e_lo, int E_local, int block_rows,
-                                                                  int with_shared, int max_blocks, MoeLists L) {
+                                                                  int shared_lo, int shared_n, int max_blocks, MoeLists L) {
   extern __shared__ int lists_smem[];
   pdl_wait();
   pdl_launch();
@@ -357,7 +357,7 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
       }
       c = run;
     } else {
-      c = with_shared ? T : 0;
+      c = shared_n;  // tokens [shared_lo, shared_lo + shared_n) get a shared-expert row
     }
     cnt[tid] = c;
     nb = (c + block_rows - 1) / block_rows;
@@ -395,11 +395,11 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
   const int blks_excl = blks_incl - nb + (warp ? wsum[32 + warp - 1] : 0);
   const int total_blocks = wsum[63];
   if (tid < E1) {
-    off[tid] = tid < E_local ? rows_excl : P;  // the shared expert's rows start after the routed region
+    off[tid] = tid < E_local ? rows_excl : P + shared_lo;  // the shared expert's rows follow the routed region, row P + t for token t
     bstart[tid] = blks_excl;
     L.counts[tid] = c;
     L.offsets[tid] = off[tid];
-    if (tid == E_local) L.offsets[E1] = P + c;
+    if (tid == E_local) L.offsets[E1] = P + shared_lo + c;
   }
   if (tid == 0) L.nblocks[0] = total_blocks <= max_blocks ? total_blocks : 0;
   __syncthreads();
@@ -413,8 +413,8 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
     }
     L.row_of_pair[p] = row;
   }
-  if (with_shared)
-    for (int t = tid; t < T; t += LISTS_THREADS) {
+  if (shared_n > 0)
+    for (int t = shared_lo + tid; t < shared_lo + shared_n; t += LISTS_THREADS) {
       const bool ok = (pos == nullptr) || (pos[t] != 0);
       L.slot_of_row[P + t] = ok ? P + t : -1;
       L.wt_of_row[P + t] = 1.f;
@@ -544,11 +544,17 @@ extern "C" int b200_moe_max_blocks(int T, int K, int E_local, int block_rows) {
 extern "C" int b200_moe_build_lists(const int32_t* ids, const float* wts, const int64_t* pos, int T, int K, int e_lo,
                                     int E_local, int block_rows, int with_shared, const b200_moe_lists* lists,
                                     void* stream) {
+  return b200_moe_build_lists_range(ids, wts, pos, T, K, e_lo, E_local, block_rows, 0, with_shared ? T : 0, lists, stream);
+}
+
+extern "C" int b200_moe_build_lists_range(const int32_t* ids, const float* wts, const int64_t* pos, int T, int K, int e_lo,
+                                          int E_local, int block_rows, int shared_lo, int shared_n,
+                                          const b200_moe_lists* lists, void* stream) {
   if (!ids || !wts || !lists || !lists->counts || !lists->offsets || !lists->row_of_pair || !lists->slot_of_row ||
       !lists->wt_of_row || !lists->blk_expert || !lists->blk_row0 || !lists->blk_rows || !lists->nblocks)
     return fail(B200_E_ARG, "b200_moe_build_lists: null pointer");
   if (T <= 0 || K <= 0 || E_local <= 0 || E_local > LISTS_MAX_E || e_lo < 0 || block_rows < 16 || block_rows > 128 ||
-      block_rows % 16)
+      block_rows % 16 || shared_lo < 0 || shared_n < 0 || shared_lo + shared_n > T)
     return fail(B200_E_ARG, "b200_moe_build_lists: bad shape (T=%d K=%d E_local=%d block_rows=%d)", T, K, E_local,
                 block_rows);
   MoeLists L{lists->counts,     lists->offsets,  lists->row_of_pair, lists->slot_of_row, lists->wt_of_row,
@@ -564,6 +570,6 @@ extern "C" int b200_moe_build_lists(const int32_t* ids, const float* wts, const 
     attr_done[dev] = true;
   }
   launch_k(moe_lists_kernel, dim3(1), dim3(LISTS_THREADS), smem, static_cast<cudaStream_t>(stream), ids, wts, pos, T, K,
-           e_lo, E_local, block_rows, with_shared, static_cast<int>(b200_moe_max_blocks(T, K, E_local, block_rows)), L);
+           e_lo, E_local, block_rows, shared_lo, shared_n, static_cast<int>(b200_moe_max_blocks(T, K, E_local, block_rows)), L);
   return launch_status("b200_moe_build_lists");
 }

@@ -93,8 +93,9 @@ class RoutingLists:
                                                    self.nblocks)])
 
 
-def build_lists(ids, wts, lists: RoutingLists, pos=None, e_lo=0, with_shared=True):
-    """Per-expert sorted rows + GEMM block list (reference: i8x_dec_lists)."""
+def build_lists(ids, wts, lists: RoutingLists, pos=None, e_lo=0, with_shared=True, shared_range=None):
+    """Per-expert sorted rows + GEMM block list (reference: i8x_dec_lists).  `shared_range` = (first token, count):
+    only these tokens get a shared-expert row (an expert-parallel rank's own tokens among the gathered ones)."""
     _need(ids, torch.int32, "ids", 2)
     _need(wts, torch.float32, "wts", 2)
     if pos is not None:
@@ -102,6 +103,12 @@ def build_lists(ids, wts, lists: RoutingLists, pos=None, e_lo=0, with_shared=Tru
     T, K = ids.shape
     if (T, K) != (lists.T, lists.K):
         raise B200Error("routing lists were sized for another (T, K)")
+    if shared_range is not None:
+        lo, n = shared_range
+        check(_lib.lib().b200_moe_build_lists_range(_p(ids), _p(wts), _p(pos), T, K, e_lo, lists.E_local,
+                                                    lists.block_rows, int(lo), int(n), C.byref(lists.c), _stream()),
+              "b200_moe_build_lists_range")
+        return lists
     check(_lib.lib().b200_moe_build_lists(_p(ids), _p(wts), _p(pos), T, K, e_lo, lists.E_local, lists.block_rows,
                                           1 if with_shared else 0, C.byref(lists.c), _stream()),
           "b200_moe_build_lists")

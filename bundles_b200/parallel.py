@@ -133,8 +133,7 @@ class FusedExpertParallelMoe:
     stores from the GEMM epilogue, `ops.moe_w8a8_ep`), then one barrier, then the home rank adds its
     tokens' rows in slot order.  The caches are symmetric-memory buffers (one per rank, mapped into
     every process); x and the packed (ids, weights) are all-gathered with NCCL (each token row is needed
-    by up to min(K, world) ranks).  The shared expert runs in the same launches over the gathered
-    tokens (its weights are streamed once either way) and keeps the rows of this rank's own tokens.
+    by up to min(K, world) ranks).  The shared expert runs in the same launches, for this rank's own tokens only.
     The whole step is captured into a CUDA graph on first use.  Bit-identical to `ExpertParallelMoe`
     and to the single-GPU block."""
 
@@ -174,7 +173,8 @@ class FusedExpertParallelMoe:
         dist.all_gather_into_tensor(self.route_all, self.route_local, group=self.group)
         self.ids_all.copy_(self.route_all[:, :K])
         self.wts_all.copy_(self.route_all[:, K:].view(torch.float32))
-        ops.build_lists(self.ids_all, self.wts_all, self.lists, None, e_lo=b.e_lo, with_shared=True)
+        ops.build_lists(self.ids_all, self.wts_all, self.lists, None, e_lo=b.e_lo,
+                        shared_range=(self.rank * self.T, self.T))   # the shared expert runs for this rank's own tokens
         # nobody may still be reading last step's rows when the first peer store of this step lands
         self.handle.barrier(channel=0)
         ops.moe_w8a8_ep(self.x_all, b.w, self.lists, self.peer_ptrs, self.rank, self.T, ws=self.ws, status=b.status)

@@ -111,6 +111,12 @@ int b200_moe_max_blocks(int T, int K, int E_local, int block_rows);
 
 int b200_moe_build_lists(const int32_t* ids, const float* wts, const int64_t* pos, int T, int K, int e_lo,
                          int E_local, int block_rows, int with_shared, const b200_moe_lists* lists, void* stream);
+/* The same with shared-expert rows for tokens [shared_lo, shared_lo + shared_n) only (0 <= shared_lo,
+ * shared_lo + shared_n <= T; shared_n = 0: none).  Expert-parallel ranks see the gathered tokens of all
+ * ranks but run the shared expert for their own tokens only.  (No counterpart in the reference.) */
+int b200_moe_build_lists_range(const int32_t* ids, const float* wts, const int64_t* pos, int T, int K, int e_lo,
+                               int E_local, int block_rows, int shared_lo, int shared_n,
+                               const b200_moe_lists* lists, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * MoE block, int8 W8A8.  Replaces i8x_decode.moe_row_batch (i8x_decode.py:528-576): up + SwiGLU
@@ -153,8 +159,9 @@ int b200_moe_w8a8(const void* x, int T, int H, int I, int K, int E_local, const 
 /* Expert-parallel form of b200_moe_w8a8 with the combine-side exchange fused into the down GEMM.
  * (No counterpart in the reference, which is single-GPU: layer.py:396-402.)
  * x holds the gathered tokens of all ranks, T = ep_world * ep_tokens_per_rank, rank r's tokens at rows
- * [r * ep_tokens_per_rank, ...); `lists` were built for this rank's experts (e_lo, E_local), with or
- * without the shared expert.  The down epilogue stores bf16(y * routing weight) for global slot
+ * [r * ep_tokens_per_rank, ...); `lists` were built for this rank's experts (e_lo, E_local), without the
+ * shared expert or with shared rows for this rank's own tokens (b200_moe_build_lists_range with
+ * shared_lo = ep_rank * ep_tokens_per_rank, shared_n = ep_tokens_per_rank).  The down epilogue stores bf16(y * routing weight) for global slot
  * s = t*K + j straight into the home rank's cache, peer_cache_host[s / (ep_tokens_per_rank*K)] +
  * (s % (ep_tokens_per_rank*K)) * H, with ordinary stores; shared-expert rows are kept only for this
  * rank's own tokens, at row ep_tokens_per_rank*K + local token of its own cache (the layout

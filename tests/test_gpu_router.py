@@ -113,3 +113,23 @@ def test_lists_expert_parallel_shard():
         assert c[64] == 0
         tot += int(c[:64].sum())
     assert tot == T * K
+
+
+def test_lists_shared_rows_for_a_token_range():
+    """An expert-parallel rank builds lists over the gathered tokens but shared-expert rows for its own only."""
+    T, E, K = 320, 512, 10
+    g = torch.Generator().manual_seed(5)
+    ids_np, w_np = orouter.topk_softmax((torch.randn(T, E, generator=g) * 2).numpy(), K)
+    lo, n = 160, 160
+    lists = ops.RoutingLists(T, K, 64, 128, dev())
+    ops.build_lists(torch.from_numpy(ids_np).to(dev()), torch.from_numpy(w_np).to(dev()), lists, None, e_lo=128,
+                    shared_range=(lo, n))
+    torch.cuda.synchronize()
+    c, off = lists.counts.cpu().numpy(), lists.offsets.cpu().numpy()
+    assert c[64] == n and off[64] == T * K + lo and off[65] == T * K + lo + n
+    slot = lists.slot_of_row.cpu().numpy()
+    assert np.array_equal(slot[T * K + lo:T * K + lo + n], np.arange(T * K + lo, T * K + lo + n))
+    nb = int(lists.nblocks.item())
+    be, b0, br = (t.cpu().numpy()[:nb] for t in (lists.blk_expert, lists.blk_row0, lists.blk_rows))
+    sh = be == 64
+    assert list(b0[sh]) == [T * K + lo, T * K + lo + 128] and list(br[sh]) == [128, 32]
