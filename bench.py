@@ -332,12 +332,14 @@ def run_expert_parallel(args, rank, world, dev, cfg):
     del full
     torch.cuda.empty_cache()
     backend = parallel.GpuMoeBackend(wr, w_local, gate_w, K, e_lo, bias=bias)
-    exchange = "peer stores from the down-GEMM epilogue into symmetric-memory caches + barrier"
+    exchange = ("tokens and routing dispatched by peer stores into every rank's symmetric-memory buffers + barrier; "
+                "peer stores from the down-GEMM epilogue into the home rank's cache + barrier (no NCCL call in the step)")
     try:
         ep = parallel.FusedExpertParallelMoe(backend, K, H, T)
     except Exception as exc:  # noqa: BLE001  (symmetric memory unavailable: NCCL reduce-scatter baseline)
         ep = parallel.ExpertParallelMoe(backend, K, H)
-        exchange = f"reduce-scatter of the weighted expert rows (NCCL); symmetric memory unavailable: {repr(exc)[:80]}"
+        exchange = ("all-gather of tokens and routing, reduce-scatter of the weighted expert rows (NCCL); "
+                    f"symmetric memory unavailable: {repr(exc)[:80]}")
     g = torch.Generator(device=dev).manual_seed(7000 + rank)
     x_dev = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
     x_host = x_dev.cpu().pin_memory()
@@ -381,8 +383,7 @@ def run_expert_parallel(args, rank, world, dev, cfg):
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "tokens_per_gpu": T,
-                           "parallelism": f"ep{world}: {E // world} experts per rank; all-gather of tokens and routing (NCCL), "
-                                          + exchange,
+                           "parallelism": f"ep{world}: {E // world} experts per rank; " + exchange,
                            "l2": "weights streamed per step exceed the 126 MB L2; no flush"},
                 "e2e": {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2,
                         "d2h_bytes_per_step": T * H * 2, "ms_per_step": ms_e2e},

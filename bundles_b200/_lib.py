@@ -35,6 +35,7 @@ PROTOTYPES = {
                             vp, i32, vp, vp]),
     "b200_moe_w8a8_ep": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(MoeWeights), C.POINTER(MoeLists), C.POINTER(vp), i32,
                                i32, i32, vp, sz, vp, vp]),
+    "b200_ep_push": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), vp]),
     "b200_moe_fp8_workspace_bytes": (sz, [i32, i32, i32, i32]),
     "b200_moe_fp8": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(MoeWeights), C.POINTER(MoeLists), vp, vp, sz, vp,
                            i32, vp, vp]),

@@ -647,6 +647,34 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const bf16* __res
   }
 }
 
+// Expert-parallel dispatch: this rank's token rows and routing go straight into every rank's gathered buffers
+// (its own included) with ordinary stores over NVLink; a barrier among the ranks follows on the host side.
+// grid (world, 32): blockIdx.x = destination rank.
+struct EpPushArgs {
+  const uint4* x;        // [T_local, H] bf16 as 16-byte words
+  const int32_t* ids;    // [T_local, K]
+  const float* wts;      // [T_local, K]
+  uint4* dst_x[8];       // rank r's x_all   [world * T_local, H]
+  int32_t* dst_ids[8];   // rank r's ids_all [world * T_local, K]
+  float* dst_wts[8];     // rank r's wts_all [world * T_local, K]
+  int rank, x_words, route_n;  // 16-byte words of x, elements of ids / wts
+};
+__global__ void __launch_bounds__(256) ep_push_kernel(const EpPushArgs a) {
+  pdl_wait();
+  pdl_launch();
+  const int d = blockIdx.x;
+  uint4* dx = a.dst_x[d] + static_cast<size_t>(a.rank) * a.x_words;
+  for (int i = blockIdx.y * 256 + threadIdx.x; i < a.x_words; i += gridDim.y * 256) dx[i] = a.x[i];
+  if (blockIdx.y == 0) {
+    int32_t* di = a.dst_ids[d] + static_cast<size_t>(a.rank) * a.route_n;
+    float* dw = a.dst_wts[d] + static_cast<size_t>(a.rank) * a.route_n;
+    for (int i = threadIdx.x; i < a.route_n; i += 256) {
+      di[i] = a.ids[i];
+      dw[i] = a.wts[i];
+    }
+  }
+}
+
 // workspace layout of the int8 block (all offsets 1024-byte aligned)
 struct W8Layout {
   size_t xq, xs, h, hq, hs, total;
@@ -837,4 +865,31 @@ extern "C" int b200_moe_combine_norm(const void* cache, const void* x, const voi
            static_cast<bf16*>(out), static_cast<bf16*>(residual), static_cast<const bf16*>(norm_w), eps,
            static_cast<bf16*>(normed));
   return launch_status("b200_moe_combine_norm");
+}
+
+extern "C" int b200_ep_push(const void* x, const int32_t* ids, const float* wts, int T_local, int H, int K, int ep_rank,
+                            int ep_world, void* const* peer_x_host, void* const* peer_ids_host,
+                            void* const* peer_wts_host, void* stream) {
+  if (!x || !ids || !wts || !peer_x_host || !peer_ids_host || !peer_wts_host)
+    return fail(B200_E_ARG, "b200_ep_push: null pointer");
+  if (T_local <= 0 || H <= 0 || H % 8 || K <= 0 || ep_world < 1 || ep_world > 8 || ep_rank < 0 || ep_rank >= ep_world)
+    return fail(B200_E_ARG, "b200_ep_push: need H %% 8 == 0, 1 <= ep_world <= 8, 0 <= ep_rank < ep_world (H=%d world=%d)", H,
+                ep_world);
+  EpPushArgs a{};
+  a.x = static_cast<const uint4*>(x);
+  a.ids = ids;
+  a.wts = wts;
+  a.rank = ep_rank;
+  a.x_words = T_local * (H / 8);
+  a.route_n = T_local * K;
+  for (int r = 0; r < ep_world; ++r) {
+    if (!peer_x_host[r] || !peer_ids_host[r] || !peer_wts_host[r] || (reinterpret_cast<uintptr_t>(peer_x_host[r]) & 15))
+      return fail(B200_E_ALIGN, "b200_ep_push: rank %d's buffers must be non-null and 16-byte aligned", r);
+    a.dst_x[r] = static_cast<uint4*>(peer_x_host[r]);
+    a.dst_ids[r] = static_cast<int32_t*>(peer_ids_host[r]);
+    a.dst_wts[r] = static_cast<float*>(peer_wts_host[r]);
+  }
+  if (reinterpret_cast<uintptr_t>(x) & 15) return fail(B200_E_ALIGN, "b200_ep_push: x must be 16-byte aligned");
+  launch_k(ep_push_kernel, dim3(ep_world, 32), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+  return launch_status("b200_ep_push");
 }

@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import B200Error, MoeLists, MoeWeights, check
 
-__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_w8a8_ep", "moe_fp8", "moe_combine", "moe_combine_norm", "attn_front", "attn_verify", "dense_fp8", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
+__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_w8a8_ep", "ep_push", "moe_fp8", "moe_combine", "moe_combine_norm", "attn_front", "attn_verify", "dense_fp8", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
            "new_status", "read_status", "B200Error"]
 
 
@@ -211,6 +211,18 @@ def moe_w8a8_ep(x_all, w: MoeW8A8Weights, lists: RoutingLists, peer_ptrs, rank, 
     check(_lib.lib().b200_moe_w8a8_ep(_p(x_all), T, H, I, K, E, C.byref(wc), C.byref(lists.c), arr, world,
                                       int(rank), int(tokens_per_rank), _p(ws), ws.numel(), _p(status), _stream()),
           "b200_moe_w8a8_ep")
+
+
+def ep_push(x, ids, wts, rank, peer_x, peer_ids, peer_wts):
+    """Store this rank's token rows and routing into every rank's gathered buffers (peer pointers as ints)."""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(ids, torch.int32, "ids", 2)
+    _need(wts, torch.float32, "wts", 2)
+    T, H = x.shape
+    world = len(peer_x)
+    arr = lambda ptrs: (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in ptrs])
+    check(_lib.lib().b200_ep_push(_p(x), _p(ids), _p(wts), T, H, ids.shape[1], int(rank), world, arr(peer_x),
+                                  arr(peer_ids), arr(peer_wts), _stream()), "b200_ep_push")
 
 
 def moe_combine(cache, x, gate_w, top_k, pos=None, out=None):

@@ -132,8 +132,9 @@ class FusedExpertParallelMoe:
     stores the weighted expert rows straight into the home rank's cache over NVLink (plain peer
     stores from the GEMM epilogue, `ops.moe_w8a8_ep`), then one barrier, then the home rank adds its
     tokens' rows in slot order.  The caches are symmetric-memory buffers (one per rank, mapped into
-    every process); x and the packed (ids, weights) are all-gathered with NCCL (each token row is needed
-    by up to min(K, world) ranks).  The shared expert runs in the same launches, for this rank's own tokens only.
+    every process); token rows and routing reach every rank's gathered buffers by peer stores too
+    (`ops.ep_push`; each token row is needed by up to min(K, world) ranks), so the step contains no NCCL
+    call.  The shared expert runs in the same launches, for this rank's own tokens only.
     The whole step is captured into a CUDA graph on first use.  Bit-identical to `ExpertParallelMoe`
     and to the single-GPU block."""
 
@@ -150,33 +151,31 @@ class FusedExpertParallelMoe:
         self.handle = symm.rendezvous(self.cache, self.group)
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         T_all = tokens_per_rank * self.world
-        self.x_all = torch.empty(T_all, hidden, dtype=torch.bfloat16, device=dev)
-        self.route_local = torch.empty(tokens_per_rank, 2 * top_k, dtype=torch.int32, device=dev)
-        self.route_all = torch.empty(T_all, 2 * top_k, dtype=torch.int32, device=dev)
-        self.ids_all = torch.empty(T_all, top_k, dtype=torch.int32, device=dev)
-        self.wts_all = torch.empty(T_all, top_k, dtype=torch.float32, device=dev)
+        # the gathered tokens and routing of all ranks: every rank stores its share into every rank's buffers
+        self.x_all = symm.empty(T_all, hidden, dtype=torch.bfloat16, device=dev)
+        self.ids_all = symm.empty(T_all, top_k, dtype=torch.int32, device=dev)
+        self.wts_all = symm.empty(T_all, top_k, dtype=torch.float32, device=dev)
+        self.peer_x = [int(p) for p in symm.rendezvous(self.x_all, self.group).buffer_ptrs]
+        self.peer_ids = [int(p) for p in symm.rendezvous(self.ids_all, self.group).buffer_ptrs]
+        self.peer_wts = [int(p) for p in symm.rendezvous(self.wts_all, self.group).buffer_ptrs]
         self.lists = backend.ops.RoutingLists(T_all, top_k, backend.E_local, 128, dev)
         self.ws = backend.ops.moe_w8a8_workspace(T_all, hidden, backend.w.w2.shape[-1], top_k, dev)
         self.x_static = torch.empty(tokens_per_rank, hidden, dtype=torch.bfloat16, device=dev)
         self.out = torch.empty(tokens_per_rank, hidden, dtype=torch.bfloat16, device=dev)
         self.use_graph, self.graph = use_graph, None
         self._pipe = None
-        self.launches_per_call = 8   # router x2, lists, quantise, up, h-quantise, down, combine (+2 NCCL, 2 barriers)
+        self.launches_per_call = 9   # router x2, dispatch, lists, quantise, up, h-quantise, down, combine (+2 barriers)
 
     def _step(self):
         b, ops, K = self.b, self.b.ops, self.K
         x = self.x_static
         ids, wts = b.route(x)
-        self.route_local[:, :K].copy_(ids)
-        self.route_local[:, K:].copy_(wts.view(torch.int32))
-        dist.all_gather_into_tensor(self.x_all, x, group=self.group)
-        dist.all_gather_into_tensor(self.route_all, self.route_local, group=self.group)
-        self.ids_all.copy_(self.route_all[:, :K])
-        self.wts_all.copy_(self.route_all[:, K:].view(torch.float32))
+        # dispatch: peer stores into every rank's gathered buffers; the barrier below makes them visible and
+        # also tells that nobody still reads last step's rows when the first peer store of this step lands
+        ops.ep_push(x, ids, wts, self.rank, self.peer_x, self.peer_ids, self.peer_wts)
+        self.handle.barrier(channel=0)
         ops.build_lists(self.ids_all, self.wts_all, self.lists, None, e_lo=b.e_lo,
                         shared_range=(self.rank * self.T, self.T))   # the shared expert runs for this rank's own tokens
-        # nobody may still be reading last step's rows when the first peer store of this step lands
-        self.handle.barrier(channel=0)
         ops.moe_w8a8_ep(self.x_all, b.w, self.lists, self.peer_ptrs, self.rank, self.T, ws=self.ws, status=b.status)
         self.handle.barrier(channel=1)      # every rank's rows for my tokens have landed
         ops.moe_combine(self.cache, x, b.gate_w, K, out=self.out)

@@ -173,6 +173,15 @@ int b200_moe_w8a8_ep(const void* x, int T, int H, int I, int K, int E_local, con
                      const b200_moe_lists* lists, void* const* peer_cache_host, int ep_world, int ep_rank,
                      int ep_tokens_per_rank, void* ws, size_t ws_bytes, int32_t* status, void* stream);
 
+/* Expert-parallel dispatch (no counterpart in the reference): this rank's T_local token rows and their routing
+ * are stored into every rank's gathered buffers at row offset ep_rank * T_local, over NVLink with ordinary
+ * stores: peer_*_host are HOST arrays of ep_world DEVICE pointers, entry r being rank r's x_all
+ * [ep_world * T_local, H] bf16, ids_all / wts_all [ep_world * T_local, K] as mapped into this process.  The
+ * caller runs a barrier among the ranks before any rank reads its gathered buffers. */
+int b200_ep_push(const void* x, const int32_t* ids, const float* wts, int T_local, int H, int K, int ep_rank,
+                 int ep_world, void* const* peer_x_host, void* const* peer_ids_host, void* const* peer_wts_host,
+                 void* stream);
+
 /* MoE block, fp8 e4m3 with 128x128 weight block scales and per-(token,128-channel) activation
  * scales.  The reference has no block-scaled fp8 MoE; the arithmetic is its scaled-GEMM recipe
  * applied per block: per 128-k block the MMA chain starts from zero and is promoted
