@@ -26,7 +26,8 @@ constexpr int AT_KS = AT_H / 128;                                 // 16
 constexpr int AT_THREADS = 320;                                   // TMA warp, MMA warp, 8 epilogue warps
 constexpr int AT_A = 128 * 128, AT_B = 256 * 128, AT_STAGE = AT_A + AT_B, AT_STAGES = 4;
 constexpr int AT_META = 2 * 2 * 128 * 4 /*ss halves, two phases*/ + 2 * 256 * 4 /*1 + w*/;
-constexpr int AT_SMEM = AT_STAGES * AT_STAGE + 1024 + 256 + AT_META;
+constexpr int AT_SCALES = 8 * (32 * AT_KS + AT_KS) * 4;  // per epilogue warp: its 32 tokens' activation scales + one weight scale row
+constexpr int AT_SMEM = AT_STAGES * AT_STAGE + 1024 + 256 + AT_META + AT_SCALES;
 
 struct AttnArgs {
   const float* a_scale;   // [T, 16]
@@ -44,6 +45,19 @@ struct AttnArgs {
   void* v;     // [T,2,256]
   int32_t* status;
 };
+
+// two fp32 FMAs in one instruction (each lane an IEEE fma, same results as two fmaf)
+__device__ __forceinline__ void fma2(float& a0, float& a1, float x0, float x1, float s) {
+  unsigned long long acc, x, sc;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(acc) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(x0), "f"(x1));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(sc) : "f"(s));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(x), "l"(sc));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc));
+}
+__device__ __forceinline__ void at_cp16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
 
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const AttnArgs p) {
@@ -160,17 +174,33 @@ attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     const int row = q * 32 + lane;        // token row inside the tile
     uint32_t g = 0, sscount = 0;
     bool ok = true;
+    // This warp's scales of a tile (its 32 tokens' 16 activation scales, the 16 weight block scales of its 128
+    // columns) are copied into shared memory asynchronously when the previous tile's k loop has ended, under that
+    // tile's epilogue: with the operand stream in flight a global load on the critical path costs microseconds.
+    float* m_as = reinterpret_cast<float*>(smem + AT_STAGES * AT_STAGE + 256 + AT_META) + (warp - 2) * (32 * AT_KS + AT_KS);
+    float* m_ws = m_as + 32 * AT_KS;
+    auto fetch_scales = [&](int tile) {
+      if (tile >= ntiles) return;
+      const int j = tile / mtiles, mt = tile - j * mtiles;
+      const int t = mt * 128 + row;
+      const float* asrow = p.a_scale + static_cast<size_t>(t < p.T ? t : 0) * AT_KS;
+#pragma unroll
+      for (int c = 0; c < AT_KS / 4; ++c) at_cp16(m_as + lane * AT_KS + 4 * c, asrow + 4 * c);
+      if (lane < AT_KS / 4) at_cp16(m_ws + 4 * lane, p.w_s + static_cast<size_t>(2 * j + hh) * AT_KS + 4 * lane);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch_scales(blockIdx.x);
     for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
       const int j = tile / mtiles, mt = tile - j * mtiles;
       const int t = mt * 128 + row;
-      const float* asrow = p.a_scale + static_cast<size_t>(t < p.T ? t : 0) * AT_KS;  // this token's scales
-      const float* wsrow = p.w_s + static_cast<size_t>(2 * j + hh) * AT_KS;
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncwarp();
       float acc[128];
 #pragma unroll
       for (int c = 0; c < 128; ++c) acc[c] = 0.f;
       for (int ks = 0; ks < AT_KS; ++ks, ++g) {
         const uint32_t pb = g & 1u, pphase = (g >> 1) & 1u;
-        const float sc = __fmul_rn(__ldg(asrow + ks), __ldg(wsrow + ks));  // issued before the wait
+        const float sc = __fmul_rn(m_as[lane * AT_KS + ks], m_ws[ks]);
         if (!mbar_wait(&pfull[pb], pphase, abort_flag, p.status, ST_WAIT_TMEM_FULL)) {
           ok = false;
           break;
@@ -183,13 +213,16 @@ attn_front_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           tmem_ld32(taddr + c0, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c0 + i] = __fmaf_rn(__uint_as_float(r[i]), sc, acc[c0 + i]);
+          for (int i = 0; i < 32; i += 2)
+            fma2(acc[c0 + i], acc[c0 + i + 1], __uint_as_float(r[i]), __uint_as_float(r[i + 1]), sc);
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&pempty[pb]);
       }
       if (!ok) break;
+      __syncwarp();
+      fetch_scales(tile + gridDim.x);  // lands during this tile's epilogue
       // ---- epilogue on the thread's 128 features of token t ----
       const bool is_q = j < 2 * AT_HQ && (j & 1) == 0;
       const bool is_gate = j < 2 * AT_HQ && (j & 1) == 1;
