@@ -163,3 +163,24 @@ def test_combine_norm_equals_combine_then_add_rmsnorm():
     assert ok, f"normed: max err {err}, {nbad} outside tolerance"
     ok, err, nbad = close_bf16(bf16_to_np(res_b), want_r)
     assert ok, f"residual: max err {err}, {nbad} outside tolerance"
+
+
+def test_forward_host_pipeline_matches_forward():
+    """The pipelined host-to-host call returns, for every call, what the plain call returns for the same input."""
+    from bundles_b200 import moe_block
+    K = 10
+    cfg = synth.moe_w8a8(seed=31, T=48, E=64, zipf_s=1.1)
+    d = _to_dev(cfg)
+    w = ops.MoeW8A8Weights(d["w13"], d["s13"], d["w2"], d["s2"], d["sh13"], d["shs13"], d["sh2"], d["shs2"])
+    blk = moe_block.MoeBlockW8A8(d["wr"], w, d["gate_w"], K, bias=d["bias"])
+    g = torch.Generator().manual_seed(32)
+    xs = [torch.randn(48, 2048, generator=g).to(torch.bfloat16).pin_memory() for _ in range(5)]
+    outs = [torch.empty(48, 2048, dtype=torch.bfloat16).pin_memory() for _ in range(5)]
+    for xh, oh in zip(xs, outs):
+        blk.forward_host(xh, oh)
+    blk.synchronize_host()
+    for xh, oh in zip(xs, outs):
+        want = blk(xh.to(dev())).clone()
+        torch.cuda.synchronize()
+        assert torch.equal(oh.to(dev()), want)
+    assert ops.read_status(blk.status) == 0

@@ -46,9 +46,17 @@ def _worker(rank, world, port, out):
         y2 = fused(xl).clone()
         y3 = fused(xl).clone()                      # a second step reuses the peer-written caches
         torch.cuda.synchronize()
+        # the pipelined host-to-host form: three calls in a row, every result equal to the plain call's
+        xh = xl.cpu().pin_memory()
+        ohs = [torch.empty_like(xh).pin_memory() for _ in range(3)]
+        for oh in ohs:
+            fused.forward_host(xh, oh)
+        fused.join_host()
+        torch.cuda.synchronize()
+        ok_host = all(torch.equal(oh.to(dev), y) for oh in ohs)
         fused.close()
         ok_moe = torch.equal(y, ref[rank * T_local:(rank + 1) * T_local]) and ops.read_status(backend.status) == 0
-        ok_moe = ok_moe and torch.equal(y2, y) and torch.equal(y3, y)
+        ok_moe = ok_moe and torch.equal(y2, y) and torch.equal(y3, y) and ok_host
         # vocab-sharded greedy token
         V = 128 * 21
         lm = synth.lmhead(seed=401, T=16, V=V)
