@@ -149,9 +149,9 @@ constexpr int I8_CACHED = 64;       // tiles per CTA whose list entries are cach
 
 template <bool UP>
 struct GemmCfg {
-  static constexpr int NA = UP ? 2 : 1;                      // weight tiles per stage (gate + up)
+  static constexpr int NA = 2;   // weight tiles per stage: gate + up rows of one channel block / two consecutive 128-row tiles of W2
   static constexpr int STAGE = NA * TILE_BYTES + TILE_BYTES;  // + token tile (<= 128 rows)
-  static constexpr int STAGES = UP ? 4 : 6;
+  static constexpr int STAGES = 4;
   static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + 8 * 128 * 20 /*row metadata, one copy per epilogue warp*/ +
                               I8_CACHED * 12 /*block-list entries of this CTA's tiles*/;
 };
@@ -255,12 +255,12 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         int e, row0, n, mt;
         if (!decode(tile, e, row0, n, mt)) continue;
         const CUtensorMap* mapW = (e == p.E_local) ? &tmWsh : &tmW;
-        const int wrow = (e == p.E_local ? 0 : e * p.w_rows) + mt * 128;
+        const int wrow = (e == p.E_local ? 0 : e * p.w_rows) + mt * (UP ? 128 : 256);
         for (int ks = 0; ks < p.ksteps && pre < C::STAGES; ++ks, ++pre) {
           uint8_t* sA = smem + pre * C::STAGE;
           mbar_expect_tx(&full[pre], C::NA * TILE_BYTES + tok_units((n + 15) >> 4) * 2048);
           tma_load_2d(sA, mapW, ks * 128, wrow, &full[pre]);
-          if (UP) tma_load_2d(sA + TILE_BYTES, mapW, ks * 128, wrow + p.I, &full[pre]);
+          tma_load_2d(sA + TILE_BYTES, mapW, ks * 128, wrow + (UP ? p.I : 128), &full[pre]);
         }
       }
       pdl_wait();
@@ -270,7 +270,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (!decode(tile, e, row0, n, mt)) continue;
         const int nb16 = (n + 15) >> 4;
         const CUtensorMap* mapW = (e == p.E_local) ? &tmWsh : &tmW;
-        const int wrow = (e == p.E_local ? 0 : e * p.w_rows) + mt * 128;
+        const int wrow = (e == p.E_local ? 0 : e * p.w_rows) + mt * (UP ? 128 : 256);
         for (int ks = 0; ks < p.ksteps; ++ks) {
           uint8_t* sA = smem + stage * C::STAGE;
           uint8_t* sB = sA + C::NA * TILE_BYTES;
@@ -282,7 +282,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             }
             mbar_expect_tx(&full[stage], C::NA * TILE_BYTES + tok_units(nb16) * 2048);
             tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
-            if (UP) tma_load_2d(sA + TILE_BYTES, mapW, ks * 128, wrow + p.I, &full[stage]);
+            tma_load_2d(sA + TILE_BYTES, mapW, ks * 128, wrow + (UP ? p.I : 128), &full[stage]);
           }
           if (big == 8) tma_load_2d(sB, &tmX128, ks * 128, row0, &full[stage]);
           if (big == 4) tma_load_2d(sB, &tmX64, ks * 128, row0, &full[stage]);
@@ -343,7 +343,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             const uint64_t db = umma_desc_sw128(sB + kk * 32);
             const uint32_t acc = (ks | kk) != 0;
             tc_mma_i8(d0, umma_desc_sw128(sA + kk * 32), db, idesc, acc);
-            if (UP) tc_mma_i8(d0 + 128, umma_desc_sw128(sA + TILE_BYTES + kk * 32), db, idesc, acc);
+            tc_mma_i8(d0 + 128, umma_desc_sw128(sA + TILE_BYTES + kk * 32), db, idesc, acc);
           }
           tc_commit(&empty[stage]);
           if (++stage == C::STAGES) {
@@ -386,9 +386,9 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       int e, row0, n, mt;
       if (tile >= ntiles || !decode(tile, e, row0, n, mt)) return;
       const float* sw = (e == p.E_local) ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * p.w_rows;
-      const int r = mt * 128 + q * 32 + lane;
+      const int r = mt * (UP ? 128 : 256) + q * 32 + lane;
       m.w0 = sw[r];
-      if (UP) m.w1 = sw[p.I + r];
+      m.w1 = sw[(UP ? p.I : 128) + r];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int c = lane + 32 * u;
@@ -451,7 +451,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (!mbar_wait(&tfull[buf], bphase, abort_flag, p.status, ST_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + buf * 256 + (static_cast<uint32_t>(q * 32) << 16);
-      const int r = mt * 128 + q * 32 + lane;  // weight row inside the expert (up: channel of I; down: column of H)
+      const int r = mt * (UP ? 128 : 256) + q * 32 + lane;  // weight row inside the expert (up: channel of I; down: column of H, and r + 128)
       if (UP) {
         const float wsg = ws0, wsu = ws1;
         bf16* __restrict__ hout = p.h_out + static_cast<size_t>(row0) * p.I + r;
@@ -486,17 +486,21 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
         }
       } else {
-        const float ws = ws0;
         for (int c0 = half * 16; c0 < n; c0 += 32) {
-          uint32_t ra[16];
+          uint32_t ra[16], rb[16];  // output columns r and r + 128 of the same token rows
           tmem_ld16(taddr + c0, ra);
+          tmem_ld16(taddr + 128 + c0, rb);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             bf16* dst = m_dst[c0 + i];
-            const float y = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ra[i])), ms[c0 + i]), ws);
-            const bf16 o = f2bf(__fmul_rn(y, m_wt[c0 + i]));
-            if (dst != nullptr) dst[r] = o;
+            const float xs = ms[c0 + i], wt = m_wt[c0 + i];
+            const float y0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ra[i])), xs), ws0);
+            const float y1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(rb[i])), xs), ws1);
+            if (dst != nullptr) {
+              dst[r] = f2bf(__fmul_rn(y0, wt));
+              dst[r + 128] = f2bf(__fmul_rn(y1, wt));
+            }
           }
         }
       }
@@ -734,8 +738,8 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
                          int ep_world, int ep_tokens_per_rank) {
   if (!x || !w || !lists || !cache || !ws || !w->w13 || !w->s13 || !w->w2 || !w->s2)
     return fail(B200_E_ARG, "b200_moe_w8a8: null pointer");
-  if (T <= 0 || K <= 0 || K > 32 || E_local <= 0 || H % 128 || I % 128 || H <= 0 || I <= 0)
-    return fail(B200_E_ARG, "b200_moe_w8a8: need H %% 128 == 0, I %% 128 == 0, 1 <= K <= 32 (T=%d H=%d I=%d K=%d)", T, H,
+  if (T <= 0 || K <= 0 || K > 32 || E_local <= 0 || H % 256 || I % 128 || H <= 0 || I <= 0)
+    return fail(B200_E_ARG, "b200_moe_w8a8: need H %% 256 == 0, I %% 128 == 0, 1 <= K <= 32 (T=%d H=%d I=%d K=%d)", T, H,
                 I, K);
   const W8Layout l = w8_layout(T, H, I, K);
   if (ws_bytes < l.total) return fail(B200_E_WS, "b200_moe_w8a8: workspace %zu < %zu bytes", ws_bytes, l.total);
@@ -818,7 +822,7 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
   if (stages & B200_MOE_STAGE_HQUANT)
     launch_k(quant_rows_i8_kernel, dim3((rows + 7) / 8), dim3(256), 0, st, h, rows, I, L.slot_of_row, hq, hs);
 
-  a.mtiles = H / 128;
+  a.mtiles = H / 256;  // two consecutive 128-row tiles of W2 per GEMM tile: the token tile is read half as often
   a.ksteps = I / 128;
   a.w_rows = H;
   a.s_w = w->s2;

@@ -129,7 +129,7 @@ int b200_moe_build_lists_range(const int32_t* ids, const float* wts, const int64
  *   w2 int8 [E_local,H,I], s2 fp32 [E_local,H];  shared expert sh13 [2I,H], shs13 [2I],
  *   sh2 [H,I], shs2 [H] (NULL sh13 = no shared expert);
  *   cache bf16 [T*(K+1),H] (output): row `slot` = bf16(down row * routing weight)
- *   (i8x_decode.py:420-422).  H % 128 == 0, I % 128 == 0.
+ *   (i8x_decode.py:420-422).  H % 256 == 0, I % 128 == 0.
  *   ws: workspace of b200_moe_w8a8_workspace_bytes() bytes, 1024-byte aligned.
  *   dbg_acc13 int32 [T*(K+1), 2I] or NULL: raw up accumulators per slot (parity checks).
  *   dbg_h bf16 [T*(K+1), I] or NULL: SwiGLU output per slot.
