@@ -87,6 +87,7 @@ def cpu_baseline(cfg_host, repeats=2):
     """The C restatement (router + int8 MoE block + combine) on the host cores, whole workload."""
     import numpy as np
     from oracle import clib
+    clib.use_all_cores()
     xb = cfg_host["x"].view(__import__("torch").int16).numpy().view(np.uint16)
     gb = cfg_host["gate_w"].view(__import__("torch").int16).numpy().view(np.uint16)
     n = {k: v.numpy() for k, v in cfg_host.items() if k not in ("x", "gate_w") and v is not None}

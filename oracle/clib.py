@@ -30,6 +30,13 @@ def threads() -> int:
     return int(lib().oracle_threads())
 
 
+def use_all_cores() -> int:
+    """Run on every core this process may use, whatever OMP_NUM_THREADS says (torchrun exports 1 for its ranks)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_threads(C.c_int(n))
+    return threads()
+
+
 def gate_logits(x_bits, wr, bias):
     T, H = x_bits.shape
     E = wr.shape[0]

@@ -30,6 +30,15 @@ static inline uint16_t f2bf(float f) {
 }
 static inline float rbf(float f) { return bf2f(f2bf(f)); }
 
+/* n > 0: use n threads from now on (a launcher may have exported OMP_NUM_THREADS=1 for its ranks) */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
