@@ -16,10 +16,14 @@
 
 namespace b200 {
 
-constexpr int RT_TOK = 64, RT_EXP = 64, RT_SLICE = 128, RT_THREADS = 256, RT_PITCH = RT_SLICE + 4;
+constexpr int RT_EXP = 64, RT_SLICE = 128, RT_THREADS = 256, RT_PITCH = RT_SLICE + 4;
 constexpr int RT_XPITCH = RT_SLICE + 8;  // bf16 elements per staged x row (272 bytes: 16-byte aligned, rows on different banks)
-constexpr int RT_WBUF = RT_EXP * RT_PITCH * 4, RT_XRAW = RT_TOK * RT_XPITCH * 2, RT_XS = RT_TOK * RT_PITCH * 4;
-constexpr int RT_SMEM = 2 * RT_WBUF + 2 * RT_XRAW + RT_XS;
+constexpr int RT_WBUF = RT_EXP * RT_PITCH * 4;
+template <int TOK>
+struct RtCfg {  // token-tile height: 64 (4 tokens per thread) up to 64 tokens, 128 (8 per thread) beyond
+  static constexpr int XRAW = TOK * RT_XPITCH * 2, XS = TOK * RT_PITCH * 4;
+  static constexpr int SMEM = 2 * RT_WBUF + 2 * XRAW + XS;
+};
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
@@ -28,18 +32,21 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// A unit of work is a 64-token x 64-expert tile of ONE 128-deep k slice.  Persistent CTAs (one per SM) take
+// A unit of work is a TOK-token x 64-expert tile of ONE 128-deep k slice.  Persistent CTAs (one per SM) take
 // units b, b + grid, ...: the next unit's operand tiles stream into shared memory with cp.async while the
 // current one is computed, so the FMA pipe never waits for a staging round trip and the last wave is not
 // a whole wave.  Both tiles are read as fp32 from shared memory (rows padded to 132 floats so 16-byte
 // reads of consecutive rows hit different banks; x is converted from its staged bf16 copy first); each
-// thread owns 4 tokens x 4 experts and runs their 16 fma chains over the slice in ascending k.  Slice
-// partials go to `part[s][t][e]`; the top-k kernel adds them in slice order.
+// thread owns TOK/16 tokens x 4 experts and runs their fma chains over the slice in ascending k (with 8 tokens
+// per thread there are 12 shared-memory reads per 128 FMAs instead of 8 per 64).  Slice partials go to
+// `part[s][t][e]`; the top-k kernel adds them in slice order.
+template <int RT_TOK>
 __global__ void __launch_bounds__(RT_THREADS, 1) router_partials_kernel(const bf16* __restrict__ x,
                                                                         const float* __restrict__ wr, int T, int H,
                                                                         int E, float* __restrict__ part) {
   extern __shared__ __align__(16) uint8_t rt_smem[];
   auto wbuf = [&](int b) { return reinterpret_cast<float*>(rt_smem + b * RT_WBUF); };
+  constexpr int RT_XRAW = RtCfg<RT_TOK>::XRAW, TI = RT_TOK / 16;
   auto xraw = [&](int b) { return reinterpret_cast<bf16*>(rt_smem + 2 * RT_WBUF + b * RT_XRAW); };
   float* xs = reinterpret_cast<float*>(rt_smem + 2 * RT_WBUF + 2 * RT_XRAW);
   const int tid = threadIdx.x;
@@ -83,20 +90,20 @@ __global__ void __launch_bounds__(RT_THREADS, 1) router_partials_kernel(const bf
     __syncthreads();
     const float* ws = wbuf(buf);
     const int ty = tid >> 4, tx = tid & 15;  // tokens ty + 16 i, experts tx + 16 j
-    float acc[4][4];
+    float acc[TI][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < TI; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 #pragma unroll 4
     for (int k = 0; k < RT_SLICE; k += 4) {
-      float4 xv[4], wv[4];
+      float4 xv[TI], wv[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) xv[i] = *reinterpret_cast<const float4*>(xs + (ty + 16 * i) * RT_PITCH + k);
+      for (int i = 0; i < TI; ++i) xv[i] = *reinterpret_cast<const float4*>(xs + (ty + 16 * i) * RT_PITCH + k);
 #pragma unroll
       for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const float4*>(ws + (tx + 16 * j) * RT_PITCH + k);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < TI; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           acc[i][j] = __fmaf_rn(xv[i].x, wv[j].x, acc[i][j]);
@@ -108,7 +115,7 @@ __global__ void __launch_bounds__(RT_THREADS, 1) router_partials_kernel(const bf
     const int et = u % etiles, tt = (u / etiles) % ttiles, s = u / (etiles * ttiles);
     const int t0 = tt * RT_TOK, e0 = et * RT_EXP;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < TI; ++i) {
       const int t = t0 + ty + 16 * i;
       if (t < T)
 #pragma unroll
@@ -461,14 +468,21 @@ extern "C" int b200_router(const void* x, const float* wr, const float* bias, in
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaFuncSetAttribute(router_partials_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM);
+    cudaFuncSetAttribute(router_partials_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, RtCfg<64>::SMEM);
+    cudaFuncSetAttribute(router_partials_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, RtCfg<128>::SMEM);
     attr_done[dev] = true;
   }
   float* part = static_cast<float*>(scratch);
   const int nslices = H / RT_SLICE;
-  const int nunits = ((T + RT_TOK - 1) / RT_TOK) * (E / RT_EXP) * nslices;
-  dim3 grid(nunits < sm_count() ? nunits : sm_count());
-  launch_k(router_partials_kernel, grid, dim3(RT_THREADS), RT_SMEM, st, static_cast<const bf16*>(x), wr, T, H, E, part);
+  if (T > 64) {
+    const int nunits = ((T + 127) / 128) * (E / RT_EXP) * nslices;
+    launch_k(router_partials_kernel<128>, dim3(nunits < sm_count() ? nunits : sm_count()), dim3(RT_THREADS), RtCfg<128>::SMEM,
+             st, static_cast<const bf16*>(x), wr, T, H, E, part);
+  } else {
+    const int nunits = (E / RT_EXP) * nslices;
+    launch_k(router_partials_kernel<64>, dim3(nunits < sm_count() ? nunits : sm_count()), dim3(RT_THREADS), RtCfg<64>::SMEM,
+             st, static_cast<const bf16*>(x), wr, T, H, E, part);
+  }
   const int rb = flags & 1;
   const int pl = (E + 127) / 128;
   if (pl <= 1)
