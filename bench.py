@@ -198,7 +198,29 @@ def other_kernels(dev, steps, warmup, only=None):
         _lmhead_entry(dev, ops, synth, timed, st, it, out, hbm)
     if want("moe_fp8_t16") or want("router"):
         _moe_fp8_router_entry(dev, ops, synth, timed, st, out, hbm, want)
+    if want("decode_step"):
+        _decode_step_entry(dev, timed, out)
     return out
+
+
+def _decode_step_entry(dev, timed, out):
+    # the whole 48-layer stack (36 GDN + 12 attention layers, fp8 experts, LM head) for one GPU's share of the
+    # 64-sequence batch under 8-way batch sharding: 8 sequences x 4 drafts, 8192 tokens of context each
+    import torch
+    from bundles_b200 import decode_step, ops
+    try:
+        torch.cuda.empty_cache()
+        step = decode_step.DecodeStep(layers=48, B=8, ctx=8192, device=dev)
+        x = torch.randn(step.T, 2048, device=dev).to(torch.bfloat16)
+        ms = timed(lambda: step.step(x), n=5)
+        out["decode_step"] = {"config": "48 layers (12 attention, 36 GDN), 512 fp8 experts top-10 per layer, B=8 x 4 drafts, "
+                                        "ctx 8192, LM head 151936 (one GPU, no expert parallelism)",
+                              "ms": ms, "launches_per_step": step.launches, "status": ops.read_status(step.status),
+                              "device_memory_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1)}
+        del step
+    except Exception as exc:  # noqa: BLE001
+        out["decode_step"] = {"error": repr(exc)[:200]}
+    torch.cuda.empty_cache()
 
 
 def _gdn_entry(dev, ops, synth, timed, st, it, out, hbm, which):
@@ -407,7 +429,8 @@ def main():
     ap.add_argument("--parallel", default="ep", choices=["ep", "replicas"],
                     help="N > 1: expert-parallel (experts split over ranks) or independent replicas")
     ap.add_argument("--only-kernel", default=None,
-                    choices=["gdn_verify", "attn_verify", "attn_front", "lmhead_shard_argmax", "moe_fp8_t16", "router"],
+                    choices=["gdn_verify", "attn_verify", "attn_front", "lmhead_shard_argmax", "moe_fp8_t16", "router",
+                             "decode_step"],
                     help="run one entry of `kernels` alone with plain launches (a small target for an ncu capture) and exit")
     args = ap.parse_args()
     if args.only_kernel:
