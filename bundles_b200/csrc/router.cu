@@ -317,8 +317,8 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
   int* cnt = lists_smem;                   // [E1]   rows per expert
   int* off = cnt + E1;                     // [E1+1] first row per expert
   int* bstart = off + E1 + 1;              // [E1+1] first block per expert
-  int* wsum = bstart + E1 + 1;             // [64]   scan scratch
-  uint16_t* cntw = reinterpret_cast<uint16_t*>(wsum + 64);        // [32][E1] per-warp counters -> bases
+  int* wsum = bstart + E1 + 1;             // [96]   scan scratch
+  uint16_t* cntw = reinterpret_cast<uint16_t*>(wsum + 96);        // [32][E1] per-warp counters -> bases
   int16_t* sid = reinterpret_cast<int16_t*>(cntw + LISTS_WARPS * E1);  // [P] local expert or -1
   uint16_t* srank = reinterpret_cast<uint16_t*>(sid + P);              // [P] rank inside the warp segment
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -353,7 +353,7 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
   }
   __syncthreads();
   // per expert: exclusive scan of the warp counters -> base of each warp's segment; total -> cnt
-  int c = 0, nb = 0;
+  int c = 0;
   if (tid < E1) {
     if (tid < E_local) {
       int run = 0;
@@ -367,43 +367,56 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
       c = shared_n;  // tokens [shared_lo, shared_lo + shared_n) get a shared-expert row
     }
     cnt[tid] = c;
-    nb = (c + block_rows - 1) / block_rows;
   }
-  // block-wide exclusive scans of (rows of routed experts, blocks) over experts
-  int rows_incl = (tid < E_local) ? c : 0, blks_incl = nb;
+  // Blocks are listed heaviest first: all full blocks, then partial blocks of 32 rows or more, then the small ones,
+  // each class in expert order.  The GEMMs deal tiles to their CTAs round-robin, so every CTA gets its share of
+  // the expensive tiles instead of whatever the expert order happens to give it.
+  const int nfull = c / block_rows, tail = c - nfull * block_rows;
+  const int nmid = tail >= 32 ? 1 : 0, nsmall = (tail > 0 && tail < 32) ? 1 : 0;
+  // block-wide exclusive scans of (rows of routed experts, blocks by class) over experts: the two partial classes
+  // share one word (16 bits each: at most one block per expert and class)
+  int rows_incl = (tid < E_local) ? c : 0, blks_incl = nfull, part_incl = nmid | (nsmall << 16);
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const int a = __shfl_up_sync(FULL_MASK, rows_incl, o), b2 = __shfl_up_sync(FULL_MASK, blks_incl, o);
+    const int p2 = __shfl_up_sync(FULL_MASK, part_incl, o);
     if (lane >= o) {
       rows_incl += a;
       blks_incl += b2;
+      part_incl += p2;
     }
   }
   if (lane == 31) {
     wsum[warp] = rows_incl;
     wsum[32 + warp] = blks_incl;
+    wsum[64 + warp] = part_incl;
   }
   __syncthreads();
   if (warp == 0) {
-    int a = wsum[lane], b2 = wsum[32 + lane];
+    int a = wsum[lane], b2 = wsum[32 + lane], p3 = wsum[64 + lane];
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int a2 = __shfl_up_sync(FULL_MASK, a, o), b3 = __shfl_up_sync(FULL_MASK, b2, o);
+      const int p4 = __shfl_up_sync(FULL_MASK, p3, o);
       if (lane >= o) {
         a += a2;
         b2 += b3;
+        p3 += p4;
       }
     }
     wsum[lane] = a;
     wsum[32 + lane] = b2;
+    wsum[64 + lane] = p3;
   }
   __syncthreads();
   const int rows_excl = rows_incl - ((tid < E_local) ? c : 0) + (warp ? wsum[warp - 1] : 0);
-  const int blks_excl = blks_incl - nb + (warp ? wsum[32 + warp - 1] : 0);
-  const int total_blocks = wsum[63];
+  const int full_excl = blks_incl - nfull + (warp ? wsum[32 + warp - 1] : 0);
+  const int part_excl = part_incl - (nmid | (nsmall << 16)) + (warp ? wsum[64 + warp - 1] : 0);
+  const int total_full = wsum[63], total_mid = wsum[95] & 0xffff, total_small = wsum[95] >> 16;
+  const int total_blocks = total_full + total_mid + total_small;
   if (tid < E1) {
     off[tid] = tid < E_local ? rows_excl : P + shared_lo;  // the shared expert's rows follow the routed region, row P + t for token t
-    bstart[tid] = blks_excl;
+    bstart[tid] = full_excl;
     L.counts[tid] = c;
     L.offsets[tid] = off[tid];
     if (tid == E_local) L.offsets[E1] = P + shared_lo + c;
@@ -428,17 +441,23 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
     }
   if (total_blocks <= max_blocks && tid < E1) {
     int b = bstart[tid];
-    for (int r0 = 0; r0 < c; r0 += block_rows, ++b) {
+    for (int j = 0; j < nfull; ++j, ++b) {
       L.blk_expert[b] = tid;
-      L.blk_row0[b] = off[tid] + r0;
-      L.blk_rows[b] = min(block_rows, c - r0);
+      L.blk_row0[b] = off[tid] + j * block_rows;
+      L.blk_rows[b] = block_rows;
+    }
+    if (tail > 0) {
+      b = nmid ? total_full + (part_excl & 0xffff) : total_full + total_mid + (part_excl >> 16);
+      L.blk_expert[b] = tid;
+      L.blk_row0[b] = off[tid] + nfull * block_rows;
+      L.blk_rows[b] = tail;
     }
   }
 }
 
 static size_t lists_smem_bytes(int T, int K, int E_local) {
   const size_t E1 = E_local + 1, P = static_cast<size_t>(T) * K;
-  return (E1 + 2 * (E1 + 1) + 64) * 4 + LISTS_WARPS * E1 * 2 + P * 4 + 16;
+  return (E1 + 2 * (E1 + 1) + 96) * 4 + LISTS_WARPS * E1 * 2 + P * 4 + 16;
 }
 
 }  // namespace b200

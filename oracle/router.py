@@ -89,9 +89,9 @@ def routing_lists(ids: np.ndarray, n_experts: int, valid: np.ndarray | None = No
     A routed pair p = t * top_k + j (the reference's slot id, i8x_decode.py:297) lands in the
     sorted row offsets[e] + rank, rank = number of earlier valid pairs with the same expert.
     Rows of tokens whose `valid` flag is false (graph padding, position == 0 in the reference:
-    qk_route.cu:229,307) get row -1 and are not counted.  The block list walks experts in
-    ascending order and cuts each expert's rows into `block`-row pieces (the reference cuts at
-    16; the target's MMA N tile is up to 128).
+    qk_route.cu:229,307) get row -1 and are not counted.  Each expert's rows are cut into `block`-row
+    pieces (the reference cuts at 16; the target's MMA N tile is up to 128); the block list is ordered
+    heaviest first (see below), the reference's walks experts in ascending order.
     Returns dict(counts, offsets [E+1], row_of_pair [T*k], pair_of_row [sum counts],
                  blk_expert, blk_row0, blk_rows).
     """
@@ -113,13 +113,17 @@ def routing_lists(ids: np.ndarray, n_experts: int, valid: np.ndarray | None = No
     pair_of_row = np.full(int(offsets[-1]), -1, dtype=np.int32)
     sel = row_of_pair >= 0
     pair_of_row[row_of_pair[sel]] = np.nonzero(sel)[0]
-    be, b0, bn = [], [], []
+    # heaviest first: full blocks, then partial blocks of 32 rows or more, then the small ones, each class in
+    # expert order (the GEMMs deal tiles to their CTAs round-robin; the reference's list is in expert order)
+    classes = ([], [], [])
     for e in range(n_experts):
         c = int(counts[e])
         for r0 in range(0, c, block):
-            be.append(e)
-            b0.append(int(offsets[e]) + r0)
-            bn.append(min(block, c - r0))
+            n = min(block, c - r0)
+            classes[0 if n == block else (1 if n >= 32 else 2)].append((e, int(offsets[e]) + r0, n))
+    be = [t[0] for cl in classes for t in cl]
+    b0 = [t[1] for cl in classes for t in cl]
+    bn = [t[2] for cl in classes for t in cl]
     return dict(counts=counts, offsets=offsets, row_of_pair=row_of_pair, pair_of_row=pair_of_row,
                 blk_expert=np.asarray(be, dtype=np.int32), blk_row0=np.asarray(b0, dtype=np.int32),
                 blk_rows=np.asarray(bn, dtype=np.int32))

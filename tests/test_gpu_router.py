@@ -91,9 +91,17 @@ def test_lists_match_oracle():
         nb = int(lists.nblocks[0])
         nref = len(ref["blk_expert"])
         assert nb == nref + (T + block - 1) // block
-        assert np.array_equal(lists.blk_expert.cpu().numpy()[:nref], ref["blk_expert"])
-        assert np.array_equal(lists.blk_row0.cpu().numpy()[:nref], ref["blk_row0"])
-        assert np.array_equal(lists.blk_rows.cpu().numpy()[:nref], ref["blk_rows"])
+        # the shared expert (index E, rows T*K .. T*K + T) is the last expert of each size class
+        want = [[], [], []]
+        for e, r0, n_ in zip(ref["blk_expert"], ref["blk_row0"], ref["blk_rows"]):
+            want[0 if n_ == block else (1 if n_ >= 32 else 2)].append((int(e), int(r0), int(n_)))
+        for r0 in range(0, T, block):
+            n_ = min(block, T - r0)
+            want[0 if n_ == block else (1 if n_ >= 32 else 2)].append((E, T * K + r0, n_))
+        want = [t for cl in want for t in cl]
+        got = list(zip(lists.blk_expert.cpu().numpy()[:nb].tolist(), lists.blk_row0.cpu().numpy()[:nb].tolist(),
+                       lists.blk_rows.cpu().numpy()[:nb].tolist()))
+        assert got == want
         w_rows = lists.wt_of_row.cpu().numpy()[:n]
         assert np.array_equal(w_rows, w_np.reshape(-1)[ref["pair_of_row"]])
 
