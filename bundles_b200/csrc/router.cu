@@ -317,8 +317,8 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
   int* cnt = lists_smem;                   // [E1]   rows per expert
   int* off = cnt + E1;                     // [E1+1] first row per expert
   int* bstart = off + E1 + 1;              // [E1+1] first block per expert
-  int* wsum = bstart + E1 + 1;             // [96]   scan scratch
-  uint16_t* cntw = reinterpret_cast<uint16_t*>(wsum + 96);        // [32][E1] per-warp counters -> bases
+  int* wsum = bstart + E1 + 1;             // [128]  scan scratch
+  uint16_t* cntw = reinterpret_cast<uint16_t*>(wsum + 128);        // [32][E1] per-warp counters -> bases
   int16_t* sid = reinterpret_cast<int16_t*>(cntw + LISTS_WARPS * E1);  // [P] local expert or -1
   uint16_t* srank = reinterpret_cast<uint16_t*>(sid + P);              // [P] rank inside the warp segment
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -368,18 +368,20 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
     }
     cnt[tid] = c;
   }
-  // Blocks are listed heaviest first: all full blocks, then partial blocks of 32 rows or more, then the small ones,
-  // each class in expert order.  The GEMMs deal tiles to their CTAs round-robin, so every CTA gets its share of
+  // Blocks are listed heaviest first: all full blocks, then the partial blocks by quarter of the block size
+  // (3/4 and more, 1/2, 1/4, less), each class in expert order.  The GEMMs deal tiles to their CTAs round-robin, so every CTA gets its share of
   // the expensive tiles instead of whatever the expert order happens to give it.
   const int nfull = c / block_rows, tail = c - nfull * block_rows;
-  const int nmid = tail >= 32 ? 1 : 0, nsmall = (tail > 0 && tail < 32) ? 1 : 0;
-  // block-wide exclusive scans of (rows of routed experts, blocks by class) over experts: the two partial classes
-  // share one word (16 bits each: at most one block per expert and class)
-  int rows_incl = (tid < E_local) ? c : 0, blks_incl = nfull, part_incl = nmid | (nsmall << 16);
+  const int pcls = tail == 0 ? -1 : 3 - min(3, (4 * tail) / block_rows);  // 0: >= 3/4 of a block ... 3: < 1/4
+  const unsigned long long pone = pcls < 0 ? 0ull : 1ull << (16 * pcls);
+  // block-wide exclusive scans of (rows of routed experts, blocks by class) over experts: the four partial classes
+  // share one 64-bit word (16 bits each: at most one block per expert and class)
+  int rows_incl = (tid < E_local) ? c : 0, blks_incl = nfull;
+  unsigned long long part_incl = pone;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const int a = __shfl_up_sync(FULL_MASK, rows_incl, o), b2 = __shfl_up_sync(FULL_MASK, blks_incl, o);
-    const int p2 = __shfl_up_sync(FULL_MASK, part_incl, o);
+    const unsigned long long p2 = __shfl_up_sync(FULL_MASK, part_incl, o);
     if (lane >= o) {
       rows_incl += a;
       blks_incl += b2;
@@ -389,15 +391,18 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
   if (lane == 31) {
     wsum[warp] = rows_incl;
     wsum[32 + warp] = blks_incl;
-    wsum[64 + warp] = part_incl;
+    wsum[64 + 2 * warp] = static_cast<int>(part_incl & 0xffffffffull);
+    wsum[65 + 2 * warp] = static_cast<int>(part_incl >> 32);
   }
   __syncthreads();
   if (warp == 0) {
-    int a = wsum[lane], b2 = wsum[32 + lane], p3 = wsum[64 + lane];
+    int a = wsum[lane], b2 = wsum[32 + lane];
+    unsigned long long p3 = static_cast<unsigned int>(wsum[64 + 2 * lane]) |
+                            (static_cast<unsigned long long>(static_cast<unsigned int>(wsum[65 + 2 * lane])) << 32);
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int a2 = __shfl_up_sync(FULL_MASK, a, o), b3 = __shfl_up_sync(FULL_MASK, b2, o);
-      const int p4 = __shfl_up_sync(FULL_MASK, p3, o);
+      const unsigned long long p4 = __shfl_up_sync(FULL_MASK, p3, o);
       if (lane >= o) {
         a += a2;
         b2 += b3;
@@ -406,14 +411,25 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
     }
     wsum[lane] = a;
     wsum[32 + lane] = b2;
-    wsum[64 + lane] = p3;
+    wsum[64 + 2 * lane] = static_cast<int>(p3 & 0xffffffffull);
+    wsum[65 + 2 * lane] = static_cast<int>(p3 >> 32);
   }
   __syncthreads();
   const int rows_excl = rows_incl - ((tid < E_local) ? c : 0) + (warp ? wsum[warp - 1] : 0);
   const int full_excl = blks_incl - nfull + (warp ? wsum[32 + warp - 1] : 0);
-  const int part_excl = part_incl - (nmid | (nsmall << 16)) + (warp ? wsum[64 + warp - 1] : 0);
-  const int total_full = wsum[63], total_mid = wsum[95] & 0xffff, total_small = wsum[95] >> 16;
-  const int total_blocks = total_full + total_mid + total_small;
+  auto wsum64 = [&](int w) {
+    return static_cast<unsigned int>(wsum[64 + 2 * w]) |
+           (static_cast<unsigned long long>(static_cast<unsigned int>(wsum[65 + 2 * w])) << 32);
+  };
+  const unsigned long long part_excl = part_incl - pone + (warp ? wsum64(warp - 1) : 0ull);
+  const unsigned long long part_tot = wsum64(31);
+  const int total_full = wsum[63];
+  int cls_base[4], total_blocks = total_full;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    cls_base[k] = total_blocks;
+    total_blocks += static_cast<int>((part_tot >> (16 * k)) & 0xffffull);
+  }
   if (tid < E1) {
     off[tid] = tid < E_local ? rows_excl : P + shared_lo;  // the shared expert's rows follow the routed region, row P + t for token t
     bstart[tid] = full_excl;
@@ -447,7 +463,10 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
       L.blk_rows[b] = block_rows;
     }
     if (tail > 0) {
-      b = nmid ? total_full + (part_excl & 0xffff) : total_full + total_mid + (part_excl >> 16);
+      b = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (k == pcls) b = cls_base[k] + static_cast<int>((part_excl >> (16 * k)) & 0xffffull);
       L.blk_expert[b] = tid;
       L.blk_row0[b] = off[tid] + nfull * block_rows;
       L.blk_rows[b] = tail;
@@ -457,7 +476,7 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
 
 static size_t lists_smem_bytes(int T, int K, int E_local) {
   const size_t E1 = E_local + 1, P = static_cast<size_t>(T) * K;
-  return (E1 + 2 * (E1 + 1) + 96) * 4 + LISTS_WARPS * E1 * 2 + P * 4 + 16;
+  return (E1 + 2 * (E1 + 1) + 128) * 4 + LISTS_WARPS * E1 * 2 + P * 4 + 16;
 }
 
 }  // namespace b200

@@ -113,14 +113,14 @@ def routing_lists(ids: np.ndarray, n_experts: int, valid: np.ndarray | None = No
     pair_of_row = np.full(int(offsets[-1]), -1, dtype=np.int32)
     sel = row_of_pair >= 0
     pair_of_row[row_of_pair[sel]] = np.nonzero(sel)[0]
-    # heaviest first: full blocks, then partial blocks of 32 rows or more, then the small ones, each class in
-    # expert order (the GEMMs deal tiles to their CTAs round-robin; the reference's list is in expert order)
-    classes = ([], [], [])
+    # heaviest first: full blocks, then partial blocks by quarter of the block size (>= 3/4, >= 1/2, >= 1/4, less),
+    # each class in expert order (the GEMMs deal tiles to their CTAs round-robin; the reference's list is in expert order)
+    classes = ([], [], [], [], [])
     for e in range(n_experts):
         c = int(counts[e])
         for r0 in range(0, c, block):
             n = min(block, c - r0)
-            classes[0 if n == block else (1 if n >= 32 else 2)].append((e, int(offsets[e]) + r0, n))
+            classes[0 if n == block else 4 - min(3, (4 * n) // block)].append((e, int(offsets[e]) + r0, n))
     be = [t[0] for cl in classes for t in cl]
     b0 = [t[1] for cl in classes for t in cl]
     bn = [t[2] for cl in classes for t in cl]
