@@ -371,7 +371,10 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
   // Blocks are listed heaviest first: all full blocks, then the partial blocks by quarter of the block size
   // (3/4 and more, 1/2, 1/4, less), each class in expert order.  The GEMMs deal tiles to their CTAs round-robin, so every CTA gets its share of
   // the expensive tiles instead of whatever the expert order happens to give it.
-  const int nfull = c / block_rows, tail = c - nfull * block_rows;
+  // (Lists with smaller blocks feed the fp8 GEMMs, whose CTAs take contiguous tile ranges: those keep expert order.)
+  const bool heavy_first = block_rows == 128;
+  const int nfull = heavy_first ? c / block_rows : (c + block_rows - 1) / block_rows;
+  const int tail = heavy_first ? c - nfull * block_rows : 0;
   const int pcls = tail == 0 ? -1 : 3 - min(3, (4 * tail) / block_rows);  // 0: >= 3/4 of a block ... 3: < 1/4
   const unsigned long long pone = pcls < 0 ? 0ull : 1ull << (16 * pcls);
   // block-wide exclusive scans of (rows of routed experts, blocks by class) over experts: the four partial classes
@@ -460,7 +463,7 @@ __global__ void __launch_bounds__(LISTS_THREADS) moe_lists_kernel(const int32_t*
     for (int j = 0; j < nfull; ++j, ++b) {
       L.blk_expert[b] = tid;
       L.blk_row0[b] = off[tid] + j * block_rows;
-      L.blk_rows[b] = block_rows;
+      L.blk_rows[b] = min(block_rows, c - j * block_rows);
     }
     if (tail > 0) {
       b = 0;

@@ -106,7 +106,11 @@ typedef struct b200_moe_lists {
   int32_t* nblocks;     /* [1] */
 } b200_moe_lists;
 
-/* max_blocks the caller must provide for a given problem */
+/* Order of the block list: with block_rows = 128 the blocks come heaviest first (all full blocks, then the
+ * partial ones by quarter of the block size, each class in expert order), which balances the int8 GEMMs'
+ * round-robin tile deal; with smaller block_rows they come in expert order (the reference's order,
+ * qk_route.cu:322-357).  Consumers must not assume either.
+ * max_blocks the caller must provide for a given problem: */
 int b200_moe_max_blocks(int T, int K, int E_local, int block_rows);
 
 int b200_moe_build_lists(const int32_t* ids, const float* wts, const int64_t* pos, int T, int K, int e_lo,

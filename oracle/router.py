@@ -120,7 +120,8 @@ def routing_lists(ids: np.ndarray, n_experts: int, valid: np.ndarray | None = No
         c = int(counts[e])
         for r0 in range(0, c, block):
             n = min(block, c - r0)
-            classes[0 if n == block else 4 - min(3, (4 * n) // block)].append((e, int(offsets[e]) + r0, n))
+            cls = 0 if (n == block or block != 128) else 4 - min(3, (4 * n) // block)  # only 128-row lists are reordered
+            classes[cls].append((e, int(offsets[e]) + r0, n))
     be = [t[0] for cl in classes for t in cl]
     b0 = [t[1] for cl in classes for t in cl]
     bn = [t[2] for cl in classes for t in cl]

@@ -94,10 +94,10 @@ def test_lists_match_oracle():
         # the shared expert (index E, rows T*K .. T*K + T) is the last expert of each size class
         want = [[], [], [], [], []]
         for e, r0, n_ in zip(ref["blk_expert"], ref["blk_row0"], ref["blk_rows"]):
-            want[0 if n_ == block else 4 - min(3, (4 * n_) // block)].append((int(e), int(r0), int(n_)))
+            want[0 if (n_ == block or block != 128) else 4 - min(3, (4 * n_) // block)].append((int(e), int(r0), int(n_)))
         for r0 in range(0, T, block):
             n_ = min(block, T - r0)
-            want[0 if n_ == block else 4 - min(3, (4 * n_) // block)].append((E, T * K + r0, n_))
+            want[0 if (n_ == block or block != 128) else 4 - min(3, (4 * n_) // block)].append((E, T * K + r0, n_))
         want = [t for cl in want for t in cl]
         got = list(zip(lists.blk_expert.cpu().numpy()[:nb].tolist(), lists.blk_row0.cpu().numpy()[:nb].tolist(),
                        lists.blk_rows.cpu().numpy()[:nb].tolist()))
