@@ -198,9 +198,54 @@ def other_kernels(dev, steps, warmup, only=None):
         _lmhead_entry(dev, ops, synth, timed, st, it, out, hbm)
     if want("moe_fp8_t16") or want("router"):
         _moe_fp8_router_entry(dev, ops, synth, timed, st, out, hbm, want)
+    if want("moe_w8a8_prefill"):
+        _moe_w8a8_prefill_entry(dev, ops, synth, timed, st, out)
     if want("decode_step"):
         _decode_step_entry(dev, timed, out)
     return out
+
+
+def _moe_w8a8_prefill_entry(dev, ops, synth, timed, st, out):
+    # the int8 block at prefill-sized chunks (1024 and 2048 tokens): the same kernels over longer block lists,
+    # many experts with several 128-row blocks; int8 operations per second over the routed + shared rows
+    import torch
+    torch.cuda.empty_cache()
+    try:
+        Hh, Ii, Kk = 2048, 512, 10
+        c = synth.moe_w8a8(T=2048, device=dev)
+        w = ops.MoeW8A8Weights(c["w13"], c["s13"], c["w2"], c["s2"], c["sh13"], c["shs13"], c["sh2"], c["shs2"])
+        for Tn in (1024, 2048):
+            x = c["x"][:Tn].contiguous()
+            lists = ops.RoutingLists(Tn, Kk, 512, 128, dev)
+            scr = ops.router_scratch(Tn, Hh, 512, dev)
+            ids = torch.empty(Tn, Kk, dtype=torch.int32, device=dev)
+            wts = torch.empty(Tn, Kk, dtype=torch.float32, device=dev)
+            ws = ops.moe_w8a8_workspace(Tn, Hh, Ii, Kk, dev)
+            cache = torch.zeros(Tn * (Kk + 1), Hh, dtype=torch.bfloat16, device=dev)
+            res = torch.empty(Tn, Hh, dtype=torch.bfloat16, device=dev)
+
+            def block():
+                ops.router(x, c["wr"], Kk, c["bias"], scratch=scr, want_logits=False, ids=ids, wts=wts)
+                ops.build_lists(ids, wts, lists)
+                ops.moe_w8a8(x, w, lists, cache=cache, ws=ws, status=st)
+                ops.moe_combine(cache, x, c["gate_w"], Kk, out=res)
+
+            ms = timed(block)
+            ms_gemm = timed(lambda: ops.moe_w8a8(x, w, lists, cache=cache, ws=ws, status=st))
+            rows = Tn * (Kk + 1)
+            iops = 2 * rows * 3 * Hh * Ii
+            act = int((lists.counts > 0).sum().item())
+            out[f"moe_w8a8_prefill_t{Tn}"] = {
+                "config": f"T={Tn}, E=512, top-10 + shared, int8 W8A8, Zipf(1.1) (router, lists, 4 GEMM-chain launches, combine)",
+                "ms": ms, "tokens_per_s": Tn / ms * 1e3, "ms_quant_up_hquant_down": ms_gemm,
+                "int8_tops_gemm_chain": iops / ms_gemm / 1e9, "active_experts": act,
+                "blocks": int(lists.nblocks.item()), "weight_bytes_once": act * 3 * Hh * Ii,
+                "status": ops.read_status(st)}
+            del lists, scr, ws, cache, res
+        del c, w
+    except Exception as exc:  # noqa: BLE001
+        out["moe_w8a8_prefill"] = {"error": repr(exc)[:300]}
+    torch.cuda.empty_cache()
 
 
 def _decode_step_entry(dev, timed, out):
@@ -430,7 +475,7 @@ def main():
                     help="N > 1: expert-parallel (experts split over ranks) or independent replicas")
     ap.add_argument("--only-kernel", default=None,
                     choices=["gdn_verify", "attn_verify", "attn_front", "lmhead_shard_argmax", "moe_fp8_t16", "router",
-                             "decode_step"],
+                             "moe_w8a8_prefill", "decode_step"],
                     help="run one entry of `kernels` alone with plain launches (a small target for an ncu capture) and exit")
     args = ap.parse_args()
     if args.only_kernel:

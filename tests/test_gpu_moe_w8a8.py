@@ -99,6 +99,13 @@ def test_full_config_t256_e512():
     _check(cfg, 10)
 
 
+def test_prefill_chunk_t1024():
+    # a prefill-sized chunk: 10 240 routed pairs over 64 experts, every expert with several 128-row blocks
+    # (the reference runs its W8A8 lanes at >= 1024 rows per chunk, qk_moe_prefill_i8.cu:3646-3655)
+    cfg = synth.moe_w8a8(seed=18, T=1024, E=64, zipf_s=1.1)
+    _check(cfg, 10)
+
+
 def test_linearity_property_full_size():
     # size-independent property: doubling a routing weight doubles that slot's cache row (exactly, in bf16,
     # up to the rounding of y * w): checked through the combine with K = 1 and weight 1 vs the cache row itself
