@@ -18,6 +18,18 @@
 // three CTAs share an SM so the copies of one overlap the arithmetic of the others; the CTAs are persistent
 // and walk the units.  The two value heads of a key head run as a 2-CTA cluster: both read the q/k conv
 // state, meet at a cluster barrier, then rank 0 rolls it.
+//
+// The same kernel has a second form (REPLAY) for the state layout the reference's engine hands its kernel
+// (qk_gdn_verify.cu:61-73,586-593,631-647,706-717,769-781): a read-only fp32 checkpoint H0 per slot plus a
+// 16-entry circular ring of (d, k, g) per request, of which the first write_pos logical entries (physical
+// entry (cache_base + c) & 15) are committed.  The state the window sees is
+//   S = e^{total} H0 + sum_c e^{total - pre_c} d_c k_c^T,   pre_c = g_0 + .. + g_c, total = pre_{wp-1},
+// so S x = e^{total} (H0 x) + sum_c e^{total - pre_c} d_c (k_c . x): the H0 products run on the tensor core as
+// before, the ring keys' dots against [q | k] on the CUDA cores.  Nothing is written to the checkpoint: the
+// window's D_s, unit keys and gates are appended to the ring as bf16 high and low parts (g in fp32) at
+// logical entries write_pos + s (those below 16), the conv state is rolled by the whole window and the
+// per-draft windows are recorded as [s1 s2 x0 x1 x2 x3] per channel; which of it survives is the engine's
+// move of the ring cursor.
 #include "common.cuh"
 #include "host.h"
 
@@ -28,6 +40,7 @@ constexpr int G_QDIM = G_HK * G_D;             // 2048
 constexpr int G_CONV = 2 * G_QDIM + G_HV * G_D;  // 8192
 constexpr int G_ZDIM = G_HV * G_D;             // 4096
 constexpr int G_THREADS = 256;
+constexpr int G_RING = 16;                     // ReplaySSM ring entries per request
 constexpr uint32_t G_TILE_BYTES = G_D * G_D * 4;
 
 // Shared memory of one unit.  S holds the state tile as four 128-row x 32-float sub-tiles in the
@@ -48,6 +61,10 @@ struct GdnSmem {
   float cE[G_NT], cR[G_NT], cC[G_NT];  // e^{G_s}; beta_s; e^{G_{n-1} - G_i} for i < n_acc else 0
   float red[8][G_NT];
   float nrm[2][G_NT][4];
+  float xr[G_RING][8];      // REPLAY: ring key c . [q | k]
+  float gr[G_RING];         // REPLAY: committed g in logical order (0 past the history)
+  float dec[G_RING];        // REPLAY: e^{total - pre_c} (0 past the history)
+  float tdec;               // REPLAY: e^{total}
   uint64_t bar_load, bar_mma;
   uint32_t tmem_slot;
   int abort_flag;
@@ -102,6 +119,15 @@ __device__ __forceinline__ void conv_roll(const ConvIn& in, bf16* __restrict__ c
   cs_b[ch * 3 + 2] = c;
 }
 
+// the per-draft windows of a channel, deduplicated: [s1 s2 x0 x1 x2 x3] (Conv4::store, qk_gdn_verify.cu:277-289)
+__device__ __forceinline__ void conv_record(const ConvIn& in, bf16* __restrict__ wrec, int ch) {
+  uint32_t* dst = reinterpret_cast<uint32_t*>(wrec + static_cast<size_t>(ch) * 6);
+#pragma unroll
+  for (int i = 0; i < 3; ++i)
+    dst[i] = static_cast<uint32_t>(__bfloat16_as_ushort(in.win[1 + 2 * i])) |
+             (static_cast<uint32_t>(__bfloat16_as_ushort(in.win[2 + 2 * i])) << 16);
+}
+
 struct GdnArgs {
   const bf16* mixed;
   const bf16* z;
@@ -118,8 +144,21 @@ struct GdnArgs {
   int B;
   bf16* out;
   int32_t* status;
+  // REPLAY form: `state` is the read-only checkpoint pool, indexed by state_idx[b] like conv_state
+  bf16* window;             // [window slots, 8192, 6]
+  bf16* d_ring;             // [ring slots, 32, 16, 128] high parts (read and appended)
+  bf16* dlo_ring;           // low parts (appended only)
+  bf16* k_ring;             // [ring slots, 16, 16, 128]
+  bf16* klo_ring;
+  float* g_ring;            // [ring slots, 32, 16]
+  const int32_t* state_idx;   // [B] checkpoint / conv-state slot, < 0: padded request (zero output, nothing written)
+  const int32_t* ring_idx;    // [B] ring slot
+  const int32_t* win_idx;     // [B] window slot
+  const int32_t* write_pos;   // [ring slots] committed entries
+  const int32_t* cache_base;  // [ring slots] physical entry of logical entry 0
 };
 
+template <bool REPLAY>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 3)
 gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -146,14 +185,29 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   bool ok = true;
   uint32_t par = 0;  // parity of this unit's phase of both mbarriers
   for (int pair = blockIdx.x >> 1; pair < npairs; pair += ncl, par ^= 1u) {
+  const int b = pair / G_HK, hk = pair - b * G_HK, hv = 2 * hk + rank;
+  int slot = b;
+  if constexpr (REPLAY) {
+    slot = p.state_idx[b];
+    if (slot < 0) {  // a padded request: zero output, nothing read or written; no barrier phase is used
+      if (ok && tid < G_D)
+#pragma unroll
+        for (int s = 0; s < G_NT; ++s)
+          p.out[(static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv * G_D + tid] = f2bf(0.f);
+      par ^= 1u;
+      continue;
+    }
+  }
   if (!ok) {  // after an abandoned wait the CTA only keeps its partner's cluster barriers company
     cluster_sync();
     continue;
   }
-  const int b = pair / G_HK, hk = pair - b * G_HK, hv = 2 * hk + rank;
-  int n_acc = p.accepted[b];
-  n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
-  const int srow0 = (b * G_HV + hv) * G_D;  // first row of this unit in the [B*32*128, 128] view of the state
+  int n_acc = G_NT;  // REPLAY: the conv state is rolled by the whole window
+  if constexpr (!REPLAY) {
+    n_acc = p.accepted[b];
+    n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
+  }
+  const int srow0 = (slot * G_HV + hv) * G_D;  // first row of this unit in the [slots*32*128, 128] view of the state
   if (tid == 0) {
     bulk_wait_read_all();  // the previous unit's tile has left shared memory
     mbar_expect_tx(&sm.bar_load, G_TILE_BYTES);
@@ -163,9 +217,16 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
 
   // ---- every global input of this unit is requested before anything is computed ----
   const bf16* mixed_b = p.mixed + static_cast<size_t>(b) * G_NT * G_CONV;
-  bf16* cs_b = p.conv_state + static_cast<size_t>(b) * G_CONV * 3;
+  bf16* cs_b = p.conv_state + static_cast<size_t>(slot) * G_CONV * 3;
   const int c = tid & 127;
   const bool is_k = tid >= 128;
+  int ring = 0, wp = 0, cb = 0;
+  if constexpr (REPLAY) {
+    ring = p.ring_idx[b];
+    wp = p.write_pos[ring];
+    cb = p.cache_base[ring];
+    wp = wp < 0 ? 0 : (wp > G_RING ? G_RING : wp);
+  }
   const int ch_qk = (is_k ? G_QDIM : 0) + hk * G_D + c;
   const int ch_v = 2 * G_QDIM + hv * G_D + c;
   ConvIn in_qk, in_v;
@@ -183,8 +244,27 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     const float bv = bf2f(p.b[(static_cast<size_t>(b) * G_NT + s) * G_HV + hv]);
     const float xg = av + p.dt_bias[hv];
     const float sp = xg <= 20.f ? log1pf(expf(xg)) : xg;
-    sm.g[s] = -expf(p.a_log[hv]) * sp;
+    const float g = -expf(p.a_log[hv]) * sp;
+    sm.g[s] = g;
     sm.beta[s] = 1.f / (1.f + expf(-bv));
+    if constexpr (REPLAY)  // this window's gates join the ring (qk_gdn_verify.cu:631)
+      if (wp + s < G_RING) p.g_ring[(static_cast<size_t>(ring) * G_HV + hv) * G_RING + ((cb + wp + s) & (G_RING - 1))] = g;
+  } else if (REPLAY && tid < 128 + G_NT + G_RING) {
+    const int e = tid - 128 - G_NT;  // committed gates in logical order
+    sm.gr[e] = e < wp ? p.g_ring[(static_cast<size_t>(ring) * G_HV + hv) * G_RING + ((cb + e) & (G_RING - 1))] : 0.f;
+  }
+  // REPLAY: warps 1..7 fetch the committed ring keys they will multiply (entries warp - 1, + 7, + 14), four
+  // dimensions per lane
+  uint2 rk[3] = {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)};
+  if constexpr (REPLAY) {
+    if (warp > 0)
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int e = warp - 1 + 7 * i;
+        if (e < wp)
+          rk[i] = *reinterpret_cast<const uint2*>(p.k_ring + ((static_cast<size_t>(ring) * G_HK + hk) * G_RING +
+                                                              ((cb + e) & (G_RING - 1))) * G_D + 4 * lane);
+      }
   }
   // ---- conv + SiLU on q, k (key head hk) and v (value head hv); L2 norms ----
   {
@@ -216,6 +296,16 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
       const int row = (is_k ? 4 : 0) + s;
       sm.QK[sub][row * 32 + sw_chunk(row, chk) + e] = val;
       if (is_k) sm.k[s][c] = val;
+      if constexpr (REPLAY) {
+        // the unit keys join the key ring as bf16 high and low parts (qk_gdn_verify.cu:586-593); entries past the
+        // history, disjoint from the entries read
+        if (is_k && (hv & 1) == 0 && wp + s < G_RING) {
+          const size_t at = ((static_cast<size_t>(ring) * G_HK + hk) * G_RING + ((cb + wp + s) & (G_RING - 1))) * G_D + c;
+          const bf16 hi = f2bf(val);
+          p.k_ring[at] = hi;
+          p.klo_ring[at] = f2bf(val - bf2f(hi));
+        }
+      }
     }
   }
   // the q/k conv state is shared by the two value heads of the key head: both have read it once the
@@ -223,6 +313,18 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   cluster_sync();
   if ((hv & 1) == 0) conv_roll(in_qk, cs_b, ch_qk, n_acc);
   if (!is_k) conv_roll(in_v, cs_b, ch_v, n_acc);
+  uint16_t dr[G_RING];  // REPLAY: this value row's committed d entries (high parts), logical order
+  if constexpr (REPLAY) {
+    bf16* wrec = p.window + static_cast<size_t>(p.win_idx[b]) * G_CONV * 6;
+    if ((hv & 1) == 0) conv_record(in_qk, wrec, ch_qk);
+    if (!is_k) {
+      conv_record(in_v, wrec, ch_v);
+      const unsigned short* dsrc = reinterpret_cast<const unsigned short*>(p.d_ring) +
+                                   (static_cast<size_t>(ring) * G_HV + hv) * G_RING * G_D + c;
+#pragma unroll
+      for (int e = 0; e < G_RING; ++e) dr[e] = e < wp ? dsrc[((cb + e) & (G_RING - 1)) * G_D] : static_cast<uint16_t>(0);
+    }
+  }
   fence_proxy_async();  // the QK tile was written with ordinary stores; the tensor core reads it through the async proxy
   __syncthreads();
 
@@ -257,7 +359,59 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(FULL_MASK, acc, o);
     if (lane == 0) (d < 16 ? sm.kk : sm.kq)[i][j] = acc;
   }
+  if constexpr (REPLAY) {
+    // committed ring keys . [q | k] (rows 0..15 of the reference's key tile, qk_gdn_verify.cu:597-604,662-671)
+    if (warp > 0) {
+      float4 cq[G_NT], ck[G_NT];
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) {
+        cq[s] = *reinterpret_cast<const float4*>(&sm.QK[lane >> 3][s * 32 + sw_chunk(s, lane & 7)]);
+        ck[s] = *reinterpret_cast<const float4*>(&sm.k[s][4 * lane]);
+      }
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int e = warp - 1 + 7 * i;
+        if (e < G_RING) {
+          const float k0 = bf_lo(rk[i].x), k1 = bf_hi(rk[i].x), k2 = bf_lo(rk[i].y), k3 = bf_hi(rk[i].y);
+          float acc[8];
+#pragma unroll
+          for (int s = 0; s < G_NT; ++s) {
+            acc[s] = fmaf(k3, cq[s].w, fmaf(k2, cq[s].z, fmaf(k1, cq[s].y, k0 * cq[s].x)));
+            acc[4 + s] = fmaf(k3, ck[s].w, fmaf(k2, ck[s].z, fmaf(k1, ck[s].y, k0 * ck[s].x)));
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int n = 0; n < 8; ++n) acc[n] += __shfl_xor_sync(FULL_MASK, acc[n], o);
+          if (lane < 8) {
+            float mine = acc[0];
+#pragma unroll
+            for (int n = 1; n < 8; ++n) mine = lane == n ? acc[n] : mine;
+            sm.xr[e][lane] = mine;
+          }
+        }
+      }
+    }
+  }
   __syncthreads();  // kk, kq visible; thread 0 has issued (or abandoned) the MMAs
+  if constexpr (REPLAY) {
+    if (warp == 2) {
+      // decay of every committed entry up to the window: e^{total - pre_c}, and of the checkpoint: e^{total}
+      // (qk_gdn_verify.cu:633-647)
+      const int e = lane & 15;
+      float pre = sm.gr[e];
+#pragma unroll
+      for (int o = 1; o < G_RING; o <<= 1) {
+        const float n = __shfl_up_sync(FULL_MASK, pre, o, G_RING);
+        if (e >= o) pre += n;
+      }
+      const float total = __shfl_sync(FULL_MASK, pre, G_RING - 1, G_RING);
+      if (lane < G_RING) {
+        sm.dec[e] = e < wp ? __expf(total - pre) : 0.f;
+        if (e == 0) sm.tdec = __expf(total);
+      }
+    }
+  }
   if (warp == 1) {
     // the window's scalar coefficients, once per unit instead of once per value row
     float G[G_NT];
@@ -304,9 +458,35 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     uint32_t hr[16];
     tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16), hr);  // warps 0..3 own TMEM lane quadrants 0..3
     tmem_ld_wait();
+    float hq[G_NT], hk_[G_NT];
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) {
+      hq[s] = __uint_as_float(hr[s]);
+      hk_[s] = __uint_as_float(hr[4 + s]);
+    }
+    if constexpr (REPLAY) {
+      // S x = e^{total} H0 x + sum_c (d_c e^{total - pre_c}) (k_c . x)   (qk_gdn_verify.cu:706-742)
+      float aq[G_NT] = {0.f, 0.f, 0.f, 0.f}, ak[G_NT] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int e = 0; e < G_RING; ++e) {
+        const float dsc = __uint_as_float(static_cast<uint32_t>(dr[e]) << 16) * sm.dec[e];
+        const float4 xq = *reinterpret_cast<const float4*>(&sm.xr[e][0]);
+        const float4 xk = *reinterpret_cast<const float4*>(&sm.xr[e][4]);
+        aq[0] = fmaf(dsc, xq.x, aq[0]); aq[1] = fmaf(dsc, xq.y, aq[1]);
+        aq[2] = fmaf(dsc, xq.z, aq[2]); aq[3] = fmaf(dsc, xq.w, aq[3]);
+        ak[0] = fmaf(dsc, xk.x, ak[0]); ak[1] = fmaf(dsc, xk.y, ak[1]);
+        ak[2] = fmaf(dsc, xk.z, ak[2]); ak[3] = fmaf(dsc, xk.w, ak[3]);
+      }
+      const float td = sm.tdec;
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) {
+        hq[s] = fmaf(td, hq[s], aq[s]);
+        hk_[s] = fmaf(td, hk_[s], ak[s]);
+      }
+    }
     float R[G_NT], D[G_NT];
 #pragma unroll
-    for (int s = 0; s < G_NT; ++s) R[s] = sm.cR[s] * (sm.v[s][v] - sm.cE[s] * __uint_as_float(hr[4 + s]));
+    for (int s = 0; s < G_NT; ++s) R[s] = sm.cR[s] * (sm.v[s][v] - sm.cE[s] * hk_[s]);
 #pragma unroll
     for (int i = 0; i < G_NT; ++i) {
       float d = R[i];
@@ -316,10 +496,22 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     }
 #pragma unroll
     for (int s = 0; s < G_NT; ++s) {
-      float acc = sm.cE[s] * __uint_as_float(hr[s]);
+      float acc = sm.cE[s] * hq[s];
 #pragma unroll
       for (int i = 0; i <= s; ++i) acc = fmaf(D[i], sm.cF[i][s], acc);
       o[s] = rbf(acc);  // the core output is stored in bf16 before the norm (qk_gdn_verify.cu:761)
+    }
+    if constexpr (REPLAY) {
+      // the window's D join the ring as bf16 high and low parts (qk_gdn_verify.cu:769-781)
+      const size_t base = (static_cast<size_t>(ring) * G_HV + hv) * G_RING * G_D + v;
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s)
+        if (wp + s < G_RING) {
+          const size_t at = base + static_cast<size_t>((cb + wp + s) & (G_RING - 1)) * G_D;
+          const bf16 hi = f2bf(D[s]);
+          p.d_ring[at] = hi;
+          p.dlo_ring[at] = f2bf(D[s] - bf2f(hi));
+        }
     }
     __syncwarp();
     // c_i D_i for the state update replaces v (each thread only touches its own column)
@@ -351,7 +543,7 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   }
 
   // ---- state after n_acc tokens, in place in the swizzled tile, then four TMA tensor stores ----
-  if (ok && n_acc > 0) {
+  if (!REPLAY && ok && n_acc > 0) {
     // thread = 4 state rows x one 16-byte chunk position of each 32-float sub-tile row
     const int rg = tid >> 3, ks = tid & 7;
     const float decay = sm.cE[n_acc - 1];
@@ -419,9 +611,22 @@ extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, 
   if (reinterpret_cast<uintptr_t>(state) & 15) return fail(B200_E_ALIGN, "b200_gdn_verify: state must be 16-byte aligned");
   if (reinterpret_cast<uintptr_t>(conv_w) & 7) return fail(B200_E_ALIGN, "b200_gdn_verify: conv_w must be 8-byte aligned");
   if (B == 0) return 0;
-  GdnArgs p{static_cast<const bf16*>(mixed), static_cast<const bf16*>(z), static_cast<const bf16*>(a),
-            static_cast<const bf16*>(b), static_cast<bf16*>(conv_state), static_cast<const bf16*>(conv_w), a_log,
-            dt_bias, state, accepted, static_cast<const bf16*>(norm_w), eps, B, static_cast<bf16*>(out), status};
+  GdnArgs p{};
+  p.mixed = static_cast<const bf16*>(mixed);
+  p.z = static_cast<const bf16*>(z);
+  p.a = static_cast<const bf16*>(a);
+  p.b = static_cast<const bf16*>(b);
+  p.conv_state = static_cast<bf16*>(conv_state);
+  p.conv_w = static_cast<const bf16*>(conv_w);
+  p.a_log = a_log;
+  p.dt_bias = dt_bias;
+  p.state = state;
+  p.accepted = accepted;
+  p.norm_w = static_cast<const bf16*>(norm_w);
+  p.eps = eps;
+  p.B = B;
+  p.out = static_cast<bf16*>(out);
+  p.status = status;
   CUtensorMap tmS;
   if (int rc = make_tmap_f32_2d(&tmS, state, static_cast<uint64_t>(B) * G_HV * G_D, G_D, G_D, "gdn state")) return rc;
   const int smem = static_cast<int>(sizeof(GdnSmem)) + 1024;
@@ -429,12 +634,75 @@ extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, 
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaFuncSetAttribute(gdn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(gdn_verify_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     attr_done[dev] = true;
   }
   // three CTAs per SM (shared memory), in clusters of two
   int ncl = (sm_count() * 3) / 2;
   if (ncl > B * G_HK) ncl = B * G_HK;
-  gdn_verify_kernel<<<dim3(2 * ncl), G_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tmS, p);
+  gdn_verify_kernel<false><<<dim3(2 * ncl), G_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tmS, p);
   return launch_status("b200_gdn_verify");
+}
+
+extern "C" int b200_gdn_verify_replay(const void* mixed, const void* z, const void* a, const void* b, void* conv_state,
+                                      const void* conv_w, void* window, const float* a_log, const float* dt_bias,
+                                      const float* checkpoint, int state_slots, void* d_ring, void* dlo_ring,
+                                      void* k_ring, void* klo_ring, float* g_ring, const int32_t* state_idx,
+                                      const int32_t* ring_idx, const int32_t* win_idx, const int32_t* write_pos,
+                                      const int32_t* cache_base, const void* norm_w, float eps, int B, void* out,
+                                      int32_t* status, void* stream) {
+  if (!mixed || !z || !a || !b || !conv_state || !conv_w || !window || !a_log || !dt_bias || !checkpoint || !d_ring ||
+      !dlo_ring || !k_ring || !klo_ring || !g_ring || !state_idx || !ring_idx || !win_idx || !write_pos || !cache_base ||
+      !norm_w || !out)
+    return fail(B200_E_ARG, "b200_gdn_verify_replay: null pointer");
+  if (B < 0 || B > 65535 || state_slots <= 0 || state_slots > 131071)
+    return fail(B200_E_ARG, "b200_gdn_verify_replay: B=%d or state_slots=%d out of range", B, state_slots);
+  if (reinterpret_cast<uintptr_t>(checkpoint) & 15)
+    return fail(B200_E_ALIGN, "b200_gdn_verify_replay: checkpoint must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(conv_w) & 7) || (reinterpret_cast<uintptr_t>(k_ring) & 7) ||
+      (reinterpret_cast<uintptr_t>(window) & 3))
+    return fail(B200_E_ALIGN, "b200_gdn_verify_replay: conv_w and k_ring must be 8-byte, window 4-byte aligned");
+  if (B == 0) return 0;
+  GdnArgs p{};
+  p.mixed = static_cast<const bf16*>(mixed);
+  p.z = static_cast<const bf16*>(z);
+  p.a = static_cast<const bf16*>(a);
+  p.b = static_cast<const bf16*>(b);
+  p.conv_state = static_cast<bf16*>(conv_state);
+  p.conv_w = static_cast<const bf16*>(conv_w);
+  p.a_log = a_log;
+  p.dt_bias = dt_bias;
+  p.state = const_cast<float*>(checkpoint);  // only read in this form
+  p.norm_w = static_cast<const bf16*>(norm_w);
+  p.eps = eps;
+  p.B = B;
+  p.out = static_cast<bf16*>(out);
+  p.status = status;
+  p.window = static_cast<bf16*>(window);
+  p.d_ring = static_cast<bf16*>(d_ring);
+  p.dlo_ring = static_cast<bf16*>(dlo_ring);
+  p.k_ring = static_cast<bf16*>(k_ring);
+  p.klo_ring = static_cast<bf16*>(klo_ring);
+  p.g_ring = g_ring;
+  p.state_idx = state_idx;
+  p.ring_idx = ring_idx;
+  p.win_idx = win_idx;
+  p.write_pos = write_pos;
+  p.cache_base = cache_base;
+  CUtensorMap tmS;
+  if (int rc = make_tmap_f32_2d(&tmS, const_cast<float*>(checkpoint), static_cast<uint64_t>(state_slots) * G_HV * G_D, G_D,
+                                G_D, "gdn checkpoint"))
+    return rc;
+  const int smem = static_cast<int>(sizeof(GdnSmem)) + 1024;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaFuncSetAttribute(gdn_verify_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    attr_done[dev] = true;
+  }
+  int ncl = (sm_count() * 3) / 2;
+  if (ncl > B * G_HK) ncl = B * G_HK;
+  gdn_verify_kernel<true><<<dim3(2 * ncl), G_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tmS, p);
+  return launch_status("b200_gdn_verify_replay");
 }

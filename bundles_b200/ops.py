@@ -398,3 +398,39 @@ def gdn_verify(mixed, z, a, b, conv_state, conv_w, a_log, dt_bias, state, accept
                                      _p(dt_bias), _p(state), _p(accepted), _p(norm_w), float(eps), B, _p(out),
                                      _p(status), _stream()), "b200_gdn_verify")
     return out
+
+
+def gdn_verify_replay(mixed, z, a, b, conv_state, conv_w, window, a_log, dt_bias, checkpoint, d_ring, dlo_ring, k_ring,
+                      klo_ring, g_ring, state_idx, ring_idx, win_idx, write_pos, cache_base, norm_w, eps=1e-6,
+                      out=None, status=None):
+    """Gated DeltaNet verify on the checkpoint + (d, k, g) ring state layout (reference:
+    qk_gdn_verify.gdn_verify_fused, gdn_fused.py:37-57): reads the checkpoint and the committed ring
+    entries, appends this window's entries, rolls `conv_state` and records the draft windows in place.
+    Returns out bf16 [B*4, 4096]."""
+    _need(mixed, torch.bfloat16, "mixed", 2)
+    _need(checkpoint, torch.float32, "checkpoint", 4)
+    _need(conv_state, torch.bfloat16, "conv_state", 3)
+    _need(window, torch.bfloat16, "window", 3)
+    for name, t in (("d_ring", d_ring), ("dlo_ring", dlo_ring), ("k_ring", k_ring), ("klo_ring", klo_ring)):
+        _need(t, torch.bfloat16, name, 4)
+    _need(g_ring, torch.float32, "g_ring", 3)
+    for name, t in (("state_idx", state_idx), ("ring_idx", ring_idx), ("win_idx", win_idx), ("write_pos", write_pos),
+                    ("cache_base", cache_base)):
+        _need(t, torch.int32, name, 1)
+    B = state_idx.shape[0]
+    slots, rslots = checkpoint.shape[0], g_ring.shape[0]
+    if tuple(mixed.shape) != (B * 4, 8192) or tuple(checkpoint.shape) != (slots, 32, 128, 128) or \
+            tuple(conv_state.shape) != (slots, 8192, 3) or tuple(window.shape[1:]) != (8192, 6) or \
+            tuple(d_ring.shape) != (rslots, 32, 16, 128) or tuple(dlo_ring.shape) != (rslots, 32, 16, 128) or \
+            tuple(k_ring.shape) != (rslots, 16, 16, 128) or tuple(klo_ring.shape) != (rslots, 16, 16, 128) or \
+            tuple(g_ring.shape) != (rslots, 32, 16) or ring_idx.shape[0] != B or win_idx.shape[0] != B or \
+            write_pos.shape[0] != rslots or cache_base.shape[0] != rslots:
+        raise B200Error("gdn_verify_replay: unexpected shapes")
+    if out is None:
+        out = torch.empty(B * 4, 4096, dtype=torch.bfloat16, device=mixed.device)
+    check(_lib.lib().b200_gdn_verify_replay(
+        _p(mixed), _p(z), _p(a), _p(b), _p(conv_state), _p(conv_w), _p(window), _p(a_log), _p(dt_bias), _p(checkpoint),
+        slots, _p(d_ring), _p(dlo_ring), _p(k_ring), _p(klo_ring), _p(g_ring), _p(state_idx), _p(ring_idx), _p(win_idx),
+        _p(write_pos), _p(cache_base), _p(norm_w), float(eps), B, _p(out), _p(status), _stream()),
+        "b200_gdn_verify_replay")
+    return out

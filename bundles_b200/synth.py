@@ -125,6 +125,33 @@ def gdn(seed=SEEDS["gdn"], B=32):
     )
 
 
+def gdn_replay(seed=SEEDS["gdn"] + 1, B=32, extra_slots=3):
+    """Config: the same verify step on the checkpoint + 16-entry (d, k, g) ring layout: `B + extra_slots`
+    pool slots in shuffled order, write positions 0..16 (16: the ring is full, nothing is appended), random
+    ring bases, gates of the committed entries drawn like the step's own (negative)."""
+    g = _gen(seed)
+    bf = torch.bfloat16
+    c = gdn(seed, B)
+    n = B + extra_slots
+    out = {k: c[k] for k in ("mixed", "z", "a", "b", "conv_w", "a_log", "dt_bias", "norm_w")}
+    out.update(
+        conv_state=torch.randn(n, 8192, 3, generator=g).to(bf),
+        window=torch.zeros(n, 8192, 6, dtype=bf),
+        checkpoint=torch.randn(n, 32, 128, 128, generator=g) * 0.1,
+        d_ring=(torch.randn(n, 32, 16, 128, generator=g) * 0.3).to(bf),
+        dlo_ring=torch.zeros(n, 32, 16, 128, dtype=bf),
+        k_ring=torch.nn.functional.normalize(torch.randn(n, 16, 16, 128, generator=g), dim=-1).to(bf),
+        klo_ring=torch.zeros(n, 16, 16, 128, dtype=bf),
+        g_ring=-torch.rand(n, 32, 16, generator=g) * 0.5,
+        state_idx=torch.randperm(n, generator=g)[:B].to(torch.int32),
+        ring_idx=torch.randperm(n, generator=g)[:B].to(torch.int32),
+        win_idx=torch.randperm(n, generator=g)[:B].to(torch.int32),
+        write_pos=torch.randint(0, 17, (n,), generator=g, dtype=torch.int32),
+        cache_base=torch.randint(0, 16, (n,), generator=g, dtype=torch.int32),
+    )
+    return out
+
+
 def attn(seed=SEEDS["attn"], T=4096, H=2048):
     """Config: fused gated-attention projections; W [9216, 2048] fp8 block-scaled."""
     g = _gen(seed)

@@ -231,6 +231,29 @@ int b200_gdn_verify(const void* mixed, const void* z, const void* a, const void*
                     const int32_t* accepted, const void* norm_w, float eps, int B, void* out, int32_t* status,
                     void* stream);
 
+/* The same step on the state layout the reference's engine keeps (ReplaySSM, gdn_fused.py:19-57,
+ * qk_gdn_verify.cu:61-73,586-593,631-647,706-717,769-781,883-898): a read-only fp32 checkpoint per slot
+ * plus a 16-entry circular ring of (d, k, g) per request.  Logical entry c < write_pos[r] lives at
+ * physical entry (cache_base[r] + c) & 15; the state the window sees is
+ *   e^{total} H0 + sum_c e^{total - pre_c} d_c k_c^T   (pre_c = g_0 + .. + g_c, total = pre_{write_pos-1})
+ * read from the high parts of the d and k rings.  The window's D_s, unit keys k_s (bf16 high part, and
+ * low part = bf16(value - high)) and gates g_s (fp32) are appended at logical entries write_pos + s for
+ * those below 16; the checkpoint is never written; the cursors are the caller's (rollback = the caller
+ * does not advance write_pos).  conv_state is rolled by the whole window ([x1 x2 x3]) and the per-draft
+ * windows are recorded per channel as [s1 s2 x0 x1 x2 x3] in window[win_idx[b]].
+ *   checkpoint fp32 [state_slots, 32, 128, 128]; conv_state bf16 [state_slots, 8192, 3], both indexed
+ *   by state_idx[b] (< 0: padded request, its output rows are zero and nothing else is touched);
+ *   window bf16 [window slots, 8192, 6]; d_ring, dlo_ring bf16 [ring slots, 32, 16, 128];
+ *   k_ring, klo_ring bf16 [ring slots, 16, 16, 128]; g_ring fp32 [ring slots, 32, 16];
+ *   state_idx, ring_idx, win_idx int32 [B]; write_pos, cache_base int32 [ring slots];
+ *   the other arguments as above.  Requests of one call must not share a slot. */
+int b200_gdn_verify_replay(const void* mixed, const void* z, const void* a, const void* b, void* conv_state,
+                           const void* conv_w, void* window, const float* a_log, const float* dt_bias,
+                           const float* checkpoint, int state_slots, void* d_ring, void* dlo_ring, void* k_ring,
+                           void* klo_ring, float* g_ring, const int32_t* state_idx, const int32_t* ring_idx,
+                           const int32_t* win_idx, const int32_t* write_pos, const int32_t* cache_base,
+                           const void* norm_w, float eps, int B, void* out, int32_t* status, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Attention verify core.  Replaces qk_attn_verify.attn_verify_fused (attn_fused.py:110-124;
  * attn_verify_kernel, qk_attn_verify.cu:354-744) behind the projection front above: per request

@@ -109,3 +109,107 @@ def gdn_verify(mixed, z, a, b, conv_state, conv_w, a_log, dt_bias, state, accept
         n = int(acc[bi])
         new_conv[bi] = win[bi, :, n:n + 3]
     return out.reshape(B * NT, HV * DV), new_state, new_conv
+
+
+RING = 16
+
+
+def ring_state(checkpoint, d_ring, k_ring, g_ring, write_pos, cache_base):
+    """The state a checkpoint plus the committed ring entries stand for, in float64:
+        S = e^{total} H0 + sum_{c < wp} e^{total - pre_c} d_c k_c^T,  pre_c = g_0 + .. + g_c, total = pre_{wp-1}
+    with logical entry c at physical entry (cache_base + c) & 15 (qk_gdn_verify.cu:597-604,633-647,706-717).
+    checkpoint [32, 128, 128]; d_ring [32, 16, 128]; k_ring [16, 16, 128]; g_ring [32, 16] (one request)."""
+    wp = int(min(max(write_pos, 0), RING))
+    S = np.asarray(checkpoint, dtype=np.float64).copy()
+    phys = [(int(cache_base) + c) & (RING - 1) for c in range(wp)]
+    for hv in range(HV):
+        g = np.asarray(g_ring[hv], dtype=np.float64)[phys] if wp else np.zeros(0)
+        pre = np.cumsum(g)
+        total = pre[-1] if wp else 0.0
+        S[hv] *= np.exp(total)
+        for c in range(wp):
+            d = np.asarray(d_ring[hv, phys[c]], dtype=np.float64)
+            k = np.asarray(k_ring[hv // 2, phys[c]], dtype=np.float64)
+            S[hv] += np.exp(total - pre[c]) * d[:, None] * k[None, :]
+    return S
+
+
+def gdn_verify_replay(mixed, z, a, b, conv_state, conv_w, a_log, dt_bias, checkpoint, d_ring, k_ring, g_ring,
+                      state_idx, ring_idx, write_pos, cache_base, norm_w, eps=1e-6):
+    """The verify step on the checkpoint + (d, k, g) ring layout (qk_gdn_verify.cu:293-793, gdn_fused.py:37-57).
+
+    checkpoint fp32 [slots, 32, 128, 128] and conv_state [slots, 8192, 3] are indexed by state_idx[b]
+    (< 0: padded request, zero output); d_ring [rslots, 32, 16, 128], k_ring [rslots, 16, 16, 128] (bf16 high
+    parts, the only parts the kernel reads: qk_gdn_verify.cu:63-64), g_ring fp32 [rslots, 32, 16],
+    write_pos / cache_base int [rslots], indexed by ring_idx[b].
+
+    The window runs on the state `ring_state` reconstructs; the recurrence, rounding points and the gated
+    norm are those of `gdn_verify`.  The per-token deltas d_s of the sequential recurrence are the D_s of the
+    reference's closed form (S_n = e^{G_{n-1}} S + sum_{i<n} e^{G_{n-1} - G_i} D_i k_i^T,
+    qk_gdn_verify.cu:686-752), so the appended entries are (d_s, unit key k_s, g_s).
+
+    Returns a dict: out [B*4, 4096] bf16 values; per request the appended entries
+    d_hi, d_lo [B, 4, 32, 128], k_hi, k_lo [B, 4, 16, 128] (bf16 values; low = bf16(value - high),
+    qk_gdn_verify.cu:588-593,776-778), g [B, 4, 32] fp32; `slots` [B, 4] the physical entry of draft s or -1
+    when write_pos + s >= 16 (qk_gdn_verify.cu:586,631,774); new_conv [B, 8192, 3] = [x1 x2 x3] and
+    window [B, 8192, 6] = [s1 s2 x0 x1 x2 x3] (Conv4::store, qk_gdn_verify.cu:277-289)."""
+    B = len(state_idx)
+    mixed = np.asarray(mixed, dtype=F32).reshape(B, NT, CONV)
+    z = np.asarray(z, dtype=F32).reshape(B, NT, HV, DV)
+    a = np.asarray(a, dtype=F32).reshape(B, NT, HV)
+    b = np.asarray(b, dtype=F32).reshape(B, NT, HV)
+    sidx = np.asarray(state_idx).astype(np.int64)
+    ridx = np.asarray(ring_idx).astype(np.int64)
+    live = sidx >= 0
+    cs = np.zeros((B, CONV, 3), dtype=F32)
+    cs[live] = np.asarray(conv_state, dtype=F32)[sidx[live]]
+    y, win = causal_conv(mixed, cs, conv_w)
+    q = y[:, :, :QDIM].reshape(B, NT, HK, DK)
+    k = y[:, :, QDIM:2 * QDIM].reshape(B, NT, HK, DK)
+    v = y[:, :, 2 * QDIM:].reshape(B, NT, HV, DV).astype(np.float64)
+    qn = (q / np.sqrt(np.sum(q * q, axis=-1, keepdims=True, dtype=F32) + F32(1e-6))).astype(F32)
+    qn = (qn * F32(DK ** -0.5)).astype(np.float64)
+    kn32 = (k / np.sqrt(np.sum(k * k, axis=-1, keepdims=True, dtype=F32) + F32(1e-6))).astype(F32)
+    kn = kn32.astype(np.float64)
+    xg = (a + np.asarray(dt_bias, dtype=F32)[None, None, :]).astype(np.float64)
+    sp = np.where(xg <= 20.0, np.log1p(np.exp(np.minimum(xg, 20.0))), xg)
+    g = -np.exp(np.asarray(a_log, dtype=np.float64))[None, None, :] * sp
+    beta = 1.0 / (1.0 + np.exp(-b.astype(np.float64)))
+
+    S = np.zeros((B, HV, DV, DK), dtype=np.float64)
+    slots = -np.ones((B, NT), dtype=np.int64)
+    for bi in range(B):
+        if not live[bi]:
+            continue
+        r = ridx[bi]
+        S[bi] = ring_state(checkpoint[sidx[bi]], d_ring[r], k_ring[r], g_ring[r], write_pos[r], cache_base[r])
+        wp = int(min(max(write_pos[r], 0), RING))
+        for s in range(NT):
+            if wp + s < RING:
+                slots[bi, s] = (int(cache_base[r]) + wp + s) & (RING - 1)
+    o = np.empty((B, NT, HV, DV), dtype=np.float64)
+    dd = np.empty((B, NT, HV, DV), dtype=np.float64)
+    hk_of = np.arange(HV) // 2
+    for s in range(NT):
+        ks = kn[:, s, hk_of]
+        qs = qn[:, s, hk_of]
+        S = S * np.exp(g[:, s])[:, :, None, None]
+        d = beta[:, s][:, :, None] * (v[:, s] - np.einsum("bhvk,bhk->bhv", S, ks))
+        S = S + d[:, :, :, None] * ks[:, :, None, :]
+        o[:, s] = np.einsum("bhvk,bhk->bhv", S, qs)
+        dd[:, s] = d
+    ob = bf16_round(o.astype(F32))
+    var = np.mean(ob * ob, axis=-1, keepdims=True, dtype=F32)
+    rstd = (F32(1.0) / np.sqrt(var + F32(eps))).astype(F32)
+    with np.errstate(over="ignore"):
+        gate = (z * (F32(1.0) / (F32(1.0) + np.exp(-z, dtype=F32)))).astype(F32)
+    out = bf16_round((ob * rstd * np.asarray(norm_w, dtype=F32)[None, None, None, :] * gate).astype(F32))
+    out[~live] = 0
+    d32 = dd.astype(F32)
+    d_hi = bf16_round(d32)
+    d_lo = bf16_round((d32 - d_hi).astype(F32))
+    k_hi = bf16_round(kn32)
+    k_lo = bf16_round((kn32 - k_hi).astype(F32))
+    return dict(out=out.reshape(B * NT, HV * DV), d_hi=d_hi, d_lo=d_lo, k_hi=k_hi, k_lo=k_lo, g=g.astype(F32),
+                slots=slots, new_conv=win[:, :, 4:7].copy(), window=win[:, :, 1:7].copy(), live=live,
+                state_after=S)
