@@ -287,6 +287,31 @@ def _gdn_entry(dev, ops, synth, timed, st, it, out, hbm, which):
                          "algorithmic_bytes": gbytes, "achieved_gbs": gbytes / ms / 1e6, "bound": "hbm",
                          "frac": gbytes / ms / 1e6 / hbm, "peak_source": which, "status": ops.read_status(st)}
     del states, convs, g
+    # the same step on the checkpoint + ring layout: a 128-slot pool (268 MB of checkpoints), four disjoint sets of
+    # 32 slots taken in turn so that every launch reads its checkpoints from HBM; nothing is written back but the
+    # ring entries, the conv state and the window record
+    import torch
+    r = {k: v.to(dev) for k, v in synth.gdn_replay(B=32, extra_slots=96).items()}
+    perm = torch.randperm(128, device=dev).to(torch.int32)
+    sets = [perm[32 * i:32 * i + 32].contiguous() for i in range(4)]
+
+    def replay_step():
+        i = it[0] % 4
+        it[0] += 1
+        ops.gdn_verify_replay(r["mixed"], r["z"], r["a"], r["b"], r["conv_state"], r["conv_w"], r["window"], r["a_log"],
+                              r["dt_bias"], r["checkpoint"], r["d_ring"], r["dlo_ring"], r["k_ring"], r["klo_ring"],
+                              r["g_ring"], sets[i], sets[i], sets[i], r["write_pos"], r["cache_base"], r["norm_w"], 1e-6,
+                              status=st)
+
+    ms = timed(replay_step, calls=4)
+    wp = r["write_pos"].clamp(0, 16).float().mean().item()
+    rbytes = int(B * 32 * 65536 + B * wp * (32 + 16) * 256 + B * 4 * (8192 + 4096 + 64) * 2 + B * 8192 * (3 + 3 + 6) * 2 +
+                 B * 4 * 4096 * 2 + B * 4 * (32 + 16) * 256 * 2)
+    out["gdn_verify_replay"] = {"config": "B=32 x 4 drafts on a read-only fp32 checkpoint + 16-entry (d, k, g) ring, "
+                                          "write positions ~U{0..16}", "ms": ms, "algorithmic_bytes": rbytes,
+                                "achieved_gbs": rbytes / ms / 1e6, "bound": "hbm", "frac": rbytes / ms / 1e6 / hbm,
+                                "peak_source": which, "status": ops.read_status(st)}
+    del r
 
 
 def _attn_verify_entry(dev, ops, synth, timed, st, out, hbm, which, name, Bv):

@@ -68,6 +68,12 @@ def test_argument_checks_return_codes(lib):
     assert lib.b200_attn_verify_splits(0) == 0
     assert lib.b200_moe_combine_norm(None, None, None, None, 1, 2048, 10, None, None, None, 1e-6, None, None) == -1
     assert lib.b200_moe_combine_norm(one, one, None, None, 1, 2047, 10, None, one, one, 1e-6, one, None) == -1
+    # GDN verify on the ring layout: null pointers, slot count out of range, misaligned checkpoint
+    assert lib.b200_gdn_verify_replay(*([None] * 10), 4, *([None] * 11), 1e-6, 1, None, None, None) == -1
+    ok = [one] * 10
+    assert lib.b200_gdn_verify_replay(*ok, 0, *([one] * 11), 1e-6, 1, one, None, None) == -1
+    mis = [one] * 9 + [C.c_void_p(4100)]
+    assert lib.b200_gdn_verify_replay(*mis, 4, *([one] * 11), 1e-6, 1, one, None, None) == -2
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

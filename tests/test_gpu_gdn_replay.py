@@ -51,9 +51,16 @@ def _check(cfg):
                 continue
             dsum = after["d_ring"][rs, :, ph] + after["dlo_ring"][rs, :, ph]
             dref = r["d_hi"][i, s] + r["d_lo"][i, s]
-            assert np.abs(dsum - dref).max() < 1e-3 * max(1.0, np.abs(dref).max()), "appended d"
+            # 1e-3 of the largest entry; a rare bf16 rounding flip of a conv output (fast exp in the SiLU) moves
+            # single entries by up to one bf16 step of v
+            derr, scale = np.abs(dsum - dref), max(1.0, np.abs(dref).max())
+            assert derr.max() < 2.0 ** -6 * scale and (derr > 1e-3 * scale).mean() < 1e-3, "appended d"
             ksum = after["k_ring"][rs, :, ph] + after["klo_ring"][rs, :, ph]
-            assert np.abs(ksum - (r["k_hi"][i, s] + r["k_lo"][i, s])).max() < 1e-4, "appended k"
+            kref = r["k_hi"][i, s] + r["k_lo"][i, s]
+            kerr = np.abs(ksum - kref)
+            # the conv output is a bf16 value: a rare rounding flip of it (fast exp in the SiLU) moves one key
+            # element by one bf16 step; everything else agrees to the precision of the two parts
+            assert (kerr < 2.0 ** -7 * np.abs(kref) + 1e-4).all() and (kerr > 1e-4).mean() < 1e-3, "appended k"
             assert np.abs(after["g_ring"][rs, :, ph] - r["g"][i, s]).max() < 1e-4 * max(1.0, np.abs(r["g"][i, s]).max())
             # low part = bf16(value - high): the two parts carry 16 mantissa bits of the fp32 value
             assert np.abs(after["dlo_ring"][rs, :, ph]).max() <= np.abs(after["d_ring"][rs, :, ph]).max() * 2.0 ** -7
@@ -120,6 +127,7 @@ def test_two_windows_chain_through_the_ring():
     # [1, 4) of the window record [s1 s2 x0 x1 x2 x3]
     d["write_pos"] += 2
     d["conv_state"] = d["window"][:, :, 1:4].contiguous()
+    restored = d["conv_state"].clone()
     nxt = synth.gdn(seed=93, B=2)
     for k in ("mixed", "z", "a", "b"):
         d[k] = nxt[k].to(dev())
@@ -130,7 +138,7 @@ def test_two_windows_chain_through_the_ring():
     acc2 = torch.full((2,), 2, dtype=torch.int32, device=dev())
     ops.gdn_verify(cfg["mixed"].to(dev()), cfg["z"].to(dev()), cfg["a"].to(dev()), cfg["b"].to(dev()), e_conv,
                    d["conv_w"], d["a_log"], d["dt_bias"], e_state, acc2, d["norm_w"], 1e-6, status=st)
-    assert torch.equal(e_conv, d["conv_state"]), "conv state restored from the window record"
+    assert torch.equal(e_conv, restored), "conv state restored from the window record"
     ref2 = ops.gdn_verify(d["mixed"], d["z"], d["a"], d["b"], e_conv, d["conv_w"], d["a_log"], d["dt_bias"], e_state,
                           acc2, d["norm_w"], 1e-6, status=st)
     torch.cuda.synchronize()
