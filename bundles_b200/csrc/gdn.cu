@@ -158,6 +158,18 @@ struct GdnArgs {
   const int32_t* cache_base;  // [ring slots] physical entry of logical entry 0
 };
 
+// Optional timeline of CTA 0 (compile with -DB200_TRACE): %globaltimer stamps of thread 0 per unit at: 0 unit start,
+// 1 inputs consumed (conv done), 2 operand tile built and conv state rolled, 3 MMAs issued, 4 window dots done,
+// 5 coefficients done, 6 MMAs complete, 7 outputs reduced, 8 unit end; row 9: kernel start and end.
+#ifdef B200_TRACE
+__device__ unsigned long long g_gdn_trace[16][8];
+#define G_TRACE(k, i) do { if (blockIdx.x == 0 && threadIdx.x == 0 && (i) < 8) g_gdn_trace[k][i] = globaltimer(); } while (0)
+#define G_TRACE_W(k, i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (i) < 8) g_gdn_trace[k][i] = globaltimer(); } while (0)
+#else
+#define G_TRACE(k, i) do { } while (0)
+#define G_TRACE_W(k, i) do { } while (0)
+#endif
+
 template <bool REPLAY>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 3)
 gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
@@ -182,14 +194,46 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_slot;
+  G_TRACE(9, 0);
+  int unit_no = 0;
   bool ok = true;
   uint32_t par = 0;  // parity of this unit's phase of both mbarriers
+  // REPLAY: the slot indices and ring cursors of a unit are fetched one unit ahead, so that no unit starts with a
+  // chain of dependent global loads, and its checkpoint tile is requested as soon as the previous unit's MMAs
+  // have left the (never written) tile buffer
+  int nx_slot = 0, nx_ring = 0, nx_win = 0, nx_wp = 0, nx_cb = 0;
+  bool tile_requested = false;  // thread 0: this unit's tile was requested during the previous unit
+  if constexpr (REPLAY) {
+    const int first = blockIdx.x >> 1;
+    if (first < npairs) {
+      const int b0 = first / G_HK;
+      nx_slot = p.state_idx[b0];
+      nx_ring = p.ring_idx[b0];
+      nx_win = p.win_idx[b0];
+      nx_wp = p.write_pos[nx_ring];
+      nx_cb = p.cache_base[nx_ring];
+    }
+  }
   for (int pair = blockIdx.x >> 1; pair < npairs; pair += ncl, par ^= 1u) {
   const int b = pair / G_HK, hk = pair - b * G_HK, hv = 2 * hk + rank;
-  int slot = b;
+  int slot = b, ring = 0, wp = 0, cb = 0, wslot = 0;
+  const int nb = pair + ncl < npairs ? (pair + ncl) / G_HK : -1;  // the next unit's request
   if constexpr (REPLAY) {
-    slot = p.state_idx[b];
+    slot = nx_slot;
+    ring = nx_ring;
+    wslot = nx_win;
+    cb = nx_cb;
+    wp = nx_wp < 0 ? 0 : (nx_wp > G_RING ? G_RING : nx_wp);
+    if (nb >= 0) {
+      nx_slot = p.state_idx[nb];
+      nx_ring = p.ring_idx[nb];
+      nx_win = p.win_idx[nb];
+    }
     if (slot < 0) {  // a padded request: zero output, nothing read or written; no barrier phase is used
+      if (nb >= 0) {
+        nx_wp = p.write_pos[nx_ring];
+        nx_cb = p.cache_base[nx_ring];
+      }
       if (ok && tid < G_D)
 #pragma unroll
         for (int s = 0; s < G_NT; ++s)
@@ -202,13 +246,14 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     cluster_sync();
     continue;
   }
+  G_TRACE(0, unit_no);
   int n_acc = G_NT;  // REPLAY: the conv state is rolled by the whole window
   if constexpr (!REPLAY) {
     n_acc = p.accepted[b];
     n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
   }
   const int srow0 = (slot * G_HV + hv) * G_D;  // first row of this unit in the [slots*32*128, 128] view of the state
-  if (tid == 0) {
+  if (tid == 0 && !tile_requested) {
     bulk_wait_read_all();  // the previous unit's tile has left shared memory
     mbar_expect_tx(&sm.bar_load, G_TILE_BYTES);
 #pragma unroll
@@ -220,13 +265,6 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   bf16* cs_b = p.conv_state + static_cast<size_t>(slot) * G_CONV * 3;
   const int c = tid & 127;
   const bool is_k = tid >= 128;
-  int ring = 0, wp = 0, cb = 0;
-  if constexpr (REPLAY) {
-    ring = p.ring_idx[b];
-    wp = p.write_pos[ring];
-    cb = p.cache_base[ring];
-    wp = wp < 0 ? 0 : (wp > G_RING ? G_RING : wp);
-  }
   const int ch_qk = (is_k ? G_QDIM : 0) + hk * G_D + c;
   const int ch_v = 2 * G_QDIM + hv * G_D + c;
   ConvIn in_qk, in_v;
@@ -256,7 +294,14 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   // REPLAY: warps 1..7 fetch the committed ring keys they will multiply (entries warp - 1, + 7, + 14), four
   // dimensions per lane
   uint2 rk[3] = {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)};
+  // REPLAY: the value head's committed d entries (high parts), one 16-byte chunk per thread: physical entry
+  // tid / 16, value rows 8 (tid % 16) ..; entries past the history read as zero whatever the ring holds there
+  uint4 dchunk = make_uint4(0u, 0u, 0u, 0u);
+  const int d_entry = ((tid >> 4) - cb) & (G_RING - 1);  // logical entry of this thread's chunk
   if constexpr (REPLAY) {
+    if (d_entry < wp)
+      dchunk = *reinterpret_cast<const uint4*>(p.d_ring + ((static_cast<size_t>(ring) * G_HV + hv) * G_RING + (tid >> 4)) * G_D +
+                                               (tid & 15) * 8);
     if (warp > 0)
 #pragma unroll
       for (int i = 0; i < 3; ++i) {
@@ -287,6 +332,7 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
       for (int s = 0; s < G_NT; ++s) sm.v[s][c] = yv[s];
     }
     __syncthreads();
+    G_TRACE(1, unit_no);
     const int sub = c >> 5, chk = (c & 31) >> 2, e = c & 3;
 #pragma unroll
     for (int s = 0; s < G_NT; ++s) {
@@ -313,20 +359,18 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   cluster_sync();
   if ((hv & 1) == 0) conv_roll(in_qk, cs_b, ch_qk, n_acc);
   if (!is_k) conv_roll(in_v, cs_b, ch_v, n_acc);
-  uint16_t dr[G_RING];  // REPLAY: this value row's committed d entries (high parts), logical order
   if constexpr (REPLAY) {
-    bf16* wrec = p.window + static_cast<size_t>(p.win_idx[b]) * G_CONV * 6;
-    if ((hv & 1) == 0) conv_record(in_qk, wrec, ch_qk);
-    if (!is_k) {
-      conv_record(in_v, wrec, ch_v);
-      const unsigned short* dsrc = reinterpret_cast<const unsigned short*>(p.d_ring) +
-                                   (static_cast<size_t>(ring) * G_HV + hv) * G_RING * G_D + c;
-#pragma unroll
-      for (int e = 0; e < G_RING; ++e) dr[e] = e < wp ? dsrc[((cb + e) & (G_RING - 1)) * G_D] : static_cast<uint16_t>(0);
+    if (nb >= 0) {  // the next unit's cursors: its ring slot has landed by now
+      nx_wp = p.write_pos[nx_ring];
+      nx_cb = p.cache_base[nx_ring];
     }
+    bf16* wrec = p.window + static_cast<size_t>(wslot) * G_CONV * 6;
+    if ((hv & 1) == 0) conv_record(in_qk, wrec, ch_qk);
+    if (!is_k) conv_record(in_v, wrec, ch_v);
   }
   fence_proxy_async();  // the QK tile was written with ordinary stores; the tensor core reads it through the async proxy
   __syncthreads();
+  G_TRACE(2, unit_no);
 
   // ---- S [q | k]: sixteen tf32 MMAs (M = 128 state rows, N = 16, K = 8 each) into 16 TMEM columns ----
   bool landed = true;
@@ -343,6 +387,7 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
                       umma_desc_sw128(smem_u32(sm.QK[sub]) + kk * 32), idesc, (sub | kk) != 0);
       tc_commit(&sm.bar_mma);
     }
+    G_TRACE(3, unit_no);
   }
   // k_i . k_j and k_i . q_j while the MMAs run: 32 dots of length 128 over warps 1..7 (warp 0 issues the MMAs;
   // q is read back from the QK tile)
@@ -371,7 +416,7 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
 #pragma unroll
       for (int i = 0; i < 3; ++i) {
         const int e = warp - 1 + 7 * i;
-        if (e < G_RING) {
+        if (e < wp) {  // entries past the history are never read
           const float k0 = bf_lo(rk[i].x), k1 = bf_hi(rk[i].x), k2 = bf_lo(rk[i].y), k3 = bf_hi(rk[i].y);
           float acc[8];
 #pragma unroll
@@ -379,21 +424,40 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
             acc[s] = fmaf(k3, cq[s].w, fmaf(k2, cq[s].z, fmaf(k1, cq[s].y, k0 * cq[s].x)));
             acc[4 + s] = fmaf(k3, ck[s].w, fmaf(k2, ck[s].z, fmaf(k1, ck[s].y, k0 * ck[s].x)));
           }
+          // sum over the lanes with a transposing butterfly: each step halves the columns a lane carries (the upper
+          // half of the lanes keeps the upper columns), 4 + 2 + 1 shuffles, then two plain steps: lane l ends with
+          // the total of column (l >> 4 & 1) * 4 + (l >> 3 & 1) * 2 + (l >> 2 & 1)
+          float a4[4], a2[2], a1;
+          {
+            const bool up = lane & 16;
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-            for (int n = 0; n < 8; ++n) acc[n] += __shfl_xor_sync(FULL_MASK, acc[n], o);
-          if (lane < 8) {
-            float mine = acc[0];
-#pragma unroll
-            for (int n = 1; n < 8; ++n) mine = lane == n ? acc[n] : mine;
-            sm.xr[e][lane] = mine;
+            for (int n = 0; n < 4; ++n) {
+              const float give = up ? acc[n] : acc[4 + n], keep = up ? acc[4 + n] : acc[n];
+              a4[n] = keep + __shfl_xor_sync(FULL_MASK, give, 16);
+            }
           }
+          {
+            const bool up = lane & 8;
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+              const float give = up ? a4[n] : a4[2 + n], keep = up ? a4[2 + n] : a4[n];
+              a2[n] = keep + __shfl_xor_sync(FULL_MASK, give, 8);
+            }
+          }
+          {
+            const bool up = lane & 4;
+            const float give = up ? a2[0] : a2[1], keep = up ? a2[1] : a2[0];
+            a1 = keep + __shfl_xor_sync(FULL_MASK, give, 4);
+          }
+          a1 += __shfl_xor_sync(FULL_MASK, a1, 2);
+          a1 += __shfl_xor_sync(FULL_MASK, a1, 1);
+          if ((lane & 3) == 0) sm.xr[e][((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = a1;
         }
       }
     }
   }
   __syncthreads();  // kk, kq visible; thread 0 has issued (or abandoned) the MMAs
+  G_TRACE(4, unit_no);
   if constexpr (REPLAY) {
     if (warp == 2) {
       // decay of every committed entry up to the window: e^{total - pre_c}, and of the checkpoint: e^{total}
@@ -410,8 +474,10 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
         sm.dec[e] = e < wp ? __expf(total - pre) : 0.f;
         if (e == 0) sm.tdec = __expf(total);
       }
+      G_TRACE_W(11, unit_no);
     }
   }
+  if (warp == 1) G_TRACE_W(13, unit_no);
   if (warp == 1) {
     // the window's scalar coefficients, once per unit instead of once per value row
     float G[G_NT];
@@ -444,12 +510,35 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
       sm.cC[s] = s < n_acc ? __expf(Gn - Gs) : 0.f;
       sm.G[s] = Gs;
     }
+    G_TRACE_W(10, unit_no);
   }
+  if (warp == 5) G_TRACE_W(12, unit_no);
   __syncthreads();
+  G_TRACE(5, unit_no);
   ok = mbar_wait(&sm.bar_load, par, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
        mbar_wait(&sm.bar_mma, par, &sm.abort_flag, p.status, ST_WAIT_TMEM_FULL);
   ok = __syncthreads_and(ok);  // one verdict for the CTA
   tc_fence_after();
+  G_TRACE(6, unit_no);
+  if constexpr (REPLAY) {
+    // the operand tile [q | k] has been consumed: its 4 KB now hold the d entries, [logical entry][value row] bf16
+    *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(&sm.QK[0][0]) + d_entry * G_D + (tid & 15) * 8) = dchunk;
+    __syncthreads();
+  }
+  if constexpr (REPLAY) {
+    // the MMAs were the only readers of the tile and nothing is written back: the next unit's checkpoint tile
+    // can travel during this unit's epilogue and the next unit's prologue
+    if (tid == 0) {
+      tile_requested = false;
+      if (ok && nb >= 0 && nx_slot >= 0) {
+        const int nrow0 = (nx_slot * G_HV + 2 * ((pair + ncl) % G_HK) + rank) * G_D;
+        mbar_expect_tx(&sm.bar_load, G_TILE_BYTES);
+#pragma unroll
+        for (int sub = 0; sub < 4; ++sub) tma_load_2d(sm.S[sub], &tmS, 32 * sub, nrow0, &sm.bar_load);
+        tile_requested = true;
+      }
+    }
+  }
 
   // ---- per value row: R, D = (I + A)^-1 R, outputs; gated RMSNorm ----
   float o[G_NT] = {0.f, 0.f, 0.f, 0.f};
@@ -467,9 +556,9 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     if constexpr (REPLAY) {
       // S x = e^{total} H0 x + sum_c (d_c e^{total - pre_c}) (k_c . x)   (qk_gdn_verify.cu:706-742)
       float aq[G_NT] = {0.f, 0.f, 0.f, 0.f}, ak[G_NT] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int e = 0; e < G_RING; ++e) {
-        const float dsc = __uint_as_float(static_cast<uint32_t>(dr[e]) << 16) * sm.dec[e];
+#pragma unroll 4
+      for (int e = 0; e < wp; ++e) {
+        const float dsc = bf2f(reinterpret_cast<const bf16*>(&sm.QK[0][0])[e * G_D + v]) * sm.dec[e];
         const float4 xq = *reinterpret_cast<const float4*>(&sm.xr[e][0]);
         const float4 xk = *reinterpret_cast<const float4*>(&sm.xr[e][4]);
         aq[0] = fmaf(dsc, xq.x, aq[0]); aq[1] = fmaf(dsc, xq.y, aq[1]);
@@ -532,6 +621,7 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   }
   tc_fence_before();
   __syncthreads();
+  G_TRACE(7, unit_no);
   if (ok && tid < G_D) {
 #pragma unroll
     for (int s = 0; s < G_NT; ++s) {
@@ -588,7 +678,10 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     }
   }
   __syncthreads();  // every buffer of the unit is free for the next one
+  G_TRACE(8, unit_no);
+  ++unit_no;
   }  // units
+  G_TRACE(9, 1);
   if (tid == 0) bulk_wait_read_all();  // the last tile has left shared memory; the writes complete with the grid
   __syncthreads();
   if (warp == 0) {
@@ -600,6 +693,12 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
 }  // namespace b200
 
 using namespace b200;
+
+#ifdef B200_TRACE
+extern "C" int b200_gdn_trace_read(unsigned long long* host) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_gdn_trace, sizeof(g_gdn_trace)));
+}
+#endif
 
 extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, const void* b, void* conv_state,
                                const void* conv_w, const float* a_log, const float* dt_bias, float* state,
@@ -660,8 +759,9 @@ extern "C" int b200_gdn_verify_replay(const void* mixed, const void* z, const vo
   if (reinterpret_cast<uintptr_t>(checkpoint) & 15)
     return fail(B200_E_ALIGN, "b200_gdn_verify_replay: checkpoint must be 16-byte aligned");
   if ((reinterpret_cast<uintptr_t>(conv_w) & 7) || (reinterpret_cast<uintptr_t>(k_ring) & 7) ||
-      (reinterpret_cast<uintptr_t>(window) & 3))
-    return fail(B200_E_ALIGN, "b200_gdn_verify_replay: conv_w and k_ring must be 8-byte, window 4-byte aligned");
+      (reinterpret_cast<uintptr_t>(window) & 3) || (reinterpret_cast<uintptr_t>(d_ring) & 15))
+    return fail(B200_E_ALIGN,
+                "b200_gdn_verify_replay: conv_w and k_ring must be 8-byte, window 4-byte, d_ring 16-byte aligned");
   if (B == 0) return 0;
   GdnArgs p{};
   p.mixed = static_cast<const bf16*>(mixed);

@@ -8,7 +8,8 @@ random-initialised on the device from a seed (there are no checkpoints here); ev
 state and KV pages, so a step streams what a real model would stream.
 
 Per layer (T = 4 drafts x B sequences rows, T <= 64):
-    GDN layer:        in_proj (dense fp8) -> gdn_verify -> out_proj (dense fp8)
+    GDN layer:        in_proj (dense fp8) -> gdn_verify -> out_proj (dense fp8); with `gdn_layout="ring"` the state is
+                      the engine's read-only checkpoint + 16-entry (d, k, g) ring and the step appends to the ring
     attention layer:  attn_front (projection + q/k norm + RoPE, e4m3 q/k/v) -> attn_verify -> o_proj (dense fp8)
     then              residual add + RMSNorm -> router -> lists -> fp8 experts -> combine fused with the next
                       layer's residual add + input RMSNorm
@@ -48,11 +49,16 @@ def _fp8(shape, gen, device, std=0.02, chunk=64):
 class DecodeStep:
     """`layers` layers (layer i is full attention iff i % 4 == 3), B sequences with `ctx` tokens of context each."""
 
-    def __init__(self, layers=48, B=8, ctx=8192, vocab=151936, experts=E, seed=1005, device="cuda"):
+    def __init__(self, layers=48, B=8, ctx=8192, vocab=151936, experts=E, seed=1005, device="cuda", gdn_layout="explicit",
+                 ring_fill=0):
         if 4 * B > 64:
             raise ValueError("the decode-width projections take at most 64 rows: B <= 16")
+        if gdn_layout not in ("explicit", "ring"):
+            raise ValueError("gdn_layout is 'explicit' or 'ring'")
+        self.gdn_layout = gdn_layout
         dev = torch.device(device)
         g = torch.Generator(device=dev).manual_seed(seed)
+        g_ring = torch.Generator(device=dev).manual_seed(seed + 1)   # ring contents: the weights do not depend on the layout
         bf = torch.bfloat16
         self.B, self.T, self.ctx, self.n_layers, self.E = B, 4 * B, ctx, layers, experts
         self.status = ops.new_status(dev)
@@ -78,6 +84,14 @@ class DecodeStep:
                 L["dt_bias"] = rn(32)
                 L["state"] = rn(B, 32, 128, 128, std=0.1)
                 L["gdn_norm"] = rn(128, std=0.1).to(bf)
+                if gdn_layout == "ring":   # pools of B slots, request b in slot b; `ring_fill` committed entries
+                    L["window"] = torch.zeros(B, 8192, 6, dtype=bf, device=dev)
+                    L["d_ring"] = (torch.randn(B, 32, 16, 128, generator=g_ring, device=dev) * 0.3).to(bf)
+                    L["dlo_ring"] = torch.zeros(B, 32, 16, 128, dtype=bf, device=dev)
+                    L["k_ring"] = torch.nn.functional.normalize(torch.randn(B, 16, 16, 128, generator=g_ring, device=dev),
+                                                                dim=-1).to(bf)
+                    L["klo_ring"] = torch.zeros(B, 16, 16, 128, dtype=bf, device=dev)
+                    L["g_ring"] = -torch.rand(B, 32, 16, generator=g_ring, device=dev) * 0.5
             L["post_norm"] = rn(H, std=0.1).to(bf)     # norm between the mixer and the MoE
             L["next_norm"] = rn(H, std=0.1).to(bf)     # input norm of the next layer (final norm after the last)
             L["wr"] = rn(experts, H, std=0.02)
@@ -102,6 +116,9 @@ class DecodeStep:
         self.seqlens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
         self.positions = (torch.arange(B, device=dev)[:, None] * 0 + torch.arange(ctx - 4, ctx, device=dev)[None, :]).reshape(-1).to(torch.int64).contiguous()
         self.accepted = torch.randint(0, 5, (B,), generator=g, device=dev, dtype=torch.int32)
+        self.slots = torch.arange(B, dtype=torch.int32, device=dev)
+        self.write_pos = torch.full((B,), int(ring_fill), dtype=torch.int32, device=dev)
+        self.cache_base = torch.zeros(B, dtype=torch.int32, device=dev)
         # buffers reused by every layer
         T = self.T
         self.lists = ops.RoutingLists(T, K, experts, 64, dev)
@@ -129,8 +146,14 @@ class DecodeStep:
                 p = ops.dense_fp8(h, L["in_w"], L["in_s"], status=st)
                 mixed, z = p[:, :8192].contiguous(), p[:, 8192:12288].contiguous()
                 b, a = p[:, 12288:12320].contiguous(), p[:, 12320:12352].contiguous()
-                core = ops.gdn_verify(mixed, z, a, b, L["conv_state"], L["conv_w"], L["a_log"], L["dt_bias"], L["state"],
-                                      self.accepted, L["gdn_norm"], 1e-6, status=st)
+                if self.gdn_layout == "ring":
+                    core = ops.gdn_verify_replay(mixed, z, a, b, L["conv_state"], L["conv_w"], L["window"], L["a_log"],
+                                                 L["dt_bias"], L["state"], L["d_ring"], L["dlo_ring"], L["k_ring"],
+                                                 L["klo_ring"], L["g_ring"], self.slots, self.slots, self.slots,
+                                                 self.write_pos, self.cache_base, L["gdn_norm"], 1e-6, status=st)
+                else:
+                    core = ops.gdn_verify(mixed, z, a, b, L["conv_state"], L["conv_w"], L["a_log"], L["dt_bias"], L["state"],
+                                          self.accepted, L["gdn_norm"], 1e-6, status=st)
                 proj = ops.dense_fp8(core, L["out_w"], L["out_s"], status=st)
                 n += 2 + 1 + 2
             h2 = ops.add_rmsnorm(proj, residual, L["post_norm"])

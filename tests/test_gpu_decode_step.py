@@ -26,3 +26,24 @@ def test_decode_step_small_stack():
     for bi in range(3):
         moved = not torch.equal(step.layers[0]["state"][bi], fresh.layers[0]["state"][bi])
         assert moved == (int(step.accepted[bi]) > 0)
+
+
+def test_decode_step_ring_layout_with_empty_rings_gives_the_same_tokens():
+    # the GDN layers on the checkpoint + ring layout with no committed entries see the same state as the explicit form
+    from bundles_b200 import decode_step, ops
+    dev = torch.device("cuda", 0)
+    kw = dict(layers=4, B=3, ctx=300, vocab=128 * 40 + 17, experts=64, seed=9, device=dev)
+    explicit = decode_step.DecodeStep(**kw)
+    ring = decode_step.DecodeStep(gdn_layout="ring", **kw)
+    g = torch.Generator(device=dev).manual_seed(2)
+    x = torch.randn(explicit.T, 2048, generator=g, device=dev).to(torch.bfloat16)
+    a, b = explicit.step(x), ring.step(x)
+    torch.cuda.synchronize()
+    assert ops.read_status(ring.status) == 0
+    assert torch.equal(a, b)
+    assert torch.equal(ring.layers[0]["state"], decode_step.DecodeStep(**kw).layers[0]["state"]), "checkpoint is read-only"
+    # a committed history changes the state the window sees
+    hist = decode_step.DecodeStep(gdn_layout="ring", ring_fill=7, **kw)
+    c = hist.step(x)
+    torch.cuda.synchronize()
+    assert ops.read_status(hist.status) == 0 and c.shape == a.shape
