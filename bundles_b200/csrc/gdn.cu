@@ -65,6 +65,7 @@ struct GdnSmem {
   float gr[G_RING];         // REPLAY: committed g in logical order (0 past the history)
   float dec[G_RING];        // REPLAY: e^{total - pre_c} (0 past the history)
   float tdec;               // REPLAY: e^{total}
+  int nx[5];                // REPLAY: the next unit's state slot, ring slot, window slot, write position, ring base
   uint64_t bar_load, bar_mma;
   uint32_t tmem_slot;
   int abort_flag;
@@ -127,6 +128,11 @@ __device__ __forceinline__ void conv_record(const ConvIn& in, bf16* __restrict__
     dst[i] = static_cast<uint32_t>(__bfloat16_as_ushort(in.win[1 + 2 * i])) |
              (static_cast<uint32_t>(__bfloat16_as_ushort(in.win[2 + 2 * i])) << 16);
 }
+
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 struct GdnArgs {
   const bf16* mixed;
@@ -201,39 +207,48 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   // REPLAY: the slot indices and ring cursors of a unit are fetched one unit ahead, so that no unit starts with a
   // chain of dependent global loads, and its checkpoint tile is requested as soon as the previous unit's MMAs
   // have left the (never written) tile buffer
-  int nx_slot = 0, nx_ring = 0, nx_win = 0, nx_wp = 0, nx_cb = 0;
+  // (asynchronous copies by the last thread into shared memory: a register would be spilled while its load is in
+  // flight, which is a wait)
   bool tile_requested = false;  // thread 0: this unit's tile was requested during the previous unit
+  auto idx_level1 = [&](int nb) {
+    cp_async4(&sm.nx[0], p.state_idx + nb);
+    cp_async4(&sm.nx[1], p.ring_idx + nb);
+    cp_async4(&sm.nx[2], p.win_idx + nb);
+  };
+  auto idx_level2 = [&]() {
+    cp_async_wait_all();
+    const int r = *reinterpret_cast<volatile int*>(&sm.nx[1]);
+    cp_async4(&sm.nx[3], p.write_pos + r);
+    cp_async4(&sm.nx[4], p.cache_base + r);
+  };
+  // the whole fetch at once, for the paths that skip a unit: every thread has read the current indices before
+  // the first barrier, and sees the next ones after the second
+  auto idx_fetch_now = [&](int nb) {
+    __syncthreads();
+    if (tid == G_THREADS - 1 && nb >= 0) {
+      idx_level1(nb);
+      idx_level2();
+      cp_async_wait_all();
+    }
+    __syncthreads();
+  };
   if constexpr (REPLAY) {
     const int first = blockIdx.x >> 1;
-    if (first < npairs) {
-      const int b0 = first / G_HK;
-      nx_slot = p.state_idx[b0];
-      nx_ring = p.ring_idx[b0];
-      nx_win = p.win_idx[b0];
-      nx_wp = p.write_pos[nx_ring];
-      nx_cb = p.cache_base[nx_ring];
-    }
+    idx_fetch_now(first < npairs ? first / G_HK : -1);
   }
   for (int pair = blockIdx.x >> 1; pair < npairs; pair += ncl, par ^= 1u) {
   const int b = pair / G_HK, hk = pair - b * G_HK, hv = 2 * hk + rank;
   int slot = b, ring = 0, wp = 0, cb = 0, wslot = 0;
   const int nb = pair + ncl < npairs ? (pair + ncl) / G_HK : -1;  // the next unit's request
   if constexpr (REPLAY) {
-    slot = nx_slot;
-    ring = nx_ring;
-    wslot = nx_win;
-    cb = nx_cb;
-    wp = nx_wp < 0 ? 0 : (nx_wp > G_RING ? G_RING : nx_wp);
-    if (nb >= 0) {
-      nx_slot = p.state_idx[nb];
-      nx_ring = p.ring_idx[nb];
-      nx_win = p.win_idx[nb];
-    }
+    slot = sm.nx[0];
+    ring = sm.nx[1];
+    wslot = sm.nx[2];
+    wp = sm.nx[3];
+    cb = sm.nx[4];
+    wp = wp < 0 ? 0 : (wp > G_RING ? G_RING : wp);
     if (slot < 0) {  // a padded request: zero output, nothing read or written; no barrier phase is used
-      if (nb >= 0) {
-        nx_wp = p.write_pos[nx_ring];
-        nx_cb = p.cache_base[nx_ring];
-      }
+      idx_fetch_now(nb);
       if (ok && tid < G_D)
 #pragma unroll
         for (int s = 0; s < G_NT; ++s)
@@ -243,6 +258,7 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     }
   }
   if (!ok) {  // after an abandoned wait the CTA only keeps its partner's cluster barriers company
+    if constexpr (REPLAY) idx_fetch_now(nb);  // it still has to know which units are padded (they have no barrier)
     cluster_sync();
     continue;
   }
@@ -333,6 +349,8 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     }
     __syncthreads();
     G_TRACE(1, unit_no);
+    if constexpr (REPLAY)  // every thread has read this unit's indices: the next unit's may replace them
+      if (tid == G_THREADS - 1 && nb >= 0) idx_level1(nb);
     const int sub = c >> 5, chk = (c & 31) >> 2, e = c & 3;
 #pragma unroll
     for (int s = 0; s < G_NT; ++s) {
@@ -360,10 +378,6 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   if ((hv & 1) == 0) conv_roll(in_qk, cs_b, ch_qk, n_acc);
   if (!is_k) conv_roll(in_v, cs_b, ch_v, n_acc);
   if constexpr (REPLAY) {
-    if (nb >= 0) {  // the next unit's cursors: its ring slot has landed by now
-      nx_wp = p.write_pos[nx_ring];
-      nx_cb = p.cache_base[nx_ring];
-    }
     bf16* wrec = p.window + static_cast<size_t>(wslot) * G_CONV * 6;
     if ((hv & 1) == 0) conv_record(in_qk, wrec, ch_qk);
     if (!is_k) conv_record(in_v, wrec, ch_v);
@@ -456,6 +470,8 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
       }
     }
   }
+  if constexpr (REPLAY)  // the next unit's ring slot has landed: fetch its cursors
+    if (tid == G_THREADS - 1 && nb >= 0) idx_level2();
   __syncthreads();  // kk, kq visible; thread 0 has issued (or abandoned) the MMAs
   G_TRACE(4, unit_no);
   if constexpr (REPLAY) {
@@ -530,8 +546,9 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     // can travel during this unit's epilogue and the next unit's prologue
     if (tid == 0) {
       tile_requested = false;
-      if (ok && nb >= 0 && nx_slot >= 0) {
-        const int nrow0 = (nx_slot * G_HV + 2 * ((pair + ncl) % G_HK) + rank) * G_D;
+      const int nslot = nb >= 0 ? *reinterpret_cast<volatile int*>(&sm.nx[0]) : -1;
+      if (ok && nslot >= 0) {
+        const int nrow0 = (nslot * G_HV + 2 * ((pair + ncl) % G_HK) + rank) * G_D;
         mbar_expect_tx(&sm.bar_load, G_TILE_BYTES);
 #pragma unroll
         for (int sub = 0; sub < 4; ++sub) tma_load_2d(sm.S[sub], &tmS, 32 * sub, nrow0, &sm.bar_load);
@@ -677,6 +694,8 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
     while (!mbar_try(&sm.bar_load, par) && globaltimer() - t0 < 20000000ull) {
     }
   }
+  if constexpr (REPLAY)
+    if (tid == G_THREADS - 1) cp_async_wait_all();  // the next unit's indices are in shared memory
   __syncthreads();  // every buffer of the unit is free for the next one
   G_TRACE(8, unit_no);
   ++unit_no;
