@@ -273,11 +273,13 @@ def _gdn_entry(dev, ops, synth, timed, st, it, out, hbm, which):
     states = [g["state"].clone() for _ in range(4)]
     convs = [g["conv_state"].clone() for _ in range(4)]
 
+    gws = ops.gdn_workspace(32, dev)
+
     def gdn_step():
         i = it[0] % 4
         it[0] += 1
         ops.gdn_verify(g["mixed"], g["z"], g["a"], g["b"], convs[i], g["conv_w"], g["a_log"], g["dt_bias"], states[i],
-                       g["accepted"], g["norm_w"], 1e-6, status=st)
+                       g["accepted"], g["norm_w"], 1e-6, status=st, ws=gws)
 
     ms = timed(gdn_step, calls=4)
     B = 32

@@ -52,7 +52,8 @@ PROTOTYPES = {
     "b200_lmhead_workspace_bytes": (sz, [i32, i32, i32]),
     "b200_lmhead_argmax": (i32, [vp, i32, i32, vp, vp, i32, i32, vp, vp, vp, vp, sz, vp, vp]),
     "b200_argmax_merge": (i32, [vp, vp, i32, i32, vp, vp]),
-    "b200_gdn_verify": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, f32, i32, vp, vp, vp]),
+    "b200_gdn_verify": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, f32, i32, vp, vp, sz, vp, vp]),
+    "b200_gdn_workspace_bytes": (sz, [i32]),
     "b200_gdn_verify_replay": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                      vp, f32, i32, vp, vp, vp]),
 }

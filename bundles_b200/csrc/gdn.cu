@@ -30,6 +30,8 @@
 // logical entries write_pos + s (those below 16), the conv state is rolled by the whole window and the
 // per-draft windows are recorded as [s1 s2 x0 x1 x2 x3] per channel; which of it survives is the engine's
 // move of the ring cursor.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -709,6 +711,360 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
   }
 }
 
+
+// =====================================================================================================
+// The explicit-state step as two launches: a small operand kernel and a streaming kernel.
+//
+// In the kernel above every unit runs a chain of dependent steps (input loads, conv, norms, barriers, dots,
+// coefficients) before and after the one thing that is bound by memory, the 64 KB state tile; the chain, not
+// the bytes, sets its time.  Here gdn_prep_kernel does everything that does not touch the state, once per
+// (sequence, key head): conv + SiLU, norms, gates, window dots and coefficients, and leaves per unit one operand tile
+// [q | k] already in the swizzled layout the tensor core reads plus one 2.2 KB block (conv v, z, coefficients).
+// gdn_stream_kernel then only moves state tiles: per unit one barrier for the tile and the two operand blocks
+// (TMA tensor load + two bulk copies), sixteen tf32 MMAs, the per-row epilogue, the in-place update and the
+// tile store.  It is launched with programmatic stream serialization and requests its first tile before
+// waiting for the operand kernel, since the tile does not depend on it.
+// =====================================================================================================
+struct GdnOps {              // per (sequence, value head): one bulk copy
+  bf16 v[G_NT][G_D];         // conv v (bf16 values)
+  bf16 z[G_NT][G_D];         // gate input
+  float cA[G_NT][G_NT], cF[G_NT][G_NT], cE[G_NT], cR[G_NT], cC[G_NT];
+  int n_acc;                 // tokens to advance the state by
+  int pad[3];
+};
+static_assert(sizeof(GdnOps) == 2240 && sizeof(GdnOps) % 16 == 0, "GdnOps is copied with one bulk copy");
+constexpr int G_QK_FLOATS = 4 * 8 * 32;  // the operand tile of one (sequence, key head): 4 KB
+
+struct GdnPrepSmem {
+  float q[G_NT][G_D], k[G_NT][G_D];
+  float nrm[2][G_NT][4];
+  float kk[G_NT][G_NT], kq[G_NT][G_NT];
+  float g[2][G_NT], beta[2][G_NT];
+};
+
+__global__ void __launch_bounds__(512) gdn_prep_kernel(const GdnArgs p, float* __restrict__ qk_ws, GdnOps* __restrict__ ops_ws) {
+  __shared__ GdnPrepSmem sm;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int pair = blockIdx.x, b = pair / G_HK, hk = pair - b * G_HK;
+  const int grp = tid >> 7, c = tid & 127;  // 0: q, 1: k, 2 / 3: v of value head 2 hk / 2 hk + 1
+  pdl_wait();
+  pdl_launch();
+  int n_acc = p.accepted[b];
+  n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
+  const bf16* mixed_b = p.mixed + static_cast<size_t>(b) * G_NT * G_CONV;
+  bf16* cs_b = p.conv_state + static_cast<size_t>(b) * G_CONV * 3;
+  const int hv_mine = 2 * hk + (grp & 1);  // value head of a v thread
+  const int ch = grp == 0 ? hk * G_D + c : (grp == 1 ? G_QDIM + hk * G_D + c : 2 * G_QDIM + hv_mine * G_D + c);
+  ConvIn in;
+  conv_load(mixed_b, cs_b, p.conv_w, ch, in);
+  bf16 zraw[G_NT];
+  if (grp >= 2) {
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) zraw[s] = p.z[(static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv_mine * G_D + c];
+  }
+  if (tid < 2 * G_NT) {  // gates of both value heads (qk_gdn_verify.cu:616-631)
+    const int h = tid >> 2, s = tid & 3, hv = 2 * hk + h;
+    const float av = bf2f(p.a[(static_cast<size_t>(b) * G_NT + s) * G_HV + hv]);
+    const float bv = bf2f(p.b[(static_cast<size_t>(b) * G_NT + s) * G_HV + hv]);
+    const float xg = av + p.dt_bias[hv];
+    const float sp = xg <= 20.f ? log1pf(expf(xg)) : xg;
+    const float g = -expf(p.a_log[hv]) * sp;
+    sm.g[h][s] = g;
+    sm.beta[h][s] = 1.f / (1.f + expf(-bv));
+  }
+  float y[G_NT];
+  conv_apply(in, y);
+  if (grp < 2) {
+    float ss[G_NT];
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) ss[s] = y[s] * y[s];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) ss[s] += __shfl_xor_sync(FULL_MASK, ss[s], o);
+    if (lane == 0)
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) sm.nrm[grp][s][warp & 3] = ss[s];
+  } else {
+    GdnOps& o = ops_ws[b * G_HV + hv_mine];
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) {
+      o.v[s][c] = f2bf(y[s]);
+      o.z[s][c] = zraw[s];
+    }
+  }
+  // every channel belongs to this CTA alone, and its old conv state is in registers: roll it
+  conv_roll(in, cs_b, ch, n_acc);
+  __syncthreads();
+  if (grp < 2) {
+    const int sub = c >> 5, chk = (c & 31) >> 2, e = c & 3;
+    float* qk = qk_ws + static_cast<size_t>(pair) * G_QK_FLOATS;
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) {
+      const float n = sm.nrm[grp][s][0] + sm.nrm[grp][s][1] + sm.nrm[grp][s][2] + sm.nrm[grp][s][3];
+      const float r = (1.f / sqrtf(n + 1e-6f)) * (grp ? 1.f : 0.08838834764831845f);  // d_k^-0.5 on q
+      const float val = y[s] * r;
+      const int row = grp * 4 + s;
+      qk[sub * 256 + row * 32 + sw_chunk(row, chk) + e] = val;
+      (grp ? sm.k : sm.q)[s][c] = val;
+    }
+  }
+  __syncthreads();
+  // k_i . k_j and k_i . q_j: 32 dots of length 128, two per warp
+#pragma unroll
+  for (int dd = 0; dd < 2; ++dd) {
+    const int d = 2 * warp + dd, i = (d >> 2) & 3, j = d & 3;
+    float acc = 0.f;
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+      const int cc = lane + 32 * c4;
+      acc = fmaf(sm.k[i][cc], d < 16 ? sm.k[j][cc] : sm.q[j][cc], acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(FULL_MASK, acc, o);
+    if (lane == 0) (d < 16 ? sm.kk : sm.kq)[i][j] = acc;
+  }
+  __syncthreads();
+  if (warp < 2) {
+    // the window's scalar coefficients of value head 2 hk + warp
+    GdnOps& o = ops_ws[b * G_HV + 2 * hk + warp];
+    float G[G_NT];
+    float run = 0.f;
+#pragma unroll
+    for (int s = 0; s < G_NT; ++s) {
+      run += sm.g[warp][s];
+      G[s] = run;
+    }
+    if (lane < 16) {
+      const int i = lane >> 2, j = lane & 3;
+      float Gi = 0.f, Gj = 0.f;
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) {
+        Gi = s == i ? G[s] : Gi;
+        Gj = s == j ? G[s] : Gj;
+      }
+      o.cA[i][j] = i > j ? sm.beta[warp][i] * __expf(Gi - Gj) * sm.kk[i][j] : 0.f;
+      o.cF[i][j] = i <= j ? __expf(Gj - Gi) * sm.kq[i][j] : 0.f;
+    } else if (lane < 20) {
+      const int s = lane - 16;
+      float Gs = 0.f, Gn = 0.f;
+#pragma unroll
+      for (int u = 0; u < G_NT; ++u) {
+        Gs = u == s ? G[u] : Gs;
+        Gn = u == n_acc - 1 ? G[u] : Gn;
+      }
+      o.cE[s] = __expf(Gs);
+      o.cR[s] = sm.beta[warp][s];
+      o.cC[s] = s < n_acc ? __expf(Gn - Gs) : 0.f;
+    } else if (lane == 20) {
+      o.n_acc = n_acc;
+    }
+  }
+}
+
+struct GdnStreamSmem {
+  float S[4][G_D * 32];   // 64 KB state tile, swizzled sub-tiles (1024-byte aligned)
+  float QK[4][8 * 32];    // operand tile [q | k]; the MMA's rows 8..15 alias what follows
+  GdnOps ops;             // v and z are overwritten by c_i D_i (fp32 [4][128]) for the state update
+  float red[4][G_NT];
+  uint64_t bar_tile, bar_ops, bar_mma;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+// Explicit-state form.  grid: persistent CTAs, three per SM, unit u = (sequence, value head) = blockIdx.x + i * gridDim.x.
+__global__ void __launch_bounds__(G_THREADS, 3)
+gdn_stream_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p, const float* __restrict__ qk_ws,
+                  const GdnOps* __restrict__ ops_ws) {
+  extern __shared__ uint8_t smem_raw[];
+  GdnStreamSmem& sm = *reinterpret_cast<GdnStreamSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nunits = p.B * G_HV;
+  if (tid == 0) {
+    mbar_init(&sm.bar_tile, 1);
+    mbar_init(&sm.bar_ops, 1);
+    mbar_init(&sm.bar_mma, 1);
+    sm.abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmS);
+  }
+  if (warp == 0) tmem_alloc(&sm.tmem_slot, 32);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm.tmem_slot;
+  G_TRACE(9, 0);
+  int unit_no = 0;
+  auto request_tile = [&](int u) {
+    mbar_expect_tx(&sm.bar_tile, G_TILE_BYTES);
+#pragma unroll
+    for (int sub = 0; sub < 4; ++sub) tma_load_2d(sm.S[sub], &tmS, 32 * sub, u * G_D, &sm.bar_tile);
+  };
+  auto request_ops = [&](int u) {
+    mbar_expect_tx(&sm.bar_ops, G_QK_FLOATS * 4 + sizeof(GdnOps));
+    bulk_load(sm.QK, qk_ws + static_cast<size_t>(u >> 1) * G_QK_FLOATS, G_QK_FLOATS * 4, &sm.bar_ops);
+    bulk_load(&sm.ops, ops_ws + u, sizeof(GdnOps), &sm.bar_ops);
+  };
+  // the first tile does not depend on the operand kernel: it travels while that kernel runs
+  if (tid == 0 && blockIdx.x < nunits) request_tile(blockIdx.x);
+  pdl_wait();
+  if (tid == 0 && blockIdx.x < nunits) request_ops(blockIdx.x);
+  bool ok = true;
+  uint32_t par = 0;
+  for (int u = blockIdx.x; u < nunits; u += gridDim.x, par ^= 1u) {
+    const int b = u >> 5, hv = u & 31;
+    G_TRACE(0, unit_no);
+    // ---- S [q | k]: sixteen tf32 MMAs (M = 128 state rows, N = 16, K = 8 each) into 16 TMEM columns ----
+    if (tid == 0) {
+      const bool landed = mbar_wait(&sm.bar_tile, par, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
+                          mbar_wait(&sm.bar_ops, par, &sm.abort_flag, p.status, ST_WAIT_FULL);
+      G_TRACE(1, unit_no);
+      if (landed) {
+        tc_fence_after();
+        const uint32_t idesc = umma_idesc(UMMA_C_F32, UMMA_AB_TF32, 16);
+#pragma unroll
+        for (int sub = 0; sub < 4; ++sub)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            tc_mma_tf32(tmem_base, umma_desc_sw128(smem_u32(sm.S[sub]) + kk * 32),
+                        umma_desc_sw128(smem_u32(sm.QK[sub]) + kk * 32), idesc, (sub | kk) != 0);
+        tc_commit(&sm.bar_mma);
+      }
+    }
+    ok = mbar_wait(&sm.bar_ops, par, &sm.abort_flag, p.status, ST_WAIT_FULL) &&
+         mbar_wait(&sm.bar_tile, par, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
+         mbar_wait(&sm.bar_mma, par, &sm.abort_flag, p.status, ST_WAIT_TMEM_FULL);
+    ok = __syncthreads_and(ok);  // one verdict for the CTA
+    if (!ok) break;             // `par` still names the phases this unit armed
+    tc_fence_after();
+    G_TRACE(2, unit_no);
+    const int n_acc = sm.ops.n_acc;
+    // ---- per value row: R, D = (I + A)^-1 R, outputs; gated RMSNorm ----
+    float o[G_NT] = {0.f, 0.f, 0.f, 0.f}, zz[G_NT] = {0.f, 0.f, 0.f, 0.f}, cd[G_NT] = {0.f, 0.f, 0.f, 0.f};
+    if (tid < G_D) {
+      const int v = tid;
+      uint32_t hr[16];
+      tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16), hr);  // warps 0..3 own TMEM lane quadrants 0..3
+      tmem_ld_wait();
+      float R[G_NT], D[G_NT];
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) {
+        zz[s] = bf2f(sm.ops.z[s][v]);
+        R[s] = sm.ops.cR[s] * (bf2f(sm.ops.v[s][v]) - sm.ops.cE[s] * __uint_as_float(hr[4 + s]));
+      }
+#pragma unroll
+      for (int i = 0; i < G_NT; ++i) {
+        float d = R[i];
+#pragma unroll
+        for (int j = 0; j < i; ++j) d = fmaf(-sm.ops.cA[i][j], D[j], d);
+        D[i] = d;
+      }
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) {
+        float acc = sm.ops.cE[s] * __uint_as_float(hr[s]);
+#pragma unroll
+        for (int i = 0; i <= s; ++i) acc = fmaf(D[i], sm.ops.cF[i][s], acc);
+        o[s] = rbf(acc);  // the core output is stored in bf16 before the norm (qk_gdn_verify.cu:761)
+        cd[s] = D[s] * sm.ops.cC[s];
+      }
+      float ss[G_NT];
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) ss[s] = o[s] * o[s];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int s = 0; s < G_NT; ++s) ss[s] += __shfl_xor_sync(FULL_MASK, ss[s], off);
+      if (lane == 0)
+#pragma unroll
+        for (int s = 0; s < G_NT; ++s) sm.red[warp][s] = ss[s];
+    }
+    tc_fence_before();
+    G_TRACE(3, unit_no);
+    __syncthreads();  // row sums visible; every thread has read its v and z
+    float* cdsm = reinterpret_cast<float*>(&sm.ops.v[0][0]);  // c_i D_i, fp32 [4][128], over v and z
+    if (tid < G_D) {
+      const float nw = bf2f(p.norm_w[tid]);
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) {
+        const float var = (sm.red[0][s] + sm.red[1][s] + sm.red[2][s] + sm.red[3][s]) * (1.f / G_D);
+        const float rstd = rsqrtf(var + p.eps);
+        p.out[(static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv * G_D + tid] =
+            f2bf(o[s] * rstd * nw * (zz[s] * (1.f / (1.f + __expf(-zz[s])))));
+        cdsm[s * G_D + tid] = cd[s];
+      }
+    }
+    const int un = u + gridDim.x;  // this CTA's next unit
+    G_TRACE(4, unit_no);
+    // ---- state after n_acc tokens, in place in the swizzled tile, then four TMA tensor stores ----
+    if (n_acc > 0) {
+      __syncthreads();  // c_i D_i visible
+      const int rg = tid >> 3, ks = tid & 7;  // thread = 4 state rows x one 16-byte chunk position of each sub-tile row
+      const float decay = sm.ops.cE[n_acc - 1];
+      float cdr[4][G_NT];
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int i = 0; i < G_NT; ++i) cdr[r][i] = cdsm[i * G_D + rg * 4 + r];
+#pragma unroll
+      for (int sub = 0; sub < 4; ++sub) {
+        float4 kv[G_NT];
+#pragma unroll
+        for (int t = 0; t < G_NT; ++t) kv[t] = *reinterpret_cast<const float4*>(&sm.QK[sub][(4 + t) * 32 + sw_chunk(4 + t, ks)]);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int row = rg * 4 + r;
+          float4* sp = reinterpret_cast<float4*>(&sm.S[sub][row * 32 + sw_chunk(row, ks)]);
+          float4 sv = *sp;
+          sv.x *= decay; sv.y *= decay; sv.z *= decay; sv.w *= decay;
+#pragma unroll
+          for (int t = 0; t < G_NT; ++t) {
+            sv.x = fmaf(cdr[r][t], kv[t].x, sv.x);
+            sv.y = fmaf(cdr[r][t], kv[t].y, sv.y);
+            sv.z = fmaf(cdr[r][t], kv[t].z, sv.z);
+            sv.w = fmaf(cdr[r][t], kv[t].w, sv.w);
+          }
+          *sp = sv;
+        }
+        // this 16 KB sub-tile is final: hand it to TMA while the next one is being updated
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) {
+          tma_store_2d(&tmS, 32 * sub, u * G_D, sm.S[sub]);
+          bulk_commit();
+        }
+      }
+      // the operand blocks are free: the next unit's may travel while the tile leaves
+      G_TRACE(5, unit_no);
+      if (tid == 0 && un < nunits) {
+        request_ops(un);
+        bulk_wait_read_all();  // the tile has left shared memory
+        request_tile(un);
+      }
+      G_TRACE(6, unit_no);
+    } else {
+      __syncthreads();  // every thread is done with the operand blocks and the tile
+      if (tid == 0 && un < nunits) {
+        request_ops(un);
+        request_tile(un);
+      }
+    }
+    ++unit_no;
+  }
+  G_TRACE(9, 1);
+  if (!ok && tid == 0) {
+    // an abandoned wait: give the copies in flight a bounded grace period before the CTA's memory goes away
+    const unsigned long long t0 = globaltimer();
+    while (!(mbar_try(&sm.bar_tile, par) && mbar_try(&sm.bar_ops, par)) && globaltimer() - t0 < 20000000ull) {
+    }
+  }
+  if (tid == 0) bulk_wait_read_all();  // the last tile has left shared memory; the writes complete with the grid
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 32);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -719,10 +1075,22 @@ extern "C" int b200_gdn_trace_read(unsigned long long* host) {
 }
 #endif
 
+extern "C" size_t b200_gdn_workspace_bytes(int B) {
+  return B <= 0 ? 0 : static_cast<size_t>(B) * (G_HK * G_QK_FLOATS * 4 + G_HV * sizeof(GdnOps));
+}
+
+static bool gdn_single_kernel() {  // B200_GDN_SINGLE=1: the one-launch cluster kernel (for comparison)
+  static const bool v = [] {
+    const char* e = getenv("B200_GDN_SINGLE");
+    return e && *e && *e != '0';
+  }();
+  return v;
+}
+
 extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, const void* b, void* conv_state,
                                const void* conv_w, const float* a_log, const float* dt_bias, float* state,
-                               const int32_t* accepted, const void* norm_w, float eps, int B, void* out,
-                               int32_t* status, void* stream) {
+                               const int32_t* accepted, const void* norm_w, float eps, int B, void* out, void* ws,
+                               size_t ws_bytes, int32_t* status, void* stream) {
   if (!mixed || !z || !a || !b || !conv_state || !conv_w || !a_log || !dt_bias || !state || !accepted || !norm_w || !out)
     return fail(B200_E_ARG, "b200_gdn_verify: null pointer");
   if (B < 0 || B > 65535) return fail(B200_E_ARG, "b200_gdn_verify: B=%d out of range", B);
@@ -747,10 +1115,31 @@ extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, 
   p.status = status;
   CUtensorMap tmS;
   if (int rc = make_tmap_f32_2d(&tmS, state, static_cast<uint64_t>(B) * G_HV * G_D, G_D, G_D, "gdn state")) return rc;
-  const int smem = static_cast<int>(sizeof(GdnSmem)) + 1024;
-  static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
+  if (!gdn_single_kernel()) {
+    if (!ws || ws_bytes < b200_gdn_workspace_bytes(B))
+      return fail(B200_E_WS, "b200_gdn_verify: workspace of %zu bytes needed, %zu given", b200_gdn_workspace_bytes(B),
+                  ws_bytes);
+    if (reinterpret_cast<uintptr_t>(ws) & 127) return fail(B200_E_ALIGN, "b200_gdn_verify: workspace must be 128-byte aligned");
+    float* qk_ws = static_cast<float*>(ws);
+    GdnOps* ops_ws = reinterpret_cast<GdnOps*>(qk_ws + static_cast<size_t>(B) * G_HK * G_QK_FLOATS);
+    const int ssmem = static_cast<int>(sizeof(GdnStreamSmem)) + 1024;
+    static bool sattr_done[64] = {false};
+    if (dev >= 0 && dev < 64 && !sattr_done[dev]) {
+      cudaFuncSetAttribute(gdn_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ssmem);
+      sattr_done[dev] = true;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    launch_k(gdn_prep_kernel, dim3(B * G_HK), dim3(512), 0, st, p, qk_ws, ops_ws);
+    int grid = sm_count() * 3;
+    if (grid > B * G_HV) grid = B * G_HV;
+    launch_k(gdn_stream_kernel, dim3(grid), dim3(G_THREADS), static_cast<size_t>(ssmem), st, tmS, p,
+             static_cast<const float*>(qk_ws), static_cast<const GdnOps*>(ops_ws));
+    return launch_status("b200_gdn_verify");
+  }
+  const int smem = static_cast<int>(sizeof(GdnSmem)) + 1024;
+  static bool attr_done[64] = {false};
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
     cudaFuncSetAttribute(gdn_verify_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     attr_done[dev] = true;

@@ -127,6 +127,7 @@ class DecodeStep:
         self.scratch = ops.router_scratch(T, H, experts, dev)
         self.ids = torch.empty(T, K, dtype=torch.int32, device=dev)
         self.wts = torch.empty(T, K, dtype=torch.float32, device=dev)
+        self.gdn_ws = ops.gdn_workspace(B, dev)
         self.launches = 0
 
     def step(self, x: torch.Tensor) -> torch.Tensor:
@@ -153,9 +154,9 @@ class DecodeStep:
                                                  self.write_pos, self.cache_base, L["gdn_norm"], 1e-6, status=st)
                 else:
                     core = ops.gdn_verify(mixed, z, a, b, L["conv_state"], L["conv_w"], L["a_log"], L["dt_bias"], L["state"],
-                                          self.accepted, L["gdn_norm"], 1e-6, status=st)
+                                          self.accepted, L["gdn_norm"], 1e-6, status=st, ws=self.gdn_ws)
                 proj = ops.dense_fp8(core, L["out_w"], L["out_s"], status=st)
-                n += 2 + 1 + 2
+                n += 2 + (1 if self.gdn_layout == "ring" else 2) + 2
             h2 = ops.add_rmsnorm(proj, residual, L["post_norm"])
             ops.router(h2, L["wr"], K, None, scratch=self.scratch, want_logits=False, ids=self.ids, wts=self.wts)
             ops.build_lists(self.ids, self.wts, self.lists)

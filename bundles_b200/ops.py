@@ -379,8 +379,15 @@ def argmax_merge(maxes, idxs):
     return tokens
 
 
+def gdn_workspace(B, device):
+    n = _lib.lib().b200_gdn_workspace_bytes(B)
+    buf = torch.empty(n + 128, dtype=torch.uint8, device=device)
+    off = (-buf.data_ptr()) % 128
+    return buf[off:off + n]
+
+
 def gdn_verify(mixed, z, a, b, conv_state, conv_w, a_log, dt_bias, state, accepted, norm_w, eps=1e-6, out=None,
-               status=None):
+               status=None, ws=None):
     """Gated DeltaNet verify over 4 draft tokens; updates `state` and `conv_state` in place to the
     accepted length (reference: qk_gdn_verify.gdn_verify_fused).  Returns out bf16 [B*4, 4096]."""
     _need(mixed, torch.bfloat16, "mixed", 2)
@@ -394,9 +401,11 @@ def gdn_verify(mixed, z, a, b, conv_state, conv_w, a_log, dt_bias, state, accept
                         f"conv_state={tuple(conv_state.shape)}")
     if out is None:
         out = torch.empty(B * 4, 4096, dtype=torch.bfloat16, device=mixed.device)
+    if ws is None:
+        ws = gdn_workspace(B, mixed.device)
     check(_lib.lib().b200_gdn_verify(_p(mixed), _p(z), _p(a), _p(b), _p(conv_state), _p(conv_w), _p(a_log),
                                      _p(dt_bias), _p(state), _p(accepted), _p(norm_w), float(eps), B, _p(out),
-                                     _p(status), _stream()), "b200_gdn_verify")
+                                     _p(ws), ws.numel(), _p(status), _stream()), "b200_gdn_verify")
     return out
 
 

@@ -225,11 +225,16 @@ int b200_moe_combine_norm(const void* cache, const void* x, const void* gate_w, 
  *   conv_state bf16 [B, 8192, 3] (in/out); conv_w bf16 [8192, 4]; a_log, dt_bias fp32 [32];
  *   state fp32 [B, 32, 128, 128] (S[v][k], in/out); accepted int32 [B] in 0..4;
  *   norm_w bf16 [128]; out bf16 [B*4, 4096].  state must be 16-byte aligned.
+ * Two launches: a small kernel computes everything that does not touch the state (conv, norms, gates,
+ * window coefficients) into `ws`, then a streaming kernel moves the state tiles (it starts before the first
+ * has finished and requests its first tiles meanwhile).
  */
 int b200_gdn_verify(const void* mixed, const void* z, const void* a, const void* b, void* conv_state,
                     const void* conv_w, const float* a_log, const float* dt_bias, float* state,
-                    const int32_t* accepted, const void* norm_w, float eps, int B, void* out, int32_t* status,
-                    void* stream);
+                    const int32_t* accepted, const void* norm_w, float eps, int B, void* out, void* ws,
+                    size_t ws_bytes, int32_t* status, void* stream);
+/* Scratch of b200_gdn_verify: the operands its first launch prepares for its second (128-byte aligned). */
+size_t b200_gdn_workspace_bytes(int B);
 
 /* The same step on the state layout the reference's engine keeps (ReplaySSM, gdn_fused.py:19-57,
  * qk_gdn_verify.cu:61-73,586-593,631-647,706-717,769-781,883-898): a read-only fp32 checkpoint per slot

@@ -56,7 +56,8 @@ def test_argument_checks_return_codes(lib):
     assert lib.b200_moe_max_blocks(256, 10, 512, 128) >= 512 + 20 + 2
     assert lib.b200_moe_w8a8_workspace_bytes(256, 2048, 512, 10) > 256 * 11 * 2048
     assert lib.b200_moe_combine(None, None, None, None, 1, 2048, 10, None, None) == -1
-    assert lib.b200_gdn_verify(*([None] * 11), 1e-6, 1, None, None, None) == -1
+    assert lib.b200_gdn_verify(*([None] * 11), 1e-6, 1, None, None, 0, None, None) == -1
+    assert lib.b200_gdn_workspace_bytes(2) == 2 * (16 * 4096 + 32 * 2240) and lib.b200_gdn_workspace_bytes(0) == 0
     # attention verify: null pointers, bad split count, workspace too small, misaligned cache
     assert lib.b200_attn_verify(*([None] * 6), 8, None, 4, None, 2, 0.0625, 1, None, None, 0, None, None) == -1
     av = [one] * 6 + [8, one, 4, one, 2, 0.0625]
