@@ -303,7 +303,7 @@ def _gdn_entry(dev, ops, synth, timed, st, it, out, hbm, which):
         ops.gdn_verify_replay(r["mixed"], r["z"], r["a"], r["b"], r["conv_state"], r["conv_w"], r["window"], r["a_log"],
                               r["dt_bias"], r["checkpoint"], r["d_ring"], r["dlo_ring"], r["k_ring"], r["klo_ring"],
                               r["g_ring"], sets[i], sets[i], sets[i], r["write_pos"], r["cache_base"], r["norm_w"], 1e-6,
-                              status=st)
+                              status=st, ws=gws)
 
     ms = timed(replay_step, calls=4)
     wp = r["write_pos"].clamp(0, 16).float().mean().item()

@@ -719,7 +719,7 @@ gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
 // coefficients) before and after the one thing that is bound by memory, the 64 KB state tile; the chain, not
 // the bytes, sets its time.  Here gdn_prep_kernel does everything that does not touch the state, once per
 // (sequence, key head): conv + SiLU, norms, gates, window dots and coefficients, and leaves per unit one operand tile
-// [q | k] already in the swizzled layout the tensor core reads plus one 2.2 KB block (conv v, z, coefficients).
+// [q | k] already in the swizzled layout the tensor core reads plus one 2.8 KB block (conv v, z, coefficients).
 // gdn_stream_kernel then only moves state tiles: per unit one barrier for the tile and the two operand blocks
 // (TMA tensor load + two bulk copies), sixteen tf32 MMAs, the per-row epilogue, the in-place update and the
 // tile store.  It is launched with programmatic stream serialization and requests its first tile before
@@ -729,10 +729,15 @@ struct GdnOps {              // per (sequence, value head): one bulk copy
   bf16 v[G_NT][G_D];         // conv v (bf16 values)
   bf16 z[G_NT][G_D];         // gate input
   float cA[G_NT][G_NT], cF[G_NT][G_NT], cE[G_NT], cR[G_NT], cC[G_NT];
-  int n_acc;                 // tokens to advance the state by
-  int pad[3];
+  int n_acc;                 // explicit state: tokens to advance the state by
+  int skip;                  // ring layout: padded request, nothing to do
+  int ring, wp, cb;          // ring layout: ring slot, committed entries (0..16), physical entry of logical entry 0
+  float tdec;                // ring layout: e^{total}
+  int pad[2];
+  float dec[G_RING];         // ring layout: e^{total - pre_c}, 0 past the history
+  float xr[G_RING][8];       // ring layout: ring key c . [q | k], 0 past the history
 };
-static_assert(sizeof(GdnOps) == 2240 && sizeof(GdnOps) % 16 == 0, "GdnOps is copied with one bulk copy");
+static_assert(sizeof(GdnOps) == 2832 && sizeof(GdnOps) % 16 == 0, "GdnOps is copied with one bulk copy");
 constexpr int G_QK_FLOATS = 4 * 8 * 32;  // the operand tile of one (sequence, key head): 4 KB
 
 struct GdnPrepSmem {
@@ -740,8 +745,11 @@ struct GdnPrepSmem {
   float nrm[2][G_NT][4];
   float kk[G_NT][G_NT], kq[G_NT][G_NT];
   float g[2][G_NT], beta[2][G_NT];
+  float xr[G_RING][8];
+  float gr[2][G_RING];
 };
 
+template <bool REPLAY>
 __global__ void __launch_bounds__(512) gdn_prep_kernel(const GdnArgs p, float* __restrict__ qk_ws, GdnOps* __restrict__ ops_ws) {
   __shared__ GdnPrepSmem sm;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -749,10 +757,29 @@ __global__ void __launch_bounds__(512) gdn_prep_kernel(const GdnArgs p, float* _
   const int grp = tid >> 7, c = tid & 127;  // 0: q, 1: k, 2 / 3: v of value head 2 hk / 2 hk + 1
   pdl_wait();
   pdl_launch();
-  int n_acc = p.accepted[b];
-  n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
+  int slot = b, ring = 0, wslot = 0, wp = 0, cb = 0, n_acc = G_NT;
+  if constexpr (REPLAY) {
+    slot = p.state_idx[b];
+    if (slot < 0) {  // padded request: zero rows, and the streaming kernel is told to skip both units
+      if (grp >= 2) {
+        const int hv = 2 * hk + grp - 2;
+#pragma unroll
+        for (int s = 0; s < G_NT; ++s) p.out[(static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv * G_D + c] = f2bf(0.f);
+        if (c == 0) ops_ws[b * G_HV + hv].skip = 1;
+      }
+      return;
+    }
+    ring = p.ring_idx[b];
+    wslot = p.win_idx[b];
+    wp = p.write_pos[ring];
+    cb = p.cache_base[ring];
+    wp = wp < 0 ? 0 : (wp > G_RING ? G_RING : wp);
+  } else {
+    n_acc = p.accepted[b];
+    n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
+  }
   const bf16* mixed_b = p.mixed + static_cast<size_t>(b) * G_NT * G_CONV;
-  bf16* cs_b = p.conv_state + static_cast<size_t>(b) * G_CONV * 3;
+  bf16* cs_b = p.conv_state + static_cast<size_t>(slot) * G_CONV * 3;
   const int hv_mine = 2 * hk + (grp & 1);  // value head of a v thread
   const int ch = grp == 0 ? hk * G_D + c : (grp == 1 ? G_QDIM + hk * G_D + c : 2 * G_QDIM + hv_mine * G_D + c);
   ConvIn in;
@@ -771,7 +798,17 @@ __global__ void __launch_bounds__(512) gdn_prep_kernel(const GdnArgs p, float* _
     const float g = -expf(p.a_log[hv]) * sp;
     sm.g[h][s] = g;
     sm.beta[h][s] = 1.f / (1.f + expf(-bv));
+    if constexpr (REPLAY)
+      if (wp + s < G_RING) p.g_ring[(static_cast<size_t>(ring) * G_HV + hv) * G_RING + ((cb + wp + s) & (G_RING - 1))] = g;
+  } else if (REPLAY && tid >= 32 && tid < 64) {
+    const int h = (tid - 32) >> 4, e = tid & 15;
+    sm.gr[h][e] = e < wp ? p.g_ring[(static_cast<size_t>(ring) * G_HV + 2 * hk + h) * G_RING + ((cb + e) & (G_RING - 1))] : 0.f;
   }
+  uint2 rk = make_uint2(0u, 0u);  // ring layout: warp w multiplies committed key w
+  if constexpr (REPLAY)
+    if (warp < wp)
+      rk = *reinterpret_cast<const uint2*>(p.k_ring + ((static_cast<size_t>(ring) * G_HK + hk) * G_RING +
+                                                       ((cb + warp) & (G_RING - 1))) * G_D + 4 * lane);
   float y[G_NT];
   conv_apply(in, y);
   if (grp < 2) {
@@ -795,6 +832,7 @@ __global__ void __launch_bounds__(512) gdn_prep_kernel(const GdnArgs p, float* _
   }
   // every channel belongs to this CTA alone, and its old conv state is in registers: roll it
   conv_roll(in, cs_b, ch, n_acc);
+  if constexpr (REPLAY) conv_record(in, p.window + static_cast<size_t>(wslot) * G_CONV * 6, ch);
   __syncthreads();
   if (grp < 2) {
     const int sub = c >> 5, chk = (c & 31) >> 2, e = c & 3;
@@ -807,6 +845,14 @@ __global__ void __launch_bounds__(512) gdn_prep_kernel(const GdnArgs p, float* _
       const int row = grp * 4 + s;
       qk[sub * 256 + row * 32 + sw_chunk(row, chk) + e] = val;
       (grp ? sm.k : sm.q)[s][c] = val;
+      if constexpr (REPLAY) {
+        if (grp == 1 && wp + s < G_RING) {  // unit keys join the ring as high and low parts (qk_gdn_verify.cu:586-593)
+          const size_t at = ((static_cast<size_t>(ring) * G_HK + hk) * G_RING + ((cb + wp + s) & (G_RING - 1))) * G_D + c;
+          const bf16 hi = f2bf(val);
+          p.k_ring[at] = hi;
+          p.klo_ring[at] = f2bf(val - bf2f(hi));
+        }
+      }
     }
   }
   __syncthreads();
@@ -823,6 +869,48 @@ __global__ void __launch_bounds__(512) gdn_prep_kernel(const GdnArgs p, float* _
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(FULL_MASK, acc, o);
     if (lane == 0) (d < 16 ? sm.kk : sm.kq)[i][j] = acc;
+  }
+  if constexpr (REPLAY) {
+    // committed ring key `warp` against [q | k] (qk_gdn_verify.cu:597-604,662-671); columns summed over the lanes
+    // by a transposing butterfly (lane l ends with column (l >> 4 & 1) * 4 + (l >> 3 & 1) * 2 + (l >> 2 & 1))
+    if (warp < wp) {
+      const float k0 = bf_lo(rk.x), k1 = bf_hi(rk.x), k2 = bf_lo(rk.y), k3 = bf_hi(rk.y);
+      float acc[8];
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) {
+        const float4 cq = *reinterpret_cast<const float4*>(&sm.q[s][4 * lane]);
+        const float4 ck = *reinterpret_cast<const float4*>(&sm.k[s][4 * lane]);
+        acc[s] = fmaf(k3, cq.w, fmaf(k2, cq.z, fmaf(k1, cq.y, k0 * cq.x)));
+        acc[4 + s] = fmaf(k3, ck.w, fmaf(k2, ck.z, fmaf(k1, ck.y, k0 * ck.x)));
+      }
+      float a4[4], a2[2], a1;
+      {
+        const bool up = lane & 16;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+          const float give = up ? acc[n] : acc[4 + n], keep = up ? acc[4 + n] : acc[n];
+          a4[n] = keep + __shfl_xor_sync(FULL_MASK, give, 16);
+        }
+      }
+      {
+        const bool up = lane & 8;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          const float give = up ? a4[n] : a4[2 + n], keep = up ? a4[2 + n] : a4[n];
+          a2[n] = keep + __shfl_xor_sync(FULL_MASK, give, 8);
+        }
+      }
+      {
+        const bool up = lane & 4;
+        const float give = up ? a2[0] : a2[1], keep = up ? a2[1] : a2[0];
+        a1 = keep + __shfl_xor_sync(FULL_MASK, give, 4);
+      }
+      a1 += __shfl_xor_sync(FULL_MASK, a1, 2);
+      a1 += __shfl_xor_sync(FULL_MASK, a1, 1);
+      if ((lane & 3) == 0) sm.xr[warp][((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = a1;
+    } else if (lane < 8) {
+      sm.xr[warp][lane] = 0.f;
+    }
   }
   __syncthreads();
   if (warp < 2) {
@@ -858,21 +946,49 @@ __global__ void __launch_bounds__(512) gdn_prep_kernel(const GdnArgs p, float* _
       o.cC[s] = s < n_acc ? __expf(Gn - Gs) : 0.f;
     } else if (lane == 20) {
       o.n_acc = n_acc;
+      o.skip = 0;
+      o.ring = ring;
+      o.wp = wp;
+      o.cb = cb;
+      if constexpr (!REPLAY) o.tdec = 1.f;
     }
+  } else if (REPLAY && warp < 4) {
+    // decay of every committed entry up to the window and of the checkpoint (qk_gdn_verify.cu:633-647)
+    GdnOps& o = ops_ws[b * G_HV + 2 * hk + warp - 2];
+    const int e = lane & 15;
+    float pre = sm.gr[warp - 2][e];
+#pragma unroll
+    for (int off = 1; off < G_RING; off <<= 1) {
+      const float n = __shfl_up_sync(FULL_MASK, pre, off, G_RING);
+      if (e >= off) pre += n;
+    }
+    const float total = __shfl_sync(FULL_MASK, pre, G_RING - 1, G_RING);
+    if (lane < G_RING) {
+      o.dec[e] = e < wp ? __expf(total - pre) : 0.f;
+      if (e == 0) o.tdec = __expf(total);
+    }
+  } else if (REPLAY && tid >= 128 && tid < 384) {
+    const int idx = tid - 128, h = idx >> 7, j = idx & 127;
+    ops_ws[b * G_HV + 2 * hk + h].xr[j >> 3][j & 7] = sm.xr[j >> 3][j & 7];
   }
 }
 
 struct GdnStreamSmem {
   float S[4][G_D * 32];   // 64 KB state tile, swizzled sub-tiles (1024-byte aligned)
-  float QK[4][8 * 32];    // operand tile [q | k]; the MMA's rows 8..15 alias what follows
-  GdnOps ops;             // v and z are overwritten by c_i D_i (fp32 [4][128]) for the state update
+  float QK[4][8 * 32];    // operand tile [q | k]; the MMA's rows 8..15 alias what follows.  Ring layout: once the
+                          // MMAs are done, the value head's 16 d entries (bf16 [physical entry][value row])
+  GdnOps ops;             // explicit state: v and z are overwritten by c_i D_i (fp32 [4][128]) for the state update
   float red[4][G_NT];
-  uint64_t bar_tile, bar_ops, bar_mma;
+  uint64_t bar_tile, bar_ops, bar_mma, bar_d;
   uint32_t tmem_slot;
   int abort_flag;
 };
 
-// Explicit-state form.  grid: persistent CTAs, three per SM, unit u = (sequence, value head) = blockIdx.x + i * gridDim.x.
+// Persistent CTAs, three per SM; unit u = (sequence, value head) = blockIdx.x + i * gridDim.x.
+// REPLAY (checkpoint + ring layout): the tile is only read, so the next unit's tile is requested as soon as this
+// unit's MMAs have left the buffer; the d entries are copied over the consumed operand tile; padded requests
+// (ops.skip) use no tile.
+template <bool REPLAY>
 __global__ void __launch_bounds__(G_THREADS, 3)
 gdn_stream_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p, const float* __restrict__ qk_ws,
                   const GdnOps* __restrict__ ops_ws) {
@@ -884,6 +1000,7 @@ gdn_stream_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p, cons
     mbar_init(&sm.bar_tile, 1);
     mbar_init(&sm.bar_ops, 1);
     mbar_init(&sm.bar_mma, 1);
+    mbar_init(&sm.bar_d, 1);
     sm.abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmS);
@@ -895,31 +1012,57 @@ gdn_stream_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p, cons
   const uint32_t tmem_base = sm.tmem_slot;
   G_TRACE(9, 0);
   int unit_no = 0;
-  auto request_tile = [&](int u) {
+  // thread 0 keeps the phases it has armed and not yet seen complete (-1: none), for the wind-down after an
+  // abandoned wait
+  int pend_tile = -1, pend_ops = -1, pend_d = -1;
+  uint32_t par_t = 0, par_o = 0, par_d = 0;  // phases of bar_tile (and bar_mma), bar_ops, bar_d of the current unit
+  auto request_tile = [&](int u, int slot, uint32_t phase) {  // first state row of the unit: (slot * 32 + head) * 128
     mbar_expect_tx(&sm.bar_tile, G_TILE_BYTES);
 #pragma unroll
-    for (int sub = 0; sub < 4; ++sub) tma_load_2d(sm.S[sub], &tmS, 32 * sub, u * G_D, &sm.bar_tile);
+    for (int sub = 0; sub < 4; ++sub) tma_load_2d(sm.S[sub], &tmS, 32 * sub, (slot * G_HV + (u & 31)) * G_D, &sm.bar_tile);
+    pend_tile = static_cast<int>(phase);
   };
-  auto request_ops = [&](int u) {
+  auto request_ops = [&](int u, uint32_t phase) {
     mbar_expect_tx(&sm.bar_ops, G_QK_FLOATS * 4 + sizeof(GdnOps));
     bulk_load(sm.QK, qk_ws + static_cast<size_t>(u >> 1) * G_QK_FLOATS, G_QK_FLOATS * 4, &sm.bar_ops);
     bulk_load(&sm.ops, ops_ws + u, sizeof(GdnOps), &sm.bar_ops);
+    pend_ops = static_cast<int>(phase);
   };
   // the first tile does not depend on the operand kernel: it travels while that kernel runs
-  if (tid == 0 && blockIdx.x < nunits) request_tile(blockIdx.x);
+  int nslot = -1;  // thread 0: state slot of the unit whose tile is requested next
+  if (tid == 0 && blockIdx.x < nunits) {
+    nslot = REPLAY ? p.state_idx[blockIdx.x >> 5] : static_cast<int>(blockIdx.x >> 5);
+    if (nslot >= 0) request_tile(blockIdx.x, nslot, 0);
+  }
   pdl_wait();
-  if (tid == 0 && blockIdx.x < nunits) request_ops(blockIdx.x);
+  if (tid == 0 && blockIdx.x < nunits) request_ops(blockIdx.x, 0);
   bool ok = true;
-  uint32_t par = 0;
-  for (int u = blockIdx.x; u < nunits; u += gridDim.x, par ^= 1u) {
+  for (int u = blockIdx.x; u < nunits; u += gridDim.x, par_o ^= 1u) {
     const int b = u >> 5, hv = u & 31;
+    const int un = u + gridDim.x;  // this CTA's next unit
     G_TRACE(0, unit_no);
+    if (tid == 0) nslot = un < nunits ? (REPLAY ? p.state_idx[un >> 5] : (un >> 5)) : -1;  // consumed much later
+    if constexpr (REPLAY) {
+      ok = mbar_wait(&sm.bar_ops, par_o, &sm.abort_flag, p.status, ST_WAIT_FULL);
+      ok = __syncthreads_and(ok);
+      if (!ok) break;
+      if (tid == 0) pend_ops = -1;
+      if (sm.ops.skip) {  // padded request: the operand kernel has zeroed its rows; no tile was requested
+        __syncthreads();  // every thread has read the flag
+        if (tid == 0 && un < nunits) {
+          request_ops(un, par_o ^ 1u);
+          if (nslot >= 0) request_tile(un, nslot, par_t);
+        }
+        continue;
+      }
+    }
     // ---- S [q | k]: sixteen tf32 MMAs (M = 128 state rows, N = 16, K = 8 each) into 16 TMEM columns ----
     if (tid == 0) {
-      const bool landed = mbar_wait(&sm.bar_tile, par, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
-                          mbar_wait(&sm.bar_ops, par, &sm.abort_flag, p.status, ST_WAIT_FULL);
+      const bool landed = mbar_wait(&sm.bar_tile, par_t, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
+                          mbar_wait(&sm.bar_ops, par_o, &sm.abort_flag, p.status, ST_WAIT_FULL);
       G_TRACE(1, unit_no);
       if (landed) {
+        pend_tile = pend_ops = -1;
         tc_fence_after();
         const uint32_t idesc = umma_idesc(UMMA_C_F32, UMMA_AB_TF32, 16);
 #pragma unroll
@@ -931,14 +1074,28 @@ gdn_stream_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p, cons
         tc_commit(&sm.bar_mma);
       }
     }
-    ok = mbar_wait(&sm.bar_ops, par, &sm.abort_flag, p.status, ST_WAIT_FULL) &&
-         mbar_wait(&sm.bar_tile, par, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
-         mbar_wait(&sm.bar_mma, par, &sm.abort_flag, p.status, ST_WAIT_TMEM_FULL);
+    ok = mbar_wait(&sm.bar_ops, par_o, &sm.abort_flag, p.status, ST_WAIT_FULL) &&
+         mbar_wait(&sm.bar_tile, par_t, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
+         mbar_wait(&sm.bar_mma, par_t, &sm.abort_flag, p.status, ST_WAIT_TMEM_FULL);
     ok = __syncthreads_and(ok);  // one verdict for the CTA
-    if (!ok) break;             // `par` still names the phases this unit armed
+    if (!ok) break;
     tc_fence_after();
     G_TRACE(2, unit_no);
     const int n_acc = sm.ops.n_acc;
+    if constexpr (REPLAY) {
+      // the MMAs were the only readers of the tile and of the operand tile: the d entries of the value head (4 KB,
+      // physical order) land on the operand tile, and the next unit's checkpoint tile may travel
+      if (tid == 0) {
+        mbar_expect_tx(&sm.bar_d, G_RING * G_D * 2);
+        bulk_load(sm.QK, p.d_ring + (static_cast<size_t>(sm.ops.ring) * G_HV + hv) * G_RING * G_D, G_RING * G_D * 2, &sm.bar_d);
+        pend_d = static_cast<int>(par_d);
+        if (nslot >= 0) request_tile(un, nslot, par_t ^ 1u);
+      }
+      ok = mbar_wait(&sm.bar_d, par_d, &sm.abort_flag, p.status, ST_WAIT_FULL);
+      ok = __syncthreads_and(ok);
+      if (!ok) break;
+      if (tid == 0) pend_d = -1;
+    }
     // ---- per value row: R, D = (I + A)^-1 R, outputs; gated RMSNorm ----
     float o[G_NT] = {0.f, 0.f, 0.f, 0.f}, zz[G_NT] = {0.f, 0.f, 0.f, 0.f}, cd[G_NT] = {0.f, 0.f, 0.f, 0.f};
     if (tid < G_D) {
@@ -946,11 +1103,39 @@ gdn_stream_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p, cons
       uint32_t hr[16];
       tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16), hr);  // warps 0..3 own TMEM lane quadrants 0..3
       tmem_ld_wait();
+      float hq[G_NT], hk_[G_NT];
+#pragma unroll
+      for (int s = 0; s < G_NT; ++s) {
+        hq[s] = __uint_as_float(hr[s]);
+        hk_[s] = __uint_as_float(hr[4 + s]);
+      }
+      if constexpr (REPLAY) {
+        // S x = e^{total} H0 x + sum_c (d_c e^{total - pre_c}) (k_c . x)   (qk_gdn_verify.cu:706-742)
+        const bf16* dsm = reinterpret_cast<const bf16*>(&sm.QK[0][0]);
+        const int wp = sm.ops.wp, cb = sm.ops.cb;
+        float aq[G_NT] = {0.f, 0.f, 0.f, 0.f}, ak[G_NT] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int e = 0; e < wp; ++e) {
+          const float dsc = bf2f(dsm[((cb + e) & (G_RING - 1)) * G_D + v]) * sm.ops.dec[e];
+          const float4 xq = *reinterpret_cast<const float4*>(&sm.ops.xr[e][0]);
+          const float4 xk = *reinterpret_cast<const float4*>(&sm.ops.xr[e][4]);
+          aq[0] = fmaf(dsc, xq.x, aq[0]); aq[1] = fmaf(dsc, xq.y, aq[1]);
+          aq[2] = fmaf(dsc, xq.z, aq[2]); aq[3] = fmaf(dsc, xq.w, aq[3]);
+          ak[0] = fmaf(dsc, xk.x, ak[0]); ak[1] = fmaf(dsc, xk.y, ak[1]);
+          ak[2] = fmaf(dsc, xk.z, ak[2]); ak[3] = fmaf(dsc, xk.w, ak[3]);
+        }
+        const float td = sm.ops.tdec;
+#pragma unroll
+        for (int s = 0; s < G_NT; ++s) {
+          hq[s] = fmaf(td, hq[s], aq[s]);
+          hk_[s] = fmaf(td, hk_[s], ak[s]);
+        }
+      }
       float R[G_NT], D[G_NT];
 #pragma unroll
       for (int s = 0; s < G_NT; ++s) {
         zz[s] = bf2f(sm.ops.z[s][v]);
-        R[s] = sm.ops.cR[s] * (bf2f(sm.ops.v[s][v]) - sm.ops.cE[s] * __uint_as_float(hr[4 + s]));
+        R[s] = sm.ops.cR[s] * (bf2f(sm.ops.v[s][v]) - sm.ops.cE[s] * hk_[s]);
       }
 #pragma unroll
       for (int i = 0; i < G_NT; ++i) {
@@ -961,11 +1146,24 @@ gdn_stream_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p, cons
       }
 #pragma unroll
       for (int s = 0; s < G_NT; ++s) {
-        float acc = sm.ops.cE[s] * __uint_as_float(hr[s]);
+        float acc = sm.ops.cE[s] * hq[s];
 #pragma unroll
         for (int i = 0; i <= s; ++i) acc = fmaf(D[i], sm.ops.cF[i][s], acc);
         o[s] = rbf(acc);  // the core output is stored in bf16 before the norm (qk_gdn_verify.cu:761)
         cd[s] = D[s] * sm.ops.cC[s];
+      }
+      if constexpr (REPLAY) {
+        // the window's D join the ring as bf16 high and low parts (qk_gdn_verify.cu:769-781)
+        const int wp = sm.ops.wp, cb = sm.ops.cb;
+        const size_t base = (static_cast<size_t>(sm.ops.ring) * G_HV + hv) * G_RING * G_D + v;
+#pragma unroll
+        for (int s = 0; s < G_NT; ++s)
+          if (wp + s < G_RING) {
+            const size_t at = base + static_cast<size_t>((cb + wp + s) & (G_RING - 1)) * G_D;
+            const bf16 hi = f2bf(D[s]);
+            p.d_ring[at] = hi;
+            p.dlo_ring[at] = f2bf(D[s] - bf2f(hi));
+          }
       }
       float ss[G_NT];
 #pragma unroll
@@ -990,13 +1188,12 @@ gdn_stream_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p, cons
         const float rstd = rsqrtf(var + p.eps);
         p.out[(static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv * G_D + tid] =
             f2bf(o[s] * rstd * nw * (zz[s] * (1.f / (1.f + __expf(-zz[s])))));
-        cdsm[s * G_D + tid] = cd[s];
+        if constexpr (!REPLAY) cdsm[s * G_D + tid] = cd[s];
       }
     }
-    const int un = u + gridDim.x;  // this CTA's next unit
     G_TRACE(4, unit_no);
     // ---- state after n_acc tokens, in place in the swizzled tile, then four TMA tensor stores ----
-    if (n_acc > 0) {
+    if (!REPLAY && n_acc > 0) {
       __syncthreads();  // c_i D_i visible
       const int rg = tid >> 3, ks = tid & 7;  // thread = 4 state rows x one 16-byte chunk position of each sub-tile row
       const float decay = sm.ops.cE[n_acc - 1];
@@ -1033,28 +1230,34 @@ gdn_stream_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p, cons
           bulk_commit();
         }
       }
-      // the operand blocks are free: the next unit's may travel while the tile leaves
       G_TRACE(5, unit_no);
+      // the operand blocks are free: the next unit's may travel while the tile leaves
       if (tid == 0 && un < nunits) {
-        request_ops(un);
+        request_ops(un, par_o ^ 1u);
         bulk_wait_read_all();  // the tile has left shared memory
-        request_tile(un);
+        request_tile(un, nslot, par_t ^ 1u);
       }
       G_TRACE(6, unit_no);
     } else {
-      __syncthreads();  // every thread is done with the operand blocks and the tile
+      __syncthreads();  // every thread is done with the operand blocks (and, explicit state, with the tile)
       if (tid == 0 && un < nunits) {
-        request_ops(un);
-        request_tile(un);
+        request_ops(un, par_o ^ 1u);
+        if constexpr (!REPLAY) request_tile(un, nslot, par_t ^ 1u);
       }
     }
+    par_t ^= 1u;
+    par_d ^= 1u;
     ++unit_no;
   }
   G_TRACE(9, 1);
   if (!ok && tid == 0) {
     // an abandoned wait: give the copies in flight a bounded grace period before the CTA's memory goes away
     const unsigned long long t0 = globaltimer();
-    while (!(mbar_try(&sm.bar_tile, par) && mbar_try(&sm.bar_ops, par)) && globaltimer() - t0 < 20000000ull) {
+    while (globaltimer() - t0 < 20000000ull) {
+      if (pend_tile >= 0 && mbar_try(&sm.bar_tile, static_cast<uint32_t>(pend_tile))) pend_tile = -1;
+      if (pend_ops >= 0 && mbar_try(&sm.bar_ops, static_cast<uint32_t>(pend_ops))) pend_ops = -1;
+      if (pend_d >= 0 && mbar_try(&sm.bar_d, static_cast<uint32_t>(pend_d))) pend_d = -1;
+      if (pend_tile < 0 && pend_ops < 0 && pend_d < 0) break;
     }
   }
   if (tid == 0) bulk_wait_read_all();  // the last tile has left shared memory; the writes complete with the grid
@@ -1127,14 +1330,14 @@ extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, 
     const int ssmem = static_cast<int>(sizeof(GdnStreamSmem)) + 1024;
     static bool sattr_done[64] = {false};
     if (dev >= 0 && dev < 64 && !sattr_done[dev]) {
-      cudaFuncSetAttribute(gdn_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ssmem);
+      cudaFuncSetAttribute(gdn_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ssmem);
       sattr_done[dev] = true;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    launch_k(gdn_prep_kernel, dim3(B * G_HK), dim3(512), 0, st, p, qk_ws, ops_ws);
+    launch_k(gdn_prep_kernel<false>, dim3(B * G_HK), dim3(512), 0, st, p, qk_ws, ops_ws);
     int grid = sm_count() * 3;
     if (grid > B * G_HV) grid = B * G_HV;
-    launch_k(gdn_stream_kernel, dim3(grid), dim3(G_THREADS), static_cast<size_t>(ssmem), st, tmS, p,
+    launch_k(gdn_stream_kernel<false>, dim3(grid), dim3(G_THREADS), static_cast<size_t>(ssmem), st, tmS, p,
              static_cast<const float*>(qk_ws), static_cast<const GdnOps*>(ops_ws));
     return launch_status("b200_gdn_verify");
   }
@@ -1157,7 +1360,7 @@ extern "C" int b200_gdn_verify_replay(const void* mixed, const void* z, const vo
                                       void* k_ring, void* klo_ring, float* g_ring, const int32_t* state_idx,
                                       const int32_t* ring_idx, const int32_t* win_idx, const int32_t* write_pos,
                                       const int32_t* cache_base, const void* norm_w, float eps, int B, void* out,
-                                      int32_t* status, void* stream) {
+                                      void* ws, size_t ws_bytes, int32_t* status, void* stream) {
   if (!mixed || !z || !a || !b || !conv_state || !conv_w || !window || !a_log || !dt_bias || !checkpoint || !d_ring ||
       !dlo_ring || !k_ring || !klo_ring || !g_ring || !state_idx || !ring_idx || !win_idx || !write_pos || !cache_base ||
       !norm_w || !out)
@@ -1201,10 +1404,32 @@ extern "C" int b200_gdn_verify_replay(const void* mixed, const void* z, const vo
   if (int rc = make_tmap_f32_2d(&tmS, const_cast<float*>(checkpoint), static_cast<uint64_t>(state_slots) * G_HV * G_D, G_D,
                                 G_D, "gdn checkpoint"))
     return rc;
-  const int smem = static_cast<int>(sizeof(GdnSmem)) + 1024;
-  static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
+  if (!gdn_single_kernel()) {
+    if (!ws || ws_bytes < b200_gdn_workspace_bytes(B))
+      return fail(B200_E_WS, "b200_gdn_verify_replay: workspace of %zu bytes needed, %zu given", b200_gdn_workspace_bytes(B),
+                  ws_bytes);
+    if (reinterpret_cast<uintptr_t>(ws) & 127)
+      return fail(B200_E_ALIGN, "b200_gdn_verify_replay: workspace must be 128-byte aligned");
+    float* qk_ws = static_cast<float*>(ws);
+    GdnOps* ops_ws = reinterpret_cast<GdnOps*>(qk_ws + static_cast<size_t>(B) * G_HK * G_QK_FLOATS);
+    const int ssmem = static_cast<int>(sizeof(GdnStreamSmem)) + 1024;
+    static bool sattr_done[64] = {false};
+    if (dev >= 0 && dev < 64 && !sattr_done[dev]) {
+      cudaFuncSetAttribute(gdn_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ssmem);
+      sattr_done[dev] = true;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    launch_k(gdn_prep_kernel<true>, dim3(B * G_HK), dim3(512), 0, st, p, qk_ws, ops_ws);
+    int grid = sm_count() * 3;
+    if (grid > B * G_HV) grid = B * G_HV;
+    launch_k(gdn_stream_kernel<true>, dim3(grid), dim3(G_THREADS), static_cast<size_t>(ssmem), st, tmS, p,
+             static_cast<const float*>(qk_ws), static_cast<const GdnOps*>(ops_ws));
+    return launch_status("b200_gdn_verify_replay");
+  }
+  const int smem = static_cast<int>(sizeof(GdnSmem)) + 1024;
+  static bool attr_done[64] = {false};
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
     cudaFuncSetAttribute(gdn_verify_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     attr_done[dev] = true;

@@ -151,12 +151,13 @@ class DecodeStep:
                     core = ops.gdn_verify_replay(mixed, z, a, b, L["conv_state"], L["conv_w"], L["window"], L["a_log"],
                                                  L["dt_bias"], L["state"], L["d_ring"], L["dlo_ring"], L["k_ring"],
                                                  L["klo_ring"], L["g_ring"], self.slots, self.slots, self.slots,
-                                                 self.write_pos, self.cache_base, L["gdn_norm"], 1e-6, status=st)
+                                                 self.write_pos, self.cache_base, L["gdn_norm"], 1e-6, status=st,
+                                                 ws=self.gdn_ws)
                 else:
                     core = ops.gdn_verify(mixed, z, a, b, L["conv_state"], L["conv_w"], L["a_log"], L["dt_bias"], L["state"],
                                           self.accepted, L["gdn_norm"], 1e-6, status=st, ws=self.gdn_ws)
                 proj = ops.dense_fp8(core, L["out_w"], L["out_s"], status=st)
-                n += 2 + (1 if self.gdn_layout == "ring" else 2) + 2
+                n += 2 + 2 + 2
             h2 = ops.add_rmsnorm(proj, residual, L["post_norm"])
             ops.router(h2, L["wr"], K, None, scratch=self.scratch, want_logits=False, ids=self.ids, wts=self.wts)
             ops.build_lists(self.ids, self.wts, self.lists)

@@ -411,7 +411,7 @@ def gdn_verify(mixed, z, a, b, conv_state, conv_w, a_log, dt_bias, state, accept
 
 def gdn_verify_replay(mixed, z, a, b, conv_state, conv_w, window, a_log, dt_bias, checkpoint, d_ring, dlo_ring, k_ring,
                       klo_ring, g_ring, state_idx, ring_idx, win_idx, write_pos, cache_base, norm_w, eps=1e-6,
-                      out=None, status=None):
+                      out=None, status=None, ws=None):
     """Gated DeltaNet verify on the checkpoint + (d, k, g) ring state layout (reference:
     qk_gdn_verify.gdn_verify_fused, gdn_fused.py:37-57): reads the checkpoint and the committed ring
     entries, appends this window's entries, rolls `conv_state` and records the draft windows in place.
@@ -437,9 +437,11 @@ def gdn_verify_replay(mixed, z, a, b, conv_state, conv_w, window, a_log, dt_bias
         raise B200Error("gdn_verify_replay: unexpected shapes")
     if out is None:
         out = torch.empty(B * 4, 4096, dtype=torch.bfloat16, device=mixed.device)
+    if ws is None:
+        ws = gdn_workspace(B, mixed.device)
     check(_lib.lib().b200_gdn_verify_replay(
         _p(mixed), _p(z), _p(a), _p(b), _p(conv_state), _p(conv_w), _p(window), _p(a_log), _p(dt_bias), _p(checkpoint),
         slots, _p(d_ring), _p(dlo_ring), _p(k_ring), _p(klo_ring), _p(g_ring), _p(state_idx), _p(ring_idx), _p(win_idx),
-        _p(write_pos), _p(cache_base), _p(norm_w), float(eps), B, _p(out), _p(status), _stream()),
+        _p(write_pos), _p(cache_base), _p(norm_w), float(eps), B, _p(out), _p(ws), ws.numel(), _p(status), _stream()),
         "b200_gdn_verify_replay")
     return out

@@ -251,13 +251,14 @@ size_t b200_gdn_workspace_bytes(int B);
  *   window bf16 [window slots, 8192, 6]; d_ring, dlo_ring bf16 [ring slots, 32, 16, 128];
  *   k_ring, klo_ring bf16 [ring slots, 16, 16, 128]; g_ring fp32 [ring slots, 32, 16];
  *   state_idx, ring_idx, win_idx int32 [B]; write_pos, cache_base int32 [ring slots];
- *   the other arguments as above.  Requests of one call must not share a slot. */
+ *   the other arguments as above (ws: b200_gdn_workspace_bytes(B)).  Requests of one call must not share a slot. */
 int b200_gdn_verify_replay(const void* mixed, const void* z, const void* a, const void* b, void* conv_state,
                            const void* conv_w, void* window, const float* a_log, const float* dt_bias,
                            const float* checkpoint, int state_slots, void* d_ring, void* dlo_ring, void* k_ring,
                            void* klo_ring, float* g_ring, const int32_t* state_idx, const int32_t* ring_idx,
                            const int32_t* win_idx, const int32_t* write_pos, const int32_t* cache_base,
-                           const void* norm_w, float eps, int B, void* out, int32_t* status, void* stream);
+                           const void* norm_w, float eps, int B, void* out, void* ws, size_t ws_bytes,
+                           int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Attention verify core.  Replaces qk_attn_verify.attn_verify_fused (attn_fused.py:110-124;

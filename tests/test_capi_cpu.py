@@ -57,7 +57,7 @@ def test_argument_checks_return_codes(lib):
     assert lib.b200_moe_w8a8_workspace_bytes(256, 2048, 512, 10) > 256 * 11 * 2048
     assert lib.b200_moe_combine(None, None, None, None, 1, 2048, 10, None, None) == -1
     assert lib.b200_gdn_verify(*([None] * 11), 1e-6, 1, None, None, 0, None, None) == -1
-    assert lib.b200_gdn_workspace_bytes(2) == 2 * (16 * 4096 + 32 * 2240) and lib.b200_gdn_workspace_bytes(0) == 0
+    assert lib.b200_gdn_workspace_bytes(2) == 2 * (16 * 4096 + 32 * 2832) and lib.b200_gdn_workspace_bytes(0) == 0
     # attention verify: null pointers, bad split count, workspace too small, misaligned cache
     assert lib.b200_attn_verify(*([None] * 6), 8, None, 4, None, 2, 0.0625, 1, None, None, 0, None, None) == -1
     av = [one] * 6 + [8, one, 4, one, 2, 0.0625]
@@ -70,11 +70,11 @@ def test_argument_checks_return_codes(lib):
     assert lib.b200_moe_combine_norm(None, None, None, None, 1, 2048, 10, None, None, None, 1e-6, None, None) == -1
     assert lib.b200_moe_combine_norm(one, one, None, None, 1, 2047, 10, None, one, one, 1e-6, one, None) == -1
     # GDN verify on the ring layout: null pointers, slot count out of range, misaligned checkpoint
-    assert lib.b200_gdn_verify_replay(*([None] * 10), 4, *([None] * 11), 1e-6, 1, None, None, None) == -1
+    assert lib.b200_gdn_verify_replay(*([None] * 10), 4, *([None] * 11), 1e-6, 1, None, None, 0, None, None) == -1
     ok = [one] * 10
-    assert lib.b200_gdn_verify_replay(*ok, 0, *([one] * 11), 1e-6, 1, one, None, None) == -1
+    assert lib.b200_gdn_verify_replay(*ok, 0, *([one] * 11), 1e-6, 1, one, one, 1 << 30, None, None) == -1
     mis = [one] * 9 + [C.c_void_p(4100)]
-    assert lib.b200_gdn_verify_replay(*mis, 4, *([one] * 11), 1e-6, 1, one, None, None) == -2
+    assert lib.b200_gdn_verify_replay(*mis, 4, *([one] * 11), 1e-6, 1, one, one, 1 << 30, None, None) == -2
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
