@@ -1,10 +1,8 @@
 // Gated DeltaNet speculative verify: conv + SiLU, q/k L2 norm, gates, delta-rule recurrence over
-// the 4 draft tokens in closed form, gated RMSNorm, and the explicit state / conv-state write-back
-// at the accepted length.
+// the 4 draft tokens in closed form, gated RMSNorm; then either the explicit state / conv-state write-back
+// at the accepted length, or the appends to the reference engine's (d, k, g) ring.
 //
-// Replaces qk_gdn_verify.cu:293 gdn_verify_kernel (host glue gdn_fused.py:37-57).  The reference
-// keeps a read-only fp32 checkpoint plus a (d, k, g) ring; the target carries the state explicitly,
-// so a unit reads its 128 x 128 fp32 tile, and writes it back advanced by accepted[b] tokens.
+// Replaces qk_gdn_verify.cu:293 gdn_verify_kernel (host glue gdn_fused.py:37-57).
 // The window algebra is the reference's (qk_gdn_verify.cu:633-762):
 //   hq_s = S q_s, hk_s = S k_s;  R_s = beta_s (v_s - e^{G_s} hk_s);  D = (I + A)^-1 R with
 //   A_ij = beta_i e^{G_i - G_j} k_i.k_j (i > j);  o_s = e^{G_s} hq_s + sum_{i<=s} D_i e^{G_s - G_i} k_i.q_s;
@@ -13,25 +11,30 @@
 // from the swizzled state tile in shared memory, accumulators in TMEM), the reference's precision for
 // these dots (TF32 mma.sync, qk_gdn_verify.cu:173-179); everything else is fp32.
 //
-// HBM-bound: 64 KB in and (when accepted > 0) 64 KB out per (sequence, value head).  One CTA per
-// unit; the tile moves by TMA tensor copies each way (128-byte swizzle, the layout the MMA reads),
-// three CTAs share an SM so the copies of one overlap the arithmetic of the others; the CTAs are persistent
-// and walk the units.  The two value heads of a key head run as a 2-CTA cluster: both read the q/k conv
-// state, meet at a cluster barrier, then rank 0 rolls it.
+// Two state layouts (template parameter REPLAY of both kernels):
+//  * explicit state (b200_gdn_verify): a unit reads its 128 x 128 fp32 tile and writes it back advanced by
+//    accepted[b] tokens: 64 KB in and (when accepted > 0) 64 KB out per (sequence, value head);
+//  * the layout the reference's engine hands its kernel (b200_gdn_verify_replay; qk_gdn_verify.cu:61-73,
+//    586-593,631-647,706-717,769-781): a read-only fp32 checkpoint H0 per slot plus a 16-entry circular ring
+//    of (d, k, g) per request, of which the first write_pos logical entries (physical entry
+//    (cache_base + c) & 15) are committed.  The state the window sees is
+//      S = e^{total} H0 + sum_c e^{total - pre_c} d_c k_c^T,   pre_c = g_0 + .. + g_c, total = pre_{wp-1},
+//    so S x = e^{total} (H0 x) + sum_c e^{total - pre_c} d_c (k_c . x): the H0 products run on the tensor core,
+//    the ring keys' dots against [q | k] on the CUDA cores.  Nothing is written to the checkpoint: the
+//    window's D_s, unit keys and gates are appended to the ring as bf16 high and low parts (g in fp32) at
+//    logical entries write_pos + s (those below 16), the conv state is rolled by the whole window and the
+//    per-draft windows are recorded as [s1 s2 x0 x1 x2 x3] per channel; which of it survives is the engine's
+//    move of the ring cursor.
 //
-// The same kernel has a second form (REPLAY) for the state layout the reference's engine hands its kernel
-// (qk_gdn_verify.cu:61-73,586-593,631-647,706-717,769-781): a read-only fp32 checkpoint H0 per slot plus a
-// 16-entry circular ring of (d, k, g) per request, of which the first write_pos logical entries (physical
-// entry (cache_base + c) & 15) are committed.  The state the window sees is
-//   S = e^{total} H0 + sum_c e^{total - pre_c} d_c k_c^T,   pre_c = g_0 + .. + g_c, total = pre_{wp-1},
-// so S x = e^{total} (H0 x) + sum_c e^{total - pre_c} d_c (k_c . x): the H0 products run on the tensor core as
-// before, the ring keys' dots against [q | k] on the CUDA cores.  Nothing is written to the checkpoint: the
-// window's D_s, unit keys and gates are appended to the ring as bf16 high and low parts (g in fp32) at
-// logical entries write_pos + s (those below 16), the conv state is rolled by the whole window and the
-// per-draft windows are recorded as [s1 s2 x0 x1 x2 x3] per channel; which of it survives is the engine's
-// move of the ring cursor.
-#include <cstdlib>
-
+// Two launches.  Only the state tile is bound by memory; everything else of a unit is a chain of dependent
+// steps (input loads, conv, norms, barriers, dots, coefficients).  gdn_prep_kernel does all of that, once
+// per (sequence, key head): conv + SiLU, norms, gates, window dots and coefficients, the conv-state roll (and,
+// for the ring layout, the ring key dots, decay factors, ring appends and the window record), and leaves per
+// key head one operand tile [q | k] already in the swizzled layout the tensor core reads plus, per value head,
+// one 2.8 KB block (conv v, z, coefficients).  gdn_stream_kernel then only moves state tiles: per unit one TMA
+// tensor load and two bulk copies, sixteen tf32 MMAs, the per-row epilogue, and for the explicit state the
+// in-place update and the tile store.  It is launched with programmatic stream serialization and requests its
+// first tile before waiting for the operand kernel, since the tile does not depend on it.
 #include "common.cuh"
 #include "host.h"
 
@@ -45,38 +48,7 @@ constexpr int G_THREADS = 256;
 constexpr int G_RING = 16;                     // ReplaySSM ring entries per request
 constexpr uint32_t G_TILE_BYTES = G_D * G_D * 4;
 
-// Shared memory of one unit.  S holds the state tile as four 128-row x 32-float sub-tiles in the
-// 128-byte-swizzled K-major layout that both TMA (tensor loads / stores) and the tensor core (A operand
-// of the tf32 MMA) use: element (v, k) lives at sub-tile k / 32, row v, 16-byte chunk ((k % 32) / 4) ^
-// (v & 7).  QK holds [q_0..q_3 | k_0..k_3] as the B operand in the same layout with 8 rows per
-// sub-tile; the MMA reads 16 rows (N = 16 is the smallest N for M = 128): rows 8..15 alias the next
-// kilobyte and only feed accumulator columns nobody reads.
-struct GdnSmem {
-  float S[4][G_D * 32];     // 64 KB, 1024-byte aligned
-  float QK[4][8 * 32];      // 4 KB
-  float k[G_NT][G_D];       // normalised k, plain layout (state update, k.k / k.q dots); also the alias pad of QK
-  float v[G_NT][G_D];       // conv v; later c_i * D_i for the state update
-  float kk[G_NT][G_NT], kq[G_NT][G_NT];
-  float g[G_NT], beta[G_NT], G[G_NT];
-  float cA[G_NT][G_NT];     // beta_i e^{G_i - G_j} k_i.k_j   (i > j)
-  float cF[G_NT][G_NT];     // e^{G_s - G_i} k_i.q_s          (i <= s), indexed [i][s]
-  float cE[G_NT], cR[G_NT], cC[G_NT];  // e^{G_s}; beta_s; e^{G_{n-1} - G_i} for i < n_acc else 0
-  float red[8][G_NT];
-  float nrm[2][G_NT][4];
-  float xr[G_RING][8];      // REPLAY: ring key c . [q | k]
-  float gr[G_RING];         // REPLAY: committed g in logical order (0 past the history)
-  float dec[G_RING];        // REPLAY: e^{total - pre_c} (0 past the history)
-  float tdec;               // REPLAY: e^{total}
-  int nx[5];                // REPLAY: the next unit's state slot, ring slot, window slot, write position, ring base
-  uint64_t bar_load, bar_mma;
-  uint32_t tmem_slot;
-  int abort_flag;
-};
 __device__ __forceinline__ int sw_chunk(int row, int chunk) { return (chunk ^ (row & 7)) << 2; }  // float offset in a 32-float row
-
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
 
 // One conv channel: window [s0 s1 s2 x0..x3] and the four taps, loaded up front so that every global
 // load of the prologue is in flight at once.
@@ -131,11 +103,6 @@ __device__ __forceinline__ void conv_record(const ConvIn& in, bf16* __restrict__
              (static_cast<uint32_t>(__bfloat16_as_ushort(in.win[2 + 2 * i])) << 16);
 }
 
-__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
 struct GdnArgs {
   const bf16* mixed;
   const bf16* z;
@@ -166,565 +133,16 @@ struct GdnArgs {
   const int32_t* cache_base;  // [ring slots] physical entry of logical entry 0
 };
 
-// Optional timeline of CTA 0 (compile with -DB200_TRACE): %globaltimer stamps of thread 0 per unit at: 0 unit start,
-// 1 inputs consumed (conv done), 2 operand tile built and conv state rolled, 3 MMAs issued, 4 window dots done,
-// 5 coefficients done, 6 MMAs complete, 7 outputs reduced, 8 unit end; row 9: kernel start and end.
+// Optional timeline of the streaming kernel's CTA 0 (compile with -DB200_TRACE): %globaltimer stamps of thread 0 per
+// unit at: 0 unit start, 1 tile and operands landed, 2 MMAs complete, 3 epilogue done, 4 outputs stored, 5 state
+// updated and stores issued, 6 next unit requested; row 9: kernel start and end.
 #ifdef B200_TRACE
 __device__ unsigned long long g_gdn_trace[16][8];
 #define G_TRACE(k, i) do { if (blockIdx.x == 0 && threadIdx.x == 0 && (i) < 8) g_gdn_trace[k][i] = globaltimer(); } while (0)
-#define G_TRACE_W(k, i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (i) < 8) g_gdn_trace[k][i] = globaltimer(); } while (0)
 #else
 #define G_TRACE(k, i) do { } while (0)
-#define G_TRACE_W(k, i) do { } while (0)
 #endif
 
-template <bool REPLAY>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 3)
-gdn_verify_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p) {
-  extern __shared__ uint8_t smem_raw[];
-  GdnSmem& sm = *reinterpret_cast<GdnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // Persistent clusters: cluster c takes (sequence, key head) pairs c, c + #clusters, ...; its two CTAs take the
-  // pair's two value heads.  A unit's prologue (conv inputs, gates, norms: global round trips) then runs while the
-  // previous unit's state tile is still leaving shared memory, and no wave of CTAs waits for the slowest of
-  // the wave before.
-  const int rank = blockIdx.x & 1, ncl = gridDim.x >> 1, npairs = p.B * G_HK;
-
-  if (tid == 0) {
-    mbar_init(&sm.bar_load, 1);
-    mbar_init(&sm.bar_mma, 1);
-    sm.abort_flag = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&tmS);
-  }
-  if (warp == 0) tmem_alloc(&sm.tmem_slot, 32);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = sm.tmem_slot;
-  G_TRACE(9, 0);
-  int unit_no = 0;
-  bool ok = true;
-  uint32_t par = 0;  // parity of this unit's phase of both mbarriers
-  // REPLAY: the slot indices and ring cursors of a unit are fetched one unit ahead, so that no unit starts with a
-  // chain of dependent global loads, and its checkpoint tile is requested as soon as the previous unit's MMAs
-  // have left the (never written) tile buffer
-  // (asynchronous copies by the last thread into shared memory: a register would be spilled while its load is in
-  // flight, which is a wait)
-  bool tile_requested = false;  // thread 0: this unit's tile was requested during the previous unit
-  auto idx_level1 = [&](int nb) {
-    cp_async4(&sm.nx[0], p.state_idx + nb);
-    cp_async4(&sm.nx[1], p.ring_idx + nb);
-    cp_async4(&sm.nx[2], p.win_idx + nb);
-  };
-  auto idx_level2 = [&]() {
-    cp_async_wait_all();
-    const int r = *reinterpret_cast<volatile int*>(&sm.nx[1]);
-    cp_async4(&sm.nx[3], p.write_pos + r);
-    cp_async4(&sm.nx[4], p.cache_base + r);
-  };
-  // the whole fetch at once, for the paths that skip a unit: every thread has read the current indices before
-  // the first barrier, and sees the next ones after the second
-  auto idx_fetch_now = [&](int nb) {
-    __syncthreads();
-    if (tid == G_THREADS - 1 && nb >= 0) {
-      idx_level1(nb);
-      idx_level2();
-      cp_async_wait_all();
-    }
-    __syncthreads();
-  };
-  if constexpr (REPLAY) {
-    const int first = blockIdx.x >> 1;
-    idx_fetch_now(first < npairs ? first / G_HK : -1);
-  }
-  for (int pair = blockIdx.x >> 1; pair < npairs; pair += ncl, par ^= 1u) {
-  const int b = pair / G_HK, hk = pair - b * G_HK, hv = 2 * hk + rank;
-  int slot = b, ring = 0, wp = 0, cb = 0, wslot = 0;
-  const int nb = pair + ncl < npairs ? (pair + ncl) / G_HK : -1;  // the next unit's request
-  if constexpr (REPLAY) {
-    slot = sm.nx[0];
-    ring = sm.nx[1];
-    wslot = sm.nx[2];
-    wp = sm.nx[3];
-    cb = sm.nx[4];
-    wp = wp < 0 ? 0 : (wp > G_RING ? G_RING : wp);
-    if (slot < 0) {  // a padded request: zero output, nothing read or written; no barrier phase is used
-      idx_fetch_now(nb);
-      if (ok && tid < G_D)
-#pragma unroll
-        for (int s = 0; s < G_NT; ++s)
-          p.out[(static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv * G_D + tid] = f2bf(0.f);
-      par ^= 1u;
-      continue;
-    }
-  }
-  if (!ok) {  // after an abandoned wait the CTA only keeps its partner's cluster barriers company
-    if constexpr (REPLAY) idx_fetch_now(nb);  // it still has to know which units are padded (they have no barrier)
-    cluster_sync();
-    continue;
-  }
-  G_TRACE(0, unit_no);
-  int n_acc = G_NT;  // REPLAY: the conv state is rolled by the whole window
-  if constexpr (!REPLAY) {
-    n_acc = p.accepted[b];
-    n_acc = n_acc < 0 ? 0 : (n_acc > G_NT ? G_NT : n_acc);
-  }
-  const int srow0 = (slot * G_HV + hv) * G_D;  // first row of this unit in the [slots*32*128, 128] view of the state
-  if (tid == 0 && !tile_requested) {
-    bulk_wait_read_all();  // the previous unit's tile has left shared memory
-    mbar_expect_tx(&sm.bar_load, G_TILE_BYTES);
-#pragma unroll
-    for (int sub = 0; sub < 4; ++sub) tma_load_2d(sm.S[sub], &tmS, 32 * sub, srow0, &sm.bar_load);
-  }
-
-  // ---- every global input of this unit is requested before anything is computed ----
-  const bf16* mixed_b = p.mixed + static_cast<size_t>(b) * G_NT * G_CONV;
-  bf16* cs_b = p.conv_state + static_cast<size_t>(slot) * G_CONV * 3;
-  const int c = tid & 127;
-  const bool is_k = tid >= 128;
-  const int ch_qk = (is_k ? G_QDIM : 0) + hk * G_D + c;
-  const int ch_v = 2 * G_QDIM + hv * G_D + c;
-  ConvIn in_qk, in_v;
-  conv_load(mixed_b, cs_b, p.conv_w, ch_qk, in_qk);
-  float zz[G_NT] = {0.f, 0.f, 0.f, 0.f}, nw = 0.f;
-  if (!is_k) {
-    conv_load(mixed_b, cs_b, p.conv_w, ch_v, in_v);
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) zz[s] = bf2f(p.z[(static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv * G_D + c]);
-    nw = bf2f(p.norm_w[c]);
-  } else if (tid < 128 + G_NT) {
-    // gates (qk_gdn_verify.cu:616-631)
-    const int s = tid - 128;
-    const float av = bf2f(p.a[(static_cast<size_t>(b) * G_NT + s) * G_HV + hv]);
-    const float bv = bf2f(p.b[(static_cast<size_t>(b) * G_NT + s) * G_HV + hv]);
-    const float xg = av + p.dt_bias[hv];
-    const float sp = xg <= 20.f ? log1pf(expf(xg)) : xg;
-    const float g = -expf(p.a_log[hv]) * sp;
-    sm.g[s] = g;
-    sm.beta[s] = 1.f / (1.f + expf(-bv));
-    if constexpr (REPLAY)  // this window's gates join the ring (qk_gdn_verify.cu:631)
-      if (wp + s < G_RING) p.g_ring[(static_cast<size_t>(ring) * G_HV + hv) * G_RING + ((cb + wp + s) & (G_RING - 1))] = g;
-  } else if (REPLAY && tid < 128 + G_NT + G_RING) {
-    const int e = tid - 128 - G_NT;  // committed gates in logical order
-    sm.gr[e] = e < wp ? p.g_ring[(static_cast<size_t>(ring) * G_HV + hv) * G_RING + ((cb + e) & (G_RING - 1))] : 0.f;
-  }
-  // REPLAY: warps 1..7 fetch the committed ring keys they will multiply (entries warp - 1, + 7, + 14), four
-  // dimensions per lane
-  uint2 rk[3] = {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)};
-  // REPLAY: the value head's committed d entries (high parts), one 16-byte chunk per thread: physical entry
-  // tid / 16, value rows 8 (tid % 16) ..; entries past the history read as zero whatever the ring holds there
-  uint4 dchunk = make_uint4(0u, 0u, 0u, 0u);
-  const int d_entry = ((tid >> 4) - cb) & (G_RING - 1);  // logical entry of this thread's chunk
-  if constexpr (REPLAY) {
-    if (d_entry < wp)
-      dchunk = *reinterpret_cast<const uint4*>(p.d_ring + ((static_cast<size_t>(ring) * G_HV + hv) * G_RING + (tid >> 4)) * G_D +
-                                               (tid & 15) * 8);
-    if (warp > 0)
-#pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        const int e = warp - 1 + 7 * i;
-        if (e < wp)
-          rk[i] = *reinterpret_cast<const uint2*>(p.k_ring + ((static_cast<size_t>(ring) * G_HK + hk) * G_RING +
-                                                              ((cb + e) & (G_RING - 1))) * G_D + 4 * lane);
-      }
-  }
-  // ---- conv + SiLU on q, k (key head hk) and v (value head hv); L2 norms ----
-  {
-    float y[G_NT];
-    conv_apply(in_qk, y);
-    float ss[G_NT];
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) ss[s] = y[s] * y[s];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s) ss[s] += __shfl_xor_sync(FULL_MASK, ss[s], o);
-    if (lane == 0)
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s) sm.nrm[is_k][s][warp & 3] = ss[s];
-    if (!is_k) {
-      float yv[G_NT];
-      conv_apply(in_v, yv);
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s) sm.v[s][c] = yv[s];
-    }
-    __syncthreads();
-    G_TRACE(1, unit_no);
-    if constexpr (REPLAY)  // every thread has read this unit's indices: the next unit's may replace them
-      if (tid == G_THREADS - 1 && nb >= 0) idx_level1(nb);
-    const int sub = c >> 5, chk = (c & 31) >> 2, e = c & 3;
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) {
-      const float n = sm.nrm[is_k][s][0] + sm.nrm[is_k][s][1] + sm.nrm[is_k][s][2] + sm.nrm[is_k][s][3];
-      const float r = (1.f / sqrtf(n + 1e-6f)) * (is_k ? 1.f : 0.08838834764831845f);  // d_k^-0.5
-      const float val = y[s] * r;
-      const int row = (is_k ? 4 : 0) + s;
-      sm.QK[sub][row * 32 + sw_chunk(row, chk) + e] = val;
-      if (is_k) sm.k[s][c] = val;
-      if constexpr (REPLAY) {
-        // the unit keys join the key ring as bf16 high and low parts (qk_gdn_verify.cu:586-593); entries past the
-        // history, disjoint from the entries read
-        if (is_k && (hv & 1) == 0 && wp + s < G_RING) {
-          const size_t at = ((static_cast<size_t>(ring) * G_HK + hk) * G_RING + ((cb + wp + s) & (G_RING - 1))) * G_D + c;
-          const bf16 hi = f2bf(val);
-          p.k_ring[at] = hi;
-          p.klo_ring[at] = f2bf(val - bf2f(hi));
-        }
-      }
-    }
-  }
-  // the q/k conv state is shared by the two value heads of the key head: both have read it once the
-  // cluster barrier is passed, then the even head rolls it; every head rolls its own v channels
-  cluster_sync();
-  if ((hv & 1) == 0) conv_roll(in_qk, cs_b, ch_qk, n_acc);
-  if (!is_k) conv_roll(in_v, cs_b, ch_v, n_acc);
-  if constexpr (REPLAY) {
-    bf16* wrec = p.window + static_cast<size_t>(wslot) * G_CONV * 6;
-    if ((hv & 1) == 0) conv_record(in_qk, wrec, ch_qk);
-    if (!is_k) conv_record(in_v, wrec, ch_v);
-  }
-  fence_proxy_async();  // the QK tile was written with ordinary stores; the tensor core reads it through the async proxy
-  __syncthreads();
-  G_TRACE(2, unit_no);
-
-  // ---- S [q | k]: sixteen tf32 MMAs (M = 128 state rows, N = 16, K = 8 each) into 16 TMEM columns ----
-  bool landed = true;
-  if (tid == 0) {
-    landed = mbar_wait(&sm.bar_load, par, &sm.abort_flag, p.status, ST_WAIT_STATE);
-    if (landed) {
-      tc_fence_after();
-      const uint32_t idesc = umma_idesc(UMMA_C_F32, UMMA_AB_TF32, 16);
-#pragma unroll
-      for (int sub = 0; sub < 4; ++sub)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          tc_mma_tf32(tmem_base, umma_desc_sw128(smem_u32(sm.S[sub]) + kk * 32),
-                      umma_desc_sw128(smem_u32(sm.QK[sub]) + kk * 32), idesc, (sub | kk) != 0);
-      tc_commit(&sm.bar_mma);
-    }
-    G_TRACE(3, unit_no);
-  }
-  // k_i . k_j and k_i . q_j while the MMAs run: 32 dots of length 128 over warps 1..7 (warp 0 issues the MMAs;
-  // q is read back from the QK tile)
-  for (int d = warp - 1; warp > 0 && d < 32; d += 7) {
-    const int i = (d >> 2) & 3, j = d & 3;
-    float acc = 0.f;
-#pragma unroll
-    for (int c4 = 0; c4 < 4; ++c4) {
-      const int c = lane + 32 * c4;
-      const float other = d < 16 ? sm.k[j][c] : sm.QK[c >> 5][j * 32 + sw_chunk(j, (c & 31) >> 2) + (c & 3)];
-      acc = fmaf(sm.k[i][c], other, acc);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(FULL_MASK, acc, o);
-    if (lane == 0) (d < 16 ? sm.kk : sm.kq)[i][j] = acc;
-  }
-  if constexpr (REPLAY) {
-    // committed ring keys . [q | k] (rows 0..15 of the reference's key tile, qk_gdn_verify.cu:597-604,662-671)
-    if (warp > 0) {
-      float4 cq[G_NT], ck[G_NT];
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s) {
-        cq[s] = *reinterpret_cast<const float4*>(&sm.QK[lane >> 3][s * 32 + sw_chunk(s, lane & 7)]);
-        ck[s] = *reinterpret_cast<const float4*>(&sm.k[s][4 * lane]);
-      }
-#pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        const int e = warp - 1 + 7 * i;
-        if (e < wp) {  // entries past the history are never read
-          const float k0 = bf_lo(rk[i].x), k1 = bf_hi(rk[i].x), k2 = bf_lo(rk[i].y), k3 = bf_hi(rk[i].y);
-          float acc[8];
-#pragma unroll
-          for (int s = 0; s < G_NT; ++s) {
-            acc[s] = fmaf(k3, cq[s].w, fmaf(k2, cq[s].z, fmaf(k1, cq[s].y, k0 * cq[s].x)));
-            acc[4 + s] = fmaf(k3, ck[s].w, fmaf(k2, ck[s].z, fmaf(k1, ck[s].y, k0 * ck[s].x)));
-          }
-          // sum over the lanes with a transposing butterfly: each step halves the columns a lane carries (the upper
-          // half of the lanes keeps the upper columns), 4 + 2 + 1 shuffles, then two plain steps: lane l ends with
-          // the total of column (l >> 4 & 1) * 4 + (l >> 3 & 1) * 2 + (l >> 2 & 1)
-          float a4[4], a2[2], a1;
-          {
-            const bool up = lane & 16;
-#pragma unroll
-            for (int n = 0; n < 4; ++n) {
-              const float give = up ? acc[n] : acc[4 + n], keep = up ? acc[4 + n] : acc[n];
-              a4[n] = keep + __shfl_xor_sync(FULL_MASK, give, 16);
-            }
-          }
-          {
-            const bool up = lane & 8;
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-              const float give = up ? a4[n] : a4[2 + n], keep = up ? a4[2 + n] : a4[n];
-              a2[n] = keep + __shfl_xor_sync(FULL_MASK, give, 8);
-            }
-          }
-          {
-            const bool up = lane & 4;
-            const float give = up ? a2[0] : a2[1], keep = up ? a2[1] : a2[0];
-            a1 = keep + __shfl_xor_sync(FULL_MASK, give, 4);
-          }
-          a1 += __shfl_xor_sync(FULL_MASK, a1, 2);
-          a1 += __shfl_xor_sync(FULL_MASK, a1, 1);
-          if ((lane & 3) == 0) sm.xr[e][((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = a1;
-        }
-      }
-    }
-  }
-  if constexpr (REPLAY)  // the next unit's ring slot has landed: fetch its cursors
-    if (tid == G_THREADS - 1 && nb >= 0) idx_level2();
-  __syncthreads();  // kk, kq visible; thread 0 has issued (or abandoned) the MMAs
-  G_TRACE(4, unit_no);
-  if constexpr (REPLAY) {
-    if (warp == 2) {
-      // decay of every committed entry up to the window: e^{total - pre_c}, and of the checkpoint: e^{total}
-      // (qk_gdn_verify.cu:633-647)
-      const int e = lane & 15;
-      float pre = sm.gr[e];
-#pragma unroll
-      for (int o = 1; o < G_RING; o <<= 1) {
-        const float n = __shfl_up_sync(FULL_MASK, pre, o, G_RING);
-        if (e >= o) pre += n;
-      }
-      const float total = __shfl_sync(FULL_MASK, pre, G_RING - 1, G_RING);
-      if (lane < G_RING) {
-        sm.dec[e] = e < wp ? __expf(total - pre) : 0.f;
-        if (e == 0) sm.tdec = __expf(total);
-      }
-      G_TRACE_W(11, unit_no);
-    }
-  }
-  if (warp == 1) G_TRACE_W(13, unit_no);
-  if (warp == 1) {
-    // the window's scalar coefficients, once per unit instead of once per value row
-    float G[G_NT];
-    float run = 0.f;
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) {
-      run += sm.g[s];
-      G[s] = run;
-    }
-    if (lane < 16) {
-      const int i = lane >> 2, j = lane & 3;
-      float Gi = 0.f, Gj = 0.f;
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s) {
-        Gi = s == i ? G[s] : Gi;
-        Gj = s == j ? G[s] : Gj;
-      }
-      sm.cA[i][j] = i > j ? sm.beta[i] * __expf(Gi - Gj) * sm.kk[i][j] : 0.f;
-      sm.cF[i][j] = i <= j ? __expf(Gj - Gi) * sm.kq[i][j] : 0.f;
-    } else if (lane < 20) {
-      const int s = lane - 16;
-      float Gs = 0.f, Gn = 0.f;
-#pragma unroll
-      for (int u = 0; u < G_NT; ++u) {
-        Gs = u == s ? G[u] : Gs;
-        Gn = u == n_acc - 1 ? G[u] : Gn;
-      }
-      sm.cE[s] = __expf(Gs);
-      sm.cR[s] = sm.beta[s];
-      sm.cC[s] = s < n_acc ? __expf(Gn - Gs) : 0.f;
-      sm.G[s] = Gs;
-    }
-    G_TRACE_W(10, unit_no);
-  }
-  if (warp == 5) G_TRACE_W(12, unit_no);
-  __syncthreads();
-  G_TRACE(5, unit_no);
-  ok = mbar_wait(&sm.bar_load, par, &sm.abort_flag, p.status, ST_WAIT_STATE) &&
-       mbar_wait(&sm.bar_mma, par, &sm.abort_flag, p.status, ST_WAIT_TMEM_FULL);
-  ok = __syncthreads_and(ok);  // one verdict for the CTA
-  tc_fence_after();
-  G_TRACE(6, unit_no);
-  if constexpr (REPLAY) {
-    // the operand tile [q | k] has been consumed: its 4 KB now hold the d entries, [logical entry][value row] bf16
-    *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(&sm.QK[0][0]) + d_entry * G_D + (tid & 15) * 8) = dchunk;
-    __syncthreads();
-  }
-  if constexpr (REPLAY) {
-    // the MMAs were the only readers of the tile and nothing is written back: the next unit's checkpoint tile
-    // can travel during this unit's epilogue and the next unit's prologue
-    if (tid == 0) {
-      tile_requested = false;
-      const int nslot = nb >= 0 ? *reinterpret_cast<volatile int*>(&sm.nx[0]) : -1;
-      if (ok && nslot >= 0) {
-        const int nrow0 = (nslot * G_HV + 2 * ((pair + ncl) % G_HK) + rank) * G_D;
-        mbar_expect_tx(&sm.bar_load, G_TILE_BYTES);
-#pragma unroll
-        for (int sub = 0; sub < 4; ++sub) tma_load_2d(sm.S[sub], &tmS, 32 * sub, nrow0, &sm.bar_load);
-        tile_requested = true;
-      }
-    }
-  }
-
-  // ---- per value row: R, D = (I + A)^-1 R, outputs; gated RMSNorm ----
-  float o[G_NT] = {0.f, 0.f, 0.f, 0.f};
-  if (ok && tid < G_D) {
-    const int v = tid;
-    uint32_t hr[16];
-    tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16), hr);  // warps 0..3 own TMEM lane quadrants 0..3
-    tmem_ld_wait();
-    float hq[G_NT], hk_[G_NT];
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) {
-      hq[s] = __uint_as_float(hr[s]);
-      hk_[s] = __uint_as_float(hr[4 + s]);
-    }
-    if constexpr (REPLAY) {
-      // S x = e^{total} H0 x + sum_c (d_c e^{total - pre_c}) (k_c . x)   (qk_gdn_verify.cu:706-742)
-      float aq[G_NT] = {0.f, 0.f, 0.f, 0.f}, ak[G_NT] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-      for (int e = 0; e < wp; ++e) {
-        const float dsc = bf2f(reinterpret_cast<const bf16*>(&sm.QK[0][0])[e * G_D + v]) * sm.dec[e];
-        const float4 xq = *reinterpret_cast<const float4*>(&sm.xr[e][0]);
-        const float4 xk = *reinterpret_cast<const float4*>(&sm.xr[e][4]);
-        aq[0] = fmaf(dsc, xq.x, aq[0]); aq[1] = fmaf(dsc, xq.y, aq[1]);
-        aq[2] = fmaf(dsc, xq.z, aq[2]); aq[3] = fmaf(dsc, xq.w, aq[3]);
-        ak[0] = fmaf(dsc, xk.x, ak[0]); ak[1] = fmaf(dsc, xk.y, ak[1]);
-        ak[2] = fmaf(dsc, xk.z, ak[2]); ak[3] = fmaf(dsc, xk.w, ak[3]);
-      }
-      const float td = sm.tdec;
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s) {
-        hq[s] = fmaf(td, hq[s], aq[s]);
-        hk_[s] = fmaf(td, hk_[s], ak[s]);
-      }
-    }
-    float R[G_NT], D[G_NT];
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) R[s] = sm.cR[s] * (sm.v[s][v] - sm.cE[s] * hk_[s]);
-#pragma unroll
-    for (int i = 0; i < G_NT; ++i) {
-      float d = R[i];
-#pragma unroll
-      for (int j = 0; j < i; ++j) d = fmaf(-sm.cA[i][j], D[j], d);
-      D[i] = d;
-    }
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) {
-      float acc = sm.cE[s] * hq[s];
-#pragma unroll
-      for (int i = 0; i <= s; ++i) acc = fmaf(D[i], sm.cF[i][s], acc);
-      o[s] = rbf(acc);  // the core output is stored in bf16 before the norm (qk_gdn_verify.cu:761)
-    }
-    if constexpr (REPLAY) {
-      // the window's D join the ring as bf16 high and low parts (qk_gdn_verify.cu:769-781)
-      const size_t base = (static_cast<size_t>(ring) * G_HV + hv) * G_RING * G_D + v;
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s)
-        if (wp + s < G_RING) {
-          const size_t at = base + static_cast<size_t>((cb + wp + s) & (G_RING - 1)) * G_D;
-          const bf16 hi = f2bf(D[s]);
-          p.d_ring[at] = hi;
-          p.dlo_ring[at] = f2bf(D[s] - bf2f(hi));
-        }
-    }
-    __syncwarp();
-    // c_i D_i for the state update replaces v (each thread only touches its own column)
-#pragma unroll
-    for (int i = 0; i < G_NT; ++i) sm.v[i][v] = D[i] * sm.cC[i];
-  }
-  {
-    float ss[G_NT];
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) ss[s] = o[s] * o[s];
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s) ss[s] += __shfl_xor_sync(FULL_MASK, ss[s], off);
-    if (lane == 0)
-#pragma unroll
-      for (int s = 0; s < G_NT; ++s) sm.red[warp][s] = ss[s];
-  }
-  tc_fence_before();
-  __syncthreads();
-  G_TRACE(7, unit_no);
-  if (ok && tid < G_D) {
-#pragma unroll
-    for (int s = 0; s < G_NT; ++s) {
-      const float var = (sm.red[0][s] + sm.red[1][s] + sm.red[2][s] + sm.red[3][s]) * (1.f / G_D);
-      const float rstd = rsqrtf(var + p.eps);
-      const size_t idx = (static_cast<size_t>(b) * G_NT + s) * G_ZDIM + hv * G_D + tid;
-      p.out[idx] = f2bf(o[s] * rstd * nw * (zz[s] * (1.f / (1.f + __expf(-zz[s])))));
-    }
-  }
-
-  // ---- state after n_acc tokens, in place in the swizzled tile, then four TMA tensor stores ----
-  if (!REPLAY && ok && n_acc > 0) {
-    // thread = 4 state rows x one 16-byte chunk position of each 32-float sub-tile row
-    const int rg = tid >> 3, ks = tid & 7;
-    const float decay = sm.cE[n_acc - 1];
-    float cd[4][G_NT];
-#pragma unroll
-    for (int r = 0; r < 4; ++r)
-#pragma unroll
-      for (int i = 0; i < G_NT; ++i) cd[r][i] = sm.v[i][rg * 4 + r];
-#pragma unroll
-    for (int sub = 0; sub < 4; ++sub) {
-      float4 kv[G_NT];
-#pragma unroll
-      for (int t = 0; t < G_NT; ++t) kv[t] = *reinterpret_cast<const float4*>(&sm.k[t][sub * 32 + ks * 4]);
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int row = rg * 4 + r;
-        float4* sp = reinterpret_cast<float4*>(&sm.S[sub][row * 32 + sw_chunk(row, ks)]);
-        float4 sv = *sp;
-        sv.x *= decay; sv.y *= decay; sv.z *= decay; sv.w *= decay;
-#pragma unroll
-        for (int t = 0; t < G_NT; ++t) {
-          sv.x = fmaf(cd[r][t], kv[t].x, sv.x);
-          sv.y = fmaf(cd[r][t], kv[t].y, sv.y);
-          sv.z = fmaf(cd[r][t], kv[t].z, sv.z);
-          sv.w = fmaf(cd[r][t], kv[t].w, sv.w);
-        }
-        *sp = sv;
-      }
-      // this 16 KB sub-tile is final: hand it to TMA while the next one is being updated
-      fence_proxy_async();
-      __syncthreads();
-      if (tid == 0) {
-        tma_store_2d(&tmS, 32 * sub, srow0, sm.S[sub]);
-        bulk_commit();
-      }
-    }
-  }
-  if (!ok && tid == 0) {
-    // an abandoned wait: give the state copy a bounded grace period before the CTA's memory goes away
-    const unsigned long long t0 = globaltimer();
-    while (!mbar_try(&sm.bar_load, par) && globaltimer() - t0 < 20000000ull) {
-    }
-  }
-  if constexpr (REPLAY)
-    if (tid == G_THREADS - 1) cp_async_wait_all();  // the next unit's indices are in shared memory
-  __syncthreads();  // every buffer of the unit is free for the next one
-  G_TRACE(8, unit_no);
-  ++unit_no;
-  }  // units
-  G_TRACE(9, 1);
-  if (tid == 0) bulk_wait_read_all();  // the last tile has left shared memory; the writes complete with the grid
-  __syncthreads();
-  if (warp == 0) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 32);
-  }
-}
-
-
-// =====================================================================================================
-// The explicit-state step as two launches: a small operand kernel and a streaming kernel.
-//
-// In the kernel above every unit runs a chain of dependent steps (input loads, conv, norms, barriers, dots,
-// coefficients) before and after the one thing that is bound by memory, the 64 KB state tile; the chain, not
-// the bytes, sets its time.  Here gdn_prep_kernel does everything that does not touch the state, once per
-// (sequence, key head): conv + SiLU, norms, gates, window dots and coefficients, and leaves per unit one operand tile
-// [q | k] already in the swizzled layout the tensor core reads plus one 2.8 KB block (conv v, z, coefficients).
-// gdn_stream_kernel then only moves state tiles: per unit one barrier for the tile and the two operand blocks
-// (TMA tensor load + two bulk copies), sixteen tf32 MMAs, the per-row epilogue, the in-place update and the
-// tile store.  It is launched with programmatic stream serialization and requests its first tile before
-// waiting for the operand kernel, since the tile does not depend on it.
-// =====================================================================================================
 struct GdnOps {              // per (sequence, value head): one bulk copy
   bf16 v[G_NT][G_D];         // conv v (bf16 values)
   bf16 z[G_NT][G_D];         // gate input
@@ -1282,12 +700,31 @@ extern "C" size_t b200_gdn_workspace_bytes(int B) {
   return B <= 0 ? 0 : static_cast<size_t>(B) * (G_HK * G_QK_FLOATS * 4 + G_HV * sizeof(GdnOps));
 }
 
-static bool gdn_single_kernel() {  // B200_GDN_SINGLE=1: the one-launch cluster kernel (for comparison)
-  static const bool v = [] {
-    const char* e = getenv("B200_GDN_SINGLE");
-    return e && *e && *e != '0';
-  }();
-  return v;
+// operand kernel, then streaming kernel (three CTAs per SM by shared memory), both with programmatic stream
+// serialization
+template <bool REPLAY>
+static int gdn_launch(const CUtensorMap& tmS, const GdnArgs& p, int B, void* ws, size_t ws_bytes, void* stream,
+                      const char* what) {
+  if (!ws || ws_bytes < b200_gdn_workspace_bytes(B))
+    return fail(B200_E_WS, "%s: workspace of %zu bytes needed, %zu given", what, b200_gdn_workspace_bytes(B), ws_bytes);
+  if (reinterpret_cast<uintptr_t>(ws) & 127) return fail(B200_E_ALIGN, "%s: workspace must be 128-byte aligned", what);
+  float* qk_ws = static_cast<float*>(ws);
+  GdnOps* ops_ws = reinterpret_cast<GdnOps*>(qk_ws + static_cast<size_t>(B) * G_HK * G_QK_FLOATS);
+  const int smem = static_cast<int>(sizeof(GdnStreamSmem)) + 1024;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaFuncSetAttribute(gdn_stream_kernel<REPLAY>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    attr_done[dev] = true;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  launch_k(gdn_prep_kernel<REPLAY>, dim3(B * G_HK), dim3(512), 0, st, p, qk_ws, ops_ws);
+  int grid = sm_count() * 3;
+  if (grid > B * G_HV) grid = B * G_HV;
+  launch_k(gdn_stream_kernel<REPLAY>, dim3(grid), dim3(G_THREADS), static_cast<size_t>(smem), st, tmS, p,
+           static_cast<const float*>(qk_ws), static_cast<const GdnOps*>(ops_ws));
+  return launch_status(what);
 }
 
 extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, const void* b, void* conv_state,
@@ -1318,40 +755,7 @@ extern "C" int b200_gdn_verify(const void* mixed, const void* z, const void* a, 
   p.status = status;
   CUtensorMap tmS;
   if (int rc = make_tmap_f32_2d(&tmS, state, static_cast<uint64_t>(B) * G_HV * G_D, G_D, G_D, "gdn state")) return rc;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!gdn_single_kernel()) {
-    if (!ws || ws_bytes < b200_gdn_workspace_bytes(B))
-      return fail(B200_E_WS, "b200_gdn_verify: workspace of %zu bytes needed, %zu given", b200_gdn_workspace_bytes(B),
-                  ws_bytes);
-    if (reinterpret_cast<uintptr_t>(ws) & 127) return fail(B200_E_ALIGN, "b200_gdn_verify: workspace must be 128-byte aligned");
-    float* qk_ws = static_cast<float*>(ws);
-    GdnOps* ops_ws = reinterpret_cast<GdnOps*>(qk_ws + static_cast<size_t>(B) * G_HK * G_QK_FLOATS);
-    const int ssmem = static_cast<int>(sizeof(GdnStreamSmem)) + 1024;
-    static bool sattr_done[64] = {false};
-    if (dev >= 0 && dev < 64 && !sattr_done[dev]) {
-      cudaFuncSetAttribute(gdn_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ssmem);
-      sattr_done[dev] = true;
-    }
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    launch_k(gdn_prep_kernel<false>, dim3(B * G_HK), dim3(512), 0, st, p, qk_ws, ops_ws);
-    int grid = sm_count() * 3;
-    if (grid > B * G_HV) grid = B * G_HV;
-    launch_k(gdn_stream_kernel<false>, dim3(grid), dim3(G_THREADS), static_cast<size_t>(ssmem), st, tmS, p,
-             static_cast<const float*>(qk_ws), static_cast<const GdnOps*>(ops_ws));
-    return launch_status("b200_gdn_verify");
-  }
-  const int smem = static_cast<int>(sizeof(GdnSmem)) + 1024;
-  static bool attr_done[64] = {false};
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaFuncSetAttribute(gdn_verify_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    attr_done[dev] = true;
-  }
-  // three CTAs per SM (shared memory), in clusters of two
-  int ncl = (sm_count() * 3) / 2;
-  if (ncl > B * G_HK) ncl = B * G_HK;
-  gdn_verify_kernel<false><<<dim3(2 * ncl), G_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tmS, p);
-  return launch_status("b200_gdn_verify");
+  return gdn_launch<false>(tmS, p, B, ws, ws_bytes, stream, "b200_gdn_verify");
 }
 
 extern "C" int b200_gdn_verify_replay(const void* mixed, const void* z, const void* a, const void* b, void* conv_state,
@@ -1404,38 +808,5 @@ extern "C" int b200_gdn_verify_replay(const void* mixed, const void* z, const vo
   if (int rc = make_tmap_f32_2d(&tmS, const_cast<float*>(checkpoint), static_cast<uint64_t>(state_slots) * G_HV * G_D, G_D,
                                 G_D, "gdn checkpoint"))
     return rc;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!gdn_single_kernel()) {
-    if (!ws || ws_bytes < b200_gdn_workspace_bytes(B))
-      return fail(B200_E_WS, "b200_gdn_verify_replay: workspace of %zu bytes needed, %zu given", b200_gdn_workspace_bytes(B),
-                  ws_bytes);
-    if (reinterpret_cast<uintptr_t>(ws) & 127)
-      return fail(B200_E_ALIGN, "b200_gdn_verify_replay: workspace must be 128-byte aligned");
-    float* qk_ws = static_cast<float*>(ws);
-    GdnOps* ops_ws = reinterpret_cast<GdnOps*>(qk_ws + static_cast<size_t>(B) * G_HK * G_QK_FLOATS);
-    const int ssmem = static_cast<int>(sizeof(GdnStreamSmem)) + 1024;
-    static bool sattr_done[64] = {false};
-    if (dev >= 0 && dev < 64 && !sattr_done[dev]) {
-      cudaFuncSetAttribute(gdn_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ssmem);
-      sattr_done[dev] = true;
-    }
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    launch_k(gdn_prep_kernel<true>, dim3(B * G_HK), dim3(512), 0, st, p, qk_ws, ops_ws);
-    int grid = sm_count() * 3;
-    if (grid > B * G_HV) grid = B * G_HV;
-    launch_k(gdn_stream_kernel<true>, dim3(grid), dim3(G_THREADS), static_cast<size_t>(ssmem), st, tmS, p,
-             static_cast<const float*>(qk_ws), static_cast<const GdnOps*>(ops_ws));
-    return launch_status("b200_gdn_verify_replay");
-  }
-  const int smem = static_cast<int>(sizeof(GdnSmem)) + 1024;
-  static bool attr_done[64] = {false};
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaFuncSetAttribute(gdn_verify_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    attr_done[dev] = true;
-  }
-  int ncl = (sm_count() * 3) / 2;
-  if (ncl > B * G_HK) ncl = B * G_HK;
-  gdn_verify_kernel<true><<<dim3(2 * ncl), G_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tmS, p);
-  return launch_status("b200_gdn_verify_replay");
+  return gdn_launch<true>(tmS, p, B, ws, ws_bytes, stream, "b200_gdn_verify_replay");
 }
