@@ -89,21 +89,36 @@ __global__ void __launch_bounds__(256) quant_rows_i8_kernel(const bf16* __restri
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   pdl_wait();
   pdl_launch();
-  if (row >= rows || slot_of_row[row] < 0) return;
+  if (row >= rows) return;
   const bf16* hr = h + static_cast<size_t>(row) * I;
+  // I <= 1024: the row is read once, all loads in flight together with the slot lookup (every sorted row below
+  // `rows` is readable memory; a row without a slot is simply not written)
+  constexpr int MAXV = 4;
+  const bool fits = I <= MAXV * 256;
+  uint4 v[MAXV];
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i)
+      v[i] = lane * 8 + i * 256 < I ? *reinterpret_cast<const uint4*>(hr + lane * 8 + i * 256) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (slot_of_row[row] < 0) return;
   float amax = 0.f;
-  for (int c = lane * 8; c < I; c += 256) {
-    const uint4 v = *reinterpret_cast<const uint4*>(hr + c);
-    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf_lo(v.x)), fabsf(bf_hi(v.x))), fmaxf(fabsf(bf_lo(v.y)), fabsf(bf_hi(v.y)))));
-    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf_lo(v.z)), fabsf(bf_hi(v.z))), fmaxf(fabsf(bf_lo(v.w)), fabsf(bf_hi(v.w)))));
+  auto absmax = [&](const uint4& q) {
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf_lo(q.x)), fabsf(bf_hi(q.x))), fmaxf(fabsf(bf_lo(q.y)), fabsf(bf_hi(q.y)))));
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf_lo(q.z)), fabsf(bf_hi(q.z))), fmaxf(fabsf(bf_lo(q.w)), fabsf(bf_hi(q.w)))));
+  };
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) absmax(v[i]);
+  } else {
+    for (int c = lane * 8; c < I; c += 256) absmax(*reinterpret_cast<const uint4*>(hr + c));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(FULL_MASK, amax, o));
   const float scale = __fdiv_rn(amax, 127.f);
   const float safe = amax > 0.f ? scale : 1.f;
-  for (int c = lane * 8; c < I; c += 256) {
-    const uint4 v = *reinterpret_cast<const uint4*>(hr + c);
-    const float f[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+  auto emit = [&](const uint4& q, int c) {
+    const float f[8] = {bf_lo(q.x), bf_hi(q.x), bf_lo(q.y), bf_hi(q.y), bf_lo(q.z), bf_hi(q.z), bf_lo(q.w), bf_hi(q.w)};
     uint32_t lo = 0, hi = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -111,6 +126,13 @@ __global__ void __launch_bounds__(256) quant_rows_i8_kernel(const bf16* __restri
       hi |= (static_cast<uint32_t>(q8(f[4 + i], safe)) & 0xffu) << (8 * i);
     }
     *reinterpret_cast<uint2*>(hq + static_cast<size_t>(row) * I + c) = make_uint2(lo, hi);
+  };
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i)
+      if (lane * 8 + i * 256 < I) emit(v[i], lane * 8 + i * 256);
+  } else {
+    for (int c = lane * 8; c < I; c += 256) emit(*reinterpret_cast<const uint4*>(hr + c), c);
   }
   if (lane == 0) hs[row] = scale;
 }
