@@ -12,6 +12,10 @@ _lib = torch.library.Library("b200nodes", "DEF")
 _lib.define("router(Tensor x, Tensor wr, Tensor? bias, int top_k, bool round_bf16) -> (Tensor, Tensor)")
 _lib.define("gdn_verify(Tensor mixed, Tensor z, Tensor a, Tensor b, Tensor(a!) conv_state, Tensor conv_w, "
             "Tensor a_log, Tensor dt_bias, Tensor(b!) state, Tensor accepted, Tensor norm_w, float eps) -> Tensor")
+_lib.define("gdn_verify_replay(Tensor mixed, Tensor z, Tensor a, Tensor b, Tensor(a!) conv_state, Tensor conv_w, "
+            "Tensor(b!) window, Tensor a_log, Tensor dt_bias, Tensor checkpoint, Tensor(c!) d_ring, Tensor(d!) dlo_ring, "
+            "Tensor(e!) k_ring, Tensor(f!) klo_ring, Tensor(g!) g_ring, Tensor state_idx, Tensor ring_idx, Tensor win_idx, "
+            "Tensor write_pos, Tensor cache_base, Tensor norm_w, float eps) -> Tensor")
 _lib.define("attn_front(Tensor x, Tensor w, Tensor w_s, Tensor q_norm_w, Tensor k_norm_w, Tensor positions, "
             "Tensor cos_sin, float eps, bool out_fp8) -> (Tensor, Tensor, Tensor, Tensor)")
 _lib.define("attn_verify(Tensor q, Tensor gate, Tensor k_new, Tensor v_new, Tensor(a!) kcache, Tensor(b!) vcache, "
@@ -27,6 +31,12 @@ def _router(x, wr, bias, top_k, round_bf16):
 
 def _gdn(mixed, z, a, b, conv_state, conv_w, a_log, dt_bias, state, accepted, norm_w, eps):
     return ops.gdn_verify(mixed, z, a, b, conv_state, conv_w, a_log, dt_bias, state, accepted, norm_w, eps)
+
+
+def _gdn_replay(mixed, z, a, b, conv_state, conv_w, window, a_log, dt_bias, checkpoint, d_ring, dlo_ring, k_ring,
+                klo_ring, g_ring, state_idx, ring_idx, win_idx, write_pos, cache_base, norm_w, eps):
+    return ops.gdn_verify_replay(mixed, z, a, b, conv_state, conv_w, window, a_log, dt_bias, checkpoint, d_ring, dlo_ring,
+                                 k_ring, klo_ring, g_ring, state_idx, ring_idx, win_idx, write_pos, cache_base, norm_w, eps)
 
 
 def _attn(x, w, w_s, qw, kw, positions, cos_sin, eps, out_fp8):
@@ -48,6 +58,7 @@ def _combine(cache, x, gate_w, top_k, pos):
 
 _lib.impl("router", _router, "CUDA")
 _lib.impl("gdn_verify", _gdn, "CUDA")
+_lib.impl("gdn_verify_replay", _gdn_replay, "CUDA")
 _lib.impl("attn_front", _attn, "CUDA")
 _lib.impl("attn_verify", _attn_verify, "CUDA")
 _lib.impl("lmhead_argmax", _lmhead, "CUDA")

@@ -118,3 +118,14 @@ def test_logits_node_matches_oracle():
     want = np.argmax(ref, axis=1)
     for t in np.nonzero(got != want)[0]:
         assert abs(ref[t, got[t]] - ref[t, want[t]]) <= 2e-4 * max(1.0, abs(ref[t, want[t]]))
+
+
+def test_torch_ops_are_registered_for_cuda_only():
+    # hosts that dispatch by op name find every operator of the path under torch.ops.b200nodes; there is no CPU kernel
+    import bundles_b200.torch_ops  # noqa: F401
+    names = ["router", "gdn_verify", "gdn_verify_replay", "attn_front", "attn_verify", "lmhead_argmax", "moe_combine"]
+    for n in names:
+        assert hasattr(torch.ops.b200nodes, n), n
+    x = torch.zeros(4, 2048, dtype=torch.bfloat16)
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        torch.ops.b200nodes.router(x, torch.zeros(64, 2048), None, 10, False)
