@@ -54,6 +54,7 @@ PROTOTYPES = {
     "b200_argmax_merge": (i32, [vp, vp, i32, i32, vp, vp]),
     "b200_gdn_verify": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, f32, i32, vp, vp, sz, vp, vp]),
     "b200_gdn_workspace_bytes": (sz, [i32]),
+    "b200_gdn_ring_fold": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp]),
     "b200_gdn_verify_replay": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                      vp, f32, i32, vp, vp, sz, vp, vp]),
 }

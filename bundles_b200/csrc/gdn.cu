@@ -686,6 +686,80 @@ gdn_stream_kernel(const __grid_constant__ CUtensorMap tmS, const GdnArgs p, cons
   }
 }
 
+
+// Fold of the committed ring entries into the checkpoint (the step the reference leaves to its engine's pool,
+// gdn_fused.py:24 `replayssm_spec_fold`): H0 <- e^{total} H0 + sum_{c < wp} e^{total - pre_c} d_c k_c^T with the full
+// entries (high + low parts).  One CTA per (request, value head); thread = one 16-byte column group of 16 rows, so
+// every access to the tile is a coalesced 512-byte row.  The cursors stay the caller's: after the fold it sets
+// write_pos to 0.
+struct GdnFoldArgs {
+  float* checkpoint;
+  const bf16 *d_ring, *dlo_ring, *k_ring, *klo_ring;
+  const float* g_ring;
+  const int32_t *state_idx, *ring_idx, *write_pos, *cache_base;
+};
+
+__global__ void __launch_bounds__(256) gdn_fold_kernel(const GdnFoldArgs p) {
+  __shared__ float dco[G_RING][G_D];  // e^{total - pre_c} d_c[v]
+  __shared__ float ks[G_RING][G_D];   // k_c
+  __shared__ float dec[G_RING];
+  __shared__ float tdec;
+  const int tid = threadIdx.x, b = blockIdx.x / G_HV, hv = blockIdx.x % G_HV;
+  pdl_wait();
+  pdl_launch();
+  const int slot = p.state_idx[b];
+  if (slot < 0) return;
+  const int ring = p.ring_idx[b], cb = p.cache_base[ring];
+  int wp = p.write_pos[ring];
+  wp = wp < 0 ? 0 : (wp > G_RING ? G_RING : wp);
+  if (wp == 0) return;  // nothing committed: the checkpoint is the state
+  if (tid < 32) {
+    const int e = tid & 15;
+    float pre = e < wp ? p.g_ring[(static_cast<size_t>(ring) * G_HV + hv) * G_RING + ((cb + e) & (G_RING - 1))] : 0.f;
+#pragma unroll
+    for (int o = 1; o < G_RING; o <<= 1) {
+      const float n = __shfl_up_sync(FULL_MASK, pre, o, G_RING);
+      if (e >= o) pre += n;
+    }
+    const float total = __shfl_sync(FULL_MASK, pre, G_RING - 1, G_RING);
+    if (tid < G_RING) {
+      dec[e] = e < wp ? expf(total - pre) : 0.f;
+      if (e == 0) tdec = expf(total);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < wp * G_D; i += 256) {
+    const int e = i >> 7, c = i & 127, ph = (cb + e) & (G_RING - 1);
+    const size_t dat = ((static_cast<size_t>(ring) * G_HV + hv) * G_RING + ph) * G_D + c;
+    const size_t kat = ((static_cast<size_t>(ring) * G_HK + (hv >> 1)) * G_RING + ph) * G_D + c;
+    dco[e][c] = (bf2f(p.d_ring[dat]) + bf2f(p.dlo_ring[dat])) * dec[e];
+    ks[e][c] = bf2f(p.k_ring[kat]) + bf2f(p.klo_ring[kat]);
+  }
+  __syncthreads();
+  float* tile = p.checkpoint + (static_cast<size_t>(slot) * G_HV + hv) * G_D * G_D;
+  const int col = (tid & 31) * 4, r0 = tid >> 5;
+  const float td = tdec;
+  float4 acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    acc[i] = *reinterpret_cast<const float4*>(tile + (r0 + 8 * i) * G_D + col);
+    acc[i].x *= td; acc[i].y *= td; acc[i].z *= td; acc[i].w *= td;
+  }
+  for (int e = 0; e < wp; ++e) {
+    const float4 kv = *reinterpret_cast<const float4*>(&ks[e][col]);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float d = dco[e][r0 + 8 * i];
+      acc[i].x = fmaf(d, kv.x, acc[i].x);
+      acc[i].y = fmaf(d, kv.y, acc[i].y);
+      acc[i].z = fmaf(d, kv.z, acc[i].z);
+      acc[i].w = fmaf(d, kv.w, acc[i].w);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) *reinterpret_cast<float4*>(tile + (r0 + 8 * i) * G_D + col) = acc[i];
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -809,4 +883,21 @@ extern "C" int b200_gdn_verify_replay(const void* mixed, const void* z, const vo
                                 G_D, "gdn checkpoint"))
     return rc;
   return gdn_launch<true>(tmS, p, B, ws, ws_bytes, stream, "b200_gdn_verify_replay");
+}
+
+extern "C" int b200_gdn_ring_fold(float* checkpoint, const void* d_ring, const void* dlo_ring, const void* k_ring,
+                                  const void* klo_ring, const float* g_ring, const int32_t* state_idx,
+                                  const int32_t* ring_idx, const int32_t* write_pos, const int32_t* cache_base, int B,
+                                  void* stream) {
+  if (!checkpoint || !d_ring || !dlo_ring || !k_ring || !klo_ring || !g_ring || !state_idx || !ring_idx || !write_pos ||
+      !cache_base)
+    return fail(B200_E_ARG, "b200_gdn_ring_fold: null pointer");
+  if (B < 0 || B > 65535) return fail(B200_E_ARG, "b200_gdn_ring_fold: B=%d out of range", B);
+  if (reinterpret_cast<uintptr_t>(checkpoint) & 15) return fail(B200_E_ALIGN, "b200_gdn_ring_fold: checkpoint must be 16-byte aligned");
+  if (B == 0) return 0;
+  GdnFoldArgs p{checkpoint,
+                static_cast<const bf16*>(d_ring), static_cast<const bf16*>(dlo_ring), static_cast<const bf16*>(k_ring),
+                static_cast<const bf16*>(klo_ring), g_ring, state_idx, ring_idx, write_pos, cache_base};
+  launch_k(gdn_fold_kernel, dim3(B * G_HV), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
+  return launch_status("b200_gdn_ring_fold");
 }

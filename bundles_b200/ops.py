@@ -237,6 +237,20 @@ def moe_combine(cache, x, gate_w, top_k, pos=None, out=None):
     return out
 
 
+def gdn_ring_fold(checkpoint, d_ring, dlo_ring, k_ring, klo_ring, g_ring, state_idx, ring_idx, write_pos, cache_base):
+    """Folds the committed ring entries into the checkpoints in place (the engine-side step of the ring layout,
+    gdn_fused.py:24); the caller resets `write_pos` afterwards."""
+    _need(checkpoint, torch.float32, "checkpoint", 4)
+    for name, t in (("d_ring", d_ring), ("dlo_ring", dlo_ring), ("k_ring", k_ring), ("klo_ring", klo_ring)):
+        _need(t, torch.bfloat16, name, 4)
+    _need(g_ring, torch.float32, "g_ring", 3)
+    for name, t in (("state_idx", state_idx), ("ring_idx", ring_idx), ("write_pos", write_pos), ("cache_base", cache_base)):
+        _need(t, torch.int32, name, 1)
+    check(_lib.lib().b200_gdn_ring_fold(_p(checkpoint), _p(d_ring), _p(dlo_ring), _p(k_ring), _p(klo_ring), _p(g_ring),
+                                        _p(state_idx), _p(ring_idx), _p(write_pos), _p(cache_base), state_idx.shape[0],
+                                        _stream()), "b200_gdn_ring_fold")
+
+
 def attn_front(x, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, eps=1e-6, out_fp8=True, ws=None, status=None):
     """Fused QKV + gate projection with q/k RMSNorm and partial RoPE (reference: fp8.linear_q followed by
     qk_attn_verify.attn_prefill_front).  Returns (q [T,16,256], gate bf16 [T,16,256], k, v [T,2,256]);

@@ -260,6 +260,15 @@ int b200_gdn_verify_replay(const void* mixed, const void* z, const void* a, cons
                            const void* norm_w, float eps, int B, void* out, void* ws, size_t ws_bytes,
                            int32_t* status, void* stream);
 
+/* Folds the committed ring entries of B requests into their checkpoints, in place:
+ *   H0 <- e^{total} H0 + sum_{c < write_pos} e^{total - pre_c} (d_c high + low) (k_c high + low)^T.
+ * The reference leaves this to its engine's pool (gdn_fused.py:24, `replayssm_spec_fold`); it is here so that the
+ * ring layout can be driven without that engine.  Cursors are not touched: the caller sets write_pos[ring] to 0
+ * afterwards.  Requests with state_idx < 0 or an empty ring are skipped.  Arguments as b200_gdn_verify_replay. */
+int b200_gdn_ring_fold(float* checkpoint, const void* d_ring, const void* dlo_ring, const void* k_ring,
+                       const void* klo_ring, const float* g_ring, const int32_t* state_idx, const int32_t* ring_idx,
+                       const int32_t* write_pos, const int32_t* cache_base, int B, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Attention verify core.  Replaces qk_attn_verify.attn_verify_fused (attn_fused.py:110-124;
  * attn_verify_kernel, qk_attn_verify.cu:354-744) behind the projection front above: per request

@@ -73,6 +73,8 @@ def test_argument_checks_return_codes(lib):
     assert lib.b200_gdn_verify_replay(*([None] * 10), 4, *([None] * 11), 1e-6, 1, None, None, 0, None, None) == -1
     ok = [one] * 10
     assert lib.b200_gdn_verify_replay(*ok, 0, *([one] * 11), 1e-6, 1, one, one, 1 << 30, None, None) == -1
+    assert lib.b200_gdn_ring_fold(*([None] * 10), 1, None) == -1
+    assert lib.b200_gdn_ring_fold(C.c_void_p(4100), *([one] * 9), 1, None) == -2
     mis = [one] * 9 + [C.c_void_p(4100)]
     assert lib.b200_gdn_verify_replay(*mis, 4, *([one] * 11), 1e-6, 1, one, one, 1 << 30, None, None) == -2
 

@@ -145,3 +145,28 @@ def test_two_windows_chain_through_the_ring():
     assert ops.read_status(st) == 0
     ok, err, nbad = close_bf16(bf16_to_np(out2), bf16_to_np(ref2))
     assert ok, f"second window: max err {err}, {nbad} outside tolerance"
+
+
+def test_ring_fold_matches_the_state_the_ring_stands_for():
+    # fold the committed entries (high + low parts) into the checkpoint: equals the state the oracle says the ring
+    # stands for; requests with an empty ring and padded requests leave their slots alone
+    cfg = synth.gdn_replay(seed=95, B=4)
+    cfg["write_pos"][cfg["ring_idx"].long()] = torch.tensor([0, 5, 16, 9], dtype=torch.int32)
+    cfg["dlo_ring"] = (torch.randn(cfg["d_ring"].shape) * 1e-3).to(torch.bfloat16)
+    cfg["klo_ring"] = (torch.randn(cfg["k_ring"].shape) * 1e-3).to(torch.bfloat16)
+    cfg["state_idx"][3] = -1
+    c = _np(cfg)
+    d = {k: v.to(dev()).clone() for k, v in cfg.items()}
+    ops.gdn_ring_fold(d["checkpoint"], d["d_ring"], d["dlo_ring"], d["k_ring"], d["klo_ring"], d["g_ring"], d["state_idx"],
+                      d["ring_idx"], d["write_pos"], d["cache_base"])
+    torch.cuda.synchronize()
+    got = d["checkpoint"].cpu().numpy()
+    want = c["checkpoint"].copy()
+    for i in range(3):
+        rs, ss = c["ring_idx"][i], c["state_idx"][i]
+        want[ss] = ogdn.ring_state(c["checkpoint"][ss], c["d_ring"][rs] + c["dlo_ring"][rs], c["k_ring"][rs] + c["klo_ring"][rs],
+                                   c["g_ring"][rs], c["write_pos"][rs], c["cache_base"][rs])
+    assert np.abs(got - want).max() < 1e-4
+    untouched = np.ones(len(want), dtype=bool)
+    untouched[c["state_idx"][1:3]] = False          # wp = 0 and the padded request leave their slots alone
+    assert np.array_equal(got[untouched], c["checkpoint"][untouched])
