@@ -1,19 +1,22 @@
-"""Benchmark of the decode MoE hot path.
+"""Benchmark of the decode / speculative-verify hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload step|moe_int8]
 
-Workload (`config.workload`): the int8 W8A8 routed MoE block at decode, 256 tokens, hidden 2048,
-512 experts, top-10, intermediate 512, shared expert with sigmoid gate, Zipf(1.1)-skewed router
-bias; synthetic random-init weights (N(0, 0.02) quantised per output channel) and bf16 N(0, 1)
-activations.  One step = one pass of the block: gate -> top-k -> routing lists -> quantise +
-permute -> gate/up GEMM + SwiGLU -> re-quantise -> down GEMM + unpermute -> combine.
-With the Zipf bias ~90 experts are hit per step: ~300 MB of weights and rows are streamed per step,
-more than the 126 MB L2, so no flush is needed.
+Default workload (`config.workload`): one whole decode + verify step of the 48-layer stack (36 Gated DeltaNet + 12
+gated-attention layers, every layer with a 512-expert top-10 fp8 MoE + shared expert; LM head 151936 x 2048 fp8 with
+greedy argmax) for a batch of 64 sequences x 4 draft tokens at 8192 tokens of context, random-init weights and
+synthetic state / KV pages drawn from a seed.  One step = one CUDA-graph replay of every launch of the stack.
+On N GPUs the same batch is split N ways (sequences, experts and vocabulary; "strong" scaling: the batch is the
+configuration's, 64): the expert exchange is peer stores over NVLink plus the library's bounded barrier, no NCCL
+call in the step.  A step streams every expert that is hit (about 1.6 GB per layer on one GPU), far more than the
+126 MB L2, so no flush is needed.
 
-One JSON line on stdout (rank 0): tokens/s through the layer with inputs resident in HBM
-(`value`), the same through the public API from pinned host memory (`e2e`), the roofline of the
-dominant kernel (gate/up GEMM) from CUDA events, and the CPU baseline (the C restatement of the
-same arithmetic on the host cores).  `--impl reference` times only that CPU restatement.
+One JSON line on stdout (rank 0): rows (draft tokens) verified per second with inputs resident in HBM (`value`),
+the same from pinned host memory to pinned host memory (`e2e`), the roofline of the dominant kernel (the fp8 gate/up
+expert GEMM) from CUDA events, the CPU baseline (the C restatement of the same arithmetic on the host cores, on a
+stated sample) and, under `kernels`, every other kernel of the path at its named configuration (1 GPU only).
+`--workload moe_int8` measures the int8 W8A8 MoE block at 256 tokens instead (BASELINE configuration 2).
+`--impl reference` times only the CPU restatement.
 """
 from __future__ import annotations
 
@@ -31,6 +34,10 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 T, H, I, E, K = 256, 2048, 512, 512, 10
+LAYERS, BATCH, CTX, VOCAB = 48, 64, 8192, 151936
+STEP_WORKLOAD = ("48-layer decode+verify step: batch 64 x 4 draft tokens, ctx 8192, 36 GDN + 12 gated-attention layers, "
+                 "512 fp8 experts top-10 + shared per layer, LM head 151936 fp8 + greedy argmax")
+STEP_METRIC = "decode-step tokens/s @bs64 (draft-token rows verified per second; us/layer = ms_per_step*1000/48)"
 WORKLOAD = "int8 W8A8 routed MoE block at decode: T=256 H=2048 E=512 top-10 I=512 + shared expert, Zipf(1.1) router bias"
 METRIC = "decode tokens/s through one MoE layer (us/layer = ms_per_step*1000)"
 
@@ -181,6 +188,20 @@ def other_kernels(dev, steps, warmup, only=None):
     except Exception as exc:  # noqa: BLE001
         out["fp8_peak_error"] = repr(exc)[:120]
     out["fp8_dense_tflops_measured"] = fp8_peak
+    # dense int8 GEMM peak (torch._int_mm, 8192^3), the denominator of the int8 tensor-pipe fractions
+    int8_peak = None
+    try:
+        if only is not None:
+            raise RuntimeError("skipped in single-kernel mode")
+        a8 = torch.randint(-127, 128, (8192, 8192), device=dev, dtype=torch.int8)
+        b8 = torch.randint(-127, 128, (8192, 8192), device=dev, dtype=torch.int8).t()
+        ms = min(timed(lambda: torch._int_mm(a8, b8), 5, graph=False) for _ in range(3))
+        int8_peak = 2 * 8192 ** 3 / (ms * 1e-3) / 1e12
+        del a8, b8
+    except Exception as exc:  # noqa: BLE001
+        out["int8_peak_error"] = repr(exc)[:120]
+    out["int8_dense_tops_measured"] = int8_peak
+    out["_int8_peak"] = int8_peak
 
     # Gated DeltaNet verify: B = 32 x 4 drafts; 4 rotating copies of the state (268 MB > L2)
     st = ops.new_status(dev)
@@ -200,8 +221,9 @@ def other_kernels(dev, steps, warmup, only=None):
         _moe_fp8_router_entry(dev, ops, synth, timed, st, out, hbm, want)
     if want("moe_w8a8_prefill"):
         _moe_w8a8_prefill_entry(dev, ops, synth, timed, st, out)
-    if want("decode_step"):
-        _decode_step_entry(dev, timed, out)
+    out.pop("_int8_peak", None)
+    if want("moe_w8a8_t256"):
+        _moe_w8a8_block_entry(dev, ops, synth, timed, st, out, hbm, which)
     return out
 
 
@@ -238,7 +260,9 @@ def _moe_w8a8_prefill_entry(dev, ops, synth, timed, st, out):
             out[f"moe_w8a8_prefill_t{Tn}"] = {
                 "config": f"T={Tn}, E=512, top-10 + shared, int8 W8A8, Zipf(1.1) (router, lists, 4 GEMM-chain launches, combine)",
                 "ms": ms, "tokens_per_s": Tn / ms * 1e3, "ms_quant_up_hquant_down": ms_gemm,
-                "int8_tops_gemm_chain": iops / ms_gemm / 1e9, "active_experts": act,
+                "int8_tops_gemm_chain": iops / ms_gemm / 1e9,
+                "frac_of_measured_int8_dense": (iops / ms_gemm / 1e9 / out["_int8_peak"]) if out.get("_int8_peak") else None,
+                "active_experts": act,
                 "blocks": int(lists.nblocks.item()), "weight_bytes_once": act * 3 * Hh * Ii,
                 "status": ops.read_status(st)}
             del lists, scr, ws, cache, res
@@ -248,23 +272,39 @@ def _moe_w8a8_prefill_entry(dev, ops, synth, timed, st, out):
     torch.cuda.empty_cache()
 
 
-def _decode_step_entry(dev, timed, out):
-    # the whole 48-layer stack (36 GDN + 12 attention layers, fp8 experts, LM head) for one GPU's share of the
-    # 64-sequence batch under 8-way batch sharding: 8 sequences x 4 drafts, 8192 tokens of context each
+def _moe_w8a8_block_entry(dev, ops, synth, timed, st, out, hbm, which):
+    # the int8 W8A8 MoE block at 256 tokens with a Zipf(1.1) router bias (BASELINE configuration 2): the whole block as
+    # one CUDA graph, and its two GEMMs alone
     import torch
-    from bundles_b200 import decode_step, ops
+    from bundles_b200 import moe_block
     try:
         torch.cuda.empty_cache()
-        step = decode_step.DecodeStep(layers=48, B=8, ctx=8192, device=dev)
-        x = torch.randn(step.T, 2048, device=dev).to(torch.bfloat16)
-        ms = timed(lambda: step.step(x), n=5)
-        out["decode_step"] = {"config": "48 layers (12 attention, 36 GDN), 512 fp8 experts top-10 per layer, B=8 x 4 drafts, "
-                                        "ctx 8192, LM head 151936 (one GPU, no expert parallelism)",
-                              "ms": ms, "launches_per_step": step.launches, "status": ops.read_status(step.status),
-                              "device_memory_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1)}
-        del step
+        c = synth.moe_w8a8(T=T, H=H, I=I, E=E, device=dev)
+        w = ops.MoeW8A8Weights(c["w13"], c["s13"], c["w2"], c["s2"], c["sh13"], c["shs13"], c["sh2"], c["shs2"])
+        block = moe_block.MoeBlockW8A8(c["wr"], w, c["gate_w"], K, bias=c["bias"], use_graph=False)
+        ms = timed(lambda: block(c["x"]))
+        b = block._buffers(T, dev)
+        plain = dict(graph=False)
+        ms_up = timed(lambda: ops.moe_w8a8(c["x"], w, b["lists"], cache=b["cache"], ws=b["ws"], status=st, stages=ops.STAGE_UP),
+                      **plain)
+        ms_dn = timed(lambda: ops.moe_w8a8(c["x"], w, b["lists"], cache=b["cache"], ws=b["ws"], status=st, stages=ops.STAGE_DOWN),
+                      **plain)
+        counts = b["lists"].counts.cpu()
+        active, rows = int((counts > 0).sum().item()), int(counts.sum().item())
+        up_bytes = active * (2 * I * H + 2 * I * 4) + rows * (H + 4) + rows * I * 2
+        dn_bytes = active * (H * I + H * 4) + rows * (I + 12) + rows * H * 2
+        out["moe_w8a8_t256"] = {"config": "int8 W8A8 MoE block at decode: T=256, E=512, top-10 + shared, Zipf(1.1) router bias "
+                                          "(router, lists, quantise, up, re-quantise, down, combine)",
+                                "ms": ms, "tokens_per_s": T / ms * 1e3, "active_experts": active, "rows": rows,
+                                "up": {"ms": ms_up, "algorithmic_bytes": up_bytes, "achieved_gbs": up_bytes / ms_up / 1e6,
+                                       "frac": up_bytes / ms_up / 1e6 / hbm},
+                                "down": {"ms": ms_dn, "algorithmic_bytes": dn_bytes, "achieved_gbs": dn_bytes / ms_dn / 1e6,
+                                         "frac": dn_bytes / ms_dn / 1e6 / hbm},
+                                "bound": "hbm", "peak_source": which,
+                                "status": max(ops.read_status(st), ops.read_status(block.status))}
+        del block, c, w
     except Exception as exc:  # noqa: BLE001
-        out["decode_step"] = {"error": repr(exc)[:200]}
+        out["moe_w8a8_t256"] = {"error": repr(exc)[:300]}
     torch.cuda.empty_cache()
 
 
@@ -411,6 +451,280 @@ def _moe_fp8_router_entry(dev, ops, synth, timed, st, out, hbm, want):
         out[f"router_t{Tn}"] = {"ms": ms, "flops": 2 * Tn * 512 * 2048, "bytes": 4 * 512 * 2048 + 2 * Tn * 2048}
 
 
+# ---------------------------------------------------------------------------------------------------------
+# the decode + verify step (default workload)
+# ---------------------------------------------------------------------------------------------------------
+def _cpu_layer_sample(rows=256, seed=1005):
+    """Host-side inputs of the CPU baseline: the fp8 weights of ONE Gated-DeltaNet-type layer at full width (router,
+    512 experts + shared, in_proj, out_proj) and `rows` activation rows.  Thirty-two distinct experts are drawn and
+    repeated sixteen times (CPU time does not depend on the values; the footprint, 1.6 GB, is the real one)."""
+    import numpy as np
+    import torch
+    from bundles_b200.prepare import quant_fp8_blocks
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *sh, std=0.02: torch.randn(*sh, generator=g) * std  # noqa: E731
+    base = 32
+    w13, s13 = quant_fp8_blocks(rn(base, 2 * I, H))
+    w2, s2 = quant_fp8_blocks(rn(base, H, I))
+    rep = E // base
+    d = dict(w13=np.tile(w13.numpy(), (rep, 1, 1)), s13=np.tile(s13.numpy(), (rep, 1, 1)),
+             w2=np.tile(w2.numpy(), (rep, 1, 1)), s2=np.tile(s2.numpy(), (rep, 1, 1)))
+    for name, shape in (("sh13", (2 * I, H)), ("sh2", (H, I)), ("in", (12416, H)), ("out", (H, 4096))):
+        q, sc = quant_fp8_blocks(rn(*shape))
+        d[name], d[name + "_s"] = q.numpy(), sc.numpy()
+    d["wr"] = rn(E, H).numpy()
+    bits = lambda t: t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)  # noqa: E731
+    d["x"] = bits(torch.randn(rows, H, generator=g))
+    d["core"] = torch.randn(rows, 4096, generator=g).to(torch.bfloat16).float().numpy()
+    d["gate_w"] = bits(rn(H))
+    return d
+
+
+def _cpu_layer_seconds(d):
+    """One pass of the sample: in_proj GEMM, out_proj GEMM, router, fp8 expert block + combine (C, OpenMP)."""
+    import numpy as np
+    from oracle import clib
+    t0 = time.perf_counter()
+    xf = (d["x"].astype(np.uint32) << 16).view(np.float32)
+    xq, xs = clib.quant_fp8_groups(xf)
+    clib.gemm_fp8_blocks(xq, xs, d["in"][:12352], d["in_s"])
+    cq, cs = clib.quant_fp8_groups(d["core"])
+    clib.gemm_fp8_blocks(cq, cs, d["out"], d["out_s"])
+    logits = clib.gate_logits(d["x"], d["wr"], None)
+    ids, wts = clib.topk(logits, K)
+    clib.moe_fp8(d["x"], ids, wts, d["w13"], d["s13"], d["w2"], d["s2"], d["sh13"], d["sh13_s"], d["sh2"], d["sh2_s"],
+                 d["gate_w"])
+    return time.perf_counter() - t0
+
+
+CPU_SAMPLE = ("one layer of the 48 at all 256 rows: in_proj + out_proj fp8 GEMMs, router, fp8 expert block + combine "
+              "(C + OpenMP restatement); the step is taken as 48 x this, the GDN recurrence, attention core and LM head "
+              "are left out, so the CPU figure is an upper bound on its rate")
+
+
+def cpu_step_baseline(repeats=2):
+    from oracle import clib
+    cores = clib.use_all_cores()
+    d = _cpu_layer_sample(4 * BATCH)
+    best = min(_cpu_layer_seconds(d) for _ in range(repeats))
+    return {"value": 4 * BATCH / (LAYERS * best), "unit": "tokens/s", "cores": cores, "kind": "port", "sample": CPU_SAMPLE,
+            "seconds_per_layer": best}
+
+
+def run_step_reference(args, rank, world):
+    """`--impl reference` for the step workload: the CPU restatement on the host cores, one sample per step."""
+    if rank != 0:
+        return
+    from oracle import clib
+    cores = clib.use_all_cores()
+    d = _cpu_layer_sample(4 * BATCH)
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt = _cpu_layer_seconds(d)
+        if i >= args.warmup:
+            times.append(dt)
+    per_layer = sum(times) / len(times)
+    ms = 1000.0 * per_layer * LAYERS
+    val = 4 * BATCH / (ms / 1000.0)
+    line = {"impl": "reference", "metric": STEP_METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8 e4m3 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": STEP_WORKLOAD, "l2": "not applicable (CPU)"},
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": CPU_SAMPLE,
+                             "seconds_per_layer": per_layer},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def _ep_check(dev, ep, world, rank):
+    """Before anything is timed: a 4-layer stack (3 GDN + 1 attention layer) at full width (batch 64, 512 experts,
+    full vocabulary, 512 tokens of context) run in the expert-parallel form, against the one-GPU form of the same
+    stack on rank 0.  Tokens and final hidden rows must be equal bit for bit.  On one GPU the expert-parallel form
+    runs as two virtual ranks."""
+    import torch
+    import torch.distributed as dist
+    from bundles_b200 import decode_step, ops, parallel
+    kw = dict(layers=4, B=BATCH, ctx=512, vocab=VOCAB, experts=E, seed=77, device=dev)
+    g = torch.Generator(device=dev).manual_seed(78)
+    x = torch.randn(4 * BATCH, H, generator=g, device=dev).to(torch.bfloat16)
+    res = {"form": None, "tokens_equal": None, "hidden_equal": None, "status": None}
+    if world == 1:
+        single = decode_step.DecodeStep(**kw)
+        want = single.step(x)
+        vg = parallel.VirtualEpGroup(2, dev)
+        ranks = [decode_step.DecodeStep(ep=vg.view(r), **kw) for r in range(2)]
+        Tl = ranks[0].T
+        got = decode_step.step_virtual(ranks, [x[r * Tl:(r + 1) * Tl].contiguous() for r in range(2)])
+        torch.cuda.synchronize()
+        hid = torch.cat([r.final_hidden for r in ranks])
+        res.update(form="2 virtual ranks on one GPU", tokens_equal=bool(torch.equal(got[0], want) and torch.equal(got[1], want)),
+                   hidden_equal=bool(torch.equal(hid, single.final_hidden)),
+                   status=max(ops.read_status(single.status), *[ops.read_status(r.status) for r in ranks]))
+        del single, ranks, vg
+    else:
+        part = decode_step.DecodeStep(ep=ep, **kw)
+        Tl = part.T
+        got = part.step(x[rank * Tl:(rank + 1) * Tl].contiguous())
+        torch.cuda.synchronize()
+        hid = [torch.empty_like(part.final_hidden) for _ in range(world)]
+        dist.all_gather(hid, part.final_hidden.contiguous())
+        flag = torch.ones(1, device=dev)
+        st = ops.read_status(part.status)
+        if rank == 0:
+            single = decode_step.DecodeStep(**kw)
+            want = single.step(x)
+            torch.cuda.synchronize()
+            res.update(form=f"{world} ranks against the one-GPU step on rank 0", tokens_equal=bool(torch.equal(got, want)),
+                       hidden_equal=bool(torch.equal(torch.cat(hid), single.final_hidden)))
+            st = max(st, ops.read_status(single.status))
+            del single
+        sts = torch.tensor([st], device=dev)
+        dist.all_reduce(sts, op=dist.ReduceOp.MAX)
+        res["status"] = int(sts.item())
+        del part, flag
+    torch.cuda.empty_cache()
+    res["ok"] = bool(res["tokens_equal"] and res["hidden_equal"] and res["status"] == 0) if (world == 1 or rank == 0) else None
+    return res
+
+
+def run_step(args, rank, world, local, dev):
+    """The default workload on `world` GPUs (one process each)."""
+    import torch
+    import torch.distributed as dist
+    from bundles_b200 import decode_step, ops, parallel
+    ep = parallel.EpGroup(device=dev) if world > 1 else None
+    check = None if args.no_ep_check else _ep_check(dev, ep, world, rank)
+    t_build = time.perf_counter()
+    step = decode_step.DecodeStep(layers=args.layers, B=BATCH, ctx=CTX, vocab=VOCAB, experts=E, seed=1005, device=dev, ep=ep)
+    torch.cuda.synchronize()
+    t_build = time.perf_counter() - t_build
+    Tl, Ta = step.T, step.T_all
+    g = torch.Generator(device=dev).manual_seed(9000)
+    x_all = torch.randn(Ta, H, generator=g, device=dev).to(torch.bfloat16)
+    x_dev = x_all[rank * Tl:(rank + 1) * Tl].contiguous()
+    x_host = x_dev.cpu().pin_memory()
+    n_tok = Ta if world > 1 else Tl
+    tok_host = torch.empty(n_tok, dtype=torch.int32).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # one eager step (one-time set-up inside the operators), then the whole step as one CUDA graph
+    step.step(x_dev)
+    barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        tokens = step.step(x_dev)
+    barrier()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_step = timed(graph.replay, args.steps, args.warmup)
+
+    def e2e_step():
+        # the user's call: this rank's embedded rows from pinned host memory in, the step, the tokens out to pinned
+        # host memory, all on the current stream
+        x_dev.copy_(x_host, non_blocking=True)
+        graph.replay()
+        tok_host.copy_(tokens, non_blocking=True)
+
+    ms_e2e = timed(e2e_step, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # the dominant kernel alone: the fp8 gate/up expert GEMM (+ SwiGLU) of every layer in turn, each over its own
+    # weights (so that every launch streams from HBM), with the routing lists the last layer left behind
+    lists = step.lists
+    src = step.x_all if world > 1 else step.final_hidden
+
+    def up_all_layers():
+        for L in step.layers:   # this stage writes h into the workspace only; `cache` is not touched
+            ops.moe_fp8(src, L["w"], lists, cache=step.cache, ws=step.moe_ws, status=step.status, stages=ops.STAGE_UP)
+
+    ms_up = timed(up_all_layers, max(2, args.steps // 4), 1) / len(step.layers)
+    counts = lists.counts.cpu()
+    active = int((counts > 0).sum().item())
+    rows = int(counts.sum().item())
+    up_bytes = active * (2 * I * H + 2 * (I // 128) * (H // 128) * 4) + rows * (H + (H // 128) * 4) + rows * I * 2
+    status = torch.tensor([ops.read_status(step.status)], device=dev)
+    if world > 1:
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    peak, which = peaks()
+    mem_gb = round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1)
+    launches = step.launches
+    if rank != 0:
+        del graph
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    achieved = up_bytes / (ms_up * 1e-3) / 1e9
+    exchange = ("1 GPU" if world == 1 else
+                f"{world} GPUs: {BATCH // world} sequences, {E // world} experts and 1/{world} of the vocabulary per rank; rows "
+                "and routing dispatched by peer stores into every rank's symmetric-memory buffers, weighted rows stored by "
+                "the down-GEMM epilogue into the home rank's cache, (max, argmax) pairs gathered by peer stores; the library's "
+                "bounded barrier kernel between the phases (no NCCL call in the step)")
+    line = {
+        "metric": STEP_METRIC, "value": Ta / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "us_per_layer": ms_step * 1000.0 / len(step.layers),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8 e4m3 (fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": STEP_WORKLOAD, "layers": len(step.layers), "batch": BATCH, "rows_per_step": Ta,
+                   "parallelism": exchange,
+                   "l2": f"every layer streams its own expert weights ({active} experts hit on this rank in the last layer, "
+                         f"{up_bytes / 1e6:.0f} MB for the gate/up GEMM alone), {len(step.layers)} layers per step: far more than "
+                         "the 126 MB L2; no flush"},
+        "e2e": {"value": Ta / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": Tl * H * 2,
+                "d2h_bytes_per_step": n_tok * 4, "ms_per_step": ms_e2e},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"kernel": "moe_gemm_f8_kernel<UP> (fp8 gate/up expert GEMM + SwiGLU)", "bound": "hbm", "achieved": achieved,
+                     "peak": peak, "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": F8_UP_TRAFFIC_RATIO * up_bytes if F8_UP_TRAFFIC_RATIO else None,
+                     "traffic_source": "DRAM read + write of one launch of this kernel under ncu on a smaller case "
+                                       "(profiles/), scaled by this launch's algorithmic bytes",
+                     "algorithmic_bytes": up_bytes, "ms": ms_up, "active_experts": active, "rows": rows},
+        "clocks": clocks, "device_status": int(status.item()), "ep_check": check,
+        "launches_per_step": launches, "device_memory_gb": mem_gb, "build_seconds": round(t_build, 1),
+    }
+    del graph, step
+    torch.cuda.empty_cache()
+    if world == 1 and not args.no_kernels:
+        try:
+            line["kernels"] = other_kernels(dev, args.steps, args.warmup)
+        except Exception as exc:  # noqa: BLE001  (the headline line must still be printed)
+            line["kernels"] = {"error": repr(exc)[:300]}
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_step_baseline()
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one launch of moe_gemm_f8_kernel<UP> divided by its algorithmic bytes, from the ncu
+# capture summarised under profiles/ (None until a capture exists)
+F8_UP_TRAFFIC_RATIO = None
+
+
+
 def run_expert_parallel(args, rank, world, dev, cfg):
     """N > 1: experts split over the ranks (512 / N each), every rank brings its own 256 tokens (weak
     scaling: rows per rank stay ~2560 routed + 256 shared).  All ranks draw the SAME layer (seed) and keep
@@ -496,13 +810,17 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="step", choices=["step", "moe_int8"],
+                    help="step: the 48-layer decode+verify step at batch 64 (default); moe_int8: the int8 W8A8 MoE block at 256 tokens")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layers of the step workload (48; fewer only for quick checks)")
+    ap.add_argument("--no-ep-check", action="store_true", help="skip the expert-parallel == one-GPU check before the timed runs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel measurements of the other rows")
     ap.add_argument("--parallel", default="ep", choices=["ep", "replicas"],
                     help="N > 1: expert-parallel (experts split over ranks) or independent replicas")
     ap.add_argument("--only-kernel", default=None,
                     choices=["gdn_verify", "attn_verify", "attn_front", "lmhead_shard_argmax", "moe_fp8_t16", "router",
-                             "moe_w8a8_prefill", "decode_step"],
+                             "moe_w8a8_prefill", "moe_w8a8_t256"],
                     help="run one entry of `kernels` alone with plain launches (a small target for an ncu capture) and exit")
     args = ap.parse_args()
     if args.only_kernel:
@@ -516,7 +834,7 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        (run_step_reference if args.workload == "step" else run_reference)(args, rank, world)
         return
 
     import torch
@@ -527,6 +845,9 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "step":
+        run_step(args, rank, world, local, dev)
+        return
 
     # weights: the CPU random stream at rank 0 of a 1-GPU run (so the CPU baseline sees the same bytes),
     # a CUDA stream elsewhere (every rank holds a full replica of the layer and its own 256 tokens)

@@ -39,6 +39,14 @@ PROTOTYPES = {
     "b200_moe_fp8_workspace_bytes": (sz, [i32, i32, i32, i32]),
     "b200_moe_fp8": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(MoeWeights), C.POINTER(MoeLists), vp, vp, sz, vp,
                            i32, vp, vp]),
+    "b200_moe_fp8_ep": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(MoeWeights), C.POINTER(MoeLists), C.POINTER(vp), i32,
+                              i32, i32, vp, sz, vp, vp]),
+    "b200_ep_barrier": (i32, [C.POINTER(vp), vp, i32, i32, i32, C.c_ulonglong, vp, vp]),
+    "b200_ep_put": (i32, [vp, sz, sz, C.POINTER(vp), i32, vp]),
+    "b200_set_wait_budget_ns": (i32, [C.c_ulonglong]),
+    "b200_selftest_wait_expiry": (i32, [vp, vp]),
+    "b200_dense_fp8_split": (i32, [vp, i32, i32, vp, vp, i32, i32, C.POINTER(i32), C.POINTER(vp), C.POINTER(i32), vp, sz,
+                                   vp, vp]),
     "b200_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "b200_moe_combine_norm": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, f32, vp, vp]),
     "b200_attn_front_workspace_bytes": (sz, [i32]),

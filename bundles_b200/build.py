@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200nodes.so")
-SOURCES = ["host.cu", "router.cu", "moe.cu", "moe_fp8.cu", "attn.cu", "attn_verify.cu", "gdn.cu"]
+SOURCES = ["host.cu", "router.cu", "moe.cu", "moe_fp8.cu", "attn.cu", "attn_verify.cu", "gdn.cu", "ep.cu"]
 NVCC_FLAGS = ["-shared", "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
               "-std=c++17", "-cudart", "static"]
 

@@ -19,7 +19,8 @@ import copy
 
 import torch
 
-from bundles_b200 import moe_block, ops, synth
+from bundles_b200 import moe_block, ops
+from bundles_b200 import prepare as prepare_q
 
 EXPERT_FORMAT = "w8a8"      # "w8a8": int8 per-output-channel; "fp8": e4m3 with 128 x 128 block scales
 _prepared = {}              # id(module) -> replica, so that a second prepare reuses the private copy
@@ -50,7 +51,7 @@ def _check_moe(mlp):
 
 def _quantise(mlp, fmt):
     """Private quantised copy of the experts (the stock bf16 weights stay untouched)."""
-    q = synth.quant_int8_rows if fmt == "w8a8" else synth.quant_fp8_blocks
+    q = prepare_q.quant_int8_rows if fmt == "w8a8" else prepare_q.quant_fp8_blocks
     E = mlp.experts.w13_weight.shape[0]
     parts13, parts2 = [], []
     for e0 in range(0, E, 32):          # in slices: the fp32 staging copy stays small

@@ -12,7 +12,8 @@ from __future__ import annotations
 
 import torch
 
-from bundles_b200 import ops, parallel, synth
+from bundles_b200 import ops, parallel
+from bundles_b200 import prepare as prepare_q
 
 _copies = {}   # (device index, data_ptr) -> (codes uint8 [V,H], scales fp32 [V/128, H/128], shard_lo)
 
@@ -37,7 +38,7 @@ def _private_copy(weight: torch.Tensor, group=None):
         w = weight[lo:hi].float()
         if pad:
             w = torch.cat([w, torch.zeros(pad, H, device=w.device)])
-        codes, scales = synth.quant_fp8_blocks(w)
+        codes, scales = prepare_q.quant_fp8_blocks(w)
         got = (codes[:rows].contiguous(), scales.contiguous(), lo)
         _copies[key] = got
     return got

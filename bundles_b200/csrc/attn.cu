@@ -19,6 +19,8 @@
 
 namespace b200 {
 
+B200_DEFINE_WAIT_BUDGET_SETTER(set_wait_budget_attn)
+
 constexpr int AT_H = 2048, AT_HD = 256, AT_HQ = 16, AT_HKV = 2, AT_ROT = 64;
 constexpr int AT_NCOLS = AT_HQ * 2 * AT_HD + 2 * AT_HKV * AT_HD;  // 9216
 constexpr int AT_NT = AT_NCOLS / AT_HD;                           // 36 head tiles
@@ -325,13 +327,8 @@ extern "C" int b200_attn_front(const void* x, int T, const void* w, const float*
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmX, xq, T, AT_H, 128, "attn activations"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, AT_NCOLS, AT_H, 128, "attn weight"))) return rc;
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaFuncSetAttribute(attn_front_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM);
-    attr_done[dev] = true;
-  }
+  static DeviceOnce once;
+  once.run([] { cudaFuncSetAttribute(attn_front_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM); });
   b200::b200_quant_rows_f8_launch(x, T, AT_H, xq, xs, st);
   AttnArgs a{xs, w_s, static_cast<const bf16*>(q_norm_w), static_cast<const bf16*>(k_norm_w), positions, cos_sin,
              max_pos, eps, T, out_fp8, q, static_cast<bf16*>(gate), k, v, status};

@@ -22,6 +22,8 @@
 
 namespace b200 {
 
+B200_DEFINE_WAIT_BUDGET_SETTER(set_wait_budget_attn_verify)
+
 constexpr int AV_D = 256, AV_HQ = 16, AV_HKV = 2, AV_GQ = 8, AV_NT = 4, AV_ROWS = AV_GQ * AV_NT;  // 32 rows
 constexpr int AV_PAGE = 128;
 constexpr int AV_KTILE = AV_PAGE * AV_D;        // 32 KB e4m3: two [128 keys x 128 B] swizzled blocks
@@ -565,13 +567,8 @@ extern "C" int b200_attn_verify(const void* q, const void* gate, const void* k_n
   if ((rc = make_tmap_bytes_2d(&tmV, vcache, static_cast<uint64_t>(num_pages) * AV_HKV * AV_D, AV_PAGE, 256, "v cache")))
     return rc;
   if ((rc = make_tmap_bytes_2d(&tmQ, q, static_cast<uint64_t>(B) * AV_NT * AV_HQ, AV_D, 8, "q"))) return rc;
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaFuncSetAttribute(attn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AV_SMEM);
-    attr_done[dev] = true;
-  }
+  static DeviceOnce once;
+  once.run([] { cudaFuncSetAttribute(attn_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AV_SMEM); });
   launch_k(kv_append_kernel, dim3(B * AV_NT), dim3(256), 0, st, static_cast<const uint8_t*>(k_new),
            static_cast<const uint8_t*>(v_new), page_table, pt_stride, seqlens, static_cast<uint8_t*>(kcache),
            static_cast<uint8_t*>(vcache));

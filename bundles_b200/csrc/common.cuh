@@ -23,12 +23,20 @@ enum : int {
   ST_WAIT_TMEM_EMPTY = 104,
   ST_WAIT_STATE = 105,    // GDN: state tile never landed
   ST_WAIT_STORE = 106,
+  ST_WAIT_PEER = 107,     // expert-parallel barrier: a peer rank's flag never arrived
   ST_BAD_LIST = 110,      // routing list entry out of range (skipped)
 };
 
-// Every device-side wait is bounded: about one second of %globaltimer, after which the waiter
-// records a status code, raises the CTA's abort flag and every role winds down.
-constexpr unsigned long long WAIT_BUDGET_NS = 1000ull * 1000ull * 1000ull;
+// Every device-side wait is bounded: a budget of %globaltimer nanoseconds (one second unless the host changed it
+// with b200_set_wait_budget_ns), after which the waiter records a status code, raises the CTA's abort flag and
+// every role winds down.  The budget is a per-translation-unit device variable (the library is built without
+// relocatable device code); B200_DEFINE_WAIT_BUDGET_SETTER gives each unit the host function that writes its copy.
+constexpr unsigned long long WAIT_BUDGET_DEFAULT_NS = 1000ull * 1000ull * 1000ull;
+static __device__ unsigned long long g_wait_budget_ns = WAIT_BUDGET_DEFAULT_NS;
+#define B200_DEFINE_WAIT_BUDGET_SETTER(name)                                                              \
+  int name(unsigned long long ns) {                                                                       \
+    return static_cast<int>(cudaMemcpyToSymbol(b200::g_wait_budget_ns, &ns, sizeof(ns), 0, cudaMemcpyHostToDevice)); \
+  }
 
 __device__ __forceinline__ float bf2f(bf16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ bf16 f2bf(float v) { return __float2bfloat16_rn(v); }
@@ -99,7 +107,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try(bar, parity)) return true;
     if (((++spins) & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer() - t0 > WAIT_BUDGET_NS) {
+      if (globaltimer() - t0 > g_wait_budget_ns) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;

@@ -40,6 +40,8 @@
 
 namespace b200 {
 
+B200_DEFINE_WAIT_BUDGET_SETTER(set_wait_budget_gdn)
+
 constexpr int G_HK = 16, G_HV = 32, G_D = 128, G_NT = 4;
 constexpr int G_QDIM = G_HK * G_D;             // 2048
 constexpr int G_CONV = 2 * G_QDIM + G_HV * G_D;  // 8192
@@ -785,13 +787,8 @@ static int gdn_launch(const CUtensorMap& tmS, const GdnArgs& p, int B, void* ws,
   float* qk_ws = static_cast<float*>(ws);
   GdnOps* ops_ws = reinterpret_cast<GdnOps*>(qk_ws + static_cast<size_t>(B) * G_HK * G_QK_FLOATS);
   const int smem = static_cast<int>(sizeof(GdnStreamSmem)) + 1024;
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaFuncSetAttribute(gdn_stream_kernel<REPLAY>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    attr_done[dev] = true;
-  }
+  static DeviceOnce once;  // one per instantiation of this function template
+  once.run([smem] { cudaFuncSetAttribute(gdn_stream_kernel<REPLAY>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   launch_k(gdn_prep_kernel<REPLAY>, dim3(B * G_HK), dim3(512), 0, st, p, qk_ws, ops_ws);
   int grid = sm_count() * 3;

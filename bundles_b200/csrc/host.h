@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdarg.h>
+#include <mutex>
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -54,6 +55,30 @@ int make_tmap_f32_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
 void b200_quant_rows_f8_launch(const void* x, int T, int H, uint8_t* xq, float* xs, cudaStream_t st);
 
 int sm_count();  // SMs of the current device (cached per device)
+
+// One-time set-up per device (kernel attributes): `run(fn)` calls fn once for the current device, whichever
+// host thread gets there first.
+struct DeviceOnce {
+  std::once_flag flags[64];
+  template <typename F>
+  void run(F fn) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+      fn();
+      return;
+    }
+    std::call_once(flags[dev], fn);
+  }
+};
+
+// writers of each translation unit's copy of the device-side wait budget
+int set_wait_budget_router(unsigned long long ns);
+int set_wait_budget_moe(unsigned long long ns);
+int set_wait_budget_moe_fp8(unsigned long long ns);
+int set_wait_budget_attn(unsigned long long ns);
+int set_wait_budget_attn_verify(unsigned long long ns);
+int set_wait_budget_gdn(unsigned long long ns);
+int set_wait_budget_ep(unsigned long long ns);
 
 // Whether kernels are launched with programmatic stream serialization (on unless B200_NO_PDL is set in the
 // environment).  Every kernel of the library then starts while its predecessor in the stream drains: it does

@@ -17,6 +17,8 @@
 
 namespace b200 {
 
+B200_DEFINE_WAIT_BUDGET_SETTER(set_wait_budget_moe)
+
 // ---------------------------------------------------------------------------------------------------
 // activation quantise + permute (int8): one CTA per token
 // ---------------------------------------------------------------------------------------------------
@@ -162,6 +164,7 @@ struct GemmArgs {
   int ep_rows;          // routed slots per rank = tokens per rank x top-k
   int ep_rank, ep_tokens;  // this rank and tokens per rank: shared-expert rows are kept only for own tokens
   bf16* ep_cache[8];
+  int test_starve;  // self-test: the producer leaves out the token rows, so no stage ever completes and every wait runs out
 };
 
 constexpr int TILE_BYTES = 128 * 128;   // one 128-row x 128-byte operand tile
@@ -306,9 +309,11 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
             tma_load_2d(sA + TILE_BYTES, mapW, ks * 128, wrow + (UP ? p.I : 128), &full[stage]);
           }
-          if (big == 8) tma_load_2d(sB, &tmX128, ks * 128, row0, &full[stage]);
-          if (big == 4) tma_load_2d(sB, &tmX64, ks * 128, row0, &full[stage]);
-          for (int b = big; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
+          if (!p.test_starve) {
+            if (big == 8) tma_load_2d(sB, &tmX128, ks * 128, row0, &full[stage]);
+            if (big == 4) tma_load_2d(sB, &tmX64, ks * 128, row0, &full[stage]);
+            for (int b = big; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
+          }
           ++issued;
           if (++stage == C::STAGES) {
             stage = 0;
@@ -794,16 +799,13 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
   if ((rc = make_tmap_bytes_2d(&tmHq64, hq, rows, I, 64, "hq"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmHq128, hq, rows, I, 128, "hq"))) return rc;
 
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  static DeviceOnce once;
+  once.run([] {
     cudaFuncSetAttribute(moe_gemm_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<true>::SMEM);
     cudaFuncSetAttribute(moe_gemm_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<false>::SMEM);
-    attr_done[dev] = true;
-  }
+  });
 
-  if (stages == 0) stages = 15;
+  if ((stages & 15) == 0) stages |= 15;
   // tokens that get a shared-expert row: all of them, or this rank's own under expert parallelism
   int shared_lo = 0, shared_n = T;
   if ((ep_world & 0xff) >= 1) {
@@ -821,6 +823,7 @@ static int moe_w8a8_impl(const void* x, int T, int H, int I, int K, int E_local,
   a.H = H;
   a.total_rows = rows;
   a.status = status;
+  a.test_starve = (stages & B200_MOE_TEST_STARVE) ? 1 : 0;
   const int grid = sm_count();
 
   a.mtiles = I / 128;

@@ -16,6 +16,8 @@
 
 namespace b200 {
 
+B200_DEFINE_WAIT_BUDGET_SETTER(set_wait_budget_moe_fp8)
+
 constexpr int F8_TILE = 128 * 128;       // weight tile bytes per stage
 constexpr int F8_BTILE = 64 * 128;       // token tile bytes per stage (<= 64 rows)
 constexpr int F8_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
@@ -34,14 +36,15 @@ __device__ __forceinline__ float amax8(const uint4 v) {
 }
 
 // one CTA per token; 16 consecutive threads own one 128-channel group (8 channels each)
+// tokens [shared_lo, shared_lo + shared_n) also get their shared-expert row T*K + t
 __global__ void __launch_bounds__(256) quant_permute_f8_kernel(const bf16* __restrict__ x, int T, int H, int K,
                                                                const int32_t* __restrict__ row_of_pair,
-                                                               int with_shared, uint8_t* __restrict__ xq,
+                                                               int shared_lo, int shared_n, uint8_t* __restrict__ xq,
                                                                float* __restrict__ xs) {
   __shared__ int rows[40];
   const int t = blockIdx.x, tid = threadIdx.x;
   if (tid < K) rows[tid] = row_of_pair[t * K + tid];
-  if (tid == K) rows[K] = with_shared ? T * K + t : -1;
+  if (tid == K) rows[K] = (t >= shared_lo && t < shared_lo + shared_n) ? T * K + t : -1;
   __syncthreads();
   const int KG = H / 128;
   for (int c = tid * 8; c < H; c += 2048) {
@@ -94,6 +97,20 @@ struct F8Args {
   unsigned long long* lm_keys;  // [mtiles * 4][total_rows] packed (value, id) maxima, one row per (tile, warp)
   float* lm_logits;             // [total_rows, w_rows] or null
   int lm_shard_lo;
+  int lm_ld;                    // row pitch of lm_logits (elements)
+  // dense mode: output features [seg_lo[i], seg_lo[i+1]) go to seg_out[i] with row pitch seg_ld[i]; boundaries
+  // are multiples of 32, so the 32 features of a warp share one segment
+  int nseg;
+  int seg_lo[5];
+  int seg_ld[4];
+  bf16* seg_out[4];
+  // expert-parallel down epilogue: routed slot s of the gathered batch belongs to rank s / ep_rows, whose cache
+  // (this GPU's own, or a peer's mapped over NVLink) receives the row at local slot s % ep_rows; shared-expert
+  // rows are kept only for this rank's own tokens
+  int ep_world;                 // 0: single GPU, rows go to `cache`
+  int ep_rows, ep_rank, ep_tokens;
+  bf16* ep_cache[8];
+  int test_starve;  // self-test: the producer leaves out the token rows, so no stage ever completes and every wait runs out
 };
 
 constexpr int MODE_DOWN = 0, MODE_UP = 1, MODE_LM = 2, MODE_DENSE = 3;
@@ -106,7 +123,7 @@ struct F8Cfg {
   static constexpr int STAGES = UP ? 4 : 7;
   static constexpr int PW = UP ? 128 : 64;   // TMEM columns of one partial buffer
   static constexpr int NPB = 512 / PW;       // partial buffers
-  static constexpr int META_WARP = 32 * F8_MAXKG * 4 + 32 * 8 + 2 * F8_MAXKG * 4;
+  static constexpr int META_WARP = 32 * F8_MAXKG * 4 + 32 * 8 + 2 * F8_MAXKG * 4 + 32 * 8;
   static constexpr int META = 8 * META_WARP;  // per epilogue warp: activation scales, slot, weight of its 32 columns, weight scales
   static constexpr int SMEM = STAGES * STAGE + 1024 + 256 + META + F8_CACHED * 12;
   static constexpr int TMEM = 512;
@@ -278,7 +295,8 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           mbar_expect_tx(&full[stage], C::NA * F8_TILE + (nb16 > 2 ? F8_BTILE : nb16 * 2048));
           tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
           if (UP) tma_load_2d(sA + F8_TILE, mapW, ks * 128, wrow + p.I, &full[stage]);
-          if (nb16 > 2) {
+          if (p.test_starve) {
+          } else if (nb16 > 2) {
             tma_load_2d(sB, &tmX64, ks * 128, row0, &full[stage]);
           } else {
             for (int b = 0; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
@@ -353,6 +371,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     float* m_wt = m_as + 32 * F8_MAXKG;                                        // [32]
     int* m_slot = reinterpret_cast<int*>(m_wt + 32);                           // [32]
     float* m_ws = reinterpret_cast<float*>(m_slot + 32);                       // [2][F8_MAXKG] weight block scales
+    bf16** m_dst = reinterpret_cast<bf16**>(m_ws + 2 * F8_MAXKG);              // [32] destination row (down)
     const float* __restrict__ a_scale = p.a_scale;
     uint32_t g = 0;
     bool ok = true;
@@ -372,8 +391,27 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const int c = (l >> 4) * 32 + half * 16 + (l & 15);
         m_as[(i - l * p.ksteps) * 32 + l] = c < n ? a_scale[static_cast<size_t>(row0 + c) * p.ksteps + (i - l * p.ksteps)] : 0.f;
       }
-      m_slot[lane] = pre.slot < p.total_rows ? pre.slot : -1;
+      const int slot = pre.slot < p.total_rows ? pre.slot : -1;
+      m_slot[lane] = slot;
       m_wt[lane] = pre.wt;
+      if (MODE == MODE_DOWN) {
+        bf16* dst = nullptr;
+        if (slot >= 0) {
+          if (p.ep_world >= 1) {
+            const int routed = p.ep_rows * p.ep_world;
+            if (slot < routed) {
+              const int home = slot / p.ep_rows;
+              dst = p.ep_cache[home] + static_cast<size_t>(slot - home * p.ep_rows) * p.H;
+            } else {  // shared-expert row of token t: row ep_rows + local t of this rank's own cache
+              const int t = slot - routed, home = t / p.ep_tokens;
+              if (home == p.ep_rank) dst = p.ep_cache[home] + static_cast<size_t>(p.ep_rows + t - home * p.ep_tokens) * p.H;
+            }
+          } else {
+            dst = p.cache + static_cast<size_t>(slot) * p.H;
+          }
+        }
+        m_dst[lane] = dst;
+      }
     };
     int staged_blk = -1;
     if (LM) stage_block(0, p.total_rows);  // the dense modes have one block of token rows: staged once
@@ -441,11 +479,14 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (DENSE) {
         // plain projection: out[token][feature] = bf16(acc)
         if (r < p.w_rows) {
-          bf16* __restrict__ o = p.h_out + r;
+          int sg = 0;
+          while (sg + 1 < p.nseg && r >= p.seg_lo[sg + 1]) ++sg;
+          bf16* __restrict__ o = p.seg_out[sg] + (r - p.seg_lo[sg]);
+          const size_t ld = static_cast<size_t>(p.seg_ld[sg]);
 #pragma unroll
           for (int l = 0; l < 32; ++l) {
             const int c = (l >> 4) * 32 + half * 16 + (l & 15);
-            if (c < n) o[static_cast<size_t>(c) * p.w_rows] = f2bf(acc_a[l]);
+            if (c < n) o[static_cast<size_t>(c) * ld] = f2bf(acc_a[l]);
           }
         }
       } else if (LM) {
@@ -461,7 +502,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           mv[l] = live ? acc_a[l] : __int_as_float(0x7fc00000);
           if (p.lm_logits && live) {
             const int c = (l >> 4) * 32 + half * 16 + (l & 15);
-            if (c < n) p.lm_logits[static_cast<size_t>(c) * p.w_rows + r] = acc_a[l];
+            if (c < n) p.lm_logits[static_cast<size_t>(c) * p.lm_ld + r] = acc_a[l];
           }
         }
 #pragma unroll
@@ -513,11 +554,11 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
         }
       } else {
-        bf16* __restrict__ cache = p.cache + r;
 #pragma unroll
         for (int l = 0; l < 32; ++l) {
           const int c = (l >> 4) * 32 + half * 16 + (l & 15);
-          if (c < n && m_slot[l] >= 0) cache[static_cast<size_t>(m_slot[l]) * p.H] = f2bf(__fmul_rn(acc_a[l], m_wt[l]));
+          bf16* dst = m_dst[l];
+          if (c < n && dst != nullptr) dst[r] = f2bf(__fmul_rn(acc_a[l], m_wt[l]));
         }
       }
     }
@@ -539,7 +580,7 @@ extern "C" int b200_trace_read(unsigned long long* host) {
 
 // x bf16 [T, H] -> e4m3 rows [T, H] + scales [T, H/128] in token order (no permutation)
 void b200_quant_rows_f8_launch(const void* x, int T, int H, uint8_t* xq, float* xs, cudaStream_t st) {
-  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 1, xq, xs);
+  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, xq, xs);
 }
 
 struct F8Layout {
@@ -568,9 +609,10 @@ extern "C" size_t b200_moe_fp8_workspace_bytes(int T, int H, int I, int K) {
   return f8_layout(T, H, I, K).total;
 }
 
-extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
-                            const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, void* dbg_h,
-                            int stages, int32_t* status, void* stream) {
+static int moe_fp8_impl(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
+                        const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, void* dbg_h, int stages,
+                        int32_t* status, void* stream, void* const* peer_cache, int ep_world, int ep_rank,
+                        int ep_tokens_per_rank) {
   if (!x || !w || !lists || !cache || !ws || !w->w13 || !w->s13 || !w->w2 || !w->s2)
     return fail(B200_E_ARG, "b200_moe_fp8: null pointer");
   if (T <= 0 || K <= 0 || K > 32 || E_local <= 0 || H % 128 || I % 128 || H <= 0 || I <= 0 || H / 128 > F8_MAXKG ||
@@ -604,17 +646,21 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
   if ((rc = make_tmap_bytes_2d(&tmSh2, shared ? w->sh2 : w->w2, H, I, 128, "sh2"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmHq, hq, rows, I, 16, "hq"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmHq64, hq, rows, I, 64, "hq"))) return rc;
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  static DeviceOnce once;
+  once.run([] {
     cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<MODE_UP>::SMEM);
     cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<MODE_DOWN>::SMEM);
-    attr_done[dev] = true;
+  });
+  if ((stages & 15) == 0) stages |= 15;
+  // tokens that get a shared-expert row: all of them, or this rank's own under expert parallelism
+  int shared_lo = 0, shared_n = shared ? T : 0;
+  if (ep_world >= 1 && shared) {
+    shared_lo = ep_rank * ep_tokens_per_rank;
+    shared_n = ep_tokens_per_rank;
   }
-  if (stages == 0) stages = 15;
   if (stages & B200_MOE_STAGE_QUANT)
-    quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, K, L.row_of_pair, shared ? 1 : 0, xq, xs);
+    quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, K, L.row_of_pair, shared_lo, shared_n, xq,
+                                               xs);
   F8Args a{};
   a.L = L;
   a.E_local = E_local;
@@ -622,6 +668,7 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
   a.H = H;
   a.total_rows = rows;
   a.status = status;
+  a.test_starve = (stages & B200_MOE_TEST_STARVE) ? 1 : 0;
   const int grid = sm_count();
   a.mtiles = I / 128;
   a.ksteps = H / 128;
@@ -644,9 +691,35 @@ extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_loc
   a.h_out = nullptr;
   a.cache = static_cast<bf16*>(cache);
   a.dbg_h = nullptr;
+  a.ep_world = ep_world;
+  a.ep_rank = ep_rank;
+  a.ep_tokens = ep_tokens_per_rank;
+  a.ep_rows = ep_tokens_per_rank * K;
+  for (int r = 0; r < 8; ++r) a.ep_cache[r] = (peer_cache && r < ep_world) ? static_cast<bf16*>(peer_cache[r]) : nullptr;
   if (stages & B200_MOE_STAGE_DOWN)
     moe_gemm_f8_kernel<MODE_DOWN><<<grid, F8_THREADS, F8Cfg<MODE_DOWN>::SMEM, st>>>(tmW2, tmSh2, tmHq, tmHq64, a);
   return launch_status("b200_moe_fp8");
+}
+
+extern "C" int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
+                            const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, void* dbg_h,
+                            int stages, int32_t* status, void* stream) {
+  return moe_fp8_impl(x, T, H, I, K, E_local, w, lists, cache, ws, ws_bytes, dbg_h, stages, status, stream, nullptr, 0, 0,
+                      0);
+}
+
+extern "C" int b200_moe_fp8_ep(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
+                               const b200_moe_lists* lists, void* const* peer_cache_host, int ep_world, int ep_rank,
+                               int ep_tokens_per_rank, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  if (!peer_cache_host || ep_world < 1 || ep_world > 8 || ep_rank < 0 || ep_rank >= ep_world || ep_tokens_per_rank <= 0 ||
+      T != ep_world * ep_tokens_per_rank)
+    return fail(B200_E_ARG, "b200_moe_fp8_ep: need 1 <= ep_world <= 8, 0 <= ep_rank < ep_world and T == ep_world * "
+                "ep_tokens_per_rank (T=%d)", T);
+  for (int r = 0; r < ep_world; ++r)
+    if (!peer_cache_host[r] || (reinterpret_cast<uintptr_t>(peer_cache_host[r]) & 15))
+      return fail(B200_E_ARG, "b200_moe_fp8_ep: peer cache %d is null or not 16-byte aligned", r);
+  return moe_fp8_impl(x, T, H, I, K, E_local, w, lists, peer_cache_host[ep_rank], ws, ws_bytes, nullptr, 0, status, stream,
+                      peer_cache_host, ep_world, ep_rank, ep_tokens_per_rank);
 }
 
 // ---- LM head shard with fused argmax ------------------------------------------------------------------
@@ -730,10 +803,10 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
                                   int shard_lo, float* max_out, int32_t* idx_out, float* logits_out, void* ws,
                                   size_t ws_bytes, int32_t* status, void* stream) {
   if (!x || !w || !w_s || !max_out || !idx_out || !ws) return fail(B200_E_ARG, "b200_lmhead_argmax: null pointer");
-  if (T <= 0 || T > 64 || H <= 0 || H % 128 || H / 128 > F8_MAXKG || V_shard <= 0 || shard_lo < 0)
-    return fail(B200_E_ARG, "b200_lmhead_argmax: need 1 <= T <= 64, H %% 128 == 0, H <= 4096 (T=%d H=%d V=%d)", T, H,
-                V_shard);
-  const LmLayout l = lm_layout(T, H, V_shard);
+  if (T <= 0 || H <= 0 || H % 128 || H / 128 > F8_MAXKG || V_shard <= 0 || shard_lo < 0)
+    return fail(B200_E_ARG, "b200_lmhead_argmax: need T >= 1, H %% 128 == 0, H <= 4096 (T=%d H=%d V=%d)", T, H, V_shard);
+  const int TC = T < 64 ? T : 64;  // rows per launch; more rows run as consecutive 64-row chunks over the same workspace
+  const LmLayout l = lm_layout(TC, H, V_shard);
   if (ws_bytes < l.total) return fail(B200_E_WS, "b200_lmhead_argmax: workspace %zu < %zu bytes", ws_bytes, l.total);
   if (reinterpret_cast<uintptr_t>(ws) & 1023) return fail(B200_E_ALIGN, "b200_lmhead_argmax: workspace must be 1024-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -744,36 +817,38 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   CUtensorMap tmW, tmX, tmX64;
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(V_shard), H, 128, "lm_head weight"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "lm_head activations"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, 64, "lm_head activations"))) return rc;
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  if ((rc = make_tmap_bytes_2d(&tmX, xq, 64, H, 16, "lm_head activations"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX64, xq, 64, H, 64, "lm_head activations"))) return rc;
+  static DeviceOnce once;
+  once.run([] {
     cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_LM>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<MODE_LM>::SMEM);
-    attr_done[dev] = true;
+  });
+  for (int t0 = 0; t0 < T; t0 += 64) {
+    const int n = T - t0 < 64 ? T - t0 : 64;
+    // K = 0 routed picks: the "shared expert" row of token t is row t
+    quant_permute_f8_kernel<<<n, 256, 0, st>>>(static_cast<const bf16*>(x) + static_cast<size_t>(t0) * H, n, H, 0, nullptr, 0,
+                                               n, xq, xs);
+    F8Args a{};
+    a.E_local = 1;
+    a.mtiles = (V_shard + 127) / 128;
+    a.ksteps = H / 128;
+    a.w_rows = V_shard;
+    a.I = 0;
+    a.H = H;
+    a.total_rows = n;
+    a.s_w = w_s;
+    a.s_w_sh = w_s;
+    a.a_scale = xs;
+    a.status = status;
+    a.lm_keys = keys;
+    a.lm_logits = logits_out ? logits_out + static_cast<size_t>(t0) * V_shard : nullptr;
+    a.lm_ld = V_shard;
+    a.lm_shard_lo = shard_lo;
+    const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
+    moe_gemm_f8_kernel<MODE_LM><<<grid, F8_THREADS, F8Cfg<MODE_LM>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
+    launch_k(lmhead_finish_kernel, dim3(n), dim3(256), 0, st, static_cast<const unsigned long long*>(keys), a.mtiles * 4, n,
+             max_out + t0, idx_out + t0);
   }
-  // K = 0 routed picks: the "shared expert" row of token t is row t
-  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 1, xq, xs);
-  F8Args a{};
-  a.E_local = 1;
-  a.mtiles = (V_shard + 127) / 128;
-  a.ksteps = H / 128;
-  a.w_rows = V_shard;
-  a.I = 0;
-  a.H = H;
-  a.total_rows = T;
-  a.s_w = w_s;
-  a.s_w_sh = w_s;
-  a.a_scale = xs;
-  a.status = status;
-  a.lm_keys = keys;
-  a.lm_logits = logits_out;
-  a.lm_shard_lo = shard_lo;
-  const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
-  moe_gemm_f8_kernel<MODE_LM><<<grid, F8_THREADS, F8Cfg<MODE_LM>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
-  launch_k(lmhead_finish_kernel, dim3(T), dim3(256), 0, st, static_cast<const unsigned long long*>(keys), a.mtiles * 4, T,
-           max_out, idx_out);
   return launch_status("b200_lmhead_argmax");
 }
 
@@ -830,14 +905,26 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const bf16* __restrict
 extern "C" size_t b200_dense_fp8_workspace_bytes(int T, int H) {
   if (T <= 0 || H <= 0) return 0;
   auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
-  return up(static_cast<size_t>(64) * H) + up(static_cast<size_t>(T) * (H / 128) * 4);
+  return up(static_cast<size_t>(64) * H) + up(static_cast<size_t>(64) * (H / 128) * 4);
 }
 
-extern "C" int b200_dense_fp8(const void* x, int T, int H, const void* w, const float* w_s, int N, void* out, void* ws,
-                              size_t ws_bytes, int32_t* status, void* stream) {
-  if (!x || !w || !w_s || !out || !ws) return fail(B200_E_ARG, "b200_dense_fp8: null pointer");
-  if (T <= 0 || T > 64 || H <= 0 || H % 128 || H / 128 > F8_MAXKG || N <= 0)
-    return fail(B200_E_ARG, "b200_dense_fp8: need 1 <= T <= 64, H %% 128 == 0, H <= 4096 (T=%d H=%d N=%d)", T, H, N);
+extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, const float* w_s, int N, int nseg,
+                                    const int* seg_cols_host, void* const* seg_out_host, const int* seg_ld_host, void* ws,
+                                    size_t ws_bytes, int32_t* status, void* stream) {
+  if (!x || !w || !w_s || !seg_cols_host || !seg_out_host || !seg_ld_host || !ws)
+    return fail(B200_E_ARG, "b200_dense_fp8: null pointer");
+  if (T <= 0 || H <= 0 || H % 128 || H / 128 > F8_MAXKG || N <= 0 || nseg < 1 || nseg > 4)
+    return fail(B200_E_ARG, "b200_dense_fp8: need T >= 1, H %% 128 == 0, H <= 4096, 1 <= segments <= 4 (T=%d H=%d N=%d)", T,
+                H, N);
+  int lo = 0;
+  for (int i = 0; i < nseg; ++i) {
+    if (seg_cols_host[i] <= 0 || (i + 1 < nseg && seg_cols_host[i] % 32) || !seg_out_host[i] ||
+        seg_ld_host[i] < seg_cols_host[i])
+      return fail(B200_E_ARG, "b200_dense_fp8: segment %d: width must be positive (a multiple of 32 except the last), its "
+                  "row pitch at least the width, its output non-null", i);
+    lo += seg_cols_host[i];
+  }
+  if (lo != N) return fail(B200_E_ARG, "b200_dense_fp8: segment widths add up to %d, N = %d", lo, N);
   if (ws_bytes < b200_dense_fp8_workspace_bytes(T, H))
     return fail(B200_E_WS, "b200_dense_fp8: workspace %zu < %zu bytes", ws_bytes, b200_dense_fp8_workspace_bytes(T, H));
   if (reinterpret_cast<uintptr_t>(ws) & 1023) return fail(B200_E_ALIGN, "b200_dense_fp8: workspace must be 1024-byte aligned");
@@ -847,32 +934,49 @@ extern "C" int b200_dense_fp8(const void* x, int T, int H, const void* w, const 
   CUtensorMap tmW, tmX, tmX64;
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(N), H, 128, "dense weight"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "dense activations"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, 64, "dense activations"))) return rc;
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  if ((rc = make_tmap_bytes_2d(&tmX, xq, 64, H, 16, "dense activations"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX64, xq, 64, H, 64, "dense activations"))) return rc;
+  static DeviceOnce once;
+  once.run([] {
     cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          F8Cfg<MODE_DENSE>::SMEM);
-    attr_done[dev] = true;
+  });
+  // more than 64 rows run as consecutive 64-row chunks over the same workspace (stream order keeps them apart)
+  for (int t0 = 0; t0 < T; t0 += 64) {
+    const int n = T - t0 < 64 ? T - t0 : 64;
+    quant_permute_f8_kernel<<<n, 256, 0, st>>>(static_cast<const bf16*>(x) + static_cast<size_t>(t0) * H, n, H, 0, nullptr, 0,
+                                               n, xq, xs);
+    F8Args a{};
+    a.E_local = 1;
+    a.mtiles = (N + 127) / 128;
+    a.ksteps = H / 128;
+    a.w_rows = N;
+    a.H = H;
+    a.total_rows = n;
+    a.s_w = w_s;
+    a.s_w_sh = w_s;
+    a.a_scale = xs;
+    a.status = status;
+    a.nseg = nseg;
+    int c0 = 0;
+    for (int i = 0; i < nseg; ++i) {
+      a.seg_lo[i] = c0;
+      a.seg_ld[i] = seg_ld_host[i];
+      a.seg_out[i] = static_cast<bf16*>(seg_out_host[i]) + static_cast<size_t>(t0) * seg_ld_host[i];
+      c0 += seg_cols_host[i];
+    }
+    a.seg_lo[nseg] = c0;
+    const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
+    moe_gemm_f8_kernel<MODE_DENSE><<<grid, F8_THREADS, F8Cfg<MODE_DENSE>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
   }
-  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 1, xq, xs);
-  F8Args a{};
-  a.E_local = 1;
-  a.mtiles = (N + 127) / 128;
-  a.ksteps = H / 128;
-  a.w_rows = N;
-  a.H = H;
-  a.total_rows = T;
-  a.s_w = w_s;
-  a.s_w_sh = w_s;
-  a.a_scale = xs;
-  a.h_out = static_cast<bf16*>(out);
-  a.status = status;
-  const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
-  moe_gemm_f8_kernel<MODE_DENSE><<<grid, F8_THREADS, F8Cfg<MODE_DENSE>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
   return launch_status("b200_dense_fp8");
+}
+
+extern "C" int b200_dense_fp8(const void* x, int T, int H, const void* w, const float* w_s, int N, void* out, void* ws,
+                              size_t ws_bytes, int32_t* status, void* stream) {
+  if (!out) return fail(B200_E_ARG, "b200_dense_fp8: null pointer");
+  void* outs[1] = {out};
+  return b200_dense_fp8_split(x, T, H, w, w_s, N, 1, &N, outs, &N, ws, ws_bytes, status, stream);
 }
 
 extern "C" int b200_add_rmsnorm(const void* proj, void* residual, const void* w, float eps, int T, int H, void* out,

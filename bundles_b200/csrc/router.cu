@@ -16,6 +16,8 @@
 
 namespace b200 {
 
+B200_DEFINE_WAIT_BUDGET_SETTER(set_wait_budget_router)
+
 constexpr int RT_EXP = 64, RT_SLICE = 128, RT_THREADS = 256, RT_PITCH = RT_SLICE + 4;
 constexpr int RT_XPITCH = RT_SLICE + 8;  // bf16 elements per staged x row (272 bytes: 16-byte aligned, rows on different banks)
 constexpr int RT_WBUF = RT_EXP * RT_PITCH * 4;
@@ -505,14 +507,11 @@ extern "C" int b200_router(const void* x, const float* wr, const float* bias, in
   if (scratch_bytes < b200_router_scratch_bytes(T, H, E))
     return fail(B200_E_WS, "b200_router: scratch %zu < %zu bytes", scratch_bytes, b200_router_scratch_bytes(T, H, E));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  static DeviceOnce once;
+  once.run([] {
     cudaFuncSetAttribute(router_partials_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, RtCfg<64>::SMEM);
     cudaFuncSetAttribute(router_partials_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, RtCfg<128>::SMEM);
-    attr_done[dev] = true;
-  }
+  });
   float* part = static_cast<float*>(scratch);
   const int nslices = H / RT_SLICE;
   if (T > 64) {
@@ -617,13 +616,8 @@ extern "C" int b200_moe_build_lists_range(const int32_t* ids, const float* wts, 
   const size_t smem = lists_smem_bytes(T, K, E_local);
   if (smem > 200 * 1024 || T * (K + 1) > 65535 * 4)
     return fail(B200_E_ARG, "b200_moe_build_lists: T*K = %d is above the single-CTA limit", T * K);
-  static bool attr_done[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaFuncSetAttribute(moe_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_done[dev] = true;
-  }
+  static DeviceOnce once;
+  once.run([] { cudaFuncSetAttribute(moe_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); });
   launch_k(moe_lists_kernel, dim3(1), dim3(LISTS_THREADS), smem, static_cast<cudaStream_t>(stream), ids, wts, pos, T, K,
            e_lo, E_local, block_rows, shared_lo, shared_n, static_cast<int>(b200_moe_max_blocks(T, K, E_local, block_rows)), L);
   return launch_status("b200_moe_build_lists");

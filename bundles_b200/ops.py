@@ -15,8 +15,11 @@ import torch
 from . import _lib
 from ._lib import B200Error, MoeLists, MoeWeights, check
 
-__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_w8a8_ep", "ep_push", "moe_fp8", "moe_combine", "moe_combine_norm", "attn_front", "attn_verify", "dense_fp8", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
-           "new_status", "read_status", "B200Error"]
+__all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_w8a8_ep", "ep_push", "ep_put",
+           "ep_barrier", "moe_fp8", "moe_fp8_ep", "moe_combine", "moe_combine_norm", "attn_front", "attn_verify",
+           "dense_fp8", "dense_fp8_split", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
+           "gdn_verify_replay", "gdn_ring_fold", "set_wait_budget_ns", "selftest_wait_expiry", "new_status",
+           "read_status", "B200Error"]
 
 
 def _p(t):
@@ -140,6 +143,7 @@ def moe_w8a8_workspace(T, H, I, K, device):
 
 
 STAGE_QUANT, STAGE_UP, STAGE_HQUANT, STAGE_DOWN = 1, 2, 4, 8
+TEST_STARVE = 16     # B200_MOE_TEST_STARVE: self-test of the wait-expiry path, see include/b200nodes.h
 
 
 def moe_w8a8(x, w: MoeW8A8Weights, lists: RoutingLists, cache=None, ws=None, status=None, dbg_acc13=None,
@@ -206,7 +210,7 @@ def moe_w8a8_ep(x_all, w: MoeW8A8Weights, lists: RoutingLists, peer_ptrs, rank, 
     if ws is None:
         ws = moe_w8a8_workspace(T, H, I, K, x_all.device)
     world = len(peer_ptrs)
-    arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_ptrs])
+    arr = _ptr_array(peer_ptrs)
     wc = w.c_struct()
     check(_lib.lib().b200_moe_w8a8_ep(_p(x_all), T, H, I, K, E, C.byref(wc), C.byref(lists.c), arr, world,
                                       int(rank), int(tokens_per_rank), _p(ws), ws.numel(), _p(status), _stream()),
@@ -223,6 +227,55 @@ def ep_push(x, ids, wts, rank, peer_x, peer_ids, peer_wts):
     arr = lambda ptrs: (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in ptrs])
     check(_lib.lib().b200_ep_push(_p(x), _p(ids), _p(wts), T, H, ids.shape[1], int(rank), world, arr(peer_x),
                                   arr(peer_ids), arr(peer_wts), _stream()), "b200_ep_push")
+
+
+def _ptr_array(ptrs):
+    return (C.c_void_p * len(ptrs))(*[C.c_void_p(int(p)) for p in ptrs])
+
+
+def moe_fp8_ep(x_all, w: MoeW8A8Weights, lists: RoutingLists, peer_ptrs, rank, tokens_per_rank, ws=None, status=None):
+    """Expert-parallel fp8 experts: this rank's experts over the gathered tokens, the weighted down rows stored
+    straight into every home rank's routed cache (`peer_ptrs`: device pointers, one per rank)."""
+    _need(x_all, torch.bfloat16, "x_all", 2)
+    _need(w.w13, torch.uint8, "w13", 3)
+    if lists.block_rows > 64:
+        raise B200Error("moe_fp8_ep needs routing lists built with block_rows <= 64")
+    T, H = x_all.shape
+    E, twoI, _ = w.w13.shape
+    I = twoI // 2
+    K = lists.K
+    if ws is None:
+        ws = moe_fp8_workspace(T, H, I, K, x_all.device)
+    wc = w.c_struct()
+    check(_lib.lib().b200_moe_fp8_ep(_p(x_all), T, H, I, K, E, C.byref(wc), C.byref(lists.c), _ptr_array(peer_ptrs),
+                                     len(peer_ptrs), int(rank), int(tokens_per_rank), _p(ws), ws.numel(), _p(status),
+                                     _stream()), "b200_moe_fp8_ep")
+
+
+def ep_put(src, dst_offset_bytes, peer_ptrs):
+    """Store the bytes of `src` into every rank's buffer at `dst_offset_bytes` (an all-gather by peer stores)."""
+    if not (isinstance(src, torch.Tensor) and src.is_cuda and src.is_contiguous()):
+        raise B200Error("ep_put: src must be a contiguous CUDA tensor")
+    check(_lib.lib().b200_ep_put(_p(src), src.numel() * src.element_size(), int(dst_offset_bytes), _ptr_array(peer_ptrs),
+                                 len(peer_ptrs), _stream()), "b200_ep_put")
+
+
+def ep_barrier(peer_flags, epochs, rank, channel, timeout_ns=200_000_000, status=None):
+    """Barrier among the ranks of an expert-parallel group as one small kernel with a bounded wait (`peer_flags`:
+    device pointers of every rank's flag array; `epochs`: this rank's private uint64 counters)."""
+    _need(epochs, torch.int64, "epochs", 1)
+    check(_lib.lib().b200_ep_barrier(_ptr_array(peer_flags), _p(epochs), len(peer_flags), int(rank), int(channel),
+                                     int(timeout_ns), _p(status), _stream()), "b200_ep_barrier")
+
+
+def set_wait_budget_ns(ns: int) -> None:
+    """Budget of the device-side waits of kernels launched on the current device from now on (0: the default, 1 s)."""
+    check(_lib.lib().b200_set_wait_budget_ns(int(ns)), "b200_set_wait_budget_ns")
+
+
+def selftest_wait_expiry(status) -> None:
+    """Launches a one-CTA kernel whose wait can never succeed; `status` reads B200_ST_WAIT_FULL (101) afterwards."""
+    check(_lib.lib().b200_selftest_wait_expiry(_p(status), _stream()), "b200_selftest_wait_expiry")
 
 
 def moe_combine(cache, x, gate_w, top_k, pos=None, out=None):
@@ -326,9 +379,16 @@ def attn_verify(q, gate, k_new, v_new, kcache, vcache, page_table, seqlens, scal
     return out
 
 
+def dense_fp8_workspace(T, H, device):
+    n = _lib.lib().b200_dense_fp8_workspace_bytes(T, H)
+    buf = torch.empty(n + 1024, dtype=torch.uint8, device=device)
+    off = (-buf.data_ptr()) % 1024
+    return buf[off:off + n]
+
+
 def dense_fp8(x, w, w_s, out=None, ws=None, status=None):
-    """Decode-width projection out = bf16(x . W^T) with an fp8 block-scaled weight, T <= 64 rows
-    (reference: qk_proj_decode gdn_in_proj / qkv_proj / dense8)."""
+    """Decode-width projection out = bf16(x . W^T) with an fp8 block-scaled weight; more than 64 rows run as
+    consecutive 64-row launches (reference: qk_proj_decode gdn_in_proj / qkv_proj / dense8)."""
     _need(x, torch.bfloat16, "x", 2)
     _need(w, torch.uint8, "w", 2)
     _need(w_s, torch.float32, "w_s", 2)
@@ -337,13 +397,34 @@ def dense_fp8(x, w, w_s, out=None, ws=None, status=None):
     if out is None:
         out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
     if ws is None:
-        n = _lib.lib().b200_dense_fp8_workspace_bytes(T, H)
-        buf = torch.empty(n + 1024, dtype=torch.uint8, device=x.device)
-        off = (-buf.data_ptr()) % 1024
-        ws = buf[off:off + n]
+        ws = dense_fp8_workspace(T, H, x.device)
     check(_lib.lib().b200_dense_fp8(_p(x), T, H, _p(w), _p(w_s), N, _p(out), _p(ws), ws.numel(), _p(status),
                                     _stream()), "b200_dense_fp8")
     return out
+
+
+def dense_fp8_split(x, w, w_s, widths, outs=None, ws=None, status=None):
+    """dense_fp8 with the N output features cut into up to four consecutive segments (`widths`), each written to
+    its own contiguous tensor [T, width] (the GDN in_proj's [q k v | z | b | a], dense8.py:64-68)."""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(w, torch.uint8, "w", 2)
+    _need(w_s, torch.float32, "w_s", 2)
+    T, H = x.shape
+    N = w.shape[0]
+    n = len(widths)
+    if outs is None:
+        outs = [torch.empty(T, wd, dtype=torch.bfloat16, device=x.device) for wd in widths]
+    for o, wd in zip(outs, widths):
+        _need(o, torch.bfloat16, "segment output", 2)
+        if tuple(o.shape) != (T, wd):
+            raise B200Error("dense_fp8_split: a segment output must be [T, width]")
+    if ws is None:
+        ws = dense_fp8_workspace(T, H, x.device)
+    cols = (C.c_int * n)(*[int(v) for v in widths])
+    lds = (C.c_int * n)(*[int(v) for v in widths])
+    check(_lib.lib().b200_dense_fp8_split(_p(x), T, H, _p(w), _p(w_s), N, n, cols, _ptr_array([o.data_ptr() for o in outs]),
+                                          lds, _p(ws), ws.numel(), _p(status), _stream()), "b200_dense_fp8_split")
+    return outs
 
 
 def add_rmsnorm(proj, residual, w, eps=1e-6, out=None):

@@ -127,6 +127,129 @@ class GpuMoeBackend:
         return ops.moe_combine(cache, x, self.gate_w, K)
 
 
+EP_CHANNELS = 4   # B200_EP_CHANNELS of the C ABI
+
+
+class EpGroup:
+    """Buffers that every rank of an expert-parallel group can store into, and the barrier among the ranks.
+    One process per GPU; the buffers are symmetric memory (`torch.distributed._symmetric_memory`: one allocation per
+    rank, each mapped into every process), the barrier is the library's own one-warp kernel (`ops.ep_barrier`):
+    peer stores of an epoch counter, a poll bounded by `timeout_ns` that ends with status B200_ST_WAIT_PEER
+    instead of spinning on (torch's symmetric-memory barrier spins without a limit, or traps the GPU when
+    given one).  `shared()` must be called in the same order with the same shapes on every rank."""
+
+    def __init__(self, group=None, device=None, timeout_ns=1_000_000_000):
+        import torch.distributed._symmetric_memory as symm
+        from . import ops
+        self._symm, self._ops = symm, ops
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.timeout_ns = int(timeout_ns)
+        self.flags, self.peer_flags = self.shared((EP_CHANNELS * 8,), torch.int64, zero=True)
+        self.epochs = torch.zeros(EP_CHANNELS, dtype=torch.int64, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)       # nobody signals before every flag array is zero
+
+    def shared(self, shape, dtype, zero=False):
+        """(this rank's tensor, [device pointer of every rank's tensor as mapped into this process])."""
+        t = self._symm.empty(*shape, dtype=dtype, device=self.device)
+        if zero:
+            t.zero_()
+        handle = self._symm.rendezvous(t, self.group)
+        return t, [int(p) for p in handle.buffer_ptrs]
+
+    def barrier(self, channel, status=None):
+        self._ops.ep_barrier(self.peer_flags, self.epochs, self.rank, channel, self.timeout_ns, status)
+
+
+class VirtualEpGroup:
+    """The ranks of an expert-parallel group emulated in ONE process on ONE GPU, for checking the expert-parallel
+    data path (per-rank lists, peer destinations of the down GEMM, gathered buffers) where there is a single GPU:
+    every virtual rank has its own buffers in the same device memory, "peer" pointers are simply the other virtual
+    ranks' buffers, and the ranks' steps are run in lockstep on one stream (`run_lockstep`), phase by phase, so that
+    stream order stands in for the barriers (kernels that wait on one another must never run as separate launches
+    on one GPU, so the barrier kernel is not launched here)."""
+
+    def __init__(self, world, device):
+        self.world, self.device = int(world), torch.device(device)
+        self._bufs = []
+
+    def view(self, rank):
+        return _VirtualRank(self, int(rank))
+
+
+class _VirtualRank:
+    def __init__(self, parent, rank):
+        self.parent, self.rank, self.world, self.device = parent, rank, parent.world, parent.device
+        self._n = 0
+
+    def shared(self, shape, dtype, zero=False):
+        i, bufs = self._n, self.parent._bufs
+        self._n += 1
+        if len(bufs) <= i:
+            bufs.append([torch.zeros(*shape, dtype=dtype, device=self.device) for _ in range(self.world)])
+        if tuple(bufs[i][0].shape) != tuple(shape) or bufs[i][0].dtype != dtype:
+            raise ValueError("virtual ranks must request their shared buffers in the same order and shapes")
+        return bufs[i][self.rank], [t.data_ptr() for t in bufs[i]]
+
+    def barrier(self, channel, status=None):
+        pass
+
+
+class RankLost(RuntimeError):
+    """A rank of the expert-parallel group did not report for a step in time."""
+
+
+class StepGate:
+    """Host-side roll call before an expert-parallel step.  Every rank posts the number of the step it is about to
+    launch into a `torch.distributed` store and then reads its peers' entries; a peer that has not posted within
+    `timeout_s` makes `sync` raise `RankLost` BEFORE this rank launches kernels that would wait for that peer on
+    the device (where the wait is bounded too, but costs a whole step's worth of garbage).  A rank that leaves does
+    so between steps, with none of its kernels in flight."""
+
+    def __init__(self, store, rank, world, timeout_s=5.0, prefix="b200/step", poll_s=0.002):
+        self.store, self.rank, self.world = store, int(rank), int(world)
+        self.timeout_s, self.prefix, self.poll_s = float(timeout_s), prefix, float(poll_s)
+        self.step = 0
+
+    def _key(self, r):
+        return f"{self.prefix}/{r}"
+
+    def sync(self):
+        """Post the next step's number and wait for every peer to have posted it (or a later one)."""
+        import time
+        self.step += 1
+        self.store.set(self._key(self.rank), str(self.step))
+        deadline = time.monotonic() + self.timeout_s
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            while True:
+                if self.store.check([self._key(r)]) and int(self.store.get(self._key(r))) >= self.step:
+                    break
+                if time.monotonic() > deadline:
+                    raise RankLost(f"rank {r} did not report for step {self.step} within {self.timeout_s} s")
+                time.sleep(self.poll_s)
+        return self.step
+
+
+def run_lockstep(generators):
+    """Advance the per-rank step generators of a VirtualEpGroup phase by phase (every generator yields at each
+    point where the real group runs a barrier); returns their return values."""
+    results = [None] * len(generators)
+    live = list(range(len(generators)))
+    while live:
+        for i in list(live):
+            try:
+                next(generators[i])
+            except StopIteration as stop:
+                results[i] = stop.value
+                live.remove(i)
+    return results
+
+
 class FusedExpertParallelMoe:
     """Expert-parallel MoE block whose combine-side exchange is fused into the down GEMM: every rank
     stores the weighted expert rows straight into the home rank's cache over NVLink (plain peer
@@ -139,32 +262,26 @@ class FusedExpertParallelMoe:
     and to the single-GPU block."""
 
     def __init__(self, backend: "GpuMoeBackend", top_k: int, hidden: int, tokens_per_rank: int, group=None,
-                 use_graph=True):
-        import torch.distributed._symmetric_memory as symm
+                 use_graph=True, ep=None):
         self.b, self.K, self.H, self.T = backend, top_k, hidden, tokens_per_rank
-        self.group = group if group is not None else dist.group.WORLD
-        self.world = dist.get_world_size(self.group)
-        self.rank = dist.get_rank(self.group)
         dev = backend.wr.device
+        self.ep = ep if ep is not None else EpGroup(group, dev)
+        self.world, self.rank = self.ep.world, self.ep.rank
+        self.group = getattr(self.ep, "group", group)
         # rows of this rank's tokens: K routed rows per token (written by every rank) + the shared-expert row
-        self.cache = symm.empty(tokens_per_rank * (top_k + 1), hidden, dtype=torch.bfloat16, device=dev)
-        self.handle = symm.rendezvous(self.cache, self.group)
-        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.cache, self.peer_ptrs = self.ep.shared((tokens_per_rank * (top_k + 1), hidden), torch.bfloat16)
         T_all = tokens_per_rank * self.world
         # the gathered tokens and routing of all ranks: every rank stores its share into every rank's buffers
-        self.x_all = symm.empty(T_all, hidden, dtype=torch.bfloat16, device=dev)
-        self.ids_all = symm.empty(T_all, top_k, dtype=torch.int32, device=dev)
-        self.wts_all = symm.empty(T_all, top_k, dtype=torch.float32, device=dev)
-        self.peer_x = [int(p) for p in symm.rendezvous(self.x_all, self.group).buffer_ptrs]
-        self.peer_ids = [int(p) for p in symm.rendezvous(self.ids_all, self.group).buffer_ptrs]
-        self.peer_wts = [int(p) for p in symm.rendezvous(self.wts_all, self.group).buffer_ptrs]
+        self.x_all, self.peer_x = self.ep.shared((T_all, hidden), torch.bfloat16)
+        self.ids_all, self.peer_ids = self.ep.shared((T_all, top_k), torch.int32)
+        self.wts_all, self.peer_wts = self.ep.shared((T_all, top_k), torch.float32)
         self.lists = backend.ops.RoutingLists(T_all, top_k, backend.E_local, 128, dev)
         self.ws = backend.ops.moe_w8a8_workspace(T_all, hidden, backend.w.w2.shape[-1], top_k, dev)
         self.x_static = torch.empty(tokens_per_rank, hidden, dtype=torch.bfloat16, device=dev)
         self.out = torch.empty(tokens_per_rank, hidden, dtype=torch.bfloat16, device=dev)
         self.use_graph, self.graph = use_graph, None
         self._pipe = None
-        self.launches_per_call = 9   # router x2, dispatch, lists, quantise, up, h-quantise, down, combine (+2 barriers)
+        self.launches_per_call = 11  # router x2, dispatch, barrier, lists, quantise, up, h-quantise, down, barrier, combine
 
     def _step(self):
         b, ops, K = self.b, self.b.ops, self.K
@@ -173,11 +290,11 @@ class FusedExpertParallelMoe:
         # dispatch: peer stores into every rank's gathered buffers; the barrier below makes them visible and
         # also tells that nobody still reads last step's rows when the first peer store of this step lands
         ops.ep_push(x, ids, wts, self.rank, self.peer_x, self.peer_ids, self.peer_wts)
-        self.handle.barrier(channel=0)
+        self.ep.barrier(0, b.status)
         ops.build_lists(self.ids_all, self.wts_all, self.lists, None, e_lo=b.e_lo,
                         shared_range=(self.rank * self.T, self.T))   # the shared expert runs for this rank's own tokens
         ops.moe_w8a8_ep(self.x_all, b.w, self.lists, self.peer_ptrs, self.rank, self.T, ws=self.ws, status=b.status)
-        self.handle.barrier(channel=1)      # every rank's rows for my tokens have landed
+        self.ep.barrier(1, b.status)        # every rank's rows for my tokens have landed
         ops.moe_combine(self.cache, x, b.gate_w, K, out=self.out)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -40,10 +40,22 @@ extern "C" {
 #define B200_ST_WAIT_TMEM_EMPTY 104
 #define B200_ST_WAIT_STATE 105
 #define B200_ST_WAIT_STORE 106
+#define B200_ST_WAIT_PEER 107   /* expert-parallel barrier: a peer rank's flag did not arrive in time */
 #define B200_ST_BAD_LIST 110
 
 int b200_abi_version(void);
 const char* b200_last_error(void);
+
+/* Budget of every device-side wait on an asynchronous copy or a tensor-core commit, in nanoseconds of
+ * %globaltimer, for kernels launched on the CURRENT device after this call (0 restores the default of one
+ * second).  The reference's waits spin without a limit (qk_gdn_verify.cu:140-144, qk_moe_up16.cu:656);
+ * here a wait that runs out records a B200_ST_* code in the call's status word, and every role of the CTA
+ * winds down (copies in flight are given a bounded time to land, TMEM is freed) and returns.
+ * Not to be changed while kernels of the library are running on the device. */
+int b200_set_wait_budget_ns(unsigned long long ns);
+/* Self-test of that path: one CTA waits on a barrier that nothing arrives on and must come back with
+ * B200_ST_WAIT_FULL in `status` after the budget.  The GPU stays usable. */
+int b200_selftest_wait_expiry(int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Router.  Replaces qk_route.route / route48 / route16w (qk_route.cu:214,496,972) and the Triton
@@ -144,6 +156,9 @@ int b200_moe_build_lists_range(const int32_t* ids, const float* wts, const int64
 #define B200_MOE_STAGE_UP 2      /* gate/up GEMM + SwiGLU */
 #define B200_MOE_STAGE_HQUANT 4  /* re-quantise h */
 #define B200_MOE_STAGE_DOWN 8    /* down GEMM + weighted unpermute */
+#define B200_MOE_TEST_STARVE 16  /* self-test, OR-ed into `stages`: the GEMM producers leave out the token rows, so no
+                                    pipeline stage ever completes, every bounded wait runs out and the kernels return
+                                    with a B200_ST_WAIT_* status (set a short b200_set_wait_budget_ns first) */
 typedef struct b200_moe_weights {
   const void* w13;
   const float* s13;
@@ -199,6 +214,36 @@ size_t b200_moe_fp8_workspace_bytes(int T, int H, int I, int K);
 int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
                  const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, void* dbg_h, int stages,
                  int32_t* status, void* stream);
+
+/* Expert-parallel form of b200_moe_fp8, as b200_moe_w8a8_ep is of b200_moe_w8a8: x holds the gathered tokens
+ * of all ranks, the lists are this rank's (block_rows <= 64, shared rows for its own tokens), and the down epilogue
+ * stores every weighted row into its home rank's cache with ordinary stores over NVLink.  (No counterpart in the
+ * reference.) */
+int b200_moe_fp8_ep(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
+                    const b200_moe_lists* lists, void* const* peer_cache_host, int ep_world, int ep_rank,
+                    int ep_tokens_per_rank, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
+/* Barrier among the ranks of an expert-parallel group, as one small kernel on `stream` (no counterpart in the
+ * reference).  Every rank owns a flag array uint64 [B200_EP_CHANNELS][8] in memory that all ranks can store to
+ * (peer-mapped), zeroed once, and a private epoch array uint64 [B200_EP_CHANNELS], zeroed once.  A call advances
+ * this rank's epoch of `channel`, stores it into entry [channel][ep_rank] of every rank's flag array with
+ * release stores at system scope (after a system-scope fence, so that everything this rank's earlier kernels on the
+ * stream wrote to peers is visible first), then polls its own entries [channel][0..ep_world) until every rank's
+ * epoch has arrived.  The poll is bounded by `timeout_ns` of %globaltimer: when it runs out the kernel records
+ * B200_ST_WAIT_PEER in `status` and returns; it never traps and never spins without a limit.  Once `status` is
+ * non-zero later barriers return at once, so a dead peer costs one timeout, not one per barrier.  All ranks must call
+ * with the same channel sequence.  peer_flags_host: HOST array of ep_world DEVICE pointers (entry r = rank r's
+ * flag array as mapped into this process).  Plain loads and stores only: no multimem, no TMA. */
+#define B200_EP_CHANNELS 4
+int b200_ep_barrier(void* const* peer_flags_host, unsigned long long* epochs, int ep_world, int ep_rank, int channel,
+                    unsigned long long timeout_ns, int32_t* status, void* stream);
+
+/* All-gather by peer stores (no counterpart in the reference): `bytes` bytes at `src` are stored into every rank's
+ * buffer at byte offset dst_offset_bytes (peer_dst_host: HOST array of ep_world DEVICE pointers).  4-byte
+ * granularity; ordinary stores.  The caller runs b200_ep_barrier before any rank reads its buffer.  Used for the
+ * hidden rows in front of the vocabulary-sharded LM head and for its (max, argmax) pairs. */
+int b200_ep_put(const void* src, size_t bytes, size_t dst_offset_bytes, void* const* peer_dst_host, int ep_world,
+                void* stream);
 
 /* Combine.  Replaces i8x_dec_combine (i8x_decode.py:425-443) / combine_norm_kernel
  * (qk_route.cu:686-820, without the next-layer norm): out[t] = bf16(sum_j cache[t*K+j] in slot
@@ -323,13 +368,21 @@ int b200_attn_front(const void* x, int T, const void* w, const float* w_s, const
  * target keeps every weight in the one fp8 block-scaled format.
  *   b200_dense_fp8: out[T,N] = bf16(x[T,H] . W[N,H]^T), x bf16 quantised per token per 128
  *     channels, W e4m3 [N,H] with scales fp32 [ceil(N/128), H/128], per-128-k promotion;
- *     1 <= T <= 64, H % 128 == 0, H <= 4096; ws: b200_dense_fp8_workspace_bytes(T,H), 1024-aligned.
+ *     T >= 1 (more than 64 rows run as consecutive 64-row launches), H % 128 == 0, H <= 4096;
+     ws: b200_dense_fp8_workspace_bytes(T,H), 1024-aligned.
+ *   b200_dense_fp8_split: the same GEMM with the N output features cut into 1..4 consecutive segments, segment i
+ *     (seg_cols_host[i] features, a multiple of 32 except the last) written to seg_out_host[i] with row pitch
+ *     seg_ld_host[i] elements: the GDN in_proj's [q k v | z | b | a] land in the four buffers the verify kernel
+ *     takes (dense8.py:64-68 slices them after the GEMM).  seg_*_host are HOST arrays.
  *   b200_add_rmsnorm: residual <- bf16(proj + residual) (proj is already bf16; the add is fp32:
  *     proj.py:75-77), out = bf16(residual * rsqrt(mean residual^2 + eps) * (1 + w)) (proj.py:78-81).
  */
 size_t b200_dense_fp8_workspace_bytes(int T, int H);
 int b200_dense_fp8(const void* x, int T, int H, const void* w, const float* w_s, int N, void* out, void* ws,
                    size_t ws_bytes, int32_t* status, void* stream);
+int b200_dense_fp8_split(const void* x, int T, int H, const void* w, const float* w_s, int N, int nseg,
+                         const int* seg_cols_host, void* const* seg_out_host, const int* seg_ld_host, void* ws,
+                         size_t ws_bytes, int32_t* status, void* stream);
 int b200_add_rmsnorm(const void* proj, void* residual, const void* w, float eps, int T, int H, void* out,
                      void* stream);
 
@@ -339,7 +392,8 @@ int b200_add_rmsnorm(const void* proj, void* residual, const void* w, float eps,
  * side, weight streamed once); the reference returns logits and has no argmax
  * (node.py:136-151).  Per row of x: the largest fp8 block-scaled logit over this shard's
  * vocabulary rows and its global id (shard_lo + local row); ties go to the lower id, NaN never wins.
- *   x bf16 [T,H], 1 <= T <= 64, H % 128 == 0, H <= 4096; w e4m3 [V_shard,H];
+ *   x bf16 [T,H], T >= 1 (more than 64 rows run as consecutive 64-row launches), H % 128 == 0, H <= 4096;
+ *   w e4m3 [V_shard,H];
  *   w_s fp32 [ceil(V_shard/128), H/128]; max_out fp32 [T]; idx_out int32 [T];
  *   logits_out fp32 [T,V_shard] or NULL; ws: b200_lmhead_workspace_bytes(T,H,V_shard) bytes,
  *   1024-byte aligned.

@@ -63,3 +63,43 @@ def moe_w8a8(x_bits, ids, wts, w13, s13, w2, s2, sh13, shs13, sh2, shs2, gate_w_
     lib().oracle_moe_w8a8(_p(x_bits), _p(ids), _p(wts), T, H, I, K, _p(w13), _p(s13), _p(w2), _p(s2), _p(sh13),
                           _p(shs13), _p(sh2), _p(shs2), _p(gate_w_bits), _p(cache), _p(out))
     return out, cache
+
+
+def e4m3_encode(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint8)
+    lib().oracle_e4m3_encode(_p(x), C.c_size_t(x.size), _p(out))
+    return out
+
+
+def quant_fp8_groups(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, n = x.shape
+    q = np.empty((rows, n), dtype=np.uint8)
+    s = np.empty((rows, n // 128), dtype=np.float32)
+    lib().oracle_quant_fp8_groups(_p(x), rows, n, _p(q), _p(s))
+    return q, s
+
+
+def gemm_fp8_blocks(aq, a_s, wq, w_s):
+    """out fp32 [M, N]: the block-scaled GEMM with per-128-k promotion (oracle/moe.py gemm_fp8_blocks)."""
+    M, K = aq.shape
+    N = wq.shape[0]
+    out = np.empty((M, N), dtype=np.float32)
+    lib().oracle_gemm_fp8_blocks(_p(np.ascontiguousarray(aq)), _p(np.ascontiguousarray(a_s, dtype=np.float32)), M, K,
+                                 _p(np.ascontiguousarray(wq)), _p(np.ascontiguousarray(w_s, dtype=np.float32)), N, _p(out))
+    return out
+
+
+def moe_fp8(x_bits, ids, wts, w13, s13, w2, s2, sh13, shs13, sh2, shs2, gate_w_bits):
+    """fp8 block-scaled MoE block; all arrays C-contiguous numpy (x_bits / gate_w_bits uint16 bf16 patterns, weights
+    uint8 e4m3 codes).  Returns (out bits [T,H], cache bits [T*(K+1),H])."""
+    T, H = x_bits.shape
+    K = ids.shape[1]
+    E = w13.shape[0]
+    I = w2.shape[-1]
+    cache = np.zeros((T * (K + 1), H), dtype=np.uint16)
+    out = np.empty((T, H), dtype=np.uint16)
+    lib().oracle_moe_fp8(_p(x_bits), _p(ids), _p(wts), T, H, I, K, E, _p(w13), _p(s13), _p(w2), _p(s2), _p(sh13),
+                         _p(shs13), _p(sh2), _p(shs2), _p(gate_w_bits), _p(cache), _p(out))
+    return out, cache

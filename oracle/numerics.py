@@ -62,7 +62,7 @@ def e4m3_encode(x: np.ndarray) -> np.ndarray:
     """fp32 -> e4m3 byte, round to nearest even, saturating to +-448 (PTX cvt.rn.satfinite.e4m3x2.f32,
     the conversion the reference uses for q/k/v: qk_attn_verify.cu:142-146)."""
     x = np.asarray(x, dtype=F32)
-    a = np.minimum(np.abs(x), E4M3_MAX).astype(np.float64)
+    a = np.minimum(np.abs(np.where(np.isnan(x), F32(0.0), x)), E4M3_MAX).astype(np.float64)   # NaN is set at the end
     with np.errstate(divide="ignore"):
         e = np.floor(np.log2(np.where(a > 0, a, 1.0)))
     e = np.maximum(e, -6.0)

@@ -75,6 +75,20 @@ def test_argument_checks_return_codes(lib):
     assert lib.b200_gdn_verify_replay(*ok, 0, *([one] * 11), 1e-6, 1, one, one, 1 << 30, None, None) == -1
     assert lib.b200_gdn_ring_fold(*([None] * 10), 1, None) == -1
     assert lib.b200_gdn_ring_fold(C.c_void_p(4100), *([one] * 9), 1, None) == -2
+    # expert-parallel plumbing
+    assert lib.b200_ep_barrier(None, None, 2, 0, 0, 1000, None, None) == -1
+    ptrs = (C.c_void_p * 2)(4096, 8192)
+    assert lib.b200_ep_barrier(ptrs, one, 9, 0, 0, 1000, None, None) == -1          # more than 8 ranks
+    assert lib.b200_ep_barrier(ptrs, one, 2, 0, 4, 1000, None, None) == -1          # channel out of range
+    assert lib.b200_ep_barrier(ptrs, one, 2, 0, 0, 0, None, None) == -1             # a barrier without a time limit
+    odd = (C.c_void_p * 2)(4096, 8194)
+    assert lib.b200_ep_barrier(odd, one, 2, 0, 0, 1000, None, None) == -2
+    assert lib.b200_ep_put(one, 6, 0, ptrs, 2, None) == -1                          # not a multiple of 4 bytes
+    assert lib.b200_ep_put(one, 0, 0, ptrs, 2, None) == 0                           # nothing to store
+    assert lib.b200_moe_fp8_ep(one, 64, 2048, 512, 10, 8, None, None, ptrs, 2, 0, 16, one, 1 << 30, None, None) == -1
+    assert lib.b200_selftest_wait_expiry(None, None) == -1
+    cols, lds = (C.c_int * 2)(100, 28), (C.c_int * 2)(100, 28)
+    assert lib.b200_dense_fp8_split(one, 4, 2048, one, one, 128, 2, cols, ptrs, lds, one, 1 << 30, None, None) == -1
     mis = [one] * 9 + [C.c_void_p(4100)]
     assert lib.b200_gdn_verify_replay(*mis, 4, *([one] * 11), 1e-6, 1, one, one, 1 << 30, None, None) == -2
 

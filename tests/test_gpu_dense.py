@@ -10,7 +10,8 @@ from tests.util import bf16_to_np, close_bf16, dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("T,H,N", [(64, 2048, 12352), (8, 4096, 2048), (1, 2048, 9216), (33, 2048, 200)])
+@pytest.mark.parametrize("T,H,N", [(64, 2048, 12352), (8, 4096, 2048), (1, 2048, 9216), (33, 2048, 200), (150, 2048, 640),
+                                   (256, 4096, 2048)])
 def test_dense_projection(T, H, N):
     g = torch.Generator().manual_seed(T + N)
     npad = (N + 127) // 128 * 128
@@ -26,6 +27,31 @@ def test_dense_projection(T, H, N):
     ref = oat.dense_fp8(bf16_to_np(x), codes.numpy(), scales.numpy())
     ok, err, nbad = close_bf16(bf16_to_np(out), ref)
     assert ok, (err, nbad)
+
+
+def test_split_outputs_equal_the_plain_projection():
+    # the GDN in_proj's four consumers get their own buffers; 80 rows run as two launches
+    g = torch.Generator().manual_seed(9)
+    T, H, widths = 80, 2048, (8192, 4096, 32, 32)
+    N = sum(widths)
+    npad = (N + 127) // 128 * 128
+    w = torch.zeros(npad, H)
+    w[:N] = torch.randn(N, H, generator=g) * 0.02
+    codes, scales = synth.quant_fp8_blocks(w)
+    codes = codes[:N].contiguous().to(dev())
+    scales = scales.to(dev())
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev())
+    st = ops.new_status(dev())
+    whole = ops.dense_fp8(x, codes, scales, status=st)
+    parts = ops.dense_fp8_split(x, codes, scales, widths, status=st)
+    torch.cuda.synchronize()
+    assert ops.read_status(st) == 0
+    lo = 0
+    for p, wd in zip(parts, widths):
+        assert tuple(p.shape) == (T, wd) and torch.equal(p, whole[:, lo:lo + wd])
+        lo += wd
+    with pytest.raises(ops.B200Error):
+        ops.dense_fp8_split(x, codes, scales, (8192, 4100, 28, 32))     # inner boundary not a multiple of 32
 
 
 def test_add_rmsnorm():

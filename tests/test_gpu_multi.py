@@ -66,7 +66,25 @@ def _worker(rank, world, port, out):
                                       lm["w_s"][lo // 128:(hi + 127) // 128].contiguous().to(dev), lo)
         _, idx, _ = ops.lmhead_argmax(x, lm["w"].to(dev), lm["w_s"].to(dev), 0)
         torch.cuda.synchronize()
-        torch.save({"moe": ok_moe, "lm": torch.equal(tok, idx)}, os.path.join(out, f"r{rank}.pt"))
+        # the whole decode + verify step on the ranks (sequences, experts and vocabulary split, the library's own
+        # barrier between the phases) against the one-GPU step; twice, the second step on the advanced state
+        from bundles_b200 import decode_step
+        kw = dict(layers=4, B=4, ctx=300, vocab=128 * 40 + 17, experts=64, seed=21, device=dev)
+        part = decode_step.DecodeStep(ep=parallel.EpGroup(device=dev), **kw)
+        single = decode_step.DecodeStep(**kw)
+        gx = torch.Generator(device=dev).manual_seed(5)
+        xs = torch.randn(single.T, 2048, generator=gx, device=dev).to(torch.bfloat16)
+        Tl = part.T
+        ok_step = True
+        for _ in range(2):
+            got = part.step(xs[rank * Tl:(rank + 1) * Tl].contiguous())
+            want = single.step(xs)
+            torch.cuda.synchronize()
+            ok_step = ok_step and torch.equal(got, want) and \
+                torch.equal(part.final_hidden, single.final_hidden[rank * Tl:(rank + 1) * Tl])
+        ok_step = ok_step and ops.read_status(part.status) == 0 and ops.read_status(single.status) == 0
+        dist.barrier()
+        torch.save({"moe": ok_moe, "lm": torch.equal(tok, idx), "step": ok_step}, os.path.join(out, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -80,3 +98,4 @@ def test_expert_parallel_matches_single_gpu(tmp_path):
         got = torch.load(os.path.join(tmp_path, f"r{r}.pt"))
         assert got["moe"], f"rank {r}: expert-parallel output differs from the single-GPU block"
         assert got["lm"], f"rank {r}: sharded argmax differs"
+        assert got["step"], f"rank {r}: the expert-parallel decode step differs from the one-GPU step"

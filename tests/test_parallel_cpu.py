@@ -104,6 +104,55 @@ def test_expert_parallel_and_vocab_merge_on_two_cpu_ranks(tmp_path):
         assert torch.equal(got["tok"], got["ref_tok"].to(torch.int32))
 
 
+def _gate_worker(rank, world, path, out):
+    store = dist.FileStore(path, world)
+    gate = parallel.StepGate(store, rank, world, timeout_s=1.0)
+    log = []
+    try:
+        for step in range(1, 4):
+            if rank == 1 and step == 3:
+                break                      # this rank leaves between steps and never reports for step 3
+            log.append(gate.sync())
+        log.append("left" if rank == 1 else "done")
+    except parallel.RankLost as exc:
+        log.append(f"lost: {exc}")
+    torch.save(log, os.path.join(out, f"gate{rank}.pt"))
+
+
+def test_a_rank_that_never_reports_is_noticed_on_the_host(tmp_path):
+    """Rank 1 takes part in two steps and leaves; rank 0's roll call for step 3 ends with RankLost after its time limit
+    instead of launching a step that would wait for rank 1 on the device."""
+    world = 2
+    mp.spawn(_gate_worker, args=(world, str(tmp_path / "store"), str(tmp_path)), nprocs=world, join=True)
+    log0 = torch.load(os.path.join(tmp_path, "gate0.pt"))
+    log1 = torch.load(os.path.join(tmp_path, "gate1.pt"))
+    assert log1 == [1, 2, "left"]
+    assert log0[:2] == [1, 2] and log0[2].startswith("lost: rank 1 did not report for step 3")
+
+
+def test_virtual_ranks_share_buffers_and_run_in_lockstep():
+    vg = parallel.VirtualEpGroup(3, "cpu")
+    views = [vg.view(r) for r in range(3)]
+    bufs = [v.shared((4, 2), torch.float32) for v in views]
+    ptrs = bufs[0][1]
+    assert all(b[1] == ptrs for b in bufs) and len(set(ptrs)) == 3
+    assert [b[0].data_ptr() for b in bufs] == ptrs
+    with pytest.raises(ValueError):
+        views[0].shared((4, 2), torch.float32)
+        views[1].shared((4, 2), torch.float32)
+        views[2].shared((5, 2), torch.float32)        # a rank asking for another shape
+    order = []
+
+    def rank_step(r):
+        for phase in range(3):
+            order.append((phase, r))
+            yield phase
+        return r * 10
+
+    assert parallel.run_lockstep([rank_step(r) for r in range(3)]) == [0, 10, 20]
+    assert order == [(p, r) for p in range(3) for r in range(3)]
+
+
 def test_partition_math():
     assert parallel.expert_range(512, 3, 8) == (192, 64)
     with pytest.raises(ValueError):
