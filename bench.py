@@ -545,7 +545,7 @@ def _ep_check(dev, ep, world, rank):
     import torch
     import torch.distributed as dist
     from bundles_b200 import decode_step, ops, parallel
-    kw = dict(layers=4, B=BATCH, ctx=512, vocab=VOCAB, experts=E, seed=77, device=dev)
+    kw = dict(layers=4, B=BATCH, ctx=512, vocab=VOCAB, experts=E, seed=77, device=dev, attn_splits=2)   # same split count in both forms
     g = torch.Generator(device=dev).manual_seed(78)
     x = torch.randn(4 * BATCH, H, generator=g, device=dev).to(torch.bfloat16)
     res = {"form": None, "tokens_equal": None, "hidden_equal": None, "status": None}

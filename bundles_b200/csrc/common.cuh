@@ -57,6 +57,17 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
   return e4m3x2(a, b) | (e4m3x2(c, d) << 16);
 }
 
+// Global stores that the compiler need not order against the C++ loads around them (no "memory" clobber): an
+// epilogue that reads its row metadata from shared memory and stores through pointers it also read from there
+// would otherwise reload after every store (a generic pointer may alias shared memory), one dependent
+// shared-memory round trip per store.  Only for global destinations that the kernel never reads back.
+__device__ __forceinline__ void st_global_na(bf16* p, bf16 v) {
+  asm volatile("st.global.b16 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "h"(*reinterpret_cast<unsigned short*>(&v)));
+}
+__device__ __forceinline__ void st_global_na(float* p, float v) {
+  asm volatile("st.global.f32 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "f"(v));
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

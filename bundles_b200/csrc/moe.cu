@@ -497,7 +497,7 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            if (c0 + i < n) hout[static_cast<size_t>(c0 + i) * p.I] = hv[i];
+            if (c0 + i < n) st_global_na(hout + static_cast<size_t>(c0 + i) * p.I, hv[i]);
           if (p.dbg_acc || p.dbg_h) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -525,8 +525,8 @@ moe_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             const float y0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(ra[i])), xs), ws0);
             const float y1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(rb[i])), xs), ws1);
             if (dst != nullptr) {
-              dst[r] = f2bf(__fmul_rn(y0, wt));
-              dst[r + 128] = f2bf(__fmul_rn(y1, wt));
+              st_global_na(dst + r, f2bf(__fmul_rn(y0, wt)));
+              st_global_na(dst + r + 128, f2bf(__fmul_rn(y1, wt)));
             }
           }
         }

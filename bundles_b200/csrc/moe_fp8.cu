@@ -23,6 +23,7 @@ constexpr int F8_BTILE = 64 * 128;       // token tile bytes per stage (<= 64 ro
 constexpr int F8_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int F8_CACHED = 64;            // tiles per CTA whose block-list entries are cached in shared memory
 constexpr int F8_MAXKG = 32;             // k blocks per row of scales held in shared memory (K <= 4096)
+constexpr int F8_WS_FLOATS = 1024;       // weight block scales of the CTA's first tiles, cached in shared memory
 
 // ---- activation quantisers ----------------------------------------------------------------------------
 // scale = max(amax / 448, 1e-12), y = e4m3(x * (1 / scale)) per (row, 128-channel group): fp8.py:21-34.
@@ -123,16 +124,17 @@ struct F8Cfg {
   static constexpr int STAGES = UP ? 4 : 7;
   static constexpr int PW = UP ? 128 : 64;   // TMEM columns of one partial buffer
   static constexpr int NPB = 512 / PW;       // partial buffers
-  static constexpr int META_WARP = 32 * F8_MAXKG * 4 + 32 * 8 + 2 * F8_MAXKG * 4 + 32 * 8;
+  static constexpr int META_WARP = 32 * F8_MAXKG * 4 + 32 * 8 + 2 * F8_MAXKG * 4;
   static constexpr int META = 8 * META_WARP;  // per epilogue warp: activation scales, slot, weight of its 32 columns, weight scales
-  static constexpr int SMEM = STAGES * STAGE + 1024 + 256 + META + F8_CACHED * 12;
+  static constexpr int SMEM = STAGES * STAGE + 1024 + 256 + META + F8_CACHED * 12 + F8_WS_FLOATS * 4;
   static constexpr int TMEM = 512;
 };
 
 // Optional timeline of CTA 0 (compile with -DB200_TRACE): %globaltimer stamps of the producer's TMA issues (row 0),
 // the MMA issuer's stage arrivals (row 1), the first epilogue warp's promotions (row 2) and tile boundaries (row 3).
 #ifdef B200_TRACE
-__device__ unsigned long long g_trace[4][256];
+__device__ unsigned long long g_trace[6][256];
+__device__ unsigned long long g_cta[256][4];
 #define TRACE(k, i) do { if (blockIdx.x == 0 && (i) < 256) g_trace[k][i] = globaltimer(); } while (0)
 #else
 #define TRACE(k, i) do { } while (0)
@@ -154,6 +156,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint8_t* meta = smem + C::STAGES * C::STAGE + 256;
   int* tinfo = reinterpret_cast<int*>(meta + C::META);
+  float* ws_cache = reinterpret_cast<float*>(tinfo + F8_CACHED * 3);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -176,11 +179,15 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   // consecutive tiles mostly share their block and its metadata.  The list entries of the CTA's blocks are
   // read once, before the weight stream starts: afterwards a dependent global load costs microseconds (it
   // queues behind the stages in flight).
-  const int nblocks = LM ? 1 : p.L.nblocks[0];
+  // (The dense modes have no lists: their blocks are the 64-row chunks of the token rows, and a tile is
+  // (weight tile, chunk) with the chunk fastest, so the chunks of one weight tile run back to back on one CTA
+  // and all but the first find the weight tile in L2.)
+  const int nblocks = LM ? (p.total_rows + 63) / 64 : p.L.nblocks[0];
   const int ntiles = nblocks * p.mtiles;
   const int t_lo = static_cast<int>(static_cast<long long>(blockIdx.x) * ntiles / gridDim.x);
   const int t_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * ntiles / gridDim.x);
   const int blk_lo = t_lo / p.mtiles;
+  auto blk_of = [&](int tile) { return LM ? tile % nblocks : tile / p.mtiles; };
   if (!LM && threadIdx.x < F8_CACHED) {
     const int blk = blk_lo + threadIdx.x;
     if (blk < nblocks && blk * p.mtiles < t_hi) {
@@ -192,12 +199,12 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
 
   auto decode = [&](int tile, int& e, int& row0, int& n, int& mt) -> bool {
-    if (LM) {  // dense: every tile is 128 vocabulary rows against all the tokens
+    if (LM) {  // dense: 128 weight rows against one 64-row chunk of the tokens
       e = 0;
-      row0 = 0;
-      n = p.total_rows;
-      mt = tile;
-      return n >= 1 && n <= 64;
+      mt = tile / nblocks;
+      row0 = (tile - mt * nblocks) * 64;
+      n = p.total_rows - row0 < 64 ? p.total_rows - row0 : 64;
+      return n >= 1;
     }
     const int blk = tile / p.mtiles;
     mt = tile - blk * p.mtiles;
@@ -225,13 +232,13 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     int slot;
   };
   const int ep_half = (warp - 2) >> 2;
-  auto fetch = [&](int blk, Meta& m) {
+  auto fetch = [&](int tile, Meta& m) {  // the metadata of the block that `tile` belongs to
     m.wt = 0.f;
     m.slot = -1;
 #pragma unroll
     for (int u = 0; u < 16; ++u) m.v[u] = 0.f;
     int e, row0, n, mt;
-    if (blk >= nblocks || blk * p.mtiles >= t_hi || !decode(blk * p.mtiles, e, row0, n, mt)) return;
+    if (tile >= t_hi || !decode(tile, e, row0, n, mt)) return;
     const int c = (lane >> 4) * 32 + ep_half * 16 + (lane & 15);
     if (!LM && c < n) {
       m.slot = p.L.slot_of_row[row0 + c];
@@ -248,10 +255,16 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   };
+  // Weight block scales: those of the CTA's first tiles are read into shared memory by the epilogue warps while the
+  // first stages are in flight (a dependent global load issued once the weight stream saturates the memory system
+  // takes microseconds, and one per tile was what paced these kernels); tiles past the cache fall back on a
+  // register queue loaded two tiles ahead.
+  const int ws_per_tile = C::NA * p.ksteps;
+  const int ws_ncache = (t_hi - t_lo) < F8_WS_FLOATS / ws_per_tile ? (t_hi - t_lo) : F8_WS_FLOATS / ws_per_tile;
   auto load_ws = [&](int tile, float& w0, float& w1) {
     w0 = w1 = 0.f;
     int e, row0, n, mt;
-    if (tile >= t_hi || lane >= p.ksteps || !decode(tile, e, row0, n, mt)) return;
+    if (tile - t_lo < ws_ncache || tile >= t_hi || lane >= p.ksteps || !decode(tile, e, row0, n, mt)) return;
     const float* swb = (e == p.E_local) ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * (p.w_rows / 128) * p.ksteps;
     w0 = swb[static_cast<size_t>(mt) * p.ksteps + lane];                        // gate / down block row
     if (UP) w1 = swb[static_cast<size_t>(p.I / 128 + mt) * p.ksteps + lane];    // up block row
@@ -259,7 +272,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   Meta pre;
   float wsa1 = 0.f, wsb1 = 0.f, wsa2 = 0.f, wsb2 = 0.f;
   if (warp >= 2) {
-    fetch(blk_lo, pre);
+    fetch(t_lo, pre);
     load_ws(t_lo, wsa1, wsb1);
     load_ws(t_lo + 1, wsa2, wsb2);
   }
@@ -270,6 +283,9 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) TRACE(3, 0);
+#ifdef B200_TRACE
+  if (threadIdx.x == 0 && blockIdx.x < 256) { g_cta[blockIdx.x][0] = globaltimer(); g_cta[blockIdx.x][2] = t_hi - t_lo; }
+#endif
 
   if (warp == 0) {
     if (lane == 0) {  // ---------------- TMA producer ----------------
@@ -371,11 +387,15 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     float* m_wt = m_as + 32 * F8_MAXKG;                                        // [32]
     int* m_slot = reinterpret_cast<int*>(m_wt + 32);                           // [32]
     float* m_ws = reinterpret_cast<float*>(m_slot + 32);                       // [2][F8_MAXKG] weight block scales
-    bf16** m_dst = reinterpret_cast<bf16**>(m_ws + 2 * F8_MAXKG);              // [32] destination row (down)
     const float* __restrict__ a_scale = p.a_scale;
     uint32_t g = 0;
     bool ok = true;
-    // local column l (0..31) of this warp is tile column col(l) = (l / 16) * 32 + half * 16 + l % 16
+    // local column l (0..31) of this warp is tile column col(l) = (l / 16) * 32 + half * 16 + l % 16.
+    // Destination row and routing weight of local column `lane` stay in this lane's registers and reach the
+    // other lanes by shuffles in the down epilogue (a shared-memory read per stored value there made one
+    // dependent round trip per column, 1.7 us per tile).
+    bf16* cur_dst = nullptr;
+    float cur_wt = 0.f;
     auto stage_block = [&](int row0, int n) {
       const int total = 32 * p.ksteps;
 #pragma unroll
@@ -410,33 +430,53 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             dst = p.cache + static_cast<size_t>(slot) * p.H;
           }
         }
-        m_dst[lane] = dst;
+        cur_dst = dst;
+        cur_wt = pre.wt;
       }
     };
     int staged_blk = -1;
-    if (LM) stage_block(0, p.total_rows);  // the dense modes have one block of token rows: staged once
+    for (int idx = static_cast<int>(threadIdx.x) - 64; idx < ws_ncache * ws_per_tile; idx += F8_THREADS - 64) {
+      const int ti = idx / ws_per_tile, rem = idx - ti * ws_per_tile;
+      const int which = rem / p.ksteps, ks = rem - which * p.ksteps;
+      int e, row0, n, mt;
+      float v = 0.f;
+      if (decode(t_lo + ti, e, row0, n, mt)) {
+        const float* swb = (e == p.E_local) ? p.s_w_sh : p.s_w + static_cast<size_t>(e) * (p.w_rows / 128) * p.ksteps;
+        v = swb[static_cast<size_t>(which ? p.I / 128 + mt : mt) * p.ksteps + ks];
+      }
+      ws_cache[idx] = v;
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");  // the epilogue warps' fill of ws_cache is complete
     for (int tile = t_lo; ok && tile < t_hi; ++tile) {
       int e, row0, n, mt;
+      const bool cached = tile - t_lo < ws_ncache;
       const float ws_a = wsa1, ws_b = wsb1;  // this tile's weight block scales; the queue moves on every tile
       wsa1 = wsa2;
       wsb1 = wsb2;
-      load_ws(tile + 2, wsa2, wsb2);
+      load_ws(tile + 2, wsa2, wsb2);  // returns at once for a cached tile
       if (!decode(tile, e, row0, n, mt)) {
         if (lane == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_LIST);
         continue;
       }
       __syncwarp();
-      const int blk = LM ? 0 : tile / p.mtiles;
-      if (!LM && blk != staged_blk) {  // first tile of a block
+#ifndef B200_EXP_STAMP2
+      if (warp == 2 && lane == 0) TRACE(5, tile - t_lo);
+#endif
+      const int blk = blk_of(tile);
+      if (blk != staged_blk) {  // first tile of a block (dense modes: of a chunk of token rows)
         staged_blk = blk;
         stage_block(row0, n);
-        fetch(blk + 1, pre);  // in flight during this block's tiles
+        // the next block's metadata is requested now and consumed at that block's first tile
+        const int next = LM ? (nblocks > 1 ? tile + 1 : t_hi) : (blk + 1) * p.mtiles;
+        fetch(next, pre);
       }
-      if (lane < p.ksteps) {
+      if (!cached && lane < p.ksteps) {
         m_ws[lane] = ws_a;
         if (UP) m_ws[F8_MAXKG + lane] = ws_b;
       }
       __syncwarp();
+      const float* __restrict__ wsc_a = cached ? ws_cache + (tile - t_lo) * ws_per_tile : m_ws;
+      const float* __restrict__ wsc_b = cached ? wsc_a + p.ksteps : m_ws + F8_MAXKG;
       if (warp == 2 && lane == 0) TRACE(3, 2 + 2 * ((tile - t_lo)));
       float acc_a[32], acc_b[UP ? 32 : 1];
 #pragma unroll
@@ -446,7 +486,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         for (int c = 0; c < 32; ++c) acc_b[c] = 0.f;
       for (int ks = 0; ks < p.ksteps; ++ks, ++g) {
         const uint32_t pb = g % C::NPB, pphase = (g / C::NPB) & 1u;
-        const float wsa = m_ws[ks], wsb = UP ? m_ws[F8_MAXKG + ks] : 0.f;
+        const float wsa = wsc_a[ks], wsb = UP ? wsc_b[ks] : 0.f;
         if (!mbar_wait(&pfull[pb], pphase, abort_flag, p.status, ST_WAIT_TMEM_FULL)) {
           ok = false;
           break;
@@ -475,6 +515,9 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       if (!ok) break;
       if (warp == 2 && lane == 0) TRACE(3, 3 + 2 * ((tile - t_lo)));
+#ifdef B200_EXP_STAMP2
+      if (warp == 2 && lane == 0) TRACE(5, tile - t_lo);
+#endif
       const int r = mt * 128 + q * 32 + lane;
       if (DENSE) {
         // plain projection: out[token][feature] = bf16(acc)
@@ -486,7 +529,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
           for (int l = 0; l < 32; ++l) {
             const int c = (l >> 4) * 32 + half * 16 + (l & 15);
-            if (c < n) o[static_cast<size_t>(c) * ld] = f2bf(acc_a[l]);
+            if (c < n) st_global_na(o + static_cast<size_t>(row0 + c) * ld, f2bf(acc_a[l]));
           }
         }
       } else if (LM) {
@@ -502,7 +545,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           mv[l] = live ? acc_a[l] : __int_as_float(0x7fc00000);
           if (p.lm_logits && live) {
             const int c = (l >> 4) * 32 + half * 16 + (l & 15);
-            if (c < n) p.lm_logits[static_cast<size_t>(c) * p.lm_ld + r] = acc_a[l];
+            if (c < n) st_global_na(p.lm_logits + static_cast<size_t>(row0 + c) * p.lm_ld + r, acc_a[l]);
           }
         }
 #pragma unroll
@@ -538,7 +581,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             } else if (live_mask) {  // only NaN among the live rows: value part 1, the lowest live row
               key = (1ull << 32) | (0xffffffffu - static_cast<uint32_t>(base_id + __ffs(live_mask) - 1));
             }
-            p.lm_keys[(static_cast<size_t>(tile) * 4 + q) * n + c] = key;
+            p.lm_keys[(static_cast<size_t>(mt) * 4 + q) * p.total_rows + row0 + c] = key;
           }
         }
       } else if (UP) {
@@ -549,21 +592,28 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           if (c < n) {
             const float gv = rbf(acc_a[l]), uv = rbf(acc_b[l]);
             const bf16 hv = f2bf(__fmul_rn(__fdiv_rn(gv, 1.f + __expf(-gv)), uv));
-            hout[static_cast<size_t>(c) * p.I] = hv;
-            if (p.dbg_h && m_slot[l] >= 0) p.dbg_h[static_cast<size_t>(m_slot[l]) * p.I + r] = hv;
+            st_global_na(hout + static_cast<size_t>(c) * p.I, hv);
+            if (p.dbg_h && m_slot[l] >= 0) st_global_na(p.dbg_h + static_cast<size_t>(m_slot[l]) * p.I + r, hv);
           }
         }
       } else {
 #pragma unroll
         for (int l = 0; l < 32; ++l) {
           const int c = (l >> 4) * 32 + half * 16 + (l & 15);
-          bf16* dst = m_dst[l];
-          if (c < n && dst != nullptr) dst[r] = f2bf(__fmul_rn(acc_a[l], m_wt[l]));
+          if (c < n) {  // the same for every lane of the warp
+            bf16* dst = reinterpret_cast<bf16*>(__shfl_sync(FULL_MASK, reinterpret_cast<unsigned long long>(cur_dst), l));
+            const float wt = __shfl_sync(FULL_MASK, cur_wt, l);
+            if (dst != nullptr) st_global_na(dst + r, f2bf(__fmul_rn(acc_a[l], wt)));
+          }
         }
       }
+      if (warp == 2 && lane == 0) TRACE(4, tile - t_lo);
     }
   }
   if (warp == 2 && lane == 0) TRACE(3, 1);
+#ifdef B200_TRACE
+  if (warp == 2 && lane == 0 && blockIdx.x < 256) g_cta[blockIdx.x][1] = globaltimer();
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -575,6 +625,9 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #ifdef B200_TRACE
 extern "C" int b200_trace_read(unsigned long long* host) {
   return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace)));
+}
+extern "C" int b200_trace_read_cta(unsigned long long* host) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_cta, sizeof(g_cta)));
 }
 #endif
 
@@ -786,7 +839,7 @@ static LmLayout lm_layout(int T, int H, int V_shard) {
   auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
   LmLayout l;
   size_t o = 0;
-  l.xq = o; o = up(o + static_cast<size_t>(64) * H);  // 64 rows so that every 16-row TMA box is in bounds
+  l.xq = o; o = up(o + static_cast<size_t>(T < 64 ? 64 : T) * H);  // at least 64 rows
   l.xs = o; o = up(o + static_cast<size_t>(T) * (H / 128) * 4);
   l.keys = o; o = up(o + static_cast<size_t>((V_shard + 127) / 128) * 4 * T * 8);
   l.total = o;
@@ -805,8 +858,7 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   if (!x || !w || !w_s || !max_out || !idx_out || !ws) return fail(B200_E_ARG, "b200_lmhead_argmax: null pointer");
   if (T <= 0 || H <= 0 || H % 128 || H / 128 > F8_MAXKG || V_shard <= 0 || shard_lo < 0)
     return fail(B200_E_ARG, "b200_lmhead_argmax: need T >= 1, H %% 128 == 0, H <= 4096 (T=%d H=%d V=%d)", T, H, V_shard);
-  const int TC = T < 64 ? T : 64;  // rows per launch; more rows run as consecutive 64-row chunks over the same workspace
-  const LmLayout l = lm_layout(TC, H, V_shard);
+  const LmLayout l = lm_layout(T, H, V_shard);
   if (ws_bytes < l.total) return fail(B200_E_WS, "b200_lmhead_argmax: workspace %zu < %zu bytes", ws_bytes, l.total);
   if (reinterpret_cast<uintptr_t>(ws) & 1023) return fail(B200_E_ALIGN, "b200_lmhead_argmax: workspace must be 1024-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -817,38 +869,35 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   CUtensorMap tmW, tmX, tmX64;
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(V_shard), H, 128, "lm_head weight"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX, xq, 64, H, 16, "lm_head activations"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX64, xq, 64, H, 64, "lm_head activations"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "lm_head activations"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, 64, "lm_head activations"))) return rc;
   static DeviceOnce once;
   once.run([] {
     cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_LM>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<MODE_LM>::SMEM);
   });
-  for (int t0 = 0; t0 < T; t0 += 64) {
-    const int n = T - t0 < 64 ? T - t0 : 64;
-    // K = 0 routed picks: the "shared expert" row of token t is row t
-    quant_permute_f8_kernel<<<n, 256, 0, st>>>(static_cast<const bf16*>(x) + static_cast<size_t>(t0) * H, n, H, 0, nullptr, 0,
-                                               n, xq, xs);
-    F8Args a{};
-    a.E_local = 1;
-    a.mtiles = (V_shard + 127) / 128;
-    a.ksteps = H / 128;
-    a.w_rows = V_shard;
-    a.I = 0;
-    a.H = H;
-    a.total_rows = n;
-    a.s_w = w_s;
-    a.s_w_sh = w_s;
-    a.a_scale = xs;
-    a.status = status;
-    a.lm_keys = keys;
-    a.lm_logits = logits_out ? logits_out + static_cast<size_t>(t0) * V_shard : nullptr;
-    a.lm_ld = V_shard;
-    a.lm_shard_lo = shard_lo;
-    const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
-    moe_gemm_f8_kernel<MODE_LM><<<grid, F8_THREADS, F8Cfg<MODE_LM>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
-    launch_k(lmhead_finish_kernel, dim3(n), dim3(256), 0, st, static_cast<const unsigned long long*>(keys), a.mtiles * 4, n,
-             max_out + t0, idx_out + t0);
-  }
+  // K = 0 routed picks: the "shared expert" row of token t is row t
+  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, xq, xs);
+  F8Args a{};
+  a.E_local = 1;
+  a.mtiles = (V_shard + 127) / 128;
+  a.ksteps = H / 128;
+  a.w_rows = V_shard;
+  a.I = 0;
+  a.H = H;
+  a.total_rows = T;   // more than 64 rows: 64-row chunks, every weight tile against each chunk in turn
+  a.s_w = w_s;
+  a.s_w_sh = w_s;
+  a.a_scale = xs;
+  a.status = status;
+  a.lm_keys = keys;
+  a.lm_logits = logits_out;
+  a.lm_ld = V_shard;
+  a.lm_shard_lo = shard_lo;
+  const int ntiles = a.mtiles * ((T + 63) / 64);
+  const int grid = ntiles < sm_count() ? ntiles : sm_count();
+  moe_gemm_f8_kernel<MODE_LM><<<grid, F8_THREADS, F8Cfg<MODE_LM>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
+  launch_k(lmhead_finish_kernel, dim3(T), dim3(256), 0, st, static_cast<const unsigned long long*>(keys), a.mtiles * 4, T,
+           max_out, idx_out);
   return launch_status("b200_lmhead_argmax");
 }
 
@@ -905,7 +954,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const bf16* __restrict
 extern "C" size_t b200_dense_fp8_workspace_bytes(int T, int H) {
   if (T <= 0 || H <= 0) return 0;
   auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
-  return up(static_cast<size_t>(64) * H) + up(static_cast<size_t>(64) * (H / 128) * 4);
+  return up(static_cast<size_t>(T < 64 ? 64 : T) * H) + up(static_cast<size_t>(T) * (H / 128) * 4);
 }
 
 extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, const float* w_s, int N, int nseg,
@@ -930,45 +979,41 @@ extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, 
   if (reinterpret_cast<uintptr_t>(ws) & 1023) return fail(B200_E_ALIGN, "b200_dense_fp8: workspace must be 1024-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* xq = static_cast<uint8_t*>(ws);
-  float* xs = reinterpret_cast<float*>(xq + ((static_cast<size_t>(64) * H + 1023) & ~size_t(1023)));
+  float* xs = reinterpret_cast<float*>(xq + ((static_cast<size_t>(T < 64 ? 64 : T) * H + 1023) & ~size_t(1023)));
   CUtensorMap tmW, tmX, tmX64;
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(N), H, 128, "dense weight"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX, xq, 64, H, 16, "dense activations"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX64, xq, 64, H, 64, "dense activations"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "dense activations"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, 64, "dense activations"))) return rc;
   static DeviceOnce once;
   once.run([] {
     cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          F8Cfg<MODE_DENSE>::SMEM);
   });
-  // more than 64 rows run as consecutive 64-row chunks over the same workspace (stream order keeps them apart)
-  for (int t0 = 0; t0 < T; t0 += 64) {
-    const int n = T - t0 < 64 ? T - t0 : 64;
-    quant_permute_f8_kernel<<<n, 256, 0, st>>>(static_cast<const bf16*>(x) + static_cast<size_t>(t0) * H, n, H, 0, nullptr, 0,
-                                               n, xq, xs);
-    F8Args a{};
-    a.E_local = 1;
-    a.mtiles = (N + 127) / 128;
-    a.ksteps = H / 128;
-    a.w_rows = N;
-    a.H = H;
-    a.total_rows = n;
-    a.s_w = w_s;
-    a.s_w_sh = w_s;
-    a.a_scale = xs;
-    a.status = status;
-    a.nseg = nseg;
-    int c0 = 0;
-    for (int i = 0; i < nseg; ++i) {
-      a.seg_lo[i] = c0;
-      a.seg_ld[i] = seg_ld_host[i];
-      a.seg_out[i] = static_cast<bf16*>(seg_out_host[i]) + static_cast<size_t>(t0) * seg_ld_host[i];
-      c0 += seg_cols_host[i];
-    }
-    a.seg_lo[nseg] = c0;
-    const int grid = a.mtiles < sm_count() ? a.mtiles : sm_count();
-    moe_gemm_f8_kernel<MODE_DENSE><<<grid, F8_THREADS, F8Cfg<MODE_DENSE>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
+  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, xq, xs);
+  F8Args a{};
+  a.E_local = 1;
+  a.mtiles = (N + 127) / 128;
+  a.ksteps = H / 128;
+  a.w_rows = N;
+  a.H = H;
+  a.total_rows = T;   // more than 64 rows: 64-row chunks, every weight tile against each chunk in turn
+  a.s_w = w_s;
+  a.s_w_sh = w_s;
+  a.a_scale = xs;
+  a.status = status;
+  a.nseg = nseg;
+  int c0 = 0;
+  for (int i = 0; i < nseg; ++i) {
+    a.seg_lo[i] = c0;
+    a.seg_ld[i] = seg_ld_host[i];
+    a.seg_out[i] = static_cast<bf16*>(seg_out_host[i]);
+    c0 += seg_cols_host[i];
   }
+  a.seg_lo[nseg] = c0;
+  const int ntiles = a.mtiles * ((T + 63) / 64);
+  const int grid = ntiles < sm_count() ? ntiles : sm_count();
+  moe_gemm_f8_kernel<MODE_DENSE><<<grid, F8_THREADS, F8Cfg<MODE_DENSE>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
   return launch_status("b200_dense_fp8");
 }
 

@@ -49,12 +49,16 @@ class DecodeStep:
     Every rank draws the same model from `seed` and keeps its part.  `gate`: an optional `parallel.StepGate`."""
 
     def __init__(self, layers=48, B=8, ctx=8192, vocab=151936, experts=E, seed=1005, device="cuda", gdn_layout="explicit",
-                 ring_fill=0, ep=None, gate=None):
+                 ring_fill=0, ep=None, gate=None, attn_splits=None):
         if gdn_layout not in ("explicit", "ring"):
             raise ValueError("gdn_layout is 'explicit' or 'ring'")
         self.gdn_layout = gdn_layout
         self.ep = ep
         self.gate = gate        # optional parallel.StepGate: host-side roll call of the ranks before every step
+        # CTAs per (request, kv head) of the attention core; None lets the kernel fill the GPU for this rank's
+        # batch.  The split count sets the order in which partial sums are merged, so two forms of the step give
+        # the same bits only with the same count.
+        self.attn_splits = attn_splits
         self.world = 1 if ep is None else ep.world
         self.rank = 0 if ep is None else ep.rank
         if B % self.world or experts % self.world:
@@ -153,7 +157,7 @@ class DecodeStep:
         self.gdn_ws = ops.gdn_workspace(Bl, dev)
         self.dense_ws = ops.dense_fp8_workspace(T, 4096, dev)
         self.gdn_in = [torch.empty(T, wd, dtype=bf, device=dev) for wd in GDN_SPLIT]
-        self.lm_ws = ops.lmhead_workspace(min(Ta, 64), H, self.shard_hi - self.shard_lo, dev)
+        self.lm_ws = ops.lmhead_workspace(Ta if ep is not None else T, H, self.shard_hi - self.shard_lo, dev)
         if ep is None:
             self.cache = torch.zeros(T * (K + 1), H, dtype=bf, device=dev)
         else:
@@ -223,7 +227,8 @@ class DecodeStep:
         if L["attn"]:
             q, gate, k, v = ops.attn_front(h, L["qkv_w"], L["qkv_s"], L["q_norm"], L["k_norm"], self.positions,
                                            self.cos_sin, 1e-6, True, status=st)
-            core = ops.attn_verify(q, gate, k, v, L["kcache"], L["vcache"], L["page_table"], self.seqlens, status=st)
+            core = ops.attn_verify(q, gate, k, v, L["kcache"], L["vcache"], L["page_table"], self.seqlens,
+                                   splits=self.attn_splits, status=st)
             proj = ops.dense_fp8(core, L["o_w"], L["o_s"], ws=self.dense_ws, status=st)
             return proj, 2 + 3 + 2 * self._chunks
         mixed, z, b, a = ops.dense_fp8_split(h, L["in_w"], L["in_s"], GDN_SPLIT, outs=self.gdn_in, ws=self.dense_ws, status=st)
@@ -244,7 +249,7 @@ class DecodeStep:
         group must meet (the caller runs the barrier, or advances the other virtual ranks); returns the tokens."""
         st, ep = self.status, self.ep
         T, R = self.T, self.rank
-        self._chunks = (T + 63) // 64
+        self._chunks = 1          # the dense projections take any number of rows in one launch
         residual = torch.zeros_like(x)
         h = ops.add_rmsnorm(x, residual, self.first_norm)          # residual <- x, h = norm(x)
         n = 1
@@ -286,7 +291,7 @@ class DecodeStep:
         ops.ep_put(idx, R * Ta * 4, self.peer_idx)
         yield 3
         tokens = ops.argmax_merge(self.max_all, self.idx_all)      # the tokens of ALL sequences, on every rank
-        self.launches = n + 1 + 1 + 3 * ((Ta + 63) // 64) + 2 + 1 + 1
+        self.launches = n + 1 + 1 + 3 + 2 + 1 + 1
         return tokens
 
     def step(self, x: torch.Tensor) -> torch.Tensor:

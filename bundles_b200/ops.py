@@ -387,8 +387,7 @@ def dense_fp8_workspace(T, H, device):
 
 
 def dense_fp8(x, w, w_s, out=None, ws=None, status=None):
-    """Decode-width projection out = bf16(x . W^T) with an fp8 block-scaled weight; more than 64 rows run as
-    consecutive 64-row launches (reference: qk_proj_decode gdn_in_proj / qkv_proj / dense8)."""
+    """Decode-width projection out = bf16(x . W^T) with an fp8 block-scaled weight, any number of rows (reference: qk_proj_decode gdn_in_proj / qkv_proj / dense8)."""
     _need(x, torch.bfloat16, "x", 2)
     _need(w, torch.uint8, "w", 2)
     _need(w_s, torch.float32, "w_s", 2)

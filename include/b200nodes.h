@@ -368,8 +368,8 @@ int b200_attn_front(const void* x, int T, const void* w, const float* w_s, const
  * target keeps every weight in the one fp8 block-scaled format.
  *   b200_dense_fp8: out[T,N] = bf16(x[T,H] . W[N,H]^T), x bf16 quantised per token per 128
  *     channels, W e4m3 [N,H] with scales fp32 [ceil(N/128), H/128], per-128-k promotion;
- *     T >= 1 (more than 64 rows run as consecutive 64-row launches), H % 128 == 0, H <= 4096;
-     ws: b200_dense_fp8_workspace_bytes(T,H), 1024-aligned.
+ *     T >= 1 (more than 64 rows: 64-row chunks, every weight tile against each chunk in turn inside one launch),
+     H % 128 == 0, H <= 4096; ws: b200_dense_fp8_workspace_bytes(T,H), 1024-aligned.
  *   b200_dense_fp8_split: the same GEMM with the N output features cut into 1..4 consecutive segments, segment i
  *     (seg_cols_host[i] features, a multiple of 32 except the last) written to seg_out_host[i] with row pitch
  *     seg_ld_host[i] elements: the GDN in_proj's [q k v | z | b | a] land in the four buffers the verify kernel
@@ -392,7 +392,7 @@ int b200_add_rmsnorm(const void* proj, void* residual, const void* w, float eps,
  * side, weight streamed once); the reference returns logits and has no argmax
  * (node.py:136-151).  Per row of x: the largest fp8 block-scaled logit over this shard's
  * vocabulary rows and its global id (shard_lo + local row); ties go to the lower id, NaN never wins.
- *   x bf16 [T,H], T >= 1 (more than 64 rows run as consecutive 64-row launches), H % 128 == 0, H <= 4096;
+ *   x bf16 [T,H], T >= 1 (more than 64 rows: 64-row chunks inside one launch), H % 128 == 0, H <= 4096;
  *   w e4m3 [V_shard,H];
  *   w_s fp32 [ceil(V_shard/128), H/128]; max_out fp32 [T]; idx_out int32 [T];
  *   logits_out fp32 [T,V_shard] or NULL; ws: b200_lmhead_workspace_bytes(T,H,V_shard) bytes,

@@ -69,7 +69,7 @@ def _worker(rank, world, port, out):
         # the whole decode + verify step on the ranks (sequences, experts and vocabulary split, the library's own
         # barrier between the phases) against the one-GPU step; twice, the second step on the advanced state
         from bundles_b200 import decode_step
-        kw = dict(layers=4, B=4, ctx=300, vocab=128 * 40 + 17, experts=64, seed=21, device=dev)
+        kw = dict(layers=4, B=4, ctx=300, vocab=128 * 40 + 17, experts=64, seed=21, device=dev, attn_splits=2)
         part = decode_step.DecodeStep(ep=parallel.EpGroup(device=dev), **kw)
         single = decode_step.DecodeStep(**kw)
         gx = torch.Generator(device=dev).manual_seed(5)
