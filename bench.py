@@ -224,6 +224,8 @@ def other_kernels(dev, steps, warmup, only=None):
     out.pop("_int8_peak", None)
     if want("moe_w8a8_t256"):
         _moe_w8a8_block_entry(dev, ops, synth, timed, st, out, hbm, which)
+    if want("moe_fp8_t256"):
+        _moe_fp8_block_entry(dev, ops, timed, st, out, hbm, which, sets=1 if only is not None else 3)
     return out
 
 
@@ -269,6 +271,68 @@ def _moe_w8a8_prefill_entry(dev, ops, synth, timed, st, out):
         del c, w
     except Exception as exc:  # noqa: BLE001
         out["moe_w8a8_prefill"] = {"error": repr(exc)[:300]}
+    torch.cuda.empty_cache()
+
+
+def _moe_fp8_block_entry(dev, ops, timed, st, out, hbm, which, sets=3):
+    # the fp8 expert block of ONE layer at the one-GPU batch-64 shape (256 rows, 512 experts, top-10 + shared) and
+    # at the shape one rank of 8 sees (256 gathered rows, its 64 experts): gate/up and down GEMMs alone, over
+    # `sets` weight sets taken in turn so that every launch streams from HBM
+    import torch
+    from bundles_b200.prepare import quant_fp8_blocks
+    for name, En in (("moe_fp8_t256", 512), ("moe_fp8_t256_rank_of_8", 64)):
+        try:
+            torch.cuda.empty_cache()
+            g = torch.Generator(device=dev).manual_seed(1011)
+
+            def fp8(n, rows, cols):
+                q = torch.empty(n, rows, cols, dtype=torch.uint8, device=dev)
+                sc = torch.empty(n, rows // 128, cols // 128, device=dev)
+                for e0 in range(0, n, 64):
+                    m = min(64, n - e0)
+                    q[e0:e0 + m], sc[e0:e0 + m] = quant_fp8_blocks(torch.randn(m, rows, cols, generator=g, device=dev) * 0.02)
+                return q, sc
+
+            ws_ = []
+            for _ in range(sets):
+                w13, s13 = fp8(En, 2 * I, H)
+                w2, s2 = fp8(En, H, I)
+                sh13, shs13 = quant_fp8_blocks(torch.randn(2 * I, H, generator=g, device=dev) * 0.02)
+                sh2, shs2 = quant_fp8_blocks(torch.randn(H, I, generator=g, device=dev) * 0.02)
+                ws_.append(ops.MoeW8A8Weights(w13, s13, w2, s2, sh13, shs13, sh2, shs2))
+            x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+            wr = torch.randn(512, H, generator=g, device=dev) * 0.02
+            _, ids, wts = ops.router(x, wr, K)
+            lists = ops.RoutingLists(T, K, En, 64, dev)
+            ops.build_lists(ids, wts, lists, None, e_lo=0)          # the rank's experts are ids 0..En-1
+            wsb = ops.moe_fp8_workspace(T, H, I, K, dev)
+            cache = torch.zeros(T * (K + 1), H, dtype=torch.bfloat16, device=dev)
+            for w in ws_:
+                ops.moe_fp8(x, w, lists, cache=cache, ws=wsb, status=st)
+            counts = lists.counts.cpu()
+            act, rows = int((counts > 0).sum().item()), int(counts.sum().item())
+            upb = act * (2 * I * H + 2 * (I // 128) * (H // 128) * 4) + rows * (H + (H // 128) * 4) + rows * I * 2
+            dnb = act * (H * I + (H // 128) * (I // 128) * 4) + rows * (I + (I // 128) * 4) + rows * H * 2
+            it = [0]
+
+            def stage(mask):
+                def run():
+                    w = ws_[it[0] % sets]
+                    it[0] += 1
+                    ops.moe_fp8(x, w, lists, cache=cache, ws=wsb, status=st, stages=mask)
+                return run
+
+            ms_up = timed(stage(ops.STAGE_UP), calls=sets)
+            ms_dn = timed(stage(ops.STAGE_DOWN), calls=sets)
+            ms_all = timed(stage(15), calls=sets)
+            out[name] = {"config": f"fp8 expert block, 256 rows, {En} local experts of 512, top-10 + shared (4 launches)",
+                         "active_experts": act, "rows": rows, "blocks": int(lists.nblocks.item()), "ms": ms_all,
+                         "up": {"ms": ms_up, "algorithmic_bytes": upb, "achieved_gbs": upb / ms_up / 1e6, "frac": upb / ms_up / 1e6 / hbm},
+                         "down": {"ms": ms_dn, "algorithmic_bytes": dnb, "achieved_gbs": dnb / ms_dn / 1e6, "frac": dnb / ms_dn / 1e6 / hbm},
+                         "bound": "hbm", "peak_source": which, "status": ops.read_status(st)}
+            del ws_, wsb, cache, lists
+        except Exception as exc:  # noqa: BLE001
+            out[name] = {"error": repr(exc)[:300]}
     torch.cuda.empty_cache()
 
 
@@ -588,11 +652,50 @@ def _ep_check(dev, ep, world, rank):
     return res
 
 
+def run_step_virtual(args, dev):
+    """Diagnostic (one GPU): the N ranks of the expert-parallel step as virtual ranks in one process, their launches
+    in lockstep on one stream inside one CUDA graph.  The time of one replay divided by N is what one rank of N spends
+    in its own kernels per step (no NVLink latency, no barrier wait); `ncu` on this command lists the rank-shaped
+    kernels.  Prints one JSON line that is NOT the benchmark's headline."""
+    import torch
+    from bundles_b200 import decode_step, ops, parallel
+    n = args.virtual_ranks
+    vg = parallel.VirtualEpGroup(n, dev)
+    steps = [decode_step.DecodeStep(layers=args.layers, B=BATCH, ctx=CTX, vocab=VOCAB, experts=E, seed=1005, device=dev,
+                                    ep=vg.view(r)) for r in range(n)]
+    Tl = steps[0].T
+    g = torch.Generator(device=dev).manual_seed(9000)
+    x_all = torch.randn(steps[0].T_all, H, generator=g, device=dev).to(torch.bfloat16)
+    xs = [x_all[r * Tl:(r + 1) * Tl].contiguous() for r in range(n)]
+    decode_step.step_virtual(steps, xs)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        decode_step.step_virtual(steps, xs)
+    for _ in range(args.warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"diagnostic": "virtual ranks on one GPU", "virtual_ranks": n, "layers": args.layers,
+                      "ms_all_ranks": ms, "ms_per_rank_step": ms / n, "us_per_rank_layer": ms / n * 1000.0 / args.layers,
+                      "launches_per_rank_step": steps[0].launches,
+                      "status": max(ops.read_status(s.status) for s in steps)}), flush=True)
+
+
 def run_step(args, rank, world, local, dev):
     """The default workload on `world` GPUs (one process each)."""
     import torch
     import torch.distributed as dist
     from bundles_b200 import decode_step, ops, parallel
+    if world == 1 and args.virtual_ranks > 1:
+        run_step_virtual(args, dev)
+        return
     ep = parallel.EpGroup(device=dev) if world > 1 else None
     check = None if args.no_ep_check else _ep_check(dev, ep, world, rank)
     t_build = time.perf_counter()
@@ -813,6 +916,8 @@ def main():
     ap.add_argument("--workload", default="step", choices=["step", "moe_int8"],
                     help="step: the 48-layer decode+verify step at batch 64 (default); moe_int8: the int8 W8A8 MoE block at 256 tokens")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers of the step workload (48; fewer only for quick checks)")
+    ap.add_argument("--virtual-ranks", type=int, default=0,
+                    help="one GPU only, diagnostic: run the N-rank expert-parallel step as N virtual ranks and print its time")
     ap.add_argument("--no-ep-check", action="store_true", help="skip the expert-parallel == one-GPU check before the timed runs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel measurements of the other rows")
@@ -820,7 +925,7 @@ def main():
                     help="N > 1: expert-parallel (experts split over ranks) or independent replicas")
     ap.add_argument("--only-kernel", default=None,
                     choices=["gdn_verify", "attn_verify", "attn_front", "lmhead_shard_argmax", "moe_fp8_t16", "router",
-                             "moe_w8a8_prefill", "moe_w8a8_t256"],
+                             "moe_w8a8_prefill", "moe_w8a8_t256", "moe_fp8_t256"],
                     help="run one entry of `kernels` alone with plain launches (a small target for an ncu capture) and exit")
     args = ap.parse_args()
     if args.only_kernel:

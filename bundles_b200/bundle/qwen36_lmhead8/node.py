@@ -26,6 +26,11 @@ def _private_copy(weight: torch.Tensor, group=None):
     key = (weight.device.index, weight.data_ptr(), None if group is None else id(group))
     got = _copies.get(key)
     if got is None:
+        if torch.cuda.is_current_stream_capturing():
+            # the reference builds its private copy outside capture only (node.py:127-128): a copy made while a graph
+            # is being captured would live in the graph's memory pool
+            raise UnsupportedHead("qwen36_lmhead8: the private fp8 copy of lm_head.weight must exist before stream "
+                                  "capture; run one forward (or `prepared.warm(lm_head)`) first")
         V, H = weight.shape
         if H % 128 or H > 4096:
             raise UnsupportedHead(f"qwen36_lmhead8: hidden size {H} is not supported")
@@ -51,22 +56,35 @@ class _Node:
         self.module, self.group = module, group
         self.last_token_ids = None
 
-    def logits(self, lm_head, hidden_states, want_logits=True):
-        """fp32 logits [T, V] (this rank's shard when sharded) and the greedy token ids [T]."""
+    def warm(self, lm_head):
+        """Build the private copy now (call once before the engine captures its graphs)."""
+        _private_copy(lm_head.weight, self.group)
+
+    def logits(self, lm_head, hidden_states):
+        """fp32 logits [T, V] over the whole vocabulary (what the stock processor goes on with) and, as a side
+        effect, the greedy token ids [T] in `last_token_ids`.  With a process group every rank holds one vocabulary
+        shard: the (max, argmax) pairs are gathered and merged, and the shards' logits are gathered into [T, V]."""
         x = hidden_states.to(torch.bfloat16).contiguous()
         codes, scales, lo = _private_copy(lm_head.weight, self.group)
-        outs, toks = [], []
-        for t0 in range(0, x.shape[0], 64):                   # the GEMM takes up to 64 rows per call
-            xs = x[t0:t0 + 64]
-            if self.group is None:
-                mx, idx, lg = ops.lmhead_argmax(xs, codes, scales, lo, want_logits)
-            else:
-                lg = None
-                idx = parallel.sharded_argmax(xs, codes, scales, lo, self.group)
-            outs.append(lg)
-            toks.append(idx)
-        self.last_token_ids = torch.cat(toks)
-        return torch.cat(outs) if outs[0] is not None else None
+        mx, idx, lg = ops.lmhead_argmax(x, codes, scales, lo, True)
+        if self.group is None:
+            self.last_token_ids = idx
+            return lg
+        import torch.distributed as dist
+        world = dist.get_world_size(self.group)
+        T, V = x.shape[0], lm_head.weight.shape[0]
+        maxes = torch.empty(world, T, dtype=torch.float32, device=x.device)
+        idxs = torch.empty(world, T, dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(maxes, mx, group=self.group)
+        dist.all_gather_into_tensor(idxs, idx, group=self.group)
+        self.last_token_ids = ops.argmax_merge(maxes, idxs)
+        shards = parallel.vocab_shards(V, world)
+        wmax = max(hi - lo_ for lo_, hi in shards)
+        mine = torch.zeros(T, wmax, dtype=torch.float32, device=x.device)      # shards differ by one scale block
+        mine[:, :lg.shape[1]] = lg
+        parts = torch.empty(world, T, wmax, dtype=torch.float32, device=x.device)
+        dist.all_gather_into_tensor(parts, mine, group=self.group)
+        return torch.cat([parts[r, :, :hi - lo_] for r, (lo_, hi) in enumerate(shards)], dim=1)
 
     def __call__(self, input_ids, hidden_states, lm_head, logits_metadata, *args, **kwargs):
         node = self

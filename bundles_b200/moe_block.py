@@ -7,6 +7,8 @@ allocated once per (device, T) and reused, as the reference's `Workspace` is (i8
 """
 from __future__ import annotations
 
+from collections import OrderedDict
+
 import torch
 
 from . import ops
@@ -15,6 +17,9 @@ from . import ops
 class MoeBlockW8A8:
     """int8 W8A8 experts (per-output-channel weight scales, per-token activation scales)."""
     BLOCK_ROWS = 128          # largest N tile of the int8 GEMMs
+    GRAPH_MAX_T = 256         # row counts up to this are replayed from a captured CUDA graph (decode / verify batches)
+    CHUNK = 2048              # larger batches (prefill / extend) run eagerly in chunks of at most this many rows
+    MAX_CACHED = 6            # buffer sets / graphs kept (least recently used beyond that are dropped)
 
     def __init__(self, wr, weights: ops.MoeW8A8Weights, gate_w, top_k, bias=None, e_lo=0, round_bf16=False,
                  use_graph=True):
@@ -23,8 +28,8 @@ class MoeBlockW8A8:
         self.E_local = weights.w13.shape[0]
         self.I = weights.w2.shape[-1]
         self.H = weights.w13.shape[-1]
-        self._ws = {}
-        self._graphs = {}
+        self._ws = OrderedDict()
+        self._graphs = OrderedDict()
         self._pipes = {}
         self.use_graph = use_graph
         self.status = ops.new_status(wr.device)
@@ -32,7 +37,11 @@ class MoeBlockW8A8:
 
     def _buffers(self, T, device):
         b = self._ws.get(T)
+        if b is not None:
+            self._ws.move_to_end(T)
         if b is None:
+            while len(self._ws) >= self.MAX_CACHED:      # variable-length batches must not grow memory without bound
+                self._ws.popitem(last=False)
             K = self.top_k
             b = dict(lists=ops.RoutingLists(T, K, self.E_local, self.BLOCK_ROWS, device),
                      ws=self._workspace(T, K, device),
@@ -49,12 +58,22 @@ class MoeBlockW8A8:
         positions) are captured once into a CUDA graph and replayed (the reference's ops run inside the
         engine's captured decode graph as well, layer.py:174-189); the input is copied into the graph's
         static buffer and the returned tensor is the graph's static output, overwritten by the next call."""
-        if not self.use_graph or torch.cuda.is_current_stream_capturing():
-            return self._forward_eager(x, positions)
         T = x.shape[0]
+        if T > self.CHUNK:          # prefill-sized batch: chunks through one reusable buffer set per chunk size
+            outs = []
+            for t0 in range(0, T, self.CHUNK):
+                ps = None if positions is None else positions[t0:t0 + self.CHUNK].contiguous()
+                outs.append(self._forward_eager(x[t0:t0 + self.CHUNK].contiguous(), ps).clone())
+            return torch.cat(outs)
+        if not self.use_graph or T > self.GRAPH_MAX_T or torch.cuda.is_current_stream_capturing():
+            return self._forward_eager(x, positions)
         key = (T, positions is not None)
         g = self._graphs.get(key)
+        if g is not None:
+            self._graphs.move_to_end(key)
         if g is None:
+            while len(self._graphs) >= self.MAX_CACHED:
+                self._graphs.popitem(last=False)
             dev = self.wr.device
             xs = torch.empty(x.shape, dtype=x.dtype, device=dev)
             ps = None if positions is None else torch.empty(positions.shape, dtype=positions.dtype, device=dev)
@@ -86,6 +105,19 @@ class MoeBlockW8A8:
                                out=b["out"])
 
     __call__ = forward
+
+    def forward_combine_norm(self, x, positions, residual, norm_w, eps):
+        """One pass of the block whose combine also does the next layer's residual add and input norm (the reference's
+        combine_norm, qk_route.cu:779-819): `residual` <- bf16(out + residual) in place; returns (out, normed), both
+        fresh tensors.  Runs eagerly on the current stream (inside the engine's own graph capture, if any)."""
+        T = x.shape[0]
+        b = self._buffers(T, x.device)
+        ops.router(x, self.wr, self.top_k, self.bias, self.round_bf16, scratch=b["scratch"], want_logits=False,
+                   ids=b["ids"], wts=b["wts"])
+        ops.build_lists(b["ids"], b["wts"], b["lists"], positions, e_lo=self.e_lo, with_shared=self.w.sh13 is not None)
+        self._experts(x, b)
+        return ops.moe_combine_norm(b["cache"], x, self.gate_w if self.w.sh13 is not None else None, self.top_k, residual,
+                                    norm_w, eps, positions)
 
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
         """Host-to-host form for a serving loop: `x_host` (pinned bf16 [T, H]) is copied in, the block runs, and

@@ -22,6 +22,21 @@ _lib.define("attn_verify(Tensor q, Tensor gate, Tensor k_new, Tensor v_new, Tens
             "Tensor page_table, Tensor seqlens, float scale) -> Tensor")
 _lib.define("lmhead_argmax(Tensor x, Tensor w, Tensor w_s, int shard_lo) -> (Tensor, Tensor)")
 _lib.define("moe_combine(Tensor cache, Tensor x, Tensor? gate_w, int top_k, Tensor? pos) -> Tensor")
+_lib.define("moe_combine_norm(Tensor cache, Tensor x, Tensor? gate_w, int top_k, Tensor(a!) residual, Tensor norm_w, "
+            "float eps, Tensor? pos) -> (Tensor, Tensor)")
+# The routing lists travel as one int32 tensor and one fp32 tensor (the C ABI's nine device arrays laid end to end,
+# see `lists_pack`), so that the three MoE ops below compose through the registry without Python objects.
+_lib.define("build_lists(Tensor ids, Tensor wts, Tensor? pos, int e_lo, int n_local, int block_rows, bool with_shared) "
+            "-> (Tensor, Tensor)")
+_lib.define("moe_w8a8(Tensor x, Tensor w13, Tensor s13, Tensor w2, Tensor s2, Tensor? sh13, Tensor? shs13, Tensor? sh2, "
+            "Tensor? shs2, Tensor lists_i, Tensor lists_f, int top_k, int block_rows) -> Tensor")
+_lib.define("moe_fp8(Tensor x, Tensor w13, Tensor s13, Tensor w2, Tensor s2, Tensor? sh13, Tensor? shs13, Tensor? sh2, "
+            "Tensor? shs2, Tensor lists_i, Tensor lists_f, int top_k, int block_rows) -> Tensor")
+_lib.define("dense_fp8(Tensor x, Tensor w, Tensor w_s) -> Tensor")
+_lib.define("add_rmsnorm(Tensor proj, Tensor(a!) residual, Tensor w, float eps) -> Tensor")
+_lib.define("argmax_merge(Tensor maxes, Tensor idxs) -> Tensor")
+_lib.define("gdn_ring_fold(Tensor(a!) checkpoint, Tensor d_ring, Tensor dlo_ring, Tensor k_ring, Tensor klo_ring, "
+            "Tensor g_ring, Tensor state_idx, Tensor ring_idx, Tensor write_pos, Tensor cache_base) -> ()")
 
 
 def _router(x, wr, bias, top_k, round_bf16):
@@ -56,7 +71,80 @@ def _combine(cache, x, gate_w, top_k, pos):
     return ops.moe_combine(cache, x, gate_w, top_k, pos)
 
 
+def _combine_norm(cache, x, gate_w, top_k, residual, norm_w, eps, pos):
+    return ops.moe_combine_norm(cache, x, gate_w, top_k, residual, norm_w, eps, pos)
+
+
+def lists_pack(T, K, n_local, block_rows, device):
+    """RoutingLists whose nine arrays are views into one int32 and one fp32 tensor."""
+    mb = ops._lib.lib().b200_moe_max_blocks(T, K, n_local, block_rows)
+    sizes = [n_local + 1, n_local + 2, T * K, T * (K + 1), mb, mb, mb, 1]
+    li = torch.zeros(sum(sizes), dtype=torch.int32, device=device)
+    lf = torch.zeros(T * (K + 1), dtype=torch.float32, device=device)
+    return _lists_view(li, lf, T, K, n_local, block_rows), li, lf
+
+
+def _lists_view(li, lf, T, K, n_local, block_rows):
+    mb = ops._lib.lib().b200_moe_max_blocks(T, K, n_local, block_rows)
+    sizes = [n_local + 1, n_local + 2, T * K, T * (K + 1), mb, mb, mb, 1]
+    if li.numel() != sum(sizes) or lf.numel() != T * (K + 1):
+        raise ops.B200Error("routing-list tensors do not match (T, K, n_local, block_rows)")
+    parts = torch.split(li, sizes)
+    L = ops.RoutingLists.__new__(ops.RoutingLists)
+    L.T, L.K, L.E_local, L.block_rows, L.max_blocks = T, K, n_local, block_rows, mb
+    (L.counts, L.offsets, L.row_of_pair, L.slot_of_row, L.blk_expert, L.blk_row0, L.blk_rows, L.nblocks) = parts
+    L.wt_of_row = lf
+    L.c = ops.MoeLists(*[t.data_ptr() for t in (L.counts, L.offsets, L.row_of_pair, L.slot_of_row, L.wt_of_row,
+                                                 L.blk_expert, L.blk_row0, L.blk_rows, L.nblocks)])
+    return L
+
+
+def _build_lists(ids, wts, pos, e_lo, n_local, block_rows, with_shared):
+    T, K = ids.shape
+    L, li, lf = lists_pack(T, K, n_local, block_rows, ids.device)
+    ops.build_lists(ids, wts, L, pos, e_lo=e_lo, with_shared=with_shared)
+    return li, lf
+
+
+def _weights(w13, s13, w2, s2, sh13, shs13, sh2, shs2):
+    return ops.MoeW8A8Weights(w13, s13, w2, s2, sh13, shs13, sh2, shs2)
+
+
+def _moe_w8a8(x, w13, s13, w2, s2, sh13, shs13, sh2, shs2, lists_i, lists_f, top_k, block_rows):
+    L = _lists_view(lists_i, lists_f, x.shape[0], top_k, w13.shape[0], block_rows)
+    return ops.moe_w8a8(x, _weights(w13, s13, w2, s2, sh13, shs13, sh2, shs2), L)
+
+
+def _moe_fp8(x, w13, s13, w2, s2, sh13, shs13, sh2, shs2, lists_i, lists_f, top_k, block_rows):
+    L = _lists_view(lists_i, lists_f, x.shape[0], top_k, w13.shape[0], block_rows)
+    return ops.moe_fp8(x, _weights(w13, s13, w2, s2, sh13, shs13, sh2, shs2), L)
+
+
+def _dense(x, w, w_s):
+    return ops.dense_fp8(x, w, w_s)
+
+
+def _add_norm(proj, residual, w, eps):
+    return ops.add_rmsnorm(proj, residual, w, eps)
+
+
+def _merge(maxes, idxs):
+    return ops.argmax_merge(maxes, idxs)
+
+
+def _fold(checkpoint, d_ring, dlo_ring, k_ring, klo_ring, g_ring, state_idx, ring_idx, write_pos, cache_base):
+    ops.gdn_ring_fold(checkpoint, d_ring, dlo_ring, k_ring, klo_ring, g_ring, state_idx, ring_idx, write_pos, cache_base)
+
+
 _lib.impl("router", _router, "CUDA")
+_lib.impl("moe_combine_norm", _combine_norm, "CUDA")
+_lib.impl("build_lists", _build_lists, "CUDA")
+_lib.impl("moe_w8a8", _moe_w8a8, "CUDA")
+_lib.impl("moe_fp8", _moe_fp8, "CUDA")
+_lib.impl("dense_fp8", _dense, "CUDA")
+_lib.impl("add_rmsnorm", _add_norm, "CUDA")
+_lib.impl("argmax_merge", _merge, "CUDA")
+_lib.impl("gdn_ring_fold", _fold, "CUDA")
 _lib.impl("gdn_verify", _gdn, "CUDA")
 _lib.impl("gdn_verify_replay", _gdn_replay, "CUDA")
 _lib.impl("attn_front", _attn, "CUDA")

@@ -83,8 +83,26 @@ def _worker(rank, world, port, out):
             ok_step = ok_step and torch.equal(got, want) and \
                 torch.equal(part.final_hidden, single.final_hidden[rank * Tl:(rank + 1) * Tl])
         ok_step = ok_step and ops.read_status(part.status) == 0 and ops.read_status(single.status) == 0
+        # the logits node with a process group: full logits for the stock processor + the merged greedy tokens
+        import sys
+        bundle = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bundles_b200", "bundle")
+        if bundle not in sys.path:
+            sys.path.insert(0, bundle)
+        from qwen36_lmhead8 import node as qnode
+        from tests.fake_engine import FakeLogitsProcessor
+        gw = torch.Generator().manual_seed(402)
+        wfull = (torch.randn(V, 2048, generator=gw) * 0.02).to(torch.bfloat16).to(dev)
+        head = type("Head", (), {"weight": wfull})()
+        xs16 = lm["x"].to(dev)
+        sharded = qnode.forward(qnode.prepare(FakeLogitsProcessor(V), dist.group.WORLD), None, xs16, head, None)
+        whole = qnode.forward(qnode.prepare(FakeLogitsProcessor(V)), None, xs16, head, None)
+        torch.cuda.synchronize()
+        ok_node = (sharded.next_token_logits.shape == whole.next_token_logits.shape
+                   and torch.equal(sharded.next_token_logits, whole.next_token_logits)
+                   and torch.equal(sharded.next_token_ids, whole.next_token_ids))
         dist.barrier()
-        torch.save({"moe": ok_moe, "lm": torch.equal(tok, idx), "step": ok_step}, os.path.join(out, f"r{rank}.pt"))
+        torch.save({"moe": ok_moe, "lm": torch.equal(tok, idx), "step": ok_step, "node": ok_node},
+                   os.path.join(out, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -99,3 +117,4 @@ def test_expert_parallel_matches_single_gpu(tmp_path):
         assert got["moe"], f"rank {r}: expert-parallel output differs from the single-GPU block"
         assert got["lm"], f"rank {r}: sharded argmax differs"
         assert got["step"], f"rank {r}: the expert-parallel decode step differs from the one-GPU step"
+        assert got["node"], f"rank {r}: the logits node with a process group differs from the one-rank node"
