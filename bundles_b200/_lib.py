@@ -47,6 +47,8 @@ PROTOTYPES = {
     "b200_selftest_wait_expiry": (i32, [vp, vp]),
     "b200_dense_fp8_split": (i32, [vp, i32, i32, vp, vp, i32, i32, C.POINTER(i32), C.POINTER(vp), C.POINTER(i32), vp, sz,
                                    vp, vp]),
+    "b200_dense_fp8_add_rmsnorm_workspace_bytes": (sz, [i32, i32, i32]),
+    "b200_dense_fp8_add_rmsnorm": (i32, [vp, i32, i32, vp, vp, i32, vp, vp, f32, vp, vp, vp, sz, vp, vp]),
     "b200_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "b200_moe_combine_norm": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, f32, vp, vp]),
     "b200_attn_front_workspace_bytes": (sz, [i32]),

@@ -241,11 +241,12 @@ def _install_projection(layer, replica, state, owner, owner_name, projection, pr
                     or not residual.is_contiguous()):
                 hidden_states, _ = projection.forward(x)
                 return stock_prepare_mlp(communicator, hidden_states, residual, forward_batch, *args, **kwargs)
-            proj = ops.dense_fp8(x, codes, scales, status=state.status)
-            out = ops.add_rmsnorm(proj, residual, norm_w, eps)      # residual <- proj + residual, in place
+            proj = torch.empty_like(residual) if state.trace is not None else None
+            # split-K fp8 projection, then one kernel: residual <- proj + residual (in place) and the norm
+            out = ops.dense_fp8_add_rmsnorm(x, codes, scales, residual, norm_w, eps, proj_out=proj, status=state.status)
             state.residual = residual
             if state.trace is not None:
-                state.trace.update(core=x.clone(), proj=proj.clone(), h2=out.clone(), residual_mid=residual.clone())
+                state.trace.update(core=x.clone(), proj=proj, h2=out.clone(), residual_mid=residual.clone())
             return out, residual
         state.residual = None
         return stock_prepare_mlp(communicator, hidden_states, residual, forward_batch, *args, **kwargs)

@@ -496,30 +496,47 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const uint8_t* __restric
 }
 
 // Merge of the split partials and the output gate: per (request, kv head, row) the splits are added in split order
-// with weights 2^(m_s - M); out = bf16(bf16(o / l) * sigmoid(gate)).  One CTA per (group, token), 256 threads = dims.
+// with weights 2^(m_s - M); out = bf16(bf16(o / l) * sigmoid(gate)).  One CTA per (group, token, q head of the group),
+// 256 threads = dims; every load of a row's splits is issued before the first is used (one dependent round trip per
+// row instead of two per split).
+constexpr int AV_MAXS = 64;
 __global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                            const bf16* __restrict__ gate, int splits,
                                                            bf16* __restrict__ out) {
+  __shared__ float s_m[AV_MAXS], s_l[AV_MAXS];
   pdl_wait();
   pdl_launch();
-  const int grp = blockIdx.x / AV_NT, t = blockIdx.x % AV_NT, d = threadIdx.x;
+  const int g = blockIdx.x % AV_GQ, t = (blockIdx.x / AV_GQ) % AV_NT, grp = blockIdx.x / (AV_GQ * AV_NT);
+  const int d = threadIdx.x;
   const int h = grp % AV_HKV, r = grp / AV_HKV;
-  for (int g = 0; g < AV_GQ; ++g) {
-    const int row = t * AV_GQ + g;
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(static_cast<size_t>(grp) * splits + s) * 2 * AV_ROWS + row]);
-    float num = 0.f, den = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const size_t c = static_cast<size_t>(grp) * splits + s;
-      const float m = part_ml[c * 2 * AV_ROWS + row];
-      const float w = m == -INFINITY ? 0.f : exp2f(m - M);
-      num = fmaf(part_o[(c * AV_ROWS + row) * AV_D + d], w, num);
-      den = fmaf(part_ml[c * 2 * AV_ROWS + AV_ROWS + row], w, den);
-    }
-    const size_t o = (static_cast<size_t>(r) * AV_NT + t) * (AV_HQ * AV_D) + static_cast<size_t>(h * AV_GQ + g) * AV_D + d;
-    const float gv = bf2f(gate[o]);
-    out[o] = f2bf(rbf(num / den) * (1.f / (1.f + __expf(-gv))));
+  const int row = t * AV_GQ + g;
+  const size_t c0 = static_cast<size_t>(grp) * splits;
+  if (d < splits) {
+    s_m[d] = part_ml[(c0 + d) * 2 * AV_ROWS + row];
+    s_l[d] = part_ml[(c0 + d) * 2 * AV_ROWS + AV_ROWS + row];
   }
+  const size_t o = (static_cast<size_t>(r) * AV_NT + t) * (AV_HQ * AV_D) + static_cast<size_t>(h * AV_GQ + g) * AV_D + d;
+  const float gv = bf2f(gate[o]);
+  float num = 0.f, den = 0.f, M = -INFINITY;
+  // the partial rows of up to 8 splits at a time are in flight together
+  for (int s0 = 0; s0 < splits; s0 += 8) {
+    float po[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) po[u] = s0 + u < splits ? part_o[((c0 + s0 + u) * AV_ROWS + row) * AV_D + d] : 0.f;
+    if (s0 == 0) {
+      __syncthreads();
+      for (int s = 0; s < splits; ++s) M = fmaxf(M, s_m[s]);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (s0 + u < splits) {
+        const float m = s_m[s0 + u];
+        const float w = m == -INFINITY ? 0.f : exp2f(m - M);
+        num = fmaf(po[u], w, num);
+        den = fmaf(s_l[s0 + u], w, den);
+      }
+  }
+  out[o] = f2bf(rbf(num / den) * (1.f / (1.f + __expf(-gv))));
 }
 
 }  // namespace b200
@@ -583,7 +600,7 @@ extern "C" int b200_attn_verify(const void* q, const void* gate, const void* k_n
   a.part_ml = a.part_o + static_cast<size_t>(B) * AV_HKV * splits * AV_ROWS * AV_D;
   a.status = status;
   launch_k(attn_verify_kernel, dim3(B * AV_HKV * splits), dim3(AV_THREADS), AV_SMEM, st, tmK, tmV, tmQ, a);
-  launch_k(attn_combine_kernel, dim3(B * AV_HKV * AV_NT), dim3(256), 0, st, static_cast<const float*>(a.part_o),
+  launch_k(attn_combine_kernel, dim3(B * AV_HKV * AV_NT * AV_GQ), dim3(256), 0, st, static_cast<const float*>(a.part_o),
            static_cast<const float*>(a.part_ml), static_cast<const bf16*>(gate), splits, static_cast<bf16*>(out));
   return launch_status("b200_attn_verify");
 }

@@ -113,6 +113,12 @@ struct F8Args {
   bf16* ep_cache[8];
   int test_starve;  // self-test: the producer leaves out the token rows, so no stage ever completes and every wait runs out
   int cost_base;    // cost of a tile in 16-row units of tokens, before its token rows are counted (tile partition)
+  // dense mode with partial sums: the K range is cut into `kparts` equal parts whose fp32 sums (each a promotion
+  // chain from zero) go to partials[part][row][feature]; the consumer adds the parts in part order, so the
+  // arithmetic is fixed by `kparts` alone.  A tile covers kparts / ksplit consecutive parts: `ksplit` only says over
+  // how many CTAs the K range of one (weight tile, row chunk) is spread (1: bf16 outputs when partials is null).
+  int ksplit, kparts;
+  float* partials;
 };
 
 constexpr int MODE_DOWN = 0, MODE_UP = 1, MODE_LM = 2, MODE_DENSE = 3;
@@ -195,10 +201,13 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   // (weight tile, chunk) with the chunk fastest, so the chunks of one weight tile run back to back on one CTA
   // and all but the first find the weight tile in L2.)
   const int nblocks = LM ? (p.total_rows + 63) / 64 : p.L.nblocks[0];
-  const int ntiles = nblocks * p.mtiles;
+  const int ntiles = nblocks * p.mtiles * (DENSE ? p.ksplit : 1);
   int t_lo = static_cast<int>(static_cast<long long>(blockIdx.x) * ntiles / gridDim.x);
   int t_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * ntiles / gridDim.x);
   auto blk_of = [&](int tile) { return LM ? tile % nblocks : tile / p.mtiles; };
+  // k blocks of one tile and the first of them (split-K in the dense mode; the whole K otherwise)
+  const int kn = DENSE ? p.ksteps / p.ksplit : p.ksteps;
+  auto k0_of = [&](int tile) { return DENSE ? ((tile / nblocks) % p.ksplit) * kn : 0; };
   if (C::LISTS) {
     const int ncached = nblocks < F8_CACHED ? nblocks : F8_CACHED;
     for (int blk = threadIdx.x; blk < ncached; blk += F8_THREADS) {
@@ -247,10 +256,11 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
 
   auto decode = [&](int tile, int& e, int& row0, int& n, int& mt) -> bool {
-    if (LM) {  // dense: 128 weight rows against one 64-row chunk of the tokens
+    if (LM) {  // dense: 128 weight rows against one 64-row chunk of the tokens (and one part of K when split)
       e = 0;
-      mt = tile / nblocks;
-      row0 = (tile - mt * nblocks) * 64;
+      const int mx = tile / nblocks;
+      mt = DENSE ? mx / p.ksplit : mx;
+      row0 = (tile - mx * nblocks) * 64;
       n = p.total_rows - row0 < 64 ? p.total_rows - row0 : 64;
       return n >= 1;
     }
@@ -345,7 +355,8 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const int nb16 = (n + 15) >> 4;
         const CUtensorMap* mapW = (e == p.E_local) ? &tmWsh : &tmW;
         const int wrow = (e == p.E_local ? 0 : e * p.w_rows) + mt * MROWS;
-        for (int ks = 0; ks < p.ksteps; ++ks) {
+        const int kfirst = k0_of(tile);
+        for (int ks = kfirst; ks < kfirst + kn; ++ks) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) {
             ok = false;
             break;
@@ -397,7 +408,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (!decode(tile, e, row0, n, mt)) continue;
         const uint32_t N = static_cast<uint32_t>((n + 15) & ~15);
         const uint32_t idesc = umma_idesc(UMMA_C_F32, UMMA_AB_E4M3, N);
-        for (int ks = 0; ks < p.ksteps && ok; ++ks, ++g) {
+        for (int ks = 0; ks < kn && ok; ++ks, ++g) {
           const uint32_t pb = g % C::NPB, pphase = (g / C::NPB) & 1u;
           if (!mbar_wait(&pempty[pb], pphase ^ 1u, abort_flag, p.status, ST_WAIT_TMEM_EMPTY) ||
               !mbar_wait(&full[stage], phase, abort_flag, p.status, ST_WAIT_FULL)) {
@@ -532,7 +543,8 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (DUAL)
 #pragma unroll
         for (int c = 0; c < 32; ++c) acc_b[c] = 0.f;
-      for (int ks = 0; ks < p.ksteps; ++ks, ++g) {
+      const int kfirst = k0_of(tile);
+      for (int ks = kfirst; ks < kfirst + kn; ++ks, ++g) {
         const uint32_t pb = g % C::NPB, pphase = (g / C::NPB) & 1u;
         const float wsa = wsc_a[ks], wsb = DUAL ? wsc_b[ks] : 0.f;
         if (!mbar_wait(&pfull[pb], pphase, abort_flag, p.status, ST_WAIT_TMEM_FULL)) {
@@ -560,6 +572,19 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&pempty[pb]);
+        if (DENSE && p.partials != nullptr) {
+          const int plen = p.ksteps / p.kparts;
+          if ((ks + 1) % plen == 0) {   // this part is complete: its sums leave, the accumulators start again from zero
+            const int rr = mt * MROWS + q * 32 + lane;
+            float* __restrict__ o = p.partials + (static_cast<size_t>(ks / plen) * p.total_rows + row0) * p.w_rows + rr;
+#pragma unroll
+            for (int l = 0; l < 32; ++l) {
+              const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+              if (c < n && rr < p.w_rows) st_global_na(o + static_cast<size_t>(c) * p.w_rows, acc_a[l]);
+              acc_a[l] = 0.f;
+            }
+          }
+        }
       }
       if (!ok) break;
       if (warp == 2 && lane == 0) TRACE(3, 3 + 2 * ((tile - t_lo)));
@@ -569,7 +594,9 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int r = mt * MROWS + q * 32 + lane;  // down: this lane also holds output feature r + 128
       if (DENSE) {
         // plain projection: out[token][feature] = bf16(acc)
-        if (r < p.w_rows) {
+        if (p.partials != nullptr) {
+          // the parts' sums were stored as each part completed
+        } else if (r < p.w_rows) {
           int sg = 0;
           while (sg + 1 < p.nseg && r >= p.seg_lo[sg + 1]) ++sg;
           bf16* __restrict__ o = p.seg_out[sg] + (r - p.seg_lo[sg]);
@@ -1055,6 +1082,8 @@ extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, 
   a.s_w_sh = w_s;
   a.a_scale = xs;
   a.status = status;
+  a.ksplit = 1;
+  a.kparts = 1;
   a.nseg = nseg;
   int c0 = 0;
   for (int i = 0; i < nseg; ++i) {
@@ -1075,6 +1104,139 @@ extern "C" int b200_dense_fp8(const void* x, int T, int H, const void* w, const 
   if (!out) return fail(B200_E_ARG, "b200_dense_fp8: null pointer");
   void* outs[1] = {out};
   return b200_dense_fp8_split(x, T, H, w, w_s, N, 1, &N, outs, &N, ws, ws_bytes, status, stream);
+}
+
+namespace b200 {
+// The add + norm behind a split-K projection: proj = bf16(sum of the S partial rows, in split order), then as
+// add_rmsnorm_kernel.  One CTA per row.
+__global__ void __launch_bounds__(256) add_rmsnorm_partials_kernel(const float* __restrict__ partials, int S, int T,
+                                                                   bf16* __restrict__ residual, const bf16* __restrict__ w,
+                                                                   float eps, int H, bf16* __restrict__ out,
+                                                                   bf16* __restrict__ proj_out) {
+  __shared__ float red[8];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  float ss = 0.f;
+  for (int c = tid * 8; c < H; c += 2048) {
+    float p[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < S; ++s) {
+      const float4* src = reinterpret_cast<const float4*>(partials + (static_cast<size_t>(s) * T + t) * H + c);
+      const float4 a = src[0], b = src[1];
+      p[0] += a.x; p[1] += a.y; p[2] += a.z; p[3] += a.w;
+      p[4] += b.x; p[5] += b.y; p[6] += b.z; p[7] += b.w;
+    }
+    const uint4 rb = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * H + c);
+    const float rv[8] = {bf_lo(rb.x), bf_hi(rb.x), bf_lo(rb.y), bf_hi(rb.y), bf_lo(rb.z), bf_hi(rb.z), bf_lo(rb.w), bf_hi(rb.w)};
+    float r[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      p[i] = rbf(p[i]);                 // the projection is rounded to bf16 before the fp32 residual add (proj.py:75-77)
+      r[i] = rbf(p[i] + rv[i]);
+      ss = fmaf(r[i], r[i], ss);
+    }
+    if (proj_out)
+      *reinterpret_cast<uint4*>(proj_out + static_cast<size_t>(t) * H + c) =
+          make_uint4(pack_bf2(p[0], p[1]), pack_bf2(p[2], p[3]), pack_bf2(p[4], p[5]), pack_bf2(p[6], p[7]));
+    *reinterpret_cast<uint4*>(residual + static_cast<size_t>(t) * H + c) =
+        make_uint4(pack_bf2(r[0], r[1]), pack_bf2(r[2], r[3]), pack_bf2(r[4], r[5]), pack_bf2(r[6], r[7]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(FULL_MASK, ss, o);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rstd = rsqrtf(tot / H + eps);
+  for (int c = tid * 8; c < H; c += 2048) {  // each thread re-reads the rows it wrote itself
+    const uint4 b = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * H + c);
+    const uint4 g = *reinterpret_cast<const uint4*>(w + c);
+    const float r[8] = {bf_lo(b.x), bf_hi(b.x), bf_lo(b.y), bf_hi(b.y), bf_lo(b.z), bf_hi(b.z), bf_lo(b.w), bf_hi(b.w)};
+    const float gw[8] = {bf_lo(g.x), bf_hi(g.x), bf_lo(g.y), bf_hi(g.y), bf_lo(g.z), bf_hi(g.z), bf_lo(g.w), bf_hi(g.w)};
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = r[i] * rstd * (1.f + gw[i]);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + c) =
+        make_uint4(pack_bf2(y[0], y[1]), pack_bf2(y[2], y[3]), pack_bf2(y[4], y[5]), pack_bf2(y[6], y[7]));
+  }
+}
+
+// K parts of the projection in front of an add + norm: as many as would let weight tiles x parts fill the GPU at the
+// smallest batch.  The part count fixes the arithmetic (a row's sum does not depend on the batch it is in); over how
+// many CTAs the parts of one (weight tile, row chunk) are spread is a scheduling choice that shrinks as the rows grow.
+static int proj_kparts(int N, int K) {
+  const int mtiles = (N + 127) / 128, ksteps = K / 128;
+  int s = 1;
+  while (s * 2 <= ksteps && ksteps % (s * 2) == 0 && mtiles * s * 2 <= 148) s *= 2;
+  return s;
+}
+static int proj_ksplit(int N, int K, int T) {
+  const int units = ((N + 127) / 128) * ((T + 63) / 64);
+  int s = proj_kparts(N, K);
+  while (s > 1 && units * s > sm_count()) s >>= 1;
+  return s;
+}
+}  // namespace b200
+
+extern "C" size_t b200_dense_fp8_add_rmsnorm_workspace_bytes(int T, int K, int N) {
+  if (T <= 0 || K <= 0 || N <= 0 || K % 128) return 0;
+  auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+  return b200_dense_fp8_workspace_bytes(T, K) + up(static_cast<size_t>(proj_kparts(N, K)) * T * N * 4);
+}
+
+extern "C" int b200_dense_fp8_add_rmsnorm(const void* x, int T, int K, const void* w, const float* w_s, int N, void* residual,
+                                          const void* norm_w, float eps, void* out, void* proj_out, void* ws,
+                                          size_t ws_bytes, int32_t* status, void* stream) {
+  if (!x || !w || !w_s || !residual || !norm_w || !out || !ws) return fail(B200_E_ARG, "b200_dense_fp8_add_rmsnorm: null pointer");
+  if (T <= 0 || K <= 0 || K % 128 || K / 128 > F8_MAXKG || N <= 0 || N % 8)
+    return fail(B200_E_ARG, "b200_dense_fp8_add_rmsnorm: need T >= 1, K %% 128 == 0, K <= 4096, N %% 8 == 0 (T=%d K=%d N=%d)",
+                T, K, N);
+  if (ws_bytes < b200_dense_fp8_add_rmsnorm_workspace_bytes(T, K, N))
+    return fail(B200_E_WS, "b200_dense_fp8_add_rmsnorm: workspace %zu < %zu bytes", ws_bytes,
+                b200_dense_fp8_add_rmsnorm_workspace_bytes(T, K, N));
+  if (reinterpret_cast<uintptr_t>(ws) & 1023)
+    return fail(B200_E_ALIGN, "b200_dense_fp8_add_rmsnorm: workspace must be 1024-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+  uint8_t* xq = static_cast<uint8_t*>(ws);
+  float* xs = reinterpret_cast<float*>(xq + up(static_cast<size_t>(T < 64 ? 64 : T) * K));
+  float* partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + b200_dense_fp8_workspace_bytes(T, K));
+  CUtensorMap tmW, tmX, tmX64;
+  int rc;
+  if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(N), K, 128, "projection weight"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX, xq, T, K, 16, "projection activations"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, K, 64, "projection activations"))) return rc;
+  static DeviceOnce once;
+  once.run([] {
+    cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         F8Cfg<MODE_DENSE>::SMEM);
+  });
+  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, K, 0, nullptr, 0, T, xq, xs);
+  F8Args a{};
+  a.E_local = 1;
+  a.mtiles = (N + 127) / 128;
+  a.ksteps = K / 128;
+  a.w_rows = N;
+  a.H = K;
+  a.total_rows = T;
+  a.s_w = w_s;
+  a.s_w_sh = w_s;
+  a.a_scale = xs;
+  a.status = status;
+  a.kparts = proj_kparts(N, K);
+  a.ksplit = proj_ksplit(N, K, T);
+  a.partials = partials;
+  a.nseg = 1;
+  a.seg_lo[0] = 0;
+  a.seg_lo[1] = N;
+  a.seg_ld[0] = N;
+  a.seg_out[0] = nullptr;   // not used: the sums go through `partials` (also when there is a single K part)
+  const int S = a.kparts;
+  const int ntiles = a.mtiles * ((T + 63) / 64) * a.ksplit;
+  const int grid = ntiles < sm_count() ? ntiles : sm_count();
+  moe_gemm_f8_kernel<MODE_DENSE><<<grid, F8_THREADS, F8Cfg<MODE_DENSE>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
+  add_rmsnorm_partials_kernel<<<T, 256, 0, st>>>(partials, S, T, static_cast<bf16*>(residual),
+                                                 static_cast<const bf16*>(norm_w), eps, N, static_cast<bf16*>(out),
+                                                 static_cast<bf16*>(proj_out));
+  return launch_status("b200_dense_fp8_add_rmsnorm");
 }
 
 extern "C" int b200_add_rmsnorm(const void* proj, void* residual, const void* w, float eps, int T, int H, void* out,

@@ -8,11 +8,11 @@ random-initialised on the device from a seed (there are no checkpoints here); ev
 state and KV pages, so a step streams what a real model would stream.
 
 Per layer, for this rank's rows (4 drafts x its sequences):
-    GDN layer:        in_proj (dense fp8, outputs split into q k v | z | b | a) -> gdn_verify -> out_proj (dense fp8);
+    GDN layer:        in_proj (dense fp8, outputs split into q k v | z | b | a) -> gdn_verify;
                       with `gdn_layout="ring"` the state is the engine's read-only checkpoint + 16-entry (d, k, g)
                       ring and the step appends to the ring
-    attention layer:  attn_front (projection + q/k norm + RoPE, e4m3 q/k/v) -> attn_verify -> o_proj (dense fp8)
-    then              residual add + RMSNorm -> router -> lists -> fp8 experts -> combine fused with the next
+    attention layer:  attn_front (projection + q/k norm + RoPE, e4m3 q/k/v) -> attn_verify
+    then              out_proj / o_proj (split-K fp8) fused with the residual add + RMSNorm -> router -> lists -> fp8 experts -> combine fused with the next
                       layer's residual add + input RMSNorm
 and after the last layer the vocabulary argmax.
 
@@ -156,6 +156,7 @@ class DecodeStep:
         self.wts = torch.empty(T, K, dtype=torch.float32, device=dev)
         self.gdn_ws = ops.gdn_workspace(Bl, dev)
         self.dense_ws = ops.dense_fp8_workspace(T, 4096, dev)
+        self.proj_ws = ops.dense_fp8_add_rmsnorm_workspace(T, 4096, H, dev)
         self.gdn_in = [torch.empty(T, wd, dtype=bf, device=dev) for wd in GDN_SPLIT]
         self.lm_ws = ops.lmhead_workspace(Ta if ep is not None else T, H, self.shard_hi - self.shard_lo, dev)
         if ep is None:
@@ -229,8 +230,7 @@ class DecodeStep:
                                            self.cos_sin, 1e-6, True, status=st)
             core = ops.attn_verify(q, gate, k, v, L["kcache"], L["vcache"], L["page_table"], self.seqlens,
                                    splits=self.attn_splits, status=st)
-            proj = ops.dense_fp8(core, L["o_w"], L["o_s"], ws=self.dense_ws, status=st)
-            return proj, 2 + 3 + 2 * self._chunks
+            return core, L["o_w"], L["o_s"], 2 + 3
         mixed, z, b, a = ops.dense_fp8_split(h, L["in_w"], L["in_s"], GDN_SPLIT, outs=self.gdn_in, ws=self.dense_ws, status=st)
         if self.gdn_layout == "ring":
             core = ops.gdn_verify_replay(mixed, z, a, b, L["conv_state"], L["conv_w"], L["window"], L["a_log"],
@@ -241,8 +241,7 @@ class DecodeStep:
         else:
             core = ops.gdn_verify(mixed, z, a, b, L["conv_state"], L["conv_w"], L["a_log"], L["dt_bias"], L["state"],
                                   self.accepted, L["gdn_norm"], 1e-6, status=st, ws=self.gdn_ws)
-        proj = ops.dense_fp8(core, L["out_w"], L["out_s"], ws=self.dense_ws, status=st)
-        return proj, 2 * self._chunks + 2 + 2 * self._chunks
+        return core, L["out_w"], L["out_s"], 2 + 2
 
     def run(self, x: torch.Tensor):
         """Generator form of `step`: yields the barrier channel at every point where the ranks of an expert-parallel
@@ -255,10 +254,12 @@ class DecodeStep:
         n = 1
         for li, L in enumerate(self.layers):
             rec = None if self.trace is None else dict(h_in=h.clone(), residual_in=residual.clone())
-            proj, nl = self._mixer(L, h)
-            h2 = ops.add_rmsnorm(proj, residual, L["post_norm"])
+            core, ow, osc, nl = self._mixer(L, h)
+            # output projection (split-K) + residual add + post-attention norm
+            proj = torch.empty_like(residual) if rec is not None else None
+            h2 = ops.dense_fp8_add_rmsnorm(core, ow, osc, residual, L["post_norm"], 1e-6, proj_out=proj, ws=self.proj_ws, status=st)
             ops.router(h2, L["wr"], K, None, scratch=self.scratch, want_logits=False, ids=self.ids, wts=self.wts)
-            n += nl + 1 + 2
+            n += nl + 3 + 2
             if ep is None:
                 ops.build_lists(self.ids, self.wts, self.lists)
                 ops.moe_fp8(h2, L["w"], self.lists, cache=self.cache, ws=self.moe_ws, status=st)
@@ -271,7 +272,7 @@ class DecodeStep:
                 yield 1                                            # every rank's rows for my tokens have landed
                 n += 1 + 1 + 1 + 4 + 1
             if rec is not None:
-                rec.update(proj=proj.clone(), h2=h2.clone(), ids=self.ids.clone(), wts=self.wts.clone(),
+                rec.update(core=core.clone(), proj=proj, h2=h2.clone(), ids=self.ids.clone(), wts=self.wts.clone(),
                            cache=self.cache.clone(), residual_mid=residual.clone())
             out, h = ops.moe_combine_norm(self.cache, h2, L["gate_w"], K, residual, L["next_norm"])
             n += 1

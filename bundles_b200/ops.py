@@ -17,7 +17,7 @@ from ._lib import B200Error, MoeLists, MoeWeights, check
 
 __all__ = ["router", "RoutingLists", "build_lists", "MoeW8A8Weights", "moe_w8a8", "moe_w8a8_ep", "ep_push", "ep_put",
            "ep_barrier", "moe_fp8", "moe_fp8_ep", "moe_combine", "moe_combine_norm", "attn_front", "attn_verify",
-           "dense_fp8", "dense_fp8_split", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
+           "dense_fp8", "dense_fp8_split", "dense_fp8_add_rmsnorm", "add_rmsnorm", "lmhead_argmax", "argmax_merge", "gdn_verify",
            "gdn_verify_replay", "gdn_ring_fold", "set_wait_budget_ns", "selftest_wait_expiry", "new_status",
            "read_status", "B200Error"]
 
@@ -424,6 +424,36 @@ def dense_fp8_split(x, w, w_s, widths, outs=None, ws=None, status=None):
     check(_lib.lib().b200_dense_fp8_split(_p(x), T, H, _p(w), _p(w_s), N, n, cols, _ptr_array([o.data_ptr() for o in outs]),
                                           lds, _p(ws), ws.numel(), _p(status), _stream()), "b200_dense_fp8_split")
     return outs
+
+
+def dense_fp8_add_rmsnorm_workspace(T, K, N, device):
+    n = _lib.lib().b200_dense_fp8_add_rmsnorm_workspace_bytes(T, K, N)
+    buf = torch.empty(n + 1024, dtype=torch.uint8, device=device)
+    off = (-buf.data_ptr()) % 1024
+    return buf[off:off + n]
+
+
+def dense_fp8_add_rmsnorm(x, w, w_s, residual, norm_w, eps=1e-6, out=None, proj_out=None, ws=None, status=None):
+    """A mixer's output projection fused with the residual add and the norm behind it (reference:
+    proj.project_add_norm): split-K fp8 GEMM into fp32 partials, then one kernel that sums them, rounds the projection
+    to bf16, adds it to `residual` in place and norms.  Returns the normed rows bf16 [T, N]."""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(w, torch.uint8, "w", 2)
+    _need(w_s, torch.float32, "w_s", 2)
+    _need(residual, torch.bfloat16, "residual", 2)
+    _need(norm_w, torch.bfloat16, "norm_w", 1)
+    T, K = x.shape
+    N = w.shape[0]
+    if tuple(residual.shape) != (T, N):
+        raise B200Error("dense_fp8_add_rmsnorm: residual must be [T, N]")
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    if ws is None:
+        ws = dense_fp8_add_rmsnorm_workspace(T, K, N, x.device)
+    check(_lib.lib().b200_dense_fp8_add_rmsnorm(_p(x), T, K, _p(w), _p(w_s), N, _p(residual), _p(norm_w), float(eps), _p(out),
+                                                _p(proj_out), _p(ws), ws.numel(), _p(status), _stream()),
+          "b200_dense_fp8_add_rmsnorm")
+    return out
 
 
 def add_rmsnorm(proj, residual, w, eps=1e-6, out=None):

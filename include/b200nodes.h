@@ -383,6 +383,19 @@ int b200_dense_fp8(const void* x, int T, int H, const void* w, const float* w_s,
 int b200_dense_fp8_split(const void* x, int T, int H, const void* w, const float* w_s, int N, int nseg,
                          const int* seg_cols_host, void* const* seg_out_host, const int* seg_ld_host, void* ws,
                          size_t ws_bytes, int32_t* status, void* stream);
+/* The output projection of a mixer fused with what follows it, as proj.project_add_norm does (proj.py:84-112: split-K
+ * partials in fp32, then one kernel that sums them, adds the residual and norms):
+ *   proj = bf16(x[T,K] . W[N,K]^T) with the K range cut into parts so that weight tiles x parts fill the GPU (a
+ *   [2048, 4096] weight has only 16 weight tiles), the parts' fp32 sums added in part order;
+ *   residual <- bf16(proj + residual); out = bf16(residual * rsqrt(mean residual^2 + eps) * (1 + norm_w)).
+ * The number of parts depends on the weight's shape only, so a row's result does not depend on the batch it is in.
+ *   x bf16 [T,K]; w e4m3 [N,K], w_s fp32 [ceil(N/128), K/128]; residual bf16 [T,N] (in/out); norm_w bf16 [N];
+ *   out bf16 [T,N]; proj_out bf16 [T,N] or NULL (the rounded projection, for checks);
+ *   ws: b200_dense_fp8_add_rmsnorm_workspace_bytes(T,K,N) bytes, 1024-byte aligned.  K % 128 == 0, K <= 4096, N % 8 == 0. */
+size_t b200_dense_fp8_add_rmsnorm_workspace_bytes(int T, int K, int N);
+int b200_dense_fp8_add_rmsnorm(const void* x, int T, int K, const void* w, const float* w_s, int N, void* residual,
+                               const void* norm_w, float eps, void* out, void* proj_out, void* ws, size_t ws_bytes,
+                               int32_t* status, void* stream);
 int b200_add_rmsnorm(const void* proj, void* residual, const void* w, float eps, int T, int H, void* out,
                      void* stream);
 

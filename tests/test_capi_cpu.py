@@ -89,6 +89,9 @@ def test_argument_checks_return_codes(lib):
     assert lib.b200_selftest_wait_expiry(None, None) == -1
     cols, lds = (C.c_int * 2)(100, 28), (C.c_int * 2)(100, 28)
     assert lib.b200_dense_fp8_split(one, 4, 2048, one, one, 128, 2, cols, ptrs, lds, one, 1 << 30, None, None) == -1
+    assert lib.b200_dense_fp8_add_rmsnorm(one, 4, 4000, one, one, 2048, one, one, 1e-6, one, None, one, 1 << 30, None, None) == -1
+    assert lib.b200_dense_fp8_add_rmsnorm(one, 4, 4096, one, one, 2048, one, one, 1e-6, one, None, one, 64, None, None) == -3
+    assert lib.b200_dense_fp8_add_rmsnorm_workspace_bytes(4, 4096, 2048) > 4 * 2048 * 4
     mis = [one] * 9 + [C.c_void_p(4100)]
     assert lib.b200_gdn_verify_replay(*mis, 4, *([one] * 11), 1e-6, 1, one, one, 1 << 30, None, None) == -2
 

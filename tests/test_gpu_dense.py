@@ -54,6 +54,38 @@ def test_split_outputs_equal_the_plain_projection():
         ops.dense_fp8_split(x, codes, scales, (8192, 4100, 28, 32))     # inner boundary not a multiple of 32
 
 
+@pytest.mark.parametrize("T", [5, 32, 150])
+def test_projection_fused_with_add_and_norm(T):
+    """The split-K output projection + residual add + norm against the oracle's projection followed by its add + norm
+    (the rounded projection within the bf16 tolerance, the add and the norm exact on that projection), and a row's
+    result independent of the batch it is in."""
+    g = torch.Generator().manual_seed(40 + T)
+    K, N = 4096, 2048
+    w = torch.randn(N, K, generator=g) * 0.02
+    codes, scales = synth.quant_fp8_blocks(w)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    res = torch.randn(T, N, generator=g).to(torch.bfloat16)
+    nw = (torch.randn(N, generator=g) * 0.1).to(torch.bfloat16)
+    st = ops.new_status(dev())
+    r_dev = res.to(dev()).clone()
+    proj = torch.empty(T, N, dtype=torch.bfloat16, device=dev())
+    cd, sd, xd, nd = codes.to(dev()), scales.to(dev()), x.to(dev()), nw.to(dev())
+    y = ops.dense_fp8_add_rmsnorm(xd, cd, sd, r_dev, nd, 1e-6, proj_out=proj, status=st)
+    torch.cuda.synchronize()
+    assert ops.read_status(st) == 0
+    ok, err, nbad = close_bf16(bf16_to_np(proj), oat.dense_fp8(bf16_to_np(x), codes.numpy(), scales.numpy()))
+    assert ok, (err, nbad)
+    ry, rr = oat.add_rmsnorm(bf16_to_np(proj), bf16_to_np(res), bf16_to_np(nw), 1e-6)
+    assert np.array_equal(bf16_to_np(r_dev), rr)
+    ok, err, nbad = close_bf16(bf16_to_np(y), ry)
+    assert ok, (err, nbad)
+    if T > 8:   # the first 8 rows alone give the same bits
+        r8 = res[:8].to(dev()).clone()
+        y8 = ops.dense_fp8_add_rmsnorm(xd[:8].contiguous(), cd, sd, r8, nd, 1e-6, status=st)
+        torch.cuda.synchronize()
+        assert torch.equal(y8, y[:8]) and torch.equal(r8, r_dev[:8])
+
+
 def test_add_rmsnorm():
     g = torch.Generator().manual_seed(5)
     T, H = 37, 2048
