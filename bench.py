@@ -42,6 +42,25 @@ WORKLOAD = "int8 W8A8 routed MoE block at decode: T=256 H=2048 E=512 top-10 I=51
 METRIC = "decode tokens/s through one MoE layer (us/layer = ms_per_step*1000)"
 
 
+_OUT = None
+
+
+def quiet_stdout():
+    """From here on file descriptor 1 is stderr, so that whatever a library writes to stdout (NCCL's version line at
+    communicator set-up) cannot land beside the result; `emit` writes the JSON line to the real stdout."""
+    global _OUT
+    if _OUT is None:
+        sys.stdout.flush()
+        _OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line):
+    out = _OUT if _OUT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -131,7 +150,7 @@ def run_reference(args, rank, world):
                              "sample": "whole workload (256 tokens), every step"},
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def other_kernels(dev, steps, warmup, only=None):
@@ -598,7 +617,7 @@ def run_step_reference(args, rank, world):
                              "seconds_per_layer": per_layer},
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def _ep_check(dev, ep, world, rank):
@@ -682,10 +701,9 @@ def run_step_virtual(args, dev):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
-    print(json.dumps({"diagnostic": "virtual ranks on one GPU", "virtual_ranks": n, "layers": args.layers,
-                      "ms_all_ranks": ms, "ms_per_rank_step": ms / n, "us_per_rank_layer": ms / n * 1000.0 / args.layers,
-                      "launches_per_rank_step": steps[0].launches,
-                      "status": max(ops.read_status(s.status) for s in steps)}), flush=True)
+    emit({"diagnostic": "virtual ranks on one GPU", "virtual_ranks": n, "layers": args.layers,
+          "ms_all_ranks": ms, "ms_per_rank_step": ms / n, "us_per_rank_layer": ms / n * 1000.0 / args.layers,
+          "launches_per_rank_step": steps[0].launches, "status": max(ops.read_status(s.status) for s in steps)})
 
 
 def run_step(args, rank, world, local, dev):
@@ -802,8 +820,9 @@ def run_step(args, rank, world, local, dev):
         "roofline": {"kernel": "moe_gemm_f8_kernel<UP> (fp8 gate/up expert GEMM + SwiGLU)", "bound": "hbm", "achieved": achieved,
                      "peak": peak, "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": F8_UP_TRAFFIC_RATIO * up_bytes if F8_UP_TRAFFIC_RATIO else None,
-                     "traffic_source": "DRAM read + write of one launch of this kernel under ncu on a smaller case "
-                                       "(profiles/), scaled by this launch's algorithmic bytes",
+                     "traffic_source": "DRAM read + write of one launch of this kernel under ncu on the same case (one layer, 256 "
+                                       "rows x 512 experts; profiles/moe_fp8_up_down_t256.md), scaled by this launch's "
+                                       "algorithmic bytes",
                      "algorithmic_bytes": up_bytes, "ms": ms_up, "active_experts": active, "rows": rows},
         "clocks": clocks, "device_status": int(status.item()), "ep_check": check,
         "launches_per_step": launches, "device_memory_gb": mem_gb, "build_seconds": round(t_build, 1),
@@ -817,14 +836,14 @@ def run_step(args, rank, world, local, dev):
             line["kernels"] = {"error": repr(exc)[:300]}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_step_baseline()
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
 # DRAM bytes (read + write) of one launch of moe_gemm_f8_kernel<UP> divided by its algorithmic bytes, from the ncu
-# capture summarised under profiles/ (None until a capture exists)
-F8_UP_TRAFFIC_RATIO = None
+# capture summarised in profiles/moe_fp8_up_down_t256.md (1.1077 GB read + 12.5 MB written for 1.0786 GB)
+F8_UP_TRAFFIC_RATIO = 1.0385
 
 
 
@@ -901,7 +920,7 @@ def run_expert_parallel(args, rank, world, dev, cfg):
                         "d2h_bytes_per_step": T * H * 2, "ms_per_step": ms_e2e},
                 "gpu_launches": getattr(ep, "launches_per_call", backend.launches_per_call) * args.steps, "clocks": clocks,
                 "device_status": int(status.item())}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if hasattr(ep, "close"):
         ep.close()      # the captured graph holds NCCL kernels: release it before the communicator
     dist.destroy_process_group()
@@ -928,11 +947,11 @@ def main():
                              "moe_w8a8_prefill", "moe_w8a8_t256", "moe_fp8_t256"],
                     help="run one entry of `kernels` alone with plain launches (a small target for an ncu capture) and exit")
     args = ap.parse_args()
+    quiet_stdout()
     if args.only_kernel:
         import torch
         torch.cuda.set_device(0)
-        print(json.dumps({"kernels": other_kernels(torch.device("cuda", 0), min(args.steps, 3), 1, only=args.only_kernel)}),
-              flush=True)
+        emit({"kernels": other_kernels(torch.device("cuda", 0), min(args.steps, 3), 1, only=args.only_kernel)})
         return
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -1067,7 +1086,7 @@ def main():
         dt, cores = cpu_baseline(cfg_host)
         line["cpu_baseline"] = {"value": T / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
                                 "sample": "whole workload (256 tokens, 2816 expert rows), best of 2", "seconds": dt}
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 

@@ -43,6 +43,7 @@ import torch
 
 from bundles_b200 import moe_block, ops
 from bundles_b200 import prepare as prepare_q
+from bundles_b200.evidence import note
 
 EXPERT_FORMAT = "w8a8"      # "w8a8": int8 per-output-channel; "fp8": e4m3 with 128 x 128 block scales
 HIDDEN, PROJ_IN = 2048, 4096
@@ -164,12 +165,14 @@ class _MoeOverride(torch.nn.Module):
             # the combine also writes the next layer's residual and normed rows (qk_route.cu:779-819); that layer's
             # prepare_attn picks them up instead of running its input norm (layer.py:555-566)
             residual, norm_w, eps, key = nxt
+            note("moe_combine_norm_handoff", x.shape[0])
             out, normed = self.block.forward_combine_norm(x, pos, residual, norm_w, eps)
             _handoff[key] = dict(out=out, residual=residual, normed=normed)
             if self.owner.trace is not None:
                 self.owner.trace.update(normed=normed.clone())
             return out.reshape(shape)
         # rows whose position is 0 are graph padding and come back as zeros (layer.py:476-477)
+        note("moe_block", x.shape[0])
         return self.block(x, pos).reshape(shape).clone()
 
 
@@ -241,6 +244,7 @@ def _install_projection(layer, replica, state, owner, owner_name, projection, pr
                     or not residual.is_contiguous()):
                 hidden_states, _ = projection.forward(x)
                 return stock_prepare_mlp(communicator, hidden_states, residual, forward_batch, *args, **kwargs)
+            note("proj_add_norm", x.shape[0])
             proj = torch.empty_like(residual) if state.trace is not None else None
             # split-K fp8 projection, then one kernel: residual <- proj + residual (in place) and the norm
             out = ops.dense_fp8_add_rmsnorm(x, codes, scales, residual, norm_w, eps, proj_out=proj, status=state.status)
@@ -313,6 +317,7 @@ def _install_gdn(gdn, gdn_replica, state):
             _require_gdn_layout(lin, attn, norm, params, pool, forward_batch.spec_info.draft_token_num)
             checked[0] = True
         T = x.shape[0]
+        note("gdn_verify", T)
         outs = bufs.get(T)
         if outs is None:
             outs = bufs[T] = [torch.empty(T, wd, dtype=torch.bfloat16, device=x.device) for wd in GDN_SPLIT]
@@ -378,6 +383,7 @@ def _install_attention(module, replica, state):
             cos_sin[0] = cs.float().contiguous()           # [max_pos, 64] = [cos 32 | sin 32]
             checked[0] = True
         md = backend.forward_metadata
+        note("attn_verify", x.shape[0])
         pos = positions if positions.dtype == torch.int64 else positions.to(torch.int64)
         q, gate, k, v = ops.attn_front(x, codes, scales, module.q_norm.weight, module.k_norm.weight, pos.contiguous(),
                                        cos_sin[0], module.q_norm.variance_epsilon, True, status=state.status)

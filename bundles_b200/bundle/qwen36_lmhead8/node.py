@@ -14,6 +14,7 @@ import torch
 
 from bundles_b200 import ops, parallel
 from bundles_b200 import prepare as prepare_q
+from bundles_b200.evidence import note
 
 _copies = {}   # (device index, data_ptr) -> (codes uint8 [V,H], scales fp32 [V/128, H/128], shard_lo)
 
@@ -66,6 +67,7 @@ class _Node:
         shard: the (max, argmax) pairs are gathered and merged, and the shards' logits are gathered into [T, V]."""
         x = hidden_states.to(torch.bfloat16).contiguous()
         codes, scales, lo = _private_copy(lm_head.weight, self.group)
+        note("lmhead_argmax" if self.group is None else "lmhead_argmax_sharded", x.shape[0])
         mx, idx, lg = ops.lmhead_argmax(x, codes, scales, lo, True)
         if self.group is None:
             self.last_token_ids = idx

@@ -225,6 +225,9 @@ def test_recurrent_layer_verify_branch_and_handoff(monkeypatch):
     assert out2.shape == out.shape and torch.isfinite(out2.float()).all()
     for st in (prepared[0].state, prepared[1].state):
         assert ops_status(st.status) == 0
+    from bundles_b200 import evidence
+    paths = {k[2] for k in evidence.seen()}
+    assert {"gdn_verify", "proj_add_norm", "moe_combine_norm_handoff"} <= paths      # one line per path, not per layer
     # a decode batch runs the stock recurrent block
     fb_dec = type("FB", (), dict(forward_mode=FakeMode("decode"), positions=fb.positions, attn_backend=backend,
                                  req_pool_indices=pool["ring_idx"]))()

@@ -161,3 +161,11 @@ def test_partition_math():
     assert [hi - lo for lo, hi in sh] == [19072] * 3 + [18944] * 5
     assert sh[0][0] == 0 and sh[-1][1] == 151936 and all(lo % 128 == 0 for lo, _ in sh)
     assert parallel.vocab_shards(300, 2) == [(0, 256), (256, 300)]
+
+
+def test_evidence_prints_one_line_per_path(capsys):
+    from bundles_b200 import evidence
+    evidence.note("unit_test_path", 12)
+    evidence.note("unit_test_path", 40)          # same (process, rank, path, capture state): no second line
+    err = capsys.readouterr().err
+    assert err.count("B200NODES: unit_test_path") == 1 and "rows=12" in err and "captured=0" in err
