@@ -612,6 +612,80 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const bf16* __res
   pdl_wait();
   pdl_launch();
   const bool pad = pos != nullptr && pos[t] == 0;
+  // H == 2048 and K <= 12 (the decode shapes): a thread owns 8 columns, and everything it reads (its x and gate
+  // columns, the K + 1 cache rows, the residual, the norm weight) is requested before anything is used: one round
+  // trip to memory instead of three.  The arithmetic and its order are those of the general path below.
+  if (H == 2048 && K <= 12) {
+    const int c = tid * 8;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    const bool gated = gate_w != nullptr;
+    const uint4 xa = (!pad && gated) ? *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H + c) : zero4;
+    const uint4 gw4 = (!pad && gated) ? *reinterpret_cast<const uint4*>(gate_w + c) : zero4;
+    uint4 rows[13];
+#pragma unroll
+    for (int j = 0; j < 12; ++j)
+      rows[j] = (!pad && j < K) ? *reinterpret_cast<const uint4*>(cache + (static_cast<size_t>(t) * K + j) * H + c) : zero4;
+    rows[12] = (!pad && gated) ? *reinterpret_cast<const uint4*>(cache + (static_cast<size_t>(T) * K + t) * H + c) : zero4;
+    const uint4 b = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * H + c);
+    const uint4 g = *reinterpret_cast<const uint4*>(norm_w + c);
+    float gate = 0.f;
+    if (!pad && gated) {
+      float dot = 0.f;
+      dot = fmaf(bf_lo(xa.x), bf_lo(gw4.x), dot); dot = fmaf(bf_hi(xa.x), bf_hi(gw4.x), dot);
+      dot = fmaf(bf_lo(xa.y), bf_lo(gw4.y), dot); dot = fmaf(bf_hi(xa.y), bf_hi(gw4.y), dot);
+      dot = fmaf(bf_lo(xa.z), bf_lo(gw4.z), dot); dot = fmaf(bf_hi(xa.z), bf_hi(gw4.z), dot);
+      dot = fmaf(bf_lo(xa.w), bf_lo(gw4.w), dot); dot = fmaf(bf_hi(xa.w), bf_hi(gw4.w), dot);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(FULL_MASK, dot, o);
+      if ((tid & 31) == 0) red[tid >> 5] = dot;
+    }
+    __syncthreads();
+    if (!pad && gated) {
+      float s = 0.f;
+      for (int w = 0; w < 8; ++w) s += red[w];
+      gate = 1.f / (1.f + __expf(-s));
+    }
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (!pad) {
+#pragma unroll
+      for (int j = 0; j < 12; ++j)
+        if (j < K) {
+          const uint4 v = rows[j];
+          acc[0] += bf_lo(v.x); acc[1] += bf_hi(v.x); acc[2] += bf_lo(v.y); acc[3] += bf_hi(v.y);
+          acc[4] += bf_lo(v.z); acc[5] += bf_hi(v.z); acc[6] += bf_lo(v.w); acc[7] += bf_hi(v.w);
+        }
+      if (gated) {
+        const uint4 v = rows[12];
+        acc[0] += gate * bf_lo(v.x); acc[1] += gate * bf_hi(v.x); acc[2] += gate * bf_lo(v.y); acc[3] += gate * bf_hi(v.y);
+        acc[4] += gate * bf_lo(v.z); acc[5] += gate * bf_hi(v.z); acc[6] += gate * bf_lo(v.w); acc[7] += gate * bf_hi(v.w);
+      }
+    }
+    const uint4 o4 = make_uint4(pack_bf2(acc[0], acc[1]), pack_bf2(acc[2], acc[3]), pack_bf2(acc[4], acc[5]),
+                                pack_bf2(acc[6], acc[7]));
+    if (out != nullptr) *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + c) = o4;
+    float r[8] = {rbf(bf_lo(o4.x) + bf_lo(b.x)), rbf(bf_hi(o4.x) + bf_hi(b.x)), rbf(bf_lo(o4.y) + bf_lo(b.y)),
+                  rbf(bf_hi(o4.y) + bf_hi(b.y)), rbf(bf_lo(o4.z) + bf_lo(b.z)), rbf(bf_hi(o4.z) + bf_hi(b.z)),
+                  rbf(bf_lo(o4.w) + bf_lo(b.w)), rbf(bf_hi(o4.w) + bf_hi(b.w))};
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(r[i], r[i], ss);
+    *reinterpret_cast<uint4*>(residual + static_cast<size_t>(t) * H + c) =
+        make_uint4(pack_bf2(r[0], r[1]), pack_bf2(r[2], r[3]), pack_bf2(r[4], r[5]), pack_bf2(r[6], r[7]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(FULL_MASK, ss, o);
+    if ((tid & 31) == 0) red2[tid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < 8; ++i) tot += red2[i];
+    const float rstd = rsqrtf(tot / H + eps);
+    const float gwn[8] = {bf_lo(g.x), bf_hi(g.x), bf_lo(g.y), bf_hi(g.y), bf_lo(g.z), bf_hi(g.z), bf_lo(g.w), bf_hi(g.w)};
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = r[i] * rstd * (1.f + gwn[i]);
+    *reinterpret_cast<uint4*>(normed + static_cast<size_t>(t) * H + c) =
+        make_uint4(pack_bf2(y[0], y[1]), pack_bf2(y[2], y[3]), pack_bf2(y[4], y[5]), pack_bf2(y[6], y[7]));
+    return;
+  }
   float gate = 0.f;
   if (!pad && gate_w != nullptr) {
     float dot = 0.f;

@@ -158,7 +158,7 @@ def test_ring_layout_with_empty_rings_gives_the_same_tokens():
     assert ops.read_status(hist.status) == 0 and c.shape == a.shape
 
 
-@pytest.mark.parametrize("world,B", [(2, 4), (4, 4), (2, 20)])
+@pytest.mark.parametrize("world,B", [(2, 4), (4, 4), (2, 20), (8, 8)])
 def test_expert_parallel_form_equals_the_single_gpu_form(world, B):
     """Virtual ranks on one GPU (every rank's buffers in the same memory, steps in lockstep): sequences, experts and
     vocabulary split `world` ways give the same tokens, hidden rows, GDN states and KV bytes as the one-GPU step.
