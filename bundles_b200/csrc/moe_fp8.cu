@@ -122,6 +122,10 @@ struct F8Args {
 };
 
 constexpr int MODE_DOWN = 0, MODE_UP = 1, MODE_LM = 2, MODE_DENSE = 3;
+// The dense modes over 128-row chunks of the token rows (more than 64 rows in the call): the weight tile is read half
+// as often per row, and every activation scale of the call sits in shared memory from the start.
+constexpr int MODE_DENSE_W = 4, MODE_LM_W = 5;
+constexpr int F8_AS_FLOATS = 8192;       // wide modes: activation scales [k blocks][rows padded to 128]
 
 template <int MODE>
 struct F8Cfg {
@@ -129,16 +133,17 @@ struct F8Cfg {
   // two weight tiles per stage against one token tile: gate + up rows of one channel block (up), two consecutive
   // 128-row tiles of W2 (down: the token tile is read half as often and every per-tile cost is paid half as often)
   static constexpr bool DUAL = MODE == MODE_UP || MODE == MODE_DOWN;
+  static constexpr bool WIDE = MODE == MODE_DENSE_W || MODE == MODE_LM_W;
   static constexpr int NA = DUAL ? 2 : 1;
-  static constexpr int STAGE = NA * F8_TILE + F8_BTILE;
-  static constexpr int STAGES = DUAL ? 4 : 7;
-  static constexpr int PW = DUAL ? 128 : 64;   // TMEM columns of one partial buffer
+  static constexpr int STAGE = NA * F8_TILE + (WIDE ? F8_TILE : F8_BTILE);
+  static constexpr int STAGES = DUAL ? 4 : (WIDE ? 5 : 7);
+  static constexpr int PW = (DUAL || WIDE) ? 128 : 64;   // TMEM columns of one partial buffer
   static constexpr int NPB = 512 / PW;       // partial buffers
-  static constexpr int META_WARP = 32 * F8_MAXKG * 4 + 32 * 8 + 2 * F8_MAXKG * 4;
+  static constexpr int META_WARP = (WIDE ? 0 : 32 * F8_MAXKG * 4) + 32 * 8 + 2 * F8_MAXKG * 4;
   static constexpr int META = 8 * META_WARP;  // per epilogue warp: activation scales, slot, weight of its 32 columns, weight scales
   static constexpr bool LISTS = MODE == MODE_UP || MODE == MODE_DOWN;
   static constexpr int TINFO = LISTS ? F8_CACHED * 12 + (F8_CACHED + 32) * 4 : 64;  // block entries + cost prefix
-  static constexpr int SMEM = STAGES * STAGE + 1024 + 256 + META + TINFO + F8_WS_FLOATS * 4;
+  static constexpr int SMEM = STAGES * STAGE + 1024 + 256 + META + TINFO + F8_WS_FLOATS * 4 + (WIDE ? F8_AS_FLOATS * 4 : 0);
   static constexpr int TMEM = 512;
 };
 
@@ -157,8 +162,10 @@ __global__ void __launch_bounds__(F8_THREADS, 1)
 moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWsh,
                    const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmX64, const F8Args p) {
   using C = F8Cfg<MODE>;
-  constexpr bool UP = MODE == MODE_UP, LM = MODE == MODE_LM || MODE == MODE_DENSE, DENSE = MODE == MODE_DENSE;
-  constexpr bool DUAL = C::DUAL;
+  constexpr bool UP = MODE == MODE_UP, DENSE = MODE == MODE_DENSE || MODE == MODE_DENSE_W;
+  constexpr bool LM = MODE == MODE_LM || MODE == MODE_LM_W || DENSE;   // no lists: blocks are chunks of the token rows
+  constexpr bool DUAL = C::DUAL, WIDE = C::WIDE;
+  constexpr int CH = WIDE ? 128 : 64;   // token rows of a chunk in the dense modes
   constexpr int MROWS = (MODE == MODE_DOWN) ? 256 : 128;  // weight rows (output features) per tile
   // second weight tile of a stage: the up rows of the same channels (I rows further), or the next 128 rows of W2
   extern __shared__ uint8_t smem_raw[];
@@ -173,6 +180,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   int* tinfo = reinterpret_cast<int*>(meta + C::META);   // [F8_CACHED][3] expert, first row, rows of each block
   int* cprefix = tinfo + F8_CACHED * 3;                  // [F8_CACHED + 1] cost of the blocks before each block
   float* ws_cache = reinterpret_cast<float*>(meta + C::META + C::TINFO);
+  float* as_all = ws_cache + F8_WS_FLOATS;               // wide modes: [ksteps][tpad]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -200,7 +208,8 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   // (The dense modes have no lists: their blocks are the 64-row chunks of the token rows, and a tile is
   // (weight tile, chunk) with the chunk fastest, so the chunks of one weight tile run back to back on one CTA
   // and all but the first find the weight tile in L2.)
-  const int nblocks = LM ? (p.total_rows + 63) / 64 : p.L.nblocks[0];
+  const int nblocks = LM ? (p.total_rows + CH - 1) / CH : p.L.nblocks[0];
+  const int tpad = nblocks * 128;
   const int ntiles = nblocks * p.mtiles * (DENSE ? p.ksplit : 1);
   int t_lo = static_cast<int>(static_cast<long long>(blockIdx.x) * ntiles / gridDim.x);
   int t_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * ntiles / gridDim.x);
@@ -260,8 +269,8 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       e = 0;
       const int mx = tile / nblocks;
       mt = DENSE ? mx / p.ksplit : mx;
-      row0 = (tile - mx * nblocks) * 64;
-      n = p.total_rows - row0 < 64 ? p.total_rows - row0 : 64;
+      row0 = (tile - mx * nblocks) * CH;
+      n = p.total_rows - row0 < CH ? p.total_rows - row0 : CH;
       return n >= 1;
     }
     const int blk = tile / p.mtiles;
@@ -295,7 +304,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
     for (int u = 0; u < 16; ++u) m.v[u] = 0.f;
     int e, row0, n, mt;
-    if (tile >= t_hi || !decode(tile, e, row0, n, mt)) return;
+    if (WIDE || tile >= t_hi || !decode(tile, e, row0, n, mt)) return;
     const int c = (lane >> 4) * 32 + ep_half * 16 + (lane & 15);
     if (!LM && c < n) {
       m.slot = p.L.slot_of_row[row0 + c];
@@ -366,11 +375,11 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           // every TMA instruction costs the issuing thread ~80 ns: more than 32 token rows come as one 64-row
           // box (rows past the block belong to the next expert or are zero-filled past the end; the MMA's N
           // ignores them) instead of three or four 16-row boxes
-          mbar_expect_tx(&full[stage], C::NA * F8_TILE + (nb16 > 2 ? F8_BTILE : nb16 * 2048));
+          mbar_expect_tx(&full[stage], C::NA * F8_TILE + (WIDE ? F8_TILE : nb16 > 2 ? F8_BTILE : nb16 * 2048));
           tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
           if (DUAL) tma_load_2d(sA + F8_TILE, mapW, ks * 128, wrow + (UP ? p.I : 128), &full[stage]);
           if (p.test_starve) {
-          } else if (nb16 > 2) {
+          } else if (WIDE || nb16 > 2) {   // wide modes: tmX64 carries a 128-row box
             tma_load_2d(sB, &tmX64, ks * 128, row0, &full[stage]);
           } else {
             for (int b = 0; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
@@ -442,7 +451,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     float* m_as = reinterpret_cast<float*>(meta + (warp - 2) * C::META_WARP);  // [ksteps][32]
-    float* m_wt = m_as + 32 * F8_MAXKG;                                        // [32]
+    float* m_wt = m_as + (WIDE ? 0 : 32 * F8_MAXKG);                           // [32]
     int* m_slot = reinterpret_cast<int*>(m_wt + 32);                           // [32]
     float* m_ws = reinterpret_cast<float*>(m_slot + 32);                       // [2][F8_MAXKG] weight block scales
     const float* __restrict__ a_scale = p.a_scale;
@@ -505,7 +514,14 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       ws_cache[idx] = v;
     }
-    asm volatile("bar.sync 1, 256;" ::: "memory");  // the epilogue warps' fill of ws_cache is complete
+    if (WIDE) {   // lane -> row, so the shared-memory writes of a warp fall in consecutive banks
+      const int et = static_cast<int>(threadIdx.x) - 64;
+      for (int idx = et; idx < tpad * p.ksteps; idx += F8_THREADS - 64) {
+        const int ks = idx / tpad, row = idx - ks * tpad;
+        as_all[idx] = row < p.total_rows ? a_scale[static_cast<size_t>(row) * p.ksteps + ks] : 0.f;
+      }
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");  // the epilogue warps' fill of ws_cache (and as_all) is complete
     for (int tile = t_lo; ok && tile < t_hi; ++tile) {
       int e, row0, n, mt;
       const bool cached = tile - t_lo < ws_ncache;
@@ -522,7 +538,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (warp == 2 && lane == 0) TRACE(5, tile - t_lo);
 #endif
       const int blk = blk_of(tile);
-      if (blk != staged_blk) {  // first tile of a block (dense modes: of a chunk of token rows)
+      if (!WIDE && blk != staged_blk) {  // first tile of a block (dense modes: of a chunk of token rows)
         staged_blk = blk;
         stage_block(row0, n);
         // the next block's metadata is requested now and consumed at that block's first tile
@@ -537,10 +553,10 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const float* __restrict__ wsc_a = cached ? ws_cache + (tile - t_lo) * ws_per_tile : m_ws;
       const float* __restrict__ wsc_b = cached ? wsc_a + p.ksteps : m_ws + F8_MAXKG;
       if (warp == 2 && lane == 0) TRACE(3, 2 + 2 * ((tile - t_lo)));
-      float acc_a[32], acc_b[DUAL ? 32 : 1];
+      float acc_a[32], acc_b[(DUAL || WIDE) ? 32 : 1];   // wide: acc_b holds the columns 64 further
 #pragma unroll
       for (int c = 0; c < 32; ++c) acc_a[c] = 0.f;
-      if (DUAL)
+      if (DUAL || WIDE)
 #pragma unroll
         for (int c = 0; c < 32; ++c) acc_b[c] = 0.f;
       const int kfirst = k0_of(tile);
@@ -554,18 +570,22 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         tc_fence_after();
         if (warp == 2 && lane == 0) TRACE(2, g);
         const uint32_t taddr = tmem_base + pb * C::PW + half * 16 + (static_cast<uint32_t>(q * 32) << 16);
+        const float* __restrict__ as_w = as_all + ks * tpad + row0 + half * 16;   // wide: scales of this warp's columns
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
           if (h2 * 32 + half * 16 < n) {
             uint32_t ra[16], rb[16];
+            const bool far = WIDE && 64 + h2 * 32 + half * 16 < n;   // the same for the whole warp
             tmem_ld16(taddr + h2 * 32, ra);
-            if (DUAL) tmem_ld16(taddr + 64 + h2 * 32, rb);
+            if (DUAL || far) tmem_ld16(taddr + 64 + h2 * 32, rb);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float as = m_as[ks * 32 + h2 * 16 + i];
+              const float as = WIDE ? as_w[h2 * 32 + i] : m_as[ks * 32 + h2 * 16 + i];
               acc_a[h2 * 16 + i] = __fmaf_rn(__uint_as_float(ra[i]), __fmul_rn(as, wsa), acc_a[h2 * 16 + i]);
               if (DUAL) acc_b[h2 * 16 + i] = __fmaf_rn(__uint_as_float(rb[i]), __fmul_rn(as, wsb), acc_b[h2 * 16 + i]);
+              if (far)
+                acc_b[h2 * 16 + i] = __fmaf_rn(__uint_as_float(rb[i]), __fmul_rn(as_w[64 + h2 * 32 + i], wsa), acc_b[h2 * 16 + i]);
             }
           }
         }
@@ -582,6 +602,10 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
               const int c = (l >> 4) * 32 + half * 16 + (l & 15);
               if (c < n && rr < p.w_rows) st_global_na(o + static_cast<size_t>(c) * p.w_rows, acc_a[l]);
               acc_a[l] = 0.f;
+              if (WIDE) {
+                if (c + 64 < n && rr < p.w_rows) st_global_na(o + static_cast<size_t>(c + 64) * p.w_rows, acc_b[l]);
+                acc_b[l] = 0.f;
+              }
             }
           }
         }
@@ -605,6 +629,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           for (int l = 0; l < 32; ++l) {
             const int c = (l >> 4) * 32 + half * 16 + (l & 15);
             if (c < n) st_global_na(o + static_cast<size_t>(row0 + c) * ld, f2bf(acc_a[l]));
+            if (WIDE && c + 64 < n) st_global_na(o + static_cast<size_t>(row0 + c + 64) * ld, f2bf(acc_b[l]));
           }
         }
       } else if (LM) {
@@ -614,50 +639,56 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         // against a number, -0 and +0 compare equal), after which lane l holds local column l; the row
         // comes from a ballot of the lanes whose value equals the maximum.
         const bool live = r < p.w_rows;
-        float mv[32];
+        auto reduce_cols = [&](const float* acc, int cofs) {   // the 32 columns of `acc`, tile columns cofs further
+          float mv[32];
 #pragma unroll
-        for (int l = 0; l < 32; ++l) {
-          mv[l] = live ? acc_a[l] : __int_as_float(0x7fc00000);
-          if (p.lm_logits && live) {
-            const int c = (l >> 4) * 32 + half * 16 + (l & 15);
-            if (c < n) st_global_na(p.lm_logits + static_cast<size_t>(row0 + c) * p.lm_ld + r, acc_a[l]);
-          }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          const bool up_half = (lane & o) != 0;
-#pragma unroll
-          for (int i = 0; i < o; ++i) {
-            const float send = up_half ? mv[i] : mv[i + o];
-            const float keep = up_half ? mv[i + o] : mv[i];
-            mv[i] = fmaxf(keep, __shfl_xor_sync(FULL_MASK, send, o));
-          }
-        }
-        const float best = mv[0];  // column `lane`: NaN only if every live row is NaN (or none is live)
-        uint32_t mine = 0u;
-#pragma unroll
-        for (int l = 0; l < 32; ++l) {
-          const float bl = __shfl_sync(FULL_MASK, best, l);
-          const uint32_t hit = __ballot_sync(FULL_MASK, live && acc_a[l] == bl);
-          if (lane == l) mine = hit;
-        }
-        const uint32_t live_mask = __ballot_sync(FULL_MASK, live);
-        {
-          const int c = (lane >> 4) * 32 + half * 16 + (lane & 15);
-          if (c < n) {
-            unsigned long long key = 0ull;  // no live row
-            const int base_id = p.lm_shard_lo + mt * 128 + q * 32;
-            if (mine) {
-              uint32_t k = __float_as_uint(best + 0.f);
-              k = (k & 0x80000000u) ? ~k : (k | 0x80000000u);
-              if (k < 2u) k = 2u;
-              key = (static_cast<unsigned long long>(k) << 32) |
-                    (0xffffffffu - static_cast<uint32_t>(base_id + __ffs(mine) - 1));
-            } else if (live_mask) {  // only NaN among the live rows: value part 1, the lowest live row
-              key = (1ull << 32) | (0xffffffffu - static_cast<uint32_t>(base_id + __ffs(live_mask) - 1));
+          for (int l = 0; l < 32; ++l) {
+            mv[l] = live ? acc[l] : __int_as_float(0x7fc00000);
+            if (p.lm_logits && live) {
+              const int c = cofs + (l >> 4) * 32 + half * 16 + (l & 15);
+              if (c < n) st_global_na(p.lm_logits + static_cast<size_t>(row0 + c) * p.lm_ld + r, acc[l]);
             }
-            p.lm_keys[(static_cast<size_t>(mt) * 4 + q) * p.total_rows + row0 + c] = key;
           }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            const bool up_half = (lane & o) != 0;
+#pragma unroll
+            for (int i = 0; i < o; ++i) {
+              const float send = up_half ? mv[i] : mv[i + o];
+              const float keep = up_half ? mv[i + o] : mv[i];
+              mv[i] = fmaxf(keep, __shfl_xor_sync(FULL_MASK, send, o));
+            }
+          }
+          const float best = mv[0];  // column `lane`: NaN only if every live row is NaN (or none is live)
+          uint32_t mine = 0u;
+#pragma unroll
+          for (int l = 0; l < 32; ++l) {
+            const float bl = __shfl_sync(FULL_MASK, best, l);
+            const uint32_t hit = __ballot_sync(FULL_MASK, live && acc[l] == bl);
+            if (lane == l) mine = hit;
+          }
+          const uint32_t live_mask = __ballot_sync(FULL_MASK, live);
+          {
+            const int c = cofs + (lane >> 4) * 32 + half * 16 + (lane & 15);
+            if (c < n) {
+              unsigned long long key = 0ull;  // no live row
+              const int base_id = p.lm_shard_lo + mt * 128 + q * 32;
+              if (mine) {
+                uint32_t k = __float_as_uint(best + 0.f);
+                k = (k & 0x80000000u) ? ~k : (k | 0x80000000u);
+                if (k < 2u) k = 2u;
+                key = (static_cast<unsigned long long>(k) << 32) |
+                      (0xffffffffu - static_cast<uint32_t>(base_id + __ffs(mine) - 1));
+              } else if (live_mask) {  // only NaN among the live rows: value part 1, the lowest live row
+                key = (1ull << 32) | (0xffffffffu - static_cast<uint32_t>(base_id + __ffs(live_mask) - 1));
+              }
+              p.lm_keys[(static_cast<size_t>(mt) * 4 + q) * p.total_rows + row0 + c] = key;
+            }
+          }
+        };
+        reduce_cols(acc_a, 0);
+        if constexpr (WIDE) {
+          if (64 + half * 16 < n) reduce_cols(acc_b, 64);
         }
       } else if (UP) {
         bf16* __restrict__ hout = p.h_out + static_cast<size_t>(row0) * p.I + r;
@@ -915,6 +946,23 @@ __global__ void argmax_merge_kernel(const float* __restrict__ maxes, const int32
 struct LmLayout {
   size_t xq, xs, keys, total;
 };
+// The dense modes take 128-row chunks when there are more than 64 rows and the activation scales of all rows fit
+// the kernel's shared-memory table; the per-element arithmetic is the same either way.
+static bool dense_wide(int T, int K) { return T > 64 && ((T + 127) / 128) * 128 * (K / 128) <= F8_AS_FLOATS; }
+static int dense_chunks(int T, int K) { return dense_wide(T, K) ? (T + 127) / 128 : (T + 63) / 64; }
+template <int NARROW, int WIDEM>
+static void launch_dense(bool wide, int grid, const CUtensorMap& tmW, const CUtensorMap& tmX, const CUtensorMap& tmXbox,
+                         const F8Args& a, cudaStream_t st) {
+  static DeviceOnce once;
+  once.run([] {
+    cudaFuncSetAttribute(moe_gemm_f8_kernel<NARROW>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<NARROW>::SMEM);
+    cudaFuncSetAttribute(moe_gemm_f8_kernel<WIDEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<WIDEM>::SMEM);
+  });
+  if (wide)
+    moe_gemm_f8_kernel<WIDEM><<<grid, F8_THREADS, F8Cfg<WIDEM>::SMEM, st>>>(tmW, tmW, tmX, tmXbox, a);
+  else
+    moe_gemm_f8_kernel<NARROW><<<grid, F8_THREADS, F8Cfg<NARROW>::SMEM, st>>>(tmW, tmW, tmX, tmXbox, a);
+}
 static LmLayout lm_layout(int T, int H, int V_shard) {
   auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
   LmLayout l;
@@ -950,11 +998,8 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(V_shard), H, 128, "lm_head weight"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "lm_head activations"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, 64, "lm_head activations"))) return rc;
-  static DeviceOnce once;
-  once.run([] {
-    cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_LM>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<MODE_LM>::SMEM);
-  });
+  const bool wide = dense_wide(T, H);
+  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, wide ? 128 : 64, "lm_head activations"))) return rc;
   // K = 0 routed picks: the "shared expert" row of token t is row t
   quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, xq, xs);
   F8Args a{};
@@ -964,7 +1009,7 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   a.w_rows = V_shard;
   a.I = 0;
   a.H = H;
-  a.total_rows = T;   // more than 64 rows: 64-row chunks, every weight tile against each chunk in turn
+  a.total_rows = T;   // more than 64 rows: 64- or 128-row chunks, every weight tile against each chunk in turn
   a.s_w = w_s;
   a.s_w_sh = w_s;
   a.a_scale = xs;
@@ -973,9 +1018,9 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   a.lm_logits = logits_out;
   a.lm_ld = V_shard;
   a.lm_shard_lo = shard_lo;
-  const int ntiles = a.mtiles * ((T + 63) / 64);
+  const int ntiles = a.mtiles * dense_chunks(T, H);
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
-  moe_gemm_f8_kernel<MODE_LM><<<grid, F8_THREADS, F8Cfg<MODE_LM>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
+  launch_dense<MODE_LM, MODE_LM_W>(wide, grid, tmW, tmX, tmX64, a, st);
   launch_k(lmhead_finish_kernel, dim3(T), dim3(256), 0, st, static_cast<const unsigned long long*>(keys), a.mtiles * 4, T,
            max_out, idx_out);
   return launch_status("b200_lmhead_argmax");
@@ -1064,12 +1109,8 @@ extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, 
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(N), H, 128, "dense weight"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "dense activations"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, 64, "dense activations"))) return rc;
-  static DeviceOnce once;
-  once.run([] {
-    cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         F8Cfg<MODE_DENSE>::SMEM);
-  });
+  const bool wide = dense_wide(T, H);
+  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, wide ? 128 : 64, "dense activations"))) return rc;
   quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, xq, xs);
   F8Args a{};
   a.E_local = 1;
@@ -1077,7 +1118,7 @@ extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, 
   a.ksteps = H / 128;
   a.w_rows = N;
   a.H = H;
-  a.total_rows = T;   // more than 64 rows: 64-row chunks, every weight tile against each chunk in turn
+  a.total_rows = T;   // more than 64 rows: 64- or 128-row chunks, every weight tile against each chunk in turn
   a.s_w = w_s;
   a.s_w_sh = w_s;
   a.a_scale = xs;
@@ -1093,9 +1134,9 @@ extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, 
     c0 += seg_cols_host[i];
   }
   a.seg_lo[nseg] = c0;
-  const int ntiles = a.mtiles * ((T + 63) / 64);
+  const int ntiles = a.mtiles * dense_chunks(T, H);
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
-  moe_gemm_f8_kernel<MODE_DENSE><<<grid, F8_THREADS, F8Cfg<MODE_DENSE>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
+  launch_dense<MODE_DENSE, MODE_DENSE_W>(wide, grid, tmW, tmX, tmX64, a, st);
   return launch_status("b200_dense_fp8");
 }
 
@@ -1169,7 +1210,7 @@ static int proj_kparts(int N, int K) {
   return s;
 }
 static int proj_ksplit(int N, int K, int T) {
-  const int units = ((N + 127) / 128) * ((T + 63) / 64);
+  const int units = ((N + 127) / 128) * dense_chunks(T, K);
   int s = proj_kparts(N, K);
   while (s > 1 && units * s > sm_count()) s >>= 1;
   return s;
@@ -1203,12 +1244,8 @@ extern "C" int b200_dense_fp8_add_rmsnorm(const void* x, int T, int K, const voi
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(N), K, 128, "projection weight"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmX, xq, T, K, 16, "projection activations"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, K, 64, "projection activations"))) return rc;
-  static DeviceOnce once;
-  once.run([] {
-    cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         F8Cfg<MODE_DENSE>::SMEM);
-  });
+  const bool wide = dense_wide(T, K);
+  if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, K, wide ? 128 : 64, "projection activations"))) return rc;
   quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, K, 0, nullptr, 0, T, xq, xs);
   F8Args a{};
   a.E_local = 1;
@@ -1230,9 +1267,9 @@ extern "C" int b200_dense_fp8_add_rmsnorm(const void* x, int T, int K, const voi
   a.seg_ld[0] = N;
   a.seg_out[0] = nullptr;   // not used: the sums go through `partials` (also when there is a single K part)
   const int S = a.kparts;
-  const int ntiles = a.mtiles * ((T + 63) / 64) * a.ksplit;
+  const int ntiles = a.mtiles * dense_chunks(T, K) * a.ksplit;
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
-  moe_gemm_f8_kernel<MODE_DENSE><<<grid, F8_THREADS, F8Cfg<MODE_DENSE>::SMEM, st>>>(tmW, tmW, tmX, tmX64, a);
+  launch_dense<MODE_DENSE, MODE_DENSE_W>(wide, grid, tmW, tmX, tmX64, a, st);
   add_rmsnorm_partials_kernel<<<T, 256, 0, st>>>(partials, S, T, static_cast<bf16*>(residual),
                                                  static_cast<const bf16*>(norm_w), eps, N, static_cast<bf16*>(out),
                                                  static_cast<bf16*>(proj_out));

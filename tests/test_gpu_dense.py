@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("T,H,N", [(64, 2048, 12352), (8, 4096, 2048), (1, 2048, 9216), (33, 2048, 200), (150, 2048, 640),
-                                   (256, 4096, 2048)])
+                                   (256, 4096, 2048), (100, 2048, 640), (512, 2048, 256), (600, 2048, 256)])
 def test_dense_projection(T, H, N):
     g = torch.Generator().manual_seed(T + N)
     npad = (N + 127) // 128 * 128
@@ -27,6 +27,23 @@ def test_dense_projection(T, H, N):
     ref = oat.dense_fp8(bf16_to_np(x), codes.numpy(), scales.numpy())
     ok, err, nbad = close_bf16(bf16_to_np(out), ref)
     assert ok, (err, nbad)
+
+
+def test_rows_do_not_depend_on_the_batch_they_are_in():
+    # 64-row calls take 64-row chunks, larger calls 128-row chunks: a row's bits are the same in both
+    g = torch.Generator().manual_seed(21)
+    H, N = 2048, 640
+    w = torch.randn(N, H, generator=g) * 0.02
+    codes, scales = synth.quant_fp8_blocks(w)
+    codes, scales = codes.to(dev()), scales.to(dev())
+    x = torch.randn(230, H, generator=g).to(torch.bfloat16).to(dev())
+    st = ops.new_status(dev())
+    whole = ops.dense_fp8(x, codes, scales, status=st)
+    for lo, hi in ((0, 64), (64, 100), (128, 230), (200, 230)):
+        part = ops.dense_fp8(x[lo:hi].contiguous(), codes, scales, status=st)
+        assert torch.equal(part, whole[lo:hi]), (lo, hi)
+    torch.cuda.synchronize()
+    assert ops.read_status(st) == 0
 
 
 def test_split_outputs_equal_the_plain_projection():
@@ -54,7 +71,7 @@ def test_split_outputs_equal_the_plain_projection():
         ops.dense_fp8_split(x, codes, scales, (8192, 4100, 28, 32))     # inner boundary not a multiple of 32
 
 
-@pytest.mark.parametrize("T", [5, 32, 150])
+@pytest.mark.parametrize("T", [5, 32, 150, 256])
 def test_projection_fused_with_add_and_norm(T):
     """The split-K output projection + residual add + norm against the oracle's projection followed by its add + norm
     (the rounded projection within the bf16 tolerance, the add and the norm exact on that projection), and a row's

@@ -22,7 +22,7 @@ def _check_ids(idx, mx, ref_logits, lo=0):
     return int((idx != r_idx).sum())
 
 
-@pytest.mark.parametrize("T,V", [(64, 4096), (5, 1280), (16, 128 * 37), (150, 128 * 9 + 5)])
+@pytest.mark.parametrize("T,V", [(64, 4096), (5, 1280), (16, 128 * 37), (150, 128 * 9 + 5), (100, 128 * 3), (256, 128 * 5 + 40)])
 def test_single_shard(T, V):
     cfg = synth.lmhead(seed=70 + T, T=T, V=V)
     mx, idx, logits = ops.lmhead_argmax(cfg["x"].to(dev()), cfg["w"].to(dev()), cfg["w_s"].to(dev()), 0, True,
