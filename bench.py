@@ -322,7 +322,7 @@ def _moe_fp8_block_entry(dev, ops, timed, st, out, hbm, which, sets=3):
             x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
             wr = torch.randn(512, H, generator=g, device=dev) * 0.02
             _, ids, wts = ops.router(x, wr, K)
-            lists = ops.RoutingLists(T, K, En, 64, dev)
+            lists = ops.RoutingLists(T, K, En, 32, dev)
             ops.build_lists(ids, wts, lists, None, e_lo=0)          # the rank's experts are ids 0..En-1
             wsb = ops.moe_fp8_workspace(T, H, I, K, dev)
             cache = torch.zeros(T * (K + 1), H, dtype=torch.bfloat16, device=dev)
@@ -511,7 +511,7 @@ def _moe_fp8_router_entry(dev, ops, synth, timed, st, out, hbm, want):
     c = {k: (v.to(dev) if v is not None else None) for k, v in synth.moe_fp8(E=512).items()}
     w = ops.MoeW8A8Weights(c["w13"], c["s13"], c["w2"], c["s2"], c["sh13"], c["shs13"], c["sh2"], c["shs2"])
     _, ids, wts = ops.router(c["x"], c["wr"], 10)
-    lists = ops.RoutingLists(16, 10, 512, 64, dev)
+    lists = ops.RoutingLists(16, 10, 512, 32, dev)
     ops.build_lists(ids, wts, lists)
     wsb = ops.moe_fp8_workspace(16, 2048, 512, 10, dev)
     cache = torch.zeros(16 * 11, 2048, dtype=torch.bfloat16, device=dev)

@@ -19,7 +19,8 @@ namespace b200 {
 B200_DEFINE_WAIT_BUDGET_SETTER(set_wait_budget_moe_fp8)
 
 constexpr int F8_TILE = 128 * 128;       // weight tile bytes per stage
-constexpr int F8_BTILE = 64 * 128;       // token tile bytes per stage (<= 64 rows)
+constexpr int F8_BTILE = 64 * 128;       // token tile bytes per stage, dense modes (<= 64 rows)
+constexpr int F8_BTILE_MOE = 32 * 128;   // the same in the expert GEMMs (blocks of <= 32 rows)
 constexpr int F8_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int F8_CACHED = 1024;          // blocks of the list whose entries every CTA of a MoE GEMM keeps in shared memory
 constexpr int F8_MAXKG = 32;             // k blocks per row of scales held in shared memory (K <= 4096)
@@ -135,11 +136,15 @@ struct F8Cfg {
   static constexpr bool DUAL = MODE == MODE_UP || MODE == MODE_DOWN;
   static constexpr bool WIDE = MODE == MODE_DENSE_W || MODE == MODE_LM_W;
   static constexpr int NA = DUAL ? 2 : 1;
-  static constexpr int STAGE = NA * F8_TILE + (WIDE ? F8_TILE : F8_BTILE);
-  static constexpr int STAGES = DUAL ? 4 : (WIDE ? 5 : 7);
-  static constexpr int PW = (DUAL || WIDE) ? 128 : 64;   // TMEM columns of one partial buffer
+  static constexpr int STAGE = NA * F8_TILE + (WIDE ? F8_TILE : DUAL ? F8_BTILE_MOE : F8_BTILE);
+  static constexpr int STAGES = WIDE ? 5 : (DUAL ? 5 : 7);
+  // TMEM columns of one partial buffer.  The expert GEMMs take blocks of at most 32 rows, so a partial is 2 x 32
+  // columns and eight of them fit: the MMA issuer runs up to eight k blocks ahead of the promotion, which covers a
+  // tile's epilogue (and two whole tiles of the down GEMM).
+  static constexpr int PW = WIDE ? 128 : 64;
   static constexpr int NPB = 512 / PW;       // partial buffers
-  static constexpr int META_WARP = (WIDE ? 0 : 32 * F8_MAXKG * 4) + 32 * 8 + 2 * F8_MAXKG * 4;
+  static constexpr int NL = DUAL ? 16 : 32;  // columns (token rows) of a tile that one epilogue warp owns
+  static constexpr int META_WARP = (WIDE ? 0 : NL * F8_MAXKG * 4) + 32 * 8 + 2 * F8_MAXKG * 4;
   static constexpr int META = 8 * META_WARP;  // per epilogue warp: activation scales, slot, weight of its 32 columns, weight scales
   static constexpr bool LISTS = MODE == MODE_UP || MODE == MODE_DOWN;
   static constexpr int TINFO = LISTS ? F8_CACHED * 12 + (F8_CACHED + 32) * 4 : 64;  // block entries + cost prefix
@@ -165,6 +170,8 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   constexpr bool UP = MODE == MODE_UP, DENSE = MODE == MODE_DENSE || MODE == MODE_DENSE_W;
   constexpr bool LM = MODE == MODE_LM || MODE == MODE_LM_W || DENSE;   // no lists: blocks are chunks of the token rows
   constexpr bool DUAL = C::DUAL, WIDE = C::WIDE;
+  constexpr int NL = C::NL, NH2 = DUAL ? 1 : 2;
+  constexpr int BROWS = DUAL ? 32 : 64;   // most rows of a block
   constexpr int CH = WIDE ? 128 : 64;   // token rows of a chunk in the dense modes
   constexpr int MROWS = (MODE == MODE_DOWN) ? 256 : 128;  // weight rows (output features) per tile
   // second weight tile of a stage: the up rows of the same channels (I rows further), or the next 128 rows of W2
@@ -284,7 +291,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       row0 = p.L.blk_row0[blk];
       n = p.L.blk_rows[blk];
     }
-    return e >= 0 && e <= p.E_local && n >= 1 && n <= 64 && row0 >= 0 && row0 + n <= p.total_rows;
+    return e >= 0 && e <= p.E_local && n >= 1 && n <= BROWS && row0 >= 0 && row0 + n <= p.total_rows;
   };
 
   // Per-block metadata of an epilogue warp (activation scales, slot and routing weight of its 32 columns) is
@@ -298,6 +305,8 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     int slot;
   };
   const int ep_half = (warp - 2) >> 2;
+  // tile column of an epilogue warp's local column l: the two warps of a lane quadrant take alternate 16-column chunks
+  auto col_of = [&](int l) { return DUAL ? ep_half * 16 + l : (l >> 4) * 32 + ep_half * 16 + (l & 15); };
   auto fetch = [&](int tile, Meta& m) {  // the metadata of the block that `tile` belongs to
     m.wt = 0.f;
     m.slot = -1;
@@ -305,18 +314,18 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     for (int u = 0; u < 16; ++u) m.v[u] = 0.f;
     int e, row0, n, mt;
     if (WIDE || tile >= t_hi || !decode(tile, e, row0, n, mt)) return;
-    const int c = (lane >> 4) * 32 + ep_half * 16 + (lane & 15);
-    if (!LM && c < n) {
+    const int c = col_of(lane);
+    if (!LM && lane < NL && c < n) {
       m.slot = p.L.slot_of_row[row0 + c];
       m.wt = p.L.wt_of_row[row0 + c];
     }
-    const int total = 32 * p.ksteps;
+    const int total = NL * p.ksteps;
 #pragma unroll
     for (int u = 0; u < 16; ++u) {
       const int i = u * 32 + lane;  // i = l * ksteps + ks: consecutive lanes read consecutive floats
       if (i < total) {
         const int l = i / p.ksteps;
-        const int cc = (l >> 4) * 32 + ep_half * 16 + (l & 15);
+        const int cc = col_of(l);
         if (cc < n) m.v[u] = p.a_scale[static_cast<size_t>(row0 + cc) * p.ksteps + (i - l * p.ksteps)];
       }
     }
@@ -375,11 +384,11 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           // every TMA instruction costs the issuing thread ~80 ns: more than 32 token rows come as one 64-row
           // box (rows past the block belong to the next expert or are zero-filled past the end; the MMA's N
           // ignores them) instead of three or four 16-row boxes
-          mbar_expect_tx(&full[stage], C::NA * F8_TILE + (WIDE ? F8_TILE : nb16 > 2 ? F8_BTILE : nb16 * 2048));
+          mbar_expect_tx(&full[stage], C::NA * F8_TILE + (WIDE ? F8_TILE : (!DUAL && nb16 > 2) ? F8_BTILE : nb16 * 2048));
           tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
           if (DUAL) tma_load_2d(sA + F8_TILE, mapW, ks * 128, wrow + (UP ? p.I : 128), &full[stage]);
           if (p.test_starve) {
-          } else if (WIDE || nb16 > 2) {   // wide modes: tmX64 carries a 128-row box
+          } else if (WIDE || (!DUAL && nb16 > 2)) {   // wide modes: tmX64 carries a 128-row box
             tma_load_2d(sB, &tmX64, ks * 128, row0, &full[stage]);
           } else {
             for (int b = 0; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
@@ -433,7 +442,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           for (int kk = 0; kk < 4; ++kk) {
             const uint64_t db = umma_desc_sw128(sB + kk * 32);
             tc_mma_f8(d0, umma_desc_sw128(sA + kk * 32), db, idesc, kk != 0);
-            if (DUAL) tc_mma_f8(d0 + 64, umma_desc_sw128(sA + F8_TILE + kk * 32), db, idesc, kk != 0);
+            if (DUAL) tc_mma_f8(d0 + 32, umma_desc_sw128(sA + F8_TILE + kk * 32), db, idesc, kk != 0);
           }
           tc_commit(&empty[stage]);
           tc_commit(&pfull[pb]);
@@ -450,33 +459,34 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     // thread keeps at most 32 (+32 for up) accumulators ----------------
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    float* m_as = reinterpret_cast<float*>(meta + (warp - 2) * C::META_WARP);  // [ksteps][32]
-    float* m_wt = m_as + (WIDE ? 0 : 32 * F8_MAXKG);                           // [32]
+    float* m_as = reinterpret_cast<float*>(meta + (warp - 2) * C::META_WARP);  // [ksteps][NL]
+    float* m_wt = m_as + (WIDE ? 0 : NL * F8_MAXKG);                           // [32]
     int* m_slot = reinterpret_cast<int*>(m_wt + 32);                           // [32]
     float* m_ws = reinterpret_cast<float*>(m_slot + 32);                       // [2][F8_MAXKG] weight block scales
     const float* __restrict__ a_scale = p.a_scale;
     uint32_t g = 0;
     bool ok = true;
-    // local column l (0..31) of this warp is tile column col(l) = (l / 16) * 32 + half * 16 + l % 16.
+    // local column l of this warp is tile column col_of(l): half * 16 + l (l < 16) in the expert GEMMs,
+    // (l / 16) * 32 + half * 16 + l % 16 (l < 32) in the dense modes.
     // Destination row and routing weight of local column `lane` stay in this lane's registers and reach the
     // other lanes by shuffles in the down epilogue (a shared-memory read per stored value there made one
     // dependent round trip per column, 1.7 us per tile).
     bf16* cur_dst = nullptr;
     float cur_wt = 0.f;
     auto stage_block = [&](int row0, int n) {
-      const int total = 32 * p.ksteps;
+      const int total = NL * p.ksteps;
 #pragma unroll
       for (int u = 0; u < 16; ++u) {
         const int i = u * 32 + lane;
         if (i < total) {
           const int l = i / p.ksteps;
-          m_as[(i - l * p.ksteps) * 32 + l] = pre.v[u];
+          m_as[(i - l * p.ksteps) * NL + l] = pre.v[u];
         }
       }
-      for (int i = 512 + lane; i < total; i += 32) {  // more than 16 k blocks: the rest is fetched in place
+      for (int i = 512 + lane; i < total; i += 32) {  // more than 512 scales: the rest is fetched in place
         const int l = i / p.ksteps;
-        const int c = (l >> 4) * 32 + half * 16 + (l & 15);
-        m_as[(i - l * p.ksteps) * 32 + l] = c < n ? a_scale[static_cast<size_t>(row0 + c) * p.ksteps + (i - l * p.ksteps)] : 0.f;
+        const int c = col_of(l);
+        m_as[(i - l * p.ksteps) * NL + l] = c < n ? a_scale[static_cast<size_t>(row0 + c) * p.ksteps + (i - l * p.ksteps)] : 0.f;
       }
       const int slot = pre.slot < p.total_rows ? pre.slot : -1;
       m_slot[lane] = slot;
@@ -553,12 +563,12 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const float* __restrict__ wsc_a = cached ? ws_cache + (tile - t_lo) * ws_per_tile : m_ws;
       const float* __restrict__ wsc_b = cached ? wsc_a + p.ksteps : m_ws + F8_MAXKG;
       if (warp == 2 && lane == 0) TRACE(3, 2 + 2 * ((tile - t_lo)));
-      float acc_a[32], acc_b[(DUAL || WIDE) ? 32 : 1];   // wide: acc_b holds the columns 64 further
+      float acc_a[NL], acc_b[(DUAL || WIDE) ? NL : 1];   // wide: acc_b holds the columns 64 further
 #pragma unroll
-      for (int c = 0; c < 32; ++c) acc_a[c] = 0.f;
+      for (int c = 0; c < NL; ++c) acc_a[c] = 0.f;
       if (DUAL || WIDE)
 #pragma unroll
-        for (int c = 0; c < 32; ++c) acc_b[c] = 0.f;
+        for (int c = 0; c < NL; ++c) acc_b[c] = 0.f;
       const int kfirst = k0_of(tile);
       for (int ks = kfirst; ks < kfirst + kn; ++ks, ++g) {
         const uint32_t pb = g % C::NPB, pphase = (g / C::NPB) & 1u;
@@ -572,16 +582,16 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const uint32_t taddr = tmem_base + pb * C::PW + half * 16 + (static_cast<uint32_t>(q * 32) << 16);
         const float* __restrict__ as_w = as_all + ks * tpad + row0 + half * 16;   // wide: scales of this warp's columns
 #pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) {
+        for (int h2 = 0; h2 < NH2; ++h2) {
           if (h2 * 32 + half * 16 < n) {
             uint32_t ra[16], rb[16];
             const bool far = WIDE && 64 + h2 * 32 + half * 16 < n;   // the same for the whole warp
             tmem_ld16(taddr + h2 * 32, ra);
-            if (DUAL || far) tmem_ld16(taddr + 64 + h2 * 32, rb);
+            if (DUAL || far) tmem_ld16(taddr + (DUAL ? 32 : 64) + h2 * 32, rb);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float as = WIDE ? as_w[h2 * 32 + i] : m_as[ks * 32 + h2 * 16 + i];
+              const float as = WIDE ? as_w[h2 * 32 + i] : m_as[ks * NL + h2 * 16 + i];
               acc_a[h2 * 16 + i] = __fmaf_rn(__uint_as_float(ra[i]), __fmul_rn(as, wsa), acc_a[h2 * 16 + i]);
               if (DUAL) acc_b[h2 * 16 + i] = __fmaf_rn(__uint_as_float(rb[i]), __fmul_rn(as, wsb), acc_b[h2 * 16 + i]);
               if (far)
@@ -592,7 +602,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&pempty[pb]);
-        if (DENSE && p.partials != nullptr) {
+        if constexpr (DENSE) if (p.partials != nullptr) {
           const int plen = p.ksteps / p.kparts;
           if ((ks + 1) % plen == 0) {   // this part is complete: its sums leave, the accumulators start again from zero
             const int rr = mt * MROWS + q * 32 + lane;
@@ -616,7 +626,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (warp == 2 && lane == 0) TRACE(5, tile - t_lo);
 #endif
       const int r = mt * MROWS + q * 32 + lane;  // down: this lane also holds output feature r + 128
-      if (DENSE) {
+      if constexpr (DENSE) {
         // plain projection: out[token][feature] = bf16(acc)
         if (p.partials != nullptr) {
           // the parts' sums were stored as each part completed
@@ -632,7 +642,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             if (WIDE && c + 64 < n) st_global_na(o + static_cast<size_t>(row0 + c + 64) * ld, f2bf(acc_b[l]));
           }
         }
-      } else if (LM) {
+      } else if constexpr (LM) {
         // per token: the largest logit of this warp's 32 vocabulary rows and the lowest row that holds it,
         // as one packed 64-bit key per (tile, quadrant, token); a small kernel takes the max over them.
         // The maximum over the lanes is a transposing butterfly of fmaxf (31 exchanges; NaN never survives
@@ -690,11 +700,11 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if constexpr (WIDE) {
           if (64 + half * 16 < n) reduce_cols(acc_b, 64);
         }
-      } else if (UP) {
+      } else if constexpr (UP) {
         bf16* __restrict__ hout = p.h_out + static_cast<size_t>(row0) * p.I + r;
 #pragma unroll
-        for (int l = 0; l < 32; ++l) {
-          const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+        for (int l = 0; l < NL; ++l) {
+          const int c = col_of(l);
           if (c < n) {
             const float gv = rbf(acc_a[l]), uv = rbf(acc_b[l]);
             const bf16 hv = f2bf(__fmul_rn(__fdiv_rn(gv, 1.f + __expf(-gv)), uv));
@@ -704,8 +714,8 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
       } else {
 #pragma unroll
-        for (int l = 0; l < 32; ++l) {
-          const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+        for (int l = 0; l < NL; ++l) {
+          const int c = col_of(l);
           if (c < n) {  // the same for every lane of the warp
             bf16* dst = reinterpret_cast<bf16*>(__shfl_sync(FULL_MASK, reinterpret_cast<unsigned long long>(cur_dst), l));
             const float wt = __shfl_sync(FULL_MASK, cur_wt, l);

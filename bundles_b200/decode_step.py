@@ -28,6 +28,8 @@ bits as the single-GPU step: every row's arithmetic is independent of which othe
 """
 from __future__ import annotations
 
+import os
+
 import math
 import zlib
 
@@ -149,7 +151,7 @@ class DecodeStep:
         # buffers reused by every layer
         T, Ta = self.T, self.T_all
         Tm = Ta if ep is not None else T                      # rows the expert GEMMs of this rank see
-        self.lists = ops.RoutingLists(Tm, K, self.E_local, 64, dev)
+        self.lists = ops.RoutingLists(Tm, K, self.E_local, 32, dev)   # the fp8 expert GEMMs take blocks of <= 32 rows
         self.moe_ws = ops.moe_fp8_workspace(Tm, H, I, K, dev)
         self.scratch = ops.router_scratch(T, H, experts, dev)
         self.ids = torch.empty(T, K, dtype=torch.int32, device=dev)

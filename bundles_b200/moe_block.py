@@ -182,7 +182,7 @@ class MoeBlockW8A8:
 
 class MoeBlockFp8(MoeBlockW8A8):
     """fp8 e4m3 experts with 128 x 128 weight block scales and per-(token, 128-channel) activation scales."""
-    BLOCK_ROWS = 64           # the fp8 GEMMs keep their final accumulators in registers: N <= 64
+    BLOCK_ROWS = 32           # the fp8 expert GEMMs take blocks of at most 32 rows (eight partial buffers in TMEM)
 
     def _workspace(self, T, K, device):
         return ops.moe_fp8_workspace(T, self.H, self.I, K, device)

@@ -177,13 +177,13 @@ def moe_fp8_workspace(T, H, I, K, device):
 
 def moe_fp8(x, w: MoeW8A8Weights, lists: RoutingLists, cache=None, ws=None, status=None, dbg_h=None, stages=0):
     """Routed + shared expert MLPs in fp8 e4m3 with 128 x 128 block scales (weights as uint8 codes in
-    the same container as the int8 block; scales [E, rows/128, K/128]).  Lists need block_rows <= 64.
+    the same container as the int8 block; scales [E, rows/128, K/128]).  Lists need block_rows <= 32.
     Returns cache bf16 [T*(K+1), H] indexed by slot."""
     _need(x, torch.bfloat16, "x", 2)
     _need(w.w13, torch.uint8, "w13", 3)
     _need(w.w2, torch.uint8, "w2", 3)
-    if lists.block_rows > 64:
-        raise B200Error("moe_fp8 needs routing lists built with block_rows <= 64")
+    if lists.block_rows > 32:
+        raise B200Error("moe_fp8 needs routing lists built with block_rows <= 32")
     T, H = x.shape
     E, twoI, _ = w.w13.shape
     I = twoI // 2
@@ -238,8 +238,8 @@ def moe_fp8_ep(x_all, w: MoeW8A8Weights, lists: RoutingLists, peer_ptrs, rank, t
     straight into every home rank's routed cache (`peer_ptrs`: device pointers, one per rank)."""
     _need(x_all, torch.bfloat16, "x_all", 2)
     _need(w.w13, torch.uint8, "w13", 3)
-    if lists.block_rows > 64:
-        raise B200Error("moe_fp8_ep needs routing lists built with block_rows <= 64")
+    if lists.block_rows > 32:
+        raise B200Error("moe_fp8_ep needs routing lists built with block_rows <= 32")
     T, H = x_all.shape
     E, twoI, _ = w.w13.shape
     I = twoI // 2

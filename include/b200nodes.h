@@ -104,7 +104,7 @@ int b200_router_static(const void* x, const float* wr, const float* bias, int T,
  * expert's rows are [T*K, T*K + T) (slot T*K + t, i8x_decode.py:442).  Only experts in
  * [e_lo, e_lo + E_local) are listed (expert-parallel shard); tokens with pos[t] == 0 are graph
  * padding and are skipped (qk_route.cu:229,307).  `block_rows` is the largest N tile of the
- * GEMM that will consume the lists (128 for int8, 64 for fp8).
+ * GEMM that will consume the lists (128 for int8, 32 for fp8).
  */
 typedef struct b200_moe_lists {
   int32_t* counts;      /* [E_local + 1]   rows per local expert; entry E_local = shared expert */
@@ -209,14 +209,14 @@ int b200_ep_push(const void* x, const int32_t* ids, const float* wts, int T_loca
  * y = e4m3(x * (1/scale)) (fp8.py:21-34); SwiGLU rounding points as in the int8 block.
  * Same layouts with e4m3 bytes; s13 fp32 [E_local, 2I/128, H/128], s2 fp32 [E_local, H/128, I/128];
  * shared scales likewise without the expert axis.  The routing lists must have been built with
- * block_rows <= 64.  H, I multiples of 128, <= 4096. */
+ * block_rows <= 32 (a block with more rows is reported as B200_ST_BAD_LIST).  H, I multiples of 128, <= 4096. */
 size_t b200_moe_fp8_workspace_bytes(int T, int H, int I, int K);
 int b200_moe_fp8(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,
                  const b200_moe_lists* lists, void* cache, void* ws, size_t ws_bytes, void* dbg_h, int stages,
                  int32_t* status, void* stream);
 
 /* Expert-parallel form of b200_moe_fp8, as b200_moe_w8a8_ep is of b200_moe_w8a8: x holds the gathered tokens
- * of all ranks, the lists are this rank's (block_rows <= 64, shared rows for its own tokens), and the down epilogue
+ * of all ranks, the lists are this rank's (block_rows <= 32, shared rows for its own tokens), and the down epilogue
  * stores every weighted row into its home rank's cache with ordinary stores over NVLink.  (No counterpart in the
  * reference.) */
 int b200_moe_fp8_ep(const void* x, int T, int H, int I, int K, int E_local, const b200_moe_weights* w,

@@ -345,11 +345,11 @@ def test_moe_block_through_the_op_registry_equals_the_python_operators():
     K = 10
     t = torch.ops.b200nodes
     ids, wts = t.router(d["x"], d["wr"], None, K, False)
-    li, lf = t.build_lists(ids, wts, None, 0, 64, 64, True)
-    cache = t.moe_fp8(d["x"], d["w13"], d["s13"], d["w2"], d["s2"], d["sh13"], d["shs13"], d["sh2"], d["shs2"], li, lf, K, 64)
+    li, lf = t.build_lists(ids, wts, None, 0, 64, 32, True)
+    cache = t.moe_fp8(d["x"], d["w13"], d["s13"], d["w2"], d["s2"], d["sh13"], d["shs13"], d["sh2"], d["shs2"], li, lf, K, 32)
     out = t.moe_combine(cache, d["x"], d["gate_w"], K, None)
     _, ids2, wts2 = ops.router(d["x"], d["wr"], K, want_logits=False)
-    lists = ops.RoutingLists(20, K, 64, 64, dev)
+    lists = ops.RoutingLists(20, K, 64, 32, dev)
     ops.build_lists(ids2, wts2, lists)
     w = ops.MoeW8A8Weights(d["w13"], d["s13"], d["w2"], d["s2"], d["sh13"], d["shs13"], d["sh2"], d["shs2"])
     want = ops.moe_combine(ops.moe_fp8(d["x"], w, lists), d["x"], d["gate_w"], K)

@@ -63,7 +63,7 @@ def test_fp8_gemm_winds_down_when_its_stages_never_fill(short_budget):
     cfg = synth.moe_fp8(seed=32, T=8, E=64)
     d = {k: (v.to(dev()) if isinstance(v, torch.Tensor) else v) for k, v in cfg.items()}
     _, ids, wts = ops.router(d["x"], d["wr"], 10)
-    lists = ops.RoutingLists(8, 10, 64, 64, dev())
+    lists = ops.RoutingLists(8, 10, 64, 32, dev())
     ops.build_lists(ids, wts, lists)
     w = ops.MoeW8A8Weights(d["w13"], d["s13"], d["w2"], d["s2"], d["sh13"], d["shs13"], d["sh2"], d["shs2"])
     st = ops.new_status(dev())

@@ -13,7 +13,7 @@ from tests.util import bf16_to_np, close_bf16, dev
 pytestmark = pytest.mark.gpu
 
 
-def _run(cfg, K, pos=None, block_rows=64):
+def _run(cfg, K, pos=None, block_rows=32):
     T, H = cfg["x"].shape
     E = cfg["wr"].shape[0]
     I = cfg["w2"].shape[-1]
@@ -31,7 +31,7 @@ def _run(cfg, K, pos=None, block_rows=64):
     return ids.cpu().numpy(), wts.cpu().numpy(), bf16_to_np(hd), bf16_to_np(cache), bf16_to_np(out)
 
 
-def _check(cfg, K, pos=None, block_rows=64):
+def _check(cfg, K, pos=None, block_rows=32):
     ids, wts, h, cache, out = _run(cfg, K, pos, block_rows)
     _, ref_ids, _ = orouter.route(bf16_to_np(cfg["x"]), cfg["wr"].numpy(), K)
     assert np.array_equal(ids, ref_ids)
