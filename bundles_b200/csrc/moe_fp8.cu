@@ -22,6 +22,7 @@ constexpr int F8_TILE = 128 * 128;       // weight tile bytes per stage
 constexpr int F8_BTILE = 64 * 128;       // token tile bytes per stage, dense modes (<= 64 rows)
 constexpr int F8_BTILE_MOE = 32 * 128;   // the same in the expert GEMMs (blocks of <= 32 rows)
 constexpr int F8_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
+constexpr int F8_THREADS_WIDE = 576;     // the same with 16 epilogue warps (four per quadrant, 32 columns each)
 constexpr int F8_CACHED = 1024;          // blocks of the list whose entries every CTA of a MoE GEMM keeps in shared memory
 constexpr int F8_MAXKG = 32;             // k blocks per row of scales held in shared memory (K <= 4096)
 constexpr int F8_WS_FLOATS = 1024;       // weight block scales of the CTA's first tiles, cached in shared memory
@@ -144,8 +145,10 @@ struct F8Cfg {
   static constexpr int PW = WIDE ? 128 : 64;
   static constexpr int NPB = 512 / PW;       // partial buffers
   static constexpr int NL = DUAL ? 16 : 32;  // columns (token rows) of a tile that one epilogue warp owns
+  static constexpr int THREADS = WIDE ? F8_THREADS_WIDE : F8_THREADS;
+  static constexpr int EPI_WARPS = (THREADS - 64) / 32;
   static constexpr int META_WARP = (WIDE ? 0 : NL * F8_MAXKG * 4) + 32 * 8 + 2 * F8_MAXKG * 4;
-  static constexpr int META = 8 * META_WARP;  // per epilogue warp: activation scales, slot, weight of its 32 columns, weight scales
+  static constexpr int META = EPI_WARPS * META_WARP;  // per epilogue warp: activation scales, slot, weight of its 32 columns, weight scales
   static constexpr bool LISTS = MODE == MODE_UP || MODE == MODE_DOWN;
   static constexpr int TINFO = LISTS ? F8_CACHED * 12 + (F8_CACHED + 32) * 4 : 64;  // block entries + cost prefix
   static constexpr int SMEM = STAGES * STAGE + 1024 + 256 + META + TINFO + F8_WS_FLOATS * 4 + (WIDE ? F8_AS_FLOATS * 4 : 0);
@@ -163,7 +166,7 @@ __device__ unsigned long long g_cta[256][4];
 #endif
 
 template <int MODE>
-__global__ void __launch_bounds__(F8_THREADS, 1)
+__global__ void __launch_bounds__(F8Cfg<MODE>::THREADS, 1)
 moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWsh,
                    const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmX64, const F8Args p) {
   using C = F8Cfg<MODE>;
@@ -197,7 +200,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
     for (int b = 0; b < C::NPB; ++b) {
       mbar_init(&pfull[b], 1);
-      mbar_init(&pempty[b], 8);
+      mbar_init(&pempty[b], C::EPI_WARPS);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -226,7 +229,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   auto k0_of = [&](int tile) { return DENSE ? ((tile / nblocks) % p.ksplit) * kn : 0; };
   if (C::LISTS) {
     const int ncached = nblocks < F8_CACHED ? nblocks : F8_CACHED;
-    for (int blk = threadIdx.x; blk < ncached; blk += F8_THREADS) {
+    for (int blk = threadIdx.x; blk < ncached; blk += C::THREADS) {
       tinfo[blk * 3 + 0] = p.L.blk_expert[blk];
       tinfo[blk * 3 + 1] = p.L.blk_row0[blk];
       tinfo[blk * 3 + 2] = p.L.blk_rows[blk];
@@ -306,7 +309,9 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   };
   const int ep_half = (warp - 2) >> 2;
   // tile column of an epilogue warp's local column l: the two warps of a lane quadrant take alternate 16-column chunks
-  auto col_of = [&](int l) { return DUAL ? ep_half * 16 + l : (l >> 4) * 32 + ep_half * 16 + (l & 15); };
+  auto col_of = [&](int l) {
+    return DUAL ? ep_half * 16 + l : WIDE ? ep_half * 32 + l : (l >> 4) * 32 + ep_half * 16 + (l & 15);
+  };
   auto fetch = [&](int tile, Meta& m) {  // the metadata of the block that `tile` belongs to
     m.wt = 0.f;
     m.slot = -1;
@@ -454,9 +459,11 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   } else {
-    // ---------------- promotion + epilogue: warps 2..9.  TMEM lane quadrant = warp % 4; the two warps of a
-    // quadrant share a scheduler and take alternate 16-column chunks (chunk index parity = `half`), so each
-    // thread keeps at most 32 (+32 for up) accumulators ----------------
+    // ---------------- promotion + epilogue: warps 2 and up.  TMEM lane quadrant = warp % 4; the warps of a
+    // quadrant share a scheduler and split the tile's columns among them (`half` = which share): two warps with
+    // alternate 16-column chunks, or four with 32 consecutive columns each in the wide modes, where the promotion
+    // of 128 columns per k block is what paces the kernel and four warps per scheduler hide its latencies.  A
+    // thread keeps at most 32 accumulators (16 + 16 in the expert GEMMs) ----------------
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     float* m_as = reinterpret_cast<float*>(meta + (warp - 2) * C::META_WARP);  // [ksteps][NL]
@@ -512,7 +519,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     };
     int staged_blk = -1;
-    for (int idx = static_cast<int>(threadIdx.x) - 64; idx < ws_ncache * ws_per_tile; idx += F8_THREADS - 64) {
+    for (int idx = static_cast<int>(threadIdx.x) - 64; idx < ws_ncache * ws_per_tile; idx += C::THREADS - 64) {
       const int ti = idx / ws_per_tile, rem = idx - ti * ws_per_tile;
       const int which = rem / p.ksteps, ks = rem - which * p.ksteps;
       int e, row0, n, mt;
@@ -526,12 +533,12 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
     if (WIDE) {   // lane -> row, so the shared-memory writes of a warp fall in consecutive banks
       const int et = static_cast<int>(threadIdx.x) - 64;
-      for (int idx = et; idx < tpad * p.ksteps; idx += F8_THREADS - 64) {
+      for (int idx = et; idx < tpad * p.ksteps; idx += C::THREADS - 64) {
         const int ks = idx / tpad, row = idx - ks * tpad;
         as_all[idx] = row < p.total_rows ? a_scale[static_cast<size_t>(row) * p.ksteps + ks] : 0.f;
       }
     }
-    asm volatile("bar.sync 1, 256;" ::: "memory");  // the epilogue warps' fill of ws_cache (and as_all) is complete
+    asm volatile("bar.sync 1, %0;" ::"n"(C::THREADS - 64) : "memory");  // the epilogue warps' fill of ws_cache (and as_all) is complete
     for (int tile = t_lo; ok && tile < t_hi; ++tile) {
       int e, row0, n, mt;
       const bool cached = tile - t_lo < ws_ncache;
@@ -563,10 +570,10 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const float* __restrict__ wsc_a = cached ? ws_cache + (tile - t_lo) * ws_per_tile : m_ws;
       const float* __restrict__ wsc_b = cached ? wsc_a + p.ksteps : m_ws + F8_MAXKG;
       if (warp == 2 && lane == 0) TRACE(3, 2 + 2 * ((tile - t_lo)));
-      float acc_a[NL], acc_b[(DUAL || WIDE) ? NL : 1];   // wide: acc_b holds the columns 64 further
+      float acc_a[NL], acc_b[DUAL ? NL : 1];
 #pragma unroll
       for (int c = 0; c < NL; ++c) acc_a[c] = 0.f;
-      if (DUAL || WIDE)
+      if (DUAL)
 #pragma unroll
         for (int c = 0; c < NL; ++c) acc_b[c] = 0.f;
       const int kfirst = k0_of(tile);
@@ -579,23 +586,22 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
         tc_fence_after();
         if (warp == 2 && lane == 0) TRACE(2, g);
-        const uint32_t taddr = tmem_base + pb * C::PW + half * 16 + (static_cast<uint32_t>(q * 32) << 16);
-        const float* __restrict__ as_w = as_all + ks * tpad + row0 + half * 16;   // wide: scales of this warp's columns
+        // chunk h2 (16 columns) of this warp sits at TMEM column tcol(h2) of the partial
+        const uint32_t taddr = tmem_base + pb * C::PW + (static_cast<uint32_t>(q * 32) << 16);
+        const float* __restrict__ as_w = as_all + ks * tpad + row0 + half * 32;   // wide: scales of this warp's columns
 #pragma unroll
         for (int h2 = 0; h2 < NH2; ++h2) {
-          if (h2 * 32 + half * 16 < n) {
+          const int tcol = WIDE ? half * 32 + h2 * 16 : half * 16 + h2 * 32;
+          if (tcol < n) {   // the same for the whole warp
             uint32_t ra[16], rb[16];
-            const bool far = WIDE && 64 + h2 * 32 + half * 16 < n;   // the same for the whole warp
-            tmem_ld16(taddr + h2 * 32, ra);
-            if (DUAL || far) tmem_ld16(taddr + (DUAL ? 32 : 64) + h2 * 32, rb);
+            tmem_ld16(taddr + tcol, ra);
+            if (DUAL) tmem_ld16(taddr + 32 + tcol, rb);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float as = WIDE ? as_w[h2 * 32 + i] : m_as[ks * NL + h2 * 16 + i];
+              const float as = WIDE ? as_w[h2 * 16 + i] : m_as[ks * NL + h2 * 16 + i];
               acc_a[h2 * 16 + i] = __fmaf_rn(__uint_as_float(ra[i]), __fmul_rn(as, wsa), acc_a[h2 * 16 + i]);
               if (DUAL) acc_b[h2 * 16 + i] = __fmaf_rn(__uint_as_float(rb[i]), __fmul_rn(as, wsb), acc_b[h2 * 16 + i]);
-              if (far)
-                acc_b[h2 * 16 + i] = __fmaf_rn(__uint_as_float(rb[i]), __fmul_rn(as_w[64 + h2 * 32 + i], wsa), acc_b[h2 * 16 + i]);
             }
           }
         }
@@ -609,13 +615,9 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             float* __restrict__ o = p.partials + (static_cast<size_t>(ks / plen) * p.total_rows + row0) * p.w_rows + rr;
 #pragma unroll
             for (int l = 0; l < 32; ++l) {
-              const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+              const int c = col_of(l);
               if (c < n && rr < p.w_rows) st_global_na(o + static_cast<size_t>(c) * p.w_rows, acc_a[l]);
               acc_a[l] = 0.f;
-              if (WIDE) {
-                if (c + 64 < n && rr < p.w_rows) st_global_na(o + static_cast<size_t>(c + 64) * p.w_rows, acc_b[l]);
-                acc_b[l] = 0.f;
-              }
             }
           }
         }
@@ -637,9 +639,8 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           const size_t ld = static_cast<size_t>(p.seg_ld[sg]);
 #pragma unroll
           for (int l = 0; l < 32; ++l) {
-            const int c = (l >> 4) * 32 + half * 16 + (l & 15);
+            const int c = col_of(l);
             if (c < n) st_global_na(o + static_cast<size_t>(row0 + c) * ld, f2bf(acc_a[l]));
-            if (WIDE && c + 64 < n) st_global_na(o + static_cast<size_t>(row0 + c + 64) * ld, f2bf(acc_b[l]));
           }
         }
       } else if constexpr (LM) {
@@ -649,13 +650,13 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         // against a number, -0 and +0 compare equal), after which lane l holds local column l; the row
         // comes from a ballot of the lanes whose value equals the maximum.
         const bool live = r < p.w_rows;
-        auto reduce_cols = [&](const float* acc, int cofs) {   // the 32 columns of `acc`, tile columns cofs further
+        auto reduce_cols = [&](const float* acc) {
           float mv[32];
 #pragma unroll
           for (int l = 0; l < 32; ++l) {
             mv[l] = live ? acc[l] : __int_as_float(0x7fc00000);
             if (p.lm_logits && live) {
-              const int c = cofs + (l >> 4) * 32 + half * 16 + (l & 15);
+              const int c = col_of(l);
               if (c < n) st_global_na(p.lm_logits + static_cast<size_t>(row0 + c) * p.lm_ld + r, acc[l]);
             }
           }
@@ -679,7 +680,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
           const uint32_t live_mask = __ballot_sync(FULL_MASK, live);
           {
-            const int c = cofs + (lane >> 4) * 32 + half * 16 + (lane & 15);
+            const int c = col_of(lane);
             if (c < n) {
               unsigned long long key = 0ull;  // no live row
               const int base_id = p.lm_shard_lo + mt * 128 + q * 32;
@@ -696,10 +697,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             }
           }
         };
-        reduce_cols(acc_a, 0);
-        if constexpr (WIDE) {
-          if (64 + half * 16 < n) reduce_cols(acc_b, 64);
-        }
+        reduce_cols(acc_a);
       } else if constexpr (UP) {
         bf16* __restrict__ hout = p.h_out + static_cast<size_t>(row0) * p.I + r;
 #pragma unroll
@@ -969,7 +967,7 @@ static void launch_dense(bool wide, int grid, const CUtensorMap& tmW, const CUte
     cudaFuncSetAttribute(moe_gemm_f8_kernel<WIDEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<WIDEM>::SMEM);
   });
   if (wide)
-    moe_gemm_f8_kernel<WIDEM><<<grid, F8_THREADS, F8Cfg<WIDEM>::SMEM, st>>>(tmW, tmW, tmX, tmXbox, a);
+    moe_gemm_f8_kernel<WIDEM><<<grid, F8Cfg<WIDEM>::THREADS, F8Cfg<WIDEM>::SMEM, st>>>(tmW, tmW, tmX, tmXbox, a);
   else
     moe_gemm_f8_kernel<NARROW><<<grid, F8_THREADS, F8Cfg<NARROW>::SMEM, st>>>(tmW, tmW, tmX, tmXbox, a);
 }
