@@ -386,17 +386,17 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
           uint8_t* sA = smem + stage * C::STAGE;
           uint8_t* sB = sA + C::NA * F8_TILE;
-          // every TMA instruction costs the issuing thread ~80 ns: more than 32 token rows come as one 64-row
-          // box (rows past the block belong to the next expert or are zero-filled past the end; the MMA's N
-          // ignores them) instead of three or four 16-row boxes
-          mbar_expect_tx(&full[stage], C::NA * F8_TILE + (WIDE ? F8_TILE : (!DUAL && nb16 > 2) ? F8_BTILE : nb16 * 2048));
+          // every TMA instruction costs the issuing thread about 100 ns: more than 16 token rows come as ONE box of
+          // the mode's largest size (rows past the block belong to the next expert or are zero-filled past the end;
+          // the MMA's N ignores them)
+          mbar_expect_tx(&full[stage], C::NA * F8_TILE + (WIDE ? F8_TILE : nb16 == 1 ? 2048 : DUAL ? F8_BTILE_MOE : F8_BTILE));
           tma_load_2d(sA, mapW, ks * 128, wrow, &full[stage]);
           if (DUAL) tma_load_2d(sA + F8_TILE, mapW, ks * 128, wrow + (UP ? p.I : 128), &full[stage]);
           if (p.test_starve) {
-          } else if (WIDE || (!DUAL && nb16 > 2)) {   // wide modes: tmX64 carries a 128-row box
+          } else if (WIDE || nb16 > 1) {   // tmX64 carries the mode's largest box: 128 rows (wide), 32 (expert GEMMs), 64
             tma_load_2d(sB, &tmX64, ks * 128, row0, &full[stage]);
           } else {
-            for (int b = 0; b < nb16; ++b) tma_load_2d(sB + b * 2048, &tmX, ks * 128, row0 + 16 * b, &full[stage]);
+            tma_load_2d(sB, &tmX, ks * 128, row0, &full[stage]);
           }
           TRACE(0, issued);
           ++issued;
@@ -811,11 +811,11 @@ static int moe_fp8_impl(const void* x, int T, int H, int I, int K, int E_local, 
   if ((rc = make_tmap_bytes_2d(&tmW13, w->w13, static_cast<uint64_t>(E_local) * 2 * I, H, 128, "w13"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmSh13, shared ? w->sh13 : w->w13, 2 * I, H, 128, "sh13"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmXq, xq, rows, H, 16, "xq"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmXq64, xq, rows, H, 64, "xq"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmXq64, xq, rows, H, 32, "xq"))) return rc;   // the largest block: 32 rows
   if ((rc = make_tmap_bytes_2d(&tmW2, w->w2, static_cast<uint64_t>(E_local) * H, I, 128, "w2"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmSh2, shared ? w->sh2 : w->w2, H, I, 128, "sh2"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmHq, hq, rows, I, 16, "hq"))) return rc;
-  if ((rc = make_tmap_bytes_2d(&tmHq64, hq, rows, I, 64, "hq"))) return rc;
+  if ((rc = make_tmap_bytes_2d(&tmHq64, hq, rows, I, 32, "hq"))) return rc;
   static DeviceOnce once;
   once.run([] {
     cudaFuncSetAttribute(moe_gemm_f8_kernel<MODE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Cfg<MODE_UP>::SMEM);
