@@ -843,7 +843,7 @@ def run_step(args, rank, world, local, dev):
 
 # DRAM bytes (read + write) of one launch of moe_gemm_f8_kernel<UP> divided by its algorithmic bytes, from the ncu
 # capture summarised in profiles/moe_fp8_up_down_t256.md (1.1077 GB read + 12.5 MB written for 1.0786 GB)
-F8_UP_TRAFFIC_RATIO = 1.0385
+F8_UP_TRAFFIC_RATIO = 1.032
 
 
 
