@@ -51,6 +51,10 @@ PROTOTYPES = {
     "b200_dense_fp8_add_rmsnorm": (i32, [vp, i32, i32, vp, vp, i32, vp, vp, f32, vp, vp, vp, sz, vp, vp]),
     "b200_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "b200_moe_combine_norm": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, f32, vp, vp]),
+    "b200_moe_combine_norm_q": (i32, [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, f32, vp, vp, vp, vp]),
+    "b200_dense_fp8_split_q": (i32, [vp, vp, i32, i32, vp, vp, i32, i32, C.POINTER(i32), C.POINTER(vp), C.POINTER(i32), vp,
+                                     vp]),
+    "b200_attn_front_q": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, f32, i32, vp, vp, vp, vp, vp, vp]),
     "b200_attn_front_workspace_bytes": (sz, [i32]),
     "b200_attn_front": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, i32, f32, i32, vp, vp, vp, vp, vp, sz, vp, vp]),
     "b200_attn_verify_splits": (i32, [i32]),

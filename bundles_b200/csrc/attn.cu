@@ -307,33 +307,56 @@ extern "C" size_t b200_attn_front_workspace_bytes(int T) {
   return up(static_cast<size_t>(T) * AT_H) + up(static_cast<size_t>(T) * AT_KS * 4);
 }
 
-extern "C" int b200_attn_front(const void* x, int T, const void* w, const float* w_s, const void* q_norm_w,
-                               const void* k_norm_w, const int64_t* positions, const float* cos_sin, int max_pos,
-                               float eps, int out_fp8, void* q, void* gate, void* k, void* v, void* ws,
-                               size_t ws_bytes, int32_t* status, void* stream) {
-  if (!x || !w || !w_s || !q_norm_w || !k_norm_w || !positions || !cos_sin || !q || !gate || !k || !v || !ws)
+// `x` bf16 rows quantised here into `ws`, or (x == nullptr) rows that arrive as e4m3 `xq_in` + scales `xs_in`
+static int attn_front_impl(const void* x, const void* xq_in, const float* xs_in, int T, const void* w, const float* w_s,
+                           const void* q_norm_w, const void* k_norm_w, const int64_t* positions, const float* cos_sin,
+                           int max_pos, float eps, int out_fp8, void* q, void* gate, void* k, void* v, void* ws,
+                           size_t ws_bytes, int32_t* status, void* stream) {
+  const bool pre = x == nullptr;
+  if ((!pre && !ws) || (pre && (!xq_in || !xs_in)) || !w || !w_s || !q_norm_w || !k_norm_w || !positions || !cos_sin || !q ||
+      !gate || !k || !v)
     return fail(B200_E_ARG, "b200_attn_front: null pointer");
   if (T <= 0 || max_pos <= 0) return fail(B200_E_ARG, "b200_attn_front: bad shape (T=%d max_pos=%d)", T, max_pos);
-  if (ws_bytes < b200_attn_front_workspace_bytes(T))
+  if (!pre && ws_bytes < b200_attn_front_workspace_bytes(T))
     return fail(B200_E_WS, "b200_attn_front: workspace %zu < %zu bytes", ws_bytes, b200_attn_front_workspace_bytes(T));
-  if (reinterpret_cast<uintptr_t>(ws) & 1023) return fail(B200_E_ALIGN, "b200_attn_front: workspace must be 1024-byte aligned");
-  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(gate) |
+  if (!pre && (reinterpret_cast<uintptr_t>(ws) & 1023))
+    return fail(B200_E_ALIGN, "b200_attn_front: workspace must be 1024-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(pre ? xq_in : x) | reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(gate) |
        reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(cos_sin)) & 15)
     return fail(B200_E_ALIGN, "b200_attn_front: x, q, gate, k, v and cos_sin must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  uint8_t* xq = static_cast<uint8_t*>(ws);
-  float* xs = reinterpret_cast<float*>(xq + ((static_cast<size_t>(T) * AT_H + 1023) & ~size_t(1023)));
+  const uint8_t* xq = pre ? static_cast<const uint8_t*>(xq_in) : static_cast<uint8_t*>(ws);
+  const float* xs = pre ? xs_in
+                        : reinterpret_cast<float*>(static_cast<uint8_t*>(ws) +
+                                                   ((static_cast<size_t>(T) * AT_H + 1023) & ~size_t(1023)));
   CUtensorMap tmX, tmW;
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmX, xq, T, AT_H, 128, "attn activations"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, AT_NCOLS, AT_H, 128, "attn weight"))) return rc;
   static DeviceOnce once;
   once.run([] { cudaFuncSetAttribute(attn_front_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM); });
-  b200::b200_quant_rows_f8_launch(x, T, AT_H, xq, xs, st);
+  if (!pre) b200::b200_quant_rows_f8_launch(x, T, AT_H, const_cast<uint8_t*>(xq), const_cast<float*>(xs), st);
   AttnArgs a{xs, w_s, static_cast<const bf16*>(q_norm_w), static_cast<const bf16*>(k_norm_w), positions, cos_sin,
              max_pos, eps, T, out_fp8, q, static_cast<bf16*>(gate), k, v, status};
   const int ntiles = ((T + 127) / 128) * AT_NT;
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
   attn_front_kernel<<<grid, AT_THREADS, AT_SMEM, st>>>(tmX, tmW, a);
   return launch_status("b200_attn_front");
+}
+
+extern "C" int b200_attn_front(const void* x, int T, const void* w, const float* w_s, const void* q_norm_w,
+                               const void* k_norm_w, const int64_t* positions, const float* cos_sin, int max_pos,
+                               float eps, int out_fp8, void* q, void* gate, void* k, void* v, void* ws,
+                               size_t ws_bytes, int32_t* status, void* stream) {
+  if (!x) return fail(B200_E_ARG, "b200_attn_front: null pointer");
+  return attn_front_impl(x, nullptr, nullptr, T, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, max_pos, eps, out_fp8, q,
+                         gate, k, v, ws, ws_bytes, status, stream);
+}
+
+extern "C" int b200_attn_front_q(const void* xq, const float* xs, int T, const void* w, const float* w_s,
+                                 const void* q_norm_w, const void* k_norm_w, const int64_t* positions,
+                                 const float* cos_sin, int max_pos, float eps, int out_fp8, void* q, void* gate, void* k,
+                                 void* v, int32_t* status, void* stream) {
+  return attn_front_impl(nullptr, xq, xs, T, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, max_pos, eps, out_fp8, q, gate,
+                         k, v, nullptr, 0, status, stream);
 }

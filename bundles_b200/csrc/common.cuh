@@ -57,6 +57,17 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
   return e4m3x2(a, b) | (e4m3x2(c, d) << 16);
 }
 
+// ---- e4m3 activation quantisation of 8 bf16 values -----------------------------------------------
+// scale = max(amax / 448, 1e-12), y = e4m3(x * (1 / scale)) per (row, 128-channel group): fp8.py:21-34.
+__device__ __forceinline__ uint2 quant8_e4m3(const uint4 v, float inv) {
+  return make_uint2(e4m3x4(bf_lo(v.x) * inv, bf_hi(v.x) * inv, bf_lo(v.y) * inv, bf_hi(v.y) * inv),
+                    e4m3x4(bf_lo(v.z) * inv, bf_hi(v.z) * inv, bf_lo(v.w) * inv, bf_hi(v.w) * inv));
+}
+__device__ __forceinline__ float amax8(const uint4 v) {
+  float a = fmaxf(fmaxf(fabsf(bf_lo(v.x)), fabsf(bf_hi(v.x))), fmaxf(fabsf(bf_lo(v.y)), fabsf(bf_hi(v.y))));
+  return fmaxf(a, fmaxf(fmaxf(fabsf(bf_lo(v.z)), fabsf(bf_hi(v.z))), fmaxf(fabsf(bf_lo(v.w)), fabsf(bf_hi(v.w)))));
+}
+
 // Global stores that the compiler need not order against the C++ loads around them (no "memory" clobber): an
 // epilogue that reads its row metadata from shared memory and stores through pointers it also read from there
 // would otherwise reload after every store (a generic pointer may alias shared memory), one dependent

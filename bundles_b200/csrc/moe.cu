@@ -606,7 +606,8 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const bf16* __res
                                                                const int64_t* __restrict__ pos, int T, int H, int K,
                                                                bf16* __restrict__ out, bf16* __restrict__ residual,
                                                                const bf16* __restrict__ norm_w, float eps,
-                                                               bf16* __restrict__ normed) {
+                                                               bf16* __restrict__ normed, uint8_t* __restrict__ xq_out,
+                                                               float* __restrict__ xs_out) {
   __shared__ float red[8], red2[8];
   const int t = blockIdx.x, tid = threadIdx.x;
   pdl_wait();
@@ -682,8 +683,18 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const bf16* __res
     float y[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) y[i] = r[i] * rstd * (1.f + gwn[i]);
-    *reinterpret_cast<uint4*>(normed + static_cast<size_t>(t) * H + c) =
-        make_uint4(pack_bf2(y[0], y[1]), pack_bf2(y[2], y[3]), pack_bf2(y[4], y[5]), pack_bf2(y[6], y[7]));
+    const uint4 y4 = make_uint4(pack_bf2(y[0], y[1]), pack_bf2(y[2], y[3]), pack_bf2(y[4], y[5]), pack_bf2(y[6], y[7]));
+    *reinterpret_cast<uint4*>(normed + static_cast<size_t>(t) * H + c) = y4;
+    if (xq_out != nullptr) {
+      // the normed row also leaves in the e4m3 form the next projection reads (the arithmetic of
+      // quant_permute_f8_kernel: 16 consecutive threads own one 128-channel group)
+      float amax = amax8(y4);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(FULL_MASK, amax, o));
+      const float scale = fmaxf(__fdiv_rn(amax, 448.f), 1e-12f);
+      *reinterpret_cast<uint2*>(xq_out + static_cast<size_t>(t) * H + c) = quant8_e4m3(y4, __fdiv_rn(1.f, scale));
+      if ((tid & 15) == 0) xs_out[static_cast<size_t>(t) * (H / 128) + (c >> 7)] = scale;
+    }
     return;
   }
   float gate = 0.f;
@@ -956,18 +967,34 @@ extern "C" int b200_moe_combine(const void* cache, const void* x, const void* ga
   return launch_status("b200_moe_combine");
 }
 
-extern "C" int b200_moe_combine_norm(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T, int H,
-                                     int K, void* out, void* residual, const void* norm_w, float eps, void* normed,
-                                     void* stream) {
+static int combine_norm_impl(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T, int H, int K,
+                             void* out, void* residual, const void* norm_w, float eps, void* normed, void* xq_out,
+                             float* xs_out, void* stream) {
   if (!cache || !x || !residual || !norm_w || !normed) return fail(B200_E_ARG, "b200_moe_combine_norm: null pointer");
   if (T < 0 || H <= 0 || H % 8 || K <= 0)
     return fail(B200_E_ARG, "b200_moe_combine_norm: need H %% 8 == 0 (H=%d K=%d)", H, K);
+  if ((xq_out != nullptr) != (xs_out != nullptr) || (xq_out != nullptr && (H != 2048 || K > 12)))
+    return fail(B200_E_ARG, "b200_moe_combine_norm_q: the quantised row needs both outputs, H == 2048 and K <= 12 (H=%d K=%d)",
+                H, K);
   if (T == 0) return 0;
   launch_k(moe_combine_norm_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream),
            static_cast<const bf16*>(cache), static_cast<const bf16*>(x), static_cast<const bf16*>(gate_w), pos, T, H, K,
            static_cast<bf16*>(out), static_cast<bf16*>(residual), static_cast<const bf16*>(norm_w), eps,
-           static_cast<bf16*>(normed));
+           static_cast<bf16*>(normed), static_cast<uint8_t*>(xq_out), xs_out);
   return launch_status("b200_moe_combine_norm");
+}
+
+extern "C" int b200_moe_combine_norm(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T, int H,
+                                     int K, void* out, void* residual, const void* norm_w, float eps, void* normed,
+                                     void* stream) {
+  return combine_norm_impl(cache, x, gate_w, pos, T, H, K, out, residual, norm_w, eps, normed, nullptr, nullptr, stream);
+}
+
+extern "C" int b200_moe_combine_norm_q(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T,
+                                       int H, int K, void* out, void* residual, const void* norm_w, float eps,
+                                       void* normed, void* xq_out, float* xs_out, void* stream) {
+  if (!xq_out || !xs_out) return fail(B200_E_ARG, "b200_moe_combine_norm_q: null pointer");
+  return combine_norm_impl(cache, x, gate_w, pos, T, H, K, out, residual, norm_w, eps, normed, xq_out, xs_out, stream);
 }
 
 extern "C" int b200_ep_push(const void* x, const int32_t* ids, const float* wts, int T_local, int H, int K, int ep_rank,

@@ -27,17 +27,7 @@ constexpr int F8_CACHED = 1024;          // blocks of the list whose entries eve
 constexpr int F8_MAXKG = 32;             // k blocks per row of scales held in shared memory (K <= 4096)
 constexpr int F8_WS_FLOATS = 1024;       // weight block scales of the CTA's first tiles, cached in shared memory
 
-// ---- activation quantisers ----------------------------------------------------------------------------
-// scale = max(amax / 448, 1e-12), y = e4m3(x * (1 / scale)) per (row, 128-channel group): fp8.py:21-34.
-__device__ __forceinline__ uint2 quant8_e4m3(const uint4 v, float inv) {
-  return make_uint2(e4m3x4(bf_lo(v.x) * inv, bf_hi(v.x) * inv, bf_lo(v.y) * inv, bf_hi(v.y) * inv),
-                    e4m3x4(bf_lo(v.z) * inv, bf_hi(v.z) * inv, bf_lo(v.w) * inv, bf_hi(v.w) * inv));
-}
-__device__ __forceinline__ float amax8(const uint4 v) {
-  float a = fmaxf(fmaxf(fabsf(bf_lo(v.x)), fabsf(bf_hi(v.x))), fmaxf(fabsf(bf_lo(v.y)), fabsf(bf_hi(v.y))));
-  return fmaxf(a, fmaxf(fmaxf(fabsf(bf_lo(v.z)), fabsf(bf_hi(v.z))), fmaxf(fabsf(bf_lo(v.w)), fabsf(bf_hi(v.w)))));
-}
-
+// ---- activation quantisers (quant8_e4m3 / amax8: common.cuh) ----
 // one CTA per token; 16 consecutive threads own one 128-channel group (8 channels each)
 // tokens [shared_lo, shared_lo + shared_n) also get their shared-expert row T*K + t
 __global__ void __launch_bounds__(256) quant_permute_f8_kernel(const bf16* __restrict__ x, int T, int H, int K,
@@ -1090,10 +1080,12 @@ extern "C" size_t b200_dense_fp8_workspace_bytes(int T, int H) {
   return up(static_cast<size_t>(T < 64 ? 64 : T) * H) + up(static_cast<size_t>(T) * (H / 128) * 4);
 }
 
-extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, const float* w_s, int N, int nseg,
-                                    const int* seg_cols_host, void* const* seg_out_host, const int* seg_ld_host, void* ws,
-                                    size_t ws_bytes, int32_t* status, void* stream) {
-  if (!x || !w || !w_s || !seg_cols_host || !seg_out_host || !seg_ld_host || !ws)
+// `x` bf16 rows quantised here into `ws`, or (x == nullptr) rows that arrive as e4m3 `xq_in` + scales `xs_in`
+static int dense_split_impl(const void* x, const void* xq_in, const float* xs_in, int T, int H, const void* w,
+                            const float* w_s, int N, int nseg, const int* seg_cols_host, void* const* seg_out_host,
+                            const int* seg_ld_host, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  const bool pre = x == nullptr;
+  if ((!pre && !ws) || (pre && (!xq_in || !xs_in)) || !w || !w_s || !seg_cols_host || !seg_out_host || !seg_ld_host)
     return fail(B200_E_ARG, "b200_dense_fp8: null pointer");
   if (T <= 0 || H <= 0 || H % 128 || H / 128 > F8_MAXKG || N <= 0 || nseg < 1 || nseg > 4)
     return fail(B200_E_ARG, "b200_dense_fp8: need T >= 1, H %% 128 == 0, H <= 4096, 1 <= segments <= 4 (T=%d H=%d N=%d)", T,
@@ -1107,19 +1099,26 @@ extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, 
     lo += seg_cols_host[i];
   }
   if (lo != N) return fail(B200_E_ARG, "b200_dense_fp8: segment widths add up to %d, N = %d", lo, N);
-  if (ws_bytes < b200_dense_fp8_workspace_bytes(T, H))
+  if (!pre && ws_bytes < b200_dense_fp8_workspace_bytes(T, H))
     return fail(B200_E_WS, "b200_dense_fp8: workspace %zu < %zu bytes", ws_bytes, b200_dense_fp8_workspace_bytes(T, H));
-  if (reinterpret_cast<uintptr_t>(ws) & 1023) return fail(B200_E_ALIGN, "b200_dense_fp8: workspace must be 1024-byte aligned");
+  if (!pre && (reinterpret_cast<uintptr_t>(ws) & 1023))
+    return fail(B200_E_ALIGN, "b200_dense_fp8: workspace must be 1024-byte aligned");
+  if (pre && (reinterpret_cast<uintptr_t>(xq_in) & 15))
+    return fail(B200_E_ALIGN, "b200_dense_fp8_split_q: the e4m3 rows must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  uint8_t* xq = static_cast<uint8_t*>(ws);
-  float* xs = reinterpret_cast<float*>(xq + ((static_cast<size_t>(T < 64 ? 64 : T) * H + 1023) & ~size_t(1023)));
+  const uint8_t* xq = pre ? static_cast<const uint8_t*>(xq_in) : static_cast<uint8_t*>(ws);
+  const float* xs = pre ? xs_in
+                        : reinterpret_cast<float*>(static_cast<uint8_t*>(ws) +
+                                                   ((static_cast<size_t>(T < 64 ? 64 : T) * H + 1023) & ~size_t(1023)));
   CUtensorMap tmW, tmX, tmX64;
   int rc;
   if ((rc = make_tmap_bytes_2d(&tmW, w, static_cast<uint64_t>(N), H, 128, "dense weight"))) return rc;
   if ((rc = make_tmap_bytes_2d(&tmX, xq, T, H, 16, "dense activations"))) return rc;
   const bool wide = dense_wide(T, H);
   if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, wide ? 128 : 64, "dense activations"))) return rc;
-  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, xq, xs);
+  if (!pre)
+    quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, const_cast<uint8_t*>(xq),
+                                               const_cast<float*>(xs));
   F8Args a{};
   a.E_local = 1;
   a.mtiles = (N + 127) / 128;
@@ -1146,6 +1145,21 @@ extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, 
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
   launch_dense<MODE_DENSE, MODE_DENSE_W>(wide, grid, tmW, tmX, tmX64, a, st);
   return launch_status("b200_dense_fp8");
+}
+
+extern "C" int b200_dense_fp8_split(const void* x, int T, int H, const void* w, const float* w_s, int N, int nseg,
+                                    const int* seg_cols_host, void* const* seg_out_host, const int* seg_ld_host, void* ws,
+                                    size_t ws_bytes, int32_t* status, void* stream) {
+  if (!x) return fail(B200_E_ARG, "b200_dense_fp8: null pointer");
+  return dense_split_impl(x, nullptr, nullptr, T, H, w, w_s, N, nseg, seg_cols_host, seg_out_host, seg_ld_host, ws, ws_bytes,
+                          status, stream);
+}
+
+extern "C" int b200_dense_fp8_split_q(const void* xq, const float* xs, int T, int H, const void* w, const float* w_s, int N,
+                                      int nseg, const int* seg_cols_host, void* const* seg_out_host, const int* seg_ld_host,
+                                      int32_t* status, void* stream) {
+  return dense_split_impl(nullptr, xq, xs, T, H, w, w_s, N, nseg, seg_cols_host, seg_out_host, seg_ld_host, nullptr, 0, status,
+                          stream);
 }
 
 extern "C" int b200_dense_fp8(const void* x, int T, int H, const void* w, const float* w_s, int N, void* out, void* ws,

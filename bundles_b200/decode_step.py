@@ -158,6 +158,8 @@ class DecodeStep:
         self.wts = torch.empty(T, K, dtype=torch.float32, device=dev)
         self.gdn_ws = ops.gdn_workspace(Bl, dev)
         self.dense_ws = ops.dense_fp8_workspace(T, 4096, dev)
+        self.hq = torch.empty(T, H, dtype=torch.uint8, device=dev)          # a layer's input rows as e4m3 + scales,
+        self.hs = torch.empty(T, H // 128, dtype=torch.float32, device=dev)  # left by the previous layer's combine + norm
         self.proj_ws = ops.dense_fp8_add_rmsnorm_workspace(T, 4096, H, dev)
         self.gdn_in = [torch.empty(T, wd, dtype=bf, device=dev) for wd in GDN_SPLIT]
         self.lm_ws = ops.lmhead_workspace(Ta if ep is not None else T, H, self.shard_hi - self.shard_lo, dev)
@@ -225,15 +227,18 @@ class DecodeStep:
         return q, s
 
     # ---- the step ----------------------------------------------------------------------------------------------
-    def _mixer(self, L, h):
+    def _mixer(self, L, h, hq=None):
+        """`hq`: the rows of `h` in e4m3 + scales when the kernel that made `h` left them (one launch less)."""
         st = self.status
+        nq = 0 if hq is not None else 1
         if L["attn"]:
             q, gate, k, v = ops.attn_front(h, L["qkv_w"], L["qkv_s"], L["q_norm"], L["k_norm"], self.positions,
-                                           self.cos_sin, 1e-6, True, status=st)
+                                           self.cos_sin, 1e-6, True, status=st, quantised=hq)
             core = ops.attn_verify(q, gate, k, v, L["kcache"], L["vcache"], L["page_table"], self.seqlens,
                                    splits=self.attn_splits, status=st)
-            return core, L["o_w"], L["o_s"], 2 + 3
-        mixed, z, b, a = ops.dense_fp8_split(h, L["in_w"], L["in_s"], GDN_SPLIT, outs=self.gdn_in, ws=self.dense_ws, status=st)
+            return core, L["o_w"], L["o_s"], 1 + nq + 3
+        mixed, z, b, a = ops.dense_fp8_split(h, L["in_w"], L["in_s"], GDN_SPLIT, outs=self.gdn_in, ws=self.dense_ws, status=st,
+                                             quantised=hq)
         if self.gdn_layout == "ring":
             core = ops.gdn_verify_replay(mixed, z, a, b, L["conv_state"], L["conv_w"], L["window"], L["a_log"],
                                          L["dt_bias"], L["state"], L["d_ring"], L["dlo_ring"], L["k_ring"],
@@ -243,7 +248,7 @@ class DecodeStep:
         else:
             core = ops.gdn_verify(mixed, z, a, b, L["conv_state"], L["conv_w"], L["a_log"], L["dt_bias"], L["state"],
                                   self.accepted, L["gdn_norm"], 1e-6, status=st, ws=self.gdn_ws)
-        return core, L["out_w"], L["out_s"], 2 + 2
+        return core, L["out_w"], L["out_s"], 1 + nq + 2
 
     def run(self, x: torch.Tensor):
         """Generator form of `step`: yields the barrier channel at every point where the ranks of an expert-parallel
@@ -254,9 +259,10 @@ class DecodeStep:
         residual = torch.zeros_like(x)
         h = ops.add_rmsnorm(x, residual, self.first_norm)          # residual <- x, h = norm(x)
         n = 1
+        hq = None
         for li, L in enumerate(self.layers):
             rec = None if self.trace is None else dict(h_in=h.clone(), residual_in=residual.clone())
-            core, ow, osc, nl = self._mixer(L, h)
+            core, ow, osc, nl = self._mixer(L, h, hq)
             # output projection (split-K) + residual add + post-attention norm
             proj = torch.empty_like(residual) if rec is not None else None
             h2 = ops.dense_fp8_add_rmsnorm(core, ow, osc, residual, L["post_norm"], 1e-6, proj_out=proj, ws=self.proj_ws, status=st)
@@ -276,7 +282,8 @@ class DecodeStep:
             if rec is not None:
                 rec.update(core=core.clone(), proj=proj, h2=h2.clone(), ids=self.ids.clone(), wts=self.wts.clone(),
                            cache=self.cache.clone(), residual_mid=residual.clone())
-            out, h = ops.moe_combine_norm(self.cache, h2, L["gate_w"], K, residual, L["next_norm"])
+            hq = (self.hq, self.hs)   # the next layer's projection reads these instead of quantising h again
+            out, h = ops.moe_combine_norm(self.cache, h2, L["gate_w"], K, residual, L["next_norm"], quantised=hq)
             n += 1
             if rec is not None:
                 rec.update(moe_out=out.clone(), h_out=h.clone(), residual_out=residual.clone())

@@ -304,10 +304,12 @@ def gdn_ring_fold(checkpoint, d_ring, dlo_ring, k_ring, klo_ring, g_ring, state_
                                         _stream()), "b200_gdn_ring_fold")
 
 
-def attn_front(x, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, eps=1e-6, out_fp8=True, ws=None, status=None):
+def attn_front(x, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, eps=1e-6, out_fp8=True, ws=None, status=None,
+               quantised=None):
     """Fused QKV + gate projection with q/k RMSNorm and partial RoPE (reference: fp8.linear_q followed by
     qk_attn_verify.attn_prefill_front).  Returns (q [T,16,256], gate bf16 [T,16,256], k, v [T,2,256]);
-    q, k, v are uint8 e4m3 codes when out_fp8 else bf16."""
+    q, k, v are uint8 e4m3 codes when out_fp8 else bf16.  `quantised` = (xq, xs) of the same rows as left by
+    `moe_combine_norm(quantised=...)`: the activation quantiser launch is skipped."""
     _need(x, torch.bfloat16, "x", 2)
     _need(w, torch.uint8, "w", 2)
     _need(w_s, torch.float32, "w_s", 2)
@@ -321,6 +323,16 @@ def attn_front(x, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, eps=1e-6, out_
     k = torch.empty(T, 2, 256, dtype=dt, device=x.device)
     v = torch.empty(T, 2, 256, dtype=dt, device=x.device)
     gate = torch.empty(T, 16, 256, dtype=torch.bfloat16, device=x.device)
+    if quantised is not None:
+        xq, xs = quantised
+        _need(xq, torch.uint8, "xq", 2)
+        _need(xs, torch.float32, "xs", 2)
+        if tuple(xq.shape) != (T, 2048) or tuple(xs.shape) != (T, 16):
+            raise B200Error("attn_front: quantised rows must be [T, 2048] and [T, 16]")
+        check(_lib.lib().b200_attn_front_q(_p(xq), _p(xs), T, _p(w), _p(w_s), _p(q_norm_w), _p(k_norm_w), _p(positions),
+                                           _p(cos_sin), cos_sin.shape[0], float(eps), 1 if out_fp8 else 0, _p(q), _p(gate),
+                                           _p(k), _p(v), _p(status), _stream()), "b200_attn_front_q")
+        return q, gate, k, v
     if ws is None:
         n = _lib.lib().b200_attn_front_workspace_bytes(T)
         buf = torch.empty(n + 1024, dtype=torch.uint8, device=x.device)
@@ -332,9 +344,10 @@ def attn_front(x, w, w_s, q_norm_w, k_norm_w, positions, cos_sin, eps=1e-6, out_
     return q, gate, k, v
 
 
-def moe_combine_norm(cache, x, gate_w, top_k, residual, norm_w, eps=1e-6, pos=None, out=None, normed=None):
+def moe_combine_norm(cache, x, gate_w, top_k, residual, norm_w, eps=1e-6, pos=None, out=None, normed=None, quantised=None):
     """Combine with the next layer's input norm folded in (reference: qk_route.combine_norm): `residual` is updated
-    in place to bf16(out + residual); returns (out, normed)."""
+    in place to bf16(out + residual); returns (out, normed).  `quantised` = (xq uint8 [T, H], xs fp32 [T, H/128]):
+    the normed rows are also written there in the e4m3 form that `dense_fp8_split_q` / `attn_front_q` read."""
     _need(cache, torch.bfloat16, "cache", 2)
     _need(x, torch.bfloat16, "x", 2)
     _need(residual, torch.bfloat16, "residual", 2)
@@ -344,6 +357,16 @@ def moe_combine_norm(cache, x, gate_w, top_k, residual, norm_w, eps=1e-6, pos=No
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
     if normed is None:
         normed = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    if quantised is not None:
+        xq, xs = quantised
+        _need(xq, torch.uint8, "xq", 2)
+        _need(xs, torch.float32, "xs", 2)
+        if tuple(xq.shape) != (T, H) or tuple(xs.shape) != (T, H // 128):
+            raise B200Error("moe_combine_norm: quantised outputs must be [T, H] and [T, H/128]")
+        check(_lib.lib().b200_moe_combine_norm_q(_p(cache), _p(x), _p(gate_w), _p(pos), T, H, int(top_k), _p(out),
+                                                 _p(residual), _p(norm_w), float(eps), _p(normed), _p(xq), _p(xs),
+                                                 _stream()), "b200_moe_combine_norm_q")
+        return out, normed
     check(_lib.lib().b200_moe_combine_norm(_p(cache), _p(x), _p(gate_w), _p(pos), T, H, int(top_k), _p(out), _p(residual),
                                            _p(norm_w), float(eps), _p(normed), _stream()), "b200_moe_combine_norm")
     return out, normed
@@ -402,7 +425,7 @@ def dense_fp8(x, w, w_s, out=None, ws=None, status=None):
     return out
 
 
-def dense_fp8_split(x, w, w_s, widths, outs=None, ws=None, status=None):
+def dense_fp8_split(x, w, w_s, widths, outs=None, ws=None, status=None, quantised=None):
     """dense_fp8 with the N output features cut into up to four consecutive segments (`widths`), each written to
     its own contiguous tensor [T, width] (the GDN in_proj's [q k v | z | b | a], dense8.py:64-68)."""
     _need(x, torch.bfloat16, "x", 2)
@@ -417,10 +440,20 @@ def dense_fp8_split(x, w, w_s, widths, outs=None, ws=None, status=None):
         _need(o, torch.bfloat16, "segment output", 2)
         if tuple(o.shape) != (T, wd):
             raise B200Error("dense_fp8_split: a segment output must be [T, width]")
-    if ws is None:
-        ws = dense_fp8_workspace(T, H, x.device)
     cols = (C.c_int * n)(*[int(v) for v in widths])
     lds = (C.c_int * n)(*[int(v) for v in widths])
+    if quantised is not None:   # the rows as left by moe_combine_norm(quantised=...): no activation quantiser launch
+        xq, xs = quantised
+        _need(xq, torch.uint8, "xq", 2)
+        _need(xs, torch.float32, "xs", 2)
+        if tuple(xq.shape) != (T, H) or tuple(xs.shape) != (T, H // 128):
+            raise B200Error("dense_fp8_split: quantised rows must be [T, H] and [T, H/128]")
+        check(_lib.lib().b200_dense_fp8_split_q(_p(xq), _p(xs), T, H, _p(w), _p(w_s), N, n, cols,
+                                                _ptr_array([o.data_ptr() for o in outs]), lds, _p(status), _stream()),
+              "b200_dense_fp8_split_q")
+        return outs
+    if ws is None:
+        ws = dense_fp8_workspace(T, H, x.device)
     check(_lib.lib().b200_dense_fp8_split(_p(x), T, H, _p(w), _p(w_s), N, n, cols, _ptr_array([o.data_ptr() for o in outs]),
                                           lds, _p(ws), ws.numel(), _p(status), _stream()), "b200_dense_fp8_split")
     return outs

@@ -259,6 +259,13 @@ int b200_moe_combine(const void* cache, const void* x, const void* gate_w, const
 int b200_moe_combine_norm(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T, int H,
                           int K, void* out, void* residual, const void* norm_w, float eps, void* normed,
                           void* stream);
+/* The same, and the normed rows also leave in the form the next layer's first projection reads: e4m3 xq_out [T, H] and
+ * scales xs_out fp32 [T, H/128] (per token per 128 channels, scale = max(amax / 448, 1e-12): the arithmetic of the
+ * projections' own activation quantiser, fp8.py:21-34), to be passed to b200_dense_fp8_split_q or b200_attn_front_q.
+ * H == 2048, K <= 12.  (The reference quantises inside its projection kernels.) */
+int b200_moe_combine_norm_q(const void* cache, const void* x, const void* gate_w, const int64_t* pos, int T, int H,
+                            int K, void* out, void* residual, const void* norm_w, float eps, void* normed, void* xq_out,
+                            float* xs_out, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Gated DeltaNet speculative verify.  Replaces qk_gdn_verify.gdn_verify_fused
@@ -360,6 +367,11 @@ int b200_attn_front(const void* x, int T, const void* w, const float* w_s, const
                     const void* k_norm_w, const int64_t* positions, const float* cos_sin, int max_pos, float eps,
                     int out_fp8, void* q, void* gate, void* k, void* v, void* ws, size_t ws_bytes, int32_t* status,
                     void* stream);
+/* The same on rows that are already quantised (xq e4m3 [T, 2048], 16-byte aligned, xs fp32 [T, 16]: the outputs of
+ * b200_moe_combine_norm_q); no workspace, one launch less. */
+int b200_attn_front_q(const void* xq, const float* xs, int T, const void* w, const float* w_s, const void* q_norm_w,
+                      const void* k_norm_w, const int64_t* positions, const float* cos_sin, int max_pos, float eps,
+                      int out_fp8, void* q, void* gate, void* k, void* v, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Decode-width dense projections.  Replace the reference's weight-streaming projections between
@@ -383,6 +395,11 @@ int b200_dense_fp8(const void* x, int T, int H, const void* w, const float* w_s,
 int b200_dense_fp8_split(const void* x, int T, int H, const void* w, const float* w_s, int N, int nseg,
                          const int* seg_cols_host, void* const* seg_out_host, const int* seg_ld_host, void* ws,
                          size_t ws_bytes, int32_t* status, void* stream);
+/* b200_dense_fp8_split on rows that are already quantised (xq e4m3 [T, H], 16-byte aligned, xs fp32 [T, H/128]: the
+ * outputs of b200_moe_combine_norm_q); no workspace, one launch less, the same bits. */
+int b200_dense_fp8_split_q(const void* xq, const float* xs, int T, int H, const void* w, const float* w_s, int N, int nseg,
+                           const int* seg_cols_host, void* const* seg_out_host, const int* seg_ld_host, int32_t* status,
+                           void* stream);
 /* The output projection of a mixer fused with what follows it, as proj.project_add_norm does (proj.py:84-112: split-K
  * partials in fp32, then one kernel that sums them, adds the residual and norms):
  *   proj = bf16(x[T,K] . W[N,K]^T) with the K range cut into parts so that weight tiles x parts fill the GPU (a

@@ -77,3 +77,28 @@ def test_norm_property_full_size():
     for g, r in zip((q, gate, k, v), ref):
         ok, err, nbad = close_bf16(bf16_to_np(g[sl]), r)
         assert ok, (err, nbad)
+
+
+def test_rows_quantised_upstream_give_the_same_bits():
+    # x handed over as e4m3 + scales by the kernel that made it (moe_combine_norm(quantised=...)): the front then skips its
+    # own quantiser; the rows here come from the dense projection's quantiser, which uses the same arithmetic
+    T = 40
+    cfg = synth.attn(seed=97, T=T)
+    d = {k: v.to(dev()) for k, v in cfg.items()}
+    cs = torch.from_numpy(oat.rope_table(4096)).to(dev())
+    K = 10
+    cache = torch.zeros(T * (K + 1), 2048, dtype=torch.bfloat16, device=dev())
+    # residual = x, zero cache, zero norm weight: the normed rows are x * rsqrt(mean x^2 + eps)
+    res = d["x"].clone()
+    xq = torch.empty(T, 2048, dtype=torch.uint8, device=dev())
+    xs = torch.empty(T, 16, dtype=torch.float32, device=dev())
+    _, h = ops.moe_combine_norm(cache, d["x"], None, K, res, torch.zeros(2048, dtype=torch.bfloat16, device=dev()),
+                                quantised=(xq, xs))
+    st = ops.new_status(dev())
+    a = ops.attn_front(h, d["w"], d["w_s"], d["q_norm_w"], d["k_norm_w"], d["positions"], cs, 1e-6, True, status=st)
+    b = ops.attn_front(h, d["w"], d["w_s"], d["q_norm_w"], d["k_norm_w"], d["positions"], cs, 1e-6, True, status=st,
+                       quantised=(xq, xs))
+    torch.cuda.synchronize()
+    assert ops.read_status(st) == 0
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)

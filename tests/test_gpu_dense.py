@@ -116,3 +116,34 @@ def test_add_rmsnorm():
     assert np.array_equal(bf16_to_np(r_dev), rr)
     ok, err, nbad = close_bf16(bf16_to_np(y), ry)
     assert ok, (err, nbad)
+
+
+def test_rows_quantised_by_the_combine_give_the_same_projection_bits():
+    # combine + norm leaves the normed rows also as e4m3 + scales; the projections read those instead of quantising again
+    g = torch.Generator().manual_seed(33)
+    T, H, K = 37, 2048, 10
+    cache = (torch.randn(T * (K + 1), H, generator=g) * 0.3).to(torch.bfloat16).to(dev())
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev())
+    gate_w = (torch.randn(H, generator=g) * 0.02).to(torch.bfloat16).to(dev())
+    norm_w = (torch.randn(H, generator=g) * 0.1).to(torch.bfloat16).to(dev())
+    res_a = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev())
+    res_b = res_a.clone()
+    xq = torch.empty(T, H, dtype=torch.uint8, device=dev())
+    xs = torch.empty(T, H // 128, dtype=torch.float32, device=dev())
+    out_a, h_a = ops.moe_combine_norm(cache, x, gate_w, K, res_a, norm_w)
+    out_b, h_b = ops.moe_combine_norm(cache, x, gate_w, K, res_b, norm_w, quantised=(xq, xs))
+    assert torch.equal(out_a, out_b) and torch.equal(h_a, h_b) and torch.equal(res_a, res_b)
+    widths = (8192, 4096, 32, 32)
+    N = sum(widths)
+    w = torch.randn(N, H, generator=g) * 0.02
+    codes, scales = synth.quant_fp8_blocks(torch.cat([w, torch.zeros((-N) % 128, H)]))
+    codes, scales = codes[:N].contiguous().to(dev()), scales.to(dev())
+    st = ops.new_status(dev())
+    plain = ops.dense_fp8_split(h_a, codes, scales, widths, status=st)
+    pre = ops.dense_fp8_split(h_a, codes, scales, widths, status=st, quantised=(xq, xs))
+    torch.cuda.synchronize()
+    assert ops.read_status(st) == 0
+    for a, b in zip(plain, pre):
+        assert torch.equal(a, b)
+    with pytest.raises(ops.B200Error):
+        ops.moe_combine_norm(cache, x, gate_w, K, res_b, norm_w, quantised=(xq[:, :1024].contiguous(), xs))
