@@ -541,9 +541,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         continue;
       }
       __syncwarp();
-#ifndef B200_EXP_STAMP2
       if (warp == 2 && lane == 0) TRACE(5, tile - t_lo);
-#endif
       const int blk = blk_of(tile);
       if (!WIDE && blk != staged_blk) {  // first tile of a block (dense modes: of a chunk of token rows)
         staged_blk = blk;
@@ -614,9 +612,6 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       if (!ok) break;
       if (warp == 2 && lane == 0) TRACE(3, 3 + 2 * ((tile - t_lo)));
-#ifdef B200_EXP_STAMP2
-      if (warp == 2 && lane == 0) TRACE(5, tile - t_lo);
-#endif
       const int r = mt * MROWS + q * 32 + lane;  // down: this lane also holds output feature r + 128
       if constexpr (DENSE) {
         // plain projection: out[token][feature] = bf16(acc)
