@@ -170,7 +170,7 @@ struct GdnPrepSmem {
 };
 
 template <bool REPLAY>
-__global__ void __launch_bounds__(512) gdn_prep_kernel(const GdnArgs p, float* __restrict__ qk_ws, GdnOps* __restrict__ ops_ws) {
+__global__ void __launch_bounds__(512, 4) gdn_prep_kernel(const GdnArgs p, float* __restrict__ qk_ws, GdnOps* __restrict__ ops_ws) {
   __shared__ GdnPrepSmem sm;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pair = blockIdx.x, b = pair / G_HK, hk = pair - b * G_HK;
