@@ -28,14 +28,103 @@ constexpr int F8_MAXKG = 32;             // k blocks per row of scales held in s
 constexpr int F8_WS_FLOATS = 1024;       // weight block scales of the CTA's first tiles, cached in shared memory
 
 // ---- activation quantisers (quant8_e4m3 / amax8: common.cuh) ----
+// How the expert GEMMs cut their tile sequence over the CTAs: tile = (block, weight tile), weight tile fastest; a tile
+// costs cost_base + 16-row units of its block; CTA j of `grid` takes the tiles whose cost interval starts in
+// [total j / grid, total (j + 1) / grid).  The table of the grid + 1 boundaries is computed once per call by one extra
+// CTA of the activation quantiser's launch, for the gate/up GEMM (table 0) and the down GEMM (table 1), so that a GEMM CTA
+// starts streaming after two short round trips to memory instead of caching and scanning the whole block list (4.9 us
+// before the first load at 516 blocks).  table[0] = -1: no table (more than F8_CACHED blocks).
+struct F8Partition {
+  const int32_t* blk_rows;
+  const int32_t* nblocks;
+  int grid;
+  int mtiles[2], cost_base[2];
+  int32_t* table[2];   // [grid + 1] each
+};
+constexpr int F8_PART_INTS = 160;   // room for grid + 1 boundaries (148 SMs)
+
+__device__ void f8_partition_tiles(const F8Partition& q) {
+  __shared__ int cpre[2][F8_CACHED + 1];
+  __shared__ int wsum[2][8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nblocks = q.nblocks[0];
+  if (nblocks > F8_CACHED || nblocks < 0 || q.grid + 1 > F8_PART_INTS) {
+    if (tid == 0) q.table[0][0] = q.table[1][0] = -1;
+    return;
+  }
+  // thread t owns blocks [4 t, 4 t + 4): F8_CACHED = 4 x 256
+  int nb16[4], sum[2] = {0, 0};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int b = 4 * tid + i;
+    nb16[i] = b < nblocks ? (q.blk_rows[b] + 15) >> 4 : -1;
+    if (nb16[i] >= 0) {
+      sum[0] += q.mtiles[0] * (q.cost_base[0] + nb16[i]);
+      sum[1] += q.mtiles[1] * (q.cost_base[1] + nb16[i]);
+    }
+  }
+  int incl[2] = {sum[0], sum[1]};
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1)
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      const int v = __shfl_up_sync(FULL_MASK, incl[g], o);
+      if (lane >= o) incl[g] += v;
+    }
+  if (lane == 31) {
+    wsum[0][warp] = incl[0];
+    wsum[1][warp] = incl[1];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    int run = incl[g] - sum[g];
+    for (int w = 0; w < warp; ++w) run += wsum[g][w];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (nb16[i] >= 0) {
+        cpre[g][4 * tid + i] = run;
+        run += q.mtiles[g] * (q.cost_base[g] + nb16[i]);
+      }
+    if (4 * tid < nblocks && 4 * tid + 4 >= nblocks) cpre[g][nblocks] = run;   // the owner of the last block
+  }
+  __syncthreads();
+  for (int j = tid; j <= q.grid; j += 256)
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      const int ntiles = nblocks * q.mtiles[g];
+      const long long total = nblocks > 0 ? cpre[g][nblocks] : 0;
+      const long long c = total * j / q.grid;
+      int at = ntiles;
+      if (j == 0) {
+        at = 0;
+      } else if (j < q.grid && c < total) {
+        int lo = 0, hi = nblocks - 1;   // last block with cpre[blk] <= c
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (cpre[g][mid] <= c) lo = mid; else hi = mid - 1;
+        }
+        const int tc = (cpre[g][lo + 1] - cpre[g][lo]) / q.mtiles[g];
+        int within = static_cast<int>((c - cpre[g][lo]) / tc);
+        if (within >= q.mtiles[g]) within = q.mtiles[g] - 1;
+        at = lo * q.mtiles[g] + within;
+      }
+      q.table[g][j] = at;
+    }
+}
+
 // one CTA per token; 16 consecutive threads own one 128-channel group (8 channels each)
 // tokens [shared_lo, shared_lo + shared_n) also get their shared-expert row T*K + t
 __global__ void __launch_bounds__(256) quant_permute_f8_kernel(const bf16* __restrict__ x, int T, int H, int K,
                                                                const int32_t* __restrict__ row_of_pair,
                                                                int shared_lo, int shared_n, uint8_t* __restrict__ xq,
-                                                               float* __restrict__ xs) {
+                                                               float* __restrict__ xs, const F8Partition part) {
   __shared__ int rows[40];
   const int t = blockIdx.x, tid = threadIdx.x;
+  if (t == T) {   // the extra CTA of the expert block's launch: tile boundaries of the two GEMMs that follow
+    f8_partition_tiles(part);
+    return;
+  }
   if (tid < K) rows[tid] = row_of_pair[t * K + tid];
   if (tid == K) rows[K] = (t >= shared_lo && t < shared_lo + shared_n) ? T * K + t : -1;
   __syncthreads();
@@ -111,6 +200,7 @@ struct F8Args {
   // how many CTAs the K range of one (weight tile, row chunk) is spread (1: bf16 outputs when partials is null).
   int ksplit, kparts;
   float* partials;
+  const int32_t* part;   // expert GEMMs: this launch's tile boundaries [grid + 1] (F8Partition), or null
 };
 
 constexpr int MODE_DOWN = 0, MODE_UP = 1, MODE_LM = 2, MODE_DENSE = 3;
@@ -199,6 +289,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tma_prefetch_desc(&tmX);
     tma_prefetch_desc(&tmX64);
   }
+  if (warp == 1) tmem_alloc(tmem_slot, C::TMEM);   // its latency hides behind the list reads below
   // Tiles are (block, weight tile) pairs, weight tile fastest; each CTA takes a contiguous range, so consecutive
   // tiles mostly share their block and its metadata.  Every CTA reads the whole block list into shared memory
   // before the weight stream starts (afterwards a dependent global load costs microseconds: it queues behind
@@ -217,7 +308,23 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   // k blocks of one tile and the first of them (split-K in the dense mode; the whole K otherwise)
   const int kn = DENSE ? p.ksteps / p.ksplit : p.ksteps;
   auto k0_of = [&](int tile) { return DENSE ? ((tile / nblocks) % p.ksplit) * kn : 0; };
-  if (C::LISTS) {
+  bool have_part = false;
+  if (C::LISTS && p.part != nullptr) {
+    // boundaries computed by the quantiser launch of this call: only this CTA's own blocks are cached
+    const int lo = p.part[blockIdx.x], hi = p.part[blockIdx.x + 1];
+    if (p.part[0] == 0 && lo >= 0 && lo <= hi && hi <= ntiles && (blockIdx.x + 1 < gridDim.x || hi == ntiles)) {
+      have_part = true;
+      t_lo = lo;
+      t_hi = hi;
+      const int b_lo = lo / p.mtiles, b_hi = hi > lo ? (hi - 1) / p.mtiles : b_lo - 1;
+      for (int blk = b_lo + static_cast<int>(threadIdx.x); blk <= b_hi && blk < F8_CACHED; blk += C::THREADS) {
+        tinfo[blk * 3 + 0] = p.L.blk_expert[blk];
+        tinfo[blk * 3 + 1] = p.L.blk_row0[blk];
+        tinfo[blk * 3 + 2] = p.L.blk_rows[blk];
+      }
+    }
+  }
+  if (C::LISTS && !have_part) {
     const int ncached = nblocks < F8_CACHED ? nblocks : F8_CACHED;
     for (int blk = threadIdx.x; blk < ncached; blk += C::THREADS) {
       tinfo[blk * 3 + 0] = p.L.blk_expert[blk];
@@ -347,7 +454,6 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     load_ws(t_lo + 1, wsa2, wsb2);
   }
 
-  if (warp == 1) tmem_alloc(tmem_slot, C::TMEM);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -735,11 +841,11 @@ extern "C" int b200_trace_read_cta(unsigned long long* host) {
 
 // x bf16 [T, H] -> e4m3 rows [T, H] + scales [T, H/128] in token order (no permutation)
 void b200_quant_rows_f8_launch(const void* x, int T, int H, uint8_t* xq, float* xs, cudaStream_t st) {
-  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, xq, xs);
+  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, xq, xs, F8Partition{});
 }
 
 struct F8Layout {
-  size_t xq, xs, h, hq, hs, total;
+  size_t xq, xs, h, hq, hs, part, total;
 };
 static F8Layout f8_layout(int T, int H, int I, int K) {
   const size_t rows = static_cast<size_t>(T) * (K + 1);
@@ -751,6 +857,7 @@ static F8Layout f8_layout(int T, int H, int I, int K) {
   l.h = o;  o = up(o + rows * I * 2);
   l.hq = o; o = up(o + rows * I);
   l.hs = o; o = up(o + rows * (I / 128) * 4);
+  l.part = o; o = up(o + 2 * F8_PART_INTS * 4);
   l.total = o;
   return l;
 }
@@ -813,9 +920,25 @@ static int moe_fp8_impl(const void* x, int T, int H, int I, int K, int E_local, 
     shared_lo = ep_rank * ep_tokens_per_rank;
     shared_n = ep_tokens_per_rank;
   }
-  if (stages & B200_MOE_STAGE_QUANT)
-    quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, K, L.row_of_pair, shared_lo, shared_n, xq,
-                                               xs);
+  const int grid = sm_count();
+  // the quantiser's launch carries one extra CTA that cuts the tile sequences of the two GEMMs over their CTAs; a call
+  // without the quantise stage leaves that to every GEMM CTA itself
+  int32_t* part = reinterpret_cast<int32_t*>(base + l.part);
+  const bool with_part = (stages & B200_MOE_STAGE_QUANT) && grid + 1 <= F8_PART_INTS;
+  if (stages & B200_MOE_STAGE_QUANT) {
+    F8Partition q{};
+    q.blk_rows = L.blk_rows;
+    q.nblocks = L.nblocks;
+    q.grid = grid;
+    q.mtiles[0] = I / 128;
+    q.cost_base[0] = 7;
+    q.mtiles[1] = H / 256;
+    q.cost_base[1] = 5;
+    q.table[0] = part;
+    q.table[1] = part + F8_PART_INTS;
+    quant_permute_f8_kernel<<<T + (with_part ? 1 : 0), 256, 0, st>>>(static_cast<const bf16*>(x), T, H, K, L.row_of_pair,
+                                                                    shared_lo, shared_n, xq, xs, q);
+  }
   F8Args a{};
   a.L = L;
   a.E_local = E_local;
@@ -824,11 +947,11 @@ static int moe_fp8_impl(const void* x, int T, int H, int I, int K, int E_local, 
   a.total_rows = rows;
   a.status = status;
   a.test_starve = (stages & B200_MOE_TEST_STARVE) ? 1 : 0;
-  const int grid = sm_count();
   a.mtiles = I / 128;
   a.ksteps = H / 128;
   a.w_rows = 2 * I;
   a.cost_base = 7;   // measured: a 64-row gate/up tile takes 1.36 x the time of a 16-row one
+  a.part = with_part ? part : nullptr;
   a.s_w = w->s13;
   a.s_w_sh = w->shs13;
   a.a_scale = xs;
@@ -842,6 +965,7 @@ static int moe_fp8_impl(const void* x, int T, int H, int I, int K, int E_local, 
   a.ksteps = I / 128;
   a.w_rows = H;
   a.cost_base = 5;
+  a.part = with_part ? part + F8_PART_INTS : nullptr;
   a.s_w = w->s2;
   a.s_w_sh = w->shs2;
   a.a_scale = hs;
@@ -994,7 +1118,7 @@ extern "C" int b200_lmhead_argmax(const void* x, int T, int H, const void* w, co
   const bool wide = dense_wide(T, H);
   if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, wide ? 128 : 64, "lm_head activations"))) return rc;
   // K = 0 routed picks: the "shared expert" row of token t is row t
-  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, xq, xs);
+  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, xq, xs, F8Partition{});
   F8Args a{};
   a.E_local = 1;
   a.mtiles = (V_shard + 127) / 128;
@@ -1113,7 +1237,7 @@ static int dense_split_impl(const void* x, const void* xq_in, const float* xs_in
   if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, H, wide ? 128 : 64, "dense activations"))) return rc;
   if (!pre)
     quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, H, 0, nullptr, 0, T, const_cast<uint8_t*>(xq),
-                                               const_cast<float*>(xs));
+                                               const_cast<float*>(xs), F8Partition{});
   F8Args a{};
   a.E_local = 1;
   a.mtiles = (N + 127) / 128;
@@ -1263,7 +1387,7 @@ extern "C" int b200_dense_fp8_add_rmsnorm(const void* x, int T, int K, const voi
   if ((rc = make_tmap_bytes_2d(&tmX, xq, T, K, 16, "projection activations"))) return rc;
   const bool wide = dense_wide(T, K);
   if ((rc = make_tmap_bytes_2d(&tmX64, xq, T, K, wide ? 128 : 64, "projection activations"))) return rc;
-  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, K, 0, nullptr, 0, T, xq, xs);
+  quant_permute_f8_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(x), T, K, 0, nullptr, 0, T, xq, xs, F8Partition{});
   F8Args a{};
   a.E_local = 1;
   a.mtiles = (N + 127) / 128;
