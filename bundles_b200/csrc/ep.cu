@@ -27,10 +27,13 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
   return v;
 }
 
-// One warp.  Launched without programmatic serialization: it starts when every earlier kernel of the stream
-// has finished, and the next kernel starts when it has.
+// One warp.  Launched with programmatic serialization: the warp may be resident while the kernel before it still runs,
+// but nothing is signalled before the dependency wait has returned (that kernel complete, its stores to the peers
+// performed); the kernel after it may be resident early in the same way and waits at its own top.
 __global__ void __launch_bounds__(32) ep_barrier_kernel(const EpBarrierArgs a) {
   const int lane = threadIdx.x;
+  pdl_wait();
+  pdl_launch();
   // a rank that has already given up on a peer does not wait again (its epoch still advances, so that the
   // ranks stay in step if the host decides to carry on)
   const bool dead = a.status != nullptr && *reinterpret_cast<volatile int32_t*>(a.status) != 0;
@@ -117,7 +120,7 @@ extern "C" int b200_ep_barrier(void* const* peer_flags_host, unsigned long long*
   a.channel = channel;
   a.timeout_ns = timeout_ns;
   a.status = status;
-  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  launch_k(ep_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), a);
   return launch_status("b200_ep_barrier");
 }
 
