@@ -3,14 +3,14 @@
 // epilogues.  The reference has no block-scaled fp8 MoE; the structure follows its int8 twin
 // (qk_moe_prefill_i8.cu:3649-3651, 3905-3945): per 128-k block the MMA chain starts from zero in a
 // TMEM partial buffer and is promoted by the epilogue warps, acc = fma(partial, a_scale * w_scale,
-// acc).  All 512 TMEM columns are partial buffers (8 of 64 columns, 4 of 128 for the up GEMM), so the MMA
-// issuer runs as far ahead as the weight stream allows and the promotions follow back to back instead of
-// paying one MMA -> commit -> wait -> load round trip per block.
+// acc).  All 512 TMEM columns are partial buffers (8 of 64 columns: 2 x 32 in the expert GEMMs, whose blocks have at
+// most 32 rows; 4 of 128 in the dense modes over 128-row chunks), so the MMA issuer runs up to eight k blocks ahead
+// of the promotion warps, which also run the epilogue: a tile's epilogue no longer stalls the weight stream.
 //
 // Orientation as in the int8 kernels: M = 128 weight rows (exactly one weight scale block row),
-// N = 16..64 tokens of one expert, K = 32 bytes per MMA; weights and expert-sorted token rows arrive
-// by 2-D TMA with the 128-byte swizzle.  Final accumulators live in registers (2 x 64 fp32 per thread
-// for gate and up), which is what limits N to 64 here.
+// N = 16 or 32 tokens of one expert (16..128 rows of a chunk in the dense modes), K = 32 bytes per MMA; weights and
+// expert-sorted token rows arrive by 2-D TMA with the 128-byte swizzle.  Final accumulators live in registers
+// (16 + 16 fp32 per thread for the two weight tiles of a stage; 32 in the dense modes).
 #include "common.cuh"
 #include "host.h"
 
@@ -296,7 +296,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   // the stages in flight) and cuts the tile sequence by COST, not by count: a tile with many token rows takes
   // longer (more token bytes, more accumulator columns to promote), and the blocks of one expert, the shared
   // expert above all, are neighbours in the list, so equal counts would hand one CTA all the heavy tiles.
-  // (The dense modes have no lists: their blocks are the 64-row chunks of the token rows, and a tile is
+  // (The dense modes have no lists: their blocks are the 64- or 128-row chunks of the token rows, and a tile is
   // (weight tile, chunk) with the chunk fastest, so the chunks of one weight tile run back to back on one CTA
   // and all but the first find the weight tile in L2.)
   const int nblocks = LM ? (p.total_rows + CH - 1) / CH : p.L.nblocks[0];
@@ -372,7 +372,7 @@ moe_gemm_f8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
 
   auto decode = [&](int tile, int& e, int& row0, int& n, int& mt) -> bool {
-    if (LM) {  // dense: 128 weight rows against one 64-row chunk of the tokens (and one part of K when split)
+    if (LM) {  // dense: 128 weight rows against one chunk of the token rows (and one part of K when split)
       e = 0;
       const int mx = tile / nblocks;
       mt = DENSE ? mx / p.ksplit : mx;
@@ -950,7 +950,7 @@ static int moe_fp8_impl(const void* x, int T, int H, int I, int K, int E_local, 
   a.mtiles = I / 128;
   a.ksteps = H / 128;
   a.w_rows = 2 * I;
-  a.cost_base = 7;   // measured: a 64-row gate/up tile takes 1.36 x the time of a 16-row one
+  a.cost_base = 7;   // a tile costs 7 + 16-row units of its block (a sweep of 1..30 moved the kernel by less than 2 %)
   a.part = with_part ? part : nullptr;
   a.s_w = w->s13;
   a.s_w_sh = w->shs13;
