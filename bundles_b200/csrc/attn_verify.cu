@@ -198,7 +198,9 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0 && ntiles > 0) {  // ---------------- MMA issuer ----------------
       const uint32_t idesc_s = umma_idesc(UMMA_C_F32, UMMA_AB_E4M3, AV_ROWS);   // M = 128 keys, N = 32 rows
-      const uint32_t idesc_o = umma_idesc(UMMA_C_F32, UMMA_AB_F16, AV_D);       // M = 128 rows, N = 256 dims
+      // O^T = V^T . P^T: M = 128 of the 256 dims (two accumulators), N = 32 rows.  With the rows on the M side an MMA
+      // would spend 128 rows' worth of tensor time on 32
+      const uint32_t idesc_o = umma_idesc(UMMA_C_F32, UMMA_AB_F16, AV_ROWS);
       const uint32_t q_base = smem_u32(smem + AV_OFF_Q);
       bool ok = mbar_wait(qfull, 0, abort_flag, p.status, ST_WAIT_FULL);
       auto issue_s = [&](int j) -> bool {
@@ -244,8 +246,10 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {  // 4 x 16 keys
             const int kk = hk * 4 + k4;
-            const uint64_t da = umma_desc_sw128(p_base + hk * (AV_ROWS * 128) + k4 * 32);
-            tc_mma_f16(tmem_base + AV_TM_O, da, umma_desc_sw128(v_base + hk * (AV_D * 128) + k4 * 32), idesc_o, (i | kk) != 0);
+            const uint64_t dp = umma_desc_sw128(p_base + hk * (AV_ROWS * 128) + k4 * 32);
+            const uint32_t vb = v_base + hk * (AV_D * 128) + k4 * 32;
+            tc_mma_f16(tmem_base + AV_TM_O, umma_desc_sw128(vb), dp, idesc_o, (i | kk) != 0);                    // dims 0..127
+            tc_mma_f16(tmem_base + AV_TM_O + AV_ROWS, umma_desc_sw128(vb + 128 * 128), dp, idesc_o, (i | kk) != 0);  // 128..255
           }
           tc_commit(&hfree[hk]);
         }
@@ -314,18 +318,20 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       if (move) l_run *= __shfl_sync(FULL_MASK, alpha, half * 16 + (lane & 15));
       // the P buffer (and O, for a rescale) must be free: P . V of page i - 2 (same buffer) / i - 1 done
       if (i >= 2 && !mbar_wait(&pvdone[b], ph ^ 1u, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) break;
-      if (move && i > 0 && q == 0) {
-        // rows sit on TMEM lanes 0..31 of O: the quadrant-0 warps scale their half of the 256 columns by alpha;
-        // the first page overwrites O instead
+      if (move && i > 0) {
+        // O^T: dims on the TMEM lanes (accumulator a holds dims 128 a + lane), rows on the columns.  This warp scales
+        // the 32 lanes of its quadrant in accumulator `half`, column j by row j's alpha (held by lane j); the first
+        // page overwrites O instead
         if (!mbar_wait(&pvdone[b ^ 1], ((i - 1) >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
-        for (int c = 0; c < 8; ++c) {
-          const uint32_t col = AV_TM_O + half * 128 + c * 16;
+        for (int c = 0; c < 2; ++c) {
+          const uint32_t col = AV_TM_O + half * AV_ROWS + c * 16 + (static_cast<uint32_t>(q * 32) << 16);
           uint32_t v[16];
           tmem_ld16(tmem_base + col, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+          for (int j = 0; j < 16; ++j)
+            v[j] = __float_as_uint(__uint_as_float(v[j]) * __shfl_sync(FULL_MASK, alpha, c * 16 + j));
           tmem_st16(tmem_base + col, v);
         }
         tmem_st_wait();
@@ -367,18 +373,18 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 #pragma unroll
       for (int j = 0; j < 16; ++j) sc_cur[j] = sc_next[j];
     }
-    // ---------------- epilogue: the row sums of the eight warps meet in shared memory; the quadrant-0 warps write
-    // this split's partial (rows on lanes 0..31 of O) ----------------
+    // ---------------- epilogue: the row sums of the eight warps meet in shared memory; every warp writes its 32 dims
+    // (lanes of its quadrant in accumulator `half`) of the 32 rows of this split's partial ----------------
     float* lsum = redm + 3 * 4 * 32;  // [8 warps][16]
     if (lane < 16) lsum[(warp - 2) * 16 + lane] = l_run;
     __syncwarp();
     if (lane == 0) mbar_arrive(&sbar[ntiles & 1]);
-    if (ok && q == 0) {
-      float* po = p.part_o + static_cast<size_t>(cta) * AV_ROWS * AV_D + static_cast<size_t>(lane) * AV_D + half * 128;
+    if (ok) {
+      float* po = p.part_o + static_cast<size_t>(cta) * AV_ROWS * AV_D + half * 128 + q * 32 + lane;   // + row * AV_D
       float* pml = p.part_ml + static_cast<size_t>(cta) * 2 * AV_ROWS;
       if (ntiles == 0) {
-        for (int c = 0; c < 128; c += 4) *reinterpret_cast<float4*>(po + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (half == 0) {
+        for (int j = 0; j < AV_ROWS; ++j) po[static_cast<size_t>(j) * AV_D] = 0.f;
+        if (half == 0 && q == 0) {
           pml[lane] = -INFINITY;
           pml[AV_ROWS + lane] = 0.f;
         }
@@ -387,16 +393,14 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         if (mbar_wait(&pvdone[last & 1], (last >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL) &&
             mbar_wait(&sbar[ntiles & 1], (ntiles >> 1) & 1, abort_flag, p.status, ST_WAIT_STATE)) {
           tc_fence_after();
-          for (int c = 0; c < 8; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t v[16];
-            tmem_ld16(tmem_base + AV_TM_O + half * 128 + c * 16, v);
+            tmem_ld16(tmem_base + AV_TM_O + half * AV_ROWS + c * 16 + (static_cast<uint32_t>(q * 32) << 16), v);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; j += 4)
-              *reinterpret_cast<float4*>(po + c * 16 + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                                         __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+            for (int j = 0; j < 16; ++j) po[static_cast<size_t>(c * 16 + j) * AV_D] = __uint_as_float(v[j]);
           }
-          if (half == 0) {
+          if (half == 0 && q == 0) {
             // row `lane`: its sum lives in the four warps of half lane / 16 (warp index = 4 * half + quadrant slot)
             const int hw = lane >> 4, j = lane & 15;
             float l = 0.f;
