@@ -174,7 +174,10 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   };
 
   if (warp == 0) {
-    if (lane == 0 && ntiles > 0) {  // ---------------- TMA producer ----------------
+    // ---------------- TMA producers: lane 0 streams Q and the K pages, lane 1 the V pages.  One thread for both would
+    // hold the next K page back until a V stage is free, and a V stage is free only after the page of two rounds
+    // back has been converted, which waits for that page's P . V ----------------
+    if (lane == 0 && ntiles > 0) {
       mbar_expect_tx(qfull, AV_QBUF);
       for (int t = 0; t < AV_NT; ++t)
         for (int c = 0; c < 2; ++c)  // the 8 q heads of this kv head for token t: one 8-row swizzle group
@@ -189,6 +192,12 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         mbar_expect_tx(&kfull[st], AV_KTILE);
         tma_load_2d(smem + AV_OFF_K + st * AV_KTILE, &tmK, 0, (page * AV_HKV + h) * AV_PAGE, &kfull[st]);
         tma_load_2d(smem + AV_OFF_K + st * AV_KTILE + AV_KTILE / 2, &tmK, 128, (page * AV_HKV + h) * AV_PAGE, &kfull[st]);
+      }
+    } else if (lane == 1 && ntiles > 0) {
+      for (int i = 0; i < ntiles; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        const int page = page_of(i);
         if (!mbar_wait(&vempty[st], ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) break;
         mbar_expect_tx(&vfull[st], AV_KTILE);
         tma_load_2d(smem + AV_OFF_V8 + st * AV_KTILE, &tmV, 0, (page * AV_HKV + h) * AV_D, &vfull[st]);
@@ -439,9 +448,12 @@ attn_verify_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         const uint32_t hi_delta = sw128(d0, c4 * 2 + 1) - sw128(d0, c4 * 2);  // the pair's second chunk (may be negative)
         const int k0 = c * 16;
         const bool ragged = k0 + 16 > keys_valid;
+        uint4 vin[4];   // the four chunks are requested before the first is converted
+#pragma unroll
+        for (int k = 0; k < 4; ++k) vin[k] = *reinterpret_cast<const uint4*>(sp + k * 8192);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          uint4 v = *reinterpret_cast<const uint4*>(sp + k * 8192);
+          uint4 v = vin[k];
           if (ragged) {
             uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
