@@ -71,3 +71,23 @@ def test_padding_rows_ragged_T_and_block16():
 
 def test_config_t16_e512():
     _check(synth.moe_fp8(), 10)                              # T=16, H=2048, E=512, top-10, I=512
+
+
+def test_more_blocks_than_the_cached_list_give_the_same_bits():
+    # 16-row blocks at 1200 tokens x 512 experts make more than 1024 blocks: every GEMM CTA then cuts the tile sequence
+    # itself by count instead of reading the precomputed boundaries.  A row's arithmetic does not depend on the blocking.
+    cfg = synth.moe_fp8(seed=46, T=1200, E=512)
+    K = 10
+    d = {k: (v.to(dev()) if isinstance(v, torch.Tensor) else v) for k, v in cfg.items()}
+    _, ids, wts = ops.router(d["x"], d["wr"], K, d["bias"])
+    w = ops.MoeW8A8Weights(d["w13"], d["s13"], d["w2"], d["s2"], d["sh13"], d["shs13"], d["sh2"], d["shs2"])
+    status = ops.new_status(dev())
+    outs = []
+    for block_rows in (32, 16):
+        lists = ops.RoutingLists(1200, K, 512, block_rows, dev())
+        ops.build_lists(ids, wts, lists)
+        outs.append((ops.moe_fp8(d["x"], w, lists, status=status).clone(), int(lists.nblocks.item())))
+    torch.cuda.synchronize()
+    assert ops.read_status(status) == 0
+    assert outs[0][1] <= 1024 < outs[1][1], (outs[0][1], outs[1][1])
+    assert torch.equal(outs[0][0], outs[1][0])
